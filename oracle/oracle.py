@@ -1,0 +1,258 @@
+"""ctypes binding of the CPU oracle (``liboracle.so``): TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+Only the test suite, the smoke check and the CPU-baseline / reference legs of the benchmark import
+this module. The CUDA engine (``oxinfer_b200``) never does.
+
+The oracle restates oxinfer's CPU arithmetic (see ``oracle.cpp`` for the per-function citations).
+Parity is pinned against the reference's own known-answer hashes: ``REF_HASHES`` below is the
+table of ``src/ggml.rs:1547-1577`` for the kinds this oracle implements.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "liboracle.so"
+
+# GGUF type ids (src/ggml.rs:42-93)
+F32, F16, Q8_0, Q4_K, Q6_K, BF16, F8E4M3 = 0, 1, 8, 12, 14, 30, 0x1000
+
+# FNV-1a-64 of the f32 bits of dequantize_row(kind, fixture(kind)), from src/ggml.rs:1547-1577.
+REF_HASHES = {
+    BF16: 0x767E77C423088E31,
+    F16: 0xD03C69EE7934955F,
+    F32: 0x8C4157552256808B,
+    Q4_K: 0xDE4DA39C1D9096B2,
+    Q6_K: 0x20A51CC0FEAAE638,
+    Q8_0: 0x3199BE3DEDDF5C1A,
+}
+FIXTURE_ELEMS = 1024  # src/ggml.rs:1535
+
+
+def build(force: bool = False) -> Path:
+    """Compiles ``liboracle.so`` next to this file if it is missing or older than its source."""
+    src = _HERE / "oracle.cpp"
+    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(_HERE), "-B", "liboracle.so"], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(str(_LIB_PATH))
+        sz, vp, i32, u64, f32 = C.c_size_t, C.c_void_p, C.c_int, C.c_uint64, C.c_float
+        sig = {
+            "orc_lcg": (u64, [C.POINTER(u64)]),
+            "orc_block_size": (sz, [i32]),
+            "orc_type_size": (sz, [i32]),
+            "orc_f16_to_f32": (f32, [C.c_uint16]),
+            "orc_f32_to_f16": (C.c_uint16, [f32]),
+            "orc_f32_to_bf16": (C.c_uint16, [f32]),
+            "orc_e4m3_to_f32": (f32, [C.c_uint8]),
+            "orc_f32_to_e4m3": (C.c_uint8, [f32]),
+            "orc_fast_exp": (f32, [f32]),
+            "orc_fnv_f32": (u64, [vp, sz]),
+            "orc_random_blocks": (None, [i32, sz, C.POINTER(u64), vp]),
+            "orc_dequantize_row": (None, [i32, vp, vp, sz]),
+            "orc_matrix_from_mlx_q4": (vp, [vp, vp, vp, sz, sz, sz]),
+            "orc_matrix_gguf": (vp, [i32, vp, sz, sz, vp, sz, sz]),
+            "orc_matrix_free": (None, [vp]),
+            "orc_matrix_bytes": (sz, [vp]),
+            "orc_matrix_dequantize_rows": (None, [vp, sz, sz, vp]),
+            "orc_mlx_dequant_row": (None, [vp, vp, vp, sz, vp, sz]),
+            "orc_matmul_cpu": (None, [vp, vp, sz, vp, i32]),
+            "orc_matmul_prefill": (None, [vp, vp, sz, vp, i32]),
+            "orc_matmul_f64": (None, [vp, vp, sz, vp, i32]),
+            "orc_quantize_act": (None, [vp, sz, sz, vp, vp, vp, vp, vp]),
+            "orc_route_top_k": (None, [vp, sz, sz, vp, vp]),
+            "orc_moe_forward": (None, [vp, vp, sz, sz, sz, vp, sz, vp, vp, sz, vp, i32, i32]),
+            "orc_quantize_act_e4m3": (None, [vp, sz, sz, sz, vp, vp]),
+            "orc_encode_q8_0": (None, [vp, sz, vp]),
+            "orc_encode_q4_k": (None, [vp, sz, vp]),
+            "orc_encode_q6_k": (None, [vp, sz, vp]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray) -> int:
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+def cpu_threads() -> int:
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def block_size(kind: int) -> int:
+    return lib().orc_block_size(kind)
+
+
+def type_size(kind: int) -> int:
+    return lib().orc_type_size(kind)
+
+
+def row_bytes(kind: int, n: int) -> int:
+    return n // block_size(kind) * type_size(kind)
+
+
+def random_blocks(kind: int, nb: int, seed: int) -> tuple[np.ndarray, int]:
+    """``random_blocks`` of src/ggml.rs:1446: returns (bytes, advanced seed)."""
+    out = np.zeros(nb * type_size(kind), dtype=np.uint8)
+    s = C.c_uint64(seed)
+    lib().orc_random_blocks(kind, nb, C.byref(s), _p(out))
+    return out, s.value
+
+
+def fixture(kind: int) -> np.ndarray:
+    """``fixture(kind)`` of src/ggml.rs:1537-1541."""
+    return random_blocks(kind, FIXTURE_ELEMS // block_size(kind), 1000 + kind)[0]
+
+
+def dequantize_row(kind: int, src: np.ndarray, n: int) -> np.ndarray:
+    out = np.zeros(n, dtype=np.float32)
+    assert src.dtype == np.uint8 and src.size == row_bytes(kind, n)
+    lib().orc_dequantize_row(kind, _p(src), _p(out), n)
+    return out
+
+
+def fnv_f32(v: np.ndarray) -> int:
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    return lib().orc_fnv_f32(_p(v), v.size)
+
+
+class Matrix:
+    """A weight matrix as the reference's CPU path holds it (Q4 + offsets, or raw GGUF rows)."""
+
+    def __init__(self, handle: int, n_out: int, n_in: int, keep=()):
+        self.h, self.n_out, self.n_in, self._keep = handle, n_out, n_in, keep
+
+    @classmethod
+    def from_mlx_q4(cls, w: np.ndarray, scales: np.ndarray, biases: np.ndarray, n_out: int, n_in: int, group: int = 64) -> "Matrix":
+        assert w.dtype == np.uint32 and scales.dtype == np.uint16 and biases.dtype == np.uint16
+        assert w.size == n_out * n_in // 8 and scales.size == n_out * n_in // group == biases.size
+        return cls(lib().orc_matrix_from_mlx_q4(_p(w), _p(scales), _p(biases), n_out, n_in, group), n_out, n_in)
+
+    @classmethod
+    def gguf(cls, kind: int, data: np.ndarray, n_out: int, n_in: int, block_scales: np.ndarray | None = None, bs_rows: int = 128,
+             bs_cols: int = 128) -> "Matrix":
+        assert data.dtype == np.uint8 and data.size == n_out * row_bytes(kind, n_in)
+        bs = None if block_scales is None else np.ascontiguousarray(block_scales, dtype=np.float32)
+        return cls(lib().orc_matrix_gguf(kind, _p(data), n_out, n_in, None if bs is None else _p(bs), bs_rows, bs_cols), n_out, n_in)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().orc_matrix_free(self.h)
+            self.h = None
+
+    def bytes(self) -> int:
+        return lib().orc_matrix_bytes(self.h)
+
+    def dequantize_rows(self, r0: int = 0, r1: int | None = None) -> np.ndarray:
+        r1 = self.n_out if r1 is None else r1
+        out = np.zeros((r1 - r0, self.n_in), dtype=np.float32)
+        lib().orc_matrix_dequantize_rows(self.h, r0, r1, _p(out))
+        return out
+
+    def matmul_cpu(self, x: np.ndarray, threads: int | None = None) -> np.ndarray:
+        """The CPU path's own result (int8-activation decode kernels up to 7 rows, f32 GEMM above)."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.n_in)
+        y = np.zeros((x.shape[0], self.n_out), dtype=np.float32)
+        lib().orc_matmul_cpu(self.h, _p(x), x.shape[0], _p(y), threads or cpu_threads())
+        return y
+
+    def matmul_prefill(self, x: np.ndarray, threads: int | None = None) -> np.ndarray:
+        """The f32 prefill-GEMM arithmetic (sequential FMA over k) at any number of rows."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.n_in)
+        y = np.zeros((x.shape[0], self.n_out), dtype=np.float32)
+        lib().orc_matmul_prefill(self.h, _p(x), x.shape[0], _p(y), threads or cpu_threads())
+        return y
+
+    def matmul_f64(self, x: np.ndarray, threads: int | None = None) -> np.ndarray:
+        """f64 product of the bit-exact dequantized weights with x (the definition)."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.n_in)
+        y = np.zeros((x.shape[0], self.n_out), dtype=np.float64)
+        lib().orc_matmul_f64(self.h, _p(x), x.shape[0], _p(y), threads or cpu_threads())
+        return y
+
+
+def mlx_dequant_row(w: np.ndarray, scales: np.ndarray, biases: np.ndarray, group: int, n: int) -> np.ndarray:
+    out = np.zeros(n, dtype=np.float32)
+    lib().orc_mlx_dequant_row(_p(w), _p(scales), _p(biases), group, _p(out), n)
+    return out
+
+
+def quantize_act(x: np.ndarray):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    t, n_in = x.shape
+    bpr = n_in // 32
+    q = np.zeros((t, n_in), np.int8)
+    scales, fsums = np.zeros((t, bpr), np.float32), np.zeros((t, bpr), np.float32)
+    sums, hsums = np.zeros((t, bpr), np.int32), np.zeros((t, 2 * bpr), np.float32)
+    lib().orc_quantize_act(_p(x), t, n_in, _p(q), _p(scales), _p(sums), _p(fsums), _p(hsums))
+    return q, scales, sums, fsums, hsums
+
+
+def route_top_k(logits: np.ndarray, k: int):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    ids, w = np.zeros(k, np.int32), np.zeros(k, np.float32)
+    lib().orc_route_top_k(_p(logits), logits.size, k, _p(ids), _p(w))
+    return ids, w
+
+
+def moe_forward(gate_up: list[Matrix], down: list[Matrix], h: int, inter: int, x: np.ndarray, route_ids: np.ndarray, route_w: np.ndarray,
+                y: np.ndarray | None = None, exact: bool = True, threads: int | None = None) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    t, k = route_ids.shape
+    ids = np.ascontiguousarray(route_ids, dtype=np.int32)
+    w = np.ascontiguousarray(route_w, dtype=np.float32)
+    y = np.zeros((t, h), np.float32) if y is None else np.ascontiguousarray(y, dtype=np.float32).copy()
+    n = len(gate_up)
+    gu = (C.c_void_p * n)(*[m.h for m in gate_up])
+    dn = (C.c_void_p * n)(*[m.h for m in down])
+    lib().orc_moe_forward(C.cast(gu, C.c_void_p), C.cast(dn, C.c_void_p), n, h, inter, _p(x), t, _p(ids), _p(w), k, _p(y),
+                          threads or cpu_threads(), 1 if exact else 0)
+    return y
+
+
+def quantize_act_e4m3(x: np.ndarray, blk: int = 128):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    t, n_in = x.shape
+    nb = (n_in + blk - 1) // blk
+    q, s = np.zeros((t, n_in), np.uint8), np.zeros((t, nb), np.float32)
+    lib().orc_quantize_act_e4m3(_p(x), t, n_in, blk, _p(q), _p(s))
+    return q, s
+
+
+def e4m3_table() -> np.ndarray:
+    return np.array([lib().orc_e4m3_to_f32(b) for b in range(256)], dtype=np.float32)
+
+
+def encode(kind: int, w: np.ndarray) -> np.ndarray:
+    """Synthetic-data encoders (not from the reference, which has no K-quant encoder)."""
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1)
+    out = np.zeros(row_bytes(kind, w.size), dtype=np.uint8)
+    {Q8_0: lib().orc_encode_q8_0, Q4_K: lib().orc_encode_q4_k, Q6_K: lib().orc_encode_q6_k}[kind](_p(w), w.size, _p(out))
+    return out
+
+
+def row_err(y: np.ndarray, r: np.ndarray) -> float:
+    """Worst per-row ``max|y - r| / max|r|`` (src/cuda.rs:1582-1592); rows are the leading axis."""
+    y = np.asarray(y, dtype=np.float64).reshape(r.shape)
+    r = np.asarray(r, dtype=np.float64)
+    num = np.abs(y - r).reshape(r.shape[0], -1).max(axis=1)
+    den = np.maximum(np.abs(r).reshape(r.shape[0], -1).max(axis=1), 1e-30)
+    return float((num / den).max())
