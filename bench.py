@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (the configuration the headline metric is quoted on): GGUF Q4_K prefill dequant-GEMM,
+activations M = 512 tokens x K = 4096 (bf16, N(0,1)), weights N = 14336 x K = 4096 in Q4_K super-blocks
+(f16 d and dmin ~ |N(0, 0.01)|, uniform 6-bit scales / mins, uniform 4-bit quants), f32 output.
+One step = one pass of that matmul over the 512-token batch. Seeded synthetic data.
+
+On N > 1 GPUs the weight rows are sharded (tensor parallel, N / world rows per rank), every rank
+multiplies the same activations by its shard and the outputs are all-gathered over NCCL: total work
+is fixed, so scaling is "strong". Timing is on the device (CUDA events on the launching stream,
+barrier + synchronize on both sides, max over ranks).
+
+Prints ONE JSON line on rank 0. `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the
+same metric through the host-buffer call of the C ABI (b2_matmul: pinned f32 x in, f32 y out, both
+copies inside the timed region); `roofline` is the tensor-core GEMM kernel alone against the measured
+bf16 peak; `cpu_baseline` is the CPU oracle's restatement of the reference's AVX2 prefill path on
+the box's host cores. `--impl reference` times only that CPU path, on the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M_TOK, K_IN, N_OUT = 512, 4096, 14336
+FLOP_PER_STEP = 2.0 * M_TOK * K_IN * N_OUT
+WORKLOAD = "gguf_q4_k_prefill_gemm M=512 K=4096 N=14336 (bf16 activations, f32 output)"
+METRIC = "prefill dequant-GEMM throughput (Q4_K, M=512 K=4096 N=14336)"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_prefill_tflops(threads: int, steps: int, warmup: int):
+    """The reference's CPU prefill path (dequantize 8 rows + f32 FMA tiles, src/kernels.rs:1998-2038)
+    as restated by the oracle, on the full workload, all host threads."""
+    from oracle import oracle as O
+    from oxinfer_b200 import synth
+
+    ref = synth.q4_k(N_OUT, K_IN, 1)
+    m = O.Matrix.gguf(O.Q4_K, ref.data, N_OUT, K_IN)
+    x = synth.activations(M_TOK, K_IN, 2)
+    for _ in range(warmup):
+        m.matmul_cpu(x, threads)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        m.matmul_cpu(x, threads)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    from oracle import oracle as O
+
+    threads = O.cpu_threads()
+    steps = max(1, min(args.steps, 10))
+    warm = max(1, min(args.warmup, 2))
+    times = cpu_prefill_tflops(threads, steps, warm)
+    ms = 1e3 * sum(times) / len(times)
+    v = FLOP_PER_STEP / (ms * 1e-3) / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "path": "CPU: dequantize 8 rows + 8x8 f32 FMA tiles (oracle port of the reference's AVX2 prefill path)"},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": "full workload per step"},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def gemv_extras(be, torch, peaks, steps):
+    """Achieved HBM GB/s of the batch-1 dequant-GEMV kernels (algorithmic bytes / CUDA-event time),
+    rotating over weight copies larger than L2."""
+    from oxinfer_b200 import synth
+
+    out = {}
+    cases = [("mlx4_4096x4096", "mlx4", 4096, 4096), ("q4_k_14336x4096", "q4_k", 14336, 4096), ("q6_k_32064x4096", "q6_k", 32064, 4096),
+             ("f8_e4m3_7168x12288", "f8_e4m3", 7168, 12288)]
+    for name, fmt, n_out, n_in in cases:
+        ref = synth.make(fmt, n_out, n_in, 5)
+        dev0 = be.upload(ref, n_out, n_in)
+        wbytes = dev0.bytes()
+        copies = max(2, min(48, -(-2 * L2_BYTES // wbytes)))
+        devs = [dev0] + [be.upload(ref, n_out, n_in) for _ in range(copies - 1)]
+        x = torch.randn(n_in, device="cuda", dtype=torch.float32)
+        y = torch.empty(n_out, device="cuda", dtype=torch.float32)
+        for i in range(3):
+            be.matvec_dev(devs[i % copies], x, y)
+        torch.cuda.synchronize()
+        n = max(steps, 2 * copies)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for i in range(n):
+            be.matvec_dev(devs[i % copies], x, y)
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) * 1e3 / n
+        algo = wbytes + 4 * n_in + 4 * n_out
+        out[name] = {"us_per_gemv": us, "bytes": algo, "gbs": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peaks["hbm_gbs"],
+                     "launches_per_gemv": 1 if fmt == "f8_e4m3" else 2}
+        for d in devs:
+            d.free()
+    return out
+
+
+def run_b200(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+
+    import oxinfer_b200 as ob
+    from oxinfer_b200 import synth
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = measured_peaks()
+    be = ob.Backend(local_rank)
+    stream = torch.cuda.current_stream()
+    be.set_stream(stream.cuda_stream)
+
+    assert N_OUT % world == 0
+    n_local = N_OUT // world
+    ref = synth.q4_k(n_local, K_IN, 1 + rank)
+    shard_bytes = ref.data.size
+    copies = max(8, -(-2 * L2_BYTES // shard_bytes))  # rotate through > 2 x L2 of weights: every step streams from HBM
+    devs = [be.upload(ref, n_local, K_IN) for _ in range(copies)]
+    x_host = synth.activations(M_TOK, K_IN, 2)
+    x_bf16 = torch.from_numpy(x_host).cuda().to(torch.bfloat16)
+    x_f16 = torch.from_numpy(x_host).cuda().to(torch.float16)
+    ycopies = 4
+    ys = [torch.empty((M_TOK, n_local), device="cuda", dtype=torch.float32) for _ in range(ycopies)]
+    y_full = torch.empty((world, M_TOK, n_local), device="cuda", dtype=torch.float32) if world > 1 else None
+
+    def step(i):
+        y = ys[i % ycopies]
+        ok = be.matmul_dev(devs[i % copies], x_bf16, y)
+        assert ok
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    sync_all()
+    be.check_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    sync_all()
+    launches0 = be.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    sync_all()
+    ms_total = e0.elapsed_time(e1)
+    launches = be.launch_count() - launches0
+    be.check_status()
+
+    # ---- the GEMM kernel alone (f16 activations are used in place: one launch per call) ----
+    n_k = max(args.steps, 20)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_k)]
+    for i in range(3):
+        be.matmul_dev(devs[i % copies], x_f16, ys[i % ycopies])
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(pairs):
+        a.record()
+        be.matmul_dev(devs[i % copies], x_f16, ys[i % ycopies])
+        b.record()
+    torch.cuda.synchronize()
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+    be.check_status()
+
+    # ---- end to end through the host-buffer call (b2_matmul): pinned x in, y out, every step ----
+    xh = torch.from_numpy(x_host).pin_memory()
+    yh = torch.empty((M_TOK, n_local), dtype=torch.float32).pin_memory()
+    xh_np, yh_np = xh.numpy(), yh.numpy()
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(2):
+        assert be.matmul(xh_np, [ob.Job(devs[i % copies], yh_np)])
+    sync_all()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for i in range(e2e_steps):
+        assert be.matmul(xh_np, [ob.Job(devs[i % copies], yh_np)])
+    e3.record()
+    sync_all()
+    e2e_ms_total = e2.elapsed_time(e3)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms_total, e2e_ms_total, kern_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms_total, kern_ms = (float(v) for v in t.cpu())
+
+    if rank == 0:
+        ms = ms_total / args.steps
+        value = FLOP_PER_STEP / (ms * 1e-3) / 1e12
+        e2e_ms = e2e_ms_total / e2e_steps
+        kern_flop = FLOP_PER_STEP / world
+        achieved = kern_flop / (kern_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"tp{world} (weight rows sharded, NCCL all-gather of y)" if world > 1 else "single GPU",
+                       "l2": f"inputs larger than L2: rotating over {copies} weight copies ({copies * shard_bytes / 1e6:.0f} MB) and {ycopies} outputs",
+                       "step": "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel" + (" + all-gather" if world > 1 else "")},
+            "e2e": {"value": FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(xh.numel() * 4), "d2h_bytes_per_step": int(yh.numel() * 4) * world,
+                    "call": "b2_matmul (Backend::matmul): pinned host f32 x in, f32 y out, synchronous"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"kernel": "gemm_q4k_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": None, "us_per_launch": kern_ms * 1e3,
+                         "flop_per_launch": kern_flop, "peak_source": f"bf16 burst, {peaks['source']}"},
+        }
+        if world == 1:
+            from oracle import oracle as O
+
+            threads = O.cpu_threads()
+            times = cpu_prefill_tflops(threads, 2, 1)
+            line["cpu_baseline"] = {"value": FLOP_PER_STEP / min(times) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": "full workload (512 tokens x 14336 rows), best of 2 after 1 warm-up"}
+            try:
+                line["extra"] = {"gemv": gemv_extras(be, torch, peaks, 40)}
+            except Exception as e:  # the headline line must still print
+                line["extra"] = {"gemv_error": str(e)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,149 @@
+/*
+ * b200qmm - C ABI of the B200 (sm_100a) quantized-matmul engine for oxinfer.
+ *
+ * The library is loaded at run time (dlopen / libloading / ctypes); nothing here needs to be
+ * linked when the host program is built. It carries its CUDA runtime statically and finds the
+ * driver (libcuda.so.1) itself on first use, so it loads on machines without a GPU and every
+ * entry point then returns an error instead of crashing.
+ *
+ * Each entry point replaces one method of oxinfer's accelerator boundary, the `Backend` trait of
+ * src/gpu.rs:151-294 as implemented for CUDA in src/cuda.rs; the citation beside each
+ * declaration names the method. Conventions carried over from that trait:
+ *   - nothing panics or aborts across the boundary (src/gpu.rs:158-160): a return of 0 means the
+ *     work was done, > 0 means "declined, run it on the CPU" (B2_DECLINED), < 0 is an error whose
+ *     text b2_last_error returns. In both non-zero cases no output was written.
+ *   - host buffers stay owned by the caller and are only read during the call;
+ *   - weights are uploaded once and referred to by opaque 64-bit handles.
+ *
+ * Matrices are row-major `[n_out][n_in]` ("out x in"), activations `[t][n_in]`, results
+ * `[t][n_out]`, exactly as src/gpu.rs:60-75 lays them out.
+ */
+#ifndef B200QMM_H
+#define B200QMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_OK 0
+#define B2_DECLINED 1
+#define B2_ERR_CUDA (-1)
+#define B2_ERR_ARG (-2)
+#define B2_ERR_NOMEM (-3)
+#define B2_ERR_TIMEOUT (-4)
+
+/* Weight formats. The GGUF ones keep the ids of src/ggml.rs:42-93. */
+#define B2_FMT_MLX4 1      /* MLX affine 4-bit, u32 words + bf16 scale/bias per group (src/quant.rs:518-563) */
+#define B2_FMT_Q8_0 8      /* GGUF Q8_0  (src/ggml.rs:707-712) */
+#define B2_FMT_Q4_K 12     /* GGUF Q4_K  (src/ggml.rs:750-773) */
+#define B2_FMT_Q6_K 14     /* GGUF Q6_K  (src/ggml.rs:774-793) */
+#define B2_FMT_F8E4M3 4096 /* FP8 e4m3fn + f32 block scales (src/ggml.rs:240-293,433-443) */
+
+/* Element types of device-resident activations / results. */
+#define B2_F32 0
+#define B2_BF16 1
+#define B2_F16 2
+
+/* Output modes of a matrix-vector product: the five modes of dmv_out, src/cuda_decode.cu:131-137. */
+#define B2_MODE_STORE 0     /* y = a */
+#define B2_MODE_ADD 1       /* y += a */
+#define B2_MODE_SILU_PAIR 2 /* y = silu(a) * b, b from a second matrix of the same shape */
+#define B2_MODE_GELU_PAIR 3 /* y = gelu_tanh(a) * b */
+#define B2_MODE_ADD_GATED 4 /* y += a * sigmoid(gate[0]) */
+
+typedef struct b2_ctx b2_ctx;
+typedef uint64_t b2_weight;
+
+/* One matmul of a batch sharing the input x: `Job` of src/gpu.rs:60-65. */
+typedef struct {
+    b2_weight w;
+    size_t n_out;
+    float* y; /* host, [t][n_out] */
+} b2_job;
+
+/* One matrix-vector job of `matvec_rows`: `RowsJob` of src/gpu.rs:69-75. `up` = 0 for a plain
+ * product, else y = silu(W x) * (U x). */
+typedef struct {
+    b2_weight w;
+    b2_weight up;
+    size_t n_out;
+    float* y; /* host, [t][n_out] */
+} b2_rows_job;
+
+/* ---- lifetime ---------------------------------------------------------------------------- */
+
+/* Replaces CudaBackend::new(ordinal), src/cuda.rs:448-570: binds device `ordinal` (its primary
+ * context, shared with any other CUDA runtime user in the process) and checks that it is an
+ * sm_100 part. B2_DECLINED when there is no driver, no such device or another architecture. */
+int b2_open(int ordinal, b2_ctx** out);
+void b2_close(b2_ctx* ctx);
+/* Text of the last error on this context (valid until the next call on it). */
+const char* b2_last_error(b2_ctx* ctx);
+/* Library-level error for calls that have no context yet (b2_open). */
+const char* b2_open_error(void);
+/* Kernels are launched on `cuda_stream` (a cudaStream_t / CUstream; NULL = the default stream,
+ * which is what src/cuda.rs:609-629 uses). Host-buffer entry points synchronize that stream. */
+int b2_set_stream(b2_ctx* ctx, void* cuda_stream);
+/* `Backend::stats`, src/cuda.rs:1120-1132: cumulative copy-in / kernel / copy-out time as text. */
+const char* b2_stats(b2_ctx* ctx);
+/* Count of kernel launches issued by this context since it was opened. */
+uint64_t b2_launch_count(b2_ctx* ctx);
+
+/* ---- weights ----------------------------------------------------------------------------- */
+
+/* `Backend::wants`, src/cuda.rs:1134-1136. 1 = offer this matmul, 0 = keep it on the CPU. */
+int b2_wants(b2_ctx* ctx, size_t n_out, size_t n_in, size_t t);
+
+/* `Backend::upload` for WeightRef::Q4 with offsets, src/cuda.rs:640-699, taking the MLX triple as
+ * it is on disk (src/safetensors.rs:767-853): w `[n_out][n_in/8]` u32, scales and biases
+ * `[n_out][n_in/group]` bf16 bits. group must be 64; n_in a multiple of 64. */
+int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in,
+                   size_t group, b2_weight* out);
+/* `Backend::upload` for WeightRef::Gguf (declined by the reference at src/cuda.rs:642): raw GGUF
+ * rows of `fmt` (B2_FMT_Q4_K / Q6_K / Q8_0 / F8E4M3). For F8E4M3, `block_scales` is
+ * `[ceil(n_out/bs_rows)][ceil(n_in/bs_cols)]` f32 (BlockScales, src/ggml.rs:250-256), else NULL. */
+int b2_upload_gguf(b2_ctx* ctx, int fmt, const uint8_t* data, size_t n_out, size_t n_in, const float* block_scales, size_t bs_rows,
+                   size_t bs_cols, b2_weight* out);
+/* Rows [r0, r1) of an uploaded matrix as their own handle sharing the device memory (tensor-
+ * parallel row shards; no counterpart in the reference, which has a single device). */
+int b2_shard_rows(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, b2_weight* out);
+int b2_free_weight(b2_ctx* ctx, b2_weight w);
+size_t b2_weight_bytes(b2_ctx* ctx, b2_weight w);
+
+/* The dequantized f32 values of rows [r0, r1), bit-exact with the reference's CPU decode:
+ * dequantize_rows_q4 (src/quant.rs:586-606) for MLX4, GgufMatrix::dequantize_rows
+ * (src/ggml.rs:409-460) for the GGUF / FP8 formats. `out` is host memory, [r1-r0][n_in]. */
+int b2_dequantize_rows(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, float* out);
+/* Same, into device memory. */
+int b2_dequantize_rows_dev(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, float* out_dev);
+
+/* ---- matmul ------------------------------------------------------------------------------ */
+
+/* `Backend::matmul`, src/cuda.rs:1428-1493: y_j[t][n_out_j] = x[t][n_in] * W_j^T for every job,
+ * host x and y, one submission, synchronous. */
+int b2_matmul(b2_ctx* ctx, const float* x, size_t t, size_t n_in, b2_job* jobs, size_t n_jobs);
+
+/* `Backend::matvec_rows`, src/gpu.rs:165-167 / src/cuda.rs (dmv_* kernels,
+ * src/cuda_decode.cu:139-174): t in 1..4 rows of x against every job, host buffers. */
+int b2_matvec_rows(b2_ctx* ctx, const float* x, size_t t, size_t n_in, b2_rows_job* jobs, size_t n_jobs);
+
+/* Device-resident forms of the two calls above (what a decode plan issues per op,
+ * src/cuda_decode.rs:1233-1410): no copies, no synchronization, launched on the context's stream.
+ * x_dev is [t][n_in] of x_dtype, y_dev is [t][n_out] of y_dtype. */
+int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_dtype, size_t t, void* y_dev, int y_dtype);
+/* One token: y = mode(W x [, U x]). x_dev f32 [n_in]; y_dev f32 [n_out]; gate_dev f32[1] or NULL. */
+int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev);
+
+/* After the caller has synchronized the stream: B2_OK, or B2_ERR_TIMEOUT when a device-side wait of
+ * the tensor-core GEMM ran into its time limit (the kernel then returned early and its output is
+ * not valid). The reference logs a failed launch and returns false (src/cuda.rs:625-628); this is
+ * the same report for the device-resident calls, which do not synchronize themselves. */
+int b2_check_status(b2_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200QMM_H */

@@ -1,0 +1,88 @@
+"""ctypes binding of ``libb200qmm.so``, the C-ABI engine declared in ``include/b200qmm.h``.
+
+There is no CPU fallback anywhere in this package: if the library is missing, or no sm_100 GPU is
+present, the calls raise. Building is explicit (``oxinfer_b200.build()`` or ``make`` in ``csrc``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "libb200qmm.so"
+CSRC = PKG_DIR / "csrc"
+HEADER = PKG_DIR.parent / "include" / "b200qmm.h"
+
+OK, DECLINED, ERR_CUDA, ERR_ARG, ERR_NOMEM, ERR_TIMEOUT = 0, 1, -1, -2, -3, -4
+FMT_MLX4, FMT_Q8_0, FMT_Q4_K, FMT_Q6_K, FMT_F8E4M3 = 1, 8, 12, 14, 4096
+F32, BF16, F16 = 0, 1, 2
+MODE_STORE, MODE_ADD, MODE_SILU_PAIR, MODE_GELU_PAIR, MODE_ADD_GATED = 0, 1, 2, 3, 4
+
+
+class Job(C.Structure):
+    _fields_ = [("w", C.c_uint64), ("n_out", C.c_size_t), ("y", C.c_void_p)]
+
+
+class RowsJob(C.Structure):
+    _fields_ = [("w", C.c_uint64), ("up", C.c_uint64), ("n_out", C.c_size_t), ("y", C.c_void_p)]
+
+
+def build(verbose: bool = False) -> Path:
+    """Compiles every CUDA source for sm_100a into ``libb200qmm.so`` (nvcc cross-compiles without a GPU)."""
+    r = subprocess.run(["make", "-C", str(CSRC), "-j8"], capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        print(r.stdout[-4000:], r.stderr[-4000:])
+    if r.returncode != 0:
+        raise RuntimeError("building libb200qmm.so failed")
+    return LIB_PATH
+
+
+_SIGNATURES = {
+    # name: (restype, argtypes)
+    "b2_open": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "b2_close": (None, [C.c_void_p]),
+    "b2_last_error": (C.c_char_p, [C.c_void_p]),
+    "b2_open_error": (C.c_char_p, []),
+    "b2_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b2_stats": (C.c_char_p, [C.c_void_p]),
+    "b2_launch_count": (C.c_uint64, [C.c_void_p]),
+    "b2_wants": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "b2_upload_mlx4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_upload_gguf": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_shard_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_free_weight": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "b2_weight_bytes": (C.c_size_t, [C.c_void_p, C.c_uint64]),
+    "b2_dequantize_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "b2_dequantize_rows_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "b2_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(Job), C.c_size_t]),
+    "b2_matvec_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(RowsJob), C.c_size_t]),
+    "b2_matmul_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
+    "b2_matvec_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_check_status": (C.c_int, [C.c_void_p]),
+}
+
+_lib = None
+
+
+def exported_names() -> list[str]:
+    """Every function ``include/b200qmm.h`` declares (parsed from the header text)."""
+    import re
+
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b2_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib() -> C.CDLL:
+    """Loads the engine. Raises if it has not been built: nothing in this package computes without it."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: run oxinfer_b200.build() (or make -C {CSRC}); there is no CPU fallback")
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib

@@ -1,0 +1,647 @@
+// Host side of the engine: a C++ mirror of oxinfer's `gpu::Backend` trait for CUDA
+// (src/gpu.rs:151-294, implemented by CudaBackend in src/cuda.rs) and the C ABI over it
+// (include/b200qmm.h). Same method names, argument meaning and error behaviour: a call either does
+// all of its work or none of it, and reports "declined" so that the caller can run the batch on the
+// CPU (src/gpu.rs:158-160, src/model.rs:875-886).
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.h"
+
+namespace b2 {
+
+struct Weight {
+    WeightDev dev{};
+    std::vector<void*> owned;  // device allocations freed with the weight (empty for row shards)
+    size_t bytes = 0;
+};
+
+// A device buffer that only grows.
+struct Scratch {
+    void* p = nullptr;
+    size_t cap = 0;
+    cudaError_t reserve(size_t n) {
+        if (n <= cap) return cudaSuccess;
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+        size_t want = (n + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+        cudaError_t e = cudaMalloc(&p, want);
+        if (e == cudaSuccess) cap = want;
+        return e;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+    }
+};
+
+class Backend {
+  public:
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;  // calls serialize, like the staging lock of src/cuda.rs:430,1443
+    std::string err;
+    std::string stats_text;
+    std::unordered_map<uint64_t, Weight> weights;
+    uint64_t next_handle = 1;
+    uint64_t launches = 0;
+    // staging for the host-buffer entry points
+    Scratch x_dev, y_dev, x16, xplanes, pair_tmp;
+    GemmStatus* gemm_status = nullptr;  // device
+    // one cached activation tensor map (the staging buffer and shape rarely change)
+    GemmPlan* plan = nullptr;
+    const void* plan_x16 = nullptr;
+    size_t plan_t = 0, plan_K = 0, plan_nout = 0;
+    // cumulative times, like Backend::stats (src/cuda.rs:403-409)
+    double ns_in = 0, ns_gpu = 0, ns_out = 0;
+    uint64_t calls = 0;
+
+    int fail(int code, const char* fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        err = buf;
+        return code;
+    }
+    int cuda_fail(cudaError_t e, const char* what) {
+        return fail(e == cudaErrorMemoryAllocation ? B2_ERR_NOMEM : B2_ERR_CUDA, "[b200qmm: %s: %s]", what, cudaGetErrorString(e));
+    }
+    bool bind() { return cudaSetDevice(device) == cudaSuccess; }
+
+    Weight* find(uint64_t h) {
+        auto it = weights.find(h);
+        return it == weights.end() ? nullptr : &it->second;
+    }
+
+    // ---- Backend::wants (src/cuda.rs:1134-1136): the reference offers a matmul to CUDA from 32 tokens
+    // and 1 GFLOP up, n_out % 64 == 0, n_in % 32 == 0. Here every supported shape is worth it (the
+    // weights are resident and a B200 GEMV outruns the host cores by two orders of magnitude), so the
+    // only conditions are the kernels' shape rules.
+    bool wants(size_t n_out, size_t n_in, size_t t) const { return t >= 1 && n_out >= 1 && n_in % 32 == 0; }
+
+    int alloc_copy(const void* host, size_t bytes, void** out, std::vector<void*>& owned) {
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(weight)");
+        owned.push_back(p);
+        if (host && bytes) {
+            e = cudaMemcpyAsync(p, host, bytes, cudaMemcpyHostToDevice, stream);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(weight)");
+        }
+        *out = p;
+        return B2_OK;
+    }
+    void drop(std::vector<void*>& owned) {
+        for (void* p : owned) cudaFree(p);
+        owned.clear();
+    }
+
+    // ---- Backend::upload (src/cuda.rs:640-699)
+    int upload_mlx4(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in, size_t group,
+                    uint64_t* out) {
+        if (!w || !scales || !biases || !out) return fail(B2_ERR_ARG, "[b200qmm: upload_mlx4: null argument]");
+        if (group != 64 || n_in % 64 != 0 || n_out == 0) return fail(B2_DECLINED, "[b200qmm: upload_mlx4: group must be 64 and n_in a multiple of 64]");
+        Weight wt;
+        void *p0, *p1, *p2;
+        int rc;
+        if ((rc = alloc_copy(w, n_out * n_in / 2, &p0, wt.owned)) || (rc = alloc_copy(scales, n_out * (n_in / 64) * 2, &p1, wt.owned)) ||
+            (rc = alloc_copy(biases, n_out * (n_in / 64) * 2, &p2, wt.owned))) {
+            drop(wt.owned);
+            return rc;
+        }
+        cudaStreamSynchronize(stream);
+        wt.dev.fmt = B2_FMT_MLX4;
+        wt.dev.n_out = n_out;
+        wt.dev.n_in = n_in;
+        wt.dev.group = group;
+        wt.dev.p0 = (const uint8_t*)p0;
+        wt.dev.p1 = (const uint8_t*)p1;
+        wt.dev.p2 = (const uint8_t*)p2;
+        wt.bytes = n_out * n_in / 2 + 2 * n_out * (n_in / 64) * 2;
+        *out = next_handle++;
+        weights[*out] = std::move(wt);
+        return B2_OK;
+    }
+
+    int upload_gguf(int fmt, const uint8_t* data, size_t n_out, size_t n_in, const float* bscales, size_t bs_rows, size_t bs_cols,
+                    uint64_t* out) {
+        if (!data || !out || n_out == 0) return fail(B2_ERR_ARG, "[b200qmm: upload_gguf: null argument]");
+        Weight wt;
+        wt.dev.fmt = fmt;
+        wt.dev.n_out = n_out;
+        wt.dev.n_in = n_in;
+        int rc = B2_OK;
+        cudaError_t e = cudaSuccess;
+        if (fmt == B2_FMT_Q4_K) {
+            if (n_in % 256) return fail(B2_DECLINED, "[b200qmm: Q4_K needs n_in %% 256 == 0]");
+            void* p;
+            wt.bytes = n_out * (n_in / 256) * 144;
+            if ((rc = alloc_copy(data, wt.bytes, &p, wt.owned))) return rc;
+            wt.dev.p0 = (const uint8_t*)p;
+        } else if (fmt == B2_FMT_Q6_K) {
+            if (n_in % 256) return fail(B2_DECLINED, "[b200qmm: Q6_K needs n_in %% 256 == 0]");
+            size_t nb = n_out * (n_in / 256);
+            wt.bytes = nb * 210;
+            std::vector<void*> tmp;
+            void *raw, *ql, *qh, *sc, *d;
+            if ((rc = alloc_copy(data, nb * 210, &raw, tmp)) || (rc = alloc_copy(nullptr, nb * 128, &ql, wt.owned)) ||
+                (rc = alloc_copy(nullptr, nb * 64, &qh, wt.owned)) || (rc = alloc_copy(nullptr, nb * 16, &sc, wt.owned)) ||
+                (rc = alloc_copy(nullptr, nb * 2, &d, wt.owned))) {
+                drop(tmp);
+                drop(wt.owned);
+                return rc;
+            }
+            e = launch_repack_q6k((const uint8_t*)raw, n_out, n_in, (uint8_t*)ql, (uint8_t*)qh, (int8_t*)sc, (uint16_t*)d, stream);
+            launches++;
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+            drop(tmp);
+            if (e != cudaSuccess) {
+                drop(wt.owned);
+                return cuda_fail(e, "repack_q6k");
+            }
+            wt.dev.p0 = (const uint8_t*)ql;
+            wt.dev.p1 = (const uint8_t*)qh;
+            wt.dev.p2 = (const uint8_t*)sc;
+            wt.dev.p3 = (const uint8_t*)d;
+        } else if (fmt == B2_FMT_Q8_0) {
+            if (n_in % 32) return fail(B2_DECLINED, "[b200qmm: Q8_0 needs n_in %% 32 == 0]");
+            size_t nb = n_out * (n_in / 32);
+            wt.bytes = nb * 34;
+            std::vector<void*> tmp;
+            void *raw, *qs, *d;
+            if ((rc = alloc_copy(data, nb * 34, &raw, tmp)) || (rc = alloc_copy(nullptr, nb * 32, &qs, wt.owned)) ||
+                (rc = alloc_copy(nullptr, nb * 2, &d, wt.owned))) {
+                drop(tmp);
+                drop(wt.owned);
+                return rc;
+            }
+            e = launch_repack_q8_0((const uint8_t*)raw, n_out, n_in, (int8_t*)qs, (uint16_t*)d, stream);
+            launches++;
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+            drop(tmp);
+            if (e != cudaSuccess) {
+                drop(wt.owned);
+                return cuda_fail(e, "repack_q8_0");
+            }
+            wt.dev.p0 = (const uint8_t*)qs;
+            wt.dev.p1 = (const uint8_t*)d;
+        } else if (fmt == B2_FMT_F8E4M3) {
+            if (n_in % 16) return fail(B2_DECLINED, "[b200qmm: F8E4M3 needs n_in %% 16 == 0]");
+            void* p;
+            wt.bytes = n_out * n_in;
+            if ((rc = alloc_copy(data, n_out * n_in, &p, wt.owned))) return rc;
+            wt.dev.p0 = (const uint8_t*)p;
+            if (bscales) {
+                if (!bs_rows || !bs_cols) {
+                    drop(wt.owned);
+                    return fail(B2_ERR_ARG, "[b200qmm: F8E4M3 block scales need bs_rows, bs_cols > 0]");
+                }
+                size_t ncb = (n_in + bs_cols - 1) / bs_cols, nrb = (n_out + bs_rows - 1) / bs_rows;
+                void* s;
+                if ((rc = alloc_copy(bscales, ncb * nrb * 4, &s, wt.owned))) {
+                    drop(wt.owned);
+                    return rc;
+                }
+                wt.dev.p1 = (const uint8_t*)s;
+                wt.dev.bs_rows = bs_rows;
+                wt.dev.bs_cols = bs_cols;
+                wt.dev.bs_ncb = ncb;
+                wt.bytes += ncb * nrb * 4;
+            }
+        } else {
+            return fail(B2_DECLINED, "[b200qmm: format %d has no device kernels]", fmt);
+        }
+        cudaStreamSynchronize(stream);
+        *out = next_handle++;
+        weights[*out] = std::move(wt);
+        return B2_OK;
+    }
+
+    int shard_rows(uint64_t h, size_t r0, size_t r1, uint64_t* out) {
+        Weight* w = find(h);
+        if (!w || !out) return fail(B2_ERR_ARG, "[b200qmm: shard_rows: unknown weight]");
+        if (r0 >= r1 || r1 > w->dev.n_out) return fail(B2_ERR_ARG, "[b200qmm: shard_rows: bad row range]");
+        Weight s;
+        s.dev = w->dev;
+        s.dev.n_out = r1 - r0;
+        size_t K = w->dev.n_in;
+        switch (w->dev.fmt) {
+            case B2_FMT_MLX4:
+                s.dev.p0 += r0 * K / 2;
+                s.dev.p1 += r0 * (K / 64) * 2;
+                s.dev.p2 += r0 * (K / 64) * 2;
+                break;
+            case B2_FMT_Q4_K: s.dev.p0 += r0 * (K / 256) * 144; break;
+            case B2_FMT_Q6_K:
+                s.dev.p0 += r0 * (K / 2);
+                s.dev.p1 += r0 * (K / 4);
+                s.dev.p2 += r0 * (K / 16);
+                s.dev.p3 += r0 * (K / 256) * 2;
+                break;
+            case B2_FMT_Q8_0:
+                s.dev.p0 += r0 * K;
+                s.dev.p1 += r0 * (K / 32) * 2;
+                break;
+            case B2_FMT_F8E4M3:
+                s.dev.p0 += r0 * K;
+                s.dev.bs_row0 += r0;
+                break;
+        }
+        s.bytes = w->bytes / w->dev.n_out * (r1 - r0);
+        *out = next_handle++;
+        weights[*out] = std::move(s);
+        return B2_OK;
+    }
+
+    int free_weight(uint64_t h) {
+        auto it = weights.find(h);
+        if (it == weights.end()) return fail(B2_ERR_ARG, "[b200qmm: free_weight: unknown weight]");
+        cudaStreamSynchronize(stream);
+        drop(it->second.owned);
+        weights.erase(it);
+        return B2_OK;
+    }
+
+    int dequantize_rows_dev(uint64_t h, size_t r0, size_t r1, float* out_dev) {
+        Weight* w = find(h);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: unknown weight]");
+        if (r0 > r1 || r1 > w->dev.n_out) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: bad row range]");
+        cudaError_t e = launch_dequantize(w->dev, r0, r1 - r0, out_dev, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "dequantize");
+        return B2_OK;
+    }
+
+    int dequantize_rows(uint64_t h, size_t r0, size_t r1, float* out) {
+        Weight* w = find(h);
+        if (!w || !out) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: unknown weight]");
+        if (r0 > r1 || r1 > w->dev.n_out) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: bad row range]");
+        size_t bytes = (r1 - r0) * w->dev.n_in * 4;
+        if (bytes == 0) return B2_OK;
+        cudaError_t e = y_dev.reserve(bytes);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
+        int rc = dequantize_rows_dev(h, r0, r1, (float*)y_dev.p);
+        if (rc) return rc;
+        e = cudaMemcpyAsync(out, y_dev.p, bytes, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "dequantize copy-out");
+        return B2_OK;
+    }
+
+    // One token on the device: activation planes, then the GEMV.
+    int matvec_dev(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
+        Weight* w = find(h);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
+        bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
+        Weight* u = nullptr;
+        if (pair) {
+            u = find(up);
+            if (!u) return fail(B2_ERR_ARG, "[b200qmm: matvec: pair mode needs the second matrix]");
+            if (u->dev.fmt != w->dev.fmt || u->dev.n_in != w->dev.n_in || u->dev.n_out != w->dev.n_out)
+                return fail(B2_DECLINED, "[b200qmm: matvec: the pair's matrices differ in shape or format]");
+        }
+        if (mode < 0 || mode > 4 || (mode == B2_MODE_ADD_GATED && !gate)) return fail(B2_ERR_ARG, "[b200qmm: matvec: bad mode]");
+        if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec: shape not supported by the GEMV kernels]");
+        XPlanes xp{};
+        cudaError_t e;
+        if (w->dev.fmt != B2_FMT_F8E4M3) {
+            e = xplanes.reserve(xplanes_bytes(w->dev.n_in));
+            if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
+            xp = xplanes_at(xplanes.p, w->dev.n_in);
+            e = launch_xplanes(x_dev_, w->dev.n_in, w->dev.fmt == B2_FMT_MLX4, xp, stream);
+            launches++;
+            if (e != cudaSuccess) return cuda_fail(e, "xplanes");
+        }
+        e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "gemv");
+        return B2_OK;
+    }
+
+    int ensure_status() {
+        if (gemm_status) return B2_OK;
+        cudaError_t e = cudaMalloc((void**)&gemm_status, sizeof(GemmStatus));
+        if (e == cudaSuccess) e = cudaMemset(gemm_status, 0, sizeof(GemmStatus));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
+        return B2_OK;
+    }
+
+    // t tokens on the device through the tensor-core GEMM (or token by token through the GEMV).
+    int matmul_dev(uint64_t h, const void* x, int x_dtype, size_t t, void* y, int y_dtype) {
+        Weight* w = find(h);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul: unknown weight]");
+        if (t == 0) return B2_OK;
+        if (y_dtype != B2_F32 && y_dtype != B2_BF16) return fail(B2_ERR_ARG, "[b200qmm: matmul: y must be f32 or bf16]");
+        size_t K = w->dev.n_in;
+        if (t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev)) {
+            for (size_t i = 0; i < t; i++) {
+                int rc = matvec_dev(h, 0, (const float*)x + i * K, (float*)y + i * w->dev.n_out, B2_MODE_STORE, nullptr);
+                if (rc) return rc;
+            }
+            return B2_OK;
+        }
+        if (!gemm_tc_supports(w->dev, t)) return fail(B2_DECLINED, "[b200qmm: matmul: no tensor-core kernel for this format / shape]");
+        int rc = ensure_status();
+        if (rc) return rc;
+        cudaError_t e;
+        const void* xh = x;  // f16 activations are used where they lie (16-byte aligned rows)
+        if (x_dtype != B2_F16 || ((uintptr_t)x & 15)) {
+            e = x16.reserve(t * K * 2);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(x16)");
+            e = launch_to_f16(x, x_dtype, t, t, K, x16.p, stream);
+            launches++;
+            if (e != cudaSuccess) return cuda_fail(e, "to_f16");
+            xh = x16.p;
+        }
+        if (!plan || plan_x16 != xh || plan_t != t || plan_K != K || plan_nout != w->dev.n_out) {
+            if (plan) gemm_tc_plan_destroy(plan);
+            plan = nullptr;
+            char msg[256] = {0};
+            e = gemm_tc_plan_create(w->dev, xh, t, &plan, msg, sizeof msg);
+            if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
+            plan_x16 = xh;
+            plan_t = t;
+            plan_K = K;
+            plan_nout = w->dev.n_out;
+        }
+        e = launch_gemm_tc(plan, w->dev, t, y, y_dtype, gemm_status, sm_count, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "gemm_tc");
+        return B2_OK;
+    }
+
+    // Reads the status word the GEMM writes when a bounded wait gives up (after a synchronize).
+    int check_gemm_status() {
+        if (!gemm_status) return B2_OK;
+        GemmStatus s{};
+        cudaError_t e = cudaMemcpy(&s, gemm_status, sizeof s, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return cuda_fail(e, "status read");
+        if (s.code) {
+            cudaMemset(gemm_status, 0, sizeof s);
+            return fail(B2_ERR_TIMEOUT, "[b200qmm: gemm: a device wait gave up (wait %u, cta %u, k-stage %u)]", s.where, s.cta, s.iter);
+        }
+        return B2_OK;
+    }
+
+    using clk = std::chrono::steady_clock;
+    static double since(clk::time_point t0) { return std::chrono::duration<double, std::nano>(clk::now() - t0).count(); }
+
+    // ---- Backend::matmul (src/cuda.rs:1428-1493)
+    int matmul(const float* x, size_t t, size_t n_in, b2_job* jobs, size_t n_jobs) {
+        if (t == 0 || n_jobs == 0) return B2_OK;
+        if (!x || !jobs) return fail(B2_ERR_ARG, "[b200qmm: matmul: null argument]");
+        size_t max_out = 0;
+        for (size_t j = 0; j < n_jobs; j++) {
+            Weight* w = find(jobs[j].w);
+            if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul: unknown weight in job %zu]", j);
+            if (w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
+                return fail(B2_ERR_ARG, "[b200qmm: matmul: job %zu does not match its weight's shape]", j);
+            bool small = t <= 8 && gemv_supports(w->dev);
+            if (!small && !gemm_tc_supports(w->dev, t)) return fail(B2_DECLINED, "[b200qmm: matmul: job %zu has no kernel at t = %zu]", j, t);
+            max_out = std::max(max_out, jobs[j].n_out);
+        }
+        auto t0 = clk::now();
+        cudaError_t e = x_dev.reserve(t * n_in * 4);
+        if (e == cudaSuccess) e = y_dev.reserve(t * max_out * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
+        e = cudaMemcpyAsync(x_dev.p, x, t * n_in * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-in");
+        ns_in += since(t0);
+        for (size_t j = 0; j < n_jobs; j++) {
+            auto t1 = clk::now();
+            int rc = matmul_dev(jobs[j].w, x_dev.p, B2_F32, t, y_dev.p, B2_F32);
+            if (rc) return rc;
+            e = cudaStreamSynchronize(stream);
+            if (e != cudaSuccess) return cuda_fail(e, "matmul kernels");
+            if ((rc = check_gemm_status())) return rc;
+            ns_gpu += since(t1);
+            auto t2 = clk::now();
+            e = cudaMemcpyAsync(jobs[j].y, y_dev.p, t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+            if (e != cudaSuccess) return cuda_fail(e, "copy-out");
+            ns_out += since(t2);
+        }
+        calls++;
+        return B2_OK;
+    }
+
+    // ---- Backend::matvec_rows (src/gpu.rs:165-167)
+    int matvec_rows(const float* x, size_t t, size_t n_in, b2_rows_job* jobs, size_t n_jobs) {
+        if (t == 0 || n_jobs == 0) return B2_OK;
+        if (t > 4) return fail(B2_DECLINED, "[b200qmm: matvec_rows: at most 4 rows]");
+        if (!x || !jobs) return fail(B2_ERR_ARG, "[b200qmm: matvec_rows: null argument]");
+        size_t max_out = 0;
+        for (size_t j = 0; j < n_jobs; j++) {
+            Weight* w = find(jobs[j].w);
+            if (!w || w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
+                return fail(B2_ERR_ARG, "[b200qmm: matvec_rows: job %zu does not match its weight]", j);
+            if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec_rows: job %zu has no kernel]", j);
+            max_out = std::max(max_out, jobs[j].n_out);
+        }
+        auto t0 = clk::now();
+        cudaError_t e = x_dev.reserve(t * n_in * 4);
+        if (e == cudaSuccess) e = y_dev.reserve(t * max_out * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
+        e = cudaMemcpyAsync(x_dev.p, x, t * n_in * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-in");
+        ns_in += since(t0);
+        for (size_t j = 0; j < n_jobs; j++) {
+            auto t1 = clk::now();
+            for (size_t i = 0; i < t; i++) {
+                int rc = matvec_dev(jobs[j].w, jobs[j].up, (const float*)x_dev.p + i * n_in, (float*)y_dev.p + i * jobs[j].n_out,
+                                    jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE, nullptr);
+                if (rc) return rc;
+            }
+            e = cudaMemcpyAsync(jobs[j].y, y_dev.p, t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+            if (e != cudaSuccess) return cuda_fail(e, "matvec_rows");
+            ns_gpu += since(t1);
+        }
+        calls++;
+        return B2_OK;
+    }
+
+    const char* stats() {
+        char buf[256];
+        snprintf(buf, sizeof buf, "b200qmm: %llu calls, %llu launches, copy-in %.3f ms, gpu %.3f ms, copy-out %.3f ms",
+                 (unsigned long long)calls, (unsigned long long)launches, ns_in * 1e-6, ns_gpu * 1e-6, ns_out * 1e-6);
+        stats_text = buf;
+        return stats_text.c_str();
+    }
+
+    void close() {
+        cudaStreamSynchronize(stream);
+        for (auto& kv : weights) drop(kv.second.owned);
+        weights.clear();
+        x_dev.release();
+        y_dev.release();
+        x16.release();
+        xplanes.release();
+        pair_tmp.release();
+        if (gemm_status) cudaFree(gemm_status);
+        gemm_status = nullptr;
+        if (plan) gemm_tc_plan_destroy(plan);
+        plan = nullptr;
+    }
+};
+
+}  // namespace b2
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+using b2::Backend;
+
+struct b2_ctx {
+    Backend be;
+};
+
+static std::string g_open_error;
+static std::mutex g_open_mu;
+
+#define B2_EXPORT extern "C" __attribute__((visibility("default")))
+#define LOCKED(ctx)                                  \
+    if (!(ctx)) return B2_ERR_ARG;                   \
+    std::lock_guard<std::mutex> lock_((ctx)->be.mu); \
+    if (!(ctx)->be.bind()) return (ctx)->be.fail(B2_ERR_CUDA, "[b200qmm: cudaSetDevice failed]");
+
+B2_EXPORT int b2_open(int ordinal, b2_ctx** out) {
+    std::lock_guard<std::mutex> lock(g_open_mu);
+    if (!out) return B2_ERR_ARG;
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        g_open_error = std::string("[b200qmm: no CUDA device: ") + cudaGetErrorString(e) + "]";
+        cudaGetLastError();
+        return B2_DECLINED;
+    }
+    if (ordinal < 0 || ordinal >= n) {
+        g_open_error = "[b200qmm: no such device ordinal]";
+        return B2_DECLINED;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, ordinal) != cudaSuccess) {
+        g_open_error = "[b200qmm: cudaGetDeviceProperties failed]";
+        return B2_ERR_CUDA;
+    }
+    if (prop.major != 10) {
+        g_open_error = "[b200qmm: device is sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
+                       ", the kernels are built for sm_100a only]";
+        return B2_DECLINED;
+    }
+    if (cudaSetDevice(ordinal) != cudaSuccess) {
+        g_open_error = "[b200qmm: cudaSetDevice failed]";
+        return B2_ERR_CUDA;
+    }
+    b2_ctx* c = new b2_ctx();
+    c->be.device = ordinal;
+    c->be.sm_count = prop.multiProcessorCount;
+    *out = c;
+    return B2_OK;
+}
+
+B2_EXPORT void b2_close(b2_ctx* ctx) {
+    if (!ctx) return;
+    {
+        std::lock_guard<std::mutex> lock(ctx->be.mu);
+        if (ctx->be.bind()) ctx->be.close();
+    }
+    delete ctx;
+}
+
+B2_EXPORT const char* b2_last_error(b2_ctx* ctx) { return ctx ? ctx->be.err.c_str() : "[b200qmm: null context]"; }
+B2_EXPORT const char* b2_open_error(void) { return g_open_error.c_str(); }
+
+B2_EXPORT int b2_set_stream(b2_ctx* ctx, void* s) {
+    LOCKED(ctx);
+    ctx->be.stream = (cudaStream_t)s;
+    return B2_OK;
+}
+
+B2_EXPORT const char* b2_stats(b2_ctx* ctx) {
+    if (!ctx) return "";
+    std::lock_guard<std::mutex> lock(ctx->be.mu);
+    return ctx->be.stats();
+}
+
+B2_EXPORT uint64_t b2_launch_count(b2_ctx* ctx) { return ctx ? ctx->be.launches : 0; }
+
+B2_EXPORT int b2_wants(b2_ctx* ctx, size_t n_out, size_t n_in, size_t t) { return ctx && ctx->be.wants(n_out, n_in, t) ? 1 : 0; }
+
+B2_EXPORT int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in,
+                             size_t group, b2_weight* out) {
+    LOCKED(ctx);
+    return ctx->be.upload_mlx4(w, scales, biases, n_out, n_in, group, out);
+}
+
+B2_EXPORT int b2_upload_gguf(b2_ctx* ctx, int fmt, const uint8_t* data, size_t n_out, size_t n_in, const float* block_scales,
+                             size_t bs_rows, size_t bs_cols, b2_weight* out) {
+    LOCKED(ctx);
+    return ctx->be.upload_gguf(fmt, data, n_out, n_in, block_scales, bs_rows, bs_cols, out);
+}
+
+B2_EXPORT int b2_shard_rows(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, b2_weight* out) {
+    LOCKED(ctx);
+    return ctx->be.shard_rows(w, r0, r1, out);
+}
+
+B2_EXPORT int b2_free_weight(b2_ctx* ctx, b2_weight w) {
+    LOCKED(ctx);
+    return ctx->be.free_weight(w);
+}
+
+B2_EXPORT size_t b2_weight_bytes(b2_ctx* ctx, b2_weight w) {
+    if (!ctx) return 0;
+    std::lock_guard<std::mutex> lock(ctx->be.mu);
+    b2::Weight* p = ctx->be.find(w);
+    return p ? p->bytes : 0;
+}
+
+B2_EXPORT int b2_dequantize_rows(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, float* out) {
+    LOCKED(ctx);
+    return ctx->be.dequantize_rows(w, r0, r1, out);
+}
+
+B2_EXPORT int b2_dequantize_rows_dev(b2_ctx* ctx, b2_weight w, size_t r0, size_t r1, float* out_dev) {
+    LOCKED(ctx);
+    return ctx->be.dequantize_rows_dev(w, r0, r1, out_dev);
+}
+
+B2_EXPORT int b2_matmul(b2_ctx* ctx, const float* x, size_t t, size_t n_in, b2_job* jobs, size_t n_jobs) {
+    LOCKED(ctx);
+    return ctx->be.matmul(x, t, n_in, jobs, n_jobs);
+}
+
+B2_EXPORT int b2_matvec_rows(b2_ctx* ctx, const float* x, size_t t, size_t n_in, b2_rows_job* jobs, size_t n_jobs) {
+    LOCKED(ctx);
+    return ctx->be.matvec_rows(x, t, n_in, jobs, n_jobs);
+}
+
+B2_EXPORT int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_dtype, size_t t, void* y_dev, int y_dtype) {
+    LOCKED(ctx);
+    return ctx->be.matmul_dev(w, x_dev, x_dtype, t, y_dev, y_dtype);
+}
+
+B2_EXPORT int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev) {
+    LOCKED(ctx);
+    return ctx->be.matvec_dev(w, up, x_dev, y_dev, mode, gate_dev);
+}
+
+// Reads (and clears) the status word of the tensor-core GEMM after the caller synchronized the
+// stream: B2_OK, or B2_ERR_TIMEOUT with the place where a bounded device wait gave up.
+B2_EXPORT int b2_check_status(b2_ctx* ctx) {
+    LOCKED(ctx);
+    return ctx->be.check_gemm_status();
+}

@@ -1,0 +1,511 @@
+// Prefill dequant-GEMM for Q4_K weights on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   y[t][n_out] = x[t][K] * W^T,  W in GGUF Q4_K super-blocks (src/ggml.rs:750-773).
+//
+// It replaces the reference's CPU prefill path for GGUF weights (dequantize 8 rows + f32 FMA tiles,
+// src/kernels.rs:1998-2038) and plays the role of gemm_q4a / gemm_body (src/cuda.rs:185-232), which
+// has no GGUF arm at all (src/cuda.rs:1011).
+//
+// One CTA computes a tile of TM = 128 * m_halves tokens x tile_n weight rows over the whole K:
+//   warp 0      : TMA producer. Activation tiles (f16, 64 k x TM tokens, 128-byte swizzle) arrive by
+//                 cp.async.bulk.tensor into a 3-stage ring.
+//   warp 1      : allocates TMEM; one lane issues tcgen05.mma.kind::f16 (M = 128 tokens per
+//                 instruction, N = tile_n weight rows, K = 16), accumulating in TMEM, and frees each
+//                 ring slot with tcgen05.commit.
+//   warps 2..9  : dequantizers. Thread r owns weight row r of the tile: it streams that row's packed
+//                 super-blocks from global memory (16-byte loads, one super-block prefetched ahead in
+//                 registers), expands each 64-group to f16 with packed half2 arithmetic
+//                 (w = d*sc*q - dmin*m) and writes the K-major, 128-byte-swizzled B operand tile.
+//                 After the main loop the same warps read the accumulators back with tcgen05.ld and
+//                 store y.
+// tile_n is chosen on the host (a multiple of 16, at most 256) so that the grid fills the 148 SMs in
+// one wave; the last tile may be ragged. Operands are f16 rather than bf16: Q4_K values carry more
+// than 8 significant bits, and bf16 activations convert to f16 exactly in the range that matters.
+//
+// Every wait is bounded: a wait that exceeds its time limit records where it gave up in a status
+// word, raises a CTA-wide abort flag, and every role then falls through to the common teardown
+// (in-flight copies are awaited, TMEM is freed) so that the kernel always returns.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "kernels.h"
+
+namespace b2 {
+
+namespace {
+
+constexpr int STAGES = 3;
+constexpr int STAGE_K = 64;                // f16 elements per row per stage = one 128-byte swizzle row
+constexpr int A_STAGE_BYTES = 256 * 128;   // up to 256 tokens
+constexpr int B_STAGE_BYTES = 256 * 128;   // up to 256 weight rows
+constexpr int GEMM_THREADS = 320;          // producer warp, MMA warp, 8 dequant / epilogue warps
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct __align__(8) Shared {
+    uint64_t a_full[STAGES];
+    uint64_t b_full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+
+constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(Shared);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait. Returns false when the CTA is aborting or the time limit passed (in which case it
+// records `where` and raises the abort flag). `heed_abort` = false is for the teardown waits.
+__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
+                                       bool heed_abort = true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = globaltimer_ns();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63) == 0) {
+            if (heed_abort && sh->abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                if (atomicCAS(&status->code, 0u, 1u) == 0u) {
+                    status->where = where;
+                    status->cta = blockIdx.x + gridDim.x * blockIdx.y;
+                    status->iter = iter;
+                }
+                sh->abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);         // start address
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Two packed nibble values (16-bit lanes, each 0..15 in its low 4 bits after masking) -> half2 of the
+// integers: OR in the exponent of 1024 (0x6400 | n = 1024 + n exactly), then subtract 1024.
+__device__ __forceinline__ __half2 nib2_to_half2(uint32_t v) {
+    uint32_t h = (v & 0x000F000Fu) | 0x64006400u;
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+    return __hsub2(*reinterpret_cast<__half2*>(&h), k1024);
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+struct Q4kRaw {
+    uint4 hdr;
+    uint4 q[8];
+};
+__device__ __forceinline__ void q4k_load(const uint8_t* blk, Q4kRaw& r) {
+    const uint4* p = (const uint4*)blk;
+    r.hdr = __ldg(p);
+#pragma unroll
+    for (int i = 0; i < 8; i++) r.q[i] = __ldg(p + 1 + i);
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int t, int tile_n, int m_halves, void* __restrict__ y,
+                   int y_dtype, GemmStatus* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_tiles = smem;
+    uint8_t* b_tiles = smem + (size_t)STAGES * A_STAGE_BYTES;
+    Shared* sh = (Shared*)(b_tiles + (size_t)STAGES * B_STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int K = (int)w.n_in;
+    const int nsb = K / 256, nks = nsb * 4;
+    const int n0 = blockIdx.x * tile_n;
+    const int m0 = blockIdx.y * 128 * m_halves;
+    const int n_out = (int)w.n_out;
+    const int ndq_warps = (tile_n + 31) / 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&sh->a_full[s], 1);
+            mbar_init(&sh->b_full[s], (uint32_t)ndq_warps);
+            mbar_init(&sh->empty[s], 1);
+        }
+        mbar_init(&sh->acc_full, 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+            const uint32_t tx_bytes = (uint32_t)(128 * m_halves * 128);
+            int issued = 0;
+            for (int ks = 0; ks < nks; ks++) {
+                int s = ks % STAGES;
+                uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)ks)) break;
+                mbar_arrive_expect_tx(&sh->a_full[s], tx_bytes);
+                tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
+                issued = ks + 1;
+            }
+            if (sh->abort_flag) {
+                // Let the copies still in flight land before the CTA's shared memory is released.
+                for (int ks = max(0, issued - STAGES); ks < issued; ks++)
+                    mbar_wait(&sh->a_full[ks % STAGES], (uint32_t)((ks / STAGES) & 1), sh, status, 2, (uint32_t)ks, false);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(tile_n >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int ks = 0; ks < nks && ok; ks++) {
+                int s = ks % STAGES;
+                uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                if (!mbar_wait(&sh->a_full[s], ph, sh, status, 3, (uint32_t)ks) ||
+                    !mbar_wait(&sh->b_full[s], ph, sh, status, 4, (uint32_t)ks)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                uint32_t a_addr = smem_u32(a_tiles + (size_t)s * A_STAGE_BYTES);
+                uint32_t b_addr = smem_u32(b_tiles + (size_t)s * B_STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < STAGE_K / 16; kk++) {
+                    uint64_t bdesc = smem_desc_sw128(b_addr + kk * 32);
+                    for (int h = 0; h < m_halves; h++) {
+                        uint64_t adesc = smem_desc_sw128(a_addr + h * (128 * 128) + kk * 32);
+                        mma_f16(tmem_base + (uint32_t)(h * 256), adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                mma_commit(&sh->empty[s]);
+            }
+            mma_commit(&sh->acc_full);
+            if (!ok) mbar_wait(&sh->acc_full, 0, sh, status, 5, 0, false);  // drain what was issued before teardown
+        }
+    } else {
+        // ---------------- dequantizers, then epilogue ----------------
+        const int dq_warp = warp - 2;
+        const int r = threadIdx.x - 64;  // weight row of the tile
+        bool ok = true;
+        if (dq_warp < ndq_warps) {
+            const bool row_live = r < tile_n && n0 + r < n_out;
+            const uint8_t* row = w.p0 + (size_t)(row_live ? n0 + r : 0) * (size_t)nsb * 144;
+            Q4kRaw cur, nxt;
+            if (row_live) q4k_load(row, nxt);
+            const uint32_t row_off = (uint32_t)r * 128u;
+            const uint32_t swz = (uint32_t)(r & 7);
+            for (int sb = 0; sb < nsb && ok; sb++) {
+                if (row_live) {
+                    cur = nxt;
+                    if (sb + 1 < nsb) q4k_load(row + (size_t)(sb + 1) * 144, nxt);
+                }
+                float d = 0.f, dmin = 0.f;
+                if (row_live) {
+                    d = __half2float(__ushort_as_half((unsigned short)(cur.hdr.x & 0xffff)));
+                    dmin = __half2float(__ushort_as_half((unsigned short)(cur.hdr.x >> 16)));
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    int ks = sb * 4 + j;
+                    int s = ks % STAGES;
+                    uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                    if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
+                    if (row_live) {
+                        uint32_t sc0, mn0, sc1, mn1;
+                        q4k_scale_min(2 * j, cur.hdr.y, cur.hdr.z, cur.hdr.w, sc0, mn0);
+                        q4k_scale_min(2 * j + 1, cur.hdr.y, cur.hdr.z, cur.hdr.w, sc1, mn1);
+                        const __half2 d1lo = __float2half2_rn(d * (float)sc0), m1lo = __float2half2_rn(-(dmin * (float)mn0));
+                        const __half2 d1hi = __float2half2_rn(d * (float)sc1), m1hi = __float2half2_rn(-(dmin * (float)mn1));
+                        const uint32_t qw[8] = {cur.q[2 * j].x,     cur.q[2 * j].y,     cur.q[2 * j].z,     cur.q[2 * j].w,
+                                                cur.q[2 * j + 1].x, cur.q[2 * j + 1].y, cur.q[2 * j + 1].z, cur.q[2 * j + 1].w};
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            // bytes 8c .. 8c+7 of the group: low nibbles -> k = 8c.., high nibbles -> k = 32 + 8c..
+                            uint32_t p0 = __byte_perm(qw[2 * c], 0, 0x4140), p1 = __byte_perm(qw[2 * c], 0, 0x4342);
+                            uint32_t p2 = __byte_perm(qw[2 * c + 1], 0, 0x4140), p3 = __byte_perm(qw[2 * c + 1], 0, 0x4342);
+                            uint4 lo, hi;
+                            lo.x = h2_bits(__hfma2(nib2_to_half2(p0), d1lo, m1lo));
+                            lo.y = h2_bits(__hfma2(nib2_to_half2(p1), d1lo, m1lo));
+                            lo.z = h2_bits(__hfma2(nib2_to_half2(p2), d1lo, m1lo));
+                            lo.w = h2_bits(__hfma2(nib2_to_half2(p3), d1lo, m1lo));
+                            hi.x = h2_bits(__hfma2(nib2_to_half2(p0 >> 4), d1hi, m1hi));
+                            hi.y = h2_bits(__hfma2(nib2_to_half2(p1 >> 4), d1hi, m1hi));
+                            hi.z = h2_bits(__hfma2(nib2_to_half2(p2 >> 4), d1hi, m1hi));
+                            hi.w = h2_bits(__hfma2(nib2_to_half2(p3 >> 4), d1hi, m1hi));
+                            *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = lo;
+                            *(uint4*)(dst + ((((uint32_t)(c + 4)) ^ swz) << 4)) = hi;
+                        }
+                    } else if (r < tile_n) {
+                        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int c = 0; c < 8; c++) *(uint4*)(dst + (c << 4)) = z;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->b_full[s]);
+                }
+            }
+        }
+        // Epilogue: warp (warp % 4) may touch TMEM lanes 32 (warp % 4) .. +32.
+        const int half = dq_warp >> 2;
+        const int quarter = warp & 3;
+        if (half < m_halves) {
+            bool acc_ok = mbar_wait(&sh->acc_full, 0, sh, status, 7, 0) && !sh->abort_flag;
+            acc_ok = __all_sync(0xffffffffu, acc_ok);
+            if (acc_ok) {
+                tc_fence_after();
+                const int token = m0 + half * 128 + quarter * 32 + lane;
+                const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
+                for (int c0 = 0; c0 < tile_n; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr0 + (uint32_t)c0, v);
+                    if (token < t) {
+                        int n = n0 + c0;
+                        if (y_dtype == B2_F32) {
+                            float* o = (float*)y + (size_t)token * n_out + n;
+                            if (n + 16 <= n_out && (n_out & 3) == 0) {
+#pragma unroll
+                                for (int i = 0; i < 4; i++)
+                                    ((float4*)o)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; i++)
+                                    if (n + i < n_out) o[i] = __uint_as_float(v[i]);
+                            }
+                        } else {
+                            __nv_bfloat16* o = (__nv_bfloat16*)y + (size_t)token * n_out + n;
+                            if (n + 16 <= n_out && (n_out & 7) == 0) {
+                                uint32_t pk[8];
+#pragma unroll
+                                for (int i = 0; i < 8; i++) {
+                                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                                    pk[i] = *reinterpret_cast<uint32_t*>(&b);
+                                }
+                                ((uint4*)o)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                                ((uint4*)o)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; i++)
+                                    if (n + i < n_out) o[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+template <typename T>
+__global__ void to_f16_kernel(const T* __restrict__ x, size_t n, __half* __restrict__ out) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 4 <= n) {
+        float f[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) f[k] = (float)x[i + k];
+        __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&a);
+        o.y = *reinterpret_cast<uint32_t*>(&b);
+        *(uint2*)(out + i) = o;
+    } else {
+        for (; i < n; i++) out[i] = __float2half_rn((float)x[i]);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+}  // namespace
+
+struct GemmPlan {
+    CUtensorMap tmap_x;
+    const void* x16;
+    size_t t, K;
+    int tile_n, m_halves, n_tiles, m_tiles;
+};
+
+bool gemm_tc_supports(const WeightDev& w, size_t t) {
+    return w.fmt == B2_FMT_Q4_K && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
+}
+
+// Tile width (weight rows per CTA): the multiple of 16 up to 256 that minimizes the time of the
+// slowest SM, i.e. waves * tile_n, over the grid ceil(n_out / tile_n) * m_tiles.
+static int pick_tile_n(size_t n_out, int m_tiles, int sm_count) {
+    // B2_GEMM_TILE_N forces a width (tests and tuning sweeps).
+    if (const char* env = getenv("B2_GEMM_TILE_N")) {
+        int v = atoi(env);
+        if (v >= 16 && v <= 256 && v % 16 == 0) return v;
+    }
+    int best = 256;
+    double best_cost = 1e30;
+    for (int tn = 256; tn >= 64; tn -= 16) {
+        size_t tiles = (n_out + tn - 1) / tn * (size_t)m_tiles;
+        size_t waves = (tiles + sm_count - 1) / sm_count;
+        double cost = (double)waves * (tn + 24);  // + fixed per-tile overhead, in units of rows
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = tn;
+        }
+    }
+    return best;
+}
+
+cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, GemmPlan** out, char* err, size_t errlen) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
+        return cudaErrorNotSupported;
+    }
+    GemmPlan* p = new GemmPlan();
+    p->x16 = x16;
+    p->t = t;
+    p->K = w.n_in;
+    p->m_halves = t > 128 ? 2 : 1;
+    int tm = 128 * p->m_halves;
+    p->m_tiles = (int)((t + tm - 1) / tm);
+    int sm_count = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count);
+    p->n_tiles = (int)((w.n_out + p->tile_n - 1) / p->tile_n);
+    cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)t};
+    cuuint64_t strides[1] = {(cuuint64_t)w.n_in * 2};
+    cuuint32_t box[2] = {(cuuint32_t)STAGE_K, (cuuint32_t)tm};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&p->tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(err, errlen, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        delete p;
+        return cudaErrorInvalidValue;
+    }
+    *out = p;
+    return cudaSuccess;
+}
+
+void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
+
+cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
+                           cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
+    gemm_q4k_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, w, (int)t, p->tile_n, p->m_halves, y, y_dtype, status_dev);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t /*t_pad*/, size_t K, void* x16, cudaStream_t st) {
+    size_t n = t * K;
+    unsigned grid = (unsigned)((n / 4 + 256) / 256);
+    if (x_dtype == B2_F32)
+        to_f16_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, (__half*)x16);
+    else if (x_dtype == B2_BF16)
+        to_f16_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, n, (__half*)x16);
+    else if (x_dtype == B2_F16)
+        return cudaMemcpyAsync(x16, x, n * 2, cudaMemcpyDeviceToDevice, st);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+}  // namespace b2

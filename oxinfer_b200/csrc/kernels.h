@@ -1,0 +1,62 @@
+// Host-callable launchers of the CUDA kernels (one translation unit per kernel family).
+#pragma once
+#include "formats.cuh"
+
+namespace b2 {
+
+// ---- dq.cu: bit-exact dequantization --------------------------------------------------------
+// Rows [r0, r0 + nrows) of `w` to f32, row-major [nrows][n_in].
+cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st);
+// Raw GGUF Q6_K / Q8_0 rows (device) -> the split planes described in formats.cuh.
+cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uint8_t* ql, uint8_t* qh, int8_t* sc, uint16_t* d,
+                              cudaStream_t st);
+cudaError_t launch_repack_q8_0(const uint8_t* raw, size_t n_out, size_t n_in, int8_t* qs, uint16_t* d, cudaStream_t st);
+
+// ---- gemv.cu: one-token dequant matrix-vector products ---------------------------------------
+// Activation vector split into three int8 planes per block of 32 (x ~= xs * (q0 + 128 q1 + 16384 q2),
+// 21 significant bits per block), plus block scales and sums. Sizes in bytes for n_in = K:
+//   planes 3K | xs 4K/32 | xsum 4K/32 | v16 4K/16
+struct XPlanes {
+    int8_t* planes;   // [3][K]
+    float* xs;        // [K/32]  block scale
+    float* xsum;      // [K/32]  xs * sum of the block's integers (the quantized block sum)
+    int32_t* v16;     // [K/16]  integer sums of each 16 elements
+};
+__host__ __device__ inline size_t xplanes_bytes(size_t K) { return 3 * K + 4 * (K / 32) * 2 + 4 * (K / 16); }
+inline XPlanes xplanes_at(void* base, size_t K) {
+    XPlanes p;
+    uint8_t* b = (uint8_t*)base;
+    p.planes = (int8_t*)b;
+    p.xs = (float*)(b + 3 * K);
+    p.xsum = p.xs + K / 32;
+    p.v16 = (int32_t*)(p.xsum + K / 32);
+    return p;
+}
+// perm8 = 1 stores each run of 8 elements as [0,2,4,6,1,3,5,7] (the MLX nibble order).
+cudaError_t launch_xplanes(const float* x, size_t K, int perm8, XPlanes out, cudaStream_t st);
+// y[n_out] = mode(W x [, U x]). `xp` must have been prepared with perm8 = (w.fmt == MLX4); the
+// FP8 kernel reads `x` (f32) directly and ignores `xp`.
+cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
+                        int sm_count, cudaStream_t st);
+// Whether launch_gemv handles this format and shape.
+bool gemv_supports(const WeightDev& w);
+
+// ---- gemm_tc.cu: prefill dequant-GEMM on tcgen05 ------------------------------------------------
+struct GemmStatus {   // written by the kernel when a bounded wait gives up
+    uint32_t code;    // 0 = ok
+    uint32_t where;   // which wait
+    uint32_t cta;
+    uint32_t iter;
+};
+bool gemm_tc_supports(const WeightDev& w, size_t t);
+// y[t][n_out] (f32 or bf16) = x[t][n_in] (f16, row-major, t padded by the caller to a multiple of
+// 256 rows in `x16`) * W^T. `tmap_x` is the host-encoded tensor map of x16 (see make_tmap_x).
+struct GemmPlan;
+cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t_pad, GemmPlan** out, char* err, size_t errlen);
+void gemm_tc_plan_destroy(GemmPlan* p);
+cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int sm_count,
+                           cudaStream_t st);
+// x (f32 / bf16 / f16, [t][K]) -> f16 [t_pad][K], pad rows zeroed.
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t t_pad, size_t K, void* x16, cudaStream_t st);
+
+}  // namespace b2

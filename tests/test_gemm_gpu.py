@@ -1,0 +1,95 @@
+"""Prefill dequant-GEMM (tcgen05) on the GPU against the pinned CPU oracle, through the C ABI.
+
+Bound: max relative error per output row 1e-3 against the f64 product of the bit-exact dequantized
+weights; the reference's CPU prefill path (f32 FMA GEMM, src/kernels.rs:1998-2038) is compared too.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oxinfer_b200 as ob
+from oracle import oracle as O
+from oxinfer_b200 import synth
+
+from util import make_pair, row_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 9), (512, 512, 64), (1000, 1024, 130), (208, 4096, 128), (2048, 2048, 300), (4096, 768, 512)])
+def test_q4k_matmul_matches_oracle(backend, shape):
+    n_out, n_in, t = shape
+    ref, m = make_pair("q4_k", n_out, n_in, 400 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 401)
+    y = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert np.isfinite(y).all()
+    exact = m.matmul_f64(x)
+    err = row_err(y, exact)
+    assert err < TOL, err
+    assert row_err(y, m.matmul_cpu(x)) < TOL  # the reference CPU path's own f32 result
+
+
+def test_q4k_matmul_two_jobs_share_x_and_stats(backend):
+    n_in, t = 1024, 96
+    refs = [make_pair("q4_k", n, n_in, 410 + n) for n in (384, 640)]
+    devs = [backend.upload(r, n, n_in) for (r, _), n in zip(refs, (384, 640))]
+    x = synth.activations(t, n_in, 411)
+    ys = [np.zeros((t, n), np.float32) for n in (384, 640)]
+    before = backend.launch_count()
+    assert backend.matmul(x, [ob.Job(d, y) for d, y in zip(devs, ys)])
+    assert backend.launch_count() > before
+    for (_, m), y in zip(refs, ys):
+        assert row_err(y, m.matmul_f64(x)) < TOL
+    assert "launches" in backend.stats()
+
+
+def test_q4k_matmul_dev_bf16_in_bf16_out(backend):
+    n_out, n_in, t = 1024, 2048, 256
+    ref, m = make_pair("q4_k", n_out, n_in, 420)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 421)
+    xd = torch.from_numpy(x).cuda().to(torch.bfloat16)  # exact: the values are bf16-representable
+    yd = torch.empty((t, n_out), device="cuda", dtype=torch.bfloat16)
+    backend.set_stream(torch.cuda.current_stream().cuda_stream)
+    assert backend.matmul_dev(dev, xd, yd)
+    torch.cuda.synchronize()
+    backend.check_status()
+    backend.set_stream(0)
+    exact = m.matmul_f64(x)
+    assert row_err(yd.float().cpu().numpy(), exact) < 6e-3  # bf16 output rounding (2^-9) on top
+    yf = torch.empty((t, n_out), device="cuda", dtype=torch.float32)
+    assert backend.matmul_dev(dev, xd, yf)
+    torch.cuda.synchronize()
+    assert row_err(yf.cpu().numpy(), exact) < TOL
+
+
+def test_q4k_matmul_full_size_config(backend):
+    """M = 512, K = 4096, N = 14336: the benchmark's shape, checked on 16 of its token rows against
+    the oracle and on all rows by linearity: matmul(a x1 + b x2) = a matmul(x1) + b matmul(x2)."""
+    n_out, n_in, t = 14336, 4096, 512
+    ref, m = make_pair("q4_k", n_out, n_in, 430)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 431)
+    y = np.zeros((t, n_out), np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    rows = np.arange(0, t, 32)
+    exact = m.matmul_f64(x[rows])
+    assert row_err(y[rows], exact) < TOL
+    # size-independent property: rows 0..255 and 256..511 summed as inputs give the summed outputs.
+    # Powers of two keep a x1 + b x2 exactly representable in f16, so only accumulation order differs.
+    x2 = (0.5 * x[:256] + 0.25 * x[256:]).astype(np.float32)
+    y2 = np.zeros((256, n_out), np.float32)
+    assert backend.matmul(x2, [ob.Job(dev, y2)])
+    assert row_err(y2, 0.5 * y[:256].astype(np.float64) + 0.25 * y[256:].astype(np.float64)) < 1e-4
+
+
+def test_matmul_declines_formats_without_a_tensor_core_kernel(backend):
+    n_out, n_in, t = 256, 512, 64
+    ref, _ = make_pair("q6_k", n_out, n_in, 440)
+    dev = backend.upload(ref, n_out, n_in)
+    y = np.full((t, n_out), 7.0, np.float32)
+    assert backend.matmul(synth.activations(t, n_in, 441), [ob.Job(dev, y)]) is False
+    assert (y == 7.0).all()  # declined: nothing written (src/gpu.rs:158-160)

@@ -1,0 +1,112 @@
+"""Batch-1 dequant matrix-vector products on the GPU against the pinned CPU oracle.
+
+Bound: max relative error per output row 1e-3 against the f64 product of the bit-exact dequantized
+weights (the definition the reference's own CUDA tests use, src/cuda.rs:1594-1602, 2285-2307, where
+the bound is 1e-5 for matvecs). The kernels are expected to be far inside it; the tighter figure is
+asserted too so that a precision regression shows.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oxinfer_b200 as ob
+from oracle import oracle as O
+from oxinfer_b200 import synth
+
+from util import FORMATS, make_pair, row_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3        # the stated bound
+TIGHT = 2e-5      # what the kernels actually achieve (x is carried with 21 bits per block of 32)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("shape", [(64, 256), (1000, 2048), (1536, 768), (4096, 4096), (37, 14336)])
+def test_matvec_rows_matches_oracle(backend, fmt, shape):
+    n_out, n_in = shape
+    ref, m = make_pair(fmt, n_out, n_in, 300 + n_out)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(1, n_in, 301)
+    # not bf16-representable values too: the planes must carry full f32 inputs
+    x = (x * np.float32(1.2345)).astype(np.float32)
+    y = np.zeros((1, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev, y)])
+    exact = m.matmul_f64(x)
+    err = row_err(y, exact)
+    assert err < TOL and err < TIGHT, err
+    # distance to the reference's int8-activation CPU decode result: informational, ~1e-3..1e-2
+    if fmt != "f8_e4m3":
+        assert row_err(y, m.matmul_cpu(x)) < 3e-2
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_matvec_rows_up_to_four_rows_and_silu_pair(backend, fmt):
+    n_out, n_in = 512, 1024
+    ref_g, mg = make_pair(fmt, n_out, n_in, 310)
+    ref_u, mu = make_pair(fmt, n_out, n_in, 311)
+    dg, du = backend.upload(ref_g, n_out, n_in), backend.upload(ref_u, n_out, n_in)
+    x = synth.activations(4, n_in, 312)
+    y = np.zeros((4, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dg, y)])
+    assert row_err(y, mg.matmul_f64(x)) < TIGHT
+    one = np.zeros((1, n_out), np.float32)
+    for i in range(4):  # each row equals the one-token result bit for bit (src/cuda_decode.cu:176-179)
+        assert backend.matvec_rows(x[i : i + 1], [ob.RowsJob(dg, one)])
+        assert np.array_equal(one[0], y[i])
+    yp = np.zeros((4, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dg, yp, up=du)])
+    g, u = mg.matmul_f64(x), mu.matmul_f64(x)
+    want = g / (1.0 + np.exp(-g)) * u
+    assert row_err(yp, want) < 1e-4
+    assert not backend.matvec_rows(np.zeros((5, n_in), np.float32), [ob.RowsJob(dg, np.zeros((5, n_out), np.float32))])  # > 4 rows: declined
+
+
+def test_matvec_dev_modes(backend):
+    n_out, n_in = 256, 512
+    ref, m = make_pair("q4_k", n_out, n_in, 320)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(1, n_in, 321)
+    a = m.matmul_f64(x)[0]
+    xd = torch.from_numpy(x[0]).cuda()
+    base = torch.linspace(-1, 1, n_out, device="cuda", dtype=torch.float32)
+    y = base.clone()
+    assert backend.matvec_dev(dev, xd, y, ob.MODE_ADD)
+    torch.cuda.synchronize()
+    assert row_err(y.cpu().numpy()[None], (a + base.cpu().numpy().astype(np.float64))[None]) < 1e-5
+    gate = torch.tensor([0.3], device="cuda")
+    y = base.clone()
+    assert backend.matvec_dev(dev, xd, y, ob.MODE_ADD_GATED, gate=gate)
+    torch.cuda.synchronize()
+    want = base.cpu().numpy().astype(np.float64) + a / (1 + np.exp(-0.3))
+    assert row_err(y.cpu().numpy()[None], want[None]) < 1e-5
+    y = torch.zeros(n_out, device="cuda")
+    assert backend.matvec_dev(dev, xd, y, ob.MODE_GELU_PAIR, up=dev)
+    torch.cuda.synchronize()
+    gelu = 0.5 * a * (1 + np.tanh(0.7978845608 * (a + 0.044715 * a**3)))
+    assert row_err(y.cpu().numpy()[None], (gelu * a)[None]) < 1e-4
+
+
+def test_matvec_zero_and_extreme_inputs(backend):
+    """All-zero blocks (scale 0) and one huge element per block keep the planes exact enough."""
+    n_out, n_in = 128, 1024
+    ref, m = make_pair("mlx4", n_out, n_in, 330)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(1, n_in, 331)
+    x[0, 64:128] = 0.0
+    x[0, 200] = 3000.0
+    y = np.zeros((1, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev, y)])
+    assert row_err(y, m.matmul_f64(x)) < TIGHT
+    x[:] = 0
+    assert backend.matvec_rows(x, [ob.RowsJob(dev, y)]) and not y.any()
+
+
+def test_matmul_small_t_uses_gemv_for_every_format(backend):
+    for fmt in FORMATS:
+        n_out, n_in = 200, 512
+        ref, m = make_pair(fmt, n_out, n_in, 340)
+        dev = backend.upload(ref, n_out, n_in)
+        x = synth.activations(3, n_in, 341)
+        y = np.zeros((3, n_out), np.float32)
+        assert backend.matmul(x, [ob.Job(dev, y)])
+        assert row_err(y, m.matmul_f64(x)) < TIGHT
