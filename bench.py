@@ -148,17 +148,37 @@ def gemv_extras(be, torch, peaks, steps):
         for i in range(3):
             be.matvec_dev(devs[i % copies], x, y)
         torch.cuda.synchronize()
+        # One GEMV is a few microseconds, less than a host launch: time a CUDA graph of n back-to-back
+        # GEMVs (each with its activation-plane kernel) over the rotating weight copies.
         n = max(steps, 2 * copies)
+        graph, timing = torch.cuda.CUDAGraph(), "cuda graph"
+        main_stream = torch.cuda.current_stream().cuda_stream
+        try:
+            with torch.cuda.graph(graph):
+                be.set_stream(torch.cuda.current_stream().cuda_stream)
+                for i in range(n):
+                    be.matvec_dev(devs[i % copies], x, y)
+            be.set_stream(main_stream)
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as e:
+            be.set_stream(main_stream)
+            graph, timing = None, f"host-launched ({type(e).__name__})"
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        reps = 5 if graph is not None else 1
         ev[0].record()
-        for i in range(n):
-            be.matvec_dev(devs[i % copies], x, y)
+        for _ in range(reps):
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(n):
+                    be.matvec_dev(devs[i % copies], x, y)
         ev[1].record()
         torch.cuda.synchronize()
-        us = ev[0].elapsed_time(ev[1]) * 1e3 / n
+        us = ev[0].elapsed_time(ev[1]) * 1e3 / (n * reps)
         algo = wbytes + 4 * n_in + 4 * n_out
         out[name] = {"us_per_gemv": us, "bytes": algo, "gbs": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peaks["hbm_gbs"],
-                     "launches_per_gemv": 1 if fmt == "f8_e4m3" else 2}
+                     "launches_per_gemv": 1 if fmt == "f8_e4m3" else 2, "timing": timing}
         for d in devs:
             d.free()
     return out
@@ -182,6 +202,9 @@ def run_b200(args, rank, world, local_rank):
     stream = torch.cuda.current_stream()
     be.set_stream(stream.cuda_stream)
 
+    if args.section == "gemv":
+        print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps)}}), flush=True)
+        return
     assert N_OUT % world == 0
     n_local = N_OUT // world
     ref = synth.q4_k(n_local, K_IN, 1 + rank)
@@ -287,7 +310,7 @@ def run_b200(args, rank, world, local_rank):
                          "frac": achieved / peaks["bf16_tflops"], "traffic": None, "us_per_launch": kern_ms * 1e3,
                          "flop_per_launch": kern_flop, "peak_source": f"bf16 burst, {peaks['source']}"},
         }
-        if world == 1:
+        if world == 1 and args.section == "all":
             from oracle import oracle as O
 
             threads = O.cpu_threads()
@@ -310,6 +333,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv"],
+                    help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

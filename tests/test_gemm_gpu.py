@@ -78,12 +78,19 @@ def test_q4k_matmul_full_size_config(backend):
     rows = np.arange(0, t, 32)
     exact = m.matmul_f64(x[rows])
     assert row_err(y[rows], exact) < TOL
-    # size-independent property: rows 0..255 and 256..511 summed as inputs give the summed outputs.
-    # Powers of two keep a x1 + b x2 exactly representable in f16, so only accumulation order differs.
-    x2 = (0.5 * x[:256] + 0.25 * x[256:]).astype(np.float32)
-    y2 = np.zeros((256, n_out), np.float32)
+    # size-independent properties over all rows. (1) Reordering and doubling the tokens reorders and
+    # doubles the outputs bit for bit (every output is its own k-ordered accumulation).
+    perm = np.arange(t)[::-1].copy()
+    x2 = (2.0 * x[perm]).astype(np.float32)
+    y2 = np.zeros((t, n_out), np.float32)
     assert backend.matmul(x2, [ob.Job(dev, y2)])
-    assert row_err(y2, 0.5 * y[:256].astype(np.float64) + 0.25 * y[256:].astype(np.float64)) < 1e-4
+    assert np.array_equal(y2, 2.0 * y[perm])
+    # (2) Linearity: matmul(a x1 + b x2) = a matmul(x1) + b matmul(x2), up to the f16 rounding of the
+    # combined activations (2^-12 per element).
+    x3 = (0.5 * x[:256] + 0.25 * x[256:]).astype(np.float32)
+    y3 = np.zeros((256, n_out), np.float32)
+    assert backend.matmul(x3, [ob.Job(dev, y3)])
+    assert row_err(y3, 0.5 * y[:256].astype(np.float64) + 0.25 * y[256:].astype(np.float64)) < 5e-4
 
 
 def test_matmul_declines_formats_without_a_tensor_core_kernel(backend):
