@@ -129,7 +129,7 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def gemv_extras(be, torch, peaks, steps):
+def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
     """Achieved HBM GB/s of the batch-1 dequant-GEMV kernels (algorithmic bytes / CUDA-event time),
     rotating over weight copies larger than L2."""
     from oxinfer_b200 import synth
@@ -137,7 +137,7 @@ def gemv_extras(be, torch, peaks, steps):
     out = {}
     cases = [("mlx4_4096x4096", "mlx4", 4096, 4096), ("q4_k_14336x4096", "q4_k", 14336, 4096), ("q6_k_32064x4096", "q6_k", 32064, 4096),
              ("f8_e4m3_7168x12288", "f8_e4m3", 7168, 12288)]
-    for name, fmt, n_out, n_in in cases:
+    for name, fmt, n_out, n_in in [c for c in cases if not only or only in c[0]]:
         ref = synth.make(fmt, n_out, n_in, 5)
         dev0 = be.upload(ref, n_out, n_in)
         wbytes = dev0.bytes()
@@ -154,6 +154,8 @@ def gemv_extras(be, torch, peaks, steps):
         graph, timing = torch.cuda.CUDAGraph(), "cuda graph"
         main_stream = torch.cuda.current_stream().cuda_stream
         try:
+            if not use_graph:
+                raise RuntimeError("graph timing switched off")
             with torch.cuda.graph(graph):
                 be.set_stream(torch.cuda.current_stream().cuda_stream)
                 for i in range(n):
@@ -203,7 +205,7 @@ def run_b200(args, rank, world, local_rank):
     be.set_stream(stream.cuda_stream)
 
     if args.section == "gemv":
-        print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps)}}), flush=True)
+        print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}), flush=True)
         return
     assert N_OUT % world == 0
     n_local = N_OUT // world
@@ -333,6 +335,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default=None, help="with --section gemv: only the cases whose name contains this text")
+    ap.add_argument("--no-graph", action="store_true", help="with --section gemv: host-launched kernels instead of a CUDA graph (profiling)")
     ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()

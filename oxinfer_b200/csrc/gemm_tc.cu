@@ -12,12 +12,12 @@
 //   warp 1      : allocates TMEM; one lane issues tcgen05.mma.kind::f16 (M = 128 tokens per
 //                 instruction, N = tile_n weight rows, K = 16), accumulating in TMEM, and frees each
 //                 ring slot with tcgen05.commit.
-//   warps 2..9  : dequantizers. Thread r owns weight row r of the tile: it streams that row's packed
-//                 super-blocks from global memory (16-byte loads, one super-block prefetched ahead in
-//                 registers), expands each 64-group to f16 with packed half2 arithmetic
-//                 (w = d*sc*q - dmin*m) and writes the K-major, 128-byte-swizzled B operand tile.
-//                 After the main loop the same warps read the accumulators back with tcgen05.ld and
-//                 store y.
+//   warps 2..17 : dequantizers. Two threads own each weight row of the tile (low / high nibbles of a
+//                 64-group): they stream the row's packed super-blocks from global memory (16-byte
+//                 loads, refilled one super-block ahead in registers), expand each 64-group to f16 with
+//                 packed half2 arithmetic (w = d*sc*q - dmin*m) and write the K-major,
+//                 128-byte-swizzled B operand tile. After the main loop the same warps read the
+//                 accumulators back with tcgen05.ld and store y.
 // tile_n is chosen on the host (a multiple of 16, at most 256) so that the grid fills the 148 SMs in
 // one wave; the last tile may be ragged. Operands are f16 rather than bf16: Q4_K values carry more
 // than 8 significant bits, and bf16 activations convert to f16 exactly in the range that matters.
@@ -41,8 +41,8 @@ constexpr int STAGES = 3;
 constexpr int STAGE_K = 64;                // f16 elements per row per stage = one 128-byte swizzle row
 constexpr int A_STAGE_BYTES = 256 * 128;   // up to 256 tokens
 constexpr int B_STAGE_BYTES = 256 * 128;   // up to 256 weight rows
-constexpr int GEMM_THREADS = 320;          // producer warp, MMA warp, 8 dequant / epilogue warps
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr int GEMM_THREADS = 576;          // producer warp, MMA warp, 16 dequant / epilogue warps
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds of SM clock
 
 struct __align__(8) Shared {
     uint64_t a_full[STAGES];
@@ -76,23 +76,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait. Returns false when the CTA is aborting or the time limit passed (in which case it
-// records `where` and raises the abort flag). `heed_abort` = false is for the teardown waits.
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
-                                       bool heed_abort = true) {
+// Bounded wait. Returns false when the CTA is aborting or the limit passed (in which case it records
+// `where` and raises the abort flag). `heed_abort` = false is for the teardown waits. The limit is
+// counted on the SM's own cycle counter (a cheap register read; the global nanosecond timer costs
+// about a microsecond per read, which is as long as a whole pipeline stage).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
+                                          bool heed_abort = true) {
     if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = globaltimer_ns();
+    const long long t0 = clock64();
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63) == 0) {
+        if ((spin & 255) == 0) {
             if (heed_abort && sh->abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 if (atomicCAS(&status->code, 0u, 1u) == 0u) {
                     status->where = where;
                     status->cta = blockIdx.x + gridDim.x * blockIdx.y;
@@ -147,25 +143,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Two packed nibble values (16-bit lanes, each 0..15 in its low 4 bits after masking) -> half2 of the
-// integers: OR in the exponent of 1024 (0x6400 | n = 1024 + n exactly), then subtract 1024.
-__device__ __forceinline__ __half2 nib2_to_half2(uint32_t v) {
-    uint32_t h = (v & 0x000F000Fu) | 0x64006400u;
-    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
-    return __hsub2(*reinterpret_cast<__half2*>(&h), k1024);
-}
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-
-struct Q4kRaw {
-    uint4 hdr;
-    uint4 q[8];
-};
-__device__ __forceinline__ void q4k_load(const uint8_t* blk, Q4kRaw& r) {
-    const uint4* p = (const uint4*)blk;
-    r.hdr = __ldg(p);
-#pragma unroll
-    for (int i = 0; i < 8; i++) r.q[i] = __ldg(p + 1 + i);
-}
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int t, int tile_n, int m_halves, void* __restrict__ y,
@@ -182,7 +160,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
     const int n_out = (int)w.n_out;
-    const int ndq_warps = (tile_n + 31) / 32;
+    const int ndq_warps = (tile_n + 15) / 16;  // two threads per weight row
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -255,75 +233,84 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
         }
     } else {
         // ---------------- dequantizers, then epilogue ----------------
+        // Two threads per weight row: `part` 0 expands the low nibbles of a 64-group (k 0..31 of the
+        // stage, sub-block 2j), `part` 1 the high nibbles (k 32..63, sub-block 2j+1). The pair sits in
+        // adjacent lanes, so their identical 16-byte loads coalesce into one request.
         const int dq_warp = warp - 2;
-        const int r = threadIdx.x - 64;  // weight row of the tile
+        const int dt = threadIdx.x - 64;
+        const int r = dt >> 1;     // weight row of the tile
+        const int part = dt & 1;
         bool ok = true;
         if (dq_warp < ndq_warps) {
             const bool row_live = r < tile_n && n0 + r < n_out;
             const uint8_t* row = w.p0 + (size_t)(row_live ? n0 + r : 0) * (size_t)nsb * 144;
-            Q4kRaw cur, nxt;
-            if (row_live) q4k_load(row, nxt);
+            uint4 q[8], hdr = make_uint4(0, 0, 0, 0), hdr_nxt = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = make_uint4(0, 0, 0, 0);
+            if (row_live) {
+                hdr = __ldg((const uint4*)row);
+#pragma unroll
+                for (int i = 0; i < 8; i++) q[i] = __ldg((const uint4*)row + 1 + i);
+            }
             const uint32_t row_off = (uint32_t)r * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
+            // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
+            // and the sub-block scale is divided by 16 (exact in f16).
+            const uint32_t nib_mask = part ? 0x00F000F0u : 0x000F000Fu;
+            const float part_scale = part ? 0.0625f : 1.0f;
+            const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
             for (int sb = 0; sb < nsb && ok; sb++) {
-                if (row_live) {
-                    cur = nxt;
-                    if (sb + 1 < nsb) q4k_load(row + (size_t)(sb + 1) * 144, nxt);
-                }
-                float d = 0.f, dmin = 0.f;
-                if (row_live) {
-                    d = __half2float(__ushort_as_half((unsigned short)(cur.hdr.x & 0xffff)));
-                    dmin = __half2float(__ushort_as_half((unsigned short)(cur.hdr.x >> 16)));
-                }
+                const bool more = row_live && sb + 1 < nsb;
+                const uint4* nrow = (const uint4*)(row + (size_t)(sb + 1) * 144);
+                if (more) hdr_nxt = __ldg(nrow);
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff))) * part_scale;
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    int ks = sb * 4 + j;
-                    int s = ks % STAGES;
-                    uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                    const int ks = sb * 4 + j;
+                    const int s = ks % STAGES;
+                    const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                    uint32_t sc, mn;
+                    q4k_scale_min(2 * j + part, hdr.y, hdr.z, hdr.w, sc, mn);
+                    const __half2 d1 = __float2half2_rn(d * (float)sc), m1 = __float2half2_rn(-(dmin * (float)mn));
+                    const uint32_t qw[8] = {q[2 * j].x,     q[2 * j].y,     q[2 * j].z,     q[2 * j].w,
+                                            q[2 * j + 1].x, q[2 * j + 1].y, q[2 * j + 1].z, q[2 * j + 1].w};
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        // bytes 4i .. 4i+3 of the group -> k = 4i .. 4i+3 of this thread's 32
+                        uint32_t p0 = __byte_perm(qw[i], 0, 0x4140), p1 = __byte_perm(qw[i], 0, 0x4342);
+                        uint32_t h0 = (p0 & nib_mask) | 0x64006400u, h1 = (p1 & nib_mask) | 0x64006400u;
+                        o[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h0), k1024), d1, m1));
+                        o[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h1), k1024), d1, m1));
+                    }
+                    if (more) {  // refill this group's registers from the next super-block
+                        q[2 * j] = __ldg(nrow + 1 + 2 * j);
+                        q[2 * j + 1] = __ldg(nrow + 2 + 2 * j);
+                    }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
                         break;
                     }
-                    uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
-                    if (row_live) {
-                        uint32_t sc0, mn0, sc1, mn1;
-                        q4k_scale_min(2 * j, cur.hdr.y, cur.hdr.z, cur.hdr.w, sc0, mn0);
-                        q4k_scale_min(2 * j + 1, cur.hdr.y, cur.hdr.z, cur.hdr.w, sc1, mn1);
-                        const __half2 d1lo = __float2half2_rn(d * (float)sc0), m1lo = __float2half2_rn(-(dmin * (float)mn0));
-                        const __half2 d1hi = __float2half2_rn(d * (float)sc1), m1hi = __float2half2_rn(-(dmin * (float)mn1));
-                        const uint32_t qw[8] = {cur.q[2 * j].x,     cur.q[2 * j].y,     cur.q[2 * j].z,     cur.q[2 * j].w,
-                                                cur.q[2 * j + 1].x, cur.q[2 * j + 1].y, cur.q[2 * j + 1].z, cur.q[2 * j + 1].w};
+                    if (r < tile_n) {
+                        uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
 #pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            // bytes 8c .. 8c+7 of the group: low nibbles -> k = 8c.., high nibbles -> k = 32 + 8c..
-                            uint32_t p0 = __byte_perm(qw[2 * c], 0, 0x4140), p1 = __byte_perm(qw[2 * c], 0, 0x4342);
-                            uint32_t p2 = __byte_perm(qw[2 * c + 1], 0, 0x4140), p3 = __byte_perm(qw[2 * c + 1], 0, 0x4342);
-                            uint4 lo, hi;
-                            lo.x = h2_bits(__hfma2(nib2_to_half2(p0), d1lo, m1lo));
-                            lo.y = h2_bits(__hfma2(nib2_to_half2(p1), d1lo, m1lo));
-                            lo.z = h2_bits(__hfma2(nib2_to_half2(p2), d1lo, m1lo));
-                            lo.w = h2_bits(__hfma2(nib2_to_half2(p3), d1lo, m1lo));
-                            hi.x = h2_bits(__hfma2(nib2_to_half2(p0 >> 4), d1hi, m1hi));
-                            hi.y = h2_bits(__hfma2(nib2_to_half2(p1 >> 4), d1hi, m1hi));
-                            hi.z = h2_bits(__hfma2(nib2_to_half2(p2 >> 4), d1hi, m1hi));
-                            hi.w = h2_bits(__hfma2(nib2_to_half2(p3 >> 4), d1hi, m1hi));
-                            *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = lo;
-                            *(uint4*)(dst + ((((uint32_t)(c + 4)) ^ swz) << 4)) = hi;
-                        }
-                    } else if (r < tile_n) {
-                        const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                        for (int c = 0; c < 8; c++) *(uint4*)(dst + (c << 4)) = z;
+                        for (int c = 0; c < 4; c++)
+                            *(uint4*)(dst + ((((uint32_t)(c + 4 * part)) ^ swz) << 4)) =
+                                row_live ? make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]) : make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->b_full[s]);
                 }
+                hdr = hdr_nxt;
             }
         }
-        // Epilogue: warp (warp % 4) may touch TMEM lanes 32 (warp % 4) .. +32.
-        const int half = dq_warp >> 2;
+        // Epilogue: warp (warp % 4) may touch TMEM lanes 32 (warp % 4) .. +32. Sixteen warps: four per
+        // lane quarter, split over the two accumulator halves and the even / odd 16-column chunks.
         const int quarter = warp & 3;
+        const int half = (dq_warp >> 2) & 1;
+        const int cpar = dq_warp >> 3;
         if (half < m_halves) {
             bool acc_ok = mbar_wait(&sh->acc_full, 0, sh, status, 7, 0) && !sh->abort_flag;
             acc_ok = __all_sync(0xffffffffu, acc_ok);
@@ -331,7 +318,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
                 tc_fence_after();
                 const int token = m0 + half * 128 + quarter * 32 + lane;
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
-                for (int c0 = 0; c0 < tile_n; c0 += 16) {
+                for (int c0 = cpar * 16; c0 < tile_n; c0 += 32) {
                     uint32_t v[16];
                     tmem_ld16(taddr0 + (uint32_t)c0, v);
                     if (token < t) {
