@@ -57,10 +57,8 @@ class Backend {
     // staging for the host-buffer entry points
     Scratch x_dev, y_dev, x16, xplanes, pair_tmp;
     GemmStatus* gemm_status = nullptr;  // device
-    // one cached activation tensor map (the staging buffer and shape rarely change)
-    GemmPlan* plan = nullptr;
-    const void* plan_x16 = nullptr;
-    size_t plan_t = 0, plan_K = 0, plan_nout = 0;
+    // cached tensor maps of the tensor-core GEMM (see matmul_dev)
+    std::vector<GemmPlan*> plans;
     // cumulative times, like Backend::stats (src/cuda.rs:403-409)
     double ns_in = 0, ns_gpu = 0, ns_out = 0;
     uint64_t calls = 0;
@@ -268,6 +266,8 @@ class Backend {
         auto it = weights.find(h);
         if (it == weights.end()) return fail(B2_ERR_ARG, "[b200qmm: free_weight: unknown weight]");
         cudaStreamSynchronize(stream);
+        for (GemmPlan* p : plans) gemm_tc_plan_destroy(p);  // tensor maps may point into this weight
+        plans.clear();
         drop(it->second.owned);
         weights.erase(it);
         return B2_OK;
@@ -364,16 +364,22 @@ class Backend {
             if (e != cudaSuccess) return cuda_fail(e, "to_f16");
             xh = x16.p;
         }
-        if (!plan || plan_x16 != xh || plan_t != t || plan_K != K || plan_nout != w->dev.n_out) {
-            if (plan) gemm_tc_plan_destroy(plan);
-            plan = nullptr;
+        // Tensor maps (activations + packed weights) are cached per (weights, activations, t).
+        GemmPlan* plan = nullptr;
+        for (GemmPlan* p : plans)
+            if (gemm_tc_plan_matches(p, w->dev, xh, t, y, y_dtype)) {
+                plan = p;
+                break;
+            }
+        if (!plan) {
+            if (plans.size() >= 256) {
+                for (GemmPlan* p : plans) gemm_tc_plan_destroy(p);
+                plans.clear();
+            }
             char msg[256] = {0};
-            e = gemm_tc_plan_create(w->dev, xh, t, &plan, msg, sizeof msg);
+            e = gemm_tc_plan_create(w->dev, xh, t, y, y_dtype, &plan, msg, sizeof msg);
             if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
-            plan_x16 = xh;
-            plan_t = t;
-            plan_K = K;
-            plan_nout = w->dev.n_out;
+            plans.push_back(plan);
         }
         e = launch_gemm_tc(plan, w->dev, t, y, y_dtype, gemm_status, sm_count, stream);
         launches++;
@@ -387,6 +393,7 @@ class Backend {
         GemmStatus s{};
         cudaError_t e = cudaMemcpy(&s, gemm_status, sizeof s, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return cuda_fail(e, "status read");
+        if (getenv("B2_GEMM_DEBUG") && (atoi(getenv("B2_GEMM_DEBUG")) & 32768)) fprintf(stderr, "[gemm debug] mma loop cycles %u over %u stages; stamps: loop start %u, loop end %u, acc seen %u, epilogue done %u, all done %u\n", s.where, s.iter, s.t[0], s.t[1], s.t[2], s.t[3], s.t[4]);
         if (s.code) {
             cudaMemset(gemm_status, 0, sizeof s);
             return fail(B2_ERR_TIMEOUT, "[b200qmm: gemm: a device wait gave up (wait %u, cta %u, k-stage %u)]", s.where, s.cta, s.iter);
@@ -491,8 +498,8 @@ class Backend {
         pair_tmp.release();
         if (gemm_status) cudaFree(gemm_status);
         gemm_status = nullptr;
-        if (plan) gemm_tc_plan_destroy(plan);
-        plan = nullptr;
+        for (GemmPlan* p : plans) gemm_tc_plan_destroy(p);
+        plans.clear();
     }
 };
 

@@ -7,22 +7,25 @@
 // has no GGUF arm at all (src/cuda.rs:1011).
 //
 // One CTA computes a tile of TM = 128 * m_halves tokens x tile_n weight rows over the whole K:
-//   warp 0      : TMA producer. Activation tiles (f16, 64 k x TM tokens, 128-byte swizzle) arrive by
-//                 cp.async.bulk.tensor into a 3-stage ring.
-//   warp 1      : allocates TMEM; one lane issues tcgen05.mma.kind::f16 (M = 128 tokens per
-//                 instruction, N = tile_n weight rows, K = 16), accumulating in TMEM, and frees each
-//                 ring slot with tcgen05.commit.
-//   warps 2..17 : dequantizers. Two threads own each weight row of the tile (low / high nibbles of a
-//                 64-group): they stream the row's packed super-blocks from global memory (16-byte
-//                 loads, refilled one super-block ahead in registers), expand each 64-group to f16 with
-//                 packed half2 arithmetic (w = d*sc*q - dmin*m) and write the K-major,
-//                 128-byte-swizzled B operand tile. After the main loop the same warps read the
-//                 accumulators back with tcgen05.ld and store y.
-// tile_n is chosen on the host (a multiple of 16, at most 256) so that the grid fills the 148 SMs in
-// one wave; the last tile may be ragged. Operands are f16 rather than bf16: Q4_K values carry more
-// than 8 significant bits, and bf16 activations convert to f16 exactly in the range that matters.
+//   warp 0       : TMA producer. Two streams of cp.async.bulk.tensor copies: the activation tiles
+//                  (f16, 64 k x TM tokens, 128-byte swizzle) into a 3-stage ring, and the PACKED weight
+//                  tile of one super-block column (144 bytes x tile_n rows, unswizzled) into a raw
+//                  staging buffer, one super-block ahead of the dequantizers.
+//   warp 1       : allocates TMEM; one lane issues tcgen05.mma.kind::f16 (M = 128 tokens per
+//                  instruction, N = tile_n weight rows, K = 16), accumulating in TMEM, and frees each
+//                  ring slot with tcgen05.commit.
+//   warps 2..17  : dequantizers. Two threads own each weight row of the tile (low / high nibbles of a
+//                  64-group): per super-block they copy the row's 144 packed bytes from the staging
+//                  buffer to registers, release the buffer, and expand one 64-group per pipeline stage
+//                  to f16 with packed half2 arithmetic (w = d*sc*q - dmin*m), writing the K-major,
+//                  128-byte-swizzled B operand tile. After the main loop the same warps read the
+//                  accumulators back with tcgen05.ld and store y.
+// tile_n is chosen on the host (a multiple of 16, at most 240) so that the grid fills the SMs in one
+// wave; the last tile may be ragged (TMA zero-fills rows past n_out, which dequantize to zeros).
+// Operands are f16 rather than bf16: Q4_K values carry more than 8 significant bits, and bf16
+// activations convert to f16 exactly in the range that matters.
 //
-// Every wait is bounded: a wait that exceeds its time limit records where it gave up in a status
+// Every wait is bounded: a wait that exceeds its cycle limit records where it gave up in a status
 // word, raises a CTA-wide abort flag, and every role then falls through to the common teardown
 // (in-flight copies are awaited, TMEM is freed) so that the kernel always returns.
 #include <cuda.h>
@@ -39,21 +42,26 @@ namespace {
 
 constexpr int STAGES = 3;
 constexpr int STAGE_K = 64;                // f16 elements per row per stage = one 128-byte swizzle row
+constexpr int MAX_TILE_N = 240;
 constexpr int A_STAGE_BYTES = 256 * 128;   // up to 256 tokens
-constexpr int B_STAGE_BYTES = 256 * 128;   // up to 256 weight rows
-constexpr int GEMM_THREADS = 576;          // producer warp, MMA warp, 16 dequant / epilogue warps
+constexpr int B_STAGE_BYTES = MAX_TILE_N * 128;
+constexpr int RAW_BYTES = MAX_TILE_N * 144;  // one super-block column of the weight tile, packed
+constexpr int GEMM_THREADS = 608;          // activation producer, MMA issuer, 16 dequant / epilogue warps, weight producer
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds of SM clock
 
 struct __align__(8) Shared {
     uint64_t a_full[STAGES];
     uint64_t b_full[STAGES];
     uint64_t empty[STAGES];
+    uint64_t raw_full;
+    uint64_t raw_empty;
     uint64_t acc_full;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
 
-constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(Shared);
+constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + RAW_BYTES + sizeof(Shared);
+static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -76,10 +84,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+
 // Bounded wait. Returns false when the CTA is aborting or the limit passed (in which case it records
 // `where` and raises the abort flag). `heed_abort` = false is for the teardown waits. The limit is
 // counted on the SM's own cycle counter (a cheap register read; the global nanosecond timer costs
-// about a microsecond per read, which is as long as a whole pipeline stage).
+// about a microsecond per read, as long as a whole pipeline stage).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
                                           bool heed_abort = true) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -146,20 +155,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int t, int tile_n, int m_halves, void* __restrict__ y,
-                   int y_dtype, GemmStatus* __restrict__ status) {
+gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
+                   int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg) {
+    const long long dbg_k0 = clock64();
+    const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + (size_t)STAGES * A_STAGE_BYTES;
-    Shared* sh = (Shared*)(b_tiles + (size_t)STAGES * B_STAGE_BYTES);
+    uint8_t* raw = b_tiles + (size_t)STAGES * B_STAGE_BYTES;
+    Shared* sh = (Shared*)(raw + RAW_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int K = (int)w.n_in;
     const int nsb = K / 256, nks = nsb * 4;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
-    const int n_out = (int)w.n_out;
     const int ndq_warps = (tile_n + 15) / 16;  // two threads per weight row
 
     if (threadIdx.x == 0) {
@@ -168,6 +179,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
             mbar_init(&sh->b_full[s], (uint32_t)ndq_warps);
             mbar_init(&sh->empty[s], 1);
         }
+        mbar_init(&sh->raw_full, 1);
+        mbar_init(&sh->raw_empty, (uint32_t)ndq_warps);
         mbar_init(&sh->acc_full, 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -183,30 +196,56 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
     const uint32_t tmem_base = sh->tmem_base;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producers: warp 0 streams the activations, warp 18 the packed weights ----------------
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
-            const uint32_t tx_bytes = (uint32_t)(128 * m_halves * 128);
-            int issued = 0;
+            const uint32_t a_bytes = (uint32_t)(128 * m_halves * 128);
+            int a_issued = 0;
             for (int ks = 0; ks < nks; ks++) {
-                int s = ks % STAGES;
-                uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                const int s = ks % STAGES;
+                const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
                 if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)ks)) break;
-                mbar_arrive_expect_tx(&sh->a_full[s], tx_bytes);
-                tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
-                issued = ks + 1;
+                if (dbg & 16) {
+                    mbar_arrive(&sh->a_full[s]);
+                } else {
+                    mbar_arrive_expect_tx(&sh->a_full[s], a_bytes);
+                    tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
+                    a_issued = ks + 1;
+                }
             }
             if (sh->abort_flag) {
                 // Let the copies still in flight land before the CTA's shared memory is released.
-                for (int ks = max(0, issued - STAGES); ks < issued; ks++)
+                for (int ks = max(0, a_issued - STAGES); ks < a_issued; ks++)
                     mbar_wait(&sh->a_full[ks % STAGES], (uint32_t)((ks / STAGES) & 1), sh, status, 2, (uint32_t)ks, false);
             }
+        }
+    } else if (warp == 18) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            const uint32_t w_bytes = (uint32_t)(tile_n * 144);
+            int w_issued = 0;
+            for (int sb = 0; sb < nsb; sb++) {
+                // the staging buffer is free once every dequant warp has taken its copy of super-block sb - 1,
+                // which they do at the start of that super-block: this copy runs a whole super-block ahead
+                if (!mbar_wait(&sh->raw_empty, (uint32_t)((sb & 1) ^ 1), sh, status, 8, (uint32_t)sb)) break;
+                if (dbg & 2) {
+                    mbar_arrive(&sh->raw_full);
+                    continue;
+                }
+                mbar_arrive_expect_tx(&sh->raw_full, w_bytes);
+                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * 144, n0);
+                w_issued = sb + 1;
+            }
+            if (sh->abort_flag && w_issued > 0)
+                mbar_wait(&sh->raw_full, (uint32_t)((w_issued - 1) & 1), sh, status, 9, (uint32_t)w_issued, false);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((uint32_t)(tile_n >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
+            const long long dbg_t0 = clock64();
+            const uint64_t a_desc_base = smem_desc_sw128(smem_u32(a_tiles)), b_desc_base = smem_desc_sw128(smem_u32(b_tiles));
             for (int ks = 0; ks < nks && ok; ks++) {
                 int s = ks % STAGES;
                 uint32_t ph = (uint32_t)((ks / STAGES) & 1);
@@ -216,42 +255,33 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
                     break;
                 }
                 tc_fence_after();
-                uint32_t a_addr = smem_u32(a_tiles + (size_t)s * A_STAGE_BYTES);
-                uint32_t b_addr = smem_u32(b_tiles + (size_t)s * B_STAGE_BYTES);
+                // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
+                const uint64_t adesc0 = a_desc_base + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
+                const uint64_t bdesc0 = b_desc_base + (uint64_t)((uint32_t)s * (B_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int kk = 0; kk < STAGE_K / 16; kk++) {
-                    uint64_t bdesc = smem_desc_sw128(b_addr + kk * 32);
-                    for (int h = 0; h < m_halves; h++) {
-                        uint64_t adesc = smem_desc_sw128(a_addr + h * (128 * 128) + kk * 32);
-                        mma_f16(tmem_base + (uint32_t)(h * 256), adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                    if (!(dbg & 4)) {
+                        mma_f16(tmem_base, adesc0 + 2 * kk, bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                        if (m_halves == 2) mma_f16(tmem_base + 256u, adesc0 + 2 * kk + ((128 * 128) >> 4), bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
                 mma_commit(&sh->empty[s]);
             }
             mma_commit(&sh->acc_full);
+            if (dbg_cta) { status->where = (uint32_t)(clock64() - dbg_t0); status->iter = (uint32_t)nks; status->t[0] = (uint32_t)(dbg_t0 - dbg_k0); status->t[1] = (uint32_t)(clock64() - dbg_k0); }
             if (!ok) mbar_wait(&sh->acc_full, 0, sh, status, 5, 0, false);  // drain what was issued before teardown
         }
     } else {
         // ---------------- dequantizers, then epilogue ----------------
         // Two threads per weight row: `part` 0 expands the low nibbles of a 64-group (k 0..31 of the
-        // stage, sub-block 2j), `part` 1 the high nibbles (k 32..63, sub-block 2j+1). The pair sits in
-        // adjacent lanes, so their identical 16-byte loads coalesce into one request.
+        // stage, sub-block 2j), `part` 1 the high nibbles (k 32..63, sub-block 2j+1).
         const int dq_warp = warp - 2;
         const int dt = threadIdx.x - 64;
-        const int r = dt >> 1;     // weight row of the tile
+        const int r = dt >> 1;  // weight row of the tile
         const int part = dt & 1;
         bool ok = true;
         if (dq_warp < ndq_warps) {
-            const bool row_live = r < tile_n && n0 + r < n_out;
-            const uint8_t* row = w.p0 + (size_t)(row_live ? n0 + r : 0) * (size_t)nsb * 144;
-            uint4 q[8], hdr = make_uint4(0, 0, 0, 0), hdr_nxt = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int i = 0; i < 8; i++) q[i] = make_uint4(0, 0, 0, 0);
-            if (row_live) {
-                hdr = __ldg((const uint4*)row);
-#pragma unroll
-                for (int i = 0; i < 8; i++) q[i] = __ldg((const uint4*)row + 1 + i);
-            }
+            const bool in_tile = r < tile_n;
             const uint32_t row_off = (uint32_t)r * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
             // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
@@ -259,10 +289,19 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
             const uint32_t nib_mask = part ? 0x00F000F0u : 0x000F000Fu;
             const float part_scale = part ? 0.0625f : 1.0f;
             const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+            const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * 144);
             for (int sb = 0; sb < nsb && ok; sb++) {
-                const bool more = row_live && sb + 1 < nsb;
-                const uint4* nrow = (const uint4*)(row + (size_t)(sb + 1) * 144);
-                if (more) hdr_nxt = __ldg(nrow);
+                // this row's packed super-block: staging buffer -> registers, then release the buffer
+                if (!mbar_wait(&sh->raw_full, (uint32_t)(sb & 1), sh, status, 10, (uint32_t)sb)) {
+                    ok = false;
+                    break;
+                }
+                uint4 hdr = my_raw[0];
+                uint4 q[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) q[i] = my_raw[1 + i];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->raw_empty);
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff))) * part_scale;
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
@@ -284,26 +323,20 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
                         o[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h0), k1024), d1, m1));
                         o[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h1), k1024), d1, m1));
                     }
-                    if (more) {  // refill this group's registers from the next super-block
-                        q[2 * j] = __ldg(nrow + 1 + 2 * j);
-                        q[2 * j + 1] = __ldg(nrow + 2 + 2 * j);
-                    }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
                         break;
                     }
-                    if (r < tile_n) {
+                    if (in_tile && !(dbg & 1)) {
                         uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
 #pragma unroll
                         for (int c = 0; c < 4; c++)
-                            *(uint4*)(dst + ((((uint32_t)(c + 4 * part)) ^ swz) << 4)) =
-                                row_live ? make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]) : make_uint4(0, 0, 0, 0);
+                            *(uint4*)(dst + ((((uint32_t)(c + 4 * part)) ^ swz) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                     }
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->b_full[s]);
                 }
-                hdr = hdr_nxt;
             }
         }
         // Epilogue: warp (warp % 4) may touch TMEM lanes 32 (warp % 4) .. +32. Sixteen warps: four per
@@ -314,15 +347,55 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
         if (half < m_halves) {
             bool acc_ok = mbar_wait(&sh->acc_full, 0, sh, status, 7, 0) && !sh->abort_flag;
             acc_ok = __all_sync(0xffffffffu, acc_ok);
+            if (dbg_cta && threadIdx.x == 64) status->t[2] = (uint32_t)(clock64() - dbg_k0);
             if (acc_ok) {
                 tc_fence_after();
-                const int token = m0 + half * 128 + quarter * 32 + lane;
+                const int token0 = m0 + half * 128 + quarter * 32;
+                const int token = token0 + lane;
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
-                for (int c0 = cpar * 16; c0 < tile_n; c0 += 32) {
+                int c0 = cpar * 32;
+                if (y_dtype == B2_F32 && !(dbg & 64)) {
+                    // f32 output through shared memory and TMA stores: each warp owns two 4 KB staging tiles
+                    // (32 tokens x 32 columns, 128-byte swizzle) in the now idle pipeline buffers, fills one
+                    // from TMEM, and lets the copy engine write it out while it fills the other. The tensor
+                    // map clips rows past t and columns past n_out.
+                    uint8_t* stage = smem + (size_t)dq_warp * 8192;
+                    int it = 0;
+                    for (; c0 + 32 <= tile_n; c0 += 64, it++) {
+                        uint8_t* buf = stage + (it & 1) * 4096;
+                        if (it >= 2) {  // the store issued two rounds ago has finished reading this tile
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            __syncwarp();
+                        }
+                        uint32_t v[16], u[16];
+                        tmem_ld16(taddr0 + (uint32_t)c0, v);
+                        tmem_ld16(taddr0 + (uint32_t)c0 + 16u, u);
+                        uint8_t* rowp = buf + lane * 128;
+                        const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+                        for (int pce = 0; pce < 4; pce++) {
+                            *(uint4*)(rowp + ((((uint32_t)pce) ^ sw) << 4)) = make_uint4(v[4 * pce], v[4 * pce + 1], v[4 * pce + 2], v[4 * pce + 3]);
+                            *(uint4*)(rowp + ((((uint32_t)(pce + 4)) ^ sw) << 4)) = make_uint4(u[4 * pce], u[4 * pce + 1], u[4 * pce + 2], u[4 * pce + 3]);
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0 && !(dbg & 8)) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
+                                         "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
+                                         : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                    // a 16-column tail (tile_n not a multiple of 32) goes to the warps whose turn it would be
+                    c0 = ((tile_n & 31) && ((tile_n >> 5) & 1) == cpar) ? (tile_n & ~31) : tile_n;
+                }
+                const int step = (y_dtype == B2_F32 && !(dbg & 64)) ? tile_n : 64;
+                for (; c0 < tile_n; c0 += step) {
+                  for (int cc = c0; cc < min(c0 + 32, tile_n); cc += 16) {
                     uint32_t v[16];
-                    tmem_ld16(taddr0 + (uint32_t)c0, v);
-                    if (token < t) {
-                        int n = n0 + c0;
+                    tmem_ld16(taddr0 + (uint32_t)cc, v);
+                    if (token < t && !(dbg & 8)) {
+                        int n = n0 + cc;
                         if (y_dtype == B2_F32) {
                             float* o = (float*)y + (size_t)token * n_out + n;
                             if (n + 16 <= n_out && (n_out & 3) == 0) {
@@ -353,13 +426,19 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, WeightDev w, int 
                             }
                         }
                     }
+                  }
                 }
+                // the staging tiles must have been read out before the CTA's shared memory goes away
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                __syncwarp();
             }
         }
     }
 
+    if (dbg_cta && threadIdx.x == 64) status->t[3] = (uint32_t)(clock64() - dbg_k0);
     tc_fence_before();
     __syncthreads();
+    if (dbg_cta && threadIdx.x == 64) status->t[4] = (uint32_t)(clock64() - dbg_k0);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
@@ -398,12 +477,23 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// B2_GEMM_DEBUG: diagnostic switches for timing experiments (the results are WRONG when any is set):
+// 1 skip the dequantizers' shared-memory stores, 4 skip the MMAs, 8 skip the epilogue's stores,
+// 16 skip the activation copies.
+int debug_switches() {
+    const char* e = getenv("B2_GEMM_DEBUG");
+    return e ? atoi(e) : 0;
+}
+
 }  // namespace
 
 struct GemmPlan {
-    CUtensorMap tmap_x;
+    CUtensorMap tmap_x, tmap_w, tmap_y;
     const void* x16;
-    size_t t, K;
+    const void* wptr;
+    const void* y;
+    int y_dtype;
+    size_t t, K, n_out;
     int tile_n, m_halves, n_tiles, m_tiles;
 };
 
@@ -411,17 +501,17 @@ bool gemm_tc_supports(const WeightDev& w, size_t t) {
     return w.fmt == B2_FMT_Q4_K && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
 }
 
-// Tile width (weight rows per CTA): the multiple of 16 up to 256 that minimizes the time of the
+// Tile width (weight rows per CTA): the multiple of 16 up to MAX_TILE_N that minimizes the time of the
 // slowest SM, i.e. waves * tile_n, over the grid ceil(n_out / tile_n) * m_tiles.
 static int pick_tile_n(size_t n_out, int m_tiles, int sm_count) {
     // B2_GEMM_TILE_N forces a width (tests and tuning sweeps).
     if (const char* env = getenv("B2_GEMM_TILE_N")) {
         int v = atoi(env);
-        if (v >= 16 && v <= 256 && v % 16 == 0) return v;
+        if (v >= 16 && v <= MAX_TILE_N && v % 16 == 0) return v;
     }
-    int best = 256;
+    int best = MAX_TILE_N;
     double best_cost = 1e30;
-    for (int tn = 256; tn >= 64; tn -= 16) {
+    for (int tn = MAX_TILE_N; tn >= 64; tn -= 16) {
         size_t tiles = (n_out + tn - 1) / tn * (size_t)m_tiles;
         size_t waves = (tiles + sm_count - 1) / sm_count;
         double cost = (double)waves * (tn + 24);  // + fixed per-tile overhead, in units of rows
@@ -433,7 +523,8 @@ static int pick_tile_n(size_t n_out, int m_tiles, int sm_count) {
     return best;
 }
 
-cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, GemmPlan** out, char* err, size_t errlen) {
+cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
+                                size_t errlen) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) {
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
@@ -441,8 +532,12 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, G
     }
     GemmPlan* p = new GemmPlan();
     p->x16 = x16;
+    p->wptr = w.p0;
+    p->y = y;
+    p->y_dtype = y_dtype;
     p->t = t;
     p->K = w.n_in;
+    p->n_out = w.n_out;
     p->m_halves = t > 128 ? 2 : 1;
     int tm = 128 * p->m_halves;
     p->m_tiles = (int)((t + tm - 1) / tm);
@@ -451,22 +546,58 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, G
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count);
     p->n_tiles = (int)((w.n_out + p->tile_n - 1) / p->tile_n);
-    cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)t};
-    cuuint64_t strides[1] = {(cuuint64_t)w.n_in * 2};
-    cuuint32_t box[2] = {(cuuint32_t)STAGE_K, (cuuint32_t)tm};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&p->tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        snprintf(err, errlen, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-        delete p;
-        return cudaErrorInvalidValue;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)t};
+        cuuint64_t strides[1] = {(cuuint64_t)w.n_in * 2};
+        cuuint32_t box[2] = {(cuuint32_t)STAGE_K, (cuuint32_t)tm};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&p->tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            snprintf(err, errlen, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
+            delete p;
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        // the packed weights as a byte matrix [n_out][row_bytes]; one box = one super-block column of the tile
+        size_t row_bytes = w.n_in / 256 * 144;
+        cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)w.n_out};
+        cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+        cuuint32_t box[2] = {144, (cuuint32_t)p->tile_n};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&p->tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.p0, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            snprintf(err, errlen, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
+            delete p;
+            return cudaErrorInvalidValue;
+        }
+    }
+    p->tmap_y = p->tmap_x;  // placeholder when the epilogue stores directly (bf16 output)
+    if (y_dtype == B2_F32) {
+        // the f32 output [t][n_out]; one box = a warp's 32 tokens x 32 columns staging tile
+        cuuint64_t dims[2] = {(cuuint64_t)w.n_out, (cuuint64_t)t};
+        cuuint64_t strides[1] = {(cuuint64_t)w.n_out * 4};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&p->tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            snprintf(err, errlen, "cuTensorMapEncodeTiled(y) failed with CUresult %d", (int)r);
+            delete p;
+            return cudaErrorInvalidValue;
+        }
     }
     *out = p;
     return cudaSuccess;
 }
 
 void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
+
+bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype) {
+    return p && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out;
+}
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
                            cudaStream_t st) {
@@ -477,7 +608,8 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         attr_set = true;
     }
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
-    gemm_q4k_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, w, (int)t, p->tile_n, p->m_halves, y, y_dtype, status_dev);
+    gemm_q4k_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
+                                                              y_dtype, status_dev, debug_switches());
     return cudaGetLastError();
 }
 

@@ -47,13 +47,16 @@ struct GemmStatus {   // written by the kernel when a bounded wait gives up
     uint32_t where;   // which wait
     uint32_t cta;
     uint32_t iter;
+    uint32_t t[8];    // cycle stamps of one CTA (diagnostics, B2_GEMM_DEBUG & 32768)
 };
 bool gemm_tc_supports(const WeightDev& w, size_t t);
 // y[t][n_out] (f32 or bf16) = x[t][n_in] (f16, row-major, t padded by the caller to a multiple of
 // 256 rows in `x16`) * W^T. `tmap_x` is the host-encoded tensor map of x16 (see make_tmap_x).
 struct GemmPlan;
-cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t_pad, GemmPlan** out, char* err, size_t errlen);
+cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
+                                size_t errlen);
 void gemm_tc_plan_destroy(GemmPlan* p);
+bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype);
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int sm_count,
                            cudaStream_t st);
 // x (f32 / bf16 / f16, [t][K]) -> f16 [t_pad][K], pad rows zeroed.
