@@ -393,7 +393,7 @@ class Backend {
         GemmStatus s{};
         cudaError_t e = cudaMemcpy(&s, gemm_status, sizeof s, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return cuda_fail(e, "status read");
-        if (getenv("B2_GEMM_DEBUG") && (atoi(getenv("B2_GEMM_DEBUG")) & 32768)) fprintf(stderr, "[gemm debug] mma loop cycles %u over %u stages; stamps: loop start %u, loop end %u, acc seen %u, epilogue done %u, all done %u\n", s.where, s.iter, s.t[0], s.t[1], s.t[2], s.t[3], s.t[4]);
+        if (getenv("B2_GEMM_DEBUG") && (atoi(getenv("B2_GEMM_DEBUG")) & 32768)) fprintf(stderr, "[gemm debug] mma loop cycles %u over %u stages; stamps: loop start %u, loop end %u, acc seen %u, epilogue done %u, all done %u; mma thread waited %u on activations, %u on weights\n", s.where, s.iter, s.t[0], s.t[1], s.t[2], s.t[3], s.t[4], s.t[5], s.t[6]);
         if (s.code) {
             cudaMemset(gemm_status, 0, sizeof s);
             return fail(B2_ERR_TIMEOUT, "[b200qmm: gemm: a device wait gave up (wait %u, cta %u, k-stage %u)]", s.where, s.cta, s.iter);

@@ -171,16 +171,16 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const int nsb = K / 256, nks = nsb * 4;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
-    const int ndq_warps = (tile_n + 15) / 16;  // two threads per weight row
+    const int set_warps = (tile_n + 31) / 32;  // live warps in each of the two dequantizer sets
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&sh->a_full[s], 1);
-            mbar_init(&sh->b_full[s], (uint32_t)ndq_warps);
+            mbar_init(&sh->b_full[s], (uint32_t)set_warps);
             mbar_init(&sh->empty[s], 1);
         }
         mbar_init(&sh->raw_full, 1);
-        mbar_init(&sh->raw_empty, (uint32_t)ndq_warps);
+        mbar_init(&sh->raw_empty, (uint32_t)(2 * set_warps));
         mbar_init(&sh->acc_full, 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -245,15 +245,16 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             const uint32_t idesc = (1u << 4) | ((uint32_t)(tile_n >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
             const long long dbg_t0 = clock64();
+            long long dbg_wa = 0, dbg_wb = 0;
             const uint64_t a_desc_base = smem_desc_sw128(smem_u32(a_tiles)), b_desc_base = smem_desc_sw128(smem_u32(b_tiles));
             for (int ks = 0; ks < nks && ok; ks++) {
                 int s = ks % STAGES;
                 uint32_t ph = (uint32_t)((ks / STAGES) & 1);
-                if (!mbar_wait(&sh->a_full[s], ph, sh, status, 3, (uint32_t)ks) ||
-                    !mbar_wait(&sh->b_full[s], ph, sh, status, 4, (uint32_t)ks)) {
-                    ok = false;
-                    break;
-                }
+                const long long w0 = dbg_cta ? clock64() : 0;
+                if (!mbar_wait(&sh->a_full[s], ph, sh, status, 3, (uint32_t)ks)) { ok = false; break; }
+                const long long w1 = dbg_cta ? clock64() : 0;
+                if (!mbar_wait(&sh->b_full[s], ph, sh, status, 4, (uint32_t)ks)) { ok = false; break; }
+                if (dbg_cta) { dbg_wa += w1 - w0; dbg_wb += clock64() - w1; }
                 tc_fence_after();
                 // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
                 const uint64_t adesc0 = a_desc_base + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
@@ -268,60 +269,69 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 mma_commit(&sh->empty[s]);
             }
             mma_commit(&sh->acc_full);
-            if (dbg_cta) { status->where = (uint32_t)(clock64() - dbg_t0); status->iter = (uint32_t)nks; status->t[0] = (uint32_t)(dbg_t0 - dbg_k0); status->t[1] = (uint32_t)(clock64() - dbg_k0); }
+            if (dbg_cta) { status->where = (uint32_t)(clock64() - dbg_t0); status->iter = (uint32_t)nks; status->t[0] = (uint32_t)(dbg_t0 - dbg_k0); status->t[1] = (uint32_t)(clock64() - dbg_k0); status->t[5] = (uint32_t)dbg_wa; status->t[6] = (uint32_t)dbg_wb; }
             if (!ok) mbar_wait(&sh->acc_full, 0, sh, status, 5, 0, false);  // drain what was issued before teardown
         }
     } else {
         // ---------------- dequantizers, then epilogue ----------------
-        // Two threads per weight row: `part` 0 expands the low nibbles of a 64-group (k 0..31 of the
-        // stage, sub-block 2j), `part` 1 the high nibbles (k 32..63, sub-block 2j+1).
+        // Two sets of eight warps take the pipeline stages in turn (set 0 the even k-stages, set 1 the odd
+        // ones), one thread per weight row: a warp then has two stage times for the serial chain
+        // "expand 64 weights, wait for the slot, store, fence, arrive", and half as many waits per weight.
         const int dq_warp = warp - 2;
         const int dt = threadIdx.x - 64;
-        const int r = dt >> 1;  // weight row of the tile
-        const int part = dt & 1;
+        const int set = dt >> 8;
+        const int r = dt & 255;  // weight row of the tile
         bool ok = true;
-        if (dq_warp < ndq_warps) {
+        if ((dq_warp & 7) < set_warps) {
             const bool in_tile = r < tile_n;
             const uint32_t row_off = (uint32_t)r * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
-            // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
-            // and the sub-block scale is divided by 16 (exact in f16).
-            const uint32_t nib_mask = part ? 0x00F000F0u : 0x000F000Fu;
-            const float part_scale = part ? 0.0625f : 1.0f;
             const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
             const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * 144);
             for (int sb = 0; sb < nsb && ok; sb++) {
-                // this row's packed super-block: staging buffer -> registers, then release the buffer
+                // this row's packed super-block: staging buffer -> registers (only the two 64-groups this set
+                // expands), then release the buffer
                 if (!mbar_wait(&sh->raw_full, (uint32_t)(sb & 1), sh, status, 10, (uint32_t)sb)) {
                     ok = false;
                     break;
                 }
-                uint4 hdr = my_raw[0];
-                uint4 q[8];
+                const uint4 hdr = my_raw[0];
+                uint4 q[4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) q[i] = my_raw[1 + i];
+                for (int jj = 0; jj < 2; jj++) {
+                    q[2 * jj] = my_raw[1 + 2 * (set + 2 * jj)];
+                    q[2 * jj + 1] = my_raw[2 + 2 * (set + 2 * jj)];
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->raw_empty);
-                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff))) * part_scale;
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
+                for (int jj = 0; jj < 2; jj++) {
+                    const int j = set + 2 * jj;
                     const int ks = sb * 4 + j;
                     const int s = ks % STAGES;
                     const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
-                    uint32_t sc, mn;
-                    q4k_scale_min(2 * j + part, hdr.y, hdr.z, hdr.w, sc, mn);
-                    const __half2 d1 = __float2half2_rn(d * (float)sc), m1 = __float2half2_rn(-(dmin * (float)mn));
-                    const uint32_t qw[8] = {q[2 * j].x,     q[2 * j].y,     q[2 * j].z,     q[2 * j].w,
-                                            q[2 * j + 1].x, q[2 * j + 1].y, q[2 * j + 1].z, q[2 * j + 1].w};
-                    uint32_t o[16];
+                    uint32_t sc0, mn0, sc1, mn1;
+                    q4k_scale_min(2 * j, hdr.y, hdr.z, hdr.w, sc0, mn0);
+                    q4k_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, sc1, mn1);
+                    // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
+                    // with that sub-block's scale divided by 16 (exact in f16).
+                    const __half2 d1lo = __float2half2_rn(d * (float)sc0), m1lo = __float2half2_rn(-(dmin * (float)mn0));
+                    const __half2 d1hi = __float2half2_rn(d * 0.0625f * (float)sc1), m1hi = __float2half2_rn(-(dmin * (float)mn1));
+                    const uint32_t qw[8] = {q[2 * jj].x,     q[2 * jj].y,     q[2 * jj].z,     q[2 * jj].w,
+                                            q[2 * jj + 1].x, q[2 * jj + 1].y, q[2 * jj + 1].z, q[2 * jj + 1].w};
+                    uint32_t lo[16], hi[16];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        // bytes 4i .. 4i+3 of the group -> k = 4i .. 4i+3 of this thread's 32
+                        // bytes 4i .. 4i+3 of the group -> k = 4i .. 4i+3 (low nibbles) and 32 + 4i .. (high nibbles)
                         uint32_t p0 = __byte_perm(qw[i], 0, 0x4140), p1 = __byte_perm(qw[i], 0, 0x4342);
-                        uint32_t h0 = (p0 & nib_mask) | 0x64006400u, h1 = (p1 & nib_mask) | 0x64006400u;
-                        o[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h0), k1024), d1, m1));
-                        o[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h1), k1024), d1, m1));
+                        uint32_t l0 = (p0 & 0x000F000Fu) | 0x64006400u, l1 = (p1 & 0x000F000Fu) | 0x64006400u;
+                        uint32_t h0 = (p0 & 0x00F000F0u) | 0x64006400u, h1 = (p1 & 0x00F000F0u) | 0x64006400u;
+                        lo[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&l0), k1024), d1lo, m1lo));
+                        lo[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&l1), k1024), d1lo, m1lo));
+                        hi[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h0), k1024), d1hi, m1hi));
+                        hi[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h1), k1024), d1hi, m1hi));
                     }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
@@ -330,8 +340,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     if (in_tile && !(dbg & 1)) {
                         uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
 #pragma unroll
-                        for (int c = 0; c < 4; c++)
-                            *(uint4*)(dst + ((((uint32_t)(c + 4 * part)) ^ swz) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                        for (int c = 0; c < 4; c++) {
+                            *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+                            *(uint4*)(dst + ((((uint32_t)(c + 4)) ^ swz) << 4)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+                        }
                     }
                     fence_proxy_async();
                     __syncwarp();
@@ -477,9 +489,10 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// B2_GEMM_DEBUG: diagnostic switches for timing experiments (the results are WRONG when any is set):
-// 1 skip the dequantizers' shared-memory stores, 4 skip the MMAs, 8 skip the epilogue's stores,
-// 16 skip the activation copies.
+// B2_GEMM_DEBUG: diagnostic switches for timing experiments (the results are WRONG when any of the
+// first five is set): 1 skip the dequantizers' shared-memory stores, 2 skip the weight copies, 4 skip
+// the MMAs, 8 skip the epilogue's stores, 16 skip the activation copies; 64 epilogue by direct stores
+// instead of TMA stores; 32768 make CTA (1, 0) write cycle stamps of its phases into the status word.
 int debug_switches() {
     const char* e = getenv("B2_GEMM_DEBUG");
     return e ? atoi(e) : 0;
