@@ -38,6 +38,9 @@ FLOP_PER_STEP = 2.0 * M_TOK * K_IN * N_OUT
 WORKLOAD = "gguf_q4_k_prefill_gemm M=512 K=4096 N=14336 (bf16 activations, f32 output)"
 METRIC = "prefill dequant-GEMM throughput (Q4_K, M=512 K=4096 N=14336)"
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes of one gemm_q4k_tc_kernel launch at this shape, from the ncu capture summarised in
+# profiles/gemm_q4k_tc_M512_K4096_N14336.txt (37.26 MB read + 1.35 MB written; the f32 output stays in L2).
+GEMM_DRAM_TRAFFIC_BYTES = 37_259_520 + 1_354_496
 
 
 def measured_peaks():
@@ -309,7 +312,8 @@ def run_b200(args, rank, world, local_rank):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"kernel": "gemm_q4k_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": None, "us_per_launch": kern_ms * 1e3,
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": GEMM_DRAM_TRAFFIC_BYTES / world if world == 1 else None,
+                         "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture of this kernel at this shape)", "us_per_launch": kern_ms * 1e3,
                          "flop_per_launch": kern_flop, "peak_source": f"bf16 burst, {peaks['source']}"},
         }
         if world == 1 and args.section == "all":

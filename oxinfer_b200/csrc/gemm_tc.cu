@@ -286,7 +286,6 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             const bool in_tile = r < tile_n;
             const uint32_t row_off = (uint32_t)r * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
-            const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
             const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * 144);
             for (int sb = 0; sb < nsb && ok; sb++) {
                 // this row's packed super-block: staging buffer -> registers (only the two 64-groups this set
@@ -304,7 +303,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->raw_empty);
-                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
+                const __half2 dh = __half2half2(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
                 for (int jj = 0; jj < 2; jj++) {
@@ -317,8 +316,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     q4k_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, sc1, mn1);
                     // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
                     // with that sub-block's scale divided by 16 (exact in f16).
-                    const __half2 d1lo = __float2half2_rn(d * (float)sc0), m1lo = __float2half2_rn(-(dmin * (float)mn0));
-                    const __half2 d1hi = __float2half2_rn(d * 0.0625f * (float)sc1), m1hi = __float2half2_rn(-(dmin * (float)mn1));
+                    // Two exact steps: t = n * sc (an integer below 2048, exact in f16: (1024 + n) * sc - 1024 * sc
+                    // inside one fma), then w = t * d - dmin * m with d the block's own f16 value; only the
+                    // min term and the result are rounded.
+                    const __half2 sclo = __float2half2_rn((float)sc0), sclo_k = __float2half2_rn(-1024.0f * (float)sc0);
+                    const __half2 schi = __float2half2_rn(0.0625f * (float)sc1), schi_k = __float2half2_rn(-64.0f * (float)sc1);
+                    const __half2 m1lo = __float2half2_rn(-(dmin * (float)mn0)), m1hi = __float2half2_rn(-(dmin * (float)mn1));
                     const uint32_t qw[8] = {q[2 * jj].x,     q[2 * jj].y,     q[2 * jj].z,     q[2 * jj].w,
                                             q[2 * jj + 1].x, q[2 * jj + 1].y, q[2 * jj + 1].z, q[2 * jj + 1].w};
                     uint32_t lo[16], hi[16];
@@ -328,10 +331,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         uint32_t p0 = __byte_perm(qw[i], 0, 0x4140), p1 = __byte_perm(qw[i], 0, 0x4342);
                         uint32_t l0 = (p0 & 0x000F000Fu) | 0x64006400u, l1 = (p1 & 0x000F000Fu) | 0x64006400u;
                         uint32_t h0 = (p0 & 0x00F000F0u) | 0x64006400u, h1 = (p1 & 0x00F000F0u) | 0x64006400u;
-                        lo[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&l0), k1024), d1lo, m1lo));
-                        lo[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&l1), k1024), d1lo, m1lo));
-                        hi[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h0), k1024), d1hi, m1hi));
-                        hi[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&h1), k1024), d1hi, m1hi));
+                        lo[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l0), sclo, sclo_k), dh, m1lo));
+                        lo[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l1), sclo, sclo_k), dh, m1lo));
+                        hi[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h0), schi, schi_k), dh, m1hi));
+                        hi[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h1), schi, schi_k), dh, m1hi));
                     }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
