@@ -143,6 +143,22 @@ int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, fl
  * the same report for the device-resident calls, which do not synchronize themselves. */
 int b2_check_status(b2_ctx* ctx);
 
+/* No counterpart in the reference (its CUDA backend allocates staging and arena memory freely,
+ * src/cuda.rs:572-699). One Q4_K matrix-vector product, y[n_out] = W x, that allocates nothing, for
+ * hosts that cannot call cudaMalloc when they need it: a server whose own arena already owns the
+ * whole device, or a decode loop that must stay out of the allocator. The activation planes the
+ * kernel needs live in a fixed device array inside the library (57,344 bytes per GPU for as long as
+ * the library is loaded), which limits n_in to B2_NOALLOC_MAX_K; larger inputs are refused with
+ * B2_ERR_ARG and a message, and go through b2_matvec_dev instead.
+ *   w_blocks_dev : raw GGUF Q4_K super-blocks on the device, [n_out][n_in/256][144], 16-byte aligned
+ *   x_dev, y_dev : f32 on the device; cuda_stream : the stream to launch on (NULL = default)
+ *   err, err_len : optional buffer that receives the error text
+ * The first call on a device looks up the array's device address; make it before any stream
+ * capture. All calls share the one array: calls that may overlap on the GPU race on it. */
+#define B2_NOALLOC_MAX_K 16384
+int b2_matvec_q4k_noalloc(const void* w_blocks_dev, size_t n_out, size_t n_in, const float* x_dev, float* y_dev, void* cuda_stream,
+                          char* err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,6 +14,8 @@
 // a warp owns ROWS rows at a time and the vector lives in shared memory, staged once per CTA.
 #include <cuda_fp8.h>
 
+#include <cstdio>
+
 #include "kernels.h"
 
 namespace b2 {
@@ -420,3 +422,87 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
 }
 
 }  // namespace b2
+
+// =============================================================================================
+// b2_matvec_q4k_noalloc: the Q4_K matrix-vector product for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need a product: a serving
+// process that handed the whole device to its own arena at start-up (oxinfer's decode plans carve
+// every buffer out of one arena they own, src/cuda_decode.rs:372-383) has nothing left for the
+// runtime to give, and a latency-critical decode loop must not enter the allocator at all. The
+// regular entry points keep their scratch (the activation planes the GEMV kernels read) in buffers
+// that grow on demand; this one keeps it in a fixed array that is part of the loaded library.
+//
+// The array below is device memory reserved once per GPU for as long as the library stays loaded:
+// 57,344 bytes, enough for an activation vector of B2_NOALLOC_MAX_K = 16384 elements.
+// In host code the name of a __device__ array is only a stand-in: the device address comes from
+// cudaGetSymbolAddress, asked for once per device with that device current (the first call on a
+// device does this set-up, so make that first call outside any stream capture).
+// Every call writes the whole part of the array it uses before reading it, so nothing has to be
+// cleared between calls; but all calls share the one array, so two calls whose kernels can overlap
+// on the GPU (different streams, no dependency between them) race on it. Serialize them.
+// =============================================================================================
+namespace b2 {
+namespace {
+constexpr size_t NOALLOC_MAX_K = 16384;
+constexpr size_t NOALLOC_BYTES = 3 * NOALLOC_MAX_K + 8 * (NOALLOC_MAX_K / 32) + 4 * (NOALLOC_MAX_K / 16);
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of g_noalloc_scratch, per device
+int g_noalloc_sms[NOALLOC_MAX_DEVICES];
+
+int noalloc_fail(char* err, size_t err_len, int code, const char* text, cudaError_t e = cudaSuccess) {
+    if (err && err_len) {
+        if (e != cudaSuccess)
+            snprintf(err, err_len, "[b200qmm: matvec_q4k_noalloc: %s: %s]", text, cudaGetErrorString(e));
+        else
+            snprintf(err, err_len, "[b200qmm: matvec_q4k_noalloc: %s]", text);
+    }
+    return code;
+}
+}  // namespace
+}  // namespace b2
+
+extern "C" __attribute__((visibility("default"))) int b2_matvec_q4k_noalloc(const void* w_blocks_dev, size_t n_out, size_t n_in,
+                                                                             const float* x_dev, float* y_dev, void* cuda_stream,
+                                                                             char* err, size_t err_len) {
+    using namespace b2;
+    if (!w_blocks_dev || !x_dev || !y_dev || n_out == 0) return noalloc_fail(err, err_len, B2_ERR_ARG, "null pointer or empty matrix");
+    if (n_in == 0 || n_in % 256 != 0) return noalloc_fail(err, err_len, B2_ERR_ARG, "n_in must be a positive multiple of 256 (Q4_K super-blocks)");
+    if (n_in > NOALLOC_MAX_K) {
+        if (err && err_len)
+            snprintf(err, err_len, "[b200qmm: matvec_q4k_noalloc: n_in = %zu exceeds the built-in scratch (at most %zu); use b2_matvec_dev]", n_in,
+                     NOALLOC_MAX_K);
+        return B2_ERR_ARG;
+    }
+    if (((uintptr_t)w_blocks_dev & 15) || ((uintptr_t)x_dev & 3) || ((uintptr_t)y_dev & 3))
+        return noalloc_fail(err, err_len, B2_ERR_ARG, "weights must be 16-byte aligned, x and y 4-byte aligned");
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, B2_ERR_CUDA, "cudaGetDevice", e);
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return noalloc_fail(err, err_len, B2_ERR_ARG, "device ordinal out of range");
+    if (!g_noalloc_ptr[dev]) {
+        // once per device, with that device current: the device-side address of the scratch array
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return noalloc_fail(err, err_len, B2_ERR_CUDA, "cudaGetSymbolAddress(scratch)", e);
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms <= 0) return noalloc_fail(err, err_len, B2_ERR_CUDA, "cudaDeviceGetAttribute", e);
+        g_noalloc_sms[dev] = sms;
+        g_noalloc_ptr[dev] = p;
+    }
+    WeightDev w{};
+    w.fmt = B2_FMT_Q4_K;
+    w.n_out = n_out;
+    w.n_in = n_in;
+    w.p0 = (const uint8_t*)w_blocks_dev;
+    XPlanes xp = xplanes_at(g_noalloc_ptr[dev], n_in);
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    e = launch_xplanes(x_dev, n_in, 0, xp, st);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, B2_ERR_CUDA, "activation planes kernel", e);
+    e = launch_gemv(w, nullptr, x_dev, xp, y_dev, B2_MODE_STORE, nullptr, g_noalloc_sms[dev], st);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, B2_ERR_CUDA, "gemv kernel", e);
+    return B2_OK;
+}
