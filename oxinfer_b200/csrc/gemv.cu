@@ -10,8 +10,11 @@
 // exact product by the 2^-21 rounding of x only. FP8 weights take the float path (hardware
 // e4m3x2 -> f16x2 conversion), with f32 x.
 //
-// Every lane issues all of its 16-byte weight loads for a row group before using any of them;
-// a warp owns ROWS rows at a time and the vector lives in shared memory, staged once per CTA.
+// A warp owns two weight rows at a time (or, for the fused SiLU / GELU pair, the same row of the
+// gate and the up matrix): every lane issues the 16-byte weight loads of both before using either,
+// and reads its slice of the activation planes from shared memory once for both. The planes are
+// staged once per CTA, with their 16-byte slots permuted so that the eight lanes of a shared-memory
+// phase, which read 64 bytes each at a 64-byte stride, fall on different banks.
 #include <cuda_fp8.h>
 
 #include <cstdio>
@@ -67,18 +70,43 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
     }
 }
 
-// The vector as the kernels see it in shared memory.
+// The vector as the kernels see it in shared memory. Plane p is K bytes at p0 + p K with its 16-byte
+// slots permuted by swz(); `sx` holds {block scale, block sum} pairs per block of 32.
 struct XS {
-    const int8_t* p0;  // plane 0, K bytes; planes 1 and 2 follow at +K, +2K
-    const float* xs;
-    const float* xsum;
+    const uint8_t* p0;
+    const float2* sx;
     const int32_t* v16;
-    const float* xf;  // FP8: the f32 vector
+    const float* xf;  // FP8: the f32 vector (slots permuted the same way)
     int K;
 };
 
+// Slot g -> g with its low two bits xor-ed by bits 3 and 4: lanes L = 0..7 of a phase that read slots
+// 4 L + i (a 64-byte stride) then cover all eight 16-byte bank groups for every i.
+__device__ __forceinline__ int swz(int g) { return g ^ ((((g >> 3) & 1) << 1) | ((g >> 4) & 1)); }
+
+__device__ __forceinline__ uint4 plane16(const XS& x, int p, int k) {  // 16 plane bytes at element k (k % 16 == 0)
+    return *(const uint4*)(x.p0 + (size_t)p * x.K + ((size_t)swz(k >> 4) << 4));
+}
+__device__ __forceinline__ void plane64(const XS& x, int p, int k0, uint32_t (&w)[16]) {  // 64 plane bytes at k0 (k0 % 64 == 0)
+    const uint8_t* base = x.p0 + (size_t)p * x.K;
+    const int g0 = k0 >> 4, c = (((g0 >> 3) & 1) << 1) | ((g0 >> 4) & 1);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint4 v = *(const uint4*)(base + ((size_t)(g0 + (i ^ c)) << 4));
+        w[4 * i] = v.x;
+        w[4 * i + 1] = v.y;
+        w[4 * i + 2] = v.z;
+        w[4 * i + 3] = v.w;
+    }
+}
+
 __device__ __forceinline__ int dp(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 __device__ __forceinline__ int planes3(int a0, int a1, int a2) { return a0 + (a1 << 7) + (a2 << 14); }
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {  // streamed once: keep it out of L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 __device__ __forceinline__ float silu(float a) { return a / (1.0f + __expf(-a)); }
 __device__ __forceinline__ float gelu_tanh(float a) {
@@ -86,8 +114,8 @@ __device__ __forceinline__ float gelu_tanh(float a) {
     return 0.5f * a * (1.0f + tanhf(t));
 }
 
-// ---- per-format row pieces: `load` issues the global loads of one warp-iteration of one row,
-// `dot` consumes them against the vector. An iteration covers ITER_K consecutive k.
+// ---- per-format pieces: `load` issues the global loads of one warp-iteration of one row, `dot2`
+// consumes two rows' loads against the vector (planes read once). An iteration covers ITER_K k.
 
 struct FmtQ4K {
     static constexpr int ITER_K = 2048;  // 8 super-blocks, 4 lanes each (one 64-group per lane)
@@ -97,41 +125,56 @@ struct FmtQ4K {
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
     __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
         const uint8_t* blk = w.p0 + (row * (w.n_in / 256) + it * 8 + (lane >> 2)) * 144;
-        r.hdr = __ldg((const uint4*)blk);
-        r.q0 = __ldg((const uint4*)(blk + 16 + 32 * (lane & 3)));
-        r.q1 = __ldg((const uint4*)(blk + 32 + 32 * (lane & 3)));
+        r.hdr = __ldg((const uint4*)blk);  // shared by the four lanes of the super-block: let it hit L1
+        r.q0 = ldg_stream(blk + 16 + 32 * (lane & 3));
+        r.q1 = ldg_stream(blk + 32 + 32 * (lane & 3));
     }
-    __device__ static __forceinline__ float dot(const Regs& r, const XS& x, int it, int lane) {
-        int j = lane & 3;
-        int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
+    __device__ static __forceinline__ void scales(const Regs& r, int j, float& d0, float& d1, float& m0, float& m1) {
         float d = __half2float(__ushort_as_half((unsigned short)(r.hdr.x & 0xffff)));
         float dmin = __half2float(__ushort_as_half((unsigned short)(r.hdr.x >> 16)));
         uint32_t sc0, mn0, sc1, mn1;
         q4k_scale_min(2 * j, r.hdr.y, r.hdr.z, r.hdr.w, sc0, mn0);
         q4k_scale_min(2 * j + 1, r.hdr.y, r.hdr.z, r.hdr.w, sc1, mn1);
-        const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
-        int lo[3], hi[3];
+        d0 = d * (float)sc0;
+        d1 = d * (float)sc1;
+        m0 = dmin * (float)mn0;
+        m1 = dmin * (float)mn1;
+    }
+    __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
+        const int j = lane & 3;
+        const int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
+        const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
+        const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
+        int la[3], ha[3], lb[3], hb[3];
 #pragma unroll
         for (int p = 0; p < 3; p++) {
-            const uint4* xp = (const uint4*)(x.p0 + (size_t)p * x.K + k0);
-            uint4 a = xp[0], b = xp[1], c = xp[2], e = xp[3];
-            const uint32_t xl[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            const uint32_t xh[8] = {c.x, c.y, c.z, c.w, e.x, e.y, e.z, e.w};
-            int sl = 0, sh = 0;
+            uint32_t xw[16];
+            plane64(x, p, k0, xw);
+            int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                sl = dp(qw[i] & 0x0F0F0F0Fu, xl[i], sl);
-                sh = dp((qw[i] >> 4) & 0x0F0F0F0Fu, xh[i], sh);
+                s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[i], s0);
+                s1 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s1);
+                s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[i], s2);
+                s3 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s3);
             }
-            lo[p] = sl;
-            hi[p] = sh;
+            la[p] = s0;
+            ha[p] = s1;
+            lb[p] = s2;
+            hb[p] = s3;
         }
-        int b0 = k0 >> 5;
-        float acc = (d * (float)sc0) * x.xs[b0] * (float)planes3(lo[0], lo[1], lo[2]);
-        acc = fmaf((d * (float)sc1) * x.xs[b0 + 1], (float)planes3(hi[0], hi[1], hi[2]), acc);
-        acc = fmaf(-(dmin * (float)mn0), x.xsum[b0], acc);
-        acc = fmaf(-(dmin * (float)mn1), x.xsum[b0 + 1], acc);
-        return acc;
+        const float4 sx = *(const float4*)(x.sx + (k0 >> 5));  // {xs, xsum} of the two blocks of 32
+        float d0, d1, m0, m1;
+        scales(a, j, d0, d1, m0, m1);
+        accA = fmaf(d0 * sx.x, (float)planes3(la[0], la[1], la[2]), accA);
+        accA = fmaf(d1 * sx.z, (float)planes3(ha[0], ha[1], ha[2]), accA);
+        accA = fmaf(-m0, sx.y, accA);
+        accA = fmaf(-m1, sx.w, accA);
+        scales(b, j, d0, d1, m0, m1);
+        accB = fmaf(d0 * sx.x, (float)planes3(lb[0], lb[1], lb[2]), accB);
+        accB = fmaf(d1 * sx.z, (float)planes3(hb[0], hb[1], hb[2]), accB);
+        accB = fmaf(-m0, sx.y, accB);
+        accB = fmaf(-m1, sx.w, accB);
     }
 };
 
@@ -144,43 +187,56 @@ struct FmtMLX4 {
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 32 + lane < K / 64; }
     __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
         size_t g = row * (w.n_in / 64) + it * 32 + lane;
-        const uint4* q = (const uint4*)(w.p0 + g * 32);
-        r.q0 = __ldg(q);
-        r.q1 = __ldg(q + 1);
+        r.q0 = ldg_stream(w.p0 + g * 32);
+        r.q1 = ldg_stream(w.p0 + g * 32 + 16);
         r.sb = (uint32_t)__ldg((const uint16_t*)w.p1 + g) | ((uint32_t)__ldg((const uint16_t*)w.p2 + g) << 16);
     }
-    __device__ static __forceinline__ float dot(const Regs& r, const XS& x, int it, int lane) {
-        int k0 = (it * 32 + lane) * 64;
-        // The CPU path's values (src/quant.rs:518-563,586-606): d = f16(scale), offset = bf16(bias + 8 scale),
-        // w = (nib - 8) d + offset = nib d + (offset - 8 d).
-        float s = bf16_bits_to_f32(r.sb & 0xffff), b = bf16_bits_to_f32(r.sb >> 16);
-        float d = __half2float(__float2half_rn(s));
-        float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(b, __fmul_rn(8.0f, s))));
-        const uint32_t qw[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
-        int sa[3], sb[3];
+    __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
+        const int k0 = (it * 32 + lane) * 64;
+        const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
+        const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
+        int a0[3], a1[3], b0[3], b1[3];
 #pragma unroll
         for (int p = 0; p < 3; p++) {
             // perm8 layout: word pair (2i, 2i+1) of the plane holds the even / odd elements of weight word i
-            const uint4* xp = (const uint4*)(x.p0 + (size_t)p * x.K + k0);
-            uint4 a = xp[0], bq = xp[1], c = xp[2], e = xp[3];
-            const uint32_t xw[16] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w, c.x, c.y, c.z, c.w, e.x, e.y, e.z, e.w};
-            int s0 = 0, s1 = 0;
+            uint32_t xw[16];
+            plane64(x, p, k0, xw);
+            int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                s0 = dp(qw[i] & 0x0F0F0F0Fu, xw[2 * i], s0);
-                s0 = dp((qw[i] >> 4) & 0x0F0F0F0Fu, xw[2 * i + 1], s0);
-                s1 = dp(qw[4 + i] & 0x0F0F0F0Fu, xw[8 + 2 * i], s1);
-                s1 = dp((qw[4 + i] >> 4) & 0x0F0F0F0Fu, xw[8 + 2 * i + 1], s1);
+                s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[2 * i], s0);
+                s0 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[2 * i + 1], s0);
+                s1 = dp(qa[4 + i] & 0x0F0F0F0Fu, xw[8 + 2 * i], s1);
+                s1 = dp((qa[4 + i] >> 4) & 0x0F0F0F0Fu, xw[8 + 2 * i + 1], s1);
+                s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[2 * i], s2);
+                s2 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[2 * i + 1], s2);
+                s3 = dp(qb[4 + i] & 0x0F0F0F0Fu, xw[8 + 2 * i], s3);
+                s3 = dp((qb[4 + i] >> 4) & 0x0F0F0F0Fu, xw[8 + 2 * i + 1], s3);
             }
-            sa[p] = s0;
-            sb[p] = s1;
+            a0[p] = s0;
+            a1[p] = s1;
+            b0[p] = s2;
+            b1[p] = s3;
         }
-        int b0 = k0 >> 5;
-        float dots = x.xs[b0] * (float)planes3(sa[0], sa[1], sa[2]);
-        dots = fmaf(x.xs[b0 + 1], (float)planes3(sb[0], sb[1], sb[2]), dots);
-        float acc = d * dots;
-        acc = fmaf(off - 8.0f * d, x.xsum[b0] + x.xsum[b0 + 1], acc);
-        return acc;
+        const float4 sx = *(const float4*)(x.sx + (k0 >> 5));
+        // The CPU path's values (src/quant.rs:518-563,586-606): d = f16(scale), offset = bf16(bias + 8 scale),
+        // w = (nib - 8) d + offset = nib d + (offset - 8 d).
+        {
+            float s = bf16_bits_to_f32(a.sb & 0xffff), bb = bf16_bits_to_f32(a.sb >> 16);
+            float d = __half2float(__float2half_rn(s));
+            float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
+            float dots = fmaf(sx.z, (float)planes3(a1[0], a1[1], a1[2]), sx.x * (float)planes3(a0[0], a0[1], a0[2]));
+            accA = fmaf(d, dots, accA);
+            accA = fmaf(off - 8.0f * d, sx.y + sx.w, accA);
+        }
+        {
+            float s = bf16_bits_to_f32(b.sb & 0xffff), bb = bf16_bits_to_f32(b.sb >> 16);
+            float d = __half2float(__float2half_rn(s));
+            float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
+            float dots = fmaf(sx.z, (float)planes3(b1[0], b1[1], b1[2]), sx.x * (float)planes3(b0[0], b0[1], b0[2]));
+            accB = fmaf(d, dots, accB);
+            accB = fmaf(off - 8.0f * d, sx.y + sx.w, accB);
+        }
     }
 };
 
@@ -196,47 +252,54 @@ struct FmtQ6K {
         size_t K = w.n_in;
         size_t blk = it * 8 + (lane >> 2);
         int n = (lane >> 1) & 1, u = lane & 1;
-        r.qh = __ldg((const uint4*)(w.p1 + row * (K / 4) + blk * 64 + 32 * n + 16 * u));
-        r.qa = __ldg((const uint4*)(w.p0 + row * (K / 2) + blk * 128 + 64 * n + 16 * u));
-        r.qb = __ldg((const uint4*)(w.p0 + row * (K / 2) + blk * 128 + 64 * n + 32 + 16 * u));
+        r.qh = ldg_stream(w.p1 + row * (K / 4) + blk * 64 + 32 * n + 16 * u);
+        r.qa = ldg_stream(w.p0 + row * (K / 2) + blk * 128 + 64 * n + 16 * u);
+        r.qb = ldg_stream(w.p0 + row * (K / 2) + blk * 128 + 64 * n + 32 + 16 * u);
         r.sc = __ldg((const uint2*)(w.p2 + row * (K / 16) + blk * 16 + 8 * n));
         r.d = __ldg((const uint16_t*)w.p3 + row * (K / 256) + blk);
     }
-    __device__ static __forceinline__ float dot(const Regs& r, const XS& x, int it, int lane) {
-        int n = (lane >> 1) & 1, u = lane & 1;
-        int kb = (it * 8 + (lane >> 2)) * 256 + 128 * n + 16 * u;  // quarter k4 adds 32 k4
-        float d = __half2float(__ushort_as_half((unsigned short)r.d));
-        const uint32_t H[4] = {r.qh.x, r.qh.y, r.qh.z, r.qh.w};
-        const uint32_t A[4] = {r.qa.x, r.qa.y, r.qa.z, r.qa.w};
-        const uint32_t B[4] = {r.qb.x, r.qb.y, r.qb.z, r.qb.w};
-        uint64_t scw = (uint64_t)r.sc.x | ((uint64_t)r.sc.y << 32);
-        float acc = 0.0f;
+    __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
+        const int n = (lane >> 1) & 1, u = lane & 1;
+        const int kb = (it * 8 + (lane >> 2)) * 256 + 128 * n + 16 * u;  // quarter k4 adds 32 k4
+        const float da = __half2float(__ushort_as_half((unsigned short)a.d)), db = __half2float(__ushort_as_half((unsigned short)b.d));
+        const uint32_t HA[4] = {a.qh.x, a.qh.y, a.qh.z, a.qh.w}, AA[4] = {a.qa.x, a.qa.y, a.qa.z, a.qa.w}, BA[4] = {a.qb.x, a.qb.y, a.qb.z, a.qb.w};
+        const uint32_t HB[4] = {b.qh.x, b.qh.y, b.qh.z, b.qh.w}, AB[4] = {b.qa.x, b.qa.y, b.qa.z, b.qa.w}, BB[4] = {b.qb.x, b.qb.y, b.qb.z, b.qb.w};
+        const uint64_t sca = (uint64_t)a.sc.x | ((uint64_t)a.sc.y << 32), scb = (uint64_t)b.sc.x | ((uint64_t)b.sc.y << 32);
 #pragma unroll
         for (int k4 = 0; k4 < 4; k4++) {
-            uint32_t q[4];
+            uint32_t qa[4], qb[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                uint32_t lo = (k4 & 1) ? B[i] : A[i];
+                uint32_t lo = (k4 & 1) ? BA[i] : AA[i];
                 lo = (k4 & 2) ? (lo >> 4) : lo;
-                uint32_t hb = (k4 == 0) ? (H[i] << 4) : (k4 == 1) ? (H[i] << 2) : (k4 == 2) ? H[i] : (H[i] >> 2);
-                q[i] = (lo & 0x0F0F0F0Fu) | (hb & 0x30303030u);
+                uint32_t hb = (k4 == 0) ? (HA[i] << 4) : (k4 == 1) ? (HA[i] << 2) : (k4 == 2) ? HA[i] : (HA[i] >> 2);
+                qa[i] = (lo & 0x0F0F0F0Fu) | (hb & 0x30303030u);
+                lo = (k4 & 1) ? BB[i] : AB[i];
+                lo = (k4 & 2) ? (lo >> 4) : lo;
+                hb = (k4 == 0) ? (HB[i] << 4) : (k4 == 1) ? (HB[i] << 2) : (k4 == 2) ? HB[i] : (HB[i] >> 2);
+                qb[i] = (lo & 0x0F0F0F0Fu) | (hb & 0x30303030u);
             }
-            int k0 = kb + 32 * k4;
-            int s[3];
+            const int k0 = kb + 32 * k4;
+            int sa[3], sb[3];
 #pragma unroll
             for (int p = 0; p < 3; p++) {
-                uint4 xv = *(const uint4*)(x.p0 + (size_t)p * x.K + k0);
-                int a = dp(q[0], xv.x, 0);
-                a = dp(q[1], xv.y, a);
-                a = dp(q[2], xv.z, a);
-                a = dp(q[3], xv.w, a);
-                s[p] = a;
+                uint4 xv = plane16(x, p, k0);
+                int t = dp(qa[0], xv.x, 0);
+                t = dp(qa[1], xv.y, t);
+                t = dp(qa[2], xv.z, t);
+                sa[p] = dp(qa[3], xv.w, t);
+                t = dp(qb[0], xv.x, 0);
+                t = dp(qb[1], xv.y, t);
+                t = dp(qb[2], xv.z, t);
+                sb[p] = dp(qb[3], xv.w, t);
             }
-            int total = planes3(s[0], s[1], s[2]) - 32 * x.v16[k0 >> 4];
-            float scale = (float)(int8_t)((scw >> (8 * (u + 2 * k4))) & 0xff);
-            acc = fmaf((d * scale) * x.xs[k0 >> 5], (float)total, acc);
+            const int off32 = 32 * x.v16[k0 >> 4];
+            const float xs = x.sx[k0 >> 5].x;
+            const float scale_a = (float)(int8_t)((sca >> (8 * (u + 2 * k4))) & 0xff);
+            const float scale_b = (float)(int8_t)((scb >> (8 * (u + 2 * k4))) & 0xff);
+            accA = fmaf((da * scale_a) * xs, (float)(planes3(sa[0], sa[1], sa[2]) - off32), accA);
+            accB = fmaf((db * scale_b) * xs, (float)(planes3(sb[0], sb[1], sb[2]) - off32), accB);
         }
-        return acc;
     }
 };
 
@@ -249,23 +312,27 @@ struct FmtQ8_0 {
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 512 + lane * 16 < K; }
     __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
         size_t k0 = (size_t)it * 512 + lane * 16;
-        r.q = __ldg((const uint4*)(w.p0 + row * w.n_in + k0));
+        r.q = ldg_stream(w.p0 + row * w.n_in + k0);
         r.d = __ldg((const uint16_t*)w.p1 + row * (w.n_in / 32) + k0 / 32);
     }
-    __device__ static __forceinline__ float dot(const Regs& r, const XS& x, int it, int lane) {
-        int k0 = it * 512 + lane * 16;
-        int s[3];
+    __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
+        const int k0 = it * 512 + lane * 16;
+        int sa[3], sb[3];
 #pragma unroll
         for (int p = 0; p < 3; p++) {
-            uint4 xv = *(const uint4*)(x.p0 + (size_t)p * x.K + k0);
-            int a = dp(r.q.x, xv.x, 0);
-            a = dp(r.q.y, xv.y, a);
-            a = dp(r.q.z, xv.z, a);
-            a = dp(r.q.w, xv.w, a);
-            s[p] = a;
+            uint4 xv = plane16(x, p, k0);
+            int t = dp(a.q.x, xv.x, 0);
+            t = dp(a.q.y, xv.y, t);
+            t = dp(a.q.z, xv.z, t);
+            sa[p] = dp(a.q.w, xv.w, t);
+            t = dp(b.q.x, xv.x, 0);
+            t = dp(b.q.y, xv.y, t);
+            t = dp(b.q.z, xv.z, t);
+            sb[p] = dp(b.q.w, xv.w, t);
         }
-        float d = __half2float(__ushort_as_half((unsigned short)r.d));
-        return (d * x.xs[k0 >> 5]) * (float)planes3(s[0], s[1], s[2]);
+        const float xs = x.sx[k0 >> 5].x;
+        accA = fmaf(__half2float(__ushort_as_half((unsigned short)a.d)) * xs, (float)planes3(sa[0], sa[1], sa[2]), accA);
+        accB = fmaf(__half2float(__ushort_as_half((unsigned short)b.d)) * xs, (float)planes3(sb[0], sb[1], sb[2]), accB);
     }
 };
 
@@ -278,31 +345,36 @@ struct FmtF8 {
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 512 + lane * 16 < K; }
     __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
         size_t k0 = (size_t)it * 512 + lane * 16;
-        r.q = __ldg((const uint4*)(w.p0 + row * w.n_in + k0));
+        r.q = ldg_stream(w.p0 + row * w.n_in + k0);
         r.s = w.p1 ? __ldg((const float*)w.p1 + ((w.bs_row0 + row) / w.bs_rows) * w.bs_ncb + k0 / w.bs_cols) : 1.0f;
     }
-    __device__ static __forceinline__ float dot(const Regs& r, const XS& x, int it, int lane) {
-        int k0 = it * 512 + lane * 16;
-        const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
-        const float4* xv = (const float4*)(x.xf + k0);
-        float part = 0.0f;
+    __device__ static __forceinline__ float part(uint32_t q, float4 xx, float acc) {
+        __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(q & 0xffff), __NV_E4M3);
+        __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(q >> 16), __NV_E4M3);
+        float2 f01 = __half22float2(*(const __half2*)&h01), f23 = __half22float2(*(const __half2*)&h23);
+        acc = fmaf(f01.x, xx.x, acc);
+        acc = fmaf(f01.y, xx.y, acc);
+        acc = fmaf(f23.x, xx.z, acc);
+        return fmaf(f23.y, xx.w, acc);
+    }
+    __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
+        const int k0 = it * 512 + lane * 16;  // 16 floats = four 16-byte slots, permuted like the planes
+        const int g0 = k0 >> 2, c = (((g0 >> 3) & 1) << 1) | ((g0 >> 4) & 1);
+        const uint32_t qa[4] = {a.q.x, a.q.y, a.q.z, a.q.w}, qb[4] = {b.q.x, b.q.y, b.q.z, b.q.w};
+        float pa = 0.0f, pb = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            float4 xx = xv[i];
-            __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(qw[i] & 0xffff), __NV_E4M3);
-            __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(qw[i] >> 16), __NV_E4M3);
-            float2 f01 = __half22float2(*(const __half2*)&h01), f23 = __half22float2(*(const __half2*)&h23);
-            part = fmaf(f01.x, xx.x, part);
-            part = fmaf(f01.y, xx.y, part);
-            part = fmaf(f23.x, xx.z, part);
-            part = fmaf(f23.y, xx.w, part);
+            float4 xx = *(const float4*)(x.xf + ((size_t)(g0 + (i ^ c)) << 2));
+            pa = part(qa[i], xx, pa);
+            pb = part(qb[i], xx, pb);
         }
-        return part * r.s;
+        accA = fmaf(pa, a.s, accA);
+        accB = fmaf(pb, b.s, accB);
     }
 };
 
-template <class F, int ROWS, bool PAIR, bool XF32>
-__global__ void __launch_bounds__(GEMV_THREADS)
+template <class F, bool PAIR, bool XF32>
+__global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
             const float* __restrict__ gate) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -311,61 +383,61 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
     xs.K = K;
     if constexpr (XF32) {
         float* xf = (float*)smem;
-        for (int i = threadIdx.x; i < K / 4; i += GEMV_THREADS) ((float4*)xf)[i] = ((const float4*)x)[i];
+        for (int g = threadIdx.x; g < K / 4; g += GEMV_THREADS) ((float4*)xf)[swz(g)] = ((const float4*)x)[g];
         xs.xf = xf;
         xs.p0 = nullptr;
-        xs.xs = xs.xsum = nullptr;
+        xs.sx = nullptr;
         xs.v16 = nullptr;
     } else {
-        // planes | xs | xsum | v16 are contiguous in global memory in this order: one 16-byte copy loop
-        size_t bytes = xplanes_bytes((size_t)K);
+        const int slots = K / 16;  // per plane
         const uint4* src = (const uint4*)xp.planes;
-        for (int i = threadIdx.x; i < (int)(bytes / 16); i += GEMV_THREADS) ((uint4*)smem)[i] = src[i];
-        xs.p0 = (const int8_t*)smem;
-        xs.xs = (const float*)(smem + 3 * (size_t)K);
-        xs.xsum = xs.xs + K / 32;
-        xs.v16 = (const int32_t*)(xs.xsum + K / 32);
+        uint4* dst = (uint4*)smem;
+        for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
+            int p = i / slots, g = i - p * slots;
+            dst[p * slots + swz(g)] = src[i];
+        }
+        float2* sx = (float2*)(smem + 3 * (size_t)K);
+        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
+        int32_t* v16 = (int32_t*)(sx + K / 32);
+        for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xp.v16[b];
+        xs.p0 = smem;
+        xs.sx = sx;
+        xs.v16 = v16;
         xs.xf = nullptr;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t n_out = w.n_out;
     const int iters = (K + F::ITER_K - 1) / F::ITER_K;
-    for (size_t r0 = ((size_t)blockIdx.x * GEMV_WARPS + warp) * ROWS; r0 < n_out; r0 += (size_t)gridDim.x * GEMV_WARPS * ROWS) {
-        float acc[ROWS], acc2[ROWS];
-#pragma unroll
-        for (int r = 0; r < ROWS; r++) acc[r] = acc2[r] = 0.0f;
+    constexpr int RW = PAIR ? 1 : 2;  // output rows per warp pass
+    for (size_t r0 = ((size_t)blockIdx.x * GEMV_WARPS + warp) * RW; r0 < n_out; r0 += (size_t)gridDim.x * GEMV_WARPS * RW) {
+        const size_t rowA = r0, rowB = PAIR ? r0 : min(r0 + 1, n_out - 1);
+        float accA = 0.0f, accB = 0.0f;
         for (int it = 0; it < iters; it++) {
             if (!F::active(K, it, lane)) continue;
-            typename F::Regs regs[ROWS], regs2[PAIR ? ROWS : 1];
-#pragma unroll
-            for (int r = 0; r < ROWS; r++) {
-                size_t row = min(r0 + r, n_out - 1);
-                F::load(w, row, it, lane, regs[r]);
-                if constexpr (PAIR) F::load(w2, row, it, lane, regs2[r]);
-            }
-#pragma unroll
-            for (int r = 0; r < ROWS; r++) {
-                acc[r] += F::dot(regs[r], xs, it, lane);
-                if constexpr (PAIR) acc2[r] += F::dot(regs2[r], xs, it, lane);
-            }
+            typename F::Regs ra, rb;
+            F::load(w, rowA, it, lane, ra);
+            F::load(PAIR ? w2 : w, rowB, it, lane, rb);
+            F::dot2(ra, rb, xs, it, lane, accA, accB);
         }
+        accA = warp_sum(accA);
+        accB = warp_sum(accB);
+        if (lane == 0) {
+            if (PAIR) {
+                y[r0] = (mode == B2_MODE_SILU_PAIR ? silu(accA) : gelu_tanh(accA)) * accB;
+            } else {
 #pragma unroll
-        for (int r = 0; r < ROWS; r++) {
-            float a = warp_sum(acc[r]);
-            float b = PAIR ? warp_sum(acc2[r]) : 0.0f;
-            if (lane == 0 && r0 + r < n_out) {
-                float* o = y + r0 + r;
-                if (mode == B2_MODE_STORE)
-                    *o = a;
-                else if (mode == B2_MODE_ADD)
-                    *o += a;
-                else if (mode == B2_MODE_SILU_PAIR)
-                    *o = silu(a) * b;
-                else if (mode == B2_MODE_GELU_PAIR)
-                    *o = gelu_tanh(a) * b;
-                else
-                    *o += a * (1.0f / (1.0f + __expf(-gate[0])));
+                for (int r = 0; r < 2; r++) {
+                    if (r0 + r >= n_out) break;
+                    const float a = r ? accB : accA;
+                    float* o = y + r0 + r;
+                    if (mode == B2_MODE_STORE)
+                        *o = a;
+                    else if (mode == B2_MODE_ADD)
+                        *o += a;
+                    else
+                        *o += a * (1.0f / (1.0f + __expf(-gate[0])));
+                }
             }
         }
     }
@@ -374,17 +446,17 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                        int sm_count, cudaStream_t st) {
-    constexpr int ROWS = 2;
     size_t smem = XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in);
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
-    auto kern = pair ? gemv_kernel<F, ROWS, true, XF32> : gemv_kernel<F, ROWS, false, XF32>;
+    auto kern = pair ? gemv_kernel<F, true, XF32> : gemv_kernel<F, false, XF32>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    size_t groups = (w.n_out + (size_t)GEMV_WARPS * ROWS - 1) / ((size_t)GEMV_WARPS * ROWS);
-    size_t per_sm = smem ? (size_t)(220 * 1024) / (smem + 1024) : 8;
-    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
+    size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
+    size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
     kern<<<(unsigned)grid, GEMV_THREADS, smem, st>>>(w, pair ? *up : w, x, xp, y, mode, gate);
     return cudaGetLastError();
@@ -394,10 +466,10 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
 
 bool gemv_supports(const WeightDev& w) {
     switch (w.fmt) {
-        case B2_FMT_MLX4: return w.group == 64 && w.n_in % 64 == 0 && w.n_in * 3 + w.n_in / 2 <= 200 * 1024;
+        case B2_FMT_MLX4: return w.group == 64 && w.n_in % 64 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
         case B2_FMT_Q4_K:
         case B2_FMT_Q6_K: return w.n_in % 256 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
-        case B2_FMT_Q8_0: return w.n_in % 32 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
+        case B2_FMT_Q8_0: return w.n_in % 64 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
         case B2_FMT_F8E4M3: return w.n_in % 16 == 0 && w.n_in * 4 <= 200 * 1024 && (w.p1 == nullptr || w.bs_cols % 16 == 0);
         default: return false;
     }
