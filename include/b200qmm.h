@@ -99,7 +99,7 @@ int b2_wants(b2_ctx* ctx, size_t n_out, size_t n_in, size_t t);
 
 /* `Backend::upload` for WeightRef::Q4 with offsets, src/cuda.rs:640-699, taking the MLX triple as
  * it is on disk (src/safetensors.rs:767-853): w `[n_out][n_in/8]` u32, scales and biases
- * `[n_out][n_in/group]` bf16 bits. group must be 64; n_in a multiple of 64. */
+ * `[n_out][n_in/group]` bf16 bits. group must be 64; n_in a multiple of 256. Repacked on the device into Q4_K-shaped blocks. */
 int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in,
                    size_t group, b2_weight* out);
 /* `Backend::upload` for WeightRef::Gguf (declined by the reference at src/cuda.rs:642): raw GGUF

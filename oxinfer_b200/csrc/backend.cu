@@ -109,24 +109,35 @@ class Backend {
     int upload_mlx4(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in, size_t group,
                     uint64_t* out) {
         if (!w || !scales || !biases || !out) return fail(B2_ERR_ARG, "[b200qmm: upload_mlx4: null argument]");
-        if (group != 64 || n_in % 64 != 0 || n_out == 0) return fail(B2_DECLINED, "[b200qmm: upload_mlx4: group must be 64 and n_in a multiple of 64]");
+        if (group != 64 || n_in % 256 != 0 || n_out == 0)
+            return fail(B2_DECLINED, "[b200qmm: upload_mlx4: group must be 64 and n_in a multiple of 256]");
+        // The triple is repacked on the device into Q4_K-shaped blocks (formats.cuh): same bytes per weight,
+        // and every 4-bit kernel then serves both formats. The reference repacks too (from_mlx_q4).
         Weight wt;
-        void *p0, *p1, *p2;
+        std::vector<void*> tmp;
+        void *p0, *p1, *p2, *blocks;
         int rc;
-        if ((rc = alloc_copy(w, n_out * n_in / 2, &p0, wt.owned)) || (rc = alloc_copy(scales, n_out * (n_in / 64) * 2, &p1, wt.owned)) ||
-            (rc = alloc_copy(biases, n_out * (n_in / 64) * 2, &p2, wt.owned))) {
+        size_t nb = n_out * (n_in / 256);
+        if ((rc = alloc_copy(w, n_out * n_in / 2, &p0, tmp)) || (rc = alloc_copy(scales, n_out * (n_in / 64) * 2, &p1, tmp)) ||
+            (rc = alloc_copy(biases, n_out * (n_in / 64) * 2, &p2, tmp)) || (rc = alloc_copy(nullptr, nb * 144, &blocks, wt.owned))) {
+            drop(tmp);
             drop(wt.owned);
             return rc;
         }
-        cudaStreamSynchronize(stream);
+        cudaError_t e = launch_repack_mlx4((const uint32_t*)p0, (const uint16_t*)p1, (const uint16_t*)p2, n_out, n_in, (uint8_t*)blocks, stream);
+        launches++;
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        drop(tmp);
+        if (e != cudaSuccess) {
+            drop(wt.owned);
+            return cuda_fail(e, "repack_mlx4");
+        }
         wt.dev.fmt = B2_FMT_MLX4;
         wt.dev.n_out = n_out;
         wt.dev.n_in = n_in;
         wt.dev.group = group;
-        wt.dev.p0 = (const uint8_t*)p0;
-        wt.dev.p1 = (const uint8_t*)p1;
-        wt.dev.p2 = (const uint8_t*)p2;
-        wt.bytes = n_out * n_in / 2 + 2 * n_out * (n_in / 64) * 2;
+        wt.dev.p0 = (const uint8_t*)blocks;
+        wt.bytes = nb * 144;
         *out = next_handle++;
         weights[*out] = std::move(wt);
         return B2_OK;
@@ -236,10 +247,6 @@ class Backend {
         size_t K = w->dev.n_in;
         switch (w->dev.fmt) {
             case B2_FMT_MLX4:
-                s.dev.p0 += r0 * K / 2;
-                s.dev.p1 += r0 * (K / 64) * 2;
-                s.dev.p2 += r0 * (K / 64) * 2;
-                break;
             case B2_FMT_Q4_K: s.dev.p0 += r0 * (K / 256) * 144; break;
             case B2_FMT_Q6_K:
                 s.dev.p0 += r0 * (K / 2);
@@ -319,7 +326,7 @@ class Backend {
             e = xplanes.reserve(xplanes_bytes(w->dev.n_in));
             if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
             xp = xplanes_at(xplanes.p, w->dev.n_in);
-            e = launch_xplanes(x_dev_, w->dev.n_in, w->dev.fmt == B2_FMT_MLX4, xp, stream);
+            e = launch_xplanes(x_dev_, w->dev.n_in, xp, stream);
             launches++;
             if (e != cudaSuccess) return cuda_fail(e, "xplanes");
         }

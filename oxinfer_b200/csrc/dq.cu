@@ -21,14 +21,16 @@ __global__ void __launch_bounds__(256) dq_kernel(WeightDev w, size_t r0, size_t 
     if constexpr (FMT == B2_FMT_MLX4) {
         // dequantize_rows_q4 over from_mlx_q4's repack (src/quant.rs:518-563, 586-606):
         // d = f16(scale), offset = bf16(bias + 8 scale), value = (nib - 8) * d + offset.
-        size_t gpr = K / w.group, g = e0 / w.group;
-        float s = bf16_bits_to_f32(((const uint16_t*)w.p1)[r * gpr + g]);
-        float b = bf16_bits_to_f32(((const uint16_t*)w.p2)[r * gpr + g]);
+        // Device blocks (repack_mlx4_kernel): 4 bf16 scales, 4 bf16 biases, 128 nibble bytes in Q4_K order.
+        const uint8_t* blk = w.p0 + (r * (K / 256) + e0 / 256) * 144;
+        int e = (int)(e0 % 256), j = e / 64, h = (e % 64) / 32, l = e % 32;
+        float s = bf16_bits_to_f32(((const uint16_t*)blk)[j]);
+        float b = bf16_bits_to_f32(((const uint16_t*)blk)[4 + j]);
         float d = __half2float(__float2half_rn(s));
         float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(b, __fmul_rn(8.0f, s))));
-        uint32_t word = ((const uint32_t*)w.p0)[r * (K / 8) + e0 / 8];
+        const uint8_t* q = blk + 16 + 32 * j + l;
 #pragma unroll
-        for (int k = 0; k < 8; k++) v[k] = __fadd_rn(__fmul_rn((float)((int)((word >> (4 * k)) & 15) - 8), d), off);
+        for (int k = 0; k < 8; k++) v[k] = __fadd_rn(__fmul_rn((float)((int)((q[k] >> (4 * h)) & 0xF) - 8), d), off);
     } else if constexpr (FMT == B2_FMT_Q4_K) {
         const uint8_t* blk = w.p0 + (r * (K / 256) + e0 / 256) * 144;
         uint32_t hdr = *(const uint32_t*)blk;
@@ -90,6 +92,25 @@ __global__ void repack_q6k_kernel(const uint8_t* __restrict__ raw, size_t nblock
     d[b] = (uint16_t)(s[208] | (s[209] << 8));
 }
 
+// MLX triple (u32 words of eight nibbles, bf16 scale and bias per 64) -> Q4_K-shaped blocks of 256 weights.
+__global__ void repack_mlx4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
+                                   size_t nblocks, uint8_t* __restrict__ out) {
+    size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // block b = 256 consecutive weights of the row-major matrix
+    if (b >= nblocks) return;
+    uint8_t* o = out + b * 144;
+    for (int g = 0; g < 4; g++) {
+        ((uint16_t*)o)[g] = scales[b * 4 + g];
+        ((uint16_t*)o)[4 + g] = biases[b * 4 + g];
+    }
+    const uint32_t* words = w + b * 32;
+    for (int j = 0; j < 4; j++)
+        for (int l = 0; l < 32; l++) {
+            int e0 = 64 * j + l, e1 = e0 + 32;
+            uint32_t n0 = (words[e0 / 8] >> (4 * (e0 % 8))) & 15, n1 = (words[e1 / 8] >> (4 * (e1 % 8))) & 15;
+            o[16 + 32 * j + l] = (uint8_t)(n0 | (n1 << 4));
+        }
+}
+
 __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, size_t nblocks, int8_t* qs, uint16_t* d) {
     size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblocks) return;
@@ -119,6 +140,13 @@ cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uin
                               cudaStream_t st) {
     size_t nb = n_out * (n_in / 256);
     repack_q6k_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(raw, nb, n_in / 256, ql, qh, sc, d);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repack_mlx4(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in, uint8_t* out,
+                               cudaStream_t st) {
+    size_t nb = n_out * (n_in / 256);
+    repack_mlx4_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(w, scales, biases, nb, out);
     return cudaGetLastError();
 }
 

@@ -36,7 +36,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---- activation planes ----------------------------------------------------------------------
-__global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, int perm8, XPlanes out) {
+__global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, XPlanes out) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= K / 32) return;
     float v = x[warp * 32 + lane];
@@ -50,12 +50,7 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
     int r1 = (q - q0) >> 7;
     int q1 = ((r1 + 64) & 127) - 64;
     int q2 = (r1 - q1) >> 7;
-    int pos = lane;
-    if (perm8) {
-        int i = lane & 7;
-        pos = (lane & ~7) | ((i & 1) ? 4 + (i >> 1) : (i >> 1));
-    }
-    size_t at = (size_t)warp * 32 + pos;
+    size_t at = (size_t)warp * 32 + lane;
     out.planes[at] = (int8_t)q0;
     out.planes[(size_t)K + at] = (int8_t)q1;
     out.planes[2 * (size_t)K + at] = (int8_t)q2;
@@ -117,126 +112,102 @@ __device__ __forceinline__ float gelu_tanh(float a) {
 // ---- per-format pieces: `load` issues the global loads of one warp-iteration of one row, `dot2`
 // consumes two rows' loads against the vector (planes read once). An iteration covers ITER_K k.
 
-struct FmtQ4K {
-    static constexpr int ITER_K = 2048;  // 8 super-blocks, 4 lanes each (one 64-group per lane)
-    struct Regs {
-        uint4 hdr, q0, q1;
-    };
-    __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
-    __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
-        const uint8_t* blk = w.p0 + (row * (w.n_in / 256) + it * 8 + (lane >> 2)) * 144;
-        r.hdr = __ldg((const uint4*)blk);  // shared by the four lanes of the super-block: let it hit L1
-        r.q0 = ldg_stream(blk + 16 + 32 * (lane & 3));
-        r.q1 = ldg_stream(blk + 32 + 32 * (lane & 3));
+// Q4_K and the repacked MLX-4 share the block shape: 16 header bytes + 128 bytes of nibbles per 256
+// weights, byte l of 64-group j holding element 64 j + l (low nibble) and 64 j + 32 + l (high nibble).
+// A warp iteration covers 8 blocks, 4 lanes each (one 64-group per lane).
+struct Q4Regs {
+    uint4 hdr, q0, q1;
+};
+__device__ __forceinline__ void q4_load(const WeightDev& w, size_t row, int it, int lane, Q4Regs& r) {
+    const uint8_t* blk = w.p0 + (row * (w.n_in / 256) + it * 8 + (lane >> 2)) * 144;
+    r.hdr = __ldg((const uint4*)blk);  // shared by the four lanes of the block: let it hit L1
+    r.q0 = ldg_stream(blk + 16 + 32 * (lane & 3));
+    r.q1 = ldg_stream(blk + 32 + 32 * (lane & 3));
+}
+// Integer dot products of the low / high nibbles of two rows' 64-groups with the three planes.
+__device__ __forceinline__ void q4_int_dots(const Q4Regs& a, const Q4Regs& b, const XS& x, int k0, int& la, int& ha, int& lb, int& hb) {
+    const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
+    const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
+    int s[3][4];
+#pragma unroll
+    for (int p = 0; p < 3; p++) {
+        uint32_t xw[16];
+        plane64(x, p, k0, xw);
+        int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[i], s0);
+            s1 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s1);
+            s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[i], s2);
+            s3 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s3);
+        }
+        s[p][0] = s0;
+        s[p][1] = s1;
+        s[p][2] = s2;
+        s[p][3] = s3;
     }
-    __device__ static __forceinline__ void scales(const Regs& r, int j, float& d0, float& d1, float& m0, float& m1) {
-        float d = __half2float(__ushort_as_half((unsigned short)(r.hdr.x & 0xffff)));
-        float dmin = __half2float(__ushort_as_half((unsigned short)(r.hdr.x >> 16)));
-        uint32_t sc0, mn0, sc1, mn1;
-        q4k_scale_min(2 * j, r.hdr.y, r.hdr.z, r.hdr.w, sc0, mn0);
-        q4k_scale_min(2 * j + 1, r.hdr.y, r.hdr.z, r.hdr.w, sc1, mn1);
-        d0 = d * (float)sc0;
-        d1 = d * (float)sc1;
-        m0 = dmin * (float)mn0;
-        m1 = dmin * (float)mn1;
+    la = planes3(s[0][0], s[1][0], s[2][0]);
+    ha = planes3(s[0][1], s[1][1], s[2][1]);
+    lb = planes3(s[0][2], s[1][2], s[2][2]);
+    hb = planes3(s[0][3], s[1][3], s[2][3]);
+}
+
+struct FmtQ4K {
+    static constexpr int ITER_K = 2048;
+    using Regs = Q4Regs;
+    __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
+    __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) { q4_load(w, row, it, lane, r); }
+    // scales / mins of sub-blocks 2j, 2j+1 without a branch on j (lanes of a warp differ in j):
+    // bytes a = B[i & 3], b = B[4 + (i & 3)], c = B[8 + (i & 3)] of the 12 (get_scale_min_k4, src/ggml.rs:501-509)
+    __device__ static __forceinline__ void tail(const Regs& r, int j, float4 sx, int lo, int hi, float& acc) {
+        const float d = __half2float(__ushort_as_half((unsigned short)(r.hdr.x & 0xffff)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(r.hdr.x >> 16)));
+        const int sh = 16 * (j & 1);                 // the pair (2j, 2j+1) = bytes 2(j&1), 2(j&1)+1 of each word
+        const uint32_t a = (r.hdr.y >> sh) & 0xffffu, b = (r.hdr.z >> sh) & 0xffffu, c = (r.hdr.w >> sh) & 0xffffu;
+        const uint32_t sc = (j < 2) ? (a & 0x3f3fu) : ((c & 0x0f0fu) | ((a >> 2) & 0x3030u));
+        const uint32_t mn = (j < 2) ? (b & 0x3f3fu) : (((c >> 4) & 0x0f0fu) | ((b >> 2) & 0x3030u));
+        acc = fmaf((d * (float)(sc & 0xff)) * sx.x, (float)lo, acc);
+        acc = fmaf((d * (float)(sc >> 8)) * sx.z, (float)hi, acc);
+        acc = fmaf(-(dmin * (float)(mn & 0xff)), sx.y, acc);
+        acc = fmaf(-(dmin * (float)(mn >> 8)), sx.w, acc);
     }
     __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
         const int j = lane & 3;
         const int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
-        const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
-        const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
-        int la[3], ha[3], lb[3], hb[3];
-#pragma unroll
-        for (int p = 0; p < 3; p++) {
-            uint32_t xw[16];
-            plane64(x, p, k0, xw);
-            int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[i], s0);
-                s1 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s1);
-                s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[i], s2);
-                s3 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s3);
-            }
-            la[p] = s0;
-            ha[p] = s1;
-            lb[p] = s2;
-            hb[p] = s3;
-        }
+        int la, ha, lb, hb;
+        q4_int_dots(a, b, x, k0, la, ha, lb, hb);
         const float4 sx = *(const float4*)(x.sx + (k0 >> 5));  // {xs, xsum} of the two blocks of 32
-        float d0, d1, m0, m1;
-        scales(a, j, d0, d1, m0, m1);
-        accA = fmaf(d0 * sx.x, (float)planes3(la[0], la[1], la[2]), accA);
-        accA = fmaf(d1 * sx.z, (float)planes3(ha[0], ha[1], ha[2]), accA);
-        accA = fmaf(-m0, sx.y, accA);
-        accA = fmaf(-m1, sx.w, accA);
-        scales(b, j, d0, d1, m0, m1);
-        accB = fmaf(d0 * sx.x, (float)planes3(lb[0], lb[1], lb[2]), accB);
-        accB = fmaf(d1 * sx.z, (float)planes3(hb[0], hb[1], hb[2]), accB);
-        accB = fmaf(-m0, sx.y, accB);
-        accB = fmaf(-m1, sx.w, accB);
+        tail(a, j, sx, la, ha, accA);
+        tail(b, j, sx, lb, hb, accB);
     }
 };
 
+// MLX affine 4-bit, repacked at upload into Q4_K-shaped blocks: header = 4 bf16 scales + 4 bf16 biases
+// (one per 64-group), then the 128 nibble bytes in the order above.
 struct FmtMLX4 {
-    static constexpr int ITER_K = 2048;  // 32 groups of 64, one per lane
-    struct Regs {
-        uint4 q0, q1;
-        uint32_t sb;  // scale | bias << 16 (bf16 bits)
-    };
-    __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 32 + lane < K / 64; }
-    __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) {
-        size_t g = row * (w.n_in / 64) + it * 32 + lane;
-        r.q0 = ldg_stream(w.p0 + g * 32);
-        r.q1 = ldg_stream(w.p0 + g * 32 + 16);
-        r.sb = (uint32_t)__ldg((const uint16_t*)w.p1 + g) | ((uint32_t)__ldg((const uint16_t*)w.p2 + g) << 16);
+    static constexpr int ITER_K = 2048;
+    using Regs = Q4Regs;
+    __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
+    __device__ static __forceinline__ void load(const WeightDev& w, size_t row, int it, int lane, Regs& r) { q4_load(w, row, it, lane, r); }
+    // The CPU path's values (src/quant.rs:518-563,586-606): d = f16(scale), offset = bf16(bias + 8 scale),
+    // w = (nib - 8) d + offset = nib d + (offset - 8 d).
+    __device__ static __forceinline__ void tail(const Regs& r, int j, float4 sx, int lo, int hi, float& acc) {
+        const uint32_t sw = (j & 2) ? r.hdr.y : r.hdr.x, bw = (j & 2) ? r.hdr.w : r.hdr.z;
+        const float s = bf16_bits_to_f32((sw >> (16 * (j & 1))) & 0xffffu), bb = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
+        const float d = __half2float(__float2half_rn(s));
+        const float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
+        const float dots = fmaf(sx.z, (float)hi, sx.x * (float)lo);
+        acc = fmaf(d, dots, acc);
+        acc = fmaf(off - 8.0f * d, sx.y + sx.w, acc);
     }
     __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
-        const int k0 = (it * 32 + lane) * 64;
-        const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
-        const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
-        int a0[3], a1[3], b0[3], b1[3];
-#pragma unroll
-        for (int p = 0; p < 3; p++) {
-            // perm8 layout: word pair (2i, 2i+1) of the plane holds the even / odd elements of weight word i
-            uint32_t xw[16];
-            plane64(x, p, k0, xw);
-            int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[2 * i], s0);
-                s0 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[2 * i + 1], s0);
-                s1 = dp(qa[4 + i] & 0x0F0F0F0Fu, xw[8 + 2 * i], s1);
-                s1 = dp((qa[4 + i] >> 4) & 0x0F0F0F0Fu, xw[8 + 2 * i + 1], s1);
-                s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[2 * i], s2);
-                s2 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[2 * i + 1], s2);
-                s3 = dp(qb[4 + i] & 0x0F0F0F0Fu, xw[8 + 2 * i], s3);
-                s3 = dp((qb[4 + i] >> 4) & 0x0F0F0F0Fu, xw[8 + 2 * i + 1], s3);
-            }
-            a0[p] = s0;
-            a1[p] = s1;
-            b0[p] = s2;
-            b1[p] = s3;
-        }
+        const int j = lane & 3;
+        const int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
+        int la, ha, lb, hb;
+        q4_int_dots(a, b, x, k0, la, ha, lb, hb);
         const float4 sx = *(const float4*)(x.sx + (k0 >> 5));
-        // The CPU path's values (src/quant.rs:518-563,586-606): d = f16(scale), offset = bf16(bias + 8 scale),
-        // w = (nib - 8) d + offset = nib d + (offset - 8 d).
-        {
-            float s = bf16_bits_to_f32(a.sb & 0xffff), bb = bf16_bits_to_f32(a.sb >> 16);
-            float d = __half2float(__float2half_rn(s));
-            float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
-            float dots = fmaf(sx.z, (float)planes3(a1[0], a1[1], a1[2]), sx.x * (float)planes3(a0[0], a0[1], a0[2]));
-            accA = fmaf(d, dots, accA);
-            accA = fmaf(off - 8.0f * d, sx.y + sx.w, accA);
-        }
-        {
-            float s = bf16_bits_to_f32(b.sb & 0xffff), bb = bf16_bits_to_f32(b.sb >> 16);
-            float d = __half2float(__float2half_rn(s));
-            float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
-            float dots = fmaf(sx.z, (float)planes3(b1[0], b1[1], b1[2]), sx.x * (float)planes3(b0[0], b0[1], b0[2]));
-            accB = fmaf(d, dots, accB);
-            accB = fmaf(off - 8.0f * d, sx.y + sx.w, accB);
-        }
+        tail(a, j, sx, la, ha, accA);
+        tail(b, j, sx, lb, hb, accB);
     }
 };
 
@@ -466,7 +437,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
 
 bool gemv_supports(const WeightDev& w) {
     switch (w.fmt) {
-        case B2_FMT_MLX4: return w.group == 64 && w.n_in % 64 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
+        case B2_FMT_MLX4:
         case B2_FMT_Q4_K:
         case B2_FMT_Q6_K: return w.n_in % 256 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
         case B2_FMT_Q8_0: return w.n_in % 64 == 0 && xplanes_bytes(w.n_in) <= 200 * 1024;
@@ -475,9 +446,9 @@ bool gemv_supports(const WeightDev& w) {
     }
 }
 
-cudaError_t launch_xplanes(const float* x, size_t K, int perm8, XPlanes out, cudaStream_t st) {
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st) {
     unsigned warps = (unsigned)(K / 32);
-    xplanes_kernel<<<(warps + 7) / 8, 256, 0, st>>>(x, (int)K, perm8, out);
+    xplanes_kernel<<<(warps + 7) / 8, 256, 0, st>>>(x, (int)K, out);
     return cudaGetLastError();
 }
 
@@ -572,7 +543,7 @@ extern "C" __attribute__((visibility("default"))) int b2_matvec_q4k_noalloc(cons
     w.p0 = (const uint8_t*)w_blocks_dev;
     XPlanes xp = xplanes_at(g_noalloc_ptr[dev], n_in);
     cudaStream_t st = (cudaStream_t)cuda_stream;
-    e = launch_xplanes(x_dev, n_in, 0, xp, st);
+    e = launch_xplanes(x_dev, n_in, xp, st);
     if (e != cudaSuccess) return noalloc_fail(err, err_len, B2_ERR_CUDA, "activation planes kernel", e);
     e = launch_gemv(w, nullptr, x_dev, xp, y_dev, B2_MODE_STORE, nullptr, g_noalloc_sms[dev], st);
     if (e != cudaSuccess) return noalloc_fail(err, err_len, B2_ERR_CUDA, "gemv kernel", e);

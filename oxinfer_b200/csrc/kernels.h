@@ -10,6 +10,8 @@ cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float
 // Raw GGUF Q6_K / Q8_0 rows (device) -> the split planes described in formats.cuh.
 cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uint8_t* ql, uint8_t* qh, int8_t* sc, uint16_t* d,
                               cudaStream_t st);
+cudaError_t launch_repack_mlx4(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in, uint8_t* out,
+                               cudaStream_t st);
 cudaError_t launch_repack_q8_0(const uint8_t* raw, size_t n_out, size_t n_in, int8_t* qs, uint16_t* d, cudaStream_t st);
 
 // ---- gemv.cu: one-token dequant matrix-vector products ---------------------------------------
@@ -32,9 +34,8 @@ inline XPlanes xplanes_at(void* base, size_t K) {
     p.v16 = (int32_t*)(p.xsum + K / 32);
     return p;
 }
-// perm8 = 1 stores each run of 8 elements as [0,2,4,6,1,3,5,7] (the MLX nibble order).
-cudaError_t launch_xplanes(const float* x, size_t K, int perm8, XPlanes out, cudaStream_t st);
-// y[n_out] = mode(W x [, U x]). `xp` must have been prepared with perm8 = (w.fmt == MLX4); the
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st);
+// y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st);
