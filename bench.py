@@ -184,6 +184,30 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
         algo = wbytes + 4 * n_in + 4 * n_out
         out[name] = {"us_per_gemv": us, "bytes": algo, "gbs": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peaks["hbm_gbs"],
                      "launches_per_gemv": 1 if fmt == "f8_e4m3" else 2, "timing": timing}
+        # The GEMV kernel alone, over planes prepared once (what a decode plan sees when one vector feeds
+        # several products): a second graph with n GEMV launches and no plane kernels.
+        if use_graph and fmt != "f8_e4m3":
+            try:
+                be.prepare_x_dev(x)
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    be.set_stream(torch.cuda.current_stream().cuda_stream)
+                    for i in range(n):
+                        be.matvec_prepared_dev(devs[i % copies], x, y)
+                be.set_stream(main_stream)
+                g2.replay()
+                torch.cuda.synchronize()
+                ev[0].record()
+                for _ in range(5):
+                    g2.replay()
+                ev[1].record()
+                torch.cuda.synchronize()
+                us2 = ev[0].elapsed_time(ev[1]) * 1e3 / (n * 5)
+                out[name].update({"us_kernel_only": us2, "gbs_kernel_only": algo / us2 / 1e3,
+                                  "frac_kernel_only": algo / us2 / 1e3 / peaks["hbm_gbs"]})
+            except Exception as e:
+                be.set_stream(main_stream)
+                out[name]["kernel_only_error"] = str(e)
         for d in devs:
             d.free()
     return out

@@ -137,6 +137,14 @@ int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_dtype, size
 /* One token: y = mode(W x [, U x]). x_dev f32 [n_in]; y_dev f32 [n_out]; gate_dev f32[1] or NULL. */
 int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev);
 
+/* The two halves of b2_matvec_dev, for a plan in which one vector feeds several products (q, k, v;
+ * gate and up): b2_prepare_x_dev splits x into the integer planes the 4- / 6- / 8-bit kernels read
+ * (the role of quantize_act, which the reference's CPU driver runs once per batch of jobs,
+ * src/kernels.rs:1731-1879), b2_matvec_prepared_dev runs one product over the planes prepared last.
+ * n_in must match; FP8 weights read x_dev itself. */
+int b2_prepare_x_dev(b2_ctx* ctx, const float* x_dev, size_t n_in);
+int b2_matvec_prepared_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev);
+
 /* After the caller has synchronized the stream: B2_OK, or B2_ERR_TIMEOUT when a device-side wait of
  * the tensor-core GEMM ran into its time limit (the kernel then returned early and its output is
  * not valid). The reference logs a failed launch and returns false (src/cuda.rs:625-628); this is

@@ -214,6 +214,15 @@ class Backend:
         return self._check(self._L.b2_matvec_dev(self._ctx, dev.handle, up.handle if up else 0, _ptr(x), _ptr(y), mode,
                                                  _ptr(gate) if gate is not None else None))
 
+    def prepare_x_dev(self, x) -> bool:
+        """Splits a device vector into the integer planes the GEMV kernels read (once per vector)."""
+        return self._check(self._L.b2_prepare_x_dev(self._ctx, _ptr(x), x.numel()))
+
+    def matvec_prepared_dev(self, dev: DeviceWeight, x, y, mode: int = MODE_STORE, up: DeviceWeight | None = None, gate=None) -> bool:
+        """One product over the planes prepared last by ``prepare_x_dev`` (same vector length)."""
+        return self._check(self._L.b2_matvec_prepared_dev(self._ctx, dev.handle, up.handle if up else 0, _ptr(x), _ptr(y), mode,
+                                                          _ptr(gate) if gate is not None else None))
+
     def dequantize_rows_dev(self, dev: DeviceWeight, out, r0: int = 0, r1: int | None = None) -> bool:
         r1 = dev.n_out if r1 is None else r1
         return self._check(self._L.b2_dequantize_rows_dev(self._ctx, dev.handle, r0, r1, _ptr(out)))

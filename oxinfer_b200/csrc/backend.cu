@@ -306,8 +306,23 @@ class Backend {
         return B2_OK;
     }
 
-    // One token on the device: activation planes, then the GEMV.
-    int matvec_dev(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
+    // The activation planes of one vector (kernels.h, XPlanes), computed once and read by every
+    // matrix-vector product over that vector: the role of quantize_act, which the reference's CPU
+    // driver also runs once per batch of jobs (src/kernels.rs:1731-1879, `xa`).
+    size_t prepared_k = 0;
+    int prepare_x(const float* x_dev_, size_t n_in) {
+        if (!x_dev_ || n_in == 0 || n_in % 32) return fail(B2_ERR_ARG, "[b200qmm: prepare_x: n_in must be a positive multiple of 32]");
+        cudaError_t e = xplanes.reserve(xplanes_bytes(n_in));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
+        e = launch_xplanes(x_dev_, n_in, xplanes_at(xplanes.p, n_in), stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "xplanes");
+        prepared_k = n_in;
+        return B2_OK;
+    }
+
+    // One token on the device over the prepared planes (FP8 weights read x itself).
+    int matvec_prepared(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
         bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
@@ -321,19 +336,24 @@ class Backend {
         if (mode < 0 || mode > 4 || (mode == B2_MODE_ADD_GATED && !gate)) return fail(B2_ERR_ARG, "[b200qmm: matvec: bad mode]");
         if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec: shape not supported by the GEMV kernels]");
         XPlanes xp{};
-        cudaError_t e;
         if (w->dev.fmt != B2_FMT_F8E4M3) {
-            e = xplanes.reserve(xplanes_bytes(w->dev.n_in));
-            if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
+            if (prepared_k != w->dev.n_in) return fail(B2_ERR_ARG, "[b200qmm: matvec: no planes prepared for n_in = %zu (b2_prepare_x_dev)]", w->dev.n_in);
             xp = xplanes_at(xplanes.p, w->dev.n_in);
-            e = launch_xplanes(x_dev_, w->dev.n_in, xp, stream);
-            launches++;
-            if (e != cudaSuccess) return cuda_fail(e, "xplanes");
         }
-        e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream);
+        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "gemv");
         return B2_OK;
+    }
+
+    int matvec_dev(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
+        Weight* w = find(h);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
+        if (w->dev.fmt != B2_FMT_F8E4M3 && gemv_supports(w->dev)) {
+            int rc = prepare_x(x_dev_, w->dev.n_in);
+            if (rc) return rc;
+        }
+        return matvec_prepared(h, up, x_dev_, y_dev_, mode, gate);
     }
 
     int ensure_status() {
@@ -651,6 +671,17 @@ B2_EXPORT int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_d
 B2_EXPORT int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev) {
     LOCKED(ctx);
     return ctx->be.matvec_dev(w, up, x_dev, y_dev, mode, gate_dev);
+}
+
+B2_EXPORT int b2_prepare_x_dev(b2_ctx* ctx, const float* x_dev, size_t n_in) {
+    LOCKED(ctx);
+    return ctx->be.prepare_x(x_dev, n_in);
+}
+
+B2_EXPORT int b2_matvec_prepared_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode,
+                                     const float* gate_dev) {
+    LOCKED(ctx);
+    return ctx->be.matvec_prepared(w, up, x_dev, y_dev, mode, gate_dev);
 }
 
 // Reads (and clears) the status word of the tensor-core GEMM after the caller synchronized the

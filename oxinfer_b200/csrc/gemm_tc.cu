@@ -154,6 +154,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
+template <int FMT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
@@ -303,25 +304,42 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->raw_empty);
-                const __half2 dh = __half2half2(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
-                const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
                 for (int jj = 0; jj < 2; jj++) {
                     const int j = set + 2 * jj;
                     const int ks = sb * 4 + j;
                     const int s = ks % STAGES;
                     const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
-                    uint32_t sc0, mn0, sc1, mn1;
-                    q4k_scale_min(2 * j, hdr.y, hdr.z, hdr.w, sc0, mn0);
-                    q4k_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, sc1, mn1);
-                    // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n,
-                    // with that sub-block's scale divided by 16 (exact in f16).
-                    // Two exact steps: t = n * sc (an integer below 2048, exact in f16: (1024 + n) * sc - 1024 * sc
-                    // inside one fma), then w = t * d - dmin * m with d the block's own f16 value; only the
-                    // min term and the result are rounded.
-                    const __half2 sclo = __float2half2_rn((float)sc0), sclo_k = __float2half2_rn(-1024.0f * (float)sc0);
-                    const __half2 schi = __float2half2_rn(0.0625f * (float)sc1), schi_k = __float2half2_rn(-64.0f * (float)sc1);
-                    const __half2 m1lo = __float2half2_rn(-(dmin * (float)mn0)), m1hi = __float2half2_rn(-(dmin * (float)mn1));
+                    // low nibbles: 0x6400 | n = 1024 + n; high nibbles stay in place: 0x6400 | (n << 4) = 1024 + 16 n.
+                    // Both formats take two fmas per pair, t = h * c1 + c2 (an exact small integer) and
+                    // w = t * dmul + add:
+                    //   Q4_K : t = n * sc    (c1 = sc or sc/16, c2 = -1024 sc or -64 sc), w = t * d - f16(dmin * m)
+                    //   MLX-4: t = n - 8     (c1 = 1 or 1/16,   c2 = -1032 or -72),      w = t * f16(scale) + f16(offset)
+                    // so only the min / offset term and the result are rounded.
+                    __half2 dmul, c1lo, c2lo, c1hi, c2hi, addlo, addhi;
+                    if constexpr (FMT == B2_FMT_MLX4) {
+                        const uint32_t sw = (j & 2) ? hdr.y : hdr.x, bw = (j & 2) ? hdr.w : hdr.z;
+                        const float sc = bf16_bits_to_f32((sw >> (16 * (j & 1))) & 0xffffu), bb = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
+                        const float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, sc))));
+                        dmul = __float2half2_rn(sc);
+                        c1lo = __float2half2_rn(1.0f);
+                        c2lo = __float2half2_rn(-1032.0f);
+                        c1hi = __float2half2_rn(0.0625f);
+                        c2hi = __float2half2_rn(-72.0f);
+                        addlo = addhi = __float2half2_rn(off);
+                    } else {
+                        uint32_t sc0, mn0, sc1, mn1;
+                        q4k_scale_min(2 * j, hdr.y, hdr.z, hdr.w, sc0, mn0);
+                        q4k_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, sc1, mn1);
+                        const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                        dmul = __half2half2(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
+                        c1lo = __float2half2_rn((float)sc0);
+                        c2lo = __float2half2_rn(-1024.0f * (float)sc0);
+                        c1hi = __float2half2_rn(0.0625f * (float)sc1);
+                        c2hi = __float2half2_rn(-64.0f * (float)sc1);
+                        addlo = __float2half2_rn(-(dmin * (float)mn0));
+                        addhi = __float2half2_rn(-(dmin * (float)mn1));
+                    }
                     const uint32_t qw[8] = {q[2 * jj].x,     q[2 * jj].y,     q[2 * jj].z,     q[2 * jj].w,
                                             q[2 * jj + 1].x, q[2 * jj + 1].y, q[2 * jj + 1].z, q[2 * jj + 1].w};
                     uint32_t lo[16], hi[16];
@@ -331,10 +349,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         uint32_t p0 = __byte_perm(qw[i], 0, 0x4140), p1 = __byte_perm(qw[i], 0, 0x4342);
                         uint32_t l0 = (p0 & 0x000F000Fu) | 0x64006400u, l1 = (p1 & 0x000F000Fu) | 0x64006400u;
                         uint32_t h0 = (p0 & 0x00F000F0u) | 0x64006400u, h1 = (p1 & 0x00F000F0u) | 0x64006400u;
-                        lo[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l0), sclo, sclo_k), dh, m1lo));
-                        lo[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l1), sclo, sclo_k), dh, m1lo));
-                        hi[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h0), schi, schi_k), dh, m1hi));
-                        hi[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h1), schi, schi_k), dh, m1hi));
+                        lo[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l0), c1lo, c2lo), dmul, addlo));
+                        lo[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&l1), c1lo, c2lo), dmul, addlo));
+                        hi[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h0), c1hi, c2hi), dmul, addhi));
+                        hi[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h1), c1hi, c2hi), dmul, addhi));
                     }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
@@ -514,7 +532,7 @@ struct GemmPlan {
 };
 
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
-    return w.fmt == B2_FMT_Q4_K && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
+    return (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
 }
 
 // Tile width (weight rows per CTA): the multiple of 16 up to MAX_TILE_N that minimizes the time of the
@@ -619,13 +637,15 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
                            cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
-    gemm_q4k_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
-                                                              y_dtype, status_dev, debug_switches());
+    auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
+                                                status_dev, debug_switches());
     return cudaGetLastError();
 }
 

@@ -101,3 +101,19 @@ def test_matmul_declines_formats_without_a_tensor_core_kernel(backend):
     y = np.full((t, n_out), 7.0, np.float32)
     assert backend.matmul(synth.activations(t, n_in, 441), [ob.Job(dev, y)]) is False
     assert (y == 7.0).all()  # declined: nothing written (src/gpu.rs:158-160)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 9), (4096, 4096, 64), (1536, 2048, 100), (2048, 768, 257), (1000, 1024, 512)])
+def test_mlx4_matmul_matches_oracle(backend, shape):
+    """MLX affine 4-bit through the same tensor-core kernel (config 0's format at prefill sizes and the
+    MoE expert shapes): the oracle's weights are the reference's own repack, (nib - 8) f16(s) + bf16(b + 8 s)."""
+    n_out, n_in, t = shape
+    ref, m = make_pair("mlx4", n_out, n_in, 450 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 451)
+    y = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert np.isfinite(y).all()
+    err = row_err(y, m.matmul_f64(x))
+    assert err < TOL, err
+    assert row_err(y, m.matmul_cpu(x)) < TOL
