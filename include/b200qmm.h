@@ -56,6 +56,7 @@ extern "C" {
 
 typedef struct b2_ctx b2_ctx;
 typedef uint64_t b2_weight;
+typedef uint64_t b2_moe_handle;
 
 /* One matmul of a batch sharing the input x: `Job` of src/gpu.rs:60-65. */
 typedef struct {
@@ -136,6 +137,25 @@ int b2_matvec_rows(b2_ctx* ctx, const float* x, size_t t, size_t n_in, b2_rows_j
 int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_dtype, size_t t, void* y_dev, int y_dtype);
 /* One token: y = mode(W x [, U x]). x_dev f32 [n_in]; y_dev f32 [n_out]; gate_dev f32[1] or NULL. */
 int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev);
+
+/* ---- routed experts (MoE) ----------------------------------------------------------------- */
+
+/* `Backend::upload_moe`, src/gpu.rs:200-215 / src/cuda.rs:777-796. The experts' matrices are uploaded
+ * one by one with b2_upload_mlx4 / b2_upload_gguf (all MLX-4 or all Q4_K): gate_up[e] is the fused
+ * gate/up projection [2 inter][h] (gate rows, then up rows), down[e] is [h][inter]. Their blocks are
+ * copied into two stacked device buffers; the per-expert handles may be freed afterwards. h and inter
+ * must be multiples of 256. The activation is SiLU (MoeAct::Silu, src/gpu.rs:36-54). */
+int b2_upload_moe(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* down, size_t experts, size_t h, size_t inter, b2_moe_handle* out);
+int b2_free_moe(b2_ctx* ctx, b2_moe_handle m);
+/* `Backend::moe`, src/gpu.rs:232-248 / src/cuda.rs:798-966: token i of x [t][h] goes through its k routes
+ * (route_ids[i k + j], route_w[i k + j]) and y[i] += sum_j w_ij down(silu(gate x_i) * up x_i), added in
+ * route order. Host x and y (y is read and written); routes are host arrays in both forms. */
+int b2_moe(b2_ctx* ctx, b2_moe_handle m, const float* x, size_t t, const int32_t* route_ids, const float* route_w, size_t k, float* y);
+/* Same with x and y resident on the device (no synchronization of the result). */
+int b2_moe_dev(b2_ctx* ctx, b2_moe_handle m, const float* x_dev, size_t t, const int32_t* route_ids, const float* route_w, size_t k, float* y_dev);
+/* route_top_k (src/moe.rs:180-193) / dtopk (src/cuda_decode.cu:285-312) on the device: for each of t rows
+ * of n_experts logits, the k largest (ties to the lower index) and exp(l - max) / sum over the chosen. */
+int b2_route_topk_dev(b2_ctx* ctx, const float* logits_dev, size_t t, size_t n_experts, size_t k, int32_t* ids_dev, float* w_dev);
 
 /* The two halves of b2_matvec_dev, for a plan in which one vector feeds several products (q, k, v;
  * gate and up): b2_prepare_x_dev splits x into the integer planes the 4- / 6- / 8-bit kernels read

@@ -60,6 +60,11 @@ _SIGNATURES = {
     "b2_matmul_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
     "b2_matvec_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "b2_check_status": (C.c_int, [C.c_void_p]),
+    "b2_upload_moe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_free_moe": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "b2_moe": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b2_moe_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b2_route_topk_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
     "b2_prepare_x_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "b2_matvec_prepared_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "b2_matvec_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),

@@ -65,6 +65,24 @@ class DeviceWeight:
             pass
 
 
+class MoeWeights:
+    """Device state of one MoE layer's routed experts (stacked gate/up and down matrices)."""
+
+    def __init__(self, backend: "Backend", handle: int, experts: int, h: int, inter: int):
+        self.backend, self.handle, self.experts, self.h, self.inter = backend, handle, experts, h, inter
+
+    def free(self) -> None:
+        if self.handle and self.backend._ctx:
+            _lib.lib().b2_free_moe(self.backend._ctx, self.handle)
+        self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 @dataclass
 class Job:
     """One matmul of a batch sharing the input (``src/gpu.rs:60-65``): ``y[t][n_out] = x W^T``."""
@@ -213,6 +231,30 @@ class Backend:
         assert x.numel() == dev.n_in and y.numel() == dev.n_out and x.is_cuda and y.is_cuda
         return self._check(self._L.b2_matvec_dev(self._ctx, dev.handle, up.handle if up else 0, _ptr(x), _ptr(y), mode,
                                                  _ptr(gate) if gate is not None else None))
+
+    # -- routed experts ---------------------------------------------------------------------------
+    def upload_moe(self, gate_up: list, down: list, h: int, inter: int) -> "MoeWeights | None":
+        """``Backend::upload_moe`` (``src/gpu.rs:200-215``): per-expert weights already uploaded with ``upload``."""
+        n = len(gate_up)
+        gu = (C.c_uint64 * n)(*[d.handle for d in gate_up])
+        dn = (C.c_uint64 * n)(*[d.handle for d in down])
+        hd = C.c_uint64()
+        if not self._check(self._L.b2_upload_moe(self._ctx, C.cast(gu, C.c_void_p), C.cast(dn, C.c_void_p), n, h, inter, C.byref(hd))):
+            return None
+        return MoeWeights(self, hd.value, n, h, inter)
+
+    def moe(self, x: np.ndarray, routes_ids: np.ndarray, routes_w: np.ndarray, dev: "MoeWeights", y: np.ndarray) -> bool:
+        """``Backend::moe`` (``src/gpu.rs:232-248``): ``y[i] += sum_j w_ij down(silu(gate x_i) * up x_i)``, y in place."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        ids = np.ascontiguousarray(routes_ids, dtype=np.int32)
+        w = np.ascontiguousarray(routes_w, dtype=np.float32)
+        t, k = ids.shape
+        assert x.shape == (t, dev.h) and y.shape == (t, dev.h) and y.dtype == np.float32 and y.flags["C_CONTIGUOUS"]
+        return self._check(self._L.b2_moe(self._ctx, dev.handle, _ptr(x), t, _ptr(ids), _ptr(w), k, _ptr(y)))
+
+    def route_topk_dev(self, logits, k: int, ids, w) -> bool:
+        t, n = logits.shape
+        return self._check(self._L.b2_route_topk_dev(self._ctx, _ptr(logits), t, n, k, _ptr(ids), _ptr(w)))
 
     def prepare_x_dev(self, x) -> bool:
         """Splits a device vector into the integer planes the GEMV kernels read (once per vector)."""

@@ -23,6 +23,16 @@ struct Weight {
 };
 
 // A device buffer that only grows.
+// Device state of the routed experts of one MoE layer (Backend::upload_moe, src/gpu.rs:200-215): the
+// experts' fused gate/up matrices stacked into one buffer, and their down matrices into another.
+struct Moe {
+    int fmt = 0;
+    size_t experts = 0, h = 0, inter = 0;
+    void* gate_up = nullptr;  // [experts][2 inter][h / 256][144]
+    void* down = nullptr;     // [experts][h][inter / 256][144]
+    size_t bytes = 0;
+};
+
 struct Scratch {
     void* p = nullptr;
     size_t cap = 0;
@@ -52,6 +62,8 @@ class Backend {
     std::string err;
     std::string stats_text;
     std::unordered_map<uint64_t, Weight> weights;
+    std::unordered_map<uint64_t, Moe> moes;
+    Scratch moe_idx, moe_xg, moe_g, moe_a, moe_o;
     uint64_t next_handle = 1;
     uint64_t launches = 0;
     // staging for the host-buffer entry points
@@ -506,6 +518,176 @@ class Backend {
         return B2_OK;
     }
 
+    // ---- Backend::upload_moe (src/gpu.rs:200-215, src/cuda.rs:777-796): the experts were uploaded one by
+    // one with b2_upload_*; their blocks are copied into two stacked buffers the grouped GEMM indexes by
+    // expert, after which the caller may free the per-expert handles.
+    int upload_moe(const uint64_t* gate_up, const uint64_t* down, size_t experts, size_t h, size_t inter, uint64_t* out) {
+        if (!gate_up || !down || !out || experts == 0) return fail(B2_ERR_ARG, "[b200qmm: upload_moe: null argument]");
+        if (h % 256 || inter % 256) return fail(B2_DECLINED, "[b200qmm: upload_moe: h and inter must be multiples of 256]");
+        Moe m;
+        m.experts = experts;
+        m.h = h;
+        m.inter = inter;
+        const size_t gu_bytes = 2 * inter * (h / 256) * 144, dn_bytes = h * (inter / 256) * 144;
+        for (size_t e = 0; e < experts; e++) {
+            Weight *g = find(gate_up[e]), *d = find(down[e]);
+            if (!g || !d) return fail(B2_ERR_ARG, "[b200qmm: upload_moe: unknown weight for expert %zu]", e);
+            if (e == 0) m.fmt = g->dev.fmt;
+            if ((m.fmt != B2_FMT_MLX4 && m.fmt != B2_FMT_Q4_K) || g->dev.fmt != m.fmt || d->dev.fmt != m.fmt)
+                return fail(B2_DECLINED, "[b200qmm: upload_moe: experts must all be MLX-4 or all Q4_K]");
+            if (g->dev.n_out != 2 * inter || g->dev.n_in != h || d->dev.n_out != h || d->dev.n_in != inter)
+                return fail(B2_ERR_ARG, "[b200qmm: upload_moe: expert %zu has the wrong shape]", e);
+        }
+        cudaError_t e1 = cudaMalloc(&m.gate_up, gu_bytes * experts), e2 = cudaSuccess;
+        if (e1 == cudaSuccess) e2 = cudaMalloc(&m.down, dn_bytes * experts);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) {
+            if (m.gate_up) cudaFree(m.gate_up);
+            return cuda_fail(e1 != cudaSuccess ? e1 : e2, "cudaMalloc(moe)");
+        }
+        for (size_t e = 0; e < experts; e++) {
+            cudaMemcpyAsync((uint8_t*)m.gate_up + e * gu_bytes, find(gate_up[e])->dev.p0, gu_bytes, cudaMemcpyDeviceToDevice, stream);
+            cudaMemcpyAsync((uint8_t*)m.down + e * dn_bytes, find(down[e])->dev.p0, dn_bytes, cudaMemcpyDeviceToDevice, stream);
+        }
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) {
+            cudaFree(m.gate_up);
+            cudaFree(m.down);
+            return cuda_fail(e, "upload_moe copies");
+        }
+        m.bytes = (gu_bytes + dn_bytes) * experts;
+        *out = next_handle++;
+        moes[*out] = m;
+        return B2_OK;
+    }
+
+    int free_moe(uint64_t h) {
+        auto it = moes.find(h);
+        if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: free_moe: unknown handle]");
+        cudaStreamSynchronize(stream);
+        cudaFree(it->second.gate_up);
+        cudaFree(it->second.down);
+        moes.erase(it);
+        return B2_OK;
+    }
+
+    // One grouped GEMM: rows of xg (f16, segments of whole 128-row tiles per expert) times the stacked matrices.
+    int grouped_gemm(int fmt, const void* stacked, size_t experts, size_t n_out, size_t n_in, const void* xg, size_t rows, const int* tile_expert,
+                     float* out_dev) {
+        WeightDev w{};
+        w.fmt = fmt;
+        w.n_out = n_out;
+        w.n_in = n_in;
+        w.p0 = (const uint8_t*)stacked;
+        GemmPlan* plan = nullptr;
+        char msg[256] = {0};
+        cudaError_t e = gemm_tc_plan_create(w, xg, rows, out_dev, B2_F32, &plan, msg, sizeof msg, experts, tile_expert, 1);
+        if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
+        e = launch_gemm_tc(plan, w, rows, out_dev, B2_F32, gemm_status, sm_count, stream);
+        launches++;
+        gemm_tc_plan_destroy(plan);  // the tensor maps were copied into the launch's parameters
+        if (e != cudaSuccess) return cuda_fail(e, "grouped gemm");
+        return B2_OK;
+    }
+
+    // ---- Backend::moe (src/gpu.rs:232-248, src/cuda.rs:798-966): y[i] += sum_j w_ij down_e(act(gate_e x_i) * up_e x_i).
+    // The host builds the per-expert segments as the reference does (src/cuda.rs:810-857), padded to the
+    // GEMM's 128-row token tile; x_dev / y_dev are device f32 [t][h].
+    int moe_dev(uint64_t handle, const float* x_dev_, size_t t, const int32_t* ids, const float* rw, size_t k, float* y_dev_) {
+        auto it = moes.find(handle);
+        if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe: unknown handle]");
+        const Moe& m = it->second;
+        if (t == 0 || k == 0) return B2_OK;
+        int rc = ensure_status();
+        if (rc) return rc;
+        std::vector<size_t> count(m.experts, 0);
+        for (size_t i = 0; i < t * k; i++) {
+            if (ids[i] < 0 || (size_t)ids[i] >= m.experts) return fail(B2_ERR_ARG, "[b200qmm: moe: expert index out of range]");
+            count[(size_t)ids[i]]++;
+        }
+        const size_t TILE = 128;
+        std::vector<size_t> off(m.experts, 0);
+        std::vector<int32_t> tile_expert;
+        size_t rows = 0;
+        for (size_t e = 0; e < m.experts; e++) {
+            off[e] = rows;
+            size_t tiles = (count[e] + TILE - 1) / TILE;
+            for (size_t i = 0; i < tiles; i++) tile_expert.push_back((int32_t)e);
+            rows += tiles * TILE;
+        }
+        std::vector<int32_t> src(rows, -1), slots(t * k);
+        std::vector<size_t> fill(m.experts, 0);
+        for (size_t i = 0; i < t; i++)
+            for (size_t j = 0; j < k; j++) {
+                size_t e = (size_t)ids[i * k + j];
+                size_t r = off[e] + fill[e]++;
+                src[r] = (int32_t)i;
+                slots[i * k + j] = (int32_t)r;
+            }
+        // index block on the device: src | slots | tile_expert | route weights
+        const size_t n_idx = rows + t * k + tile_expert.size();
+        cudaError_t e = moe_idx.reserve(n_idx * 4 + t * k * 4);
+        if (e == cudaSuccess) e = moe_xg.reserve(rows * m.h * 2);
+        if (e == cudaSuccess) e = moe_g.reserve(rows * 2 * m.inter * 4);
+        if (e == cudaSuccess) e = moe_a.reserve(rows * m.inter * 2 + rows * 4);
+        if (e == cudaSuccess) e = moe_o.reserve(rows * m.h * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(moe scratch)");
+        int32_t* d_src = (int32_t*)moe_idx.p;
+        int32_t* d_slots = d_src + rows;
+        int32_t* d_tiles = d_slots + t * k;
+        float* d_w = (float*)(d_tiles + tile_expert.size());
+        std::vector<int32_t> host(n_idx);
+        std::memcpy(host.data(), src.data(), rows * 4);
+        std::memcpy(host.data() + rows, slots.data(), t * k * 4);
+        std::memcpy(host.data() + rows + t * k, tile_expert.data(), tile_expert.size() * 4);
+        e = cudaMemcpyAsync(d_src, host.data(), n_idx * 4, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_w, rw, t * k * 4, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);  // the host vectors go out of scope
+        if (e != cudaSuccess) return cuda_fail(e, "moe index upload");
+        e = launch_moe_gather(x_dev_, d_src, rows, m.h, moe_xg.p, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "moe_gather");
+        if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p))) return rc;
+        float* d_scale = (float*)((uint8_t*)moe_a.p + rows * m.inter * 2);  // one power-of-two scale per row
+        e = launch_moe_act((const float*)moe_g.p, rows, m.inter, moe_a.p, d_scale, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "moe_act");
+        if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p))) return rc;
+        e = launch_moe_combine((const float*)moe_o.p, d_scale, d_slots, d_w, t, k, m.h, y_dev_, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "moe_combine");
+        return B2_OK;
+    }
+
+    int moe(uint64_t handle, const float* x, size_t t, const int32_t* ids, const float* rw, size_t k, float* y) {
+        auto it = moes.find(handle);
+        if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe: unknown handle]");
+        if (!x || !y || !ids || !rw) return fail(B2_ERR_ARG, "[b200qmm: moe: null argument]");
+        const size_t h = it->second.h;
+        cudaError_t e = x_dev.reserve(t * h * 4);
+        if (e == cudaSuccess) e = y_dev.reserve(t * h * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
+        e = cudaMemcpyAsync(x_dev.p, x, t * h * 4, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(y_dev.p, y, t * h * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-in");
+        int rc = moe_dev(handle, (const float*)x_dev.p, t, ids, rw, k, (float*)y_dev.p);
+        if (rc) return rc;
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "moe kernels");
+        if ((rc = check_gemm_status())) return rc;
+        e = cudaMemcpyAsync(y, y_dev.p, t * h * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-out");
+        calls++;
+        return B2_OK;
+    }
+
+    int route_topk(const float* logits_dev, size_t t, size_t n, size_t k, int32_t* ids_dev, float* w_dev) {
+        cudaError_t e = launch_route_topk(logits_dev, t, n, k, ids_dev, w_dev, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "route_topk");
+        return B2_OK;
+    }
+
     const char* stats() {
         char buf[256];
         snprintf(buf, sizeof buf, "b200qmm: %llu calls, %llu launches, copy-in %.3f ms, gpu %.3f ms, copy-out %.3f ms",
@@ -518,6 +700,16 @@ class Backend {
         cudaStreamSynchronize(stream);
         for (auto& kv : weights) drop(kv.second.owned);
         weights.clear();
+        for (auto& kv : moes) {
+            cudaFree(kv.second.gate_up);
+            cudaFree(kv.second.down);
+        }
+        moes.clear();
+        moe_idx.release();
+        moe_xg.release();
+        moe_g.release();
+        moe_a.release();
+        moe_o.release();
         x_dev.release();
         y_dev.release();
         x16.release();
@@ -671,6 +863,32 @@ B2_EXPORT int b2_matmul_dev(b2_ctx* ctx, b2_weight w, const void* x_dev, int x_d
 B2_EXPORT int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, float* y_dev, int mode, const float* gate_dev) {
     LOCKED(ctx);
     return ctx->be.matvec_dev(w, up, x_dev, y_dev, mode, gate_dev);
+}
+
+B2_EXPORT int b2_upload_moe(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* down, size_t experts, size_t h, size_t inter, b2_moe_handle* out) {
+    LOCKED(ctx);
+    return ctx->be.upload_moe(gate_up, down, experts, h, inter, out);
+}
+
+B2_EXPORT int b2_free_moe(b2_ctx* ctx, b2_moe_handle m) {
+    LOCKED(ctx);
+    return ctx->be.free_moe(m);
+}
+
+B2_EXPORT int b2_moe(b2_ctx* ctx, b2_moe_handle m, const float* x, size_t t, const int32_t* route_ids, const float* route_w, size_t k, float* y) {
+    LOCKED(ctx);
+    return ctx->be.moe(m, x, t, route_ids, route_w, k, y);
+}
+
+B2_EXPORT int b2_moe_dev(b2_ctx* ctx, b2_moe_handle m, const float* x_dev, size_t t, const int32_t* route_ids, const float* route_w, size_t k,
+                         float* y_dev) {
+    LOCKED(ctx);
+    return ctx->be.moe_dev(m, x_dev, t, route_ids, route_w, k, y_dev);
+}
+
+B2_EXPORT int b2_route_topk_dev(b2_ctx* ctx, const float* logits_dev, size_t t, size_t n_experts, size_t k, int32_t* ids_dev, float* w_dev) {
+    LOCKED(ctx);
+    return ctx->be.route_topk(logits_dev, t, n_experts, k, ids_dev, w_dev);
 }
 
 B2_EXPORT int b2_prepare_x_dev(b2_ctx* ctx, const float* x_dev, size_t n_in) {

@@ -158,7 +158,8 @@ template <int FMT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
-                   int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg) {
+                   int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg,
+                   const int* __restrict__ tile_expert) {
     const long long dbg_k0 = clock64();
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
     extern __shared__ uint8_t smem_raw[];
@@ -172,6 +173,9 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const int nsb = K / 256, nks = nsb * 4;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
+    // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
+    // belongs to one expert
+    const int w_row0 = tile_expert ? tile_expert[blockIdx.y] * n_out : 0;
     const int set_warps = (tile_n + 31) / 32;  // live warps in each of the two dequantizer sets
 
     if (threadIdx.x == 0) {
@@ -234,7 +238,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     continue;
                 }
                 mbar_arrive_expect_tx(&sh->raw_full, w_bytes);
-                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * 144, n0);
+                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * 144, w_row0 + n0);
                 w_issued = sb + 1;
             }
             if (sh->abort_flag && w_issued > 0)
@@ -523,6 +527,8 @@ int debug_switches() {
 
 struct GemmPlan {
     CUtensorMap tmap_x, tmap_w, tmap_y;
+    const int* tile_expert = nullptr;  // grouped launches: expert of each token tile (device)
+    size_t experts = 1;
     const void* x16;
     const void* wptr;
     const void* y;
@@ -558,7 +564,7 @@ static int pick_tile_n(size_t n_out, int m_tiles, int sm_count) {
 }
 
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen) {
+                                size_t errlen, size_t experts, const int* tile_expert, int force_m_halves) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) {
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
@@ -572,7 +578,9 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     p->t = t;
     p->K = w.n_in;
     p->n_out = w.n_out;
-    p->m_halves = t > 128 ? 2 : 1;
+    p->experts = experts;
+    p->tile_expert = tile_expert;
+    p->m_halves = force_m_halves ? force_m_halves : (t > 128 ? 2 : 1);
     int tm = 128 * p->m_halves;
     p->m_tiles = (int)((t + tm - 1) / tm);
     int sm_count = 148;
@@ -596,7 +604,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     {
         // the packed weights as a byte matrix [n_out][row_bytes]; one box = one super-block column of the tile
         size_t row_bytes = w.n_in / 256 * 144;
-        cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)w.n_out};
+        cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(w.n_out * experts)};
         cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
         cuuint32_t box[2] = {144, (cuuint32_t)p->tile_n};
         cuuint32_t estr[2] = {1, 1};
@@ -630,7 +638,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
 void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
 
 bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype) {
-    return p && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out;
+    return p && p->experts == 1 && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out;
 }
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
@@ -645,7 +653,7 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
     auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
-                                                status_dev, debug_switches());
+                                                status_dev, debug_switches(), p->tile_expert);
     return cudaGetLastError();
 }
 

@@ -54,13 +54,23 @@ bool gemm_tc_supports(const WeightDev& w, size_t t);
 // y[t][n_out] (f32 or bf16) = x[t][n_in] (f16, row-major, t padded by the caller to a multiple of
 // 256 rows in `x16`) * W^T. `tmap_x` is the host-encoded tensor map of x16 (see make_tmap_x).
 struct GemmPlan;
+// `experts` > 1 makes a grouped plan: w.p0 holds `experts` stacked matrices of w.n_out rows, x16 / y hold the
+// token rows of all experts in segments that are multiples of 128 * m_halves rows, and tile_expert[i]
+// (device) names the expert of token tile i.
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen);
+                                size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0);
 void gemm_tc_plan_destroy(GemmPlan* p);
 bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype);
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int sm_count,
                            cudaStream_t st);
 // x (f32 / bf16 / f16, [t][K]) -> f16 [t_pad][K], pad rows zeroed.
 cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t t_pad, size_t K, void* x16, cudaStream_t st);
+
+// ---- moe.cu: the element-wise pieces of the routed-expert layer ------------------------------------
+cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st);
+cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, cudaStream_t st);
+cudaError_t launch_moe_act(const float* g, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
+cudaError_t launch_moe_combine(const float* o, const float* row_scale, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y,
+                               cudaStream_t st);
 
 }  // namespace b2
