@@ -29,6 +29,7 @@
 // word, raises a CTA-wide abort flag, and every role then falls through to the common teardown
 // (in-flight copies are awaited, TMEM is freed) so that the kernel always returns.
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <cstdio>
 #include <cstdlib>
@@ -48,6 +49,13 @@ constexpr int B_STAGE_BYTES = MAX_TILE_N * 128;
 constexpr int RAW_BYTES = MAX_TILE_N * 144;  // one super-block column of the weight tile, packed
 constexpr int GEMM_THREADS = 608;          // activation producer, MMA issuer, 16 dequant / epilogue warps, weight producer
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds of SM clock
+
+struct F8Scales {  // block scales of an FP8 matrix (formats.cuh); s == nullptr for the 4-bit formats
+    const float* s;
+    int rows, ncb, row0;
+    float pre;  // power of two folded into the f16 weights (keeps small scales out of f16's subnormals); the
+                // epilogue multiplies the outputs by 1 / pre
+};
 
 struct __align__(8) Shared {
     uint64_t a_full[STAGES];
@@ -159,7 +167,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
                    int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg,
-                   const int* __restrict__ tile_expert) {
+                   const int* __restrict__ tile_expert, F8Scales f8) {
+    // A "raw block" is what one weight copy brings per row: a 144-byte 4-bit block (256 k, four pipeline
+    // stages) or 128 e4m3 bytes (128 k = one column of FP8 scale blocks, two stages).
+    constexpr int RAW_ROW = FMT == B2_FMT_F8E4M3 ? 128 : 144;
+    constexpr int RAW_ST = FMT == B2_FMT_F8E4M3 ? 2 : 4;
     const long long dbg_k0 = clock64();
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
     extern __shared__ uint8_t smem_raw[];
@@ -170,7 +182,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     Shared* sh = (Shared*)(raw + RAW_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nsb = K / 256, nks = nsb * 4;
+    const int nsb = K / (64 * RAW_ST), nks = nsb * RAW_ST;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
     // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
@@ -227,7 +239,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     } else if (warp == 18) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
-            const uint32_t w_bytes = (uint32_t)(tile_n * 144);
+            const uint32_t w_bytes = (uint32_t)(tile_n * RAW_ROW);
             int w_issued = 0;
             for (int sb = 0; sb < nsb; sb++) {
                 // the staging buffer is free once every dequant warp has taken its copy of super-block sb - 1,
@@ -238,7 +250,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     continue;
                 }
                 mbar_arrive_expect_tx(&sh->raw_full, w_bytes);
-                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * 144, w_row0 + n0);
+                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * RAW_ROW, w_row0 + n0);
                 w_issued = sb + 1;
             }
             if (sh->abort_flag && w_issued > 0)
@@ -291,13 +303,55 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             const bool in_tile = r < tile_n;
             const uint32_t row_off = (uint32_t)r * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
-            const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * 144);
+            const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * RAW_ROW);
             for (int sb = 0; sb < nsb && ok; sb++) {
                 // this row's packed super-block: staging buffer -> registers (only the two 64-groups this set
                 // expands), then release the buffer
                 if (!mbar_wait(&sh->raw_full, (uint32_t)(sb & 1), sh, status, 10, (uint32_t)sb)) {
                     ok = false;
                     break;
+                }
+                if constexpr (FMT == B2_FMT_F8E4M3) {
+                    // 64 e4m3 bytes of this set's stage (the raw tile is 128-byte swizzled: chunk c of row r sits
+                    // at c ^ (r & 7)), the block scale of this row and k-block, then hardware e4m3x2 -> f16x2
+                    // and one multiply by the scale per pair.
+                    uint4 qb[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) qb[c] = my_raw[((uint32_t)(4 * set + c)) ^ swz];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->raw_empty);
+                    float scale = 1.0f;
+                    if (f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb);
+                    const __half2 sc2 = __float2half2_rn(scale * f8.pre);
+                    const int ks = sb * 2 + set;
+                    const int s = ks % STAGES;
+                    const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                    uint32_t o[32];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint32_t wds[4] = {qb[c].x, qb[c].y, qb[c].z, qb[c].w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wds[i] & 0xffff), __NV_E4M3);
+                            __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wds[i] >> 16), __NV_E4M3);
+                            o[8 * c + 2 * i] = h2_bits(__hmul2(*reinterpret_cast<__half2*>(&h01), sc2));
+                            o[8 * c + 2 * i + 1] = h2_bits(__hmul2(*reinterpret_cast<__half2*>(&h23), sc2));
+                        }
+                    }
+                    if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
+                        ok = false;
+                        break;
+                    }
+                    if (in_tile && !(dbg & 1)) {
+                        uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
+#pragma unroll
+                        for (int c = 0; c < 8; c++)
+                            *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->b_full[s]);
+                    continue;
                 }
                 const uint4 hdr = my_raw[0];
                 uint4 q[4];
@@ -387,6 +441,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             if (dbg_cta && threadIdx.x == 64) status->t[2] = (uint32_t)(clock64() - dbg_k0);
             if (acc_ok) {
                 tc_fence_after();
+                const float out_scale = FMT == B2_FMT_F8E4M3 ? 1.0f / f8.pre : 1.0f;
                 const int token0 = m0 + half * 128 + quarter * 32;
                 const int token = token0 + lane;
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
@@ -407,6 +462,13 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         uint32_t v[16], u[16];
                         tmem_ld16(taddr0 + (uint32_t)c0, v);
                         tmem_ld16(taddr0 + (uint32_t)c0 + 16u, u);
+                        if (FMT == B2_FMT_F8E4M3) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) {
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * out_scale);
+                                u[i] = __float_as_uint(__uint_as_float(u[i]) * out_scale);
+                            }
+                        }
                         uint8_t* rowp = buf + lane * 128;
                         const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
@@ -431,6 +493,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                   for (int cc = c0; cc < min(c0 + 32, tile_n); cc += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr0 + (uint32_t)cc, v);
+                    if (FMT == B2_FMT_F8E4M3) {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * out_scale);
+                    }
                     if (token < t && !(dbg & 8)) {
                         int n = n0 + cc;
                         if (y_dtype == B2_F32) {
@@ -538,6 +604,7 @@ struct GemmPlan {
 };
 
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
+    if (w.fmt == B2_FMT_F8E4M3) return w.n_in % 128 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0 && (w.p1 == nullptr || w.bs_cols == 128);
     return (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
 }
 
@@ -603,13 +670,14 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     }
     {
         // the packed weights as a byte matrix [n_out][row_bytes]; one box = one super-block column of the tile
-        size_t row_bytes = w.n_in / 256 * 144;
+        const bool f8 = w.fmt == B2_FMT_F8E4M3;
+        size_t row_bytes = f8 ? w.n_in : w.n_in / 256 * 144;
         cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(w.n_out * experts)};
         cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-        cuuint32_t box[2] = {144, (cuuint32_t)p->tile_n};
+        cuuint32_t box[2] = {f8 ? 128u : 144u, (cuuint32_t)p->tile_n};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = enc(&p->tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.p0, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         f8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) {
             snprintf(err, errlen, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
             delete p;
@@ -647,13 +715,15 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
-    auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
+    auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : w.fmt == B2_FMT_F8E4M3 ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
+    F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
-                                                status_dev, debug_switches(), p->tile_expert);
+                                                status_dev, debug_switches(), p->tile_expert, f8);
     return cudaGetLastError();
 }
 

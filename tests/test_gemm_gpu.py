@@ -117,3 +117,25 @@ def test_mlx4_matmul_matches_oracle(backend, shape):
     err = row_err(y, m.matmul_f64(x))
     assert err < TOL, err
     assert row_err(y, m.matmul_cpu(x)) < TOL
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 9), (1000, 1024, 130), (3584, 1536, 128), (512, 12288, 64)])
+def test_fp8_matmul_matches_oracle(backend, shape):
+    """FP8 e4m3 weights with 128 x 128 f32 block scales: the reference's definition (e4m3 * s against f32
+    activations, src/ggml.rs:433-443), bound 2e-3 per output row. The weights go through the tensor cores
+    as f16 (exact e4m3 -> f16, one rounding for the scale); activations are NOT quantized to e4m3."""
+    n_out, n_in, t = shape
+    ref, m = make_pair("f8_e4m3", n_out, n_in, 460 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 461)
+    y = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert np.isfinite(y).all()
+    err = row_err(y, m.matmul_f64(x))
+    assert err < 2e-3 and err < 1e-3, err
+    # a row shard that starts inside the scale grid (multiple of 128 rows)
+    sh = backend.shard_rows(dev, 128, n_out) if n_out > 256 else None
+    if sh is not None:
+        ys = np.zeros((t, n_out - 128), np.float32)
+        assert backend.matmul(x, [ob.Job(sh, ys)])
+        assert np.array_equal(ys, y[:, 128:])
