@@ -171,6 +171,92 @@ int b2_matvec_prepared_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* 
  * the same report for the device-resident calls, which do not synchronize themselves. */
 int b2_check_status(b2_ctx* ctx);
 
+/* ---- decode plan: one token's whole forward pass in one submission ---------------------------
+ * Mirrors gpu::decode (src/gpu_decode.rs): the model describes a token as a list of ops over
+ * activation buffers (Graph, src/gpu_decode.rs:378-416), Backend::decode_plan turns it into a plan
+ * (src/gpu.rs:262-289; CUDA: CudaPlan, src/cuda_decode.rs:1233-1658) and DecodePlan::step runs it
+ * (src/gpu_decode.rs:538-587). Here the op list is captured once into a CUDA graph whose kernels read
+ * the position from device memory, so a step is one graph launch. Ops taken: the set a dense Llama /
+ * Qwen3 layer uses (Norm, Linear in the five modes, QkRope, Attend, Glu); a graph with any other op
+ * is declined (> 0), as decode_plan returns None and the model decodes on the CPU.
+ *
+ * Differences by design: the KV caches live on the device inside the plan ([n_kv][max_len][hd], f32, or
+ * f16 when asked) and are the authoritative copy during device decoding; b2_plan_kv_write / _read move
+ * rows between them and the host's LayerCache layout ([len][n_kv][hd] f32, src/model.rs LayerCache)
+ * where the reference's Slot appends and pushes back on every step (src/cuda_decode.rs:1466-1658). */
+typedef uint64_t b2_plan;
+typedef struct b2_view {
+    uint32_t buf; /* activation buffer */
+    uint32_t off; /* offset in floats */
+} b2_view;
+
+#define B2_OP_NORM 1    /* Op::Norm */
+#define B2_OP_LINEAR 2  /* Op::Linear */
+#define B2_OP_QK_ROPE 3 /* Op::QkRope */
+#define B2_OP_ATTEND 4  /* Op::Attend (window optional; no gate, no draft block) */
+#define B2_OP_GLU 5     /* Op::Glu */
+
+typedef struct b2_op {
+    uint32_t kind;
+    /* NORM: x -> y.  LINEAR: y = mode(W x), z = the gate scalar of B2_MODE_ADD_GATED.
+     * QK_ROPE: x = qkv, y = q_out.  ATTEND: x = q, y = out.  GLU: y = act(x) * z. */
+    b2_view x, y, z;
+    b2_weight w, w2;     /* LINEAR: the matrix, and the second matrix of a pair mode */
+    uint32_t mode;       /* LINEAR: B2_MODE_* */
+    uint32_t n_out, n_in;
+    const float* p0;     /* host f32: NORM weights [n] or NULL; QK_ROPE q_norm [hd] or NULL */
+    const float* p1;     /* host f32: QK_ROPE k_norm [hd] or NULL */
+    uint32_t n, rows, x_stride, out_stride, add; /* NORM; GLU uses n */
+    float pre, eps;      /* NORM (pre, eps); QK_ROPE (eps) */
+    uint32_t kv;         /* QK_ROPE, ATTEND: index of the KV cache */
+    uint32_t nh, nkv, hd;
+    uint32_t half_rot, q_stride, k_off, v_off, interleaved, rope, v_norm, v_from_k; /* QK_ROPE */
+    float scale;         /* ATTEND */
+    uint32_t window;     /* ATTEND: 0 = all positions */
+    uint32_t gelu;       /* GLU */
+} b2_op;
+
+typedef struct b2_graph {
+    const uint64_t* bufs; /* floats in each activation buffer */
+    uint32_t n_bufs;
+    const b2_op* ops;
+    uint32_t n_ops;
+    b2_view input;        /* where a step's x goes */
+    uint32_t n_input;
+    b2_view hidden;       /* read back after a step */
+    uint32_t n_hidden;
+    b2_view logits;       /* read back when n_logits > 0 and the step asks for them */
+    uint32_t n_logits;
+    const uint32_t* kv_nkv; /* per KV cache: KV heads and head dimension (Graph::kv) */
+    const uint32_t* kv_hd;
+    uint32_t n_kv;
+    const uint32_t* rope_halves; /* Graph::rope_halves: a step's rope_cs holds, per entry, cos[half] then sin[half] */
+    uint32_t n_rope;
+    uint32_t max_len;     /* positions each KV cache holds */
+    uint32_t kv_f16;      /* 0: f32 caches (the reference's); 1: f16 caches */
+} b2_graph;
+
+/* B2_OK and a plan, B2_DECLINED (> 0) for an op or shape outside the supported set, < 0 on error. */
+int b2_decode_plan(b2_ctx* ctx, const b2_graph* graph, b2_plan* out);
+int b2_plan_free(b2_ctx* ctx, b2_plan plan);
+/* DecodePlan::step for one token at `pos` (positions 0 .. pos-1 of every cache filled): x [n_input] and
+ * rope_cs from the host, hidden [n_hidden] and (if not NULL) logits [n_logits] back to the host.
+ * Synchronous. Nonzero: nothing valid was written. */
+int b2_plan_step(b2_ctx* ctx, b2_plan plan, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits);
+/* Rows pos0 .. pos0+n-1 of KV cache `kv` from / to host arrays laid out [n][n_kv][hd] f32. */
+int b2_plan_kv_write(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v);
+int b2_plan_kv_read(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, float* k, float* v);
+/* Greedy decoding without the host in the loop: n_tokens steps starting at position pos0 with token
+ * `first_token`; each step looks the token's row up in `embed` (any uploaded format, n_in = n_input),
+ * runs the graph, takes the first largest logit as the next token (the reference's host loop does the
+ * lookup and the argmax on the CPU between steps, src/generate.rs). rope_cs_table: host
+ * [n_tokens][sum of 2 * rope_halves], row i for position pos0 + i. out_tokens: host [n_tokens].
+ * elapsed_ms (optional): device time of the n_tokens steps. Needs n_logits > 0. */
+int b2_plan_generate(b2_ctx* ctx, b2_plan plan, b2_weight embed, int32_t first_token, size_t pos0, size_t n_tokens,
+                     const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms);
+/* Kernel launches of one step of the plan (for launch accounting). */
+int b2_plan_launches(b2_ctx* ctx, b2_plan plan, uint64_t* per_step);
+
 /* No counterpart in the reference (its CUDA backend allocates staging and arena memory freely,
  * src/cuda.rs:572-699). One Q4_K matrix-vector product, y[n_out] = W x, that allocates nothing, for
  * hosts that cannot call cudaMalloc when they need it: a server whose own arena already owns the

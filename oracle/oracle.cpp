@@ -1016,3 +1016,157 @@ ORC_API void orc_encode_q6_k(const float* w, size_t n, uint8_t* out) {
                 }
     }
 }
+
+// ---- one decode token of a Llama-style decoder on the CPU path --------------------------------
+// The per-op arithmetic follows the reference's CPU functions; the step strings them together in the
+// order of QwenModel's dense layer (src/qwen.rs:2344-2522 attention, the SiLU MLP of src/qwen.rs's
+// Mlp, final norm, head) which is also the op order of the decode graph (src/qwen.rs:1477-1528).
+
+// src/kernels.rs:2157-2164 (rmsnorm_f32w): sequential f32 sum of squares, powf(-0.5), x * r * w.
+ORC_API void orc_rmsnorm_f32w(const float* x, const float* w, size_t n, float eps, float* out) {
+    float ss = 0.0f;
+    for (size_t i = 0; i < n; i++) ss += x[i] * x[i];
+    ss = ss / (float)n + eps;
+    float r = std::pow(ss, -0.5f);
+    for (size_t i = 0; i < n; i++) out[i] = x[i] * r * w[i];
+}
+
+// src/kernels.rs:2277-2289 (rope_inv_freq): f64 power, rounded to f32; zeros past the rotated part.
+ORC_API void orc_rope_inv_freq(size_t dim, double theta, double proportion, float* out) {
+    size_t half = dim / 2, rot = (size_t)(proportion * (double)dim) / 2;
+    for (size_t i = 0; i < half; i++) out[i] = i < rot ? (float)(1.0 / std::pow(theta, (double)(2 * i) / (double)dim)) : 0.0f;
+}
+
+// src/kernels.rs:2291-2306 (rope_tables) for one position: the angle is an f32 product.
+ORC_API void orc_rope_table(size_t pos, const float* inv_freq, size_t half, float* cs) {
+    for (size_t i = 0; i < half; i++) {
+        float a = (float)pos * inv_freq[i];
+        cs[i] = std::cos(a);
+        cs[half + i] = std::sin(a);
+    }
+}
+
+// src/kernels.rs:2310-2331 (apply_rope, apply_rope_interleaved) on the first 2 * half values of v.
+ORC_API void orc_apply_rope(float* v, const float* cs, size_t half, int interleaved) {
+    const float *c = cs, *s = cs + half;
+    for (size_t i = 0; i < half; i++) {
+        float& a = interleaved ? v[2 * i] : v[i];
+        float& b = interleaved ? v[2 * i + 1] : v[half + i];
+        float x1 = a, x2 = b;
+        a = x1 * c[i] - x2 * s[i];
+        b = x2 * c[i] + x1 * s[i];
+    }
+}
+
+namespace {
+
+// src/kernels.rs:2076-2094 (dot): 8 accumulators over whole groups of 8, summed in order, then the tail.
+float dot8(const float* a, const float* b, size_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t chunks = n / 8;
+    for (size_t i = 0; i < chunks; i++)
+        for (size_t j = 0; j < 8; j++) acc[j] += a[i * 8 + j] * b[i * 8 + j];
+    float s = 0.0f;
+    for (size_t j = 0; j < 8; j++) s += acc[j];
+    for (size_t i = chunks * 8; i < n; i++) s += a[i] * b[i];
+    return s;
+}
+
+// src/kernels.rs:2333-2344 (softmax_inplace)
+void softmax_inplace(float* x, size_t n) {
+    float mx = -INFINITY;
+    for (size_t i = 0; i < n; i++) mx = std::max(mx, x[i]);
+    float sum = 0.0f;
+    for (size_t i = 0; i < n; i++) {
+        x[i] = fast_exp(x[i] - mx);
+        sum += x[i];
+    }
+    float inv = 1.0f / sum;
+    for (size_t i = 0; i < n; i++) x[i] *= inv;
+}
+
+}  // namespace
+
+ORC_API void orc_softmax_inplace(float* x, size_t n) { softmax_inplace(x, n); }
+
+// src/model.rs:2214-2309 (attention_ext, one token, causal): for each head, scores of the (already
+// scaled) query against keys lo .. len - 1 of its KV head by `dot`, softmax_inplace, then the values
+// accumulated by axpy in key order. kc / vc are [len][nkv][hd].
+ORC_API void orc_attention(const float* q, const float* kc, const float* vc, size_t len, size_t lo, size_t nh, size_t nkv, size_t hd,
+                           float* out, int threads) {
+    size_t rep = nh / nkv, n = len - lo;
+    parallel_for(nh, threads, [&](size_t h) {
+        size_t kvh = h / rep;
+        std::vector<float> sc(n);
+        for (size_t j = 0; j < n; j++) sc[j] = dot8(q + h * hd, kc + ((lo + j) * nkv + kvh) * hd, hd);
+        softmax_inplace(sc.data(), n);
+        float* o = out + h * hd;
+        for (size_t d = 0; d < hd; d++) o[d] = 0.0f;
+        for (size_t j = 0; j < n; j++) {
+            const float* v = vc + ((lo + j) * nkv + kvh) * hd;
+            float a = sc[j];
+            for (size_t d = 0; d < hd; d++) o[d] += a * v[d];
+        }
+    });
+}
+
+struct orc_llama_cfg {
+    uint32_t n_layers, h, nh, nkv, hd, inter, vocab, interleaved;
+    float eps, scale;
+};
+
+namespace {
+
+// y = W x for one token: the CPU decode path (int8 activations), or the f64 product of the dequantized
+// weights rounded to f32 (`exact`), which is what a GPU result is bounded against.
+void matvec(const Matrix& m, const float* x, float* y, int exact, int threads) {
+    if (!exact) {
+        matmul_quant(m, x, 1, y, threads);
+        return;
+    }
+    std::vector<double> yd(m.n_out);
+    orc_matmul_f64((void*)&m, x, 1, yd.data(), threads);
+    for (size_t i = 0; i < m.n_out; i++) y[i] = (float)yd[i];
+}
+
+}  // namespace
+
+// One token at position `pos`. mats: per layer q, k, v, o, gate, up, down (7 * n_layers), then the head.
+// norms: per layer ln_pre, ln_post (2 * n_layers), then the final norm. kcache / vcache:
+// [n_layers][max_len][nkv][hd], rows 0 .. pos - 1 filled; row pos is written. x: the token's embedding
+// (h values). Outputs: hidden (h, after the final norm) and logits (vocab), either may be null.
+ORC_API void orc_llama_step(const orc_llama_cfg* c, void* const* mats, const float* const* norms, float* kcache, float* vcache,
+                            size_t max_len, size_t pos, const float* x_in, const float* rope_cs, float* hidden, float* logits, int exact,
+                            int threads) {
+    size_t h = c->h, nh = c->nh, nkv = c->nkv, hd = c->hd, inter = c->inter, half = hd / 2;
+    std::vector<float> x(x_in, x_in + h), hn(h), q(nh * hd), k(nkv * hd), v(nkv * hd), att(nh * hd), y(h), g(inter), u(inter);
+    for (size_t l = 0; l < c->n_layers; l++) {
+        void* const* m = mats + 7 * l;
+        orc_rmsnorm_f32w(x.data(), norms[2 * l], h, c->eps, hn.data());
+        matvec(*(Matrix*)m[0], hn.data(), q.data(), exact, threads);
+        matvec(*(Matrix*)m[1], hn.data(), k.data(), exact, threads);
+        matvec(*(Matrix*)m[2], hn.data(), v.data(), exact, threads);
+        for (size_t hh = 0; hh < nh; hh++) {
+            orc_apply_rope(q.data() + hh * hd, rope_cs, half, (int)c->interleaved);
+            for (size_t d = 0; d < hd; d++) q[hh * hd + d] *= c->scale;
+        }
+        for (size_t hh = 0; hh < nkv; hh++) orc_apply_rope(k.data() + hh * hd, rope_cs, half, (int)c->interleaved);
+        float* kc = kcache + l * max_len * nkv * hd;
+        float* vc = vcache + l * max_len * nkv * hd;
+        std::memcpy(kc + pos * nkv * hd, k.data(), nkv * hd * sizeof(float));
+        std::memcpy(vc + pos * nkv * hd, v.data(), nkv * hd * sizeof(float));
+        orc_attention(q.data(), kc, vc, pos + 1, 0, nh, nkv, hd, att.data(), threads);
+        matvec(*(Matrix*)m[3], att.data(), y.data(), exact, threads);
+        for (size_t i = 0; i < h; i++) x[i] += y[i];
+        orc_rmsnorm_f32w(x.data(), norms[2 * l + 1], h, c->eps, hn.data());
+        matvec(*(Matrix*)m[4], hn.data(), g.data(), exact, threads);
+        matvec(*(Matrix*)m[5], hn.data(), u.data(), exact, threads);
+        // src/kernels.rs:2188-2198 (silu_mul)
+        for (size_t i = 0; i < inter; i++) g[i] = g[i] / (1.0f + fast_exp(-g[i])) * u[i];
+        matvec(*(Matrix*)m[6], g.data(), y.data(), exact, threads);
+        for (size_t i = 0; i < h; i++) x[i] += y[i];
+    }
+    orc_rmsnorm_f32w(x.data(), norms[2 * c->n_layers], h, c->eps, hn.data());
+    if (hidden) std::memcpy(hidden, hn.data(), h * sizeof(float));
+    if (logits) matvec(*(Matrix*)mats[7 * c->n_layers], hn.data(), logits, exact, threads);
+}

@@ -80,6 +80,13 @@ def lib() -> C.CDLL:
             "orc_encode_q8_0": (None, [vp, sz, vp]),
             "orc_encode_q4_k": (None, [vp, sz, vp]),
             "orc_encode_q6_k": (None, [vp, sz, vp]),
+            "orc_rmsnorm_f32w": (None, [vp, vp, sz, f32, vp]),
+            "orc_rope_inv_freq": (None, [sz, C.c_double, C.c_double, vp]),
+            "orc_rope_table": (None, [sz, vp, sz, vp]),
+            "orc_apply_rope": (None, [vp, vp, sz, i32]),
+            "orc_softmax_inplace": (None, [vp, sz]),
+            "orc_attention": (None, [vp, vp, vp, sz, sz, sz, sz, sz, vp, i32]),
+            "orc_llama_step": (None, [vp, vp, vp, vp, vp, sz, sz, vp, vp, vp, vp, i32, i32]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
@@ -256,3 +263,86 @@ def row_err(y: np.ndarray, r: np.ndarray) -> float:
     num = np.abs(y - r).reshape(r.shape[0], -1).max(axis=1)
     den = np.maximum(np.abs(r).reshape(r.shape[0], -1).max(axis=1), 1e-30)
     return float((num / den).max())
+
+
+# ---- one decode token (src/kernels.rs rmsnorm / rope / softmax, src/model.rs attention_ext, src/qwen.rs layer order) ----
+def rmsnorm_f32w(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().orc_rmsnorm_f32w(_p(x), _p(w), x.size, eps, _p(out))
+    return out
+
+
+def rope_inv_freq(dim: int, theta: float, proportion: float = 1.0) -> np.ndarray:
+    out = np.empty(dim // 2, dtype=np.float32)
+    lib().orc_rope_inv_freq(dim, theta, proportion, _p(out))
+    return out
+
+
+def rope_table(pos: int, inv_freq: np.ndarray) -> np.ndarray:
+    """cos[half] then sin[half] of one position."""
+    f = np.ascontiguousarray(inv_freq, dtype=np.float32)
+    cs = np.empty(2 * f.size, dtype=np.float32)
+    lib().orc_rope_table(pos, _p(f), f.size, _p(cs))
+    return cs
+
+
+def apply_rope(v: np.ndarray, cs: np.ndarray, interleaved: bool) -> np.ndarray:
+    v = np.array(v, dtype=np.float32)
+    cs = np.ascontiguousarray(cs, dtype=np.float32)
+    lib().orc_apply_rope(_p(v), _p(cs), cs.size // 2, int(interleaved))
+    return v
+
+
+def softmax(x: np.ndarray) -> np.ndarray:
+    x = np.array(x, dtype=np.float32)
+    lib().orc_softmax_inplace(_p(x), x.size)
+    return x
+
+
+def attention(q: np.ndarray, kc: np.ndarray, vc: np.ndarray, length: int, nh: int, nkv: int, hd: int, lo: int = 0,
+              threads: int | None = None) -> np.ndarray:
+    """q [nh][hd] already scaled; kc / vc [>= length][nkv][hd]; keys lo .. length - 1."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    kc = np.ascontiguousarray(kc, dtype=np.float32)
+    vc = np.ascontiguousarray(vc, dtype=np.float32)
+    out = np.empty(nh * hd, dtype=np.float32)
+    lib().orc_attention(_p(q), _p(kc), _p(vc), length, lo, nh, nkv, hd, _p(out), threads or cpu_threads())
+    return out
+
+
+class LlamaCfg(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_layers", "h", "nh", "nkv", "hd", "inter", "vocab", "interleaved")] + [("eps", C.c_float),
+                                                                                                                  ("scale", C.c_float)]
+
+
+class Llama:
+    """The CPU decoder: per layer matrices q k v o gate up down, norms ln_pre ln_post; final norm; head.
+    Keeps its own KV caches [n_layers][max_len][nkv][hd]."""
+
+    def __init__(self, cfg: LlamaCfg, layers: list[dict], final_norm: np.ndarray, head: Matrix, max_len: int):
+        self.cfg, self.layers, self.head, self.max_len = cfg, layers, head, max_len
+        mats = []
+        norms = []
+        for L in layers:
+            mats += [L[k].h for k in ("q", "k", "v", "o", "gate", "up", "down")]
+            norms += [np.ascontiguousarray(L["ln_pre"], dtype=np.float32), np.ascontiguousarray(L["ln_post"], dtype=np.float32)]
+        mats.append(head.h)
+        norms.append(np.ascontiguousarray(final_norm, dtype=np.float32))
+        self._norms = norms
+        self._mats = (C.c_void_p * len(mats))(*mats)
+        self._normp = (C.c_void_p * len(norms))(*[_p(n) for n in norms])
+        row = cfg.nkv * cfg.hd
+        self.kc = np.zeros((cfg.n_layers, max_len, row), dtype=np.float32)
+        self.vc = np.zeros((cfg.n_layers, max_len, row), dtype=np.float32)
+
+    def step(self, pos: int, x: np.ndarray, rope_cs: np.ndarray, exact: bool, want_logits: bool = True, threads: int | None = None):
+        """`exact`: matrix-vector products as f64 sums over the dequantized weights; else the CPU decode kernels."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        cs = np.ascontiguousarray(rope_cs, dtype=np.float32)
+        hidden = np.empty(self.cfg.h, dtype=np.float32)
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        lib().orc_llama_step(C.byref(self.cfg), self._mats, self._normp, _p(self.kc), _p(self.vc), self.max_len, pos, _p(x), _p(cs), _p(hidden),
+                             _p(logits) if logits is not None else None, int(exact), threads or cpu_threads())
+        return hidden, logits

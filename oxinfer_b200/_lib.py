@@ -28,6 +28,46 @@ class RowsJob(C.Structure):
     _fields_ = [("w", C.c_uint64), ("up", C.c_uint64), ("n_out", C.c_size_t), ("y", C.c_void_p)]
 
 
+class View(C.Structure):
+    _fields_ = [("buf", C.c_uint32), ("off", C.c_uint32)]
+
+
+OP_NORM, OP_LINEAR, OP_QK_ROPE, OP_ATTEND, OP_GLU = 1, 2, 3, 4, 5
+
+
+class Op(C.Structure):
+    """``b2_op`` of ``include/b200qmm.h`` (field order is the ABI)."""
+
+    _fields_ = [
+        ("kind", C.c_uint32),
+        ("x", View), ("y", View), ("z", View),
+        ("w", C.c_uint64), ("w2", C.c_uint64),
+        ("mode", C.c_uint32), ("n_out", C.c_uint32), ("n_in", C.c_uint32),
+        ("p0", C.c_void_p), ("p1", C.c_void_p),
+        ("n", C.c_uint32), ("rows", C.c_uint32), ("x_stride", C.c_uint32), ("out_stride", C.c_uint32), ("add", C.c_uint32),
+        ("pre", C.c_float), ("eps", C.c_float),
+        ("kv", C.c_uint32), ("nh", C.c_uint32), ("nkv", C.c_uint32), ("hd", C.c_uint32),
+        ("half_rot", C.c_uint32), ("q_stride", C.c_uint32), ("k_off", C.c_uint32), ("v_off", C.c_uint32),
+        ("interleaved", C.c_uint32), ("rope", C.c_uint32), ("v_norm", C.c_uint32), ("v_from_k", C.c_uint32),
+        ("scale", C.c_float), ("window", C.c_uint32), ("gelu", C.c_uint32),
+    ]
+
+
+class GraphDesc(C.Structure):
+    """``b2_graph``."""
+
+    _fields_ = [
+        ("bufs", C.POINTER(C.c_uint64)), ("n_bufs", C.c_uint32),
+        ("ops", C.POINTER(Op)), ("n_ops", C.c_uint32),
+        ("input", View), ("n_input", C.c_uint32),
+        ("hidden", View), ("n_hidden", C.c_uint32),
+        ("logits", View), ("n_logits", C.c_uint32),
+        ("kv_nkv", C.POINTER(C.c_uint32)), ("kv_hd", C.POINTER(C.c_uint32)), ("n_kv", C.c_uint32),
+        ("rope_halves", C.POINTER(C.c_uint32)), ("n_rope", C.c_uint32),
+        ("max_len", C.c_uint32), ("kv_f16", C.c_uint32),
+    ]
+
+
 def build(verbose: bool = False) -> Path:
     """Compiles every CUDA source for sm_100a into ``libb200qmm.so`` (nvcc cross-compiles without a GPU)."""
     r = subprocess.run(["make", "-C", str(CSRC), "-j8"], capture_output=True, text=True)
@@ -67,6 +107,14 @@ _SIGNATURES = {
     "b2_route_topk_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
     "b2_prepare_x_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "b2_matvec_prepared_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_decode_plan": (C.c_int, [C.c_void_p, C.POINTER(GraphDesc), C.POINTER(C.c_uint64)]),
+    "b2_plan_free": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "b2_plan_step": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_plan_kv_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "b2_plan_kv_read": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "b2_plan_generate": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                                   C.POINTER(C.c_float)]),
+    "b2_plan_launches": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64)]),
     "b2_matvec_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
 }
 

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "kernels.h"
+#include "plan.h"
 
 namespace b2 {
 
@@ -63,6 +64,7 @@ class Backend {
     std::string stats_text;
     std::unordered_map<uint64_t, Weight> weights;
     std::unordered_map<uint64_t, Moe> moes;
+    std::unordered_map<uint64_t, DecodePlanImpl*> decode_plans;
     Scratch moe_idx, moe_xg, moe_g, moe_a, moe_o;
     uint64_t next_handle = 1;
     uint64_t launches = 0;
@@ -284,6 +286,8 @@ class Backend {
     int free_weight(uint64_t h) {
         auto it = weights.find(h);
         if (it == weights.end()) return fail(B2_ERR_ARG, "[b200qmm: free_weight: unknown weight]");
+        for (auto& dp : decode_plans)
+            if (dp.second->uses_weight(h)) return fail(B2_ERR_ARG, "[b200qmm: free_weight: a decode plan still uses this weight (b2_plan_free first)]");
         cudaStreamSynchronize(stream);
         for (GemmPlan* p : plans) gemm_tc_plan_destroy(p);  // tensor maps may point into this weight
         plans.clear();
@@ -696,8 +700,75 @@ class Backend {
         return stats_text.c_str();
     }
 
+    // ---- Backend::decode_plan (src/gpu.rs:262-289) and DecodePlan::step (src/gpu_decode.rs:538-587) ----
+    int decode_plan(const b2_graph* g, uint64_t* out) {
+        if (!out) return fail(B2_ERR_ARG, "[b200qmm: decode_plan: null argument]");
+        DecodePlanImpl* p = nullptr;
+        std::string e;
+        int rc = DecodePlanImpl::create(
+            g,
+            [this](uint64_t h) -> const WeightDev* {
+                Weight* w = find(h);
+                return w ? &w->dev : nullptr;
+            },
+            sm_count, &p, e);
+        if (rc) {
+            err = e;
+            return rc;
+        }
+        uint64_t h = next_handle++;
+        decode_plans[h] = p;
+        launches += p->launches_per_step();  // the eager first pass
+        *out = h;
+        return B2_OK;
+    }
+    DecodePlanImpl* find_plan(uint64_t h) {
+        auto it = decode_plans.find(h);
+        return it == decode_plans.end() ? nullptr : it->second;
+    }
+    int plan_free(uint64_t h) {
+        auto it = decode_plans.find(h);
+        if (it == decode_plans.end()) return fail(B2_ERR_ARG, "[b200qmm: plan_free: unknown plan]");
+        cudaStreamSynchronize(stream);
+        delete it->second;
+        decode_plans.erase(it);
+        return B2_OK;
+    }
+    int plan_step(uint64_t h, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p) return fail(B2_ERR_ARG, "[b200qmm: plan_step: unknown plan]");
+        std::string e;
+        int rc = p->step(stream, pos, x, rope_cs, hidden, logits, e);
+        launches += p->launches_per_step() + 1;
+        calls++;
+        if (rc) err = e;
+        return rc;
+    }
+    int plan_kv(uint64_t h, bool write, uint32_t kv, size_t pos0, size_t n, float* k, float* v) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p) return fail(B2_ERR_ARG, "[b200qmm: plan_kv: unknown plan]");
+        std::string e;
+        int rc = write ? p->kv_write(stream, kv, pos0, n, k, v, e) : p->kv_read(stream, kv, pos0, n, k, v, e);
+        if (rc) err = e;
+        return rc;
+    }
+    int plan_generate(uint64_t h, uint64_t embed, int32_t first, size_t pos0, size_t n, const float* rope, int32_t* out, float* ms) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p) return fail(B2_ERR_ARG, "[b200qmm: plan_generate: unknown plan]");
+        Weight* w = find(embed);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: plan_generate: unknown embedding weight]");
+        std::string e;
+        int rc = p->generate(stream, embed, w->dev, first, pos0, n, rope, out, ms, e);
+        launches += (p->launches_per_step() + 2) * n + 1;
+        calls++;
+        if (rc) err = e;
+        return rc;
+    }
+
     void close() {
         cudaStreamSynchronize(stream);
+        for (auto& dp : decode_plans) delete dp.second;
+        decode_plans.clear();
         for (auto& kv : weights) drop(kv.second.owned);
         weights.clear();
         for (auto& kv : moes) {
@@ -907,4 +978,43 @@ B2_EXPORT int b2_matvec_prepared_dev(b2_ctx* ctx, b2_weight w, b2_weight up, con
 B2_EXPORT int b2_check_status(b2_ctx* ctx) {
     LOCKED(ctx);
     return ctx->be.check_gemm_status();
+}
+
+B2_EXPORT int b2_decode_plan(b2_ctx* ctx, const b2_graph* graph, b2_plan* out) {
+    LOCKED(ctx);
+    return ctx->be.decode_plan(graph, out);
+}
+
+B2_EXPORT int b2_plan_free(b2_ctx* ctx, b2_plan plan) {
+    LOCKED(ctx);
+    return ctx->be.plan_free(plan);
+}
+
+B2_EXPORT int b2_plan_step(b2_ctx* ctx, b2_plan plan, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits) {
+    LOCKED(ctx);
+    return ctx->be.plan_step(plan, pos, x, rope_cs, hidden, logits);
+}
+
+B2_EXPORT int b2_plan_kv_write(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v) {
+    LOCKED(ctx);
+    return ctx->be.plan_kv(plan, true, kv, pos0, n, const_cast<float*>(k), const_cast<float*>(v));
+}
+
+B2_EXPORT int b2_plan_kv_read(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, float* k, float* v) {
+    LOCKED(ctx);
+    return ctx->be.plan_kv(plan, false, kv, pos0, n, k, v);
+}
+
+B2_EXPORT int b2_plan_generate(b2_ctx* ctx, b2_plan plan, b2_weight embed, int32_t first_token, size_t pos0, size_t n_tokens,
+                               const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms) {
+    LOCKED(ctx);
+    return ctx->be.plan_generate(plan, embed, first_token, pos0, n_tokens, rope_cs_table, out_tokens, elapsed_ms);
+}
+
+B2_EXPORT int b2_plan_launches(b2_ctx* ctx, b2_plan plan, uint64_t* per_step) {
+    LOCKED(ctx);
+    b2::DecodePlanImpl* p = ctx->be.find_plan(plan);
+    if (!p || !per_step) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: plan_launches: unknown plan]");
+    *per_step = p->launches_per_step();
+    return B2_OK;
 }

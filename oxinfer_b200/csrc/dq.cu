@@ -10,8 +10,13 @@ namespace {
 
 // One thread per 8 consecutive output elements of a row.
 template <int FMT>
-__global__ void __launch_bounds__(256) dq_kernel(WeightDev w, size_t r0, size_t nrows, float* __restrict__ out) {
+__global__ void __launch_bounds__(256) dq_kernel(WeightDev w, size_t r0, size_t nrows, float* __restrict__ out,
+                                                 const int* __restrict__ row_dev) {
     size_t K = w.n_in;
+    if (row_dev) {  // the row is named on the device (a token's embedding); out-of-range ids read row 0
+        int t = *row_dev;
+        r0 = (t >= 0 && (size_t)t < w.n_out) ? (size_t)t : 0;
+    }
     size_t per_row = K / 8;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nrows * per_row) return;
@@ -121,16 +126,16 @@ __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, size_t nbloc
 
 }  // namespace
 
-cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st) {
+cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev) {
     if (nrows == 0) return cudaSuccess;
     size_t n = nrows * (w.n_in / 8);
     unsigned grid = (unsigned)((n + 255) / 256);
     switch (w.fmt) {
-        case B2_FMT_MLX4: dq_kernel<B2_FMT_MLX4><<<grid, 256, 0, st>>>(w, r0, nrows, out); break;
-        case B2_FMT_Q4_K: dq_kernel<B2_FMT_Q4_K><<<grid, 256, 0, st>>>(w, r0, nrows, out); break;
-        case B2_FMT_Q6_K: dq_kernel<B2_FMT_Q6_K><<<grid, 256, 0, st>>>(w, r0, nrows, out); break;
-        case B2_FMT_Q8_0: dq_kernel<B2_FMT_Q8_0><<<grid, 256, 0, st>>>(w, r0, nrows, out); break;
-        case B2_FMT_F8E4M3: dq_kernel<B2_FMT_F8E4M3><<<grid, 256, 0, st>>>(w, r0, nrows, out); break;
+        case B2_FMT_MLX4: dq_kernel<B2_FMT_MLX4><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
+        case B2_FMT_Q4_K: dq_kernel<B2_FMT_Q4_K><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
+        case B2_FMT_Q6_K: dq_kernel<B2_FMT_Q6_K><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
+        case B2_FMT_Q8_0: dq_kernel<B2_FMT_Q8_0><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
+        case B2_FMT_F8E4M3: dq_kernel<B2_FMT_F8E4M3><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

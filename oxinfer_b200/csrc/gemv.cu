@@ -20,6 +20,7 @@
 #include <cstdio>
 
 #include "kernels.h"
+#include "xplanes.cuh"
 
 namespace b2 {
 
@@ -27,7 +28,6 @@ namespace {
 
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr float XQ_MAX = 1040000.0f;  // |q0 + 128 q1 + 16384 q2| <= 63 + 128*63 + 16384*63 = 1040319
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -39,30 +39,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, XPlanes out) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= K / 32) return;
-    float v = x[warp * 32 + lane];
-    float a = fabsf(v);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    float s = a / XQ_MAX;
-    int q = a > 0.0f ? __float2int_rn(v * (XQ_MAX / a)) : 0;
-    q = max(-(int)XQ_MAX, min((int)XQ_MAX, q));
-    int q0 = ((q + 64) & 127) - 64;
-    int r1 = (q - q0) >> 7;
-    int q1 = ((r1 + 64) & 127) - 64;
-    int q2 = (r1 - q1) >> 7;
-    size_t at = (size_t)warp * 32 + lane;
-    out.planes[at] = (int8_t)q0;
-    out.planes[(size_t)K + at] = (int8_t)q1;
-    out.planes[2 * (size_t)K + at] = (int8_t)q2;
-    int sum16 = q;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) sum16 += __shfl_xor_sync(0xffffffffu, sum16, o);
-    int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 16);
-    if ((lane & 15) == 0) out.v16[warp * 2 + (lane >> 4)] = sum16;
-    if (lane == 0) {
-        out.xs[warp] = s;
-        out.xsum[warp] = s * (float)sum32;
-    }
+    xplanes_block(x[warp * 32 + lane], warp, lane, K, out);
 }
 
 // The vector as the kernels see it in shared memory. Plane p is K bytes at p0 + p K with its 16-byte
@@ -420,9 +397,11 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t smem = XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in);
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, XF32> : gemv_kernel<F, false, XF32>;
-    if (smem > 48 * 1024) {
+    static size_t smem_set[2] = {48 * 1024, 48 * 1024};  // largest size asked for so far, per kernel: later launches (and captures) skip the call
+    if (smem > smem_set[pair]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
+        smem_set[pair] = smem;
     }
     const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
     size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;

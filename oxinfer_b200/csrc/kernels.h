@@ -5,8 +5,9 @@
 namespace b2 {
 
 // ---- dq.cu: bit-exact dequantization --------------------------------------------------------
-// Rows [r0, r0 + nrows) of `w` to f32, row-major [nrows][n_in].
-cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st);
+// Rows [r0, r0 + nrows) of `w` to f32, row-major [nrows][n_in]. With `row_dev`, r0 is read from that
+// device word when the kernel runs (a token's embedding row inside a captured graph).
+cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev = nullptr);
 // Raw GGUF Q6_K / Q8_0 rows (device) -> the split planes described in formats.cuh.
 cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uint8_t* ql, uint8_t* qh, int8_t* sc, uint16_t* d,
                               cudaStream_t st);
@@ -72,5 +73,39 @@ cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_
 cudaError_t launch_moe_act(const float* g, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
 cudaError_t launch_moe_combine(const float* o, const float* row_scale, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y,
                                cudaStream_t st);
+
+// ---- decode_ops.cu: the non-matmul ops of one decode token -------------------------------------------
+// Every kernel reads the step words `sp` on the device: sp[0] position of the token, sp[1] position of row 0
+// of the RoPE table, sp[2] tokens generated so far (the argmax kernel advances [0] and [2]).
+struct DecNorm {
+    uint32_t n, x_stride, out_stride, add, planes;
+    float pre, eps;
+};
+struct DecRope {
+    uint32_t nh, nkv, hd, half_rot, q_stride, k_off, v_off, interleaved, v_norm, v_from_k, max_len;
+    uint32_t cs_stride, cs_off;  // floats per position in the RoPE table, and where this op's cos/sin start in a row
+    float eps;
+};
+struct DecAttn {
+    uint32_t nh, nkv, hd, max_len, window, planes;
+    float scale;
+};
+cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st);
+// KV caches are [nkv][max_len][hd], f32 or (kv_f16) f16.
+cudaError_t launch_qk_rope(const float* qkv, float* qo, void* kc, void* vc, int kv_f16, const float* qn, const float* kn, const float* cs_table,
+                           const uint32_t* sp, const DecRope& p, cudaStream_t st);
+bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
+size_t attend_part_floats(uint32_t nh, uint32_t hd);  // scratch for the per-split partials
+// counters: nkv zeroed words (left zero by every launch); status: set to 1 if a bounded wait gave up.
+cudaError_t launch_attend(const float* q, const void* kc, const void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st);
+// Host-order rows [n][nkv][hd] f32 <-> cache rows pos0 .. pos0 + n - 1.
+cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, uint32_t nkv, uint32_t hd, uint32_t max_len, uint32_t pos0,
+                           uint32_t n, cudaStream_t st);
+cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uint32_t count, int* token, int tok, cudaStream_t st);
+cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st);
+// pval / pidx: 128 words each; counter: one zeroed word.
+cudaError_t launch_argmax(const float* logits, uint32_t n, float* pval, int* pidx, uint32_t* counter, int* token, int* out_tokens, uint32_t* sp,
+                          cudaStream_t st);
 
 }  // namespace b2

@@ -1,0 +1,525 @@
+// Decode plan: resolves a b2_graph to device pointers, decides where the activation planes of each
+// matrix-vector product come from (written by the norm / attention kernel that produces the vector, or by
+// a plane kernel of their own), captures the op list into CUDA graphs, and runs steps.
+// What the reference does per token with ~11 cuLaunchKernel calls per layer from the host
+// (src/cuda_decode.rs:1466-1658) is one cudaGraphLaunch here.
+#include "plan.h"
+
+#include <cstdarg>
+#include <cstring>
+#include <algorithm>
+#include <map>
+#include <memory>
+#include <tuple>
+
+namespace b2 {
+
+namespace {
+
+constexpr uint32_t OP_XPLANES = 100;  // internal: planes of a vector no producer kernel could write
+
+std::string fmt(const char* f, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, f);
+    vsnprintf(buf, sizeof buf, f, ap);
+    va_end(ap);
+    return buf;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+#define PLAN_CUDA(call, what)                                                                  \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            err = fmt("[b200qmm: plan: %s: %s]", what, cudaGetErrorString(e_));                \
+            return e_ == cudaErrorMemoryAllocation ? B2_ERR_NOMEM : B2_ERR_CUDA;               \
+        }                                                                                      \
+    } while (0)
+
+}  // namespace
+
+DecodePlanImpl::~DecodePlanImpl() {
+    if (step_exec_) cudaGraphExecDestroy(step_exec_);
+    if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
+    if (ev0_) cudaEventDestroy(ev0_);
+    if (ev1_) cudaEventDestroy(ev1_);
+    if (cap_stream_) cudaStreamDestroy(cap_stream_);
+    for (auto& k : kv_) {
+        if (k.k) cudaFree(k.k);
+        if (k.v) cudaFree(k.v);
+    }
+    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
+    for (void* p : frees)
+        if (p) cudaFree(p);
+}
+
+bool DecodePlanImpl::uses_weight(uint64_t h) const {
+    for (uint64_t w : weight_handles_)
+        if (w == h) return true;
+    return h != 0 && h == gen_embed_;
+}
+
+int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, DecodePlanImpl** out,
+                           std::string& err) {
+    if (!g || !g->bufs || !g->ops || g->n_bufs == 0 || g->n_ops == 0 || !out) {
+        err = "[b200qmm: decode_plan: empty graph]";
+        return B2_ERR_ARG;
+    }
+    if (g->max_len == 0 || g->n_rope > 8) {
+        err = "[b200qmm: decode_plan: max_len must be positive and at most 8 RoPE tables are taken]";
+        return B2_ERR_ARG;
+    }
+    std::unique_ptr<DecodePlanImpl> p(new DecodePlanImpl());
+    p->sm_count_ = sm_count;
+    p->max_len_ = g->max_len;
+    p->kv_f16_ = g->kv_f16 ? 1 : 0;
+
+    // ---- activation buffers: one allocation, each buffer 256-byte aligned --------------------------
+    size_t total = 0;
+    std::vector<size_t> off(g->n_bufs);
+    for (uint32_t i = 0; i < g->n_bufs; i++) {
+        off[i] = total;
+        total += align_up((size_t)g->bufs[i], 64);
+    }
+    PLAN_CUDA(cudaMalloc((void**)&p->bufs_, std::max<size_t>(total, 64) * sizeof(float)), "cudaMalloc(buffers)");
+    PLAN_CUDA(cudaMemset(p->bufs_, 0, std::max<size_t>(total, 64) * sizeof(float)), "cudaMemset(buffers)");
+    for (uint32_t i = 0; i < g->n_bufs; i++) {
+        p->buf_ptr_.push_back(p->bufs_ + off[i]);
+        p->buf_len_.push_back((size_t)g->bufs[i]);
+    }
+    bool bad_view = false;
+    auto view = [&](b2_view v, size_t n) -> float* {
+        if (v.buf >= g->n_bufs || (size_t)v.off + n > p->buf_len_[v.buf]) {
+            bad_view = true;
+            return nullptr;
+        }
+        return p->buf_ptr_[v.buf] + v.off;
+    };
+
+    // ---- RoPE table layout ------------------------------------------------------------------------
+    std::vector<uint32_t> cs_off(g->n_rope + 1, 0);
+    for (uint32_t i = 0; i < g->n_rope; i++) cs_off[i + 1] = cs_off[i] + 2 * g->rope_halves[i];
+    p->cs_stride_ = cs_off[g->n_rope];
+
+    // ---- KV caches --------------------------------------------------------------------------------
+    const size_t esz = p->kv_f16_ ? 2 : 4;
+    uint32_t max_nh = 0, max_hd = 0, max_nkv = 0;
+    size_t max_row = 0;
+    for (uint32_t i = 0; i < g->n_kv; i++) {
+        Kv k;
+        k.nkv = g->kv_nkv[i];
+        k.hd = g->kv_hd[i];
+        size_t bytes = (size_t)k.nkv * g->max_len * k.hd * esz;
+        PLAN_CUDA(cudaMalloc(&k.k, bytes), "cudaMalloc(K cache)");
+        p->kv_.push_back(k);  // pushed before V so that a failure below still frees K
+        PLAN_CUDA(cudaMalloc(&p->kv_.back().v, bytes), "cudaMalloc(V cache)");
+        PLAN_CUDA(cudaMemset(p->kv_.back().k, 0, bytes), "cudaMemset(K cache)");
+        PLAN_CUDA(cudaMemset(p->kv_.back().v, 0, bytes), "cudaMemset(V cache)");
+        max_nkv = std::max(max_nkv, k.nkv);
+        max_row = std::max(max_row, (size_t)k.nkv * k.hd);
+    }
+
+    // ---- norm weights: one device block -----------------------------------------------------------
+    size_t n_consts = 0;
+    for (uint32_t i = 0; i < g->n_ops; i++) {
+        const b2_op& o = g->ops[i];
+        if (o.kind == B2_OP_NORM && o.p0) n_consts += align_up(o.n, 64);
+        if (o.kind == B2_OP_QK_ROPE) n_consts += (o.p0 ? align_up(o.hd, 64) : 0) + (o.p1 ? align_up(o.hd, 64) : 0);
+    }
+    PLAN_CUDA(cudaMalloc((void**)&p->consts_, std::max<size_t>(n_consts, 64) * sizeof(float)), "cudaMalloc(norm weights)");
+    size_t consts_at = 0;
+    auto put_const = [&](const float* host, size_t n, const float** dev) -> cudaError_t {
+        float* d = p->consts_ + consts_at;
+        consts_at += align_up(n, 64);
+        *dev = d;
+        return cudaMemcpy(d, host, n * sizeof(float), cudaMemcpyHostToDevice);
+    };
+
+    // ---- ops -------------------------------------------------------------------------------------
+    // Planes bookkeeping. key = (buffer, offset, length) of a vector; `valid` = planes of the current
+    // contents exist in that region; `writer` = index (in ops_) of the norm / attention op that wrote
+    // exactly this vector last and can still be told to write its planes.
+    using Key = std::tuple<uint32_t, uint32_t, uint32_t>;
+    std::map<Key, size_t> valid;    // -> region index
+    std::map<Key, size_t> writer;   // -> op index
+    std::vector<size_t> region_k;   // K of each planes region
+    auto touch = [&](uint32_t buf) {  // a write into `buf`: planes and writers of its vectors are stale
+        for (auto it = valid.begin(); it != valid.end();) it = std::get<0>(it->first) == buf ? valid.erase(it) : std::next(it);
+        for (auto it = writer.begin(); it != writer.end();) it = std::get<0>(it->first) == buf ? writer.erase(it) : std::next(it);
+    };
+    std::vector<std::pair<size_t, size_t>> region_of_op;  // (op index, region): xp filled in once regions are allocated
+
+    for (uint32_t i = 0; i < g->n_ops; i++) {
+        const b2_op& o = g->ops[i];
+        Op op;
+        op.kind = o.kind;
+        switch (o.kind) {
+            case B2_OP_NORM: {
+                if (o.n == 0 || o.rows == 0) {
+                    err = "[b200qmm: decode_plan: norm of nothing]";
+                    return B2_ERR_ARG;
+                }
+                size_t xs = o.x_stride ? o.x_stride : o.n, os = o.out_stride ? o.out_stride : o.n;
+                op.x = view(o.x, (size_t)(o.rows - 1) * xs + o.n);
+                op.y = view(o.y, (size_t)(o.rows - 1) * os + o.n);
+                op.norm = DecNorm{o.n, (uint32_t)xs, (uint32_t)os, o.add ? 1u : 0u, 0u, o.pre == 0.0f ? 1.0f : o.pre, o.eps};
+                op.rows = o.rows;
+                if (o.p0) PLAN_CUDA(put_const(o.p0, o.n, &op.p0), "cudaMemcpy(norm weights)");
+                touch(o.y.buf);
+                if (o.rows == 1 && o.n % 32 == 0) writer[Key{o.y.buf, o.y.off, o.n}] = p->ops_.size();
+                break;
+            }
+            case B2_OP_LINEAR: {
+                const WeightDev* w = resolve(o.w);
+                if (!w) {
+                    err = "[b200qmm: decode_plan: unknown weight handle]";
+                    return B2_ERR_ARG;
+                }
+                if (w->n_out != o.n_out || w->n_in != o.n_in) {
+                    err = fmt("[b200qmm: decode_plan: linear %u x %u does not match its weight %zu x %zu]", o.n_out, o.n_in, w->n_out, w->n_in);
+                    return B2_ERR_ARG;
+                }
+                if (!gemv_supports(*w)) {
+                    err = "[b200qmm: decode_plan: a weight's shape is outside the matrix-vector kernels]";
+                    return B2_DECLINED;
+                }
+                op.w = *w;
+                p->weight_handles_.push_back(o.w);
+                op.mode = (int)o.mode;
+                if (o.mode > B2_MODE_ADD_GATED) {
+                    err = "[b200qmm: decode_plan: bad linear mode]";
+                    return B2_ERR_ARG;
+                }
+                op.pair = o.mode == B2_MODE_SILU_PAIR || o.mode == B2_MODE_GELU_PAIR;
+                if (op.pair) {
+                    const WeightDev* u = resolve(o.w2);
+                    if (!u) {
+                        err = "[b200qmm: decode_plan: a pair needs its second matrix]";
+                        return B2_ERR_ARG;
+                    }
+                    if (u->fmt != w->fmt || u->n_in != w->n_in || u->n_out != w->n_out) {
+                        err = "[b200qmm: decode_plan: the pair's matrices differ in shape or format]";
+                        return B2_DECLINED;
+                    }
+                    op.w2 = *u;
+                    p->weight_handles_.push_back(o.w2);
+                }
+                op.x = view(o.x, o.n_in);
+                op.y = view(o.y, o.n_out);
+                if (o.mode == B2_MODE_ADD_GATED) op.z = view(o.z, 1);
+                if (w->fmt != B2_FMT_F8E4M3) {
+                    Key key{o.x.buf, o.x.off, o.n_in};
+                    size_t region;
+                    auto v = valid.find(key);
+                    if (v != valid.end()) {
+                        region = v->second;
+                    } else {
+                        region = region_k.size();
+                        region_k.push_back(o.n_in);
+                        auto wr = writer.find(key);
+                        if (wr != writer.end()) {
+                            Op& prod = p->ops_[wr->second];
+                            if (prod.kind == B2_OP_NORM) prod.norm.planes = 1;
+                            else prod.attn.planes = 1;
+                            region_of_op.push_back({wr->second, region});
+                        } else {
+                            Op xp;
+                            xp.kind = OP_XPLANES;
+                            xp.x = op.x;
+                            xp.n = o.n_in;
+                            region_of_op.push_back({p->ops_.size(), region});
+                            p->ops_.push_back(xp);
+                        }
+                        valid[key] = region;
+                    }
+                    region_of_op.push_back({p->ops_.size(), region});
+                }
+                if (o.y.buf == o.x.buf && !(o.y.off + o.n_out <= o.x.off || o.x.off + o.n_in <= o.y.off)) {
+                    err = "[b200qmm: decode_plan: a linear op writes over its own input]";
+                    return B2_ERR_ARG;
+                }
+                touch(o.y.buf);
+                break;
+            }
+            case B2_OP_QK_ROPE: {
+                if (o.kv >= g->n_kv || o.rope >= g->n_rope || g->kv_nkv[o.kv] != o.nkv || g->kv_hd[o.kv] != o.hd || o.hd > 256 || o.hd % 32 ||
+                    g->rope_halves[o.rope] != o.half_rot || 2 * o.half_rot > o.hd) {
+                    err = "[b200qmm: decode_plan: qk_rope does not match its KV cache or RoPE table]";
+                    return B2_ERR_ARG;
+                }
+                size_t q_stride = o.q_stride ? o.q_stride : o.hd;
+                size_t need = std::max({(size_t)(o.nh - 1) * q_stride + o.hd, (size_t)o.k_off + (size_t)o.nkv * o.hd,
+                                        o.v_from_k ? (size_t)0 : (size_t)o.v_off + (size_t)o.nkv * o.hd});
+                op.x = view(o.x, need);
+                op.y = view(o.y, (size_t)o.nh * o.hd);
+                op.kv = o.kv;
+                op.rope = DecRope{o.nh, o.nkv, o.hd, o.half_rot, (uint32_t)q_stride, o.k_off, o.v_off, o.interleaved, o.v_norm, o.v_from_k,
+                                  g->max_len, p->cs_stride_, cs_off[o.rope], o.eps};
+                if (o.p0) PLAN_CUDA(put_const(o.p0, o.hd, &op.p0), "cudaMemcpy(q norm)");
+                if (o.p1) PLAN_CUDA(put_const(o.p1, o.hd, &op.p1), "cudaMemcpy(k norm)");
+                touch(o.y.buf);
+                break;
+            }
+            case B2_OP_ATTEND: {
+                if (o.kv >= g->n_kv || g->kv_nkv[o.kv] != o.nkv || g->kv_hd[o.kv] != o.hd) {
+                    err = "[b200qmm: decode_plan: attend does not match its KV cache]";
+                    return B2_ERR_ARG;
+                }
+                if (!attend_supports(o.nh, o.nkv, o.hd)) {
+                    err = fmt("[b200qmm: decode_plan: attention with %u heads over %u KV heads of %u is outside the kernel (head dim 64 / 128, "
+                              "1 / 2 / 4 / 8 heads per KV head)]", o.nh, o.nkv, o.hd);
+                    return B2_DECLINED;
+                }
+                op.x = view(o.x, (size_t)o.nh * o.hd);
+                op.y = view(o.y, (size_t)o.nh * o.hd);
+                op.kv = o.kv;
+                op.attn = DecAttn{o.nh, o.nkv, o.hd, g->max_len, o.window, 0u, o.scale};
+                max_nh = std::max(max_nh, o.nh);
+                max_hd = std::max(max_hd, o.hd);
+                touch(o.y.buf);
+                writer[Key{o.y.buf, o.y.off, o.nh * o.hd}] = p->ops_.size();
+                break;
+            }
+            case B2_OP_GLU: {
+                op.x = view(o.x, o.n);
+                op.z = view(o.z, o.n);
+                op.y = view(o.y, o.n);
+                op.n = o.n;
+                op.gelu = o.gelu ? 1 : 0;
+                touch(o.y.buf);
+                break;
+            }
+            default:
+                err = fmt("[b200qmm: decode_plan: op kind %u is not taken by this backend]", o.kind);
+                return B2_DECLINED;
+        }
+        if (bad_view) {
+            err = fmt("[b200qmm: decode_plan: op %u reaches outside its buffer]", i);
+            return B2_ERR_ARG;
+        }
+        p->ops_.push_back(op);
+    }
+    p->n_input_ = g->n_input;
+    p->n_hidden_ = g->n_hidden;
+    p->n_logits_ = g->n_logits;
+    p->input_ = view(g->input, g->n_input);
+    p->hidden_ = view(g->hidden, g->n_hidden);
+    if (g->n_logits) p->logits_ = view(g->logits, g->n_logits);
+    if (bad_view) {
+        err = "[b200qmm: decode_plan: input / hidden / logits reach outside their buffers]";
+        return B2_ERR_ARG;
+    }
+
+    // ---- planes regions ---------------------------------------------------------------------------
+    size_t planes_total = 0;
+    std::vector<size_t> region_at(region_k.size());
+    for (size_t r = 0; r < region_k.size(); r++) {
+        region_at[r] = planes_total;
+        planes_total += align_up(xplanes_bytes(region_k[r]), 256);
+    }
+    PLAN_CUDA(cudaMalloc((void**)&p->planes_, std::max<size_t>(planes_total, 256)), "cudaMalloc(planes)");
+    for (auto& [oi, r] : region_of_op) p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
+
+    // ---- scratch ------------------------------------------------------------------------------------
+    if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, attend_part_floats(max_nh, max_hd) * sizeof(float)), "cudaMalloc(attention partials)");
+    size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1);
+    PLAN_CUDA(cudaMalloc((void**)&p->words_, n_words * 4), "cudaMalloc(step words)");
+    PLAN_CUDA(cudaMemset(p->words_, 0, n_words * 4), "cudaMemset(step words)");
+    p->sp_ = p->words_;
+    p->status_ = p->words_ + 4;
+    p->argmax_counter_ = p->words_ + 5;
+    p->att_counters_ = p->words_ + 8;
+    size_t table = (size_t)std::max<uint32_t>(p->cs_stride_, 1) * g->max_len;
+    PLAN_CUDA(cudaMalloc((void**)&p->rope_table_, table * sizeof(float)), "cudaMalloc(rope table)");
+    PLAN_CUDA(cudaMemset(p->rope_table_, 0, table * sizeof(float)), "cudaMemset(rope table)");
+    PLAN_CUDA(cudaMalloc((void**)&p->argmax_val_, 128 * sizeof(float)), "cudaMalloc(argmax)");
+    PLAN_CUDA(cudaMalloc((void**)&p->argmax_idx_, 128 * sizeof(int)), "cudaMalloc(argmax)");
+    PLAN_CUDA(cudaMalloc((void**)&p->token_, sizeof(int)), "cudaMalloc(token)");
+    PLAN_CUDA(cudaMalloc((void**)&p->out_tokens_, (size_t)g->max_len * sizeof(int)), "cudaMalloc(tokens)");
+    p->stage_floats_ = std::max<size_t>(max_row, 1) * 256;
+    PLAN_CUDA(cudaMalloc((void**)&p->stage_, 2 * p->stage_floats_ * sizeof(float)), "cudaMalloc(KV staging)");
+    PLAN_CUDA(cudaStreamCreateWithFlags(&p->cap_stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    PLAN_CUDA(cudaEventCreate(&p->ev0_), "cudaEventCreate");
+    PLAN_CUDA(cudaEventCreate(&p->ev1_), "cudaEventCreate");
+
+    // One eager pass (loads every kernel outside a capture, and surfaces launch errors with their op),
+    // then the step graph.
+    PLAN_CUDA(launch_set_step(p->sp_, 0, 0, 0, nullptr, 0, p->cap_stream_), "set_step");
+    int rc = p->run_ops(p->cap_stream_, err);
+    if (rc) return rc;
+    PLAN_CUDA(cudaStreamSynchronize(p->cap_stream_), "first pass");
+    rc = p->check_status(err);
+    if (rc) return rc;
+    rc = p->capture(p->cap_stream_, false, &p->step_exec_, err);
+    if (rc) return rc;
+    *out = p.release();
+    return B2_OK;
+}
+
+int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err) {
+    for (size_t i = 0; i < ops_.size(); i++) {
+        const Op& o = ops_[i];
+        cudaError_t e = cudaSuccess;
+        switch (o.kind) {
+            case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st); break;
+            case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st); break;
+            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st); break;
+            case B2_OP_QK_ROPE:
+                e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st);
+                break;
+            case B2_OP_ATTEND:
+                e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st);
+                break;
+            case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st); break;
+            default: e = cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) {
+            err = fmt("[b200qmm: plan: op %zu (kind %u): %s]", i, o.kind, cudaGetErrorString(e));
+            return B2_ERR_CUDA;
+        }
+    }
+    return B2_OK;
+}
+
+// Captures [embedding lookup,] ops [, argmax + advance] on `st` (not the legacy stream) into an executable graph.
+int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err) {
+    PLAN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    int rc = B2_OK;
+    cudaError_t e = cudaSuccess;
+    if (with_head) e = launch_dequantize(gen_embed_dev_, 0, 1, input_, st, token_);
+    if (e == cudaSuccess) rc = run_ops(st, err);
+    if (e == cudaSuccess && rc == B2_OK && with_head)
+        e = launch_argmax(logits_, n_logits_, argmax_val_, argmax_idx_, argmax_counter_, token_, out_tokens_, sp_, st);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e2 = cudaStreamEndCapture(st, &graph);
+    if (rc) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (e != cudaSuccess || e2 != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        err = fmt("[b200qmm: plan: capture: %s]", cudaGetErrorString(e != cudaSuccess ? e : e2));
+        return B2_ERR_CUDA;
+    }
+    e = cudaGraphInstantiate(out, graph, 0);
+    cudaGraphDestroy(graph);
+    PLAN_CUDA(e, "cudaGraphInstantiate");
+    return B2_OK;
+}
+
+int DecodePlanImpl::check_status(std::string& err) {
+    uint32_t s = 0;
+    PLAN_CUDA(cudaMemcpy(&s, status_, 4, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+    if (s) {
+        cudaMemset(status_, 0, 4);
+        cudaMemset(att_counters_, 0, 4 * kv_.size());  // a CTA that gave up never counted itself
+        err = "[b200qmm: plan: an attention kernel's wait on its copy ran into the time limit]";
+        return B2_ERR_TIMEOUT;
+    }
+    return B2_OK;
+}
+
+int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err) {
+    if (!x || (cs_stride_ && !rope_cs) || !hidden) {
+        err = "[b200qmm: plan step: x, rope_cs and hidden are required]";
+        return B2_ERR_ARG;
+    }
+    if (pos >= max_len_) {
+        err = fmt("[b200qmm: plan step: position %zu is past the %u the caches hold]", pos, max_len_);
+        return B2_ERR_ARG;
+    }
+    if (logits && !n_logits_) {
+        err = "[b200qmm: plan step: the graph has no logits]";
+        return B2_ERR_ARG;
+    }
+    PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos, (uint32_t)pos, 0, nullptr, 0, st), "set_step");
+    PLAN_CUDA(cudaMemcpyAsync(input_, x, n_input_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(x)");
+    if (cs_stride_) PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs, cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
+    PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
+    PLAN_CUDA(cudaMemcpyAsync(hidden, hidden_, n_hidden_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(hidden)");
+    if (logits) PLAN_CUDA(cudaMemcpyAsync(logits, logits_, n_logits_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(logits)");
+    PLAN_CUDA(cudaStreamSynchronize(st), "step");
+    return check_status(err);
+}
+
+int DecodePlanImpl::kv_write(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v, std::string& err) {
+    if (kv >= kv_.size() || !k || !v || pos0 + n > max_len_) {
+        err = "[b200qmm: plan kv_write: bad cache index, pointers or range]";
+        return B2_ERR_ARG;
+    }
+    const Kv& c = kv_[kv];
+    const size_t row = (size_t)c.nkv * c.hd, chunk = stage_floats_ / row;
+    for (size_t at = 0; at < n; at += chunk) {
+        size_t m = std::min(chunk, n - at);
+        PLAN_CUDA(cudaMemcpyAsync(stage_, k + at * row, m * row * 4, cudaMemcpyHostToDevice, st), "cudaMemcpy(K rows)");
+        PLAN_CUDA(cudaMemcpyAsync(stage_ + stage_floats_, v + at * row, m * row * 4, cudaMemcpyHostToDevice, st), "cudaMemcpy(V rows)");
+        PLAN_CUDA(launch_kv_rows(stage_, c.k, kv_f16_, true, c.nkv, c.hd, max_len_, (uint32_t)(pos0 + at), (uint32_t)m, st), "kv_rows");
+        PLAN_CUDA(launch_kv_rows(stage_ + stage_floats_, c.v, kv_f16_, true, c.nkv, c.hd, max_len_, (uint32_t)(pos0 + at), (uint32_t)m, st),
+                  "kv_rows");
+        PLAN_CUDA(cudaStreamSynchronize(st), "kv_write");  // the host rows may be pageable: the staging buffer is reused next round
+    }
+    return B2_OK;
+}
+
+int DecodePlanImpl::kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err) {
+    if (kv >= kv_.size() || !k || !v || pos0 + n > max_len_) {
+        err = "[b200qmm: plan kv_read: bad cache index, pointers or range]";
+        return B2_ERR_ARG;
+    }
+    const Kv& c = kv_[kv];
+    const size_t row = (size_t)c.nkv * c.hd, chunk = stage_floats_ / row;
+    for (size_t at = 0; at < n; at += chunk) {
+        size_t m = std::min(chunk, n - at);
+        PLAN_CUDA(launch_kv_rows(stage_, c.k, kv_f16_, false, c.nkv, c.hd, max_len_, (uint32_t)(pos0 + at), (uint32_t)m, st), "kv_rows");
+        PLAN_CUDA(launch_kv_rows(stage_ + stage_floats_, c.v, kv_f16_, false, c.nkv, c.hd, max_len_, (uint32_t)(pos0 + at), (uint32_t)m, st),
+                  "kv_rows");
+        PLAN_CUDA(cudaMemcpyAsync(k + at * row, stage_, m * row * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpy(K rows)");
+        PLAN_CUDA(cudaMemcpyAsync(v + at * row, stage_ + stage_floats_, m * row * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpy(V rows)");
+        PLAN_CUDA(cudaStreamSynchronize(st), "kv_read");
+    }
+    return B2_OK;
+}
+
+int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
+                             const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err) {
+    if (!n_logits_ || !logits_) {
+        err = "[b200qmm: plan generate: the graph has no logits]";
+        return B2_ERR_ARG;
+    }
+    if (!out_tokens || (cs_stride_ && !rope_cs_table) || n_tokens == 0 || pos0 + n_tokens > max_len_) {
+        err = fmt("[b200qmm: plan generate: %zu tokens from position %zu do not fit the %u positions of the caches, or a pointer is missing]",
+                  n_tokens, pos0, max_len_);
+        return B2_ERR_ARG;
+    }
+    if (embed.n_in != n_input_ || first_token < 0 || (size_t)first_token >= embed.n_out) {
+        err = "[b200qmm: plan generate: the embedding matrix does not match the graph's input, or the token is outside it]";
+        return B2_ERR_ARG;
+    }
+    if (!gen_exec_ || gen_embed_ != embed_handle || gen_embed_dev_.p0 != embed.p0) {
+        if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
+        gen_exec_ = nullptr;
+        gen_embed_ = embed_handle;
+        gen_embed_dev_ = embed;
+        // the two kernels the step graph does not have, once outside a capture
+        PLAN_CUDA(launch_set_step(sp_, 0, 0, 0, token_, first_token, cap_stream_), "set_step");
+        PLAN_CUDA(launch_dequantize(embed, 0, 1, input_, cap_stream_, token_), "embedding lookup");
+        PLAN_CUDA(launch_argmax(logits_, n_logits_, argmax_val_, argmax_idx_, argmax_counter_, token_, out_tokens_, sp_, cap_stream_), "argmax");
+        PLAN_CUDA(cudaStreamSynchronize(cap_stream_), "generate warm-up");
+        int rc = capture(cap_stream_, true, &gen_exec_, err);
+        if (rc) return rc;
+    }
+    PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos0, (uint32_t)pos0, 0, token_, first_token, st), "set_step");
+    if (cs_stride_)
+        PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs_table, n_tokens * cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
+    PLAN_CUDA(cudaEventRecord(ev0_, st), "cudaEventRecord");
+    for (size_t i = 0; i < n_tokens; i++) PLAN_CUDA(cudaGraphLaunch(gen_exec_, st), "cudaGraphLaunch");
+    PLAN_CUDA(cudaEventRecord(ev1_, st), "cudaEventRecord");
+    PLAN_CUDA(cudaMemcpyAsync(out_tokens, out_tokens_, n_tokens * sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpy(tokens)");
+    PLAN_CUDA(cudaStreamSynchronize(st), "generate");
+    if (elapsed_ms) PLAN_CUDA(cudaEventElapsedTime(elapsed_ms, ev0_, ev1_), "cudaEventElapsedTime");
+    return check_status(err);
+}
+
+}  // namespace b2

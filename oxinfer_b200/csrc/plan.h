@@ -1,0 +1,91 @@
+// The decode plan: a token's op list (b2_graph) resolved to device pointers, captured into a CUDA graph,
+// with the KV caches it owns. The role of CudaPlan in the reference (src/cuda_decode.rs:1233-1658).
+#pragma once
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../include/b200qmm.h"
+#include "kernels.h"
+
+namespace b2 {
+
+class DecodePlanImpl {
+  public:
+    // `resolve` maps a weight handle to its device description (nullptr: unknown handle).
+    // Returns B2_OK, B2_DECLINED or an error code; `err` gets the reason.
+    static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, DecodePlanImpl** out,
+                      std::string& err);
+    ~DecodePlanImpl();
+
+    int step(cudaStream_t st, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err);
+    int kv_write(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v, std::string& err);
+    int kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err);
+    int generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
+                 const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err);
+    uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
+    bool uses_weight(uint64_t h) const;
+
+  private:
+    struct Op {
+        uint32_t kind = 0;  // B2_OP_*, or OP_XPLANES
+        float *x = nullptr, *y = nullptr, *z = nullptr;
+        WeightDev w{}, w2{};
+        bool pair = false;
+        int mode = 0;
+        const float *p0 = nullptr, *p1 = nullptr;  // device copies of the op's weights
+        DecNorm norm{};
+        uint32_t rows = 1;
+        DecRope rope{};
+        DecAttn attn{};
+        uint32_t kv = 0;
+        uint32_t n = 0;
+        int gelu = 0;
+        XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
+    };
+    DecodePlanImpl() = default;
+    int run_ops(cudaStream_t st, std::string& err);
+    int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err);
+    int check_status(std::string& err);
+
+    std::vector<Op> ops_;
+    std::vector<uint64_t> weight_handles_;
+    int sm_count_ = 148;
+    // one allocation each
+    float* bufs_ = nullptr;
+    std::vector<float*> buf_ptr_;
+    std::vector<size_t> buf_len_;
+    uint8_t* planes_ = nullptr;
+    float* consts_ = nullptr;  // norm weights
+    struct Kv {
+        void *k = nullptr, *v = nullptr;
+        uint32_t nkv = 0, hd = 0;
+    };
+    std::vector<Kv> kv_;
+    uint32_t max_len_ = 0;
+    int kv_f16_ = 0;
+    float* part_ = nullptr;       // attention partials
+    uint32_t* words_ = nullptr;   // sp[4] | status | argmax counter | attention counters[...]
+    uint32_t* sp_ = nullptr;
+    uint32_t* status_ = nullptr;
+    uint32_t* argmax_counter_ = nullptr;
+    uint32_t* att_counters_ = nullptr;
+    float* rope_table_ = nullptr;  // [max_len][cs_stride]
+    uint32_t cs_stride_ = 0;
+    float* argmax_val_ = nullptr;
+    int* argmax_idx_ = nullptr;
+    int* token_ = nullptr;
+    int* out_tokens_ = nullptr;    // [max_len]
+    float* stage_ = nullptr;       // kv_write / kv_read staging on the device
+    size_t stage_floats_ = 0;
+    float *input_ = nullptr, *hidden_ = nullptr, *logits_ = nullptr;
+    uint32_t n_input_ = 0, n_hidden_ = 0, n_logits_ = 0;
+    cudaStream_t cap_stream_ = nullptr;
+    cudaGraphExec_t step_exec_ = nullptr;
+    cudaGraphExec_t gen_exec_ = nullptr;
+    uint64_t gen_embed_ = 0;
+    WeightDev gen_embed_dev_{};
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+};
+
+}  // namespace b2

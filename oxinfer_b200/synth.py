@@ -98,3 +98,68 @@ def f8_e4m3(n_out: int, n_in: int, seed: int, bs_rows: int = 128, bs_cols: int =
 
 def make(fmt: str, n_out: int, n_in: int, seed: int):
     return {"mlx4": mlx4, "q4_k": q4_k, "q6_k": q6_k, "q8_0": q8_0, "f8_e4m3": f8_e4m3}[fmt](n_out, n_in, seed)
+
+
+# ---- weights of a random-init model: zero mean, a chosen standard deviation --------------------------
+# The block generators above draw every byte uniformly, which exercises every code path of the decoders but
+# gives matrices with a large mean; a decoder stack needs y = W x to stay O(|x|). These keep the random
+# bytes and choose the block constants so that the decoded weights are zero-mean with std `sigma`.
+
+def q4_k_model(n_out: int, n_in: int, seed: int, sigma: float) -> Gguf:
+    """Sub-block scales and mins uniform in 0..15, quants uniform, dmin = 7.5 d: w = d (sc q - 7.5 m) has mean 0 and
+    std 63.5 d (from the moments of the three uniforms); d = sigma / 63.5 with a +-10 % spread per block."""
+    rng = np.random.default_rng(seed)
+    nb = n_out * (n_in // 256)
+    blk = rng.integers(0, 256, size=(nb, 144), dtype=np.uint16).astype(np.uint8)
+    blk[:, 4:12] &= 0x0F          # sc_j, m_j of sub-blocks 0..3 (bytes 4..11); bytes 12..15 hold sub-blocks 4..7 as nibbles
+    d = (sigma / 63.5) * (1.0 + 0.1 * rng.uniform(-1, 1, nb))
+    db, mb = _f16_bits(d), _f16_bits(7.5 * d)
+    blk[:, 0], blk[:, 1] = db & 0xFF, db >> 8
+    blk[:, 2], blk[:, 3] = mb & 0xFF, mb >> 8
+    return Gguf(FMT_Q4_K, np.ascontiguousarray(blk.reshape(-1)))
+
+
+def q6_k_model(n_out: int, n_in: int, seed: int, sigma: float) -> Gguf:
+    """Sub-block scales uniform in -8..7, quants uniform: w = d sc (q - 32) has mean ~0 and std about 4.6 * 18.5 d."""
+    rng = np.random.default_rng(seed)
+    nb = n_out * (n_in // 256)
+    blk = rng.integers(0, 256, size=(nb, 210), dtype=np.uint16).astype(np.uint8)
+    blk[:, 192:208] = rng.integers(-8, 8, size=(nb, 16)).astype(np.int8).view(np.uint8)
+    d = _f16_bits((sigma / (4.63 * 18.48)) * (1.0 + 0.1 * rng.uniform(-1, 1, nb)))
+    blk[:, 208], blk[:, 209] = d & 0xFF, d >> 8
+    return Gguf(FMT_Q6_K, np.ascontiguousarray(blk.reshape(-1)))
+
+
+def q8_0_model(n_out: int, n_in: int, seed: int, sigma: float) -> Gguf:
+    """Quants uniform in -128..127: w = d q has std 73.9 d."""
+    rng = np.random.default_rng(seed)
+    nb = n_out * (n_in // 32)
+    blk = rng.integers(0, 256, size=(nb, 34), dtype=np.uint16).astype(np.uint8)
+    d = _f16_bits((sigma / 73.9) * (1.0 + 0.1 * rng.uniform(-1, 1, nb)))
+    blk[:, 0], blk[:, 1] = d & 0xFF, d >> 8
+    return Gguf(FMT_Q8_0, np.ascontiguousarray(blk.reshape(-1)))
+
+
+def llama_weights(n_layers: int, h: int, nh: int, nkv: int, hd: int, inter: int, vocab: int, seed: int, same_layers: bool = False):
+    """Random-init weights of a Llama-style decoder in the formats of a GGUF Q4_K_M-like checkpoint: Q4_K body,
+    Q6_K head, Q8_0 embeddings, f32 norms. Returns (layers, final_norm, head, embed); each layer is a dict of
+    ``Gguf`` refs ``q k v o gate up down`` plus f32 ``ln_pre ln_post``. ``same_layers`` reuses layer 0's bytes for
+    every layer (each still uploads to its own device memory): generation time only, the work per token is unchanged."""
+    rng = np.random.default_rng(seed)
+    shapes = {"q": (nh * hd, h), "k": (nkv * hd, h), "v": (nkv * hd, h), "o": (h, nh * hd), "gate": (inter, h), "up": (inter, h),
+              "down": (h, inter)}
+    layers = []
+    for li in range(n_layers):
+        if same_layers and li > 0:
+            layers.append(dict(layers[0]))
+            continue
+        L = {}
+        for j, (name, (n_out, n_in)) in enumerate(shapes.items()):
+            L[name] = q4_k_model(n_out, n_in, seed + 100 * li + j + 1, 1.0 / np.sqrt(n_in))
+        L["ln_pre"] = (1.0 + 0.1 * rng.standard_normal(h)).astype(np.float32)
+        L["ln_post"] = (1.0 + 0.1 * rng.standard_normal(h)).astype(np.float32)
+        layers.append(L)
+    final_norm = (1.0 + 0.1 * rng.standard_normal(h)).astype(np.float32)
+    head = q6_k_model(vocab, h, seed + 7001, 1.0 / np.sqrt(h))
+    embed = q8_0_model(vocab, h, seed + 7002, 1.0)
+    return layers, final_norm, head, embed, shapes
