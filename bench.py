@@ -213,6 +213,78 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
     return out
 
 
+def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0):
+    """Config 2: greedy decode tok/s of a Llama-style decoder (hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab
+    128256; Q4_K body, Q6_K head, Q8_0 embeddings) after a `ctx`-token cache, batch 1, through the decode plan
+    (one CUDA graph launch per token, embedding lookup and argmax on the device). Random-init weights; every layer
+    has its own device memory (the same random bytes, generated once, are uploaded per layer)."""
+    import numpy as np
+
+    from oxinfer_b200 import decode as D
+    from oxinfer_b200 import synth
+
+    cfg = dict(n_layers=n_layers, h=4096, nh=32, nkv=8, hd=128, inter=14336, vocab=128256)
+    layers, final_norm, head, embed, shapes = synth.llama_weights(seed=0xB2000020, same_layers=True, **cfg)
+    dev_layers, wbytes = [], 0
+    for L in layers:
+        d = {name: be.upload(L[name], *shapes[name]) for name in shapes}
+        wbytes += sum(d[name].bytes() for name in shapes)
+        d["ln_pre"], d["ln_post"] = L["ln_pre"], L["ln_post"]
+        dev_layers.append(d)
+    dhead = be.upload(head, cfg["vocab"], cfg["h"])
+    dembed = be.upload(embed, cfg["vocab"], cfg["h"])
+    lc = D.LlamaConfig(eps=1e-5, rope_theta=500000.0, rope_interleaved=True, **cfg)
+    g = D.llama_graph(lc, dev_layers, final_norm, dhead)
+    max_len = ctx + n_tokens
+    plan = D.decode_plan(be, g, max_len, kv_f16=kv_f16)
+    if plan is None:
+        raise RuntimeError("decode plan declined: " + be.last_declined)
+    rng = np.random.default_rng(7)
+    row = cfg["nkv"] * cfg["hd"]
+    kv_rows = []
+    for li in range(n_layers):   # the prefilled cache: unit-variance keys and values
+        k = rng.standard_normal((ctx, row), dtype=np.float32)
+        v = rng.standard_normal((ctx, row), dtype=np.float32)
+        plan.kv_write(li, 0, k, v)
+        if cpu_tokens and li == 0:
+            kv_rows = [k, v]
+    inv_freq = D.rope_inv_freq(cfg["hd"], lc.rope_theta)
+    table = np.stack([D.rope_table(ctx + i, inv_freq) for i in range(n_tokens)])
+    plan.generate(dembed, 1, ctx, min(8, n_tokens), table[: min(8, n_tokens)])    # warm-up (captures the graph)
+    times = []
+    for _ in range(3):
+        toks, ms = plan.generate(dembed, 1, ctx, n_tokens, table)
+        times.append(ms)
+    ms = sorted(times)[1]
+    kv_el = 2 if kv_f16 else 4
+    kv_bytes = n_layers * 2 * (ctx + (n_tokens + 1) / 2) * row * kv_el
+    algo = wbytes + dhead.bytes() + cfg["h"] * 34 // 32 + kv_bytes
+    out = {"tok_s": n_tokens / (ms * 1e-3), "ms_per_token": ms / n_tokens, "tokens": n_tokens, "context": ctx, "layers": n_layers,
+           "kv_cache": "f16" if kv_f16 else "f32", "launches_per_token": plan.launches_per_step() + 2,
+           "bytes_per_token": int(algo), "gbs": algo / (ms / n_tokens * 1e-3) / 1e9,
+           "frac_of_hbm_peak": algo / (ms / n_tokens * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "distinct_tokens": int(len(set(toks.tolist()))), "timing": "CUDA events around the token loop, median of 3"}
+    if cpu_tokens:
+        # the reference's CPU decode path (oracle port) on the same model: a few tokens at the same context
+        from oracle import oracle as O
+
+        mats = {name: O.Matrix.gguf(O.Q4_K, layers[0][name].data, *shapes[name]) for name in shapes}
+        cl = [dict(mats, ln_pre=L["ln_pre"], ln_post=L["ln_post"]) for L in layers]
+        ocfg = O.LlamaCfg(n_layers, cfg["h"], cfg["nh"], cfg["nkv"], cfg["hd"], cfg["inter"], cfg["vocab"], 1, 1e-5, lc.scale)
+        cpu = O.Llama(ocfg, cl, final_norm, O.Matrix.gguf(O.Q6_K, head.data, cfg["vocab"], cfg["h"]), ctx + cpu_tokens)
+        for li in range(n_layers):
+            cpu.kc[li, :ctx], cpu.vc[li, :ctx] = kv_rows[0], kv_rows[1]
+        x = np.random.default_rng(1).standard_normal(cfg["h"]).astype(np.float32)
+        t0 = time.perf_counter()
+        for i in range(cpu_tokens):
+            cpu.step(ctx + i, x, table[i], exact=False)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": cpu_tokens / dt, "unit": "tok/s", "cores": O.cpu_threads(), "kind": "port",
+                               "sample": f"{cpu_tokens} tokens at context {ctx} (int8-activation decode kernels, f32 attention)"}
+    plan.close()
+    return out
+
+
 def run_b200(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -233,6 +305,9 @@ def run_b200(args, rank, world, local_rank):
 
     if args.section == "gemv":
         print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}), flush=True)
+        return
+    if args.section == "decode":
+        print(json.dumps({"extra": {"decode": decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16)}}), flush=True)
         return
     assert N_OUT % world == 0
     n_local = N_OUT // world
@@ -351,6 +426,10 @@ def run_b200(args, rank, world, local_rank):
                 line["extra"] = {"gemv": gemv_extras(be, torch, peaks, 40)}
             except Exception as e:  # the headline line must still print
                 line["extra"] = {"gemv_error": str(e)}
+            try:
+                line["extra"]["decode"] = decode_extras(be, peaks, cpu_tokens=2)
+            except Exception as e:
+                line["extra"]["decode_error"] = str(e)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -365,7 +444,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default=None, help="with --section gemv: only the cases whose name contains this text")
     ap.add_argument("--no-graph", action="store_true", help="with --section gemv: host-launched kernels instead of a CUDA graph (profiling)")
-    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv"],
+    ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")
+    ap.add_argument("--tokens", type=int, default=256, help="with --section decode: tokens to generate")
+    ap.add_argument("--kv-f16", action="store_true", help="with --section decode: f16 KV caches instead of the reference's f32")
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

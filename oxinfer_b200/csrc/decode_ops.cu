@@ -34,24 +34,60 @@ __device__ __forceinline__ float block_sum(float v, float* red) {  // red: 32 fl
 }
 
 // ---- RMSNorm ---------------------------------------------------------------------------------
-// One CTA per row. out (+)= (x * pre) * k * w with k = 1 / sqrt(mean((x pre)^2) + eps).
+// One CTA per row. out (+)= (x * pre) * k * w with k = 1 / sqrt(mean((x pre)^2) + eps). Rows of up to
+// 8 * blockDim values stay in registers between the two passes; longer rows are read twice.
+constexpr int NORM_PER_THREAD = 8;
 __global__ void __launch_bounds__(1024) norm_kernel(const float* __restrict__ x, float* __restrict__ out, const float* __restrict__ w, DecNorm p,
                                                     XPlanes xp) {
     __shared__ float red[32];
+    pdl_launch_dependents();
     const float* xr = x + (size_t)blockIdx.x * p.x_stride;
     float* o = out + (size_t)blockIdx.x * p.out_stride;
+    const bool in_regs = p.n <= NORM_PER_THREAD * blockDim.x;
+    float wv[NORM_PER_THREAD], v[NORM_PER_THREAD];
+    if (in_regs && w) {  // the weights do not depend on the kernel before this one
+#pragma unroll
+        for (int j = 0; j < NORM_PER_THREAD; j++) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            wv[j] = i < p.n ? w[i] : 0.0f;
+        }
+    }
+    pdl_wait();
     float s = 0.0f;
-    for (uint32_t i = threadIdx.x; i < p.n; i += blockDim.x) {
-        float v = xr[i] * p.pre;
-        s += v * v;
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < NORM_PER_THREAD; j++) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            v[j] = i < p.n ? xr[i] * p.pre : 0.0f;
+            s += v[j] * v[j];
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < p.n; i += blockDim.x) {
+            float t = xr[i] * p.pre;
+            s += t * t;
+        }
     }
     const float k = 1.0f / sqrtf(block_sum(s, red) / (float)p.n + p.eps);
-    for (uint32_t i = threadIdx.x; i < p.n; i += blockDim.x) {  // p.n % 32 == 0 when planes are asked for: whole warps stay
-        float v = xr[i] * p.pre * k;
-        if (w) v *= w[i];
-        if (p.add) v += o[i];
-        o[i] = v;
-        if (p.planes) xplanes_block(v, (int)(i >> 5), threadIdx.x & 31, (int)p.n, xp);
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < NORM_PER_THREAD; j++) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < p.n) {  // p.n % 32 == 0 when planes are asked for: whole warps stay together
+                float t = v[j] * k;
+                if (w) t *= wv[j];
+                if (p.add) t += o[i];
+                o[i] = t;
+                if (p.planes) xplanes_block(t, (int)(i >> 5), threadIdx.x & 31, (int)p.n, xp);
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < p.n; i += blockDim.x) {
+            float t = xr[i] * p.pre * k;
+            if (w) t *= w[i];
+            if (p.add) t += o[i];
+            o[i] = t;
+            if (p.planes) xplanes_block(t, (int)(i >> 5), threadIdx.x & 31, (int)p.n, xp);
+        }
     }
 }
 
@@ -63,6 +99,8 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const float* __restrict__ 
                                                       const uint32_t* __restrict__ sp, DecRope p) {
     __shared__ float buf[256];
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t h = blockIdx.x, i = threadIdx.x, hd = p.hd, pos = sp[0];
     const uint32_t kind = h < p.nh ? 0 : (h < p.nh + p.nkv ? 1 : 2);
     const uint32_t hh = kind == 0 ? h : (kind == 1 ? h - p.nh : h - p.nh - p.nkv);
@@ -104,6 +142,8 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const float* __restrict__ 
 // ---- act(g) * u ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) glu_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out, uint32_t n,
                                                   int gelu) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float a = g[i];
@@ -198,6 +238,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __rest
     float* alpha = lrun + G;
     int* flags = (int*)(alpha + G);  // [0] abort, [1] last
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, kvh = blockIdx.x, split = blockIdx.y;
     uint32_t len = sp[0] + 1;
     if (len > p.max_len) len = p.max_len;
@@ -211,10 +253,21 @@ __global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __rest
     const int h0 = kvh * G;
     const float NEG = -INFINITY;
 
+    const uint32_t t0 = split * per, t1 = min(tiles, t0 + per);
+    auto issue = [&](uint32_t t) {  // one thread: both copies of key tile t
+        const uint32_t j0 = lo + t * ATT_TILE, nv = min((uint32_t)ATT_TILE, len - j0);
+        const uint32_t bytes = nv * HD * (uint32_t)sizeof(T);
+        const size_t at = ((size_t)kvh * p.max_len + j0) * HD;
+        bar_expect_tx(&bars[0], bytes);
+        bulk_load(Ks, kc + at, bytes, &bars[0]);
+        bar_expect_tx(&bars[1], bytes);
+        bulk_load(Vs, vc + at, bytes, &bars[1]);
+    };
     if (tid == 0) {
         bar_init(&bars[0], 1);
         bar_init(&bars[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        issue(t0);  // the first tile is on its way while the queries are staged
         flags[0] = 0;
         flags[1] = 0;
     }
@@ -230,20 +283,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __rest
     for (int g = 0; g < G; g++) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int part_id = tid / COLS, c4 = tid % COLS;
     const int lane8 = tid & 7, slot = tid >> 3;
-    const uint32_t t0 = split * per, t1 = min(tiles, t0 + per);
     bool ok = true;
     uint32_t phase = 0;
     for (uint32_t t = t0; t < t1; t++) {
         const uint32_t j0 = lo + t * ATT_TILE, nv = min((uint32_t)ATT_TILE, len - j0);
         phase = (t - t0) & 1;
-        if (tid == 0) {
-            const uint32_t bytes = nv * HD * (uint32_t)sizeof(T);
-            const size_t at = ((size_t)kvh * p.max_len + j0) * HD;
-            bar_expect_tx(&bars[0], bytes);
-            bulk_load(Ks, kc + at, bytes, &bars[0]);
-            bar_expect_tx(&bars[1], bytes);
-            bulk_load(Vs, vc + at, bytes, &bars[1]);
-        }
+        if (tid == 0 && t > t0) issue(t);
         if (!bar_wait(&bars[0], phase)) flags[0] = 1;
         __syncthreads();
         if (flags[0]) {
@@ -408,6 +453,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int last;
+    pdl_launch_dependents();
+    pdl_wait();
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -512,24 +559,22 @@ cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uin
     return cudaGetLastError();
 }
 
-cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st) {
+cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st, bool pdl) {
     if (p.planes && (p.n % 32 || rows != 1)) return cudaErrorInvalidValue;
-    unsigned threads = p.n >= 1024 ? 1024 : ((p.n + 31) / 32) * 32;
-    norm_kernel<<<rows, threads, 0, st>>>(x, out, w, p, xp);
-    return cudaGetLastError();
+    unsigned threads = p.n >= 4096 ? 1024 : p.n >= 1024 ? 512 : ((p.n + 31) / 32) * 32;
+    return launch_k(norm_kernel, dim3(rows), dim3(threads), 0, st, pdl, x, out, w, p, xp);
 }
 
 template <typename T>
 static cudaError_t rope_t(const float* qkv, float* qo, void* kc, void* vc, const float* qn, const float* kn, const float* cs, const uint32_t* sp,
-                          const DecRope& p, cudaStream_t st) {
-    qk_rope_kernel<T><<<p.nh + 2 * p.nkv, p.hd, 0, st>>>(qkv, qo, (T*)kc, (T*)vc, qn, kn, cs, sp, p);
-    return cudaGetLastError();
+                          const DecRope& p, cudaStream_t st, bool pdl) {
+    return launch_k(qk_rope_kernel<T>, dim3(p.nh + 2 * p.nkv), dim3(p.hd), 0, st, pdl, qkv, qo, (T*)kc, (T*)vc, qn, kn, cs, sp, p);
 }
 
 cudaError_t launch_qk_rope(const float* qkv, float* qo, void* kc, void* vc, int kv_f16, const float* qn, const float* kn, const float* cs,
-                           const uint32_t* sp, const DecRope& p, cudaStream_t st) {
+                           const uint32_t* sp, const DecRope& p, cudaStream_t st, bool pdl) {
     if (p.hd > 256 || p.hd % 32 || 2 * p.half_rot > p.hd) return cudaErrorInvalidValue;
-    return kv_f16 ? rope_t<__half>(qkv, qo, kc, vc, qn, kn, cs, sp, p, st) : rope_t<float>(qkv, qo, kc, vc, qn, kn, cs, sp, p, st);
+    return kv_f16 ? rope_t<__half>(qkv, qo, kc, vc, qn, kn, cs, sp, p, st, pdl) : rope_t<float>(qkv, qo, kc, vc, qn, kn, cs, sp, p, st, pdl);
 }
 
 bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd) {
@@ -541,7 +586,7 @@ size_t attend_part_floats(uint32_t nh, uint32_t hd) { return (size_t)nh * ATT_MA
 
 template <int HD, int G, typename T>
 static cudaError_t attend_t(const float* q, const void* kc, const void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,
-                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st) {
+                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
     constexpr size_t smem = attend_smem<HD, G, T>();
     static bool set = false;  // per instantiation; the attribute is per function and device-wide values are equal
     if (!set) {
@@ -553,42 +598,40 @@ static cudaError_t attend_t(const float* q, const void* kc, const void* vc, floa
     if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
     if (splits == 0) splits = 1;
     dim3 grid(p.nkv, splits);
-    attend_kernel<HD, G, T><<<grid, ATT_THREADS, smem, st>>>(q, (const T*)kc, (const T*)vc, out, part, counters, sp, p, xp, status);
-    return cudaGetLastError();
+    return launch_k(attend_kernel<HD, G, T>, grid, dim3(ATT_THREADS), smem, st, pdl, q, (const T*)kc, (const T*)vc, out, part, counters, sp, p, xp,
+                    status);
 }
 
 template <int HD, typename T>
 static cudaError_t attend_g(uint32_t g, const float* q, const void* kc, const void* vc, float* out, float* part, uint32_t* counters,
-                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st) {
+                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
     switch (g) {
-        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st);
-        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st);
-        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st);
-        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st);
+        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_attend(const float* q, const void* kc, const void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
-                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st) {
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
     if (!attend_supports(p.nh, p.nkv, p.hd)) return cudaErrorInvalidValue;
     const uint32_t g = p.nh / p.nkv;
     if (p.hd == 64)
-        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st)
-                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st);
-    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st)
-                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st);
+        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl)
+                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl)
+                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
 }
 
-cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st) {
-    glu_kernel<<<(n + 255) / 256, 256, 0, st>>>(g, u, out, n, gelu);
-    return cudaGetLastError();
+cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st, bool pdl) {
+    return launch_k(glu_kernel, dim3((n + 255) / 256), dim3(256), 0, st, pdl, g, u, out, n, gelu);
 }
 
 cudaError_t launch_argmax(const float* logits, uint32_t n, float* pval, int* pidx, uint32_t* counter, int* token, int* out_tokens, uint32_t* sp,
-                          cudaStream_t st) {
-    argmax_kernel<<<ARGMAX_CTAS, 256, 0, st>>>(logits, n, pval, pidx, counter, token, out_tokens, sp);
-    return cudaGetLastError();
+                          cudaStream_t st, bool pdl) {
+    return launch_k(argmax_kernel, dim3(ARGMAX_CTAS), dim3(256), 0, st, pdl, logits, n, pval, pidx, counter, token, out_tokens, sp);
 }
 
 }  // namespace b2

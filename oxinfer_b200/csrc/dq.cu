@@ -3,6 +3,7 @@
 // never fuses `d1 * v - m1` (src/ggml.rs:769), `(q - 8) * d + m` (src/quant.rs:601) or
 // `d * sc * q` (src/ggml.rs:787).
 #include "kernels.h"
+#include "xplanes.cuh"
 
 namespace b2 {
 
@@ -12,6 +13,8 @@ namespace {
 template <int FMT>
 __global__ void __launch_bounds__(256) dq_kernel(WeightDev w, size_t r0, size_t nrows, float* __restrict__ out,
                                                  const int* __restrict__ row_dev) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t K = w.n_in;
     if (row_dev) {  // the row is named on the device (a token's embedding); out-of-range ids read row 0
         int t = *row_dev;
@@ -126,16 +129,16 @@ __global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, size_t nbloc
 
 }  // namespace
 
-cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev) {
+cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev, bool pdl) {
     if (nrows == 0) return cudaSuccess;
     size_t n = nrows * (w.n_in / 8);
     unsigned grid = (unsigned)((n + 255) / 256);
     switch (w.fmt) {
-        case B2_FMT_MLX4: dq_kernel<B2_FMT_MLX4><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
-        case B2_FMT_Q4_K: dq_kernel<B2_FMT_Q4_K><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
-        case B2_FMT_Q6_K: dq_kernel<B2_FMT_Q6_K><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
-        case B2_FMT_Q8_0: dq_kernel<B2_FMT_Q8_0><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
-        case B2_FMT_F8E4M3: dq_kernel<B2_FMT_F8E4M3><<<grid, 256, 0, st>>>(w, r0, nrows, out, row_dev); break;
+        case B2_FMT_MLX4: return launch_k(dq_kernel<B2_FMT_MLX4>, dim3(grid), dim3(256), 0, st, pdl, w, r0, nrows, out, row_dev);
+        case B2_FMT_Q4_K: return launch_k(dq_kernel<B2_FMT_Q4_K>, dim3(grid), dim3(256), 0, st, pdl, w, r0, nrows, out, row_dev);
+        case B2_FMT_Q6_K: return launch_k(dq_kernel<B2_FMT_Q6_K>, dim3(grid), dim3(256), 0, st, pdl, w, r0, nrows, out, row_dev);
+        case B2_FMT_Q8_0: return launch_k(dq_kernel<B2_FMT_Q8_0>, dim3(grid), dim3(256), 0, st, pdl, w, r0, nrows, out, row_dev);
+        case B2_FMT_F8E4M3: return launch_k(dq_kernel<B2_FMT_F8E4M3>, dim3(grid), dim3(256), 0, st, pdl, w, r0, nrows, out, row_dev);
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -38,6 +38,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---- activation planes ----------------------------------------------------------------------
 __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, XPlanes out) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     if (warp >= K / 32) return;
     xplanes_block(x[warp * 32 + lane], warp, lane, K, out);
 }
@@ -321,12 +323,33 @@ struct FmtF8 {
     }
 };
 
+// The kernel's order of events, chosen for back-to-back launches of a decode step:
+//   1. let the next kernel of the stream start launching (programmatic dependent launch),
+//   2. issue the loads of the warp's first weights, which depend on nothing the previous kernel wrote,
+//   3. wait for the previous kernel (it wrote the planes / the vector), stage them in shared memory,
+//   4. stream the rows.
 template <class F, bool PAIR, bool XF32>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
             const float* __restrict__ gate) {
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_launch_dependents();
     const int K = (int)w.n_in;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t n_out = w.n_out;
+    const int iters = (K + F::ITER_K - 1) / F::ITER_K;
+    constexpr int RW = PAIR ? 1 : 2;  // output rows per warp pass
+    const size_t r_first = ((size_t)blockIdx.x * GEMV_WARPS + warp) * RW, r_step = (size_t)gridDim.x * GEMV_WARPS * RW;
+    typename F::Regs na, nb;
+    auto fetch = [&](size_t r0, int it) {
+        if (F::active(K, it, lane)) {
+            F::load(w, r0, it, lane, na);
+            F::load(PAIR ? w2 : w, PAIR ? r0 : min(r0 + 1, n_out - 1), it, lane, nb);
+        }
+    };
+    if (r_first < n_out) fetch(r_first, 0);
+    pdl_wait();
+
     XS xs;
     xs.K = K;
     if constexpr (XF32) {
@@ -354,19 +377,12 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
         xs.xf = nullptr;
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t n_out = w.n_out;
-    const int iters = (K + F::ITER_K - 1) / F::ITER_K;
-    constexpr int RW = PAIR ? 1 : 2;  // output rows per warp pass
-    for (size_t r0 = ((size_t)blockIdx.x * GEMV_WARPS + warp) * RW; r0 < n_out; r0 += (size_t)gridDim.x * GEMV_WARPS * RW) {
-        const size_t rowA = r0, rowB = PAIR ? r0 : min(r0 + 1, n_out - 1);
+    for (size_t r0 = r_first; r0 < n_out; r0 += r_step) {
         float accA = 0.0f, accB = 0.0f;
         for (int it = 0; it < iters; it++) {
             if (!F::active(K, it, lane)) continue;
-            typename F::Regs ra, rb;
-            F::load(w, rowA, it, lane, ra);
-            F::load(PAIR ? w2 : w, rowB, it, lane, rb);
-            F::dot2(ra, rb, xs, it, lane, accA, accB);
+            if (it > 0 || r0 != r_first) fetch(r0, it);  // the first step's loads were issued before the wait
+            F::dot2(na, nb, xs, it, lane, accA, accB);
         }
         accA = warp_sum(accA);
         accB = warp_sum(accB);
@@ -393,7 +409,7 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
 
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                       int sm_count, cudaStream_t st) {
+                       int sm_count, cudaStream_t st, bool pdl) {
     size_t smem = XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in);
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, XF32> : gemv_kernel<F, false, XF32>;
@@ -408,8 +424,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    kern<<<(unsigned)grid, GEMV_THREADS, smem, st>>>(w, pair ? *up : w, x, xp, y, mode, gate);
-    return cudaGetLastError();
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate);
 }
 
 }  // namespace
@@ -425,20 +440,19 @@ bool gemv_supports(const WeightDev& w) {
     }
 }
 
-cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st) {
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl) {
     unsigned warps = (unsigned)(K / 32);
-    xplanes_kernel<<<(warps + 7) / 8, 256, 0, st>>>(x, (int)K, out);
-    return cudaGetLastError();
+    return launch_k(xplanes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, (int)K, out);
 }
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st) {
+                        int sm_count, cudaStream_t st, bool pdl) {
     switch (w.fmt) {
-        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st);
-        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st);
-        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st);
-        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st);
-        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st);
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
+        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
         default: return cudaErrorInvalidValue;
     }
 }

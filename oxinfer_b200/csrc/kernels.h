@@ -4,10 +4,29 @@
 
 namespace b2 {
 
+// Launch with or without the programmatic-dependent-launch attribute. With it the kernel may begin while the
+// kernel ahead of it in the stream is still running; every kernel launched this way calls pdl_wait() (xplanes.cuh)
+// before it reads what that kernel wrote or writes anything.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- dq.cu: bit-exact dequantization --------------------------------------------------------
 // Rows [r0, r0 + nrows) of `w` to f32, row-major [nrows][n_in]. With `row_dev`, r0 is read from that
 // device word when the kernel runs (a token's embedding row inside a captured graph).
-cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev = nullptr);
+cudaError_t launch_dequantize(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev = nullptr,
+                              bool pdl = false);
 // Raw GGUF Q6_K / Q8_0 rows (device) -> the split planes described in formats.cuh.
 cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uint8_t* ql, uint8_t* qh, int8_t* sc, uint16_t* d,
                               cudaStream_t st);
@@ -35,11 +54,11 @@ inline XPlanes xplanes_at(void* base, size_t K) {
     p.v16 = (int32_t*)(p.xsum + K / 32);
     return p;
 }
-cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st);
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st);
+                        int sm_count, cudaStream_t st, bool pdl = false);
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 
@@ -90,22 +109,22 @@ struct DecAttn {
     uint32_t nh, nkv, hd, max_len, window, planes;
     float scale;
 };
-cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st);
+cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st, bool pdl = false);
 // KV caches are [nkv][max_len][hd], f32 or (kv_f16) f16.
 cudaError_t launch_qk_rope(const float* qkv, float* qo, void* kc, void* vc, int kv_f16, const float* qn, const float* kn, const float* cs_table,
-                           const uint32_t* sp, const DecRope& p, cudaStream_t st);
+                           const uint32_t* sp, const DecRope& p, cudaStream_t st, bool pdl = false);
 bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
 size_t attend_part_floats(uint32_t nh, uint32_t hd);  // scratch for the per-split partials
 // counters: nkv zeroed words (left zero by every launch); status: set to 1 if a bounded wait gave up.
 cudaError_t launch_attend(const float* q, const void* kc, const void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
-                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st);
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl = false);
 // Host-order rows [n][nkv][hd] f32 <-> cache rows pos0 .. pos0 + n - 1.
 cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, uint32_t nkv, uint32_t hd, uint32_t max_len, uint32_t pos0,
                            uint32_t n, cudaStream_t st);
 cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uint32_t count, int* token, int tok, cudaStream_t st);
-cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st);
+cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st, bool pdl = false);
 // pval / pidx: 128 words each; counter: one zeroed word.
 cudaError_t launch_argmax(const float* logits, uint32_t n, float* pval, int* pidx, uint32_t* counter, int* token, int* out_tokens, uint32_t* sp,
-                          cudaStream_t st);
+                          cudaStream_t st, bool pdl = false);
 
 }  // namespace b2

@@ -6,6 +6,7 @@
 #include "plan.h"
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <algorithm>
 #include <map>
@@ -38,9 +39,55 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
         }                                                                                      \
     } while (0)
 
+// Bytes of one row in each of the (up to four) device planes of a format; 0 = plane unused.
+void row_bytes(const WeightDev& w, size_t (&rb)[4]) {
+    const size_t K = w.n_in;
+    rb[0] = rb[1] = rb[2] = rb[3] = 0;
+    switch (w.fmt) {
+        case B2_FMT_MLX4:
+        case B2_FMT_Q4_K: rb[0] = (K / 256) * 144; break;
+        case B2_FMT_Q6_K:
+            rb[0] = K / 2;
+            rb[1] = K / 4;
+            rb[2] = K / 16;
+            rb[3] = (K / 256) * 2;
+            break;
+        case B2_FMT_Q8_0:
+            rb[0] = K;
+            rb[1] = (K / 32) * 2;
+            break;
+    }
+}
+
+// One matrix whose rows are the rows of `parts` in order (same format and n_in): device copies, owned by the plan.
+cudaError_t fuse_rows(const std::vector<const WeightDev*>& parts, WeightDev* out, std::vector<void*>& owned) {
+    *out = *parts[0];
+    size_t rb[4], total = 0;
+    row_bytes(*parts[0], rb);
+    for (const WeightDev* w : parts) total += w->n_out;
+    out->n_out = total;
+    const uint8_t* WeightDev::*planes[4] = {&WeightDev::p0, &WeightDev::p1, &WeightDev::p2, &WeightDev::p3};
+    for (int pl = 0; pl < 4; pl++) {
+        if (!rb[pl]) continue;
+        uint8_t* d = nullptr;
+        cudaError_t e = cudaMalloc((void**)&d, total * rb[pl]);
+        if (e != cudaSuccess) return e;
+        owned.push_back(d);
+        size_t at = 0;
+        for (const WeightDev* w : parts) {
+            e = cudaMemcpy(d + at, w->*planes[pl], w->n_out * rb[pl], cudaMemcpyDeviceToDevice);
+            if (e != cudaSuccess) return e;
+            at += w->n_out * rb[pl];
+        }
+        out->*planes[pl] = d;
+    }
+    return cudaSuccess;
+}
+
 }  // namespace
 
 DecodePlanImpl::~DecodePlanImpl() {
+    for (void* p : fused_) cudaFree(p);
     if (step_exec_) cudaGraphExecDestroy(step_exec_);
     if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
     if (ev0_) cudaEventDestroy(ev0_);
@@ -73,6 +120,8 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     }
     std::unique_ptr<DecodePlanImpl> p(new DecodePlanImpl());
     p->sm_count_ = sm_count;
+    if (const char* e = getenv("B2_PLAN_PDL")) p->pdl_ = atoi(e) != 0;
+    if (const char* e = getenv("B2_PLAN_FUSE")) p->fuse_ = atoi(e) != 0;
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -209,6 +258,28 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                 op.x = view(o.x, o.n_in);
                 op.y = view(o.y, o.n_out);
                 if (o.mode == B2_MODE_ADD_GATED) op.z = view(o.z, 1);
+                // Products of the same vector that store into consecutive ranges (q, k, v) run as one launch over
+                // a row-wise concatenation of their matrices (a device copy the plan owns).
+                if (p->fuse_ && o.mode == B2_MODE_STORE && w->fmt != B2_FMT_F8E4M3) {
+                    std::vector<const WeightDev*> parts{w};
+                    uint32_t end = o.y.off + o.n_out, j = i + 1;
+                    for (; j < g->n_ops; j++) {
+                        const b2_op& n = g->ops[j];
+                        if (n.kind != B2_OP_LINEAR || n.mode != B2_MODE_STORE || n.x.buf != o.x.buf || n.x.off != o.x.off || n.n_in != o.n_in ||
+                            n.y.buf != o.y.buf || n.y.off != end || n.y.buf == n.x.buf)
+                            break;
+                        const WeightDev* nw = resolve(n.w);
+                        if (!nw || nw->fmt != w->fmt || nw->n_in != w->n_in || nw->n_out != n.n_out || nw->group != w->group) break;
+                        parts.push_back(nw);
+                        p->weight_handles_.push_back(n.w);
+                        end += n.n_out;
+                    }
+                    if (parts.size() > 1) {
+                        PLAN_CUDA(fuse_rows(parts, &op.w, p->fused_), "fusing matrices of one vector");
+                        op.y = view(o.y, end - o.y.off);
+                        i = j - 1;  // the fused ops are done
+                    }
+                }
                 if (w->fmt != B2_FMT_F8E4M3) {
                     Key key{o.x.buf, o.x.off, o.n_in};
                     size_t region;
@@ -347,7 +418,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     // One eager pass (loads every kernel outside a capture, and surfaces launch errors with their op),
     // then the step graph.
     PLAN_CUDA(launch_set_step(p->sp_, 0, 0, 0, nullptr, 0, p->cap_stream_), "set_step");
-    int rc = p->run_ops(p->cap_stream_, err);
+    int rc = p->run_ops(p->cap_stream_, err, false, false);
     if (rc) return rc;
     PLAN_CUDA(cudaStreamSynchronize(p->cap_stream_), "first pass");
     rc = p->check_status(err);
@@ -358,21 +429,24 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     return B2_OK;
 }
 
-int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err) {
+// `chained`: every launch but the first (`first_chained`: the first too) carries the programmatic-dependent-launch
+// attribute, so each kernel starts (and fetches its first weights) while the one before it drains.
+int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained) {
     for (size_t i = 0; i < ops_.size(); i++) {
         const Op& o = ops_[i];
+        const bool pdl = chained && (i > 0 || first_chained);
         cudaError_t e = cudaSuccess;
         switch (o.kind) {
-            case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st); break;
-            case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st); break;
-            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st); break;
+            case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st, pdl); break;
+            case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st, pdl); break;
+            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl); break;
             case B2_OP_QK_ROPE:
-                e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st);
+                e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st, pdl);
                 break;
             case B2_OP_ATTEND:
-                e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st);
+                e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st, pdl);
                 break;
-            case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st); break;
+            case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st, pdl); break;
             default: e = cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) {
@@ -389,9 +463,9 @@ int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* ou
     int rc = B2_OK;
     cudaError_t e = cudaSuccess;
     if (with_head) e = launch_dequantize(gen_embed_dev_, 0, 1, input_, st, token_);
-    if (e == cudaSuccess) rc = run_ops(st, err);
+    if (e == cudaSuccess) rc = run_ops(st, err, pdl_, with_head);
     if (e == cudaSuccess && rc == B2_OK && with_head)
-        e = launch_argmax(logits_, n_logits_, argmax_val_, argmax_idx_, argmax_counter_, token_, out_tokens_, sp_, st);
+        e = launch_argmax(logits_, n_logits_, argmax_val_, argmax_idx_, argmax_counter_, token_, out_tokens_, sp_, st, pdl_);
     cudaGraph_t graph = nullptr;
     cudaError_t e2 = cudaStreamEndCapture(st, &graph);
     if (rc) {

@@ -44,13 +44,16 @@ class DecodePlanImpl {
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
     };
     DecodePlanImpl() = default;
-    int run_ops(cudaStream_t st, std::string& err);
+    int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
     int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err);
     int check_status(std::string& err);
 
     std::vector<Op> ops_;
     std::vector<uint64_t> weight_handles_;
     int sm_count_ = 148;
+    bool pdl_ = true;  // programmatic dependent launch between the kernels of a step (B2_PLAN_PDL=0 switches it off)
+    bool fuse_ = true;  // q / k / v style products of one vector as one launch over concatenated rows (B2_PLAN_FUSE=0: off)
+    std::vector<void*> fused_;  // device copies made for that
     // one allocation each
     float* bufs_ = nullptr;
     std::vector<float*> buf_ptr_;

@@ -6,6 +6,12 @@
 
 namespace b2 {
 
+// Programmatic dependent launch: a kernel launched with the attribute may start before the kernel ahead of it in
+// the stream has finished; it must not touch anything that kernel writes until pdl_wait() returns. Both are
+// no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 constexpr float XQ_MAX = 1040000.0f;  // |q0 + 128 q1 + 16384 q2| <= 63 + 128*63 + 16384*63 = 1040319
 
 // All 32 lanes of the warp must call this with the block's values in lane order.
