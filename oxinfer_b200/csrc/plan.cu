@@ -97,7 +97,7 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.k) cudaFree(k.k);
         if (k.v) cudaFree(k.v);
     }
-    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
+    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -405,8 +405,9 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     size_t table = (size_t)std::max<uint32_t>(p->cs_stride_, 1) * g->max_len;
     PLAN_CUDA(cudaMalloc((void**)&p->rope_table_, table * sizeof(float)), "cudaMalloc(rope table)");
     PLAN_CUDA(cudaMemset(p->rope_table_, 0, table * sizeof(float)), "cudaMemset(rope table)");
-    PLAN_CUDA(cudaMalloc((void**)&p->argmax_val_, 128 * sizeof(float)), "cudaMalloc(argmax)");
-    PLAN_CUDA(cudaMalloc((void**)&p->argmax_idx_, 128 * sizeof(int)), "cudaMalloc(argmax)");
+    const size_t n_partials = std::max(128, sm_count);  // one per CTA of the argmax kernel / of the token kernel
+    PLAN_CUDA(cudaMalloc((void**)&p->argmax_val_, n_partials * sizeof(float)), "cudaMalloc(argmax)");
+    PLAN_CUDA(cudaMalloc((void**)&p->argmax_idx_, n_partials * sizeof(int)), "cudaMalloc(argmax)");
     PLAN_CUDA(cudaMalloc((void**)&p->token_, sizeof(int)), "cudaMalloc(token)");
     PLAN_CUDA(cudaMalloc((void**)&p->out_tokens_, (size_t)g->max_len * sizeof(int)), "cudaMalloc(tokens)");
     p->stage_floats_ = std::max<size_t>(max_row, 1) * 256;
@@ -425,6 +426,24 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     if (rc) return rc;
     rc = p->capture(p->cap_stream_, false, &p->step_exec_, err);
     if (rc) return rc;
+    const char* tk = getenv("B2_PLAN_TOKEN_KERNEL");
+    if (!tk || atoi(tk) != 0) {
+        p->build_program();
+        if (p->tk_ok_) {
+            PLAN_CUDA(cudaMalloc((void**)&p->prog_dev_, p->prog_.size() * sizeof(TokOp)), "cudaMalloc(program)");
+            PLAN_CUDA(cudaMemcpy(p->prog_dev_, p->prog_.data(), p->prog_.size() * sizeof(TokOp), cudaMemcpyHostToDevice), "cudaMemcpy(program)");
+            PLAN_CUDA(cudaMalloc((void**)&p->tk_ctl_, 64), "cudaMalloc(token kernel words)");
+            // one token through the kernel now: a launch that cannot be placed (shared memory, residency) shows here, and the plan
+            // then keeps to the graph
+            PLAN_CUDA(launch_set_step(p->sp_, 0, 0, 0, nullptr, 0, p->cap_stream_), "set_step");
+            std::string e2;
+            if (p->run_token_kernel(p->cap_stream_, false, 0, nullptr, 0, 0, 1, e2) != B2_OK || cudaStreamSynchronize(p->cap_stream_) != cudaSuccess ||
+                p->check_status(e2) != B2_OK) {
+                cudaGetLastError();
+                p->tk_ok_ = false;
+            }
+        }
+    }
     *out = p.release();
     return B2_OK;
 }
@@ -486,6 +505,15 @@ int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* ou
 int DecodePlanImpl::check_status(std::string& err) {
     uint32_t s = 0;
     PLAN_CUDA(cudaMemcpy(&s, status_, 4, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+    uint32_t tks[3] = {0, 0, 0};
+    if (tk_ctl_) PLAN_CUDA(cudaMemcpy(tks, tk_ctl_, 12, cudaMemcpyDeviceToHost), "cudaMemcpy(token kernel words)");
+    if (tks[2]) {
+        cudaMemset(att_counters_, 0, 4 * (kv_.empty() ? 1 : kv_.size()));
+        err = tks[2] == 2 ? "[b200qmm: plan: a grid barrier of the token kernel ran into its time limit]"
+                          : "[b200qmm: plan: an attention wait of the token kernel ran into its time limit]";
+        cudaMemset(tk_ctl_, 0, 12);
+        return B2_ERR_TIMEOUT;
+    }
     if (s) {
         cudaMemset(status_, 0, 4);
         cudaMemset(att_counters_, 0, 4 * kv_.size());  // a CTA that gave up never counted itself
@@ -511,7 +539,12 @@ int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const floa
     PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos, (uint32_t)pos, 0, nullptr, 0, st), "set_step");
     PLAN_CUDA(cudaMemcpyAsync(input_, x, n_input_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(x)");
     if (cs_stride_) PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs, cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
-    PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
+    if (tk_ok_) {
+        int rc = run_token_kernel(st, false, 0, nullptr, 0, pos, 1, err);
+        if (rc) return rc;
+    } else {
+        PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
+    }
     PLAN_CUDA(cudaMemcpyAsync(hidden, hidden_, n_hidden_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(hidden)");
     if (logits) PLAN_CUDA(cudaMemcpyAsync(logits, logits_, n_logits_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(logits)");
     PLAN_CUDA(cudaStreamSynchronize(st), "step");
@@ -571,6 +604,19 @@ int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const Weigh
         err = "[b200qmm: plan generate: the embedding matrix does not match the graph's input, or the token is outside it]";
         return B2_ERR_ARG;
     }
+    if (tk_ok_) {
+        gen_embed_ = embed_handle;
+        if (cs_stride_)
+            PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs_table, n_tokens * cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
+        PLAN_CUDA(cudaEventRecord(ev0_, st), "cudaEventRecord");
+        int rc = run_token_kernel(st, true, embed_handle, &embed, first_token, pos0, n_tokens, err);
+        if (rc) return rc;
+        PLAN_CUDA(cudaEventRecord(ev1_, st), "cudaEventRecord");
+        PLAN_CUDA(cudaMemcpyAsync(out_tokens, out_tokens_, n_tokens * sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpy(tokens)");
+        PLAN_CUDA(cudaStreamSynchronize(st), "generate");
+        if (elapsed_ms) PLAN_CUDA(cudaEventElapsedTime(elapsed_ms, ev0_, ev1_), "cudaEventElapsedTime");
+        return check_status(err);
+    }
     if (!gen_exec_ || gen_embed_ != embed_handle || gen_embed_dev_.p0 != embed.p0) {
         if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
         gen_exec_ = nullptr;
@@ -594,6 +640,167 @@ int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const Weigh
     PLAN_CUDA(cudaStreamSynchronize(st), "generate");
     if (elapsed_ms) PLAN_CUDA(cudaEventElapsedTime(elapsed_ms, ev0_, ev1_), "cudaEventElapsedTime");
     return check_status(err);
+}
+
+
+// ---- the persistent token kernel -----------------------------------------------------------------------------
+// The program: ops_ in order, a planes-staging step in front of every product whose vector is not the one already in
+// shared memory, and a grid barrier wherever an op touches memory that an op since the last barrier wrote (or writes
+// memory that one read).
+void DecodePlanImpl::build_program() {
+    struct Range {
+        const char *b, *e;
+    };
+    auto rng = [](const void* p, size_t bytes) { return Range{(const char*)p, (const char*)p + bytes}; };
+    auto hits = [](const Range& r, const std::vector<Range>& v) {
+        for (const Range& o : v)
+            if (r.b < o.e && o.b < r.e) return true;
+        return false;
+    };
+    std::vector<Range> W, R;
+    prog_.clear();
+    tk_barriers_ = 0;
+    const float* staged_ptr = nullptr;
+    size_t staged_n = 0, max_k = 0, att_smem = 0;
+    auto emit = [&](const TokOp& op, const std::vector<Range>& reads, const std::vector<Range>& writes) {
+        bool barrier = false;
+        for (const Range& r : reads) barrier = barrier || hits(r, W);
+        for (const Range& w : writes) barrier = barrier || hits(w, W) || hits(w, R);
+        if (barrier) {
+            TokOp b{};
+            b.kind = TK_BARRIER;
+            prog_.push_back(b);
+            tk_barriers_++;
+            W.clear();
+            R.clear();
+        }
+        prog_.push_back(op);
+        R.insert(R.end(), reads.begin(), reads.end());
+        W.insert(W.end(), writes.begin(), writes.end());
+        if (staged_ptr)
+            for (const Range& w : writes)
+                if (hits(w, {rng(staged_ptr, staged_n * 4)})) staged_ptr = nullptr;
+    };
+    const size_t esz = kv_f16_ ? 2 : 4;
+    for (const Op& o : ops_) {
+        TokOp t{};
+        switch (o.kind) {
+            case OP_XPLANES: break;  // the staging step below replaces it
+            case B2_OP_NORM: {
+                if (o.rows != 1 || o.norm.n % 32 || o.norm.n > TOKEN_KERNEL_MAX_NORM || o.norm.add) return;
+                t.kind = TK_NORM_STAGE;
+                t.x = o.x;
+                t.y = o.y;
+                t.p0 = o.p0;
+                t.norm = o.norm;
+                emit(t, {rng(o.x, o.norm.n * 4)}, {rng(o.y, o.norm.n * 4)});
+                staged_ptr = o.y;
+                staged_n = o.norm.n;
+                max_k = std::max<size_t>(max_k, o.norm.n);
+                break;
+            }
+            case B2_OP_LINEAR: {
+                if (o.w.fmt == B2_FMT_F8E4M3) return;
+                if (staged_ptr != o.x || staged_n != o.w.n_in) {
+                    TokOp s{};
+                    s.kind = TK_STAGE;
+                    s.x = o.x;
+                    s.n = (uint32_t)o.w.n_in;
+                    emit(s, {rng(o.x, o.w.n_in * 4)}, {});
+                    staged_ptr = o.x;
+                    staged_n = o.w.n_in;
+                }
+                max_k = std::max(max_k, o.w.n_in);
+                t.kind = TK_GEMV;
+                t.mode = (uint32_t)o.mode;
+                t.pair = o.pair ? 1 : 0;
+                t.y = o.y;
+                t.z = o.z;
+                t.w = o.w;
+                t.w2 = o.w2;
+                std::vector<Range> reads;
+                if (o.mode == B2_MODE_ADD || o.mode == B2_MODE_ADD_GATED) reads.push_back(rng(o.y, o.w.n_out * 4));
+                if (o.z) reads.push_back(rng(o.z, 4));
+                emit(t, reads, {rng(o.y, o.w.n_out * 4)});
+                break;
+            }
+            case B2_OP_QK_ROPE: {
+                t.kind = TK_ROPE;
+                t.x = o.x;
+                t.y = o.y;
+                t.p0 = o.p0;
+                t.p1 = o.p1;
+                t.kc = kv_[o.kv].k;
+                t.vc = kv_[o.kv].v;
+                t.kv_f16 = (uint32_t)kv_f16_;
+                t.rope = o.rope;
+                const size_t cache = (size_t)o.rope.nkv * max_len_ * o.rope.hd * esz;
+                const size_t qkv_n = std::max({(size_t)(o.rope.nh - 1) * o.rope.q_stride + o.rope.hd, (size_t)o.rope.k_off + (size_t)o.rope.nkv * o.rope.hd,
+                                               (size_t)o.rope.v_off + (size_t)o.rope.nkv * o.rope.hd});
+                emit(t, {rng(o.x, qkv_n * 4)}, {rng(o.y, (size_t)o.rope.nh * o.rope.hd * 4), rng(t.kc, cache), rng(t.vc, cache)});
+                break;
+            }
+            case B2_OP_ATTEND: {
+                if (!token_kernel_attend_ok(o.attn.nh, o.attn.nkv, o.attn.hd)) return;
+                t.kind = TK_ATTEND;
+                t.x = o.x;
+                t.y = o.y;
+                t.kc = kv_[o.kv].k;
+                t.vc = kv_[o.kv].v;
+                t.kv_f16 = (uint32_t)kv_f16_;
+                t.attn = o.attn;
+                t.attn.planes = 0;
+                const size_t cache = (size_t)o.attn.nkv * max_len_ * o.attn.hd * esz, qn = (size_t)o.attn.nh * o.attn.hd * 4;
+                emit(t, {rng(o.x, qn), rng(t.kc, cache), rng(t.vc, cache)},
+                     {rng(o.y, qn), rng(part_, attend_part_floats(o.attn.nh, o.attn.hd) * 4), rng(att_counters_, 4 * o.attn.nkv)});
+                staged_ptr = nullptr;  // the attention tiles use the planes' shared memory
+                att_smem = std::max(att_smem, token_kernel_smem(0, o.attn.hd, o.attn.nh / o.attn.nkv, kv_f16_));
+                break;
+            }
+            case B2_OP_GLU: {
+                t.kind = TK_GLU;
+                t.x = o.x;
+                t.z = o.z;
+                t.y = o.y;
+                t.n = o.n;
+                t.gelu = (uint32_t)o.gelu;
+                emit(t, {rng(o.x, o.n * 4), rng(o.z, o.n * 4)}, {rng(o.y, o.n * 4)});
+                break;
+            }
+            default: return;
+        }
+    }
+    tk_smem_ = std::max(att_smem, token_kernel_smem(max_k, 0, 1, 0));
+    if (tk_smem_ > 220 * 1024) return;
+    tk_ok_ = true;
+}
+
+int DecodePlanImpl::run_token_kernel(cudaStream_t st, bool with_head, uint64_t, const WeightDev* embed, int32_t first_token, size_t pos0,
+                                     size_t n_tokens, std::string& err) {
+    TokenArgs a{};
+    a.prog = prog_dev_;
+    a.n_ops = (uint32_t)prog_.size();
+    a.n_tokens = (uint32_t)n_tokens;
+    a.pos0 = (uint32_t)pos0;
+    a.table_pos0 = (uint32_t)pos0;
+    a.with_head = with_head ? 1 : 0;
+    a.n_logits = n_logits_;
+    a.max_splits = std::min<uint32_t>(64, (max_len_ + 63) / 64);
+    a.first_token = (uint32_t)first_token;
+    a.cs_table = rope_table_;
+    a.input = input_;
+    a.logits = logits_;
+    a.part = part_;
+    a.att_counters = att_counters_;
+    a.ctl = tk_ctl_;
+    a.argmax_val = argmax_val_;
+    a.argmax_idx = argmax_idx_;
+    a.token = token_;
+    a.out_tokens = out_tokens_;
+    if (embed) a.embed = *embed;
+    PLAN_CUDA(cudaMemsetAsync(tk_ctl_, 0, 64, st), "cudaMemset(token kernel words)");
+    PLAN_CUDA(launch_token_kernel(a, tk_smem_, sm_count_, st), "token kernel");
+    return B2_OK;
 }
 
 }  // namespace b2

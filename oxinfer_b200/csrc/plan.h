@@ -7,6 +7,7 @@
 
 #include "../../include/b200qmm.h"
 #include "kernels.h"
+#include "token_kernel.h"
 
 namespace b2 {
 
@@ -23,7 +24,8 @@ class DecodePlanImpl {
     int kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err);
     int generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
                  const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err);
-    uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
+    uint64_t launches_per_step() const { return tk_ok_ ? 1 : (uint64_t)ops_.size(); }
+    bool token_kernel() const { return tk_ok_; }
     bool uses_weight(uint64_t h) const;
 
   private:
@@ -47,6 +49,9 @@ class DecodePlanImpl {
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
     int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err);
     int check_status(std::string& err);
+    void build_program();  // the token kernel's program from ops_, if every op is one it takes
+    int run_token_kernel(cudaStream_t st, bool with_head, uint64_t embed_handle, const WeightDev* embed, int32_t first_token, size_t pos0,
+                         size_t n_tokens, std::string& err);
 
     std::vector<Op> ops_;
     std::vector<uint64_t> weight_handles_;
@@ -89,6 +94,13 @@ class DecodePlanImpl {
     uint64_t gen_embed_ = 0;
     WeightDev gen_embed_dev_{};
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    // the persistent token kernel (B2_PLAN_TOKEN_KERNEL=0 keeps to the one-launch-per-op graph)
+    bool tk_ok_ = false;
+    std::vector<TokOp> prog_;
+    TokOp* prog_dev_ = nullptr;
+    uint32_t* tk_ctl_ = nullptr;
+    size_t tk_smem_ = 0;
+    uint32_t tk_barriers_ = 0;
 };
 
 }  // namespace b2

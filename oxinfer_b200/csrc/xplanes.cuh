@@ -14,30 +14,43 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 constexpr float XQ_MAX = 1040000.0f;  // |q0 + 128 q1 + 16384 q2| <= 63 + 128*63 + 16384*63 = 1040319
 
-// All 32 lanes of the warp must call this with the block's values in lane order.
-__device__ __forceinline__ void xplanes_block(float v, int blk, int lane, int K, const XPlanes& out) {
+// One block of 32 values split by a warp (one value per lane, all 32 lanes call it): the lane's three plane bytes,
+// the block scale, the integer sums of the lane's half block and of the block.
+struct XSplit {
+    int q0, q1, q2, sum16, sum32;
+    float s;
+};
+__device__ __forceinline__ XSplit xplanes_split(float v) {
     float a = fabsf(v);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    float s = a / XQ_MAX;
+    XSplit r;
+    r.s = a / XQ_MAX;
     int q = a > 0.0f ? __float2int_rn(v * (XQ_MAX / a)) : 0;
     q = max(-(int)XQ_MAX, min((int)XQ_MAX, q));
-    int q0 = ((q + 64) & 127) - 64;
-    int r1 = (q - q0) >> 7;
-    int q1 = ((r1 + 64) & 127) - 64;
-    int q2 = (r1 - q1) >> 7;
-    size_t at = (size_t)blk * 32 + lane;
-    out.planes[at] = (int8_t)q0;
-    out.planes[(size_t)K + at] = (int8_t)q1;
-    out.planes[2 * (size_t)K + at] = (int8_t)q2;
+    r.q0 = ((q + 64) & 127) - 64;
+    int r1 = (q - r.q0) >> 7;
+    r.q1 = ((r1 + 64) & 127) - 64;
+    r.q2 = (r1 - r.q1) >> 7;
     int sum16 = q;
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum16 += __shfl_xor_sync(0xffffffffu, sum16, o);
-    int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 16);
-    if ((lane & 15) == 0) out.v16[blk * 2 + (lane >> 4)] = sum16;
+    r.sum16 = sum16;
+    r.sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 16);
+    return r;
+}
+
+// The split of block `blk` written to the global-memory layout (XPlanes).
+__device__ __forceinline__ void xplanes_block(float v, int blk, int lane, int K, const XPlanes& out) {
+    const XSplit r = xplanes_split(v);
+    size_t at = (size_t)blk * 32 + lane;
+    out.planes[at] = (int8_t)r.q0;
+    out.planes[(size_t)K + at] = (int8_t)r.q1;
+    out.planes[2 * (size_t)K + at] = (int8_t)r.q2;
+    if ((lane & 15) == 0) out.v16[blk * 2 + (lane >> 4)] = r.sum16;
     if (lane == 0) {
-        out.xs[blk] = s;
-        out.xsum[blk] = s * (float)sum32;
+        out.xs[blk] = r.s;
+        out.xsum[blk] = r.s * (float)r.sum32;
     }
 }
 

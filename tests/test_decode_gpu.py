@@ -21,7 +21,11 @@ pytestmark = pytest.mark.gpu
 CFG = dict(n_layers=2, h=256, nh=4, nkv=2, hd=64, inter=512, vocab=1024)
 
 
-def build(backend, cfg=CFG, seed=900, max_len=512, kv_f16=False, interleaved=True):
+def build(backend, cfg=CFG, seed=900, max_len=512, kv_f16=False, interleaved=True, token_kernel=True):
+    """`token_kernel`: the persistent one-launch-per-token kernel (the default), else the graph of one launch per op."""
+    import os
+
+    os.environ["B2_PLAN_TOKEN_KERNEL"] = "1" if token_kernel else "0"
     layers, final_norm, head, embed, shapes = synth.llama_weights(seed=seed, **cfg)
     dev_layers, cpu_layers = [], []
     for L in layers:
@@ -57,9 +61,11 @@ def prefill(plan, cpu, n, seed):
         plan.kv_write(li, 0, k, v)
 
 
+@pytest.mark.parametrize("token_kernel", [True, False])
 @pytest.mark.parametrize("interleaved", [True, False])
-def test_steps_match_oracle_across_tile_edges(backend, interleaved):
-    plan, cpu, _, cpu_embed, inv_freq, keep = build(backend, interleaved=interleaved)
+def test_steps_match_oracle_across_tile_edges(backend, interleaved, token_kernel):
+    plan, cpu, _, cpu_embed, inv_freq, keep = build(backend, interleaved=interleaved, token_kernel=token_kernel)
+    assert (plan.launches_per_step() == 1) == token_kernel
     rng = np.random.default_rng(5)
     # positions 0 (one key), then a prefilled context whose length crosses the 64-key tile edges
     x = rng.standard_normal(CFG["h"]).astype(np.float32)
@@ -101,8 +107,9 @@ def test_consecutive_steps_build_the_cache(backend):
     plan.close()
 
 
-def test_generate_matches_host_loop_and_oracle(backend):
-    plan, cpu, dembed, cpu_embed, inv_freq, keep = build(backend, seed=920)
+@pytest.mark.parametrize("token_kernel", [True, False])
+def test_generate_matches_host_loop_and_oracle(backend, token_kernel):
+    plan, cpu, dembed, cpu_embed, inv_freq, keep = build(backend, seed=920, token_kernel=token_kernel)
     n0, n = 37, 24
     prefill(plan, cpu, n0, 77)
     table = np.stack([O.rope_table(n0 + i, inv_freq) for i in range(n)])
@@ -144,6 +151,7 @@ def test_grouped_heads_and_long_context(backend):
     """8 query heads per KV head, head dim 128, and more key tiles than CTAs per KV head (several tiles per CTA)."""
     cfg = dict(n_layers=1, h=1024, nh=8, nkv=1, hd=128, inter=512, vocab=512)
     plan, cpu, _, _, inv_freq, keep = build(backend, cfg=cfg, seed=940, max_len=4500)
+    assert plan.launches_per_step() > 1   # 8 heads per KV head: outside the token kernel, the graph takes it
     n = 4300
     prefill(plan, cpu, n, 41)
     rng = np.random.default_rng(9)
@@ -152,6 +160,22 @@ def test_grouped_heads_and_long_context(backend):
     hid, logits = plan.step(n, x, cs)
     rh, rl = cpu.step(n, x, cs, exact=True)
     assert row_err(hid[None], rh[None]) < 1e-4 and row_err(logits[None], rl[None]) < 1e-4
+    plan.close()
+
+
+def test_token_kernel_long_context_several_tiles_per_unit(backend):
+    cfg = dict(n_layers=1, h=512, nh=4, nkv=1, hd=128, inter=512, vocab=512)
+    plan, cpu, _, _, inv_freq, keep = build(backend, cfg=cfg, seed=945, max_len=4500)
+    assert plan.launches_per_step() == 1
+    n = 4300
+    prefill(plan, cpu, n, 43)
+    rng = np.random.default_rng(10)
+    for pos in (n, n + 1):
+        x = rng.standard_normal(cfg["h"]).astype(np.float32)
+        cs = O.rope_table(pos, inv_freq)
+        hid, logits = plan.step(pos, x, cs)
+        rh, rl = cpu.step(pos, x, cs, exact=True)
+        assert row_err(hid[None], rh[None]) < 1e-4 and row_err(logits[None], rl[None]) < 1e-4
     plan.close()
 
 
