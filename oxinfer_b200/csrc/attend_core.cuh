@@ -3,11 +3,14 @@
 #pragma once
 #include <cuda_fp16.h>
 
+#include "async_copy.cuh"
 #include "kernels.h"
 #include "xplanes.cuh"
 
 namespace b2 {
 namespace attend_core {
+
+using namespace acopy;
 
 // Sum over the CTA (every thread calls it; threads with nothing to add pass 0). red: 32 floats of shared memory.
 __device__ __forceinline__ float block_sum(float v, float* red) {  // red: 32 floats of shared memory
@@ -29,7 +32,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {  // red: 32 fl
 // values to row `pos` of the caches [nkv][max_len][hd]. buf: 256 floats of shared memory.
 template <typename T>
 __device__ __forceinline__ void rope_head(const uint32_t h, const uint32_t i, const uint32_t pos, const uint32_t table_pos0,
-                                          const float* __restrict__ qkv, float* __restrict__ qo, T* __restrict__ kc, T* __restrict__ vc,
+                                          const float* qkv, float* qo, T* kc, T* vc,
                                           const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ cs_table,
                                           const DecRope& p, float* buf, float* red) {
     const uint32_t hd = p.hd;
@@ -37,7 +40,8 @@ __device__ __forceinline__ void rope_head(const uint32_t h, const uint32_t i, co
     const uint32_t kind = h < p.nh ? 0 : (h < p.nh + p.nkv ? 1 : 2);
     const uint32_t hh = kind == 0 ? h : (kind == 1 ? h - p.nh : h - p.nh - p.nkv);
     float v = 0.0f;
-    if (on) v = kind == 0 ? qkv[hh * p.q_stride + i] : (kind == 1 || p.v_from_k) ? qkv[p.k_off + hh * hd + i] : qkv[p.v_off + hh * hd + i];
+    // the vector is rewritten between calls by other SMs (persistent kernel): read it from L2
+    if (on) v = __ldcg(kind == 0 ? qkv + hh * p.q_stride + i : (kind == 1 || p.v_from_k) ? qkv + p.k_off + hh * hd + i : qkv + p.v_off + hh * hd + i);
     const bool norm = kind == 0 ? qn != nullptr : (kind == 1 ? kn != nullptr : p.v_norm != 0);
     if (norm) {
         float s = block_sum(v * v, red);
@@ -82,41 +86,6 @@ constexpr int ATT_MAX_SPLITS = 64;   // CTAs per KV head at most
 __device__ __forceinline__ void group_sync(int bar_id) { asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(ATT_THREADS) : "memory"); }
 constexpr long long ATT_WAIT_LIMIT = 2000000000LL;  // cycles (about a second) before a wait on a copy gives up
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_inval(uint64_t* bar) { asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory"); }
-__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded: false after ATT_WAIT_LIMIT cycles.
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
-    if (bar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t spin = 1;; spin++) {
-        if (bar_try_wait(bar, parity)) return true;
-        if ((spin & 255) == 0 && clock64() - t0 > ATT_WAIT_LIMIT) return false;
-    }
-}
-// Contiguous global -> shared copy (both 16-byte aligned, bytes a multiple of 16), completion on `bar`.
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)), "l"(src),
-                 "r"(bytes), "r"(smem_addr(bar))
-                 : "memory");
-}
-
 __device__ __forceinline__ float4 kv4(const float* p) { return *(const float4*)p; }
 __device__ __forceinline__ float4 kv4(const __half* p) {
     uint2 r = *(const uint2*)p;
@@ -149,9 +118,14 @@ __host__ __device__ constexpr size_t attend_smem() {
 // to finish (a counter, no waiting) combines the partials, writes `out` and, if asked, the planes of `out`.
 template <int HD, int G, typename T>
 __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const int bar_id, const int kvh, const int split,
-                                            const uint32_t max_splits, const uint32_t pos, const float* __restrict__ q,
-                                            const T* __restrict__ kc, const T* __restrict__ vc, float* __restrict__ out, float* part,
-                                            uint32_t* counters, DecAttn p, XPlanes xp, uint32_t* status) {
+                                            const uint32_t max_splits, const uint32_t pos, const float* q,
+                                            const T* kc, const T* vc, float* out, float* part,
+                                            uint32_t* counters, DecAttn p, XPlanes xp, uint32_t* status,
+                                            unsigned long long* prof = nullptr) {
+    const long long pt0 = clock64();
+    auto stamp = [&](int i) {
+        if (prof && tid == 0) prof[i] += (unsigned long long)(clock64() - pt0);
+    };
     constexpr int COLS = HD / 4, PARTS = ATT_THREADS / COLS, KPP = ATT_TILE / PARTS;
     constexpr size_t TILE_BYTES = 2 * (size_t)ATT_TILE * HD * sizeof(T);
     constexpr size_t RED_BYTES = (size_t)PARTS * G * HD * 4;
@@ -194,7 +168,7 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         flags[0] = 0;
         flags[1] = 0;
     }
-    for (int i = tid; i < G * HD; i += ATT_THREADS) qs[i] = q[(size_t)h0 * HD + i] * p.scale;
+    for (int i = tid; i < G * HD; i += ATT_THREADS) qs[i] = __ldcg(q + (size_t)h0 * HD + i) * p.scale;
     if (tid < G) {
         mrun[tid] = NEG;
         lrun[tid] = 0.0f;
@@ -218,36 +192,48 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
             ok = false;
             break;
         }
-        // scores: eight lanes per key, two keys per thread group
+        if (t == t0) stamp(0);
+        // scores: eight lanes per key; a thread takes keys `slot` and `slot + 32` together so that one read of the
+        // queries serves both (the queries' shared-memory reads are what bounds this step)
+        {
+            const int ja = slot, jb = slot + 32;
+            const bool va = (uint32_t)ja < nv, vb = (uint32_t)jb < nv;
+            const T* ka = Ks + ja * HD;
+            const T* kb = Ks + jb * HD;
+            float sa[G], sb[G];
 #pragma unroll
-        for (int pass = 0; pass < 2; pass++) {
-            const int j = slot + 32 * pass;
-            float s[G];
+            for (int g = 0; g < G; g++) sa[g] = sb[g] = 0.0f;
 #pragma unroll
-            for (int g = 0; g < G; g++) s[g] = 0.0f;
-            if ((uint32_t)j < nv) {
-                const T* kr = Ks + j * HD;
+            for (int i = 0; i < HD / 32; i++) {
+                const int d = lane8 * 4 + 32 * i;
+                const float4 k4a = va ? kv4(ka + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 k4b = vb ? kv4(kb + d) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < HD / 32; i++) {
-                    const int d = lane8 * 4 + 32 * i;
-                    float4 k4 = kv4(kr + d);
-#pragma unroll
-                    for (int g = 0; g < G; g++) {
-                        float4 q4 = *(const float4*)(qs + g * HD + d);
-                        s[g] = fmaf(k4.x, q4.x, s[g]);
-                        s[g] = fmaf(k4.y, q4.y, s[g]);
-                        s[g] = fmaf(k4.z, q4.z, s[g]);
-                        s[g] = fmaf(k4.w, q4.w, s[g]);
-                    }
+                for (int g = 0; g < G; g++) {
+                    const float4 q4 = *(const float4*)(qs + g * HD + d);
+                    sa[g] = fmaf(k4a.x, q4.x, sa[g]);
+                    sa[g] = fmaf(k4a.y, q4.y, sa[g]);
+                    sa[g] = fmaf(k4a.z, q4.z, sa[g]);
+                    sa[g] = fmaf(k4a.w, q4.w, sa[g]);
+                    sb[g] = fmaf(k4b.x, q4.x, sb[g]);
+                    sb[g] = fmaf(k4b.y, q4.y, sb[g]);
+                    sb[g] = fmaf(k4b.z, q4.z, sb[g]);
+                    sb[g] = fmaf(k4b.w, q4.w, sb[g]);
                 }
             }
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                float v = s[g];
+                float v = sa[g], u = sb[g];
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
+                u += __shfl_xor_sync(0xffffffffu, u, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
+                u += __shfl_xor_sync(0xffffffffu, u, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (lane8 == 0) sc[g * ATT_TILE + j] = (uint32_t)j < nv ? v : NEG;
+                u += __shfl_xor_sync(0xffffffffu, u, 4);
+                if (lane8 == 0) {
+                    sc[g * ATT_TILE + ja] = va ? v : NEG;
+                    sc[g * ATT_TILE + jb] = vb ? u : NEG;
+                }
             }
         }
         group_sync(bar_id);
@@ -272,12 +258,14 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
                 mrun[g] = mn;
             }
         }
+        if (t == t0) stamp(1);
         if (!bar_wait(&bars[1], phase)) flags[0] = 1;
         group_sync(bar_id);
         if (flags[0]) {
             ok = false;
             break;
         }
+        if (t == t0) stamp(2);
         // values: thread (part, c4) adds its KPP keys of the tile into four dimensions of every head
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -316,6 +304,7 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         }
         return;
     }
+    stamp(3);
     if (tid == 0) {  // every thread is past its last wait (the loop ends on a group barrier): the words may be reused
         bar_inval(&bars[0]);
         bar_inval(&bars[1]);
@@ -330,7 +319,7 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         float o = 0.0f;
 #pragma unroll
         for (int pp = 0; pp < PARTS; pp++) o += red[((size_t)pp * G + g) * HD + d];
-        float* ph = part + ((size_t)(h0 + g) * ATT_MAX_SPLITS + split) * (HD + 2);
+        float* ph = part + ((size_t)(h0 + g) * ATT_MAX_SPLITS + split) * (HD + 4);
         ph[d] = o;
         if (d == 0) {
             ph[HD] = mrun[g];
@@ -344,30 +333,72 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         flags[1] = prev == ns - 1;
     }
     group_sync(bar_id);
+    stamp(4);
     if (!flags[1]) return;
     __threadfence();
-    // combine (the last CTA of this KV head)
+    // combine (the last CTA of this KV head). Every load of a partial is issued before it is needed: the (m, l)
+    // pairs of all splits go to shared memory first, the partial outputs are read eight splits at a time.
+    float* msm = sc;  // [G][ATT_MAX_SPLITS] maxima (the probabilities are no longer needed)
+    float* lsm = qs;  // [G][ATT_MAX_SPLITS] sums (nor are the queries)
     for (int i = tid; i < G * (int)ns; i += ATT_THREADS) {
-        const int g = i / (int)ns;
-        const float* ph = part + (size_t)(h0 + g) * ATT_MAX_SPLITS * (HD + 2);
-        float M = NEG;
-        for (uint32_t s = 0; s < ns; s++) M = fmaxf(M, __ldcg(ph + s * (HD + 2) + HD));
-        wts[g * ATT_MAX_SPLITS + (i % (int)ns)] = expf(__ldcg(ph + (i % (int)ns) * (HD + 2) + HD) - M);
+        const int g = i / (int)ns, sp_ = i - g * (int)ns;
+        const float* ph = part + ((size_t)(h0 + g) * ATT_MAX_SPLITS + sp_) * (HD + 4);
+        msm[g * ATT_MAX_SPLITS + sp_] = __ldcg(ph + HD);
+        lsm[g * ATT_MAX_SPLITS + sp_] = __ldcg(ph + HD + 1);
     }
     group_sync(bar_id);
-    for (int idx = tid; idx < G * HD; idx += ATT_THREADS) {
-        const int g = idx / HD, d = idx % HD;
-        const float* ph = part + (size_t)(h0 + g) * ATT_MAX_SPLITS * (HD + 2);
-        float L = 0.0f, o = 0.0f;
-        for (uint32_t s = 0; s < ns; s++) {
-            const float wgt = wts[g * ATT_MAX_SPLITS + s];
-            L += __ldcg(ph + s * (HD + 2) + HD + 1) * wgt;
-            o += __ldcg(ph + s * (HD + 2) + d) * wgt;
-        }
-        const float r = o / L;
-        out[(size_t)h0 * HD + idx] = r;
-        if (p.planes) xplanes_block(r, (h0 * HD + idx) >> 5, tid & 31, (int)(p.nh * HD), xp);
+    for (int i = tid; i < G * (int)ns; i += ATT_THREADS) {
+        const int g = i / (int)ns, sp_ = i - g * (int)ns;
+        float M = NEG;
+        for (uint32_t s2 = 0; s2 < ns; s2++) M = fmaxf(M, msm[g * ATT_MAX_SPLITS + s2]);
+        wts[g * ATT_MAX_SPLITS + sp_] = expf(msm[g * ATT_MAX_SPLITS + sp_] - M);
     }
+    group_sync(bar_id);
+    // The partial outputs: G * HD / 4 columns of four values; the threads form R row groups, group rg adds the splits
+    // rg, rg + R, ... of its column (six 16-byte loads in flight at a time), and the groups' sums are added in order.
+    {
+        constexpr int NC = G * HD / 4, R = ATT_THREADS / NC;
+        const int c = tid % NC, rg = tid / NC;
+        const int g = (c * 4) / HD, d = (c * 4) % HD;
+        const float* ph = part + (size_t)(h0 + g) * ATT_MAX_SPLITS * (HD + 4) + d;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = (uint32_t)rg; s0 < ns; s0 += 6 * R) {
+            float4 v[6];
+#pragma unroll
+            for (int b2 = 0; b2 < 6; b2++) {
+                const uint32_t s2 = s0 + (uint32_t)b2 * R;
+                v[b2] = s2 < ns ? __ldcg((const float4*)(ph + (size_t)s2 * (HD + 4))) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int b2 = 0; b2 < 6; b2++) {
+                const uint32_t s2 = s0 + (uint32_t)b2 * R;
+                if (s2 < ns) {
+                    const float wgt = wts[g * ATT_MAX_SPLITS + s2];
+                    acc.x = fmaf(v[b2].x, wgt, acc.x);
+                    acc.y = fmaf(v[b2].y, wgt, acc.y);
+                    acc.z = fmaf(v[b2].z, wgt, acc.z);
+                    acc.w = fmaf(v[b2].w, wgt, acc.w);
+                }
+            }
+        }
+        *(float4*)(red + ((size_t)rg * NC + c) * 4) = acc;
+        if (tid < G) {  // the denominators
+            float L = 0.0f;
+            for (uint32_t s2 = 0; s2 < ns; s2++) L += lsm[tid * ATT_MAX_SPLITS + s2] * wts[tid * ATT_MAX_SPLITS + s2];
+            mrun[tid] = L;
+        }
+        group_sync(bar_id);
+        for (int idx = tid; idx < G * HD; idx += ATT_THREADS) {
+            float o = 0.0f;
+#pragma unroll
+            for (int r2 = 0; r2 < R; r2++) o += red[(size_t)r2 * NC * 4 + idx];
+            const float r = o / mrun[idx / HD];
+            out[(size_t)h0 * HD + idx] = r;
+            if (p.planes) xplanes_block(r, (h0 * HD + idx) >> 5, tid & 31, (int)(p.nh * HD), xp);
+        }
+    }
+    stamp(5);
+    if (prof && tid == 0) prof[6] += 1;
     if (tid == 0) counters[kvh] = 0;  // ready for the next launch
 }
 

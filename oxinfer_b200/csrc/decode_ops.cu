@@ -263,7 +263,7 @@ bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd) {
     uint32_t g = nh / nkv;
     return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4 || g == 8);
 }
-size_t attend_part_floats(uint32_t nh, uint32_t hd) { return (size_t)nh * ATT_MAX_SPLITS * (hd + 2); }
+size_t attend_part_floats(uint32_t nh, uint32_t hd) { return (size_t)nh * ATT_MAX_SPLITS * (hd + 4); }
 
 template <int HD, int G, typename T>
 static cudaError_t attend_t(const float* q, const void* kc, const void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,

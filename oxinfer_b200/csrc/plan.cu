@@ -6,6 +6,7 @@
 #include "plan.h"
 
 #include <cstdarg>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <algorithm>
@@ -97,7 +98,7 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.k) cudaFree(k.k);
         if (k.v) cudaFree(k.v);
     }
-    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_};
+    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -426,8 +427,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     if (rc) return rc;
     rc = p->capture(p->cap_stream_, false, &p->step_exec_, err);
     if (rc) return rc;
+    // The persistent token kernel is built on request (B2_PLAN_TOKEN_KERNEL=1): at the sizes measured so far the graph of
+    // one launch per op is the faster of the two (grid barriers and per-CTA staging cost what the launches saved).
     const char* tk = getenv("B2_PLAN_TOKEN_KERNEL");
-    if (!tk || atoi(tk) != 0) {
+    if (tk && atoi(tk) != 0) {
         p->build_program();
         if (p->tk_ok_) {
             PLAN_CUDA(cudaMalloc((void**)&p->prog_dev_, p->prog_.size() * sizeof(TokOp)), "cudaMalloc(program)");
@@ -509,8 +512,9 @@ int DecodePlanImpl::check_status(std::string& err) {
     if (tk_ctl_) PLAN_CUDA(cudaMemcpy(tks, tk_ctl_, 12, cudaMemcpyDeviceToHost), "cudaMemcpy(token kernel words)");
     if (tks[2]) {
         cudaMemset(att_counters_, 0, 4 * (kv_.empty() ? 1 : kv_.size()));
-        err = tks[2] == 2 ? "[b200qmm: plan: a grid barrier of the token kernel ran into its time limit]"
-                          : "[b200qmm: plan: an attention wait of the token kernel ran into its time limit]";
+        err = tks[2] == 2   ? "[b200qmm: plan: a grid barrier of the token kernel ran into its time limit]"
+              : tks[2] == 3 ? "[b200qmm: plan: a weight copy of the token kernel did not arrive within its time limit]"
+                            : "[b200qmm: plan: an attention wait of the token kernel ran into its time limit]";
         cudaMemset(tk_ctl_, 0, 12);
         return B2_ERR_TIMEOUT;
     }
@@ -660,8 +664,10 @@ void DecodePlanImpl::build_program() {
     std::vector<Range> W, R;
     prog_.clear();
     tk_barriers_ = 0;
-    const float* staged_ptr = nullptr;
-    size_t staged_n = 0, max_k = 0, att_smem = 0;
+    const float* staged_ptr = nullptr;   // the vector whose planes are in shared memory
+    const float* gplanes_ptr = nullptr;  // the vector whose planes are in global memory (gplanes)
+    XPlanes gplanes{};
+    size_t staged_n = 0, gplanes_n = 0, max_k = 0, att_smem = 0;
     auto emit = [&](const TokOp& op, const std::vector<Range>& reads, const std::vector<Range>& writes) {
         bool barrier = false;
         for (const Range& r : reads) barrier = barrier || hits(r, W);
@@ -677,15 +683,29 @@ void DecodePlanImpl::build_program() {
         prog_.push_back(op);
         R.insert(R.end(), reads.begin(), reads.end());
         W.insert(W.end(), writes.begin(), writes.end());
-        if (staged_ptr)
-            for (const Range& w : writes)
-                if (hits(w, {rng(staged_ptr, staged_n * 4)})) staged_ptr = nullptr;
+        for (const Range& w : writes) {
+            if (staged_ptr && hits(w, {rng(staged_ptr, staged_n * 4)})) staged_ptr = nullptr;
+            if (gplanes_ptr && hits(w, {rng(gplanes_ptr, gplanes_n * 4)})) gplanes_ptr = nullptr;
+        }
     };
     const size_t esz = kv_f16_ ? 2 : 4;
     for (const Op& o : ops_) {
         TokOp t{};
         switch (o.kind) {
-            case OP_XPLANES: break;  // the staging step below replaces it
+            case OP_XPLANES: {
+                // a long vector (the MLP's activations): its planes are computed once, spread over the grid, and copied
+                // by every CTA; a short one is split by every CTA for itself (TK_STAGE below) and saves the barrier
+                if (o.n < 8192) break;
+                t.kind = TK_XPLANES;
+                t.x = o.x;
+                t.n = o.n;
+                t.xp = o.xp;
+                emit(t, {rng(o.x, (size_t)o.n * 4)}, {rng(o.xp.planes, xplanes_bytes(o.n))});
+                gplanes_ptr = o.x;
+                gplanes_n = o.n;
+                gplanes = o.xp;
+                break;
+            }
             case B2_OP_NORM: {
                 if (o.rows != 1 || o.norm.n % 32 || o.norm.n > TOKEN_KERNEL_MAX_NORM || o.norm.add) return;
                 t.kind = TK_NORM_STAGE;
@@ -703,10 +723,16 @@ void DecodePlanImpl::build_program() {
                 if (o.w.fmt == B2_FMT_F8E4M3) return;
                 if (staged_ptr != o.x || staged_n != o.w.n_in) {
                     TokOp s{};
-                    s.kind = TK_STAGE;
                     s.x = o.x;
                     s.n = (uint32_t)o.w.n_in;
-                    emit(s, {rng(o.x, o.w.n_in * 4)}, {});
+                    if (gplanes_ptr == o.x && gplanes_n == o.w.n_in) {
+                        s.kind = TK_COPY;
+                        s.xp = gplanes;
+                        emit(s, {rng(gplanes.planes, xplanes_bytes(s.n))}, {});
+                    } else {
+                        s.kind = TK_STAGE;
+                        emit(s, {rng(o.x, o.w.n_in * 4)}, {});
+                    }
                     staged_ptr = o.x;
                     staged_n = o.w.n_in;
                 }
@@ -748,12 +774,18 @@ void DecodePlanImpl::build_program() {
                 t.kc = kv_[o.kv].k;
                 t.vc = kv_[o.kv].v;
                 t.kv_f16 = (uint32_t)kv_f16_;
-                t.attn = o.attn;
-                t.attn.planes = 0;
+                t.attn = o.attn;  // with planes: the CTA that combines a KV head's splits writes the planes of its outputs
+                t.xp = o.xp;
                 const size_t cache = (size_t)o.attn.nkv * max_len_ * o.attn.hd * esz, qn = (size_t)o.attn.nh * o.attn.hd * 4;
-                emit(t, {rng(o.x, qn), rng(t.kc, cache), rng(t.vc, cache)},
-                     {rng(o.y, qn), rng(part_, attend_part_floats(o.attn.nh, o.attn.hd) * 4), rng(att_counters_, 4 * o.attn.nkv)});
+                std::vector<Range> writes{rng(o.y, qn), rng(part_, attend_part_floats(o.attn.nh, o.attn.hd) * 4), rng(att_counters_, 4 * o.attn.nkv)};
+                if (o.attn.planes) writes.push_back(rng(o.xp.planes, xplanes_bytes((size_t)o.attn.nh * o.attn.hd)));
+                emit(t, {rng(o.x, qn), rng(t.kc, cache), rng(t.vc, cache)}, writes);
                 staged_ptr = nullptr;  // the attention tiles use the planes' shared memory
+                if (o.attn.planes) {
+                    gplanes_ptr = o.y;
+                    gplanes_n = (size_t)o.attn.nh * o.attn.hd;
+                    gplanes = o.xp;
+                }
                 att_smem = std::max(att_smem, token_kernel_smem(0, o.attn.hd, o.attn.nh / o.attn.nkv, kv_f16_));
                 break;
             }
@@ -770,8 +802,18 @@ void DecodePlanImpl::build_program() {
             default: return;
         }
     }
-    tk_smem_ = std::max(att_smem, token_kernel_smem(max_k, 0, 1, 0));
-    if (tk_smem_ > 220 * 1024) return;
+    // the most ring slots per warp that fit beside the planes
+    const size_t limit = 226 * 1024;
+    tk_ring_offset_ = (uint32_t)token_kernel_ring_offset(max_k);
+    tk_ring_slots_ = 0;
+    for (uint32_t sl = 4; sl >= 2; sl--)
+        if (token_kernel_fixed_bytes() + tk_ring_offset_ + token_kernel_ring_bytes(sl) <= limit) {
+            tk_ring_slots_ = sl;
+            break;
+        }
+    if (!tk_ring_slots_) return;
+    tk_smem_ = std::max(att_smem, token_kernel_fixed_bytes() + tk_ring_offset_ + token_kernel_ring_bytes(tk_ring_slots_));
+    if (tk_smem_ > limit) return;
     tk_ok_ = true;
 }
 
@@ -787,6 +829,8 @@ int DecodePlanImpl::run_token_kernel(cudaStream_t st, bool with_head, uint64_t, 
     a.n_logits = n_logits_;
     a.max_splits = std::min<uint32_t>(64, (max_len_ + 63) / 64);
     a.first_token = (uint32_t)first_token;
+    a.ring_slots = tk_ring_slots_;
+    a.ring_offset = tk_ring_offset_;
     a.cs_table = rope_table_;
     a.input = input_;
     a.logits = logits_;
@@ -798,8 +842,32 @@ int DecodePlanImpl::run_token_kernel(cudaStream_t st, bool with_head, uint64_t, 
     a.token = token_;
     a.out_tokens = out_tokens_;
     if (embed) a.embed = *embed;
+    if (getenv("B2_TK_PROF")) {
+        if (!tk_prof_) {
+            PLAN_CUDA(cudaMalloc((void**)&tk_prof_, 96 * 8), "cudaMalloc(profile)");
+        }
+        PLAN_CUDA(cudaMemsetAsync(tk_prof_, 0, 96 * 8, st), "cudaMemset(profile)");
+        a.prof = tk_prof_;
+    }
     PLAN_CUDA(cudaMemsetAsync(tk_ctl_, 0, 64, st), "cudaMemset(token kernel words)");
     PLAN_CUDA(launch_token_kernel(a, tk_smem_, sm_count_, st), "token kernel");
+    if (a.prof) {  // diagnostics: CTA 0's cycles per op kind, per token
+        unsigned long long h[96];
+        PLAN_CUDA(cudaStreamSynchronize(st), "token kernel");
+        PLAN_CUDA(cudaMemcpy(h, tk_prof_, sizeof h, cudaMemcpyDeviceToHost), "cudaMemcpy(profile)");
+        static const char* names[16] = {"", "norm_stage", "stage", "gemv", "rope", "attend", "glu", "barrier", "xplanes", "copy", "", "", "", "", "", ""};
+        for (int k = 1; k < 10; k++)
+            if (h[16 + k])
+                fprintf(stderr, "[b200qmm token kernel] %-10s %6llu ops/token  %9.0f cycles/token  %7.0f cycles/op\n", names[k],
+                        h[16 + k] / (unsigned long long)n_tokens, (double)h[k] / n_tokens, (double)h[k] / h[16 + k]);
+        for (size_t pc = 0; pc < 32 && pc < prog_.size(); pc++)
+            fprintf(stderr, "[b200qmm token kernel] op %2zu %-10s %8.0f cycles\n", pc, names[prog_[pc].kind & 15], (double)h[32 + pc] / n_tokens);
+        if (h[17]) fprintf(stderr, "[b200qmm token kernel] norm_stage: loads done %.0f, sum done %.0f (cycles from its start)\n", (double)h[64] / h[17], (double)h[65] / h[17]);
+        if (h[21])
+            fprintf(stderr, "[b200qmm token kernel] attend unit (CTA 0, group 0), cycles from its start: keys in %.0f, scores %.0f, values in %.0f, loop done %.0f, counted %.0f, combined %.0f (%llu combines)\n",
+                    (double)h[72] / h[21], (double)h[73] / h[21], (double)h[74] / h[21], (double)h[75] / h[21], (double)h[76] / h[21],
+                    h[78] ? (double)h[77] / h[78] : 0.0, h[78]);
+    }
     return B2_OK;
 }
 

@@ -100,7 +100,9 @@ class DecodePlanImpl {
     TokOp* prog_dev_ = nullptr;
     uint32_t* tk_ctl_ = nullptr;
     size_t tk_smem_ = 0;
+    uint32_t tk_ring_slots_ = 0, tk_ring_offset_ = 0;
     uint32_t tk_barriers_ = 0;
+    unsigned long long* tk_prof_ = nullptr;  // B2_TK_PROF: per-op-kind cycle counts of CTA 0
 };
 
 }  // namespace b2

@@ -9,6 +9,7 @@
 #include "attend_core.cuh"
 #include "dq_core.cuh"
 #include "gemv_core.cuh"
+#include "gemv_ring.cuh"
 
 namespace b2 {
 
@@ -30,6 +31,7 @@ struct Fixed {  // start of the dynamic shared memory
     int best_i[TK_WARPS];
     int flag;
     int token;
+    uint64_t ring_bars[TK_WARPS * 4];  // the warps' ring barriers (up to four slots each)
 };
 constexpr size_t FIXED_BYTES = (sizeof(Fixed) + 127) / 128 * 128;
 
@@ -69,21 +71,8 @@ __device__ __forceinline__ bool grid_barrier(uint32_t* ctl, uint32_t& target, Fi
     return fx->flag != 0;
 }
 
-// The planes of one block of 32 values into the shared-memory layout the GEMV code reads (XS, swz): `pl` is
-// [3][K] plane bytes, then {scale, scaled sum} per block, then the 16-element integer sums.
-__device__ __forceinline__ void stage_block(float v, int blk, int lane, int K, uint8_t* pl) {
-    const XSplit r = xplanes_split(v);
-    const int k = blk * 32 + lane;
-    const int at = (swz(k >> 4) << 4) + (k & 15);
-    pl[at] = (uint8_t)(int8_t)r.q0;
-    pl[K + at] = (uint8_t)(int8_t)r.q1;
-    pl[2 * K + at] = (uint8_t)(int8_t)r.q2;
-    float2* sx = (float2*)(pl + 3 * (size_t)K);
-    int32_t* v16 = (int32_t*)(sx + K / 32);
-    if ((lane & 15) == 0) v16[blk * 2 + (lane >> 4)] = r.sum16;
-    if (lane == 0) sx[blk] = make_float2(r.s, r.s * (float)r.sum32);
-}
-
+// The shared-memory layout the GEMV code reads (XS, swz): `pl` is [3][K] plane bytes, then {scale, scaled sum} per
+// block of 32, then the 16-element integer sums.
 __device__ __forceinline__ XS staged(uint8_t* pl, int K) {
     XS xs;
     xs.K = K;
@@ -94,36 +83,109 @@ __device__ __forceinline__ XS staged(uint8_t* pl, int K) {
     return xs;
 }
 
+// Four consecutive values per lane (element k0 .. k0 + 3, k0 a multiple of 4): the eight lanes that hold a block of
+// 32 split it together. Same arithmetic per element as xplanes_split; the plane bytes go out as 32-bit words.
+__device__ __forceinline__ void stage_quad(float4 t, int k0, int lane, int K, uint8_t* pl) {
+    const unsigned m8 = 0xffu << (lane & 24), m4 = 0xfu << (lane & 28);
+    const float v[4] = {t.x, t.y, t.z, t.w};
+    const float amax = fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w)));
+    const float a = __uint_as_float(__reduce_max_sync(m8, __float_as_uint(amax)));
+    const float sc = a / XQ_MAX, inv = XQ_MAX / a;
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    int sum = 0;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        int q = a > 0.0f ? __float2int_rn(v[e] * inv) : 0;
+        q = max(-(int)XQ_MAX, min((int)XQ_MAX, q));
+        const int q0 = ((q + 64) & 127) - 64;
+        const int r1 = (q - q0) >> 7;
+        const int q1 = ((r1 + 64) & 127) - 64;
+        const int q2 = (r1 - q1) >> 7;
+        w0 |= (uint32_t)(q0 & 0xff) << (8 * e);
+        w1 |= (uint32_t)(q1 & 0xff) << (8 * e);
+        w2 |= (uint32_t)(q2 & 0xff) << (8 * e);
+        sum += q;
+    }
+    const int at = (swz(k0 >> 4) << 4) + (k0 & 15);
+    *(uint32_t*)(pl + at) = w0;
+    *(uint32_t*)(pl + K + at) = w1;
+    *(uint32_t*)(pl + 2 * K + at) = w2;
+    const int sum16 = __reduce_add_sync(m4, sum), sum32 = __reduce_add_sync(m8, sum);
+    float2* sx = (float2*)(pl + 3 * (size_t)K);
+    int32_t* v16 = (int32_t*)(sx + K / 32);
+    if ((lane & 3) == 0) v16[k0 >> 4] = sum16;
+    if ((lane & 7) == 0) sx[k0 >> 5] = make_float2(sc, sc * (float)sum32);
+}
+
 // RMSNorm of one row (norm_kernel's arithmetic), every CTA for itself: the row's planes land in shared memory.
-__device__ __forceinline__ void norm_stage(const TokOp& op, Fixed* fx, uint8_t* pl) {
+// A thread holds two runs of four consecutive values (rows of up to 8 * 768).
+__device__ __forceinline__ void norm_stage(const TokOp& op, Fixed* fx, uint8_t* pl, unsigned long long* prof) {
+    const long long pt0 = clock64();
     const DecNorm& p = op.norm;
     const int tid = threadIdx.x;
-    float v[8], wv[8];
+    float4 v[2], wv[2];
     float s = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t i = tid + j * TK_THREADS;
-        v[j] = i < p.n ? op.x[i] * p.pre : 0.0f;
-        wv[j] = (i < p.n && op.p0) ? op.p0[i] : 1.0f;
-        s += v[j] * v[j];
+    for (int j = 0; j < 2; j++) {
+        const uint32_t i = (tid + j * TK_THREADS) * 4;
+        v[j] = i < p.n ? __ldcg((const float4*)(op.x + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        wv[j] = (i < p.n && op.p0) ? *(const float4*)(op.p0 + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        v[j].x *= p.pre;
+        v[j].y *= p.pre;
+        v[j].z *= p.pre;
+        v[j].w *= p.pre;
+        s += v[j].x * v[j].x;
+        s += v[j].y * v[j].y;
+        s += v[j].z * v[j].z;
+        s += v[j].w * v[j].w;
     }
+    if (prof && tid == 0) prof[0] += (unsigned long long)(clock64() - pt0);
     const float k = 1.0f / sqrtf(block_sum(s, fx->red) / (float)p.n + p.eps);
+    if (prof && tid == 0) prof[1] += (unsigned long long)(clock64() - pt0);
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t i = tid + j * TK_THREADS;
-        if (i < p.n) {  // p.n % 32 == 0: whole warps
-            float t = v[j] * k;
-            if (op.p0) t *= wv[j];
-            if (blockIdx.x == 0) op.y[i] = t;
-            stage_block(t, (int)(i >> 5), tid & 31, (int)p.n, pl);
+    for (int j = 0; j < 2; j++) {
+        const uint32_t i = (tid + j * TK_THREADS) * 4;
+        if (i < p.n) {  // p.n % 32 == 0: the eight lanes of a block are all here
+            float4 t = make_float4(v[j].x * k, v[j].y * k, v[j].z * k, v[j].w * k);
+            if (op.p0) t = make_float4(t.x * wv[j].x, t.y * wv[j].y, t.z * wv[j].z, t.w * wv[j].w);
+            if (blockIdx.x == 0) *(float4*)(op.y + i) = t;
+            stage_quad(t, (int)i, tid & 31, (int)p.n, pl);
         }
     }
     __syncthreads();
 }
 
 __device__ __forceinline__ void stage_vector(const float* x, int n, uint8_t* pl) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int blk = warp; blk < n / 32; blk += TK_WARPS) stage_block(x[blk * 32 + lane], blk, lane, n, pl);
+    const int tid = threadIdx.x, quads = n / 4;
+    for (int q0 = tid; q0 < quads; q0 += TK_THREADS * 4) {  // four loads in flight per lane (the vector sits in L2)
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int q = q0 + j * TK_THREADS;
+            v[j] = q < quads ? __ldcg((const float4*)x + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int q = q0 + j * TK_THREADS;
+            if (q < quads) stage_quad(v[j], q * 4, tid & 31, n, pl);
+        }
+    }
+    __syncthreads();
+}
+
+// Planes another phase left in global memory -> this CTA's shared memory (the staging step of gemv_kernel).
+__device__ __forceinline__ void copy_planes(const XPlanes& xp, int K, uint8_t* pl) {
+    const int slots = K / 16;  // per plane
+    const uint4* src = (const uint4*)xp.planes;
+    uint4* dst = (uint4*)pl;
+    for (int i = threadIdx.x; i < 3 * slots; i += TK_THREADS) {
+        const int p = i / slots, g = i - p * slots;
+        dst[p * slots + swz(g)] = __ldcg(src + i);
+    }
+    float2* sx = (float2*)(pl + 3 * (size_t)K);
+    for (int b = threadIdx.x; b < K / 32; b += TK_THREADS) sx[b] = make_float2(__ldcg(xp.xs + b), __ldcg(xp.xsum + b));
+    int32_t* v16 = (int32_t*)(sx + K / 32);
+    for (int b = threadIdx.x; b < K / 16; b += TK_THREADS) v16[b] = __ldcg(xp.v16 + b);
     __syncthreads();
 }
 
@@ -178,6 +240,16 @@ __device__ __forceinline__ void gemv_fmt(const TokOp& op, const XS& xs) {
     else gemv_rows<F, false>(op, xs);
 }
 
+// The 4-bit formats: weights through the warp's ring of bulk copies (gemv_ring.cuh).
+template <class F>
+__device__ __forceinline__ bool gemv_ring_fmt(const TokOp& op, const XS& xs, WarpRing& ring) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t rw = op.pair ? 1 : 2;
+    const size_t r_first = ((size_t)warp * gridDim.x + blockIdx.x) * rw, r_step = (size_t)gridDim.x * TK_WARPS * rw;
+    if (op.pair) return gemv4_ring<F, true>(op.w, op.w2, xs, op.y, (int)op.mode, op.z, ring, r_first, r_step, lane);
+    return gemv4_ring<F, false>(op.w, op.w2, xs, op.y, (int)op.mode, op.z, ring, r_first, r_step, lane);
+}
+
 template <int HD, int G, typename T>
 __device__ __forceinline__ void attend_all(const TokOp& op, const TokenArgs& a, uint32_t pos, uint8_t* work) {
     const DecAttn& p = op.attn;
@@ -188,11 +260,11 @@ __device__ __forceinline__ void attend_all(const TokOp& op, const TokenArgs& a, 
     const int group = threadIdx.x / ATT_THREADS, gtid = threadIdx.x % ATT_THREADS;
     constexpr size_t GROUP_BYTES = (attend_smem<HD, G, T>() + 127) / 128 * 128;
     uint8_t* gsm = work + (size_t)group * GROUP_BYTES;
-    XPlanes none{};
     // unit u = (KV head, split); consecutive units go to different SMs
     for (uint32_t u = (uint32_t)group * gridDim.x + blockIdx.x; u < p.nkv * ns; u += TK_GROUPS * gridDim.x)
         attend_unit<HD, G, T>(gsm, gtid, 1 + group, (int)(u / ns), (int)(u % ns), a.max_splits, pos, op.x, (const T*)op.kc, (const T*)op.vc,
-                              op.y, a.part, a.att_counters, p, none, &a.ctl[2]);
+                              op.y, a.part, a.att_counters, p, op.xp, &a.ctl[2],
+                              (a.prof && blockIdx.x == 0 && group == 0) ? a.prof + 72 : nullptr);
     __syncthreads();
 }
 
@@ -238,6 +310,16 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TokenArgs a) {
     uint8_t* work = smem + FIXED_BYTES;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t target = 0;
+    // the warp's ring: slots behind the planes (the attention tiles use the same memory at other times)
+    WarpRing ring;
+    ring.S = (int)a.ring_slots;
+    ring.slots = work + a.ring_offset + (size_t)warp * a.ring_slots * RING_SLOT_BYTES;
+    ring.bars = fx->ring_bars + warp * 4;
+    ring.phases = 0;
+    if (lane == 0)
+        for (int sl = 0; sl < ring.S; sl++) bar_init(&ring.bars[sl], 1);
+    if (tid == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
     for (uint32_t tok = 0; tok < a.n_tokens; tok++) {
         const uint32_t pos = a.pos0 + tok;
         if (a.with_head) {
@@ -258,19 +340,30 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TokenArgs a) {
             for (uint32_t i = tid; i < sizeof(TokOp) / 4; i += TK_THREADS) ((uint32_t*)&fx->op)[i] = ((const uint32_t*)&a.prog[pc])[i];
             __syncthreads();
             const TokOp& op = fx->op;
+            const long long prof_t0 = clock64();
             switch (op.kind) {
                 case TK_BARRIER:
                     if (!grid_barrier(a.ctl, target, fx)) return;
                     break;
-                case TK_NORM_STAGE: norm_stage(op, fx, work); break;
+                case TK_NORM_STAGE: norm_stage(op, fx, work, (a.prof && blockIdx.x == 0) ? a.prof + 64 : nullptr); break;
                 case TK_STAGE: stage_vector(op.x, (int)op.n, work); break;
+                case TK_COPY: copy_planes(op.xp, (int)op.n, work); break;
+                case TK_XPLANES:
+                    for (uint32_t blk = (uint32_t)warp * gridDim.x + blockIdx.x; blk < op.n / 32; blk += gridDim.x * TK_WARPS)
+                        xplanes_block(__ldcg(op.x + blk * 32 + lane), (int)blk, lane, (int)op.n, op.xp);
+                    break;
                 case TK_GEMV: {
                     const XS xs = staged(work, (int)op.w.n_in);
+                    bool ok = true;
                     switch (op.w.fmt) {
-                        case B2_FMT_MLX4: gemv_fmt<FmtMLX4>(op, xs); break;
-                        case B2_FMT_Q4_K: gemv_fmt<FmtQ4K>(op, xs); break;
+                        case B2_FMT_MLX4: ok = gemv_ring_fmt<FmtMLX4>(op, xs, ring); break;
+                        case B2_FMT_Q4_K: ok = gemv_ring_fmt<FmtQ4K>(op, xs, ring); break;
                         case B2_FMT_Q6_K: gemv_fmt<FmtQ6K>(op, xs); break;
                         case B2_FMT_Q8_0: gemv_fmt<FmtQ8_0>(op, xs); break;
+                    }
+                    if (!ok) {  // a copy did not arrive: every CTA leaves at its next barrier
+                        atomicExch(&a.ctl[1], 1u);
+                        atomicCAS(&a.ctl[2], 0u, 3u);
                     }
                     break;
                 }
@@ -295,7 +388,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TokenArgs a) {
                     break;
                 case TK_GLU:
                     for (uint32_t i = blockIdx.x * TK_THREADS + tid; i < op.n; i += gridDim.x * TK_THREADS) {
-                        const float g = op.x[i];
+                        const float g = __ldcg(op.x + i);
                         float r;
                         if (op.gelu) {
                             const float K2 = 2.0f * 0.7978846f;
@@ -304,9 +397,14 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TokenArgs a) {
                         } else {
                             r = g / (1.0f + expf(-g));
                         }
-                        op.y[i] = r * op.z[i];
+                        op.y[i] = r * __ldcg(op.z + i);
                     }
                     break;
+            }
+            if (a.prof && blockIdx.x == 0 && tid == 0) {
+                a.prof[op.kind & 15] += (unsigned long long)(clock64() - prof_t0);
+                a.prof[16 + (op.kind & 15)] += 1;
+                if (pc < 32) a.prof[32 + pc] += (unsigned long long)(clock64() - prof_t0);  // the first layer, op by op
             }
         }
         if (a.with_head) {
@@ -314,7 +412,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TokenArgs a) {
             if (!grid_barrier(a.ctl, target, fx)) return;
             float best = -INFINITY;
             int bi = 0x7fffffff;
-            for (uint32_t i = blockIdx.x * TK_THREADS + tid; i < a.n_logits; i += gridDim.x * TK_THREADS) best_of(best, bi, a.logits[i], (int)i);
+            for (uint32_t i = blockIdx.x * TK_THREADS + tid; i < a.n_logits; i += gridDim.x * TK_THREADS) best_of(best, bi, __ldcg(a.logits + i), (int)i);
             warp_best(best, bi);
             if (lane == 0) {
                 fx->best_v[warp] = best;
@@ -362,6 +460,10 @@ bool token_kernel_attend_ok(uint32_t nh, uint32_t nkv, uint32_t hd) {
     const uint32_t g = nh / nkv;
     return (hd == 64 || hd == 128) && (g == 1 || g == 2 || g == 4);
 }
+
+size_t token_kernel_ring_offset(size_t max_k) { return (xplanes_bytes(max_k) + 127) / 128 * 128; }
+size_t token_kernel_ring_bytes(uint32_t slots) { return (size_t)TK_WARPS * slots * RING_SLOT_BYTES; }
+size_t token_kernel_fixed_bytes() { return FIXED_BYTES; }
 
 size_t token_kernel_smem(size_t max_k, uint32_t hd, uint32_t g, int kv_f16) {
     size_t att = 0;

@@ -17,6 +17,8 @@ enum : uint32_t {
     TK_ATTEND = 5,      // (KV head, key split) units spread over the 256-thread groups of all CTAs
     TK_GLU = 6,
     TK_BARRIER = 7,
+    TK_XPLANES = 8,     // planes of the vector x -> global memory (xp), blocks spread over all warps of the grid
+    TK_COPY = 9,        // planes in global memory (xp) -> shared memory (every CTA)
 };
 
 struct TokOp {
@@ -37,6 +39,7 @@ struct TokOp {
     DecNorm norm;
     DecRope rope;
     DecAttn attn;
+    XPlanes xp;       // XPLANES / ATTEND write them, COPY reads them
 };
 
 struct TokenArgs {
@@ -49,6 +52,8 @@ struct TokenArgs {
     uint32_t n_logits;
     uint32_t max_splits;  // attention: splits per KV head at most
     uint32_t first_token;
+    uint32_t ring_slots;  // slots of each warp's weight ring (2 .. 4)
+    uint32_t ring_offset; // where the rings start in the work area (behind the planes)
     const float* cs_table;
     float* input;         // the token's embedding goes here
     const float* logits;
@@ -60,14 +65,19 @@ struct TokenArgs {
     int* token;           // the last token chosen
     int* out_tokens;
     WeightDev embed;
+    unsigned long long* prof;  // optional (diagnostics): cycles CTA 0 spent per op kind [16], and how many ops [16]
 };
 
 // Shared memory the kernel needs for planes of up to max_k values and attention with (hd, heads per KV head, cache type).
 size_t token_kernel_smem(size_t max_k, uint32_t hd, uint32_t g, int kv_f16);
+// The rings of the 4-bit products: where they start behind planes of max_k values, and their size for `slots` slots per warp.
+size_t token_kernel_ring_offset(size_t max_k);
+size_t token_kernel_ring_bytes(uint32_t slots);
+size_t token_kernel_fixed_bytes();
 // Whether the kernel takes this attention shape (head dim 64 / 128, 1 / 2 / 4 heads per KV head).
 bool token_kernel_attend_ok(uint32_t nh, uint32_t nkv, uint32_t hd);
 // The largest norm row the kernel keeps in registers.
-constexpr uint32_t TOKEN_KERNEL_MAX_NORM = 768 * 8;
+constexpr uint32_t TOKEN_KERNEL_MAX_NORM = 768 * 8;  // two runs of four values per thread
 // Cooperative launch on `st` with one CTA per SM. `ctl` must be zeroed (stream-ordered) before each launch.
 cudaError_t launch_token_kernel(const TokenArgs& args, size_t smem, int sm_count, cudaStream_t st);
 

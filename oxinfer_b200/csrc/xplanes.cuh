@@ -21,9 +21,8 @@ struct XSplit {
     float s;
 };
 __device__ __forceinline__ XSplit xplanes_split(float v) {
-    float a = fabsf(v);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    // the block's largest magnitude: non-negative floats order like their bit patterns, so one integer warp reduction
+    float a = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v))));
     XSplit r;
     r.s = a / XQ_MAX;
     int q = a > 0.0f ? __float2int_rn(v * (XQ_MAX / a)) : 0;
@@ -32,11 +31,9 @@ __device__ __forceinline__ XSplit xplanes_split(float v) {
     int r1 = (q - r.q0) >> 7;
     r.q1 = ((r1 + 64) & 127) - 64;
     r.q2 = (r1 - r.q1) >> 7;
-    int sum16 = q;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) sum16 += __shfl_xor_sync(0xffffffffu, sum16, o);
-    r.sum16 = sum16;
-    r.sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 16);
+    const unsigned half = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;  // the lane's half warp
+    r.sum16 = __reduce_add_sync(half, q);
+    r.sum32 = __reduce_add_sync(0xffffffffu, q);
     return r;
 }
 
