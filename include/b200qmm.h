@@ -195,6 +195,11 @@ typedef struct b2_view {
 #define B2_OP_QK_ROPE 3 /* Op::QkRope */
 #define B2_OP_ATTEND 4  /* Op::Attend (window optional; no gate, no draft block) */
 #define B2_OP_GLU 5     /* Op::Glu */
+/* No counterpart in the reference (one device only): tensor-parallel plans. The vector at `x` (n values) is sharded over
+ * the ranks in equal contiguous parts; every rank wrote its own part, and after the op every rank holds all of it
+ * (an all-gather). Done with stores into the peers' activation buffers over NVLink and a flag barrier between the
+ * GPUs (b2_plan_attach_peers), not with a library collective. */
+#define B2_OP_EXCHANGE 6
 
 typedef struct b2_op {
     uint32_t kind;
@@ -256,6 +261,17 @@ int b2_plan_generate(b2_ctx* ctx, b2_plan plan, b2_weight embed, int32_t first_t
                      const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms);
 /* Kernel launches of one step of the plan (for launch accounting). */
 int b2_plan_launches(b2_ctx* ctx, b2_plan plan, uint64_t* per_step);
+
+/* Tensor-parallel plans (one process per GPU; no counterpart in the reference). A graph with B2_OP_EXCHANGE ops
+ * needs its peers before the first step: every rank exports a handle to its plan's activation memory
+ * (b2_plan_export: B2_PLAN_HANDLE_BYTES bytes, to be passed to the other processes by any means, e.g. an all-gather on
+ * the host), then attaches all ranks' handles in rank order (its own entry is ignored). The ranks must build the same
+ * graph (same buffers, same exchanges) over their own weight shards. Steps are collective: every rank calls
+ * b2_plan_step / b2_plan_generate with the same arguments; a rank that does not arrive makes the others' exchange
+ * give up after a bounded wait (B2_ERR_TIMEOUT), it does not hang them. */
+#define B2_PLAN_HANDLE_BYTES 128
+int b2_plan_export(b2_ctx* ctx, b2_plan plan, void* handle_out);
+int b2_plan_attach_peers(b2_ctx* ctx, b2_plan plan, uint32_t rank, uint32_t world, const void* handles);
 
 /* No counterpart in the reference (its CUDA backend allocates staging and arena memory freely,
  * src/cuda.rs:572-699). One Q4_K matrix-vector product, y[n_out] = W x, that allocates nothing, for

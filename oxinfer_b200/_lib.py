@@ -32,7 +32,8 @@ class View(C.Structure):
     _fields_ = [("buf", C.c_uint32), ("off", C.c_uint32)]
 
 
-OP_NORM, OP_LINEAR, OP_QK_ROPE, OP_ATTEND, OP_GLU = 1, 2, 3, 4, 5
+OP_NORM, OP_LINEAR, OP_QK_ROPE, OP_ATTEND, OP_GLU, OP_EXCHANGE = 1, 2, 3, 4, 5, 6
+PLAN_HANDLE_BYTES = 128
 
 
 class Op(C.Structure):
@@ -115,6 +116,8 @@ _SIGNATURES = {
     "b2_plan_generate": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
                                    C.POINTER(C.c_float)]),
     "b2_plan_launches": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "b2_plan_export": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
+    "b2_plan_attach_peers": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]),
     "b2_matvec_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
 }
 

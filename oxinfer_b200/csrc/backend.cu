@@ -765,6 +765,23 @@ class Backend {
         return rc;
     }
 
+    int plan_export(uint64_t h, void* out) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p || !out) return fail(B2_ERR_ARG, "[b200qmm: plan_export: unknown plan]");
+        std::string e;
+        int rc = p->export_handle(out, e);
+        if (rc) err = e;
+        return rc;
+    }
+    int plan_attach(uint64_t h, uint32_t rank, uint32_t world, const void* handles) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p) return fail(B2_ERR_ARG, "[b200qmm: plan_attach_peers: unknown plan]");
+        std::string e;
+        int rc = p->attach_peers(rank, world, handles, e);
+        if (rc) err = e;
+        return rc;
+    }
+
     void close() {
         cudaStreamSynchronize(stream);
         for (auto& dp : decode_plans) delete dp.second;
@@ -1017,4 +1034,14 @@ B2_EXPORT int b2_plan_launches(b2_ctx* ctx, b2_plan plan, uint64_t* per_step) {
     if (!p || !per_step) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: plan_launches: unknown plan]");
     *per_step = p->launches_per_step();
     return B2_OK;
+}
+
+B2_EXPORT int b2_plan_export(b2_ctx* ctx, b2_plan plan, void* handle_out) {
+    LOCKED(ctx);
+    return ctx->be.plan_export(plan, handle_out);
+}
+
+B2_EXPORT int b2_plan_attach_peers(b2_ctx* ctx, b2_plan plan, uint32_t rank, uint32_t world, const void* handles) {
+    LOCKED(ctx);
+    return ctx->be.plan_attach(plan, rank, world, handles);
 }

@@ -218,6 +218,63 @@ __global__ void set_step_kernel(uint32_t* sp, uint32_t pos, uint32_t table_pos0,
     if (token) token[0] = tok;
 }
 
+// ---- all-gather of a row-sharded vector by stores into the peers' buffers ---------------------------------------
+// One CTA. The GPUs meet twice: once before anyone writes (every rank is then past the kernels that read the vector's
+// old contents), once after (every part has landed everywhere). A meeting = a store of the running epoch into each
+// peer's flag word for this rank, then a bounded wait until every peer's word here has reached the epoch.
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+constexpr long long EXCHANGE_WAIT_LIMIT = 1000000000LL;  // cycles (about half a second)
+
+__device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, int bank, uint32_t epoch, int* ok_s) {
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) *ok_s = 1;
+    __syncthreads();
+    if (tid < ps.world && tid != ps.rank) {
+        st_release_sys(ps.flags[tid] + bank + ps.rank, epoch);
+        const long long t0 = clock64();
+        uint32_t spin = 0;
+        while ((int32_t)(ld_acquire_sys(lflags + bank + tid) - epoch) < 0) {
+            if ((++spin & 15) == 0 && clock64() - t0 > EXCHANGE_WAIT_LIMIT) {
+                *ok_s = 0;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    return *ok_s != 0;
+}
+
+__global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, uint32_t n, uint32_t* lflags, uint32_t* status) {
+    __shared__ int ok_s;
+    __shared__ uint32_t epoch_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) epoch_s = lflags[0] + 1;
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    bool ok = peers_meet(ps, lflags, 8, epoch, &ok_s);
+    if (ok) {
+        const uint32_t part = n / ps.world;  // a multiple of 4 (checked on the host)
+        const float4* src = (const float4*)(ps.base[ps.rank] + off + (size_t)ps.rank * part);
+        for (uint32_t p = 0; p < ps.world; p++) {
+            if (p == ps.rank) continue;
+            float4* dst = (float4*)(ps.base[p] + off + (size_t)ps.rank * part);
+            for (uint32_t i = threadIdx.x; i < part / 4; i += blockDim.x) dst[i] = __ldcg(src + i);
+        }
+        __threadfence_system();
+        ok = peers_meet(ps, lflags, 16, epoch, &ok_s);
+    }
+    if (threadIdx.x == 0) {
+        lflags[0] = epoch;
+        if (!ok) atomicExch(status, 4u);
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, uint32_t nkv, uint32_t hd, uint32_t max_len, uint32_t pos0,
@@ -233,6 +290,11 @@ cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, 
         else kv_rows_kernel<float, false><<<grid, 256, 0, st>>>(rows, (float*)cache, nkv, hd, max_len, pos0, n);
     }
     return cudaGetLastError();
+}
+
+cudaError_t launch_exchange(const PeerSet& ps, size_t off_floats, uint32_t n, uint32_t* lflags, uint32_t* status, cudaStream_t st, bool pdl) {
+    if (ps.world < 2 || ps.world > 8 || n % (4 * ps.world)) return cudaErrorInvalidValue;
+    return launch_k(exchange_kernel, dim3(1), dim3(1024), 0, st, pdl, ps, off_floats, n, lflags, status);
 }
 
 cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uint32_t count, int* token, int tok, cudaStream_t st) {

@@ -98,7 +98,8 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.k) cudaFree(k.k);
         if (k.v) cudaFree(k.v);
     }
-    void* frees[] = {bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
+    for (void* m : peer_maps_) cudaIpcCloseMemHandle(m);
+    void* frees[] = {xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -363,6 +364,18 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                 touch(o.y.buf);
                 break;
             }
+            case B2_OP_EXCHANGE: {
+                if (o.n == 0 || o.n % 32) {
+                    err = "[b200qmm: decode_plan: an exchanged vector must be a positive multiple of 32 values]";
+                    return B2_ERR_ARG;
+                }
+                op.x = view(o.x, o.n);
+                op.n = o.n;
+                if (op.x) op.off = (size_t)(op.x - p->bufs_);
+                p->has_exchange_ = true;
+                touch(o.x.buf);
+                break;
+            }
             default:
                 err = fmt("[b200qmm: decode_plan: op kind %u is not taken by this backend]", o.kind);
                 return B2_DECLINED;
@@ -399,6 +412,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1);
     PLAN_CUDA(cudaMalloc((void**)&p->words_, n_words * 4), "cudaMalloc(step words)");
     PLAN_CUDA(cudaMemset(p->words_, 0, n_words * 4), "cudaMemset(step words)");
+    if (p->has_exchange_) {
+        PLAN_CUDA(cudaMalloc((void**)&p->xflags_, 32 * 4), "cudaMalloc(exchange flags)");
+        PLAN_CUDA(cudaMemset(p->xflags_, 0, 32 * 4), "cudaMemset(exchange flags)");
+    }
     p->sp_ = p->words_;
     p->status_ = p->words_ + 4;
     p->argmax_counter_ = p->words_ + 5;
@@ -469,6 +486,9 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
                 e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st, pdl);
                 break;
             case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st, pdl); break;
+            case B2_OP_EXCHANGE:
+                if (attached_) e = launch_exchange(peers_, o.off, o.n, xflags_, status_, st, pdl);  // the first pass of a lone rank has nobody to meet
+                break;
             default: e = cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) {
@@ -521,7 +541,8 @@ int DecodePlanImpl::check_status(std::string& err) {
     if (s) {
         cudaMemset(status_, 0, 4);
         cudaMemset(att_counters_, 0, 4 * kv_.size());  // a CTA that gave up never counted itself
-        err = "[b200qmm: plan: an attention kernel's wait on its copy ran into the time limit]";
+        err = s == 4 ? "[b200qmm: plan: a peer did not arrive at an exchange within the time limit]"
+                     : "[b200qmm: plan: an attention kernel's wait on its copy ran into the time limit]";
         return B2_ERR_TIMEOUT;
     }
     return B2_OK;
@@ -538,6 +559,10 @@ int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const floa
     }
     if (logits && !n_logits_) {
         err = "[b200qmm: plan step: the graph has no logits]";
+        return B2_ERR_ARG;
+    }
+    if (has_exchange_ && !attached_) {
+        err = "[b200qmm: plan step: a tensor-parallel plan needs its peers first (b2_plan_attach_peers)]";
         return B2_ERR_ARG;
     }
     PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos, (uint32_t)pos, 0, nullptr, 0, st), "set_step");
@@ -604,6 +629,10 @@ int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const Weigh
                   n_tokens, pos0, max_len_);
         return B2_ERR_ARG;
     }
+    if (has_exchange_ && !attached_) {
+        err = "[b200qmm: plan generate: a tensor-parallel plan needs its peers first (b2_plan_attach_peers)]";
+        return B2_ERR_ARG;
+    }
     if (embed.n_in != n_input_ || first_token < 0 || (size_t)first_token >= embed.n_out) {
         err = "[b200qmm: plan generate: the embedding matrix does not match the graph's input, or the token is outside it]";
         return B2_ERR_ARG;
@@ -646,6 +675,50 @@ int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const Weigh
     return check_status(err);
 }
 
+
+// ---- tensor-parallel plans: peers ------------------------------------------------------------------------------------
+int DecodePlanImpl::export_handle(void* out128, std::string& err) {
+    if (!has_exchange_) {
+        err = "[b200qmm: plan export: the graph has no exchange op]";
+        return B2_ERR_ARG;
+    }
+    cudaIpcMemHandle_t h[2];
+    static_assert(sizeof h == B2_PLAN_HANDLE_BYTES, "handle size");
+    PLAN_CUDA(cudaIpcGetMemHandle(&h[0], bufs_), "cudaIpcGetMemHandle(buffers)");
+    PLAN_CUDA(cudaIpcGetMemHandle(&h[1], xflags_), "cudaIpcGetMemHandle(flags)");
+    memcpy(out128, h, sizeof h);
+    return B2_OK;
+}
+
+int DecodePlanImpl::attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err) {
+    if (!has_exchange_ || attached_ || world < 2 || world > 8 || rank >= world || !handles) {
+        err = "[b200qmm: plan attach: needs a graph with exchange ops, 2 to 8 ranks, and is done once]";
+        return B2_ERR_ARG;
+    }
+    peers_.rank = rank;
+    peers_.world = world;
+    for (uint32_t p = 0; p < world; p++) {
+        if (p == rank) {
+            peers_.base[p] = bufs_;
+            peers_.flags[p] = xflags_;
+            continue;
+        }
+        cudaIpcMemHandle_t h[2];
+        memcpy(h, (const char*)handles + (size_t)p * B2_PLAN_HANDLE_BYTES, sizeof h);
+        void *b = nullptr, *f = nullptr;
+        PLAN_CUDA(cudaIpcOpenMemHandle(&b, h[0], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(buffers)");
+        peer_maps_.push_back(b);
+        PLAN_CUDA(cudaIpcOpenMemHandle(&f, h[1], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(flags)");
+        peer_maps_.push_back(f);
+        peers_.base[p] = (float*)b;
+        peers_.flags[p] = (uint32_t*)f;
+    }
+    attached_ = true;
+    // the step graph captured at creation has no exchange nodes: capture it again
+    if (step_exec_) cudaGraphExecDestroy(step_exec_);
+    step_exec_ = nullptr;
+    return capture(cap_stream_, false, &step_exec_, err);
+}
 
 // ---- the persistent token kernel -----------------------------------------------------------------------------
 // The program: ops_ in order, a planes-staging step in front of every product whose vector is not the one already in

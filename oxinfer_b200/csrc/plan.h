@@ -24,6 +24,8 @@ class DecodePlanImpl {
     int kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err);
     int generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
                  const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err);
+    int export_handle(void* out128, std::string& err);
+    int attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err);
     uint64_t launches_per_step() const { return tk_ok_ ? 1 : (uint64_t)ops_.size(); }
     bool token_kernel() const { return tk_ok_; }
     bool uses_weight(uint64_t h) const;
@@ -43,6 +45,7 @@ class DecodePlanImpl {
         uint32_t kv = 0;
         uint32_t n = 0;
         int gelu = 0;
+        size_t off = 0;  // EXCHANGE: offset of the vector in the activation block, in floats
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
     };
     DecodePlanImpl() = default;
@@ -57,6 +60,11 @@ class DecodePlanImpl {
     std::vector<uint64_t> weight_handles_;
     int sm_count_ = 148;
     bool pdl_ = true;  // programmatic dependent launch between the kernels of a step (B2_PLAN_PDL=0 switches it off)
+    // tensor-parallel plans
+    bool has_exchange_ = false, attached_ = false;
+    PeerSet peers_{};
+    uint32_t* xflags_ = nullptr;  // this rank's flag words
+    std::vector<void*> peer_maps_;  // what cudaIpcOpenMemHandle returned
     bool fuse_ = true;  // q / k / v style products of one vector as one launch over concatenated rows (B2_PLAN_FUSE=0: off)
     std::vector<void*> fused_;  // device copies made for that
     // one allocation each

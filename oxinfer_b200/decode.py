@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 from . import _lib
-from ._lib import MODE_ADD, MODE_SILU_PAIR, MODE_STORE, OP_ATTEND, OP_GLU, OP_LINEAR, OP_NORM, OP_QK_ROPE
+from ._lib import MODE_ADD, MODE_SILU_PAIR, MODE_STORE, OP_ATTEND, OP_EXCHANGE, OP_GLU, OP_LINEAR, OP_NORM, OP_QK_ROPE, PLAN_HANDLE_BYTES
 
 
 @dataclass(frozen=True)
@@ -89,6 +89,11 @@ class Graph:
     def glu(self, g: View, u: View, out: View, n: int, gelu: bool = False) -> None:
         self.ops.append(_lib.Op(kind=OP_GLU, x=g.c(), z=u.c(), y=out.c(), n=n, gelu=int(gelu)))
 
+    def exchange(self, x: View, n: int) -> None:
+        """Tensor-parallel plans (no counterpart in the reference): every rank wrote its equal contiguous part of the
+        ``n`` values at ``x``; afterwards every rank holds all of them."""
+        self.ops.append(_lib.Op(kind=OP_EXCHANGE, x=x.c(), n=n))
+
 
 class DecodePlan:
     """``DecodePlan`` (``src/gpu_decode.rs:538-587``) over the plan's own device KV caches."""
@@ -106,6 +111,19 @@ class DecodePlan:
         n = C.c_uint64()
         self._be._check(self._be._L.b2_plan_launches(self._be._ctx, self.handle, C.byref(n)))
         return n.value
+
+    # -- tensor-parallel plans: one process per GPU, the same graph over each rank's weight shards -------------------
+    def export_handle(self) -> bytes:
+        """What the other ranks need to reach this plan's activation memory (pass it by any host-side means)."""
+        buf = C.create_string_buffer(PLAN_HANDLE_BYTES)
+        self._be._check(self._be._L.b2_plan_export(self._be._ctx, self.handle, buf))
+        return buf.raw
+
+    def attach_peers(self, rank: int, world: int, handles: list) -> None:
+        """``handles``: every rank's ``export_handle()`` in rank order. Steps are collective from here on."""
+        assert len(handles) == world and all(len(h) == PLAN_HANDLE_BYTES for h in handles)
+        blob = b"".join(handles)
+        self._be._check(self._be._L.b2_plan_attach_peers(self._be._ctx, self.handle, rank, world, blob))
 
     def step(self, pos: int, x: np.ndarray, rope_cs: np.ndarray, want_logits: bool = True):
         """One token: returns (hidden, logits or None); raises on error (there is no CPU path here)."""
@@ -196,17 +214,25 @@ class LlamaConfig:
         return float(np.float32(1.0) / np.sqrt(np.float32(self.hd)))
 
 
-def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head) -> Graph:
+def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, rank: int = 0, world: int = 1) -> Graph:
     """``layers``: per layer a dict with device weights ``q k v o gate up down`` and f32 arrays ``ln_pre ln_post``.
-    Ten ops per layer (norm, q, k, v, qk-rope, attend, o, norm, gate+up pair, down), then the final norm and the head."""
+    Ten ops per layer (norm, q, k, v, qk-rope, attend, o, norm, gate+up pair, down), then the final norm and the head.
+
+    ``world > 1`` builds rank ``rank``'s graph of a tensor-parallel plan: every weight is this rank's ROW shard
+    (``shard_rows``: q / k / v by head, o / gate / up / down / head by equal row ranges), activations are replicated,
+    and an exchange follows every sharded product whose output the next op needs in full (attention outputs, both
+    residual updates, the MLP activations, the logits). Every output row is computed by the same kernel over the
+    same inputs as on one GPU, so the results are bit-identical to the single-GPU plan."""
     g = Graph()
-    h, nh, nkv, hd = cfg.h, cfg.nh, cfg.nkv, cfg.hd
+    h, hd = cfg.h, cfg.hd
+    assert cfg.nh % world == 0 and cfg.nkv % world == 0 and h % (32 * world) == 0 and cfg.inter % (32 * world) == 0 and cfg.vocab % (32 * world) == 0
+    nh, nkv = cfg.nh // world, cfg.nkv // world          # this rank's heads
     qw = nh * hd
     x = g.buf(h)
     hn = g.buf(h)
     qkv = g.buf(qw + 2 * nkv * hd)
     qo = g.buf(nh * hd)
-    att = g.buf(nh * hd)
+    att = g.buf(cfg.nh * hd)
     act = g.buf(cfg.inter)
     act2 = g.buf(cfg.inter)
     hidden = g.buf(h)
@@ -214,6 +240,7 @@ def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head) ->
     g.input, g.n_input = x, h
     g.hidden, g.n_hidden = hidden, h
     g.rope_halves = [hd // 2]
+    hs, ins, vs = h // world, cfg.inter // world, cfg.vocab // world   # row shares
     for L in layers:
         slot = len(g.kv)
         g.kv.append((nkv, hd))
@@ -222,17 +249,43 @@ def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head) ->
         g.linear(L["k"], hn, qkv.at(qw))
         g.linear(L["v"], hn, qkv.at(qw + nkv * hd))
         g.qk_rope(qkv, qo, slot, nh, nkv, hd, hd // 2, qw, qw + nkv * hd, cfg.rope_interleaved, cfg.eps)
-        g.attend(qo, att, slot, nh, nkv, hd, cfg.scale)
-        g.linear(L["o"], att, x, MODE_ADD)
+        g.attend(qo, att.at(rank * qw), slot, nh, nkv, hd, cfg.scale)
+        if world > 1:
+            g.exchange(att, cfg.nh * hd)
+        g.linear(L["o"], att, x.at(rank * hs), MODE_ADD)
+        if world > 1:
+            g.exchange(x, h)
         g.norm(x, hn, L["ln_post"], h, cfg.eps)
         if L["gate"].fmt == L["up"].fmt:   # pairable (src/gpu_decode.rs pairable)
-            g.linear(L["gate"], hn, act, MODE_SILU_PAIR, dev2=L["up"])
+            g.linear(L["gate"], hn, act.at(rank * ins), MODE_SILU_PAIR, dev2=L["up"])
         else:
-            g.linear(L["gate"], hn, act2)
-            g.linear(L["up"], hn, act)
-            g.glu(act2, act, act, cfg.inter)
-        g.linear(L["down"], act, x, MODE_ADD)
+            g.linear(L["gate"], hn, act2.at(rank * ins))
+            g.linear(L["up"], hn, act.at(rank * ins))
+            g.glu(act2.at(rank * ins), act.at(rank * ins), act.at(rank * ins), ins)
+        if world > 1:
+            g.exchange(act, cfg.inter)
+        g.linear(L["down"], act, x.at(rank * hs), MODE_ADD)
+        if world > 1:
+            g.exchange(x, h)
     g.norm(x, hidden, final_norm, h, cfg.eps)
-    g.linear(head, hidden, logits)
+    g.linear(head, hidden, logits.at(rank * vs))
+    if world > 1:
+        g.exchange(logits, cfg.vocab)
     g.logits = (logits, cfg.vocab)
     return g
+
+
+def shard_llama(be, layers: list, head, cfg: LlamaConfig, rank: int, world: int):
+    """Row shards of uploaded full matrices for rank ``rank`` (views into the same uploads): q / k / v by head, the rest
+    by equal row ranges. Returns (layers, head) for ``llama_graph(..., rank, world)``."""
+    def rows(dev, n):
+        per = n // world
+        return be.shard_rows(dev, rank * per, (rank + 1) * per)
+
+    out = []
+    for L in layers:
+        S = {"ln_pre": L["ln_pre"], "ln_post": L["ln_post"]}
+        for name in ("q", "k", "v", "o", "gate", "up", "down"):
+            S[name] = rows(L[name], L[name].n_out)
+        out.append(S)
+    return out, rows(head, head.n_out)
