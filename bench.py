@@ -213,7 +213,7 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
     return out
 
 
-def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0):
+def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0, rank=0, world=1, dist=None):
     """Config 2: greedy decode tok/s of a Llama-style decoder (hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab
     128256; Q4_K body, Q6_K head, Q8_0 embeddings) after a `ctx`-token cache, batch 1, through the decode plan
     (one CUDA graph launch per token, embedding lookup and argmax on the device). Random-init weights; every layer
@@ -234,18 +234,28 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     dhead = be.upload(head, cfg["vocab"], cfg["h"])
     dembed = be.upload(embed, cfg["vocab"], cfg["h"])
     lc = D.LlamaConfig(eps=1e-5, rope_theta=500000.0, rope_interleaved=True, **cfg)
-    g = D.llama_graph(lc, dev_layers, final_norm, dhead)
+    head_bytes = dhead.bytes()
+    if world > 1:   # tensor parallel: this rank's row shards, activations exchanged by peer stores
+        dev_layers, dhead_r = D.shard_llama(be, dev_layers, dhead, lc, rank, world)
+        g = D.llama_graph(lc, dev_layers, final_norm, dhead_r, rank, world)
+    else:
+        g = D.llama_graph(lc, dev_layers, final_norm, dhead)
     max_len = ctx + n_tokens
     plan = D.decode_plan(be, g, max_len, kv_f16=kv_f16)
     if plan is None:
         raise RuntimeError("decode plan declined: " + be.last_declined)
+    if world > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, plan.export_handle())
+        plan.attach_peers(rank, world, handles)
     rng = np.random.default_rng(7)
     row = cfg["nkv"] * cfg["hd"]
+    per = row // world
     kv_rows = []
-    for li in range(n_layers):   # the prefilled cache: unit-variance keys and values
+    for li in range(n_layers):   # the prefilled cache: unit-variance keys and values (a rank keeps its KV heads' columns)
         k = rng.standard_normal((ctx, row), dtype=np.float32)
         v = rng.standard_normal((ctx, row), dtype=np.float32)
-        plan.kv_write(li, 0, k, v)
+        plan.kv_write(li, 0, np.ascontiguousarray(k[:, rank * per:(rank + 1) * per]), np.ascontiguousarray(v[:, rank * per:(rank + 1) * per]))
         if cpu_tokens and li == 0:
             kv_rows = [k, v]
     inv_freq = D.rope_inv_freq(cfg["hd"], lc.rope_theta)
@@ -253,16 +263,25 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     plan.generate(dembed, 1, ctx, min(8, n_tokens), table[: min(8, n_tokens)])    # warm-up (captures the graph)
     times = []
     for _ in range(3):
+        if world > 1:
+            dist.barrier()
         toks, ms = plan.generate(dembed, 1, ctx, n_tokens, table)
+        if world > 1:   # the slowest rank's device time
+            import torch
+
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
         times.append(ms)
     ms = sorted(times)[1]
     kv_el = 2 if kv_f16 else 4
     kv_bytes = n_layers * 2 * (ctx + (n_tokens + 1) / 2) * row * kv_el
-    algo = wbytes + dhead.bytes() + cfg["h"] * 34 // 32 + kv_bytes
-    out = {"tok_s": n_tokens / (ms * 1e-3), "ms_per_token": ms / n_tokens, "tokens": n_tokens, "context": ctx, "layers": n_layers,
+    algo = wbytes + head_bytes + cfg["h"] * 34 // 32 + kv_bytes   # whole job (all ranks together)
+    out = {"tok_s": n_tokens / (ms * 1e-3), "ms_per_token": ms / n_tokens, "tokens": n_tokens, "context": ctx, "layers": n_layers, "n_gpus": world,
+           "parallelism": f"tp{world}: row shards, 4 exchanges per layer by peer stores over NVLink" if world > 1 else "single GPU",
            "kv_cache": "f16" if kv_f16 else "f32", "launches_per_token": plan.launches_per_step() + 2,
            "bytes_per_token": int(algo), "gbs": algo / (ms / n_tokens * 1e-3) / 1e9,
-           "frac_of_hbm_peak": algo / (ms / n_tokens * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "frac_of_hbm_peak": algo / (ms / n_tokens * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
            "distinct_tokens": int(len(set(toks.tolist()))), "timing": "CUDA events around the token loop, median of 3"}
     if cpu_tokens:
         # the reference's CPU decode path (oracle port) on the same model: a few tokens at the same context
@@ -307,7 +326,12 @@ def run_b200(args, rank, world, local_rank):
         print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}), flush=True)
         return
     if args.section == "decode":
-        print(json.dumps({"extra": {"decode": decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16)}}), flush=True)
+        d = decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
+        if rank == 0:
+            print(json.dumps({"extra": {"decode": d}}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     assert N_OUT % world == 0
     n_local = N_OUT // world
@@ -392,6 +416,12 @@ def run_b200(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms_total, kern_ms = (float(v) for v in t.cpu())
 
+    dec_tp = None
+    if world > 1 and args.section == "all":   # collective: every rank runs the tensor-parallel decode plan
+        try:
+            dec_tp = decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist)
+        except Exception as e:
+            dec_tp = {"error": str(e)}
     if rank == 0:
         ms = ms_total / args.steps
         value = FLOP_PER_STEP / (ms * 1e-3) / 1e12
@@ -430,6 +460,8 @@ def run_b200(args, rank, world, local_rank):
                 line["extra"]["decode"] = decode_extras(be, peaks, cpu_tokens=2)
             except Exception as e:
                 line["extra"]["decode_error"] = str(e)
+        if dec_tp is not None:
+            line["extra"] = {"decode": dec_tp}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
