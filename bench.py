@@ -213,6 +213,89 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
     return out
 
 
+def moe_extras(be, torch, peaks):
+    """Config 3: the routed-expert layer (128 experts, top-8, hidden 2048, expert intermediate 768, MLX 4-bit g64) at token
+    batches 1 / 64 / 512 / 4096, x and y on the device, routes on the host as in Backend::moe. Router logits N(0,1) plus a
+    per-expert bias N(0,1) (skewed load), softmax over the 8 chosen. Eight distinct random experts are uploaded 16 times each
+    (generation time only; every expert has its own device memory)."""
+    import numpy as np
+
+    from oxinfer_b200 import synth
+
+    E, K, H, I = 128, 8, 2048, 768
+    protos = [(synth.mlx4(2 * I, H, 900 + i), synth.mlx4(H, I, 950 + i)) for i in range(8)]
+    gu = [be.upload(protos[e % 8][0], 2 * I, H) for e in range(E)]
+    dn = [be.upload(protos[e % 8][1], H, I) for e in range(E)]
+    moe = be.upload_moe(gu, dn, H, I)
+    if moe is None:
+        raise RuntimeError("upload_moe declined: " + be.last_declined)
+    wbytes = sum(d.bytes() for d in gu) + sum(d.bytes() for d in dn)
+    for d in gu + dn:
+        d.free()
+    rng = np.random.default_rng(3)
+    bias = rng.standard_normal(E).astype(np.float32)
+    out = {}
+    for t in (1, 64, 512, 4096):
+        logits = rng.standard_normal((t, E)).astype(np.float32) + bias
+        ids = np.argsort(-logits, axis=1, kind="stable")[:, :K].astype(np.int32)
+        top = np.take_along_axis(logits, ids, axis=1)
+        w = np.exp(top - top[:, :1])
+        w = (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
+        x = torch.randn((t, H), device="cuda", dtype=torch.float32)
+        y = torch.zeros((t, H), device="cuda", dtype=torch.float32)
+        for _ in range(2):
+            be.moe_dev(x, ids, w, moe, y)
+        torch.cuda.synchronize()
+        be.check_status()
+        n = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            be.moe_dev(x, ids, w, moe, y)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        flop = 6.0 * t * K * H * I
+        touched = len(np.unique(ids)) / E * wbytes
+        out[f"t{t}"] = {"us": us, "tflops": flop / us / 1e6, "experts_touched": int(len(np.unique(ids))), "weight_gbs": touched / us / 1e3,
+                        "frac_of_hbm_peak": touched / us / 1e3 / peaks["hbm_gbs"], "frac_of_bf16_peak": flop / us / 1e6 / peaks["bf16_tflops"]}
+    out["note"] = "b2_moe_dev per call: host segment building + gather, grouped tensor-core GEMM (gate_up), SiLU, grouped GEMM (down), combine"
+    return out
+
+
+def fp8_extras(be, torch, peaks):
+    """Config 4: FP8 e4m3 128x128-block-scaled weights N=28672 x K=12288, f16 activations on the device, M = 128 and 8192
+    through the tensor-core GEMM (M = 1 is the f8 case of extra.gemv at another shape). FP8 keeps the reference's
+    semantics: e4m3 weight times block scale against unquantized activations, f32 accumulation."""
+    from oxinfer_b200 import synth
+
+    n_out, n_in = 28672, 12288
+    ref = synth.f8_e4m3(n_out, n_in, 1)
+    dev = be.upload(ref, n_out, n_in)
+    out = {}
+    for t in (128, 8192):
+        xd = torch.randn((t, n_in), device="cuda", dtype=torch.float16)
+        y = torch.empty((t, n_out), device="cuda", dtype=torch.float32)
+        for _ in range(2):
+            be.matmul_dev(dev, xd, y)
+        torch.cuda.synchronize()
+        be.check_status()
+        n = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            be.matmul_dev(dev, xd, y)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        flop = 2.0 * t * n_in * n_out
+        out[f"m{t}"] = {"us": us, "tflops": flop / us / 1e6, "frac_of_bf16_peak": flop / us / 1e6 / peaks["bf16_tflops"],
+                        "weight_gbs": n_out * n_in / us / 1e3, "frac_of_hbm_peak": n_out * n_in / us / 1e3 / peaks["hbm_gbs"]}
+        del xd, y
+    dev.free()
+    return out
+
+
 def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0, rank=0, world=1, dist=None):
     """Config 2: greedy decode tok/s of a Llama-style decoder (hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab
     128256; Q4_K body, Q6_K head, Q8_0 embeddings) after a `ctx`-token cache, batch 1, through the decode plan
@@ -324,6 +407,10 @@ def run_b200(args, rank, world, local_rank):
 
     if args.section == "gemv":
         print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}), flush=True)
+        return
+    if args.section in ("moe", "fp8"):
+        fn = moe_extras if args.section == "moe" else fp8_extras
+        print(json.dumps({"extra": {args.section: fn(be, torch, peaks)}}), flush=True)
         return
     if args.section == "decode":
         d = decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
@@ -456,10 +543,12 @@ def run_b200(args, rank, world, local_rank):
                 line["extra"] = {"gemv": gemv_extras(be, torch, peaks, 40)}
             except Exception as e:  # the headline line must still print
                 line["extra"] = {"gemv_error": str(e)}
-            try:
-                line["extra"]["decode"] = decode_extras(be, peaks, cpu_tokens=2)
-            except Exception as e:
-                line["extra"]["decode_error"] = str(e)
+            for name, fn in (("moe", lambda: moe_extras(be, torch, peaks)), ("fp8", lambda: fp8_extras(be, torch, peaks)),
+                             ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2))):
+                try:
+                    line["extra"][name] = fn()
+                except Exception as e:
+                    line["extra"][name + "_error"] = str(e)
         if dec_tp is not None:
             line["extra"] = {"decode": dec_tp}
         print(json.dumps(line), flush=True)
@@ -479,7 +568,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")
     ap.add_argument("--tokens", type=int, default=256, help="with --section decode: tokens to generate")
     ap.add_argument("--kv-f16", action="store_true", help="with --section decode: f16 KV caches instead of the reference's f32")
-    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode"],
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "moe", "fp8"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

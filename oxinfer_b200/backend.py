@@ -252,6 +252,13 @@ class Backend:
         assert x.shape == (t, dev.h) and y.shape == (t, dev.h) and y.dtype == np.float32 and y.flags["C_CONTIGUOUS"]
         return self._check(self._L.b2_moe(self._ctx, dev.handle, _ptr(x), t, _ptr(ids), _ptr(w), k, _ptr(y)))
 
+    def moe_dev(self, x, routes_ids: np.ndarray, routes_w: np.ndarray, dev: "MoeWeights", y) -> bool:
+        """``moe`` with x and y resident on the device (torch tensors); the routes stay host arrays. Not synchronized."""
+        ids = np.ascontiguousarray(routes_ids, dtype=np.int32)
+        w = np.ascontiguousarray(routes_w, dtype=np.float32)
+        t, k = ids.shape
+        return self._check(self._L.b2_moe_dev(self._ctx, dev.handle, _ptr(x), t, _ptr(ids), _ptr(w), k, _ptr(y)))
+
     def route_topk_dev(self, logits, k: int, ids, w) -> bool:
         t, n = logits.shape
         return self._check(self._L.b2_route_topk_dev(self._ctx, _ptr(logits), t, n, k, _ptr(ids), _ptr(w)))
