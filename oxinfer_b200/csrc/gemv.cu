@@ -18,8 +18,10 @@
 #include <cuda_fp8.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "gemv_core.cuh"
+#include "gemv_ring.cuh"
 
 namespace b2 {
 
@@ -48,7 +50,7 @@ template <class F, bool PAIR, bool XF32>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
             const float* __restrict__ gate) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     const int K = (int)w.n_in;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,6 +125,77 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
     }
 }
 
+// The 4-bit formats: the same products with the weights brought in by bulk copies into per-warp rings (gemv_ring.cuh).
+// The first copies are issued before the kernel waits for the one ahead of it in the stream.
+constexpr int RING_SLOTS = 3;
+constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
+
+template <class F, bool PAIR>
+__global__ void __launch_bounds__(GEMV_THREADS, 3)
+gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bars[GEMV_WARPS * RING_SLOTS];
+    pdl_launch_dependents();
+    const int K = (int)w.n_in;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int RW = PAIR ? 1 : 2;
+    const size_t r_first = ((size_t)warp * gridDim.x + blockIdx.x) * RW, r_step = (size_t)gridDim.x * GEMV_WARPS * RW;
+    const size_t planes_bytes = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
+    WarpRing ring;
+    ring.S = RING_SLOTS;
+    ring.slots = smem + planes_bytes + (size_t)warp * RING_SLOTS * RING_SLOT_BYTES;
+    ring.bars = bars + warp * RING_SLOTS;
+    ring.phases = 0;
+    if (lane == 0) {
+        for (int sl = 0; sl < RING_SLOTS; sl++) acopy::bar_init(&ring.bars[sl], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        ring_prime<PAIR>(w, w2, ring, r_first, r_step);
+    }
+    pdl_wait();
+    // the planes of x (written by the kernel ahead) -> shared memory, slots permuted as in gemv_kernel
+    {
+        const int slots = K / 16;
+        const uint4* src = (const uint4*)xp.planes;
+        uint4* dst = (uint4*)smem;
+        for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
+            int p = i / slots, g = i - p * slots;
+            dst[p * slots + swz(g)] = src[i];
+        }
+        float2* sx = (float2*)(smem + 3 * (size_t)K);
+        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
+        int32_t* v16 = (int32_t*)(sx + K / 32);
+        for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xp.v16[b];
+    }
+    __syncthreads();
+    XS xs;
+    xs.K = K;
+    xs.p0 = smem;
+    xs.sx = (const float2*)(smem + 3 * (size_t)K);
+    xs.v16 = (const int32_t*)(xs.sx + K / 32);
+    xs.xf = nullptr;
+    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true) && status) atomicExch(status, 5u);
+}
+
+template <class F>
+cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
+                        cudaStream_t st, bool pdl) {
+    const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
+    auto kern = pair ? gemv4_ring_kernel<F, true> : gemv4_ring_kernel<F, false>;
+    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + RING_BYTES;
+    static size_t smem_set[2] = {48 * 1024, 48 * 1024};
+    if (smem > smem_set[pair]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set[pair] = smem;
+    }
+    const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
+    const size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
+    size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+    const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr);
+}
+
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                        int sm_count, cudaStream_t st, bool pdl) {
@@ -163,6 +236,17 @@ cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t s
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl) {
+    static const bool ring = [] {
+        const char* e = getenv("B2_GEMV_RING");
+        return !e || atoi(e) != 0;
+    }();
+    // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
+    // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
+    // 11.2 us against 12.5), so plain launches keep it.
+    if (ring && pdl && (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024) {
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl);
+    }
     switch (w.fmt) {
         case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
         case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);

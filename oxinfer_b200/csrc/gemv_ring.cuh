@@ -28,40 +28,56 @@ __device__ __forceinline__ void q4_load_smem(const uint8_t* row_chunk, int lane,
     r.q1 = *(const uint4*)(blk + 32 + 32 * (lane & 3));
 }
 
+// The copies of step s of a warp's row sequence (one lane calls it).
+template <bool PAIR>
+__device__ __forceinline__ void ring_issue(const WeightDev& w, const WeightDev& w2, const WarpRing& ring, size_t r_first, size_t r_step, uint32_t s) {
+    using namespace acopy;
+    const int nblk = (int)w.n_in / 256, iters = (nblk + 7) / 8;
+    const size_t row_bytes = (size_t)nblk * 144, n_out = w.n_out;
+    const uint32_t pair = s / (uint32_t)iters, it = s - pair * (uint32_t)iters;
+    const size_t r0 = r_first + (size_t)pair * r_step;
+    const size_t rowB = PAIR ? r0 : min(r0 + 1, n_out - 1);
+    const uint32_t bytes = (uint32_t)min(8, nblk - (int)it * 8) * 144u;
+    const int slot = (int)(s % (uint32_t)ring.S);
+    uint8_t* dst = ring.slots + slot * RING_SLOT_BYTES;
+    bar_expect_tx(&ring.bars[slot], 2 * bytes);
+    bulk_load(dst, w.p0 + r0 * row_bytes + (size_t)it * RING_ROW_BYTES, bytes, &ring.bars[slot]);
+    bulk_load(dst + RING_ROW_BYTES, (PAIR ? w2.p0 : w.p0) + rowB * row_bytes + (size_t)it * RING_ROW_BYTES, bytes, &ring.bars[slot]);
+}
+
+// How many steps a warp's sequence has.
+__device__ __forceinline__ uint32_t ring_steps(const WeightDev& w, size_t r_first, size_t r_step) {
+    const int nblk = (int)w.n_in / 256, iters = (nblk + 7) / 8;
+    const uint32_t npairs = r_first < w.n_out ? (uint32_t)((w.n_out - r_first + r_step - 1) / r_step) : 0;
+    return npairs * (uint32_t)iters;
+}
+
+// The first S - 1 steps' copies (one lane). A kernel may call this before it waits for the kernel ahead of it: the
+// weights do not depend on that kernel. gemv4_ring is then told that the ring is primed.
+template <bool PAIR>
+__device__ __forceinline__ void ring_prime(const WeightDev& w, const WeightDev& w2, const WarpRing& ring, size_t r_first, size_t r_step) {
+    const uint32_t T = ring_steps(w, r_first, r_step);
+    for (uint32_t s = 0; s + 1 < (uint32_t)ring.S && s < T; s++) ring_issue<PAIR>(w, w2, ring, r_first, r_step, s);
+}
+
 // Rows r_first, r_first + r_step, ... (pairs of rows, or the same row of w and w2 with PAIR) by one warp.
 // False: a wait on a copy ran into its limit (the caller reports it and stops).
 template <class F, bool PAIR>
 __device__ __forceinline__ bool gemv4_ring(const WeightDev& w, const WeightDev& w2, const XS& xs, float* __restrict__ y, const int mode,
                                            const float* __restrict__ gate, WarpRing& ring, const size_t r_first, const size_t r_step,
-                                           const int lane) {
+                                           const int lane, const bool primed = false) {
     using namespace acopy;
     const int K = (int)w.n_in, nblk = K / 256, iters = (nblk + 7) / 8;
     const size_t n_out = w.n_out;
-    const size_t row_bytes = (size_t)nblk * 144;
-    const uint32_t npairs = r_first < n_out ? (uint32_t)((n_out - r_first + r_step - 1) / r_step) : 0;
-    const uint32_t T = npairs * (uint32_t)iters;
+    const uint32_t T = ring_steps(w, r_first, r_step);
     const int S = ring.S;
-    const uint8_t* pa = w.p0;
-    const uint8_t* pb = PAIR ? w2.p0 : w.p0;
-    auto issue = [&](uint32_t s) {  // one lane
-        const uint32_t pair = s / (uint32_t)iters, it = s - pair * (uint32_t)iters;
-        const size_t r0 = r_first + (size_t)pair * r_step;
-        const size_t rowB = PAIR ? r0 : min(r0 + 1, n_out - 1);
-        const uint32_t bytes = (uint32_t)min(8, nblk - (int)it * 8) * 144u;
-        const int slot = (int)(s % (uint32_t)S);
-        uint8_t* dst = ring.slots + slot * RING_SLOT_BYTES;
-        bar_expect_tx(&ring.bars[slot], 2 * bytes);
-        bulk_load(dst, pa + r0 * row_bytes + (size_t)it * RING_ROW_BYTES, bytes, &ring.bars[slot]);
-        bulk_load(dst + RING_ROW_BYTES, pb + rowB * row_bytes + (size_t)it * RING_ROW_BYTES, bytes, &ring.bars[slot]);
-    };
-    if (lane == 0)
-        for (uint32_t s = 0; s + 1 < (uint32_t)S && s < T; s++) issue(s);
+    if (lane == 0 && !primed) ring_prime<PAIR>(w, w2, ring, r_first, r_step);
     float accA = 0.0f, accB = 0.0f;
     uint32_t it = 0;
     size_t r0 = r_first;
     for (uint32_t s = 0; s < T; s++) {
         __syncwarp();  // every lane is done with the slot that is refilled now
-        if (lane == 0 && s + (uint32_t)S - 1 < T) issue(s + (uint32_t)S - 1);
+        if (lane == 0 && s + (uint32_t)S - 1 < T) ring_issue<PAIR>(w, w2, ring, r_first, r_step, s + (uint32_t)S - 1);
         const int slot = (int)(s % (uint32_t)S);
         if (!bar_wait(&ring.bars[slot], (ring.phases >> slot) & 1u, RING_WAIT_LIMIT)) return false;
         ring.phases ^= 1u << slot;
