@@ -54,6 +54,13 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {  // streamed once: 
     return v;
 }
 
+// A small non-negative integer (< 2^23) as a float without the conversion unit: the integer becomes the mantissa of
+// 2^23 + n, and subtracting 2^23 is exact. (Integer-to-float conversions run on a quarter-rate pipe that the
+// sub-block tails were saturating.)
+__device__ __forceinline__ float small_uint_to_float(uint32_t n) { return __uint_as_float(0x4B000000u | n) - 8388608.0f; }
+// The same for a signed byte value in -128 .. 127 held in the low 8 bits of `b`.
+__device__ __forceinline__ float int8_to_float(uint32_t b) { return __uint_as_float(0x4B000000u | ((b ^ 0x80u) & 0xffu)) - 8388736.0f; }
+
 __device__ __forceinline__ float silu(float a) { return a / (1.0f + __expf(-a)); }
 __device__ __forceinline__ float gelu_tanh(float a) {
     float t = 0.7978845608f * (a + 0.044715f * a * a * a);
@@ -117,10 +124,10 @@ struct FmtQ4K {
         const uint32_t a = (r.hdr.y >> sh) & 0xffffu, b = (r.hdr.z >> sh) & 0xffffu, c = (r.hdr.w >> sh) & 0xffffu;
         const uint32_t sc = (j < 2) ? (a & 0x3f3fu) : ((c & 0x0f0fu) | ((a >> 2) & 0x3030u));
         const uint32_t mn = (j < 2) ? (b & 0x3f3fu) : (((c >> 4) & 0x0f0fu) | ((b >> 2) & 0x3030u));
-        acc = fmaf((d * (float)(sc & 0xff)) * sx.x, (float)lo, acc);
-        acc = fmaf((d * (float)(sc >> 8)) * sx.z, (float)hi, acc);
-        acc = fmaf(-(dmin * (float)(mn & 0xff)), sx.y, acc);
-        acc = fmaf(-(dmin * (float)(mn >> 8)), sx.w, acc);
+        acc = fmaf((d * small_uint_to_float(sc & 0xff)) * sx.x, (float)lo, acc);
+        acc = fmaf((d * small_uint_to_float(sc >> 8)) * sx.z, (float)hi, acc);
+        acc = fmaf(-(dmin * small_uint_to_float(mn & 0xff)), sx.y, acc);
+        acc = fmaf(-(dmin * small_uint_to_float(mn >> 8)), sx.w, acc);
     }
     __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
         const int j = lane & 3;
@@ -217,8 +224,8 @@ struct FmtQ6K {
             }
             const int off32 = 32 * x.v16[k0 >> 4];
             const float xs = x.sx[k0 >> 5].x;
-            const float scale_a = (float)(int8_t)((sca >> (8 * (u + 2 * k4))) & 0xff);
-            const float scale_b = (float)(int8_t)((scb >> (8 * (u + 2 * k4))) & 0xff);
+            const float scale_a = int8_to_float((uint32_t)(sca >> (8 * (u + 2 * k4))));
+            const float scale_b = int8_to_float((uint32_t)(scb >> (8 * (u + 2 * k4))));
             accA = fmaf((da * scale_a) * xs, (float)(planes3(sa[0], sa[1], sa[2]) - off32), accA);
             accB = fmaf((db * scale_b) * xs, (float)(planes3(sb[0], sb[1], sb[2]) - off32), accB);
         }
