@@ -41,6 +41,22 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
     xplanes_block(x[warp * 32 + lane], warp, lane, K, out);
 }
 
+// planes(x * pre * w) without the norm factor, and each block's sum of squares of x * pre (see NormScale). A warp per block.
+__global__ void __launch_bounds__(256) norm_planes_kernel(const float* __restrict__ x, const float* __restrict__ w, float pre, int K, XPlanes out,
+                                                          float* __restrict__ partial) {
+    pdl_launch_dependents();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const float wv = (w && warp < K / 32) ? w[warp * 32 + lane] : 1.0f;  // the weights do not depend on the kernel ahead
+    pdl_wait();
+    if (warp >= K / 32) return;
+    const float v = x[warp * 32 + lane] * pre;
+    float s = v * v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) partial[warp] = s;
+    xplanes_block(v * wv, warp, lane, K, out);
+}
+
 // The kernel's order of events, chosen for back-to-back launches of a decode step:
 //   1. let the next kernel of the stream start launching (programmatic dependent launch),
 //   2. issue the loads of the warp's first weights, which depend on nothing the previous kernel wrote,
@@ -49,7 +65,7 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
 template <class F, bool PAIR, bool XF32>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
-            const float* __restrict__ gate) {
+            const float* __restrict__ gate, NormScale ns) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     const int K = (int)w.n_in;
@@ -95,6 +111,7 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
         xs.xf = nullptr;
     }
     __syncthreads();
+    const float kscale = norm_scale_factor(ns, lane);
     for (size_t r0 = r_first; r0 < n_out; r0 += r_step) {
         float accA = 0.0f, accB = 0.0f;
         for (int it = 0; it < iters; it++) {
@@ -102,8 +119,8 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
             if (it > 0 || r0 != r_first) fetch(r0, it);  // the first step's loads were issued before the wait
             F::dot2(na, nb, xs, it, lane, accA, accB);
         }
-        accA = warp_sum(accA);
-        accB = warp_sum(accB);
+        accA = warp_sum(accA) * kscale;
+        accB = warp_sum(accB) * kscale;
         if (lane == 0) {
             if (PAIR) {
                 y[r0] = (mode == B2_MODE_SILU_PAIR ? silu(accA) : gelu_tanh(accA)) * accB;
@@ -132,7 +149,8 @@ constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
 
 template <class F, bool PAIR>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
-gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status) {
+gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status,
+                  NormScale ns) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bars[GEMV_WARPS * RING_SLOTS];
     pdl_launch_dependents();
@@ -173,12 +191,13 @@ gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, 
     xs.sx = (const float2*)(smem + 3 * (size_t)K);
     xs.v16 = (const int32_t*)(xs.sx + K / 32);
     xs.xf = nullptr;
-    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true) && status) atomicExch(status, 5u);
+    const float kscale = norm_scale_factor(ns, lane);
+    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true, kscale) && status) atomicExch(status, 5u);
 }
 
 template <class F>
 cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                        cudaStream_t st, bool pdl) {
+                        cudaStream_t st, bool pdl, NormScale ns) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv4_ring_kernel<F, true> : gemv4_ring_kernel<F, false>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + RING_BYTES;
@@ -193,12 +212,12 @@ cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
     size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr);
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns);
 }
 
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                       int sm_count, cudaStream_t st, bool pdl) {
+                       int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
     size_t smem = XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in);
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, XF32> : gemv_kernel<F, false, XF32>;
@@ -213,7 +232,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate);
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns);
 }
 
 }  // namespace
@@ -234,8 +253,14 @@ cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t s
     return launch_k(xplanes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, (int)K, out);
 }
 
+cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl) {
+    if (K == 0 || K % 32) return cudaErrorInvalidValue;
+    unsigned warps = (unsigned)(K / 32);
+    return launch_k(norm_planes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, w, pre, (int)K, out, partial);
+}
+
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl) {
+                        int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
     static const bool ring = [] {
         const char* e = getenv("B2_GEMV_RING");
         return !e || atoi(e) != 0;
@@ -244,15 +269,15 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
     if (ring && pdl && (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024) {
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
     }
     switch (w.fmt) {
-        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
-        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
-        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
-        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
-        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl);
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
         default: return cudaErrorInvalidValue;
     }
 }

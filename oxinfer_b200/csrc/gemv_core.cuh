@@ -61,6 +61,17 @@ __device__ __forceinline__ float small_uint_to_float(uint32_t n) { return __uint
 // The same for a signed byte value in -128 .. 127 held in the low 8 bits of `b`.
 __device__ __forceinline__ float int8_to_float(uint32_t b) { return __uint_as_float(0x4B000000u | ((b ^ 0x80u) & 0xffu)) - 8388736.0f; }
 
+// The deferred norm factor (NormScale), computed by every warp for itself in the same order: lane-strided partial sums,
+// then a butterfly, so that all warps of all CTAs get the same bits.
+__device__ __forceinline__ float norm_scale_factor(const NormScale& ns, int lane) {
+    if (!ns.partial) return 1.0f;
+    float s = 0.0f;
+    for (uint32_t i = (uint32_t)lane; i < ns.count; i += 32) s += __ldcg(ns.partial + i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return 1.0f / sqrtf(s * ns.inv_n + ns.eps);
+}
+
 __device__ __forceinline__ float silu(float a) { return a / (1.0f + __expf(-a)); }
 __device__ __forceinline__ float gelu_tanh(float a) {
     float t = 0.7978845608f * (a + 0.044715f * a * a * a);

@@ -65,7 +65,7 @@ __device__ __forceinline__ void ring_prime(const WeightDev& w, const WeightDev& 
 template <class F, bool PAIR>
 __device__ __forceinline__ bool gemv4_ring(const WeightDev& w, const WeightDev& w2, const XS& xs, float* __restrict__ y, const int mode,
                                            const float* __restrict__ gate, WarpRing& ring, const size_t r_first, const size_t r_step,
-                                           const int lane, const bool primed = false) {
+                                           const int lane, const bool primed = false, const float kscale = 1.0f) {
     using namespace acopy;
     const int K = (int)w.n_in, nblk = K / 256, iters = (nblk + 7) / 8;
     const size_t n_out = w.n_out;
@@ -89,8 +89,8 @@ __device__ __forceinline__ bool gemv4_ring(const WeightDev& w, const WeightDev& 
             F::dot2(ra, rb, xs, (int)it, lane, accA, accB);
         }
         if (++it == (uint32_t)iters) {
-            accA = warp_sum(accA);
-            accB = warp_sum(accB);
+            accA = warp_sum(accA) * kscale;
+            accB = warp_sum(accB) * kscale;
             if (lane == 0) {
                 if (PAIR) {
                     y[r0] = (mode == B2_MODE_SILU_PAIR ? silu(accA) : gelu_tanh(accA)) * accB;

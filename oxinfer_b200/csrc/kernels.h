@@ -55,10 +55,22 @@ inline XPlanes xplanes_at(void* base, size_t K) {
     return p;
 }
 cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false);
+// A vector whose RMS-norm factor is applied after the product instead of before the split: the planes hold the split of
+// x * w (no factor), `partial` holds the sum of squares of every block of 32 of x, and the product kernel multiplies its
+// sums by k = 1 / sqrt(sum(partial) * inv_n + eps). The split of a block does not depend on a common factor, so this
+// equals the product over the normalized vector up to rounding; it lets the norm run as independent warps on many SMs
+// instead of one CTA that must first reduce the whole row. partial == nullptr: no factor.
+struct NormScale {
+    const float* partial;
+    uint32_t count;
+    float inv_n, eps;
+};
+// planes(x * pre * w) and the blocks' sums of squares of x * pre; K a multiple of 32, w may be null.
+cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl = false);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl = false);
+                        int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f});
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 

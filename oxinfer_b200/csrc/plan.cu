@@ -18,7 +18,8 @@ namespace b2 {
 
 namespace {
 
-constexpr uint32_t OP_XPLANES = 100;  // internal: planes of a vector no producer kernel could write
+constexpr uint32_t OP_XPLANES = 100;
+constexpr uint32_t OP_NORM_DEFERRED = 101;  // internal: planes of x * w and per-block sums of squares; the products apply the factor  // internal: planes of a vector no producer kernel could write
 
 std::string fmt(const char* f, ...) {
     char buf[512];
@@ -99,7 +100,7 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.v) cudaFree(k.v);
     }
     for (void* m : peer_maps_) cudaIpcCloseMemHandle(m);
-    void* frees[] = {xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
+    void* frees[] = {norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -124,6 +125,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     p->sm_count_ = sm_count;
     if (const char* e = getenv("B2_PLAN_PDL")) p->pdl_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_FUSE")) p->fuse_ = atoi(e) != 0;
+    if (const char* e = getenv("B2_PLAN_DEFER_NORM")) p->defer_norm_ = atoi(e) != 0;
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -397,6 +399,67 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         return B2_ERR_ARG;
     }
 
+    // ---- norms whose output only products read: the factor moves behind the product -----------------------------
+    // The one-CTA norm spends most of its time splitting the row into planes on a single SM; when nothing reads the
+    // normalized row itself (every reader is a product over its planes), a grid of independent warps splits x * w and
+    // leaves the blocks' sums of squares, and the products multiply by the factor (NormScale).
+    size_t norm_floats = 0;
+    if (p->defer_norm_) {
+        auto overlaps = [](const float* a, size_t na, const float* b, size_t nb) { return a && b && a < b + nb && b < a + na; };
+        for (size_t a = 0; a < p->ops_.size(); a++) {
+            Op& nrm = p->ops_[a];
+            if (nrm.kind != B2_OP_NORM || !nrm.norm.planes || nrm.rows != 1 || nrm.norm.add) continue;
+            const float* y = nrm.y;
+            const size_t n = nrm.norm.n;
+            if (overlaps(y, n, p->hidden_, p->n_hidden_) || overlaps(y, n, p->logits_, p->n_logits_) || overlaps(y, n, p->input_, p->n_input_)) continue;
+            bool ok = true;
+            std::vector<size_t> users;
+            for (size_t b = a + 1; b < p->ops_.size() && ok; b++) {
+                const Op& o = p->ops_[b];
+                bool writes = false;
+                switch (o.kind) {
+                    case B2_OP_LINEAR:
+                        if (o.x == y && o.w.n_in == n && o.w.fmt != B2_FMT_F8E4M3) users.push_back(b);
+                        else if (overlaps(y, n, o.x, o.w.n_in)) ok = false;
+                        if (overlaps(y, n, o.y, o.w.n_out)) {
+                            if (o.mode != B2_MODE_STORE && !o.pair) ok = false;  // reads what it adds to
+                            writes = true;
+                        }
+                        break;
+                    case B2_OP_NORM:
+                    case OP_NORM_DEFERRED:
+                        if (overlaps(y, n, o.x, (size_t)(o.rows - 1) * o.norm.x_stride + o.norm.n)) ok = false;
+                        writes = overlaps(y, n, o.y, (size_t)(o.rows - 1) * o.norm.out_stride + o.norm.n);
+                        break;
+                    case OP_XPLANES: ok = ok && !overlaps(y, n, o.x, o.n); break;
+                    case B2_OP_EXCHANGE:
+                        if (overlaps(y, n, o.x, o.n)) ok = false;
+                        break;
+                    case B2_OP_GLU:
+                        if (overlaps(y, n, o.x, o.n) || overlaps(y, n, o.z, o.n)) ok = false;
+                        writes = overlaps(y, n, o.y, o.n);
+                        break;
+                    default:  // RoPE, attention: any overlap of their views with the row disqualifies it
+                        if (overlaps(y, n, o.x, n) || overlaps(y, n, o.y, n)) ok = false;
+                        break;
+                }
+                if (writes) break;
+            }
+            if (!ok || users.empty()) continue;
+            nrm.kind = OP_NORM_DEFERRED;
+            nrm.ns = NormScale{(const float*)(uintptr_t)norm_floats, (uint32_t)(n / 32), 1.0f / (float)n, nrm.norm.eps};  // offset now, pointer below
+            for (size_t b : users) p->ops_[b].ns = nrm.ns;
+            norm_floats += (n / 32 + 63) / 64 * 64;
+        }
+    }
+    if (norm_floats) {
+        PLAN_CUDA(cudaMalloc((void**)&p->norm_partials_, norm_floats * sizeof(float)), "cudaMalloc(norm partial sums)");
+        PLAN_CUDA(cudaMemset(p->norm_partials_, 0, norm_floats * sizeof(float)), "cudaMemset(norm partial sums)");
+        for (Op& o : p->ops_)
+            if ((o.kind == OP_NORM_DEFERRED || o.kind == B2_OP_LINEAR) && o.ns.count)
+                o.ns.partial = p->norm_partials_ + (size_t)(uintptr_t)o.ns.partial;
+    }
+
     // ---- planes regions ---------------------------------------------------------------------------
     size_t planes_total = 0;
     std::vector<size_t> region_at(region_k.size());
@@ -478,7 +541,8 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
         switch (o.kind) {
             case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st, pdl); break;
             case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st, pdl); break;
-            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl); break;
+            case OP_NORM_DEFERRED: e = launch_norm_planes(o.x, o.p0, o.norm.pre, o.norm.n, o.xp, const_cast<float*>(o.ns.partial), st, pdl); break;
+            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl, o.ns); break;
             case B2_OP_QK_ROPE:
                 e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st, pdl);
                 break;
@@ -779,7 +843,8 @@ void DecodePlanImpl::build_program() {
                 gplanes = o.xp;
                 break;
             }
-            case B2_OP_NORM: {
+            case B2_OP_NORM:
+            case OP_NORM_DEFERRED: {  // the token kernel normalizes in full per CTA either way (its products apply no factor)
                 if (o.rows != 1 || o.norm.n % 32 || o.norm.n > TOKEN_KERNEL_MAX_NORM || o.norm.add) return;
                 t.kind = TK_NORM_STAGE;
                 t.x = o.x;

@@ -46,6 +46,7 @@ class DecodePlanImpl {
         uint32_t n = 0;
         int gelu = 0;
         size_t off = 0;  // EXCHANGE: offset of the vector in the activation block, in floats
+        NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
     };
     DecodePlanImpl() = default;
@@ -65,6 +66,8 @@ class DecodePlanImpl {
     PeerSet peers_{};
     uint32_t* xflags_ = nullptr;  // this rank's flag words
     std::vector<void*> peer_maps_;  // what cudaIpcOpenMemHandle returned
+    bool defer_norm_ = true;  // norms that feed only products: factor applied after the product (B2_PLAN_DEFER_NORM=0: off)
+    float* norm_partials_ = nullptr;
     bool fuse_ = true;  // q / k / v style products of one vector as one launch over concatenated rows (B2_PLAN_FUSE=0: off)
     std::vector<void*> fused_;  // device copies made for that
     // one allocation each
