@@ -249,7 +249,7 @@ __device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, 
     return *ok_s != 0;
 }
 
-__global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, uint32_t n, uint32_t* lflags, uint32_t* status) {
+__global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, uint32_t n, uint32_t* lflags, uint32_t* status, int meet_first) {
     __shared__ int ok_s;
     __shared__ uint32_t epoch_s;
     pdl_launch_dependents();
@@ -257,7 +257,9 @@ __global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, 
     if (threadIdx.x == 0) epoch_s = lflags[0] + 1;
     __syncthreads();
     const uint32_t epoch = epoch_s;
-    bool ok = peers_meet(ps, lflags, 8, epoch, &ok_s);
+    // The first meeting is left out where the plan has shown that no kernel between the previous exchange and this one
+    // reads the other ranks' parts of the vector (a peer can be at most one exchange ahead).
+    bool ok = meet_first ? peers_meet(ps, lflags, 8, epoch, &ok_s) : true;
     if (ok) {
         const uint32_t part = n / ps.world;  // a multiple of 4 (checked on the host)
         const float4* src = (const float4*)(ps.base[ps.rank] + off + (size_t)ps.rank * part);
@@ -292,9 +294,10 @@ cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, 
     return cudaGetLastError();
 }
 
-cudaError_t launch_exchange(const PeerSet& ps, size_t off_floats, uint32_t n, uint32_t* lflags, uint32_t* status, cudaStream_t st, bool pdl) {
+cudaError_t launch_exchange(const PeerSet& ps, size_t off_floats, uint32_t n, uint32_t* lflags, uint32_t* status, cudaStream_t st, bool pdl,
+                            bool meet_first) {
     if (ps.world < 2 || ps.world > 8 || n % (4 * ps.world)) return cudaErrorInvalidValue;
-    return launch_k(exchange_kernel, dim3(1), dim3(1024), 0, st, pdl, ps, off_floats, n, lflags, status);
+    return launch_k(exchange_kernel, dim3(1), dim3(1024), 0, st, pdl, ps, off_floats, n, lflags, status, meet_first ? 1 : 0);
 }
 
 cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uint32_t count, int* token, int tok, cudaStream_t st) {

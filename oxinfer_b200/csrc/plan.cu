@@ -551,7 +551,7 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
                 break;
             case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st, pdl); break;
             case B2_OP_EXCHANGE:
-                if (attached_) e = launch_exchange(peers_, o.off, o.n, xflags_, status_, st, pdl);  // the first pass of a lone rank has nobody to meet
+                if (attached_) e = launch_exchange(peers_, o.off, o.n, xflags_, status_, st, pdl, o.meet_first);  // the first pass of a lone rank has nobody to meet
                 break;
             default: e = cudaErrorInvalidValue;
         }
@@ -778,6 +778,45 @@ int DecodePlanImpl::attach_peers(uint32_t rank, uint32_t world, const void* hand
         peers_.flags[p] = (uint32_t*)f;
     }
     attached_ = true;
+    // Which exchanges need the meeting before the writes: those with a kernel, since the previous exchange, that reads
+    // the vector outside this rank's own part (the first exchange of the list always meets: its predecessors are the
+    // previous step's kernels).
+    {
+        auto reads_outside = [&](const float* a, size_t na, const Op& ex) {
+            if (!a || na == 0) return false;
+            const float* v = ex.x;
+            const size_t part = ex.n / world;
+            const float* own = v + (size_t)rank * part;
+            if (!(a < v + ex.n && v < a + na)) return false;  // does not touch the vector
+            return !(a >= own && a + na <= own + part);        // touches it outside the own part
+        };
+        bool first = true;
+        for (size_t i = 0; i < ops_.size(); i++) {
+            if (ops_[i].kind != B2_OP_EXCHANGE) continue;
+            Op& ex = ops_[i];
+            bool need = first;
+            first = false;
+            for (size_t b = i; b-- > 0 && !need;) {
+                const Op& o = ops_[b];
+                if (o.kind == B2_OP_EXCHANGE) break;
+                switch (o.kind) {
+                    case B2_OP_LINEAR:
+                        if (o.w.fmt == B2_FMT_F8E4M3) need = reads_outside(o.x, o.w.n_in, ex);
+                        if (o.mode != B2_MODE_STORE && !o.pair) need = need || reads_outside(o.y, o.w.n_out, ex);
+                        need = need || reads_outside(o.z, 1, ex);
+                        break;
+                    case B2_OP_NORM:
+                    case OP_NORM_DEFERRED: need = reads_outside(o.x, (size_t)(o.rows - 1) * o.norm.x_stride + o.norm.n, ex); break;
+                    case OP_XPLANES: need = reads_outside(o.x, o.n, ex); break;
+                    case B2_OP_GLU: need = reads_outside(o.x, o.n, ex) || reads_outside(o.z, o.n, ex); break;
+                    case B2_OP_QK_ROPE: need = reads_outside(o.x, (size_t)o.rope.v_off + (size_t)o.rope.nkv * o.rope.hd + (size_t)o.rope.nh * o.rope.q_stride, ex); break;
+                    case B2_OP_ATTEND: need = reads_outside(o.x, (size_t)o.attn.nh * o.attn.hd, ex); break;
+                    default: need = true;
+                }
+            }
+            ex.meet_first = need;
+        }
+    }
     // the step graph captured at creation has no exchange nodes: capture it again
     if (step_exec_) cudaGraphExecDestroy(step_exec_);
     step_exec_ = nullptr;

@@ -45,6 +45,7 @@ class DecodePlanImpl {
         uint32_t kv = 0;
         uint32_t n = 0;
         int gelu = 0;
+        bool meet_first = true;  // EXCHANGE: meet the peers before writing too
         size_t off = 0;  // EXCHANGE: offset of the vector in the activation block, in floats
         NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
