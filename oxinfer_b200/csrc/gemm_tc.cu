@@ -41,7 +41,7 @@ namespace b2 {
 
 namespace {
 
-constexpr int MAX_STAGES = 8;              // ring depth is chosen per launch (see gemm_stages): narrow tiles afford a deeper ring
+constexpr int STAGES = 3;
 constexpr int STAGE_K = 64;                // f16 elements per row per stage = one 128-byte swizzle row
 constexpr int MAX_TILE_N = 240;
 constexpr int A_STAGE_BYTES = 256 * 128;   // up to 256 tokens
@@ -58,9 +58,9 @@ struct F8Scales {  // block scales of an FP8 matrix (formats.cuh); s == nullptr 
 };
 
 struct __align__(8) Shared {
-    uint64_t a_full[MAX_STAGES];
-    uint64_t b_full[MAX_STAGES];
-    uint64_t empty[MAX_STAGES];
+    uint64_t a_full[STAGES];
+    uint64_t b_full[STAGES];
+    uint64_t empty[STAGES];
     uint64_t raw_full;
     uint64_t raw_empty;
     uint64_t acc_full;
@@ -68,19 +68,8 @@ struct __align__(8) Shared {
     volatile uint32_t abort_flag;
 };
 
-// The ring and the raw staging buffer share RING_BYTES (three stages of the widest tile, or more stages of a narrower
-// one); the barrier block sits behind them at a fixed place, clear of the epilogue's 128 KB of staging tiles.
-constexpr size_t RING_BYTES = (size_t)3 * (A_STAGE_BYTES + B_STAGE_BYTES) + RAW_BYTES;
-constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + RING_BYTES + sizeof(Shared);
+constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + RAW_BYTES + sizeof(Shared);
 static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
-static_assert(RING_BYTES >= 16 * 8192, "epilogue staging");
-
-// Stages that fit for a tile of tile_n rows and 128 * m_halves tokens.
-__host__ __device__ inline int gemm_stages(int tile_n, int m_halves) {
-    const size_t per = (size_t)m_halves * 128 * 128 + (size_t)tile_n * 128;
-    size_t st = (RING_BYTES - RAW_BYTES) / per;
-    return st < 3 ? 3 : (st > (size_t)MAX_STAGES ? MAX_STAGES : (int)st);
-}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -187,12 +176,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int STAGES = gemm_stages(tile_n, m_halves);
-    const uint32_t a_stride = (uint32_t)m_halves * 128u * 128u, b_stride = (uint32_t)tile_n * 128u;
     uint8_t* a_tiles = smem;
-    uint8_t* b_tiles = smem + (size_t)STAGES * a_stride;
-    uint8_t* raw = b_tiles + (size_t)STAGES * b_stride;
-    Shared* sh = (Shared*)(smem + RING_BYTES);
+    uint8_t* b_tiles = smem + (size_t)STAGES * A_STAGE_BYTES;
+    uint8_t* raw = b_tiles + (size_t)STAGES * B_STAGE_BYTES;
+    Shared* sh = (Shared*)(raw + RAW_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = K / (64 * RAW_ST), nks = nsb * RAW_ST;
@@ -239,7 +226,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     mbar_arrive(&sh->a_full[s]);
                 } else {
                     mbar_arrive_expect_tx(&sh->a_full[s], a_bytes);
-                    tma_load_2d(a_tiles + (size_t)s * a_stride, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
+                    tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
                     a_issued = ks + 1;
                 }
             }
@@ -287,8 +274,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 if (dbg_cta) { dbg_wa += w1 - w0; dbg_wb += clock64() - w1; }
                 tc_fence_after();
                 // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
-                const uint64_t adesc0 = a_desc_base + (uint64_t)((uint32_t)s * (a_stride >> 4));
-                const uint64_t bdesc0 = b_desc_base + (uint64_t)((uint32_t)s * (b_stride >> 4));
+                const uint64_t adesc0 = a_desc_base + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
+                const uint64_t bdesc0 = b_desc_base + (uint64_t)((uint32_t)s * (B_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int kk = 0; kk < STAGE_K / 16; kk++) {
                     if (!(dbg & 4)) {
@@ -356,7 +343,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         break;
                     }
                     if (in_tile && !(dbg & 1)) {
-                        uint8_t* dst = b_tiles + (size_t)s * b_stride + row_off;
+                        uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
 #pragma unroll
                         for (int c = 0; c < 8; c++)
                             *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
@@ -430,7 +417,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         break;
                     }
                     if (in_tile && !(dbg & 1)) {
-                        uint8_t* dst = b_tiles + (size_t)s * b_stride + row_off;
+                        uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
                             *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
