@@ -215,6 +215,152 @@ cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
     return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns);
 }
 
+// ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
+// The float path above spends about three instructions per weight (convert, widen, multiply-add) and reads four
+// bytes of x per weight from shared memory: a third of the HBM rate at best. Here the multiply-adds run as
+// mma.sync m16n8k16 (f16 operands, f32 accumulate): a warp owns 16 weight rows, A is the weights (hardware
+// e4m3x2 -> f16x2, exact), B's column 0 is x rounded to f16 and column 1 the f16 of the rounding remainder, so
+// that x enters with 22 bits and the two columns' sums are added at the end; the other six columns are zero.
+// The summation index of an MMA may be permuted freely as long as A and B agree, so a lane loads 16 consecutive
+// bytes of its row (k = 64 c + 16 t ..) and feeds them to four MMAs. The block scale (one per 128 x 128 block)
+// multiplies the accumulators once per 128 k.
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void f8x16_to_h2(const uint4& q, uint32_t (&h)[8]) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffff), __NV_E4M3);
+        __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
+        h[2 * i] = *reinterpret_cast<uint32_t*>(&lo);
+        h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&hi);
+    }
+}
+
+constexpr int F8M_CHUNK = 64;  // k per step of a warp: 16 bytes per lane and row
+
+// A CTA owns one 16-row tile at a time; its eight warps split K (whole 128-k scale blocks each) and their partial sums
+// meet in shared memory, added in warp order.
+__global__ void __launch_bounds__(GEMV_THREADS, 3)
+gemv_f8_mma_kernel(WeightDev w, const float* __restrict__ x, float* __restrict__ y, int mode, const float* __restrict__ gate) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float part[GEMV_WARPS][16];
+    pdl_launch_dependents();
+    const int K = (int)w.n_in;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const size_t n_out = w.n_out;
+    __half* xh = (__half*)smem;   // [K] x rounded to f16
+    __half* xl = xh + K;          // [K] f16 of the remainder
+    // this warp's share of the scale blocks: blocks [kb0, kb1)
+    const int nblk = K / 128;
+    const int kb0 = (int)((long long)nblk * warp / GEMV_WARPS), kb1 = (int)((long long)nblk * (warp + 1) / GEMV_WARPS);
+    const int ch0 = 2 * kb0, ch1 = 2 * kb1;  // chunks of 64 k
+    pdl_wait();
+    for (int i = threadIdx.x; i < K; i += GEMV_THREADS) {
+        const float v = x[i];
+        const __half h = __float2half_rn(v);
+        xh[i] = h;
+        xl[i] = __float2half_rn(v - __half2float(h));
+    }
+    __syncthreads();
+    const __half* xb = g == 0 ? xh : xl;  // lanes of column 0 read x, of column 1 the remainder, the rest feed zeros
+    const size_t tiles = (n_out + 15) / 16;
+    for (size_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const size_t r0 = tile * 16;
+        const size_t rowA = min(r0 + g, n_out - 1), rowB = min(r0 + g + 8, n_out - 1);
+        const uint8_t* pa = w.p0 + rowA * (size_t)K + 16 * t;
+        const uint8_t* pb = w.p0 + rowB * (size_t)K + 16 * t;
+        const float* srow = w.p1 ? (const float*)w.p1 + ((w.bs_row0 + r0) / w.bs_rows) * w.bs_ncb : nullptr;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, c[4] = {0.f, 0.f, 0.f, 0.f};
+        // four chunks of loads in flight ahead of the arithmetic
+        uint4 qa[4], qb[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (ch0 + i < ch1) {
+                qa[i] = ldg_stream(pa + (size_t)(ch0 + i) * F8M_CHUNK);
+                qb[i] = ldg_stream(pb + (size_t)(ch0 + i) * F8M_CHUNK);
+            }
+        for (int base = ch0; base < ch1; base += 4) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int ch = base + i;
+                if (ch >= ch1) break;
+                const uint4 ca = qa[i], cb = qb[i];
+                if (ch + 4 < ch1) {
+                    qa[i] = ldg_stream(pa + (size_t)(ch + 4) * F8M_CHUNK);
+                    qb[i] = ldg_stream(pb + (size_t)(ch + 4) * F8M_CHUNK);
+                }
+                uint32_t ha[8], hb[8];
+                f8x16_to_h2(ca, ha);
+                f8x16_to_h2(cb, hb);
+                uint4 b01 = make_uint4(0, 0, 0, 0), b23 = make_uint4(0, 0, 0, 0);
+                if (g < 2) {
+                    const uint4* src = (const uint4*)(xb + ch * F8M_CHUNK + 16 * t);
+                    b01 = src[0];
+                    b23 = src[1];
+                }
+                const uint32_t bw[8] = {b01.x, b01.y, b01.z, b01.w, b23.x, b23.y, b23.z, b23.w};
+#pragma unroll
+                for (int m = 0; m < 4; m++) mma_f16_16816(c, ha[2 * m], hb[2 * m], ha[2 * m + 1], hb[2 * m + 1], bw[2 * m], bw[2 * m + 1]);
+                if ((ch & 1) == 1) {  // the end of a 128-k scale block
+                    const float s = srow ? __ldg(srow + (ch >> 1)) : 1.0f;
+                    acc[0] = fmaf(c[0], s, acc[0]);
+                    acc[1] = fmaf(c[1], s, acc[1]);
+                    acc[2] = fmaf(c[2], s, acc[2]);
+                    acc[3] = fmaf(c[3], s, acc[3]);
+                    c[0] = c[1] = c[2] = c[3] = 0.f;
+                }
+            }
+        }
+        if (t == 0) {  // columns 0 and 1 of rows g and g + 8
+            part[warp][g] = acc[0] + acc[1];
+            part[warp][g + 8] = acc[2] + acc[3];
+        }
+        __syncthreads();
+        if (threadIdx.x < 16) {
+            const size_t r = r0 + threadIdx.x;
+            if (r < n_out) {
+                float v = 0.0f;
+#pragma unroll
+                for (int wv = 0; wv < GEMV_WARPS; wv++) v += part[wv][threadIdx.x];
+                float* o = y + r;
+                if (mode == B2_MODE_STORE)
+                    *o = v;
+                else if (mode == B2_MODE_ADD)
+                    *o += v;
+                else
+                    *o += v * (1.0f / (1.0f + __expf(-gate[0])));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+static bool f8_mma_ok(const WeightDev& w, int mode) {
+    if (mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR) return false;
+    if (w.n_in % 128 || w.n_in < 128 * GEMV_WARPS || w.n_in * 4 > 200 * 1024) return false;
+    if (w.p1 && (w.bs_cols != 128 || w.bs_rows % 16 || w.bs_row0 % 16)) return false;
+    return true;
+}
+
+static cudaError_t launch_f8_mma(const WeightDev& w, const float* x, float* y, int mode, const float* gate, int sm_count, cudaStream_t st, bool pdl) {
+    const size_t smem = w.n_in * 4;  // two f16 copies of x
+    static size_t smem_set = 40 * 1024;  // the kernel also has static shared memory: ask early
+    if (smem > smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_f8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set = smem;
+    }
+    const size_t tiles = (w.n_out + 15) / 16;
+    size_t per_sm = (size_t)(220 * 1024) / (smem + 2048);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+    const size_t grid = tiles < (size_t)sm_count * per_sm ? tiles : (size_t)sm_count * per_sm;
+    return launch_k(gemv_f8_mma_kernel, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, x, y, mode, gate);
+}
+
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                        int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
@@ -277,7 +423,14 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
         case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
         case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
         case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
-        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_F8E4M3: {
+            static const bool mma = [] {
+                const char* e = getenv("B2_GEMV_F8_MMA");
+                return !e || atoi(e) != 0;
+            }();
+            if (mma && !ns.partial && f8_mma_ok(w, mode)) return launch_f8_mma(w, x, y, mode, gate, sm_count, st, pdl);
+            return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        }
         default: return cudaErrorInvalidValue;
     }
 }
