@@ -274,6 +274,22 @@ def fp8_extras(be, torch, peaks):
     ref = synth.f8_e4m3(n_out, n_in, 1)
     dev = be.upload(ref, n_out, n_in)
     out = {}
+    # M = 1: the matrix-vector product (one launch; the 352 MB matrix is larger than L2 by itself)
+    x1 = torch.randn(n_in, device="cuda", dtype=torch.float32)
+    y1 = torch.empty(n_out, device="cuda", dtype=torch.float32)
+    for _ in range(3):
+        be.matvec_dev(dev, x1, y1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        be.matvec_dev(dev, x1, y1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 20
+    wb = n_out * n_in + (n_out // 128) * (n_in // 128) * 4
+    out["m1"] = {"us": us, "weight_gbs": wb / us / 1e3, "frac_of_hbm_peak": wb / us / 1e3 / peaks["hbm_gbs"],
+                 "kernel": "gemv_f8_mma_kernel (mma.sync m16n8k16, x as two f16 columns)", "timing": "host-launched, 20 back to back"}
     for t in (128, 8192):
         xd = torch.randn((t, n_in), device="cuda", dtype=torch.float16)
         y = torch.empty((t, n_out), device="cuda", dtype=torch.float32)

@@ -361,6 +361,197 @@ static cudaError_t launch_f8_mma(const WeightDev& w, const float* x, float* y, i
     return launch_k(gemv_f8_mma_kernel, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, x, y, mode, gate);
 }
 
+// ---- the 4-bit formats on the tensor cores -------------------------------------------------------------------------
+// The integer dot products of gemv_kernel cost 0.75 dp4a per weight plus as much again in nibble extraction, plane
+// loads and combining; with the sub-block tails the kernels run at 3.4 instructions per weight, above the ~3.1 the
+// SMs can issue per weight at the HBM rate. Here the products run as mma.sync m16n8k32 (s8 x s8 -> s32): a warp owns
+// 16 weight rows, A is a sub-block's 32 nibbles (masked out of the packed bytes, which already are four weights per
+// word in k order), B's columns 0..2 are the three planes of x, and one MMA replaces 48 dp4a. A lane's share of the
+// summation index is permuted (bytes 8 t .. 8 t + 7 of the 32-byte group) so that weights and planes come in 8-byte
+// reads. The sums of a group go to the quad's lane t = group, which applies that group's scales (FmtQ4K / FmtMLX4
+// ::tail, the same arithmetic as gemv_kernel), so the four lanes of a quad share the float work.
+// A CTA owns one 16-row tile at a time; its warps split K by super-blocks and bring their rows' blocks (16 copies
+// of 144 bytes per step) into per-warp rings; the warps' partial sums meet in shared memory in warp order.
+__device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+constexpr int M4_SLOTS = 3;
+constexpr int M4_SLOT_BYTES = 16 * 144;
+
+template <class F, bool PAIR>
+__global__ void __launch_bounds__(GEMV_THREADS, 3)
+gemv4_mma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, NormScale ns) {
+    using namespace acopy;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bars[GEMV_WARPS * M4_SLOTS];
+    __shared__ float part[2][GEMV_WARPS][16];
+    pdl_launch_dependents();
+    const int K = (int)w.n_in, nblk = K / 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const size_t n_out = w.n_out, row_bytes = (size_t)nblk * 144;
+    const size_t planes_bytes = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
+    uint8_t* slots = smem + planes_bytes + (size_t)warp * M4_SLOTS * M4_SLOT_BYTES;
+    uint64_t* wbars = bars + warp * M4_SLOTS;
+    uint32_t phases = 0;
+    // this warp's super-blocks of every tile: [kb0, kb1)
+    const int kb0 = (int)((long long)nblk * warp / GEMV_WARPS), kb1 = (int)((long long)nblk * (warp + 1) / GEMV_WARPS);
+    const int per_tile = (kb1 - kb0) * (PAIR ? 2 : 1);  // steps per tile (a pair runs the second matrix after the first)
+    const size_t tiles = (n_out + 15) / 16;
+    const size_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t T = (uint32_t)(my_tiles * (size_t)per_tile);
+    // step s of this warp: tile, matrix, block
+    auto issue = [&](uint32_t s) {  // whole warp: lanes 0..15 copy one row's block each
+        const size_t tile = blockIdx.x + (size_t)(s / (uint32_t)per_tile) * gridDim.x;
+        uint32_t r = s % (uint32_t)per_tile;
+        const bool second = PAIR && r >= (uint32_t)(kb1 - kb0);
+        if (second) r -= (uint32_t)(kb1 - kb0);
+        const int slot = (int)(s % M4_SLOTS);
+        if (lane == 0) bar_expect_tx(&wbars[slot], 16 * 144);
+        __syncwarp();
+        if (lane < 16) {
+            const size_t row = min(tile * 16 + lane, n_out - 1);
+            const uint8_t* src = (second ? w2.p0 : w.p0) + row * row_bytes + (size_t)(kb0 + (int)r) * 144;
+            bulk_load(slots + slot * M4_SLOT_BYTES + lane * 144, src, 144, &wbars[slot]);
+        }
+    };
+    if (lane == 0)
+        for (int sl = 0; sl < M4_SLOTS; sl++) bar_init(&wbars[sl], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    for (uint32_t s = 0; s + 1 < M4_SLOTS && s < T; s++) issue(s);  // the weights do not depend on the kernel ahead
+    pdl_wait();
+    {
+        const int nslots = K / 16;
+        const uint4* src = (const uint4*)xp.planes;
+        uint4* dst = (uint4*)smem;
+        for (int i = threadIdx.x; i < 3 * nslots; i += GEMV_THREADS) {
+            int p = i / nslots, q = i - p * nslots;
+            dst[p * nslots + swz(q)] = src[i];
+        }
+        float2* sx = (float2*)(smem + 3 * (size_t)K);
+        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
+    }
+    __syncthreads();
+    const float2* sx = (const float2*)(smem + 3 * (size_t)K);
+    const uint8_t* plane = smem + (size_t)(g < 3 ? g : 0) * K;  // the plane this lane feeds as column g
+    const float kscale = norm_scale_factor(ns, lane);
+    const uint32_t M = 0x0F0F0F0Fu;
+    uint32_t s = 0;
+    bool ok = true;
+    for (size_t ti = 0; ti < my_tiles && ok; ti++) {
+        const size_t tile = blockIdx.x + ti * gridDim.x;
+        float res[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [matrix][row g | row g + 8]
+#pragma unroll
+        for (int mat = 0; mat < (PAIR ? 2 : 1); mat++) {
+            float accA = 0.0f, accB = 0.0f;
+            for (int kb = kb0; kb < kb1; kb++, s++) {
+                __syncwarp();  // every lane is done with the slot that is refilled now
+                if (s + M4_SLOTS - 1 < T) issue(s + M4_SLOTS - 1);
+                const int slot = (int)(s % M4_SLOTS);
+                if (!bar_wait(&wbars[slot], (phases >> slot) & 1u, RING_WAIT_LIMIT)) {
+                    ok = false;
+                    break;
+                }
+                phases ^= 1u << slot;
+                const uint8_t* blkA = slots + slot * M4_SLOT_BYTES + g * 144;
+                const uint8_t* blkB = blkA + 8 * 144;
+                int mine[4] = {0, 0, 0, 0};  // this lane's group (j == t): lo / hi sums of rows g and g + 8
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint2 wa = *(const uint2*)(blkA + 16 + 32 * j + 8 * t);
+                    const uint2 wb = *(const uint2*)(blkB + 16 + 32 * j + 8 * t);
+                    const int k0 = kb * 256 + 64 * j + 8 * t;
+                    uint2 blo = make_uint2(0, 0), bhi = make_uint2(0, 0);
+                    if (g < 3) {
+                        blo = *(const uint2*)(plane + ((size_t)swz(k0 >> 4) << 4) + (k0 & 15));
+                        bhi = *(const uint2*)(plane + ((size_t)swz((k0 + 32) >> 4) << 4) + (k0 & 15));
+                    }
+                    int cl[4], chh[4];
+                    mma_s8_16832(cl, wa.x & M, wb.x & M, wa.y & M, wb.y & M, blo.x, blo.y);
+                    mma_s8_16832(chh, (wa.x >> 4) & M, (wb.x >> 4) & M, (wa.y >> 4) & M, (wb.y >> 4) & M, bhi.x, bhi.y);
+                    // lane t = 0 holds planes 0 and 1 (columns 0, 1), lane t = 1 plane 2 (column 2)
+                    int v[4] = {cl[0] + (cl[1] << 7), chh[0] + (chh[1] << 7), cl[2] + (cl[3] << 7), chh[2] + (chh[3] << 7)};
+                    const int p2[4] = {cl[0], chh[0], cl[2], chh[2]};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int hi2 = __shfl_sync(0xffffffffu, p2[i], (lane & ~3) | 1);
+                        const int tot = __shfl_sync(0xffffffffu, v[i], lane & ~3) + (hi2 << 14);
+                        if (t == j) mine[i] = tot;
+                    }
+                }
+                // the scales of group t of rows g and g + 8
+                Q4Regs ra, rb;
+                ra.hdr = *(const uint4*)blkA;
+                rb.hdr = *(const uint4*)blkB;
+                const float4 sxv = *(const float4*)(sx + (kb * 8 + 2 * t));
+                F::tail(ra, t, sxv, mine[0], mine[1], accA);
+                F::tail(rb, t, sxv, mine[2], mine[3], accB);
+            }
+            // the quad's four groups
+            accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+            accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+            accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+            res[mat][0] = accA;
+            res[mat][1] = accB;
+        }
+        if (!ok) break;
+        if (t == 0) {
+#pragma unroll
+            for (int mat = 0; mat < (PAIR ? 2 : 1); mat++) {
+                part[mat][warp][g] = res[mat][0];
+                part[mat][warp][g + 8] = res[mat][1];
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < 16) {
+            const size_t r = tile * 16 + threadIdx.x;
+            if (r < n_out) {
+                float a = 0.0f, b = 0.0f;
+#pragma unroll
+                for (int wv = 0; wv < GEMV_WARPS; wv++) {
+                    a += part[0][wv][threadIdx.x];
+                    if (PAIR) b += part[1][wv][threadIdx.x];
+                }
+                a *= kscale;
+                b *= kscale;
+                float* o = y + r;
+                if (PAIR)
+                    *o = (mode == B2_MODE_SILU_PAIR ? silu(a) : gelu_tanh(a)) * b;
+                else if (mode == B2_MODE_STORE)
+                    *o = a;
+                else if (mode == B2_MODE_ADD)
+                    *o += a;
+                else
+                    *o += a * (1.0f / (1.0f + __expf(-gate[0])));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <class F>
+cudaError_t launch_mma4(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count, cudaStream_t st,
+                        bool pdl, NormScale ns) {
+    const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
+    auto kern = pair ? gemv4_mma_kernel<F, true> : gemv4_mma_kernel<F, false>;
+    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)GEMV_WARPS * M4_SLOTS * M4_SLOT_BYTES;
+    static size_t smem_set[2] = {40 * 1024, 40 * 1024};
+    if (smem > smem_set[pair]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set[pair] = smem;
+    }
+    const size_t tiles = (w.n_out + 15) / 16;
+    size_t per_sm = (size_t)(224 * 1024) / (smem + 3072);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+    const size_t grid = tiles < (size_t)sm_count * per_sm ? tiles : (size_t)sm_count * per_sm;
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, ns);
+}
+
 template <class F, bool XF32>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                        int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
@@ -407,6 +598,19 @@ cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
+    // The tensor-core form of the 4-bit products is parity-green but not yet the faster one (14336 x 4096: 15.9 us against
+    // 11.2; a decode token 2.52 ms against 2.37): its CTA-per-tile mapping leaves 896 tiles on 444 CTAs two or three rounds
+    // deep and small products are bound by the prologue either way. It stays selectable (B2_GEMV_MMA4: 1 everywhere,
+    // 2 only in dependent-launch chains) until tiles are handed out dynamically.
+    static const int mma4 = [] {
+        const char* e = getenv("B2_GEMV_MMA4");
+        return e ? atoi(e) : 0;
+    }();
+    if (mma4 && (mma4 == 1 || pdl) && (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && w.n_in >= 256 * GEMV_WARPS &&
+        xplanes_bytes(w.n_in) + (size_t)GEMV_WARPS * M4_SLOTS * M4_SLOT_BYTES + 4096 <= 224 * 1024) {
+        if (w.fmt == B2_FMT_MLX4) return launch_mma4<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
+        return launch_mma4<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
+    }
     static const bool ring = [] {
         const char* e = getenv("B2_GEMV_RING");
         return !e || atoi(e) != 0;

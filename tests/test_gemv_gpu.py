@@ -110,3 +110,40 @@ def test_matmul_small_t_uses_gemv_for_every_format(backend):
         y = np.zeros((3, n_out), np.float32)
         assert backend.matmul(x, [ob.Job(dev, y)])
         assert row_err(y, m.matmul_f64(x)) < TIGHT
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
+@pytest.mark.parametrize("shape", [(1000, 2048), (4099, 4096), (520, 14336)])
+def test_tensor_core_path_modes_and_pairs(backend, fmt, shape):
+    """K >= 2048: the 4-bit products run on the tensor cores (mma.sync over nibbles and planes). Store / add / gated add and
+    the SiLU / GELU pairs, ragged row counts (the last 16-row tile is partial), against the f64 definition."""
+    n_out, n_in = shape
+    ref_g, mg = make_pair(fmt, n_out, n_in, 350)
+    ref_u, mu = make_pair(fmt, n_out, n_in, 351)
+    dg, du = backend.upload(ref_g, n_out, n_in), backend.upload(ref_u, n_out, n_in)
+    x = (synth.activations(1, n_in, 352) * np.float32(0.731)).astype(np.float32)
+    g, u = mg.matmul_f64(x)[0], mu.matmul_f64(x)[0]
+    xd = torch.from_numpy(x[0]).cuda()
+    y = torch.zeros(n_out, device="cuda")
+    assert backend.matvec_dev(dg, xd, y)
+    torch.cuda.synchronize()
+    assert row_err(y.cpu().numpy()[None], g[None]) < TIGHT
+    base = torch.linspace(-2, 2, n_out, device="cuda", dtype=torch.float32)
+    y = base.clone()
+    assert backend.matvec_dev(dg, xd, y, ob.MODE_ADD)
+    torch.cuda.synchronize()
+    assert row_err(y.cpu().numpy()[None], (g + base.cpu().numpy().astype(np.float64))[None]) < TIGHT
+    gate = torch.tensor([-0.4], device="cuda")
+    y = base.clone()
+    assert backend.matvec_dev(dg, xd, y, ob.MODE_ADD_GATED, gate=gate)
+    torch.cuda.synchronize()
+    assert row_err(y.cpu().numpy()[None], (base.cpu().numpy().astype(np.float64) + g / (1 + np.exp(0.4)))[None]) < TIGHT
+    y = torch.zeros(n_out, device="cuda")
+    assert backend.matvec_dev(dg, xd, y, ob.MODE_SILU_PAIR, up=du)
+    torch.cuda.synchronize()
+    assert row_err(y.cpu().numpy()[None], (g / (1.0 + np.exp(-g)) * u)[None]) < 1e-4
+    y = torch.zeros(n_out, device="cuda")
+    assert backend.matvec_dev(dg, xd, y, ob.MODE_GELU_PAIR, up=du)
+    torch.cuda.synchronize()
+    gelu = 0.5 * g * (1 + np.tanh(0.7978845608 * (g + 0.044715 * g**3)))
+    assert row_err(y.cpu().numpy()[None], (gelu * u)[None]) < 1e-4
