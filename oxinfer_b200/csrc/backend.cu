@@ -596,6 +596,59 @@ class Backend {
     // ---- Backend::moe (src/gpu.rs:232-248, src/cuda.rs:798-966): y[i] += sum_j w_ij down_e(act(gate_e x_i) * up_e x_i).
     // The host builds the per-expert segments as the reference does (src/cuda.rs:810-857), padded to the
     // GEMM's 128-row token tile; x_dev / y_dev are device f32 [t][h].
+    // A few (token, route) pairs (decode): every pair is its own matrix-vector product, so the tensor-core GEMM's 128-row
+    // tiles would be almost empty. Five launches instead: planes of the tokens, one batched GEMV over the pairs' fused
+    // gate / up matrices (SiLU pair), planes of the activations, one batched GEMV over the down matrices, and the ordered
+    // combine (src/moe.rs:625-828 does the same per expert on the CPU; exact f32 / integer arithmetic, no f16 operands).
+    int moe_small(const Moe& m, const float* x_dev_, size_t t, const int32_t* ids, const float* rw, size_t k, float* y_dev_) {
+        const size_t R = t * k;
+        const size_t sx = (xplanes_bytes(m.h) + 255) / 256 * 256, sa = (xplanes_bytes(m.inter) + 255) / 256 * 256;
+        cudaError_t e = moe_xg.reserve(t * sx);
+        if (e == cudaSuccess) e = moe_g.reserve(R * m.inter * 4);
+        if (e == cudaSuccess) e = moe_a.reserve(R * sa);
+        if (e == cudaSuccess) e = moe_o.reserve(R * m.h * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(moe scratch)");
+        // the routes travel as kernel arguments: no copy, no synchronization
+        GemvBatch b1{}, b2{};
+        SmallRoutes routes{};
+        b1.n = b2.n = (int)R;
+        for (size_t i = 0; i < R; i++) {
+            b1.expert[i] = b2.expert[i] = ids[i];
+            b1.xrow[i] = (int)(i / k);  // the pair's token
+            b2.xrow[i] = (int)i;        // the pair's own activations
+            routes.w[i] = rw[i];
+        }
+        const size_t rb_h = m.h / 256 * 144, rb_i = m.inter / 256 * 144;
+        WeightDev gate{};
+        gate.fmt = m.fmt;
+        gate.n_out = m.inter;
+        gate.n_in = m.h;
+        gate.group = 64;
+        gate.p0 = (const uint8_t*)m.gate_up;
+        WeightDev up = gate;
+        up.p0 = gate.p0 + m.inter * rb_h;
+        WeightDev down = gate;
+        down.n_out = m.h;
+        down.n_in = m.inter;
+        down.p0 = (const uint8_t*)m.down;
+        e = launch_xplanes_rows(x_dev_, t, m.h, (uint8_t*)moe_xg.p, sx, stream);
+        b1.w_stride = 2 * m.inter * rb_h;
+        b1.x_stride = sx;
+        b1.y_stride = m.inter;
+        b1.planes = (uint8_t*)moe_xg.p;
+        b2.w_stride = m.h * rb_i;
+        b2.x_stride = sa;
+        b2.y_stride = m.h;
+        b2.planes = (uint8_t*)moe_a.p;
+        if (e == cudaSuccess) e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, B2_MODE_SILU_PAIR, sm_count, stream);
+        if (e == cudaSuccess) e = launch_xplanes_rows((const float*)moe_g.p, R, m.inter, (uint8_t*)moe_a.p, sa, stream);
+        if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, sm_count, stream);
+        if (e == cudaSuccess) e = launch_moe_combine_small((const float*)moe_o.p, routes, t, k, m.h, y_dev_, stream);
+        launches += 5;
+        if (e != cudaSuccess) return cuda_fail(e, "moe (batched matrix-vector path)");
+        return B2_OK;
+    }
+
     int moe_dev(uint64_t handle, const float* x_dev_, size_t t, const int32_t* ids, const float* rw, size_t k, float* y_dev_) {
         auto it = moes.find(handle);
         if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe: unknown handle]");
@@ -608,6 +661,7 @@ class Backend {
             if (ids[i] < 0 || (size_t)ids[i] >= m.experts) return fail(B2_ERR_ARG, "[b200qmm: moe: expert index out of range]");
             count[(size_t)ids[i]]++;
         }
+        if (t * k <= 64 && !getenv("B2_MOE_NO_GEMV")) return moe_small(m, x_dev_, t, ids, rw, k, y_dev_);
         const size_t TILE = 128;
         std::vector<size_t> off(m.experts, 0);
         std::vector<int32_t> tile_expert;

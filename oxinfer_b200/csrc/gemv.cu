@@ -17,6 +17,7 @@
 // phase, which read 64 bytes each at a 64-byte stride, fall on different banks.
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 
@@ -65,9 +66,16 @@ __global__ void __launch_bounds__(256) norm_planes_kernel(const float* __restric
 template <class F, bool PAIR, bool XF32>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
-            const float* __restrict__ gate, NormScale ns) {
+            const float* __restrict__ gate, NormScale ns, GemvBatch batch) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
+    if (batch.n) {  // entry blockIdx.y of a batch: its matrix of the stack, its planes, its output
+        const size_t b = blockIdx.y, e = (size_t)batch.expert[b];
+        w.p0 += e * batch.w_stride;
+        w2.p0 += e * batch.w_stride;
+        xp = xplanes_at(batch.planes + (size_t)batch.xrow[b] * batch.x_stride, w.n_in);
+        y += b * batch.y_stride;
+    }
     const int K = (int)w.n_in;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t n_out = w.n_out;
@@ -569,7 +577,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns);
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns, GemvBatch{});
 }
 
 }  // namespace
@@ -588,6 +596,49 @@ bool gemv_supports(const WeightDev& w) {
 cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl) {
     unsigned warps = (unsigned)(K / 32);
     return launch_k(xplanes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, (int)K, out);
+}
+
+__global__ void __launch_bounds__(256) xplanes_rows_kernel(const float* __restrict__ x, int rows, int K, uint8_t* planes, size_t stride) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int per_row = K / 32;
+    if (warp >= rows * per_row) return;
+    const int r = warp / per_row, blk = warp - r * per_row;
+    xplanes_block(x[(size_t)r * K + blk * 32 + lane], blk, lane, K, xplanes_at(planes + (size_t)r * stride, (size_t)K));
+}
+
+cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st) {
+    if (rows == 0 || K % 32) return cudaErrorInvalidValue;
+    const unsigned warps = (unsigned)(rows * (K / 32));
+    xplanes_rows_kernel<<<(warps + 7) / 8, 256, 0, st>>>(x, (int)rows, (int)K, planes, stride);
+    return cudaGetLastError();
+}
+
+template <class F>
+static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
+                                      cudaStream_t st) {
+    const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
+    auto kern = pair ? gemv_kernel<F, true, false> : gemv_kernel<F, false, false>;
+    const size_t smem = xplanes_bytes(w.n_in);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
+    size_t gx = (w.n_out + rows_per_cta - 1) / rows_per_cta;
+    const size_t cap = std::max<size_t>(1, (size_t)sm_count * 3 / batch);  // about three CTAs per SM over the whole batch
+    if (gx > cap) gx = cap;
+    XPlanes none{};
+    kern<<<dim3((unsigned)gx, (unsigned)batch), GEMV_THREADS, smem, st>>>(w, pair ? *up : w, nullptr, none, y, mode, nullptr,
+                                                                         NormScale{nullptr, 0, 0.0f, 0.0f}, b);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
+                                cudaStream_t st) {
+    if (batch == 0 || batch > GEMV_BATCH_MAX || (size_t)b.n != batch || !gemv_supports(w)) return cudaErrorInvalidValue;
+    if (w.fmt == B2_FMT_MLX4) return launch_batched_fmt<FmtMLX4>(w, up, b, batch, y, mode, sm_count, st);
+    if (w.fmt == B2_FMT_Q4_K) return launch_batched_fmt<FmtQ4K>(w, up, b, batch, y, mode, sm_count, st);
+    return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl) {

@@ -45,7 +45,7 @@ struct XPlanes {
     int32_t* v16;     // [K/16]  integer sums of each 16 elements
 };
 __host__ __device__ inline size_t xplanes_bytes(size_t K) { return 3 * K + 4 * (K / 32) * 2 + 4 * (K / 16); }
-inline XPlanes xplanes_at(void* base, size_t K) {
+__host__ __device__ inline XPlanes xplanes_at(void* base, size_t K) {
     XPlanes p;
     uint8_t* b = (uint8_t*)base;
     p.planes = (int8_t*)b;
@@ -71,6 +71,22 @@ cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f});
+// A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
+// of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
+// bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),
+// so a call needs no copy of its own and no synchronization.
+constexpr int GEMV_BATCH_MAX = 64;
+struct GemvBatch {
+    int n;  // 0: not a batch
+    int expert[GEMV_BATCH_MAX];
+    int xrow[GEMV_BATCH_MAX];
+    size_t w_stride, x_stride, y_stride;
+    uint8_t* planes;
+};
+cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
+                                cudaStream_t st);
+// Planes of `rows` vectors of K values (row r at x + r * K) into blocks `stride` bytes apart.
+cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st);
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 
@@ -102,6 +118,11 @@ cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t t_pad, si
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st);
 cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, cudaStream_t st);
 cudaError_t launch_moe_act(const float* g, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
+// The same with the routes as kernel arguments (at most GEMV_BATCH_MAX pairs): slot of pair (i, j) = i k + j, no row scale.
+struct SmallRoutes {
+    float w[GEMV_BATCH_MAX];
+};
+cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
 cudaError_t launch_moe_combine(const float* o, const float* row_scale, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y,
                                cudaStream_t st);
 

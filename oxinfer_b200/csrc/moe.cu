@@ -111,7 +111,27 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const float* __r
     y[(size_t)tok * h + c] = acc;
 }
 
+// y[tok][c] += sum over the token's k routes, in order, of w * o[tok k + j][c]; the weights are kernel arguments.
+__global__ void moe_combine_small_kernel(const float* __restrict__ o, SmallRoutes r, int k, int h, float* __restrict__ y) {
+    const int tok = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= h) return;
+    float acc = y[(size_t)tok * h + c];
+    for (int j = 0; j < k; j++) {
+        const int slot = tok * k + j;
+        acc = __fadd_rn(acc, __fmul_rn(r.w[slot], o[(size_t)slot * h + c]));
+    }
+    y[(size_t)tok * h + c] = acc;
+}
+
 }  // namespace
+
+cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st) {
+    if (t * k > GEMV_BATCH_MAX) return cudaErrorInvalidValue;
+    dim3 grid((unsigned)((h + 255) / 256), (unsigned)t);
+    moe_combine_small_kernel<<<grid, 256, 0, st>>>(o, r, (int)k, (int)h, y);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st) {
     if (n > 2048 || k > 32 || k > n) return cudaErrorInvalidValue;
