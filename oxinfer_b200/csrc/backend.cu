@@ -508,7 +508,40 @@ class Backend {
         ns_in += since(t0);
         for (size_t j = 0; j < n_jobs; j++) {
             auto t1 = clk::now();
-            for (size_t i = 0; i < t; i++) {
+            // two to four rows: one launch that reads the weights once (each row's result is the one-row result bit for bit);
+            // falls back to a launch per row when the rows' vectors do not fit in shared memory together
+            bool done = false;
+            // (FP8 rows go one by one: their single-row kernel is the tensor-core one, and the rows must match it bit for bit)
+            if (t > 1 && find(jobs[j].w)->dev.fmt != B2_FMT_F8E4M3) {
+                Weight* w = find(jobs[j].w);
+                Weight* u = jobs[j].up ? find(jobs[j].up) : nullptr;
+                if (jobs[j].up && (!u || u->dev.fmt != w->dev.fmt || u->dev.n_in != w->dev.n_in || u->dev.n_out != w->dev.n_out))
+                    return fail(B2_DECLINED, "[b200qmm: matvec_rows: the pair's matrices differ in shape or format]");
+                const bool f8 = w->dev.fmt == B2_FMT_F8E4M3;
+                const size_t stride = (xplanes_bytes(n_in) + 255) / 256 * 256;
+                XPlanes xp0{};
+                e = cudaSuccess;
+                if (!f8) {
+                    e = xplanes.reserve(t * stride);
+                    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
+                    if (j == 0 || prepared_k != 0) {
+                        e = launch_xplanes_rows((const float*)x_dev.p, t, n_in, (uint8_t*)xplanes.p, stride, stream);
+                        launches++;
+                        prepared_k = 0;  // the scratch now holds several rows' planes, not one prepared vector
+                    }
+                    xp0 = xplanes_at(xplanes.p, n_in);
+                }
+                if (e == cudaSuccess)
+                    e = launch_gemv_multi(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, xp0, stride, (float*)y_dev.p, jobs[j].n_out, (int)t,
+                                          jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE, sm_count, stream);
+                if (e == cudaSuccess) {
+                    launches++;
+                    done = true;
+                } else if (e != cudaErrorInvalidValue) {
+                    return cuda_fail(e, "gemv (several rows)");
+                }
+            }
+            for (size_t i = 0; i < t && !done; i++) {
                 int rc = matvec_dev(jobs[j].w, jobs[j].up, (const float*)x_dev.p + i * n_in, (float*)y_dev.p + i * jobs[j].n_out,
                                     jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE, nullptr);
                 if (rc) return rc;

@@ -63,10 +63,18 @@ __global__ void __launch_bounds__(256) norm_planes_kernel(const float* __restric
 //   2. issue the loads of the warp's first weights, which depend on nothing the previous kernel wrote,
 //   3. wait for the previous kernel (it wrote the planes / the vector), stage them in shared memory,
 //   4. stream the rows.
-template <class F, bool PAIR, bool XF32>
-__global__ void __launch_bounds__(GEMV_THREADS, 3)
+// NT tokens at once (Backend::matvec_rows, up to four; the reference's dmvk_* kernels, src/cuda_decode.cu:176-232): the
+// weights are read once and every token keeps its own accumulators, with the single-token arithmetic, so each row of the
+// result equals the one-token result bit for bit. Token i's vector / planes sit multi.x_stride after token i - 1's
+// (floats for the f32 vector, bytes for the planes), its outputs multi.y_stride floats after.
+struct GemvMulti {
+    size_t x_stride, y_stride;
+};
+
+template <class F, bool PAIR, bool XF32, int NT>
+__global__ void __launch_bounds__(GEMV_THREADS, NT > 2 ? 2 : 3)
 gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, float* __restrict__ y, int mode,
-            const float* __restrict__ gate, NormScale ns, GemvBatch batch) {
+            const float* __restrict__ gate, NormScale ns, GemvBatch batch, GemvMulti multi) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     if (batch.n) {  // entry blockIdx.y of a batch: its matrix of the stack, its planes, its output
@@ -92,58 +100,71 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
     if (r_first < n_out) fetch(r_first, 0);
     pdl_wait();
 
-    XS xs;
-    xs.K = K;
-    if constexpr (XF32) {
-        float* xf = (float*)smem;
-        for (int g = threadIdx.x; g < K / 4; g += GEMV_THREADS) ((float4*)xf)[swz(g)] = ((const float4*)x)[g];
-        xs.xf = xf;
-        xs.p0 = nullptr;
-        xs.sx = nullptr;
-        xs.v16 = nullptr;
-    } else {
-        const int slots = K / 16;  // per plane
-        const uint4* src = (const uint4*)xp.planes;
-        uint4* dst = (uint4*)smem;
-        for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
-            int p = i / slots, g = i - p * slots;
-            dst[p * slots + swz(g)] = src[i];
+    XS xs[NT];
+    const size_t per_tok = ((XF32 ? (size_t)K * 4 : xplanes_bytes((size_t)K)) + 127) / 128 * 128;
+#pragma unroll
+    for (int tk = 0; tk < NT; tk++) {
+        uint8_t* sm = smem + (size_t)tk * per_tok;
+        xs[tk].K = K;
+        if constexpr (XF32) {
+            float* xf = (float*)sm;
+            const float* xt = x + (size_t)tk * multi.x_stride;
+            for (int g = threadIdx.x; g < K / 4; g += GEMV_THREADS) ((float4*)xf)[swz(g)] = ((const float4*)xt)[g];
+            xs[tk].xf = xf;
+            xs[tk].p0 = nullptr;
+            xs[tk].sx = nullptr;
+            xs[tk].v16 = nullptr;
+        } else {
+            const XPlanes xpt = tk == 0 ? xp : xplanes_at((uint8_t*)xp.planes + (size_t)tk * multi.x_stride, (size_t)K);
+            const int slots = K / 16;  // per plane
+            const uint4* src = (const uint4*)xpt.planes;
+            uint4* dst = (uint4*)sm;
+            for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
+                int p = i / slots, g = i - p * slots;
+                dst[p * slots + swz(g)] = src[i];
+            }
+            float2* sx = (float2*)(sm + 3 * (size_t)K);
+            for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xpt.xs[b], xpt.xsum[b]);
+            int32_t* v16 = (int32_t*)(sx + K / 32);
+            for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xpt.v16[b];
+            xs[tk].p0 = sm;
+            xs[tk].sx = sx;
+            xs[tk].v16 = v16;
+            xs[tk].xf = nullptr;
         }
-        float2* sx = (float2*)(smem + 3 * (size_t)K);
-        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
-        int32_t* v16 = (int32_t*)(sx + K / 32);
-        for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xp.v16[b];
-        xs.p0 = smem;
-        xs.sx = sx;
-        xs.v16 = v16;
-        xs.xf = nullptr;
     }
     __syncthreads();
     const float kscale = norm_scale_factor(ns, lane);
     for (size_t r0 = r_first; r0 < n_out; r0 += r_step) {
-        float accA = 0.0f, accB = 0.0f;
+        float accA[NT], accB[NT];
+#pragma unroll
+        for (int tk = 0; tk < NT; tk++) accA[tk] = accB[tk] = 0.0f;
         for (int it = 0; it < iters; it++) {
             if (!F::active(K, it, lane)) continue;
             if (it > 0 || r0 != r_first) fetch(r0, it);  // the first step's loads were issued before the wait
-            F::dot2(na, nb, xs, it, lane, accA, accB);
-        }
-        accA = warp_sum(accA) * kscale;
-        accB = warp_sum(accB) * kscale;
-        if (lane == 0) {
-            if (PAIR) {
-                y[r0] = (mode == B2_MODE_SILU_PAIR ? silu(accA) : gelu_tanh(accA)) * accB;
-            } else {
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    if (r0 + r >= n_out) break;
-                    const float a = r ? accB : accA;
-                    float* o = y + r0 + r;
-                    if (mode == B2_MODE_STORE)
-                        *o = a;
-                    else if (mode == B2_MODE_ADD)
-                        *o += a;
-                    else
-                        *o += a * (1.0f / (1.0f + __expf(-gate[0])));
+            for (int tk = 0; tk < NT; tk++) F::dot2(na, nb, xs[tk], it, lane, accA[tk], accB[tk]);
+        }
+#pragma unroll
+        for (int tk = 0; tk < NT; tk++) {
+            const float sa = warp_sum(accA[tk]) * kscale, sb = warp_sum(accB[tk]) * kscale;
+            float* yt = y + (size_t)tk * multi.y_stride;
+            if (lane == 0) {
+                if (PAIR) {
+                    yt[r0] = (mode == B2_MODE_SILU_PAIR ? silu(sa) : gelu_tanh(sa)) * sb;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        if (r0 + r >= n_out) break;
+                        const float a = r ? sb : sa;
+                        float* o = yt + r0 + r;
+                        if (mode == B2_MODE_STORE)
+                            *o = a;
+                        else if (mode == B2_MODE_ADD)
+                            *o += a;
+                        else
+                            *o += a * (1.0f / (1.0f + __expf(-gate[0])));
+                    }
                 }
             }
         }
@@ -560,12 +581,12 @@ cudaError_t launch_mma4(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
     return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, ns);
 }
 
-template <class F, bool XF32>
+template <class F, bool XF32, int NT = 1>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                       int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
-    size_t smem = XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in);
+                       int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi = GemvMulti{0, 0}) {
+    size_t smem = (((XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128) * NT;
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
-    auto kern = pair ? gemv_kernel<F, true, XF32> : gemv_kernel<F, false, XF32>;
+    auto kern = pair ? gemv_kernel<F, true, XF32, NT> : gemv_kernel<F, false, XF32, NT>;
     static size_t smem_set[2] = {48 * 1024, 48 * 1024};  // largest size asked for so far, per kernel: later launches (and captures) skip the call
     if (smem > smem_set[pair]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -577,7 +598,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns, GemvBatch{});
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns, GemvBatch{}, multi);
 }
 
 }  // namespace
@@ -617,8 +638,8 @@ template <class F>
 static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
                                       cudaStream_t st) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
-    auto kern = pair ? gemv_kernel<F, true, false> : gemv_kernel<F, false, false>;
-    const size_t smem = xplanes_bytes(w.n_in);
+    auto kern = pair ? gemv_kernel<F, true, false, 1> : gemv_kernel<F, false, false, 1>;
+    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -629,7 +650,7 @@ static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, c
     if (gx > cap) gx = cap;
     XPlanes none{};
     kern<<<dim3((unsigned)gx, (unsigned)batch), GEMV_THREADS, smem, st>>>(w, pair ? *up : w, nullptr, none, y, mode, nullptr,
-                                                                         NormScale{nullptr, 0, 0.0f, 0.0f}, b);
+                                                                         NormScale{nullptr, 0, 0.0f, 0.0f}, b, GemvMulti{0, 0});
     return cudaGetLastError();
 }
 
@@ -639,6 +660,34 @@ cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const G
     if (w.fmt == B2_FMT_MLX4) return launch_batched_fmt<FmtMLX4>(w, up, b, batch, y, mode, sm_count, st);
     if (w.fmt == B2_FMT_Q4_K) return launch_batched_fmt<FmtQ4K>(w, up, b, batch, y, mode, sm_count, st);
     return cudaErrorInvalidValue;
+}
+
+template <int NT>
+static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, int sm_count,
+                                   cudaStream_t st, GemvMulti m) {
+    const NormScale none{nullptr, 0, 0.0f, 0.0f};
+    switch (w.fmt) {
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, XPlanes xp, size_t xp_stride, float* y,
+                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st) {
+    const bool f8 = w.fmt == B2_FMT_F8E4M3;
+    const size_t per = (((f8 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128);
+    if (nt < 1 || nt > 4 || per * nt > 200 * 1024) return cudaErrorInvalidValue;
+    const GemvMulti m{f8 ? x_stride : xp_stride, y_stride};
+    switch (nt) {
+        case 1: return launch_multi_nt<1>(w, up, x, xp, y, mode, sm_count, st, m);
+        case 2: return launch_multi_nt<2>(w, up, x, xp, y, mode, sm_count, st, m);
+        case 3: return launch_multi_nt<3>(w, up, x, xp, y, mode, sm_count, st, m);
+        default: return launch_multi_nt<4>(w, up, x, xp, y, mode, sm_count, st, m);
+    }
 }
 
 cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl) {

@@ -87,6 +87,11 @@ cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const G
                                 cudaStream_t st);
 // Planes of `rows` vectors of K values (row r at x + r * K) into blocks `stride` bytes apart.
 cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st);
+// nt (1..4) tokens in one launch, the weights read once: token i's f32 vector at x + i * x_stride (FP8 weights) or planes
+// at xp + i * xp_stride bytes (the other formats), outputs at y + i * y_stride. Each token's result equals its
+// single-token result bit for bit. cudaErrorInvalidValue if the tokens' vectors do not fit in shared memory together.
+cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, XPlanes xp, size_t xp_stride, float* y,
+                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st);
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 
