@@ -206,8 +206,28 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
                 us2 = ev[0].elapsed_time(ev[1]) * 1e3 / (n * 5)
                 out[name].update({"us_kernel_only": us2, "gbs_kernel_only": algo / us2 / 1e3,
                                   "frac_kernel_only": algo / us2 / 1e3 / peaks["hbm_gbs"]})
+                # the same as a dependent-launch chain (how a decode step queues its products): every kernel may start while
+                # the one ahead drains, and the 4-bit kernels fetch their first weights before they wait for it
+                be.set_chained(True)
+                g3 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g3):
+                    be.set_stream(torch.cuda.current_stream().cuda_stream)
+                    for i in range(n):
+                        be.matvec_prepared_dev(devs[i % copies], x, y)
+                be.set_stream(main_stream)
+                be.set_chained(False)
+                g3.replay()
+                torch.cuda.synchronize()
+                ev[0].record()
+                for _ in range(5):
+                    g3.replay()
+                ev[1].record()
+                torch.cuda.synchronize()
+                us3 = ev[0].elapsed_time(ev[1]) * 1e3 / (n * 5)
+                out[name].update({"us_chained": us3, "gbs_chained": algo / us3 / 1e3, "frac_chained": algo / us3 / 1e3 / peaks["hbm_gbs"]})
             except Exception as e:
                 be.set_stream(main_stream)
+                be.set_chained(False)
                 out[name]["kernel_only_error"] = str(e)
         for d in devs:
             d.free()

@@ -88,6 +88,12 @@ const char* b2_open_error(void);
 /* Kernels are launched on `cuda_stream` (a cudaStream_t / CUstream; NULL = the default stream,
  * which is what src/cuda.rs:609-629 uses). Host-buffer entry points synchronize that stream. */
 int b2_set_stream(b2_ctx* ctx, void* cuda_stream);
+/* No counterpart in the reference. While on, the device-resident matrix-vector calls (b2_matvec_dev,
+ * b2_matvec_prepared_dev, b2_prepare_x_dev) launch with the programmatic-dependent-launch attribute: each kernel may
+ * start, and fetch its first weights, while the kernel ahead of it on the stream drains; it waits for that kernel before
+ * it reads the vector or writes its output, so results are unchanged. Meant for a caller that queues a token's
+ * products back to back (the decode plan does this by itself). Off by default. */
+int b2_set_chained(b2_ctx* ctx, int on);
 /* `Backend::stats`, src/cuda.rs:1120-1132: cumulative copy-in / kernel / copy-out time as text. */
 const char* b2_stats(b2_ctx* ctx);
 /* Count of kernel launches issued by this context since it was opened. */

@@ -164,6 +164,10 @@ class Backend:
     def stats(self) -> str:
         return self._L.b2_stats(self._ctx).decode()
 
+    def set_chained(self, on: bool) -> None:
+        """Device-resident matrix-vector calls launch as a dependent chain (each kernel may start while the one ahead drains)."""
+        self._check(self._L.b2_set_chained(self._ctx, int(on)))
+
     def check_status(self) -> None:
         self._check(self._L.b2_check_status(self._ctx))
 

@@ -59,6 +59,7 @@ class Backend {
     int device = 0;
     int sm_count = 148;
     cudaStream_t stream = nullptr;
+    bool chained = false;  // b2_set_chained
     std::mutex mu;  // calls serialize, like the staging lock of src/cuda.rs:430,1443
     std::string err;
     std::string stats_text;
@@ -330,7 +331,7 @@ class Backend {
         if (!x_dev_ || n_in == 0 || n_in % 32) return fail(B2_ERR_ARG, "[b200qmm: prepare_x: n_in must be a positive multiple of 32]");
         cudaError_t e = xplanes.reserve(xplanes_bytes(n_in));
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
-        e = launch_xplanes(x_dev_, n_in, xplanes_at(xplanes.p, n_in), stream);
+        e = launch_xplanes(x_dev_, n_in, xplanes_at(xplanes.p, n_in), stream, chained);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "xplanes");
         prepared_k = n_in;
@@ -356,7 +357,7 @@ class Backend {
             if (prepared_k != w->dev.n_in) return fail(B2_ERR_ARG, "[b200qmm: matvec: no planes prepared for n_in = %zu (b2_prepare_x_dev)]", w->dev.n_in);
             xp = xplanes_at(xplanes.p, w->dev.n_in);
         }
-        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream);
+        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "gemv");
         return B2_OK;
@@ -964,6 +965,12 @@ B2_EXPORT void b2_close(b2_ctx* ctx) {
 
 B2_EXPORT const char* b2_last_error(b2_ctx* ctx) { return ctx ? ctx->be.err.c_str() : "[b200qmm: null context]"; }
 B2_EXPORT const char* b2_open_error(void) { return g_open_error.c_str(); }
+
+B2_EXPORT int b2_set_chained(b2_ctx* ctx, int on) {
+    LOCKED(ctx);
+    ctx->be.chained = on != 0;
+    return B2_OK;
+}
 
 B2_EXPORT int b2_set_stream(b2_ctx* ctx, void* s) {
     LOCKED(ctx);
