@@ -229,6 +229,20 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
                 be.set_stream(main_stream)
                 be.set_chained(False)
                 out[name]["kernel_only_error"] = str(e)
+        if fmt == "mlx4":
+            # the reference's own CUDA kernel for this product (dmv_q4a, compiled for sm_100a into oracle/_ref where the
+            # reference's tree was present at build time), host-launched back to back on the same matrix
+            try:
+                from oracle import oracle as O
+
+                L = O.ref_cuda()
+                if L is not None:
+                    m = O.Matrix.from_mlx_q4(ref.w.reshape(-1), ref.scales.reshape(-1), ref.biases.reshape(-1), n_out, n_in, ref.group)
+                    ms = O.ref_dmv_q4a(L, m, x, y, iters=200, stream=torch.cuda.current_stream().cuda_stream)
+                    out[name]["reference_cuda_kernel"] = {"kernel": "dmv_q4a (src/cuda_decode.cu), 4 warps x 4 rows per block", "us": ms * 1e3,
+                                                          "note": "one matrix, 200 launches back to back: its 9.5 MB stay in L2, which favours it"}
+            except Exception as e:
+                out[name]["reference_cuda_kernel_error"] = str(e)
         for d in devs:
             d.free()
     return out

@@ -723,6 +723,21 @@ ORC_API void* orc_matrix_gguf(int kind, const uint8_t* data, size_t n_out, size_
 }
 
 ORC_API void orc_matrix_free(void* m) { delete (Matrix*)m; }
+// The Q4 + offsets arrays of a matrix built by orc_matrix_from_mlx_q4, as the reference's kernels take them
+// (src/quant.rs:427-440): nibbles [n_out n_in / 2], f16 scales [n_out n_in / 32], bf16 offsets [n_out n_in / group].
+ORC_API int orc_matrix_q4_parts(void* mp, const uint8_t** q, size_t* q_bytes, const uint16_t** scales, size_t* n_scales, const uint16_t** offsets,
+                                size_t* n_offsets, size_t* group) {
+    const Matrix& m = *(Matrix*)mp;
+    if (m.format != 0) return -1;
+    *q = m.q.data();
+    *q_bytes = m.q.size();
+    *scales = m.scales.data();
+    *n_scales = m.scales.size();
+    *offsets = m.offsets.data();
+    *n_offsets = m.offsets.size();
+    *group = m.group;
+    return 0;
+}
 ORC_API size_t orc_matrix_bytes(void* m) { return ((Matrix*)m)->bytes(); }
 
 ORC_API void orc_matrix_dequantize_rows(void* m, size_t r0, size_t r1, float* out) { dequantize_rows(*(Matrix*)m, r0, r1, out); }

@@ -68,6 +68,7 @@ def lib() -> C.CDLL:
             "orc_matrix_gguf": (vp, [i32, vp, sz, sz, vp, sz, sz]),
             "orc_matrix_free": (None, [vp]),
             "orc_matrix_bytes": (sz, [vp]),
+            "orc_matrix_q4_parts": (i32, [vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(vp), C.POINTER(sz), C.POINTER(vp), C.POINTER(sz), C.POINTER(sz)]),
             "orc_matrix_dequantize_rows": (None, [vp, sz, sz, vp]),
             "orc_mlx_dequant_row": (None, [vp, vp, vp, sz, vp, sz]),
             "orc_matmul_cpu": (None, [vp, vp, sz, vp, i32]),
@@ -167,6 +168,18 @@ class Matrix:
 
     def bytes(self) -> int:
         return lib().orc_matrix_bytes(self.h)
+
+    def q4_parts(self):
+        """(nibbles u8, f16 scale bits u16, bf16 offset bits u16, group) of a matrix made by ``from_mlx_q4``: the arrays
+        the reference's kernels take (copies)."""
+        q, s, o = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        nq, ns, no, g = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+        if lib().orc_matrix_q4_parts(self.h, C.byref(q), C.byref(nq), C.byref(s), C.byref(ns), C.byref(o), C.byref(no), C.byref(g)) != 0:
+            raise ValueError("not a Q4 matrix")
+        qa = np.ctypeslib.as_array(C.cast(q, C.POINTER(C.c_uint8)), (nq.value,)).copy()
+        sa = np.ctypeslib.as_array(C.cast(s, C.POINTER(C.c_uint16)), (ns.value,)).copy()
+        oa = np.ctypeslib.as_array(C.cast(o, C.POINTER(C.c_uint16)), (no.value,)).copy()
+        return qa, sa, oa, g.value
 
     def dequantize_rows(self, r0: int = 0, r1: int | None = None) -> np.ndarray:
         r1 = self.n_out if r1 is None else r1
@@ -346,3 +359,33 @@ class Llama:
         lib().orc_llama_step(C.byref(self.cfg), self._mats, self._normp, _p(self.kc), _p(self.vc), self.max_len, pos, _p(x), _p(cs), _p(hidden),
                              _p(logits) if logits is not None else None, int(exact), threads or cpu_threads())
         return hidden, logits
+
+
+# ---- the reference's own CUDA kernels (oracle/_ref/libref_cuda.so, built by build_ref.py where the reference's tree is) ----
+def ref_cuda():
+    """The harness library around the reference's CUDA decode kernels, or None when it was not built."""
+    from . import build_ref
+
+    path = build_ref.build()
+    if path is None or not Path(path).exists():
+        return None
+    L = C.CDLL(str(path))
+    L.ref_dmv_q4a.restype = C.c_int
+    L.ref_dmv_q4a.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_int,
+                              C.POINTER(C.c_float), C.c_void_p]
+    return L
+
+
+def ref_dmv_q4a(L, m: Matrix, x, y, iters: int = 1, stream: int = 0) -> float:
+    """The reference's one-token affine-Q4 matvec (src/cuda_decode.cu dmv_q4a) on the current CUDA device: ``m`` from
+    ``Matrix.from_mlx_q4``, ``x`` / ``y`` torch CUDA tensors. Returns the mean device milliseconds of a launch."""
+    import torch
+
+    q, s, o, group = m.q4_parts()
+    dq, ds, do = (torch.from_numpy(a).cuda() for a in (q, s.view(np.int16), o.view(np.int16)))
+    ms = C.c_float()
+    rc = L.ref_dmv_q4a(dq.data_ptr(), ds.data_ptr(), do.data_ptr(), m.n_in // group, group // 32, x.data_ptr(), y.data_ptr(), m.n_out, m.n_in, iters,
+                       C.byref(ms), stream)
+    if rc != 0:
+        raise RuntimeError(f"the reference kernel failed with CUDA error {rc}")
+    return ms.value
