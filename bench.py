@@ -248,6 +248,58 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
     return out
 
 
+def ref_cuda_extras(be, torch):
+    """The reference's own CUDA kernels (compiled for sm_100a into oracle/_ref where the reference's tree was present at
+    build time) beside this repository's on the same device: the prefill product at config 1's shape on an MLX 4-bit
+    matrix (the format gemm_q4a takes), and the reference's decode attention at config 2's shape."""
+    import numpy as np
+
+    import oxinfer_b200 as ob
+    from oracle import oracle as O
+    from oxinfer_b200 import synth
+
+    L = O.ref_cuda()
+    if L is None:
+        return {"unavailable": "oracle/_ref/libref_cuda.so was not built"}
+    out = {}
+    ref = synth.mlx4(N_OUT, K_IN, 77)
+    m = O.Matrix.from_mlx_q4(ref.w.reshape(-1), ref.scales.reshape(-1), ref.biases.reshape(-1), N_OUT, K_IN, ref.group)
+    dev = be.upload(ref, N_OUT, K_IN)
+    x = torch.from_numpy(synth.activations(M_TOK, K_IN, 78)).cuda()
+    y_ref = torch.empty((M_TOK, N_OUT), device="cuda")
+    ms_ref = O.ref_gemm_q4a(L, m, x, y_ref, iters=5)
+    x16 = x.to(torch.float16)
+    y = torch.empty((M_TOK, N_OUT), device="cuda")
+    for _ in range(3):
+        assert be.matmul_dev(dev, x16, y)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        be.matmul_dev(dev, x16, y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    scale = float(y_ref.abs().max())
+    out["prefill_mlx4_512x4096x14336"] = {
+        "reference_kernel": "gemm_q4a (KERNEL_SRC of src/cuda.rs): 64 x 64 tiles, f32 FMA", "reference_us": ms_ref * 1e3,
+        "reference_tflops": FLOP_PER_STEP / (ms_ref * 1e-3) / 1e12, "this_us": ms * 1e3, "this_tflops": FLOP_PER_STEP / (ms * 1e-3) / 1e12,
+        "max_abs_difference_over_max": float((y - y_ref).abs().max()) / scale,
+        "note": "one 29 MB matrix on both sides, launches back to back (weights stay in L2 for both)"}
+    dev.free()
+    nh, nkv, hd, pos = 32, 8, 128, 2048
+    rng = np.random.default_rng(5)
+    kc = torch.from_numpy(rng.standard_normal((pos + 1, nkv * hd)).astype(np.float32)).cuda()
+    vc = torch.from_numpy(rng.standard_normal((pos + 1, nkv * hd)).astype(np.float32)).cuda()
+    q = torch.from_numpy(rng.standard_normal(nh * hd).astype(np.float32)).cuda()
+    o = torch.empty(nh * hd, device="cuda")
+    sp = torch.tensor([pos, pos, 1, 0], dtype=torch.int32, device="cuda")
+    ms_att = O.ref_attend(L, q, kc, vc, o, sp, nh, nkv, hd, hd ** -0.5, iters=100)
+    out["decode_attention_32h_8kv_128_ctx2048"] = {
+        "reference_kernels": "dattn_4_4 + dattn_combine (src/cuda_decode.cu)", "reference_us": ms_att * 1e3,
+        "note": "this repository's attend kernel at the same shape: see the decode step's launch list under profiles/"}
+    return out
+
+
 def moe_extras(be, torch, peaks):
     """Config 3: the routed-expert layer (128 experts, top-8, hidden 2048, expert intermediate 768, MLX 4-bit g64) at token
     batches 1 / 64 / 512 / 4096, x and y on the device, routes on the host as in Backend::moe. Router logits N(0,1) plus a
@@ -463,6 +515,9 @@ def run_b200(args, rank, world, local_rank):
         fn = moe_extras if args.section == "moe" else fp8_extras
         print(json.dumps({"extra": {args.section: fn(be, torch, peaks)}}), flush=True)
         return
+    if args.section == "refcuda":
+        print(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}), flush=True)
+        return
     if args.section == "decode":
         d = decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
         if rank == 0:
@@ -608,7 +663,7 @@ def run_b200(args, rank, world, local_rank):
             except Exception as e:  # the headline line must still print
                 line["extra"] = {"gemv_error": str(e)}
             for name, fn in (("moe", lambda: moe_extras(be, torch, peaks)), ("fp8", lambda: fp8_extras(be, torch, peaks)),
-                             ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2))):
+                             ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2)), ("reference_cuda", lambda: ref_cuda_extras(be, torch))):
                 try:
                     line["extra"][name] = fn()
                 except Exception as e:
@@ -632,7 +687,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")
     ap.add_argument("--tokens", type=int, default=256, help="with --section decode: tokens to generate")
     ap.add_argument("--kv-f16", action="store_true", help="with --section decode: f16 KV caches instead of the reference's f32")
-    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "moe", "fp8"],
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "moe", "fp8", "refcuda"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -373,7 +373,62 @@ def ref_cuda():
     L.ref_dmv_q4a.restype = C.c_int
     L.ref_dmv_q4a.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_int,
                               C.POINTER(C.c_float), C.c_void_p]
+    vp, u, f = C.c_void_p, C.c_uint, C.c_float
+    for name, args in (("ref_norm", [vp, vp, vp, u, u, f, f, u, vp]),
+                       ("ref_qk_rope", [vp] * 10 + [u] * 5 + [f, vp]),
+                       ("ref_attend", [vp] * 6 + [u, u, u, f, u, C.c_int, C.POINTER(f), vp]),
+                       ("ref_glu", [vp, vp, vp, u, u, vp]),
+                       ("ref_gemm_q4a", [vp, vp, vp, u, u, vp, vp, u, u, u, C.c_int, C.POINTER(f), vp])):
+        fn = getattr(L, name)
+        fn.restype, fn.argtypes = C.c_int, args
     return L
+
+
+def _ref_rc(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(f"the reference kernel failed with CUDA error {rc}")
+
+
+def ref_norm(L, x, out, w, eps: float, pre: float = 1.0, add: bool = False) -> None:
+    """dnorm (src/cuda_decode.cu) over the rows of the torch CUDA tensor ``x`` [rows][n]; ``w`` a tensor or None."""
+    rows, n = x.shape
+    _ref_rc(L.ref_norm(x.data_ptr(), out.data_ptr(), w.data_ptr() if w is not None else None, n, rows, eps, pre, int(add), None))
+
+
+def ref_qk_rope(L, qkv, q_out, kc, vc, k_out, v_out, qn, kn, cs, sp, nh: int, nkv: int, hd: int, half_rot: int, interleaved: bool,
+                eps: float) -> None:
+    """dqk_rope: caches ``kc`` / ``vc`` are [max_len][nkv][hd] f32 tensors, ``sp`` an int32 tensor of 4 with sp[0] = position."""
+    _ref_rc(L.ref_qk_rope(qkv.data_ptr(), q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), k_out.data_ptr(), v_out.data_ptr(),
+                          qn.data_ptr() if qn is not None else None, kn.data_ptr() if kn is not None else None, cs.data_ptr(), sp.data_ptr(),
+                          nh, nkv, hd, half_rot, int(interleaved), eps, None))
+
+
+def ref_attend(L, q, kc, vc, out, sp, nh: int, nkv: int, hd: int, scale: float, window: int = 0, iters: int = 0) -> float:
+    """dattn_* + dattn_combine over positions 0 .. sp[0]; returns the mean device milliseconds of the pair (``iters`` > 0)."""
+    import torch
+
+    part = torch.zeros(nh * 64 * (hd + 2), device=q.device)
+    ms = C.c_float()
+    _ref_rc(L.ref_attend(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), part.data_ptr(), sp.data_ptr(), nh, nkv, hd, scale, window,
+                         iters, C.byref(ms), None))
+    return ms.value
+
+
+def ref_glu(L, g, u, out, gelu: bool = False) -> None:
+    _ref_rc(L.ref_glu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), int(gelu), None))
+
+
+def ref_gemm_q4a(L, m: Matrix, x, y, iters: int = 0) -> float:
+    """The reference's prefill kernel gemm_q4a: ``x`` [tokens][n_in], ``y`` [tokens][n_out] torch CUDA f32 tensors, tokens and
+    n_out multiples of 64. Returns the mean device milliseconds of a launch (``iters`` > 0)."""
+    import torch
+
+    q, s, o, group = m.q4_parts()
+    dq, ds, do = (torch.from_numpy(a).cuda() for a in (q, s.view(np.int16), o.view(np.int16)))
+    ms = C.c_float()
+    _ref_rc(L.ref_gemm_q4a(dq.data_ptr(), ds.data_ptr(), do.data_ptr(), m.n_in // group, group // 32, x.data_ptr(), y.data_ptr(), m.n_out, m.n_in,
+                           x.shape[0], iters, C.byref(ms), None))
+    return ms.value
 
 
 def ref_dmv_q4a(L, m: Matrix, x, y, iters: int = 1, stream: int = 0) -> float:

@@ -179,7 +179,7 @@ constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
 template <class F, bool PAIR>
 __global__ void __launch_bounds__(GEMV_THREADS, 3)
 gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status,
-                  NormScale ns) {
+                  NormScale ns, EpiPlanes epi) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bars[GEMV_WARPS * RING_SLOTS];
     pdl_launch_dependents();
@@ -221,12 +221,12 @@ gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, 
     xs.v16 = (const int32_t*)(xs.sx + K / 32);
     xs.xf = nullptr;
     const float kscale = norm_scale_factor(ns, lane);
-    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true, kscale) && status) atomicExch(status, 5u);
+    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true, kscale, epi) && status) atomicExch(status, 5u);
 }
 
 template <class F>
 cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                        cudaStream_t st, bool pdl, NormScale ns) {
+                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv4_ring_kernel<F, true> : gemv4_ring_kernel<F, false>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + RING_BYTES;
@@ -241,7 +241,7 @@ cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
     size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns);
+    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns, epi);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -696,8 +696,28 @@ cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t
     return launch_k(norm_planes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, w, pre, (int)K, out, partial);
 }
 
+static bool ring_enabled() {
+    static const bool ring = [] {
+        const char* e = getenv("B2_GEMV_RING");
+        return !e || atoi(e) != 0;
+    }();
+    return ring;
+}
+static bool ring_fits(const WeightDev& w) {
+    return (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024;
+}
+bool gemv_takes_epilogue(const WeightDev& w) {
+    const char* m = getenv("B2_GEMV_MMA4");
+    return ring_enabled() && ring_fits(w) && w.n_out % 32 == 0 && !(m && atoi(m) != 0);
+}
+
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl, NormScale ns) {
+                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+    if (epi.counters) {  // only the ring form carries the epilogue, chained or not
+        if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+    }
     // The tensor-core form of the 4-bit products is parity-green but not yet the faster one (14336 x 4096: 15.9 us against
     // 11.2; a decode token 2.52 ms against 2.37): its CTA-per-tile mapping leaves 896 tiles on 444 CTAs two or three rounds
     // deep and small products are bound by the prologue either way. It stays selectable (B2_GEMV_MMA4: 1 everywhere,
@@ -711,16 +731,12 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
         if (w.fmt == B2_FMT_MLX4) return launch_mma4<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
         return launch_mma4<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
     }
-    static const bool ring = [] {
-        const char* e = getenv("B2_GEMV_RING");
-        return !e || atoi(e) != 0;
-    }();
     // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
-    if (ring && pdl && (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024) {
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
+    if (ring_enabled() && pdl && ring_fits(w)) {
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }
     switch (w.fmt) {
         case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);

@@ -6,6 +6,7 @@
 #pragma once
 #include "async_copy.cuh"
 #include "gemv_core.cuh"
+#include "xplanes.cuh"
 
 namespace b2 {
 namespace gemv_core {
@@ -60,12 +61,36 @@ __device__ __forceinline__ void ring_prime(const WeightDev& w, const WeightDev& 
     for (uint32_t s = 0; s + 1 < (uint32_t)ring.S && s < T; s++) ring_issue<PAIR>(w, w2, ring, r_first, r_step, s);
 }
 
+// EpiPlanes: lane 0 of the calling warp has just written rows r0 .. r0 + n - 1 of y (all in one block of 32). The add
+// releases those writes and acquires the other warps'; whoever brings the block's count to 32 splits the block.
+__device__ __forceinline__ void epi_rows(const EpiPlanes& epi, const float* y, size_t r0, uint32_t n, int n_out, int lane) {
+    const int blk = (int)(r0 >> 5);
+    uint32_t done = 0;
+    if (lane == 0) {
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(done) : "l"(epi.counters + blk), "r"(n) : "memory");
+        done += n;
+    }
+    done = __shfl_sync(0xffffffffu, done, 0);
+    if (done != 32u) return;
+    __syncwarp();  // the other lanes' reads come after lane 0's acquire
+    const float v = __ldcg(y + (size_t)blk * 32 + lane) * epi.pre;
+    if (epi.partial) {
+        float s = v * v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) epi.partial[blk] = s;
+    }
+    xplanes_block(epi.w ? v * epi.w[(size_t)blk * 32 + lane] : v, blk, lane, n_out, epi.out);
+    if (lane == 0) epi.counters[blk] = 0;
+}
+
 // Rows r_first, r_first + r_step, ... (pairs of rows, or the same row of w and w2 with PAIR) by one warp.
 // False: a wait on a copy ran into its limit (the caller reports it and stops).
 template <class F, bool PAIR>
 __device__ __forceinline__ bool gemv4_ring(const WeightDev& w, const WeightDev& w2, const XS& xs, float* __restrict__ y, const int mode,
                                            const float* __restrict__ gate, WarpRing& ring, const size_t r_first, const size_t r_step,
-                                           const int lane, const bool primed = false, const float kscale = 1.0f) {
+                                           const int lane, const bool primed = false, const float kscale = 1.0f,
+                                           const EpiPlanes epi = EpiPlanes{nullptr, XPlanes{nullptr, nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f}) {
     using namespace acopy;
     const int K = (int)w.n_in, nblk = K / 256, iters = (nblk + 7) / 8;
     const size_t n_out = w.n_out;
@@ -109,6 +134,7 @@ __device__ __forceinline__ bool gemv4_ring(const WeightDev& w, const WeightDev& 
                     }
                 }
             }
+            if (epi.counters) epi_rows(epi, y, r0, PAIR ? 1u : (uint32_t)min((size_t)2, n_out - r0), (int)n_out, lane);
             accA = accB = 0.0f;
             it = 0;
             r0 += r_step;

@@ -67,10 +67,25 @@ struct NormScale {
 };
 // planes(x * pre * w) and the blocks' sums of squares of x * pre; K a multiple of 32, w may be null.
 cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl = false);
+// What a product may do with its finished output, so that the kernel which would split it for the next product is not
+// launched: every warp counts the rows it has written into its block of 32 (`counters`, one word per block, zero between
+// launches), and the warp that completes a block reads the block back and writes the planes of y * pre * w (w may be
+// null) and, with `partial`, the block's sum of squares of y * pre: what launch_xplanes / launch_norm_planes would have
+// written, bit for bit. n_out must be a multiple of 32. counters == nullptr: nothing.
+struct EpiPlanes {
+    uint32_t* counters;
+    XPlanes out;
+    const float* w;
+    float* partial;
+    float pre;
+};
+// Whether launch_gemv takes an EpiPlanes for this matrix (the 4-bit formats whose planes and rings fit in shared memory).
+bool gemv_takes_epilogue(const WeightDev& w);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f});
+                        int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f},
+                        EpiPlanes epi = EpiPlanes{nullptr, XPlanes{nullptr, nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
 // A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
 // of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
 // bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),
