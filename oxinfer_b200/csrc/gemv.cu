@@ -116,20 +116,10 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
             xs[tk].v16 = nullptr;
         } else {
             const XPlanes xpt = tk == 0 ? xp : xplanes_at((uint8_t*)xp.planes + (size_t)tk * multi.x_stride, (size_t)K);
-            const int slots = K / 16;  // per plane
-            const uint4* src = (const uint4*)xpt.planes;
-            uint4* dst = (uint4*)sm;
-            for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
-                int p = i / slots, g = i - p * slots;
-                dst[p * slots + swz(g)] = src[i];
-            }
-            float2* sx = (float2*)(sm + 3 * (size_t)K);
-            for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xpt.xs[b], xpt.xsum[b]);
-            int32_t* v16 = (int32_t*)(sx + K / 32);
-            for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xpt.v16[b];
+            xplanes_stage(xpt, K, sm, threadIdx.x, GEMV_THREADS);
             xs[tk].p0 = sm;
-            xs[tk].sx = sx;
-            xs[tk].v16 = v16;
+            xs[tk].sx = (const float2*)(sm + 3 * (size_t)K);
+            xs[tk].v16 = (const int32_t*)(xs[tk].sx + K / 32);
             xs[tk].xf = nullptr;
         }
     }
@@ -174,46 +164,46 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
 // The 4-bit formats: the same products with the weights brought in by bulk copies into per-warp rings (gemv_ring.cuh).
 // The first copies are issued before the kernel waits for the one ahead of it in the stream.
 constexpr int RING_SLOTS = 3;
+constexpr int RING_SLOTS_MAX = 4;
 constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
 
-template <class F, bool PAIR>
-__global__ void __launch_bounds__(GEMV_THREADS, 3)
+// WARPS = 8: rows interleaved over the grid's warps. With an epilogue (EpiPlanes) a CTA owns whole blocks of 32 rows,
+// 32 / WARPS per warp; WARPS = 16 then keeps two rows per warp, the depth of the plain form.
+template <class F, bool PAIR, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 1)
 gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status,
-                  NormScale ns, EpiPlanes epi) {
+                  NormScale ns, EpiPlanes epi, int slots_per_warp) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t bars[GEMV_WARPS * RING_SLOTS];
+    __shared__ uint64_t bars[WARPS * RING_SLOTS_MAX];
+    __shared__ uint64_t xbars[RING_X_STEPS];
+    __shared__ float epi_vals[2 * 32];
+    constexpr int THREADS = WARPS * 32;
     pdl_launch_dependents();
     const int K = (int)w.n_in;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int RW = PAIR ? 1 : 2;
-    const size_t r_first = ((size_t)warp * gridDim.x + blockIdx.x) * RW, r_step = (size_t)gridDim.x * GEMV_WARPS * RW;
+    const bool with_epi = epi.out.planes != nullptr;
+    const uint32_t ni = with_epi ? (uint32_t)max(1, 32 / WARPS / RW) : 1;
+    const size_t r_first = with_epi ? (size_t)blockIdx.x * 32 + (size_t)warp * (32 / WARPS) : ((size_t)warp * gridDim.x + blockIdx.x) * RW;
+    const size_t r_step = with_epi ? (size_t)gridDim.x * 32 : (size_t)gridDim.x * WARPS * RW;
     const size_t planes_bytes = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
     WarpRing ring;
-    ring.S = RING_SLOTS;
-    ring.slots = smem + planes_bytes + (size_t)warp * RING_SLOTS * RING_SLOT_BYTES;
-    ring.bars = bars + warp * RING_SLOTS;
+    ring.S = slots_per_warp;
+    ring.slots = smem + planes_bytes + (size_t)warp * slots_per_warp * RING_SLOT_BYTES;
+    ring.bars = bars + warp * RING_SLOTS_MAX;
     ring.phases = 0;
     if (lane == 0) {
-        for (int sl = 0; sl < RING_SLOTS; sl++) acopy::bar_init(&ring.bars[sl], 1);
+        for (int sl = 0; sl < slots_per_warp; sl++) acopy::bar_init(&ring.bars[sl], 1);
+        if (warp == 0)
+            for (int i = 0; i < (K / 256 + 7) / 8; i++) acopy::bar_init(&xbars[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        ring_prime<PAIR>(w, w2, ring, r_first, r_step);
+        ring_prime<PAIR>(w, w2, ring, r_first, r_step, ni);
     }
     pdl_wait();
-    // the planes of x (written by the kernel ahead) -> shared memory, slots permuted as in gemv_kernel
-    {
-        const int slots = K / 16;
-        const uint4* src = (const uint4*)xp.planes;
-        uint4* dst = (uint4*)smem;
-        for (int i = threadIdx.x; i < 3 * slots; i += GEMV_THREADS) {
-            int p = i / slots, g = i - p * slots;
-            dst[p * slots + swz(g)] = src[i];
-        }
-        float2* sx = (float2*)(smem + 3 * (size_t)K);
-        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
-        int32_t* v16 = (int32_t*)(sx + K / 32);
-        for (int b = threadIdx.x; b < K / 16; b += GEMV_THREADS) v16[b] = xp.v16[b];
-    }
-    __syncthreads();
+    // the planes of x (written by the kernel ahead) -> shared memory, a set of bulk copies per 2048 k: the rows start once
+    // the first set has landed
+    if (threadIdx.x == 0) ring_stage_planes(xp, K, smem, xbars);
+    __syncthreads();  // the barrier words are initialized for every warp
     XS xs;
     xs.K = K;
     xs.p0 = smem;
@@ -221,27 +211,53 @@ gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, 
     xs.v16 = (const int32_t*)(xs.sx + K / 32);
     xs.xf = nullptr;
     const float kscale = norm_scale_factor(ns, lane);
-    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true, kscale, epi) && status) atomicExch(status, 5u);
+    if (!gemv4_ring<F, PAIR>(w, w2, xs, y, mode, gate, ring, r_first, r_step, lane, true, kscale, ni, epi, epi_vals, THREADS, xbars) && status)
+        atomicExch(status, 5u);
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+template <class F, bool PAIR, int WARPS>
+cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
+                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, int slots) {
+    auto kern = gemv4_ring_kernel<F, PAIR, WARPS>;
+    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)WARPS * slots * RING_SLOT_BYTES;
+    if (smem + 2048 > 227 * 1024) return cudaErrorInvalidValue;
+    static size_t smem_set = 48 * 1024;  // per instantiation
+    if (smem > smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set = smem;
+    }
+    const size_t rows_per_cta = epi.out.planes ? 32 : (size_t)WARPS * (PAIR ? 1 : 2);
+    const size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
+    size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
+    const size_t cap = (size_t)(2048 / (WARPS * 32)) < 3 ? (size_t)(2048 / (WARPS * 32)) : 3;
+    per_sm = per_sm < 1 ? 1 : (per_sm > cap ? cap : per_sm);
+    if (WARPS != 8) per_sm = 1;  // the launch bounds of the wide form
+    const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
+    return launch_k(kern, dim3((unsigned)grid), dim3(WARPS * 32), smem, st, pdl, w, PAIR ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns, epi,
+                    slots);
 }
 
 template <class F>
 cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
                         cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
-    auto kern = pair ? gemv4_ring_kernel<F, true> : gemv4_ring_kernel<F, false>;
-    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + RING_BYTES;
-    static size_t smem_set[2] = {48 * 1024, 48 * 1024};
-    if (smem > smem_set[pair]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set[pair] = smem;
+    if (epi.out.planes) {
+        static const int warps = env_int("B2_EPI_WARPS", 16), slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_EPI_SLOTS", 3)));
+        if (warps == 16) {
+            const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)16 * slots * RING_SLOT_BYTES;
+            if (smem + 2048 <= 227 * 1024)
+                return pair ? launch_ring_w<F, true, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots)
+                            : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots);
+        }
     }
-    const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
-    const size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
-    size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
-    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
-    const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns, epi);
+    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, RING_SLOTS)
+                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, RING_SLOTS);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -452,17 +468,7 @@ gemv4_mma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, i
     __syncwarp();
     for (uint32_t s = 0; s + 1 < M4_SLOTS && s < T; s++) issue(s);  // the weights do not depend on the kernel ahead
     pdl_wait();
-    {
-        const int nslots = K / 16;
-        const uint4* src = (const uint4*)xp.planes;
-        uint4* dst = (uint4*)smem;
-        for (int i = threadIdx.x; i < 3 * nslots; i += GEMV_THREADS) {
-            int p = i / nslots, q = i - p * nslots;
-            dst[p * nslots + swz(q)] = src[i];
-        }
-        float2* sx = (float2*)(smem + 3 * (size_t)K);
-        for (int b = threadIdx.x; b < K / 32; b += GEMV_THREADS) sx[b] = make_float2(xp.xs[b], xp.xsum[b]);
-    }
+    xplanes_stage(xp, K, smem, threadIdx.x, GEMV_THREADS);
     __syncthreads();
     const float2* sx = (const float2*)(smem + 3 * (size_t)K);
     const uint8_t* plane = smem + (size_t)(g < 3 ? g : 0) * K;  // the plane this lane feeds as column g
@@ -704,7 +710,7 @@ static bool ring_enabled() {
     return ring;
 }
 static bool ring_fits(const WeightDev& w) {
-    return (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024;
+    return (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024 && w.n_in <= 2048 * RING_X_STEPS;
 }
 bool gemv_takes_epilogue(const WeightDev& w) {
     const char* m = getenv("B2_GEMV_MMA4");
@@ -713,7 +719,7 @@ bool gemv_takes_epilogue(const WeightDev& w) {
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
-    if (epi.counters) {  // only the ring form carries the epilogue, chained or not
+    if (epi.out.planes) {  // only the ring form carries the epilogue, chained or not
         if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
         if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
         return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);

@@ -26,9 +26,7 @@ struct XS {
     int K;
 };
 
-// Slot g -> g with its low two bits xor-ed by bits 3 and 4: lanes L = 0..7 of a phase that read slots
-// 4 L + i (a 64-byte stride) then cover all eight 16-byte bank groups for every i.
-__device__ __forceinline__ int swz(int g) { return g ^ ((((g >> 3) & 1) << 1) | ((g >> 4) & 1)); }
+__device__ __forceinline__ int swz(int g) { return xplanes_slot(g); }  // the slot permutation of the planes (kernels.h)
 
 __device__ __forceinline__ uint4 plane16(const XS& x, int p, int k) {  // 16 plane bytes at element k (k % 16 == 0)
     return *(const uint4*)(x.p0 + (size_t)p * x.K + ((size_t)swz(k >> 4) << 4));

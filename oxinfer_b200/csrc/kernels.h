@@ -36,22 +36,26 @@ cudaError_t launch_repack_q8_0(const uint8_t* raw, size_t n_out, size_t n_in, in
 
 // ---- gemv.cu: one-token dequant matrix-vector products ---------------------------------------
 // Activation vector split into three int8 planes per block of 32 (x ~= xs * (q0 + 128 q1 + 16384 q2),
-// 21 significant bits per block), plus block scales and sums. Sizes in bytes for n_in = K:
-//   planes 3K | xs 4K/32 | xsum 4K/32 | v16 4K/16
+// 21 significant bits per block), plus block scales and sums. The record in global memory is the image the product
+// kernels keep in shared memory, so staging it is a plain copy (bulk copies in the ring form). For n_in = K, in bytes:
+//   planes 3K | sx 8K/32 | v16 4K/16
+// Element k of plane p sits at p * K + 16 * xplanes_slot(k / 16) + k % 16: the 16-byte slots of each 64 bytes are
+// permuted so that the product kernels' shared-memory reads spread over the banks.
 struct XPlanes {
-    int8_t* planes;   // [3][K]
-    float* xs;        // [K/32]  block scale
-    float* xsum;      // [K/32]  xs * sum of the block's integers (the quantized block sum)
+    int8_t* planes;   // [3][K], slots permuted
+    float2* sx;       // [K/32]  (block scale, scale * sum of the block's integers = the quantized block sum)
     int32_t* v16;     // [K/16]  integer sums of each 16 elements
 };
+// Slot g -> g with its low two bits xor-ed by bits 3 and 4: lanes L = 0..7 of a phase that read slots 4 L + i (a 64-byte
+// stride) then cover all eight 16-byte bank groups for every i.
+__host__ __device__ inline int xplanes_slot(int g) { return g ^ ((((g >> 3) & 1) << 1) | ((g >> 4) & 1)); }
 __host__ __device__ inline size_t xplanes_bytes(size_t K) { return 3 * K + 4 * (K / 32) * 2 + 4 * (K / 16); }
 __host__ __device__ inline XPlanes xplanes_at(void* base, size_t K) {
     XPlanes p;
     uint8_t* b = (uint8_t*)base;
     p.planes = (int8_t*)b;
-    p.xs = (float*)(b + 3 * K);
-    p.xsum = p.xs + K / 32;
-    p.v16 = (int32_t*)(p.xsum + K / 32);
+    p.sx = (float2*)(b + 3 * K);
+    p.v16 = (int32_t*)(b + 3 * K + 8 * (K / 32));
     return p;
 }
 cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false);
@@ -68,12 +72,11 @@ struct NormScale {
 // planes(x * pre * w) and the blocks' sums of squares of x * pre; K a multiple of 32, w may be null.
 cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl = false);
 // What a product may do with its finished output, so that the kernel which would split it for the next product is not
-// launched: every warp counts the rows it has written into its block of 32 (`counters`, one word per block, zero between
-// launches), and the warp that completes a block reads the block back and writes the planes of y * pre * w (w may be
-// null) and, with `partial`, the block's sum of squares of y * pre: what launch_xplanes / launch_norm_planes would have
-// written, bit for bit. n_out must be a multiple of 32. counters == nullptr: nothing.
+// launched: the CTAs then own whole blocks of 32 consecutive rows (four per warp), the warps leave their results in
+// shared memory, and after a CTA barrier one warp writes the planes of y * pre * w (w may be null) and, with `partial`,
+// the block's sum of squares of y * pre: what launch_xplanes / launch_norm_planes would have written, bit for bit.
+// n_out must be a multiple of 32. out.planes == nullptr: nothing.
 struct EpiPlanes {
-    uint32_t* counters;
     XPlanes out;
     const float* w;
     float* partial;
@@ -85,7 +88,7 @@ bool gemv_takes_epilogue(const WeightDev& w);
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f},
-                        EpiPlanes epi = EpiPlanes{nullptr, XPlanes{nullptr, nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
+                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
 // A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
 // of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
 // bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),

@@ -126,6 +126,13 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     if (const char* e = getenv("B2_PLAN_PDL")) p->pdl_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_FUSE")) p->fuse_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_DEFER_NORM")) p->defer_norm_ = atoi(e) != 0;
+    int epi_level = 1;  // 1: products that add into the residual row (their split is a deferred norm); 2: gate / up pairs too
+    if (const char* e = getenv("B2_PLAN_EPILOGUE")) {
+        epi_level = atoi(e);
+        p->epilogue_ = epi_level != 0;
+    }
+    if (const char* e = getenv("B2_PLAN_TOKEN_KERNEL"))
+        if (atoi(e) != 0) p->epilogue_ = false;  // the token kernel's program is built from the unfused op list
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -470,6 +477,30 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     PLAN_CUDA(cudaMalloc((void**)&p->planes_, std::max<size_t>(planes_total, 256)), "cudaMalloc(planes)");
     for (auto& [oi, r] : region_of_op) p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
 
+    // ---- planes written by the product ahead ---------------------------------------------------------------------
+    // A split kernel (deferred norm, or the planes of an MLP activation) that directly follows the 4-bit product which
+    // wrote its whole input is dropped: that product's CTAs then own whole blocks of 32 rows and split each block once
+    // its rows are done (EpiPlanes). Saves a launch per product whose output feeds another product.
+    if (p->epilogue_ && p->pdl_) {
+        std::vector<Op> kept;
+        kept.reserve(p->ops_.size());
+        for (size_t b = 0; b < p->ops_.size(); b++) {
+            const Op& nx = p->ops_[b];
+            Op* lin = kept.empty() ? nullptr : &kept.back();
+            if (lin && lin->kind == B2_OP_LINEAR && !lin->epi.out.planes && gemv_takes_epilogue(lin->w)) {
+                const size_t n = lin->w.n_out;
+                const bool norm = nx.kind == OP_NORM_DEFERRED && nx.x == lin->y && nx.norm.n == n && nx.rows == 1;
+                const bool split = nx.kind == OP_XPLANES && nx.x == lin->y && nx.n == n && (epi_level >= 2 || !lin->pair);
+                if (norm || split) {
+                    lin->epi = EpiPlanes{nx.xp, norm ? nx.p0 : nullptr, norm ? const_cast<float*>(nx.ns.partial) : nullptr, norm ? nx.norm.pre : 1.0f};
+                    continue;
+                }
+            }
+            kept.push_back(nx);
+        }
+        p->ops_ = std::move(kept);
+    }
+
     // ---- scratch ------------------------------------------------------------------------------------
     if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, attend_part_floats(max_nh, max_hd) * sizeof(float)), "cudaMalloc(attention partials)");
     size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1);
@@ -542,7 +573,7 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
             case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st, pdl); break;
             case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st, pdl); break;
             case OP_NORM_DEFERRED: e = launch_norm_planes(o.x, o.p0, o.norm.pre, o.norm.n, o.xp, const_cast<float*>(o.ns.partial), st, pdl); break;
-            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl, o.ns); break;
+            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl, o.ns, o.epi); break;
             case B2_OP_QK_ROPE:
                 e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st, pdl);
                 break;

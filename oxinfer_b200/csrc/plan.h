@@ -49,6 +49,7 @@ class DecodePlanImpl {
         size_t off = 0;  // EXCHANGE: offset of the vector in the activation block, in floats
         NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
+        EpiPlanes epi{};  // LINEAR: the planes of its output, written by its own last warps (the split kernel behind it is dropped)
     };
     DecodePlanImpl() = default;
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
@@ -71,6 +72,7 @@ class DecodePlanImpl {
     float* norm_partials_ = nullptr;
     bool fuse_ = true;  // q / k / v style products of one vector as one launch over concatenated rows (B2_PLAN_FUSE=0: off)
     std::vector<void*> fused_;  // device copies made for that
+    bool epilogue_ = true;  // a 4-bit product writes the planes the next product reads (B2_PLAN_EPILOGUE=0: separate kernels)
     // one allocation each
     float* bufs_ = nullptr;
     std::vector<float*> buf_ptr_;

@@ -175,17 +175,7 @@ __device__ __forceinline__ void stage_vector(const float* x, int n, uint8_t* pl)
 
 // Planes another phase left in global memory -> this CTA's shared memory (the staging step of gemv_kernel).
 __device__ __forceinline__ void copy_planes(const XPlanes& xp, int K, uint8_t* pl) {
-    const int slots = K / 16;  // per plane
-    const uint4* src = (const uint4*)xp.planes;
-    uint4* dst = (uint4*)pl;
-    for (int i = threadIdx.x; i < 3 * slots; i += TK_THREADS) {
-        const int p = i / slots, g = i - p * slots;
-        dst[p * slots + swz(g)] = __ldcg(src + i);
-    }
-    float2* sx = (float2*)(pl + 3 * (size_t)K);
-    for (int b = threadIdx.x; b < K / 32; b += TK_THREADS) sx[b] = make_float2(__ldcg(xp.xs + b), __ldcg(xp.xsum + b));
-    int32_t* v16 = (int32_t*)(sx + K / 32);
-    for (int b = threadIdx.x; b < K / 16; b += TK_THREADS) v16[b] = __ldcg(xp.v16 + b);
+    xplanes_stage(xp, K, pl, threadIdx.x, TK_THREADS);
     __syncthreads();
 }
 

@@ -40,15 +40,20 @@ __device__ __forceinline__ XSplit xplanes_split(float v) {
 // The split of block `blk` written to the global-memory layout (XPlanes).
 __device__ __forceinline__ void xplanes_block(float v, int blk, int lane, int K, const XPlanes& out) {
     const XSplit r = xplanes_split(v);
-    size_t at = (size_t)blk * 32 + lane;
+    const size_t at = (size_t)xplanes_slot(blk * 2 + (lane >> 4)) * 16 + (lane & 15);
     out.planes[at] = (int8_t)r.q0;
     out.planes[(size_t)K + at] = (int8_t)r.q1;
     out.planes[2 * (size_t)K + at] = (int8_t)r.q2;
     if ((lane & 15) == 0) out.v16[blk * 2 + (lane >> 4)] = r.sum16;
-    if (lane == 0) {
-        out.xs[blk] = r.s;
-        out.xsum[blk] = r.s * (float)r.sum32;
-    }
+    if (lane == 0) out.sx[blk] = make_float2(r.s, r.s * (float)r.sum32);
+}
+
+// The record (planes, scales, sums) -> shared memory, a plain copy by the calling threads; the caller synchronizes.
+__device__ __forceinline__ void xplanes_stage(const XPlanes& xp, int K, uint8_t* sm, int tid, int nthreads) {
+    const uint4* src = (const uint4*)xp.planes;
+    uint4* dst = (uint4*)sm;
+    const int n = (int)(xplanes_bytes((size_t)K) / 16);
+    for (int i = tid; i < n; i += nthreads) dst[i] = __ldcg(src + i);
 }
 
 }  // namespace b2
