@@ -256,8 +256,9 @@ cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
                             : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots);
         }
     }
-    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, RING_SLOTS)
-                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, RING_SLOTS);
+    static const int plain_slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_RING_SLOTS", RING_SLOTS)));
+    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots)
+                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -408,15 +409,18 @@ static cudaError_t launch_f8_mma(const WeightDev& w, const float* x, float* y, i
 
 // ---- the 4-bit formats on the tensor cores -------------------------------------------------------------------------
 // The integer dot products of gemv_kernel cost 0.75 dp4a per weight plus as much again in nibble extraction, plane
-// loads and combining; with the sub-block tails the kernels run at 3.4 instructions per weight, above the ~3.1 the
-// SMs can issue per weight at the HBM rate. Here the products run as mma.sync m16n8k32 (s8 x s8 -> s32): a warp owns
-// 16 weight rows, A is a sub-block's 32 nibbles (masked out of the packed bytes, which already are four weights per
-// word in k order), B's columns 0..2 are the three planes of x, and one MMA replaces 48 dp4a. A lane's share of the
-// summation index is permuted (bytes 8 t .. 8 t + 7 of the 32-byte group) so that weights and planes come in 8-byte
-// reads. The sums of a group go to the quad's lane t = group, which applies that group's scales (FmtQ4K / FmtMLX4
-// ::tail, the same arithmetic as gemv_kernel), so the four lanes of a quad share the float work.
+// loads and combining (3.2 instructions per weight all told, above what the SMs can issue per weight at the HBM rate).
+// Here the products run as mma.sync m16n8k32 (s8 x s8 -> s32): a warp owns 16 weight rows, A is a sub-block's 32
+// nibbles (masked out of the packed bytes, which already are four weights per word in k order). B's eight columns hold
+// (plane 0, plane 1) four times over in a first product and (plane 2, nothing) in a second, so every lane of a quad
+// ends up with all three sums of its two rows and no lane has to ask another; lane t keeps the sums of group t and
+// applies that group's scales (FmtQ4K / FmtMLX4::tail, the same arithmetic as gemv_kernel, bit for bit), so the four
+// lanes of a quad share the float work. A lane's share of the summation index is permuted (bytes 8 t .. 8 t + 7 of the
+// 32-byte group) so that weights and planes come in 8-byte reads.
 // A CTA owns one 16-row tile at a time; its warps split K by super-blocks and bring their rows' blocks (16 copies
 // of 144 bytes per step) into per-warp rings; the warps' partial sums meet in shared memory in warp order.
+// Measured: 8.7 M warp instructions at 14336 x 4096 against 5.9 M of gemv_kernel (the waits, the per-tile CTA barriers
+// and the address arithmetic outweigh what the MMAs save) and 15.5 us against 10.7, so it stays behind B2_GEMV_MMA4.
 __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -471,7 +475,8 @@ gemv4_mma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, i
     xplanes_stage(xp, K, smem, threadIdx.x, GEMV_THREADS);
     __syncthreads();
     const float2* sx = (const float2*)(smem + 3 * (size_t)K);
-    const uint8_t* plane = smem + (size_t)(g < 3 ? g : 0) * K;  // the plane this lane feeds as column g
+    const uint8_t* plane01 = smem + (size_t)(g & 1) * K;  // the plane this lane feeds as column g of the first product
+    const uint8_t* plane2 = smem + 2 * (size_t)K;
     const float kscale = norm_scale_factor(ns, lane);
     const uint32_t M = 0x0F0F0F0Fu;
     uint32_t s = 0;
@@ -499,22 +504,27 @@ gemv4_mma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, i
                     const uint2 wa = *(const uint2*)(blkA + 16 + 32 * j + 8 * t);
                     const uint2 wb = *(const uint2*)(blkB + 16 + 32 * j + 8 * t);
                     const int k0 = kb * 256 + 64 * j + 8 * t;
-                    uint2 blo = make_uint2(0, 0), bhi = make_uint2(0, 0);
-                    if (g < 3) {
-                        blo = *(const uint2*)(plane + ((size_t)swz(k0 >> 4) << 4) + (k0 & 15));
-                        bhi = *(const uint2*)(plane + ((size_t)swz((k0 + 32) >> 4) << 4) + (k0 & 15));
+                    // first product: columns (plane 0, plane 1) four times over, so every lane of a quad holds both sums of
+                    // its two rows; second: (plane 2, nothing). No lane has to ask another for a part of a sum.
+                    const size_t at_lo = ((size_t)swz(k0 >> 4) << 4) + (k0 & 15), at_hi = ((size_t)swz((k0 + 32) >> 4) << 4) + (k0 & 15);
+                    const uint2 b01lo = *(const uint2*)(plane01 + at_lo), b01hi = *(const uint2*)(plane01 + at_hi);
+                    uint2 b2lo = make_uint2(0, 0), b2hi = make_uint2(0, 0);
+                    if ((g & 1) == 0) {
+                        b2lo = *(const uint2*)(plane2 + at_lo);
+                        b2hi = *(const uint2*)(plane2 + at_hi);
                     }
-                    int cl[4], chh[4];
-                    mma_s8_16832(cl, wa.x & M, wb.x & M, wa.y & M, wb.y & M, blo.x, blo.y);
-                    mma_s8_16832(chh, (wa.x >> 4) & M, (wb.x >> 4) & M, (wa.y >> 4) & M, (wb.y >> 4) & M, bhi.x, bhi.y);
-                    // lane t = 0 holds planes 0 and 1 (columns 0, 1), lane t = 1 plane 2 (column 2)
-                    int v[4] = {cl[0] + (cl[1] << 7), chh[0] + (chh[1] << 7), cl[2] + (cl[3] << 7), chh[2] + (chh[3] << 7)};
-                    const int p2[4] = {cl[0], chh[0], cl[2], chh[2]};
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int hi2 = __shfl_sync(0xffffffffu, p2[i], (lane & ~3) | 1);
-                        const int tot = __shfl_sync(0xffffffffu, v[i], lane & ~3) + (hi2 << 14);
-                        if (t == j) mine[i] = tot;
+                    const uint32_t al0 = wa.x & M, al1 = wb.x & M, al2 = wa.y & M, al3 = wb.y & M;
+                    const uint32_t ah0 = (wa.x >> 4) & M, ah1 = (wb.x >> 4) & M, ah2 = (wa.y >> 4) & M, ah3 = (wb.y >> 4) & M;
+                    int cl[4], chh[4], cl2[4], ch2[4];
+                    mma_s8_16832(cl, al0, al1, al2, al3, b01lo.x, b01lo.y);
+                    mma_s8_16832(cl2, al0, al1, al2, al3, b2lo.x, b2lo.y);
+                    mma_s8_16832(chh, ah0, ah1, ah2, ah3, b01hi.x, b01hi.y);
+                    mma_s8_16832(ch2, ah0, ah1, ah2, ah3, b2hi.x, b2hi.y);
+                    if (t == j) {
+                        mine[0] = cl[0] + (cl[1] << 7) + (cl2[0] << 14);
+                        mine[1] = chh[0] + (chh[1] << 7) + (ch2[0] << 14);
+                        mine[2] = cl[2] + (cl[3] << 7) + (cl2[2] << 14);
+                        mine[3] = chh[2] + (chh[3] << 7) + (ch2[2] << 14);
                     }
                 }
                 // the scales of group t of rows g and g + 8
@@ -702,13 +712,11 @@ cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t
     return launch_k(norm_planes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, w, pre, (int)K, out, partial);
 }
 
-static bool ring_enabled() {
-    static const bool ring = [] {
-        const char* e = getenv("B2_GEMV_RING");
-        return !e || atoi(e) != 0;
-    }();
-    return ring;
+static int ring_level() {  // B2_GEMV_RING: 0 never, 1 in dependent-launch chains (the default), 2 for every launch
+    static const int level = env_int("B2_GEMV_RING", 1);
+    return level;
 }
+static bool ring_enabled() { return ring_level() != 0; }
 static bool ring_fits(const WeightDev& w) {
     return (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024 && w.n_in <= 2048 * RING_X_STEPS;
 }
@@ -740,7 +748,7 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
     // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
-    if (ring_enabled() && pdl && ring_fits(w)) {
+    if (ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
         if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
         return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }

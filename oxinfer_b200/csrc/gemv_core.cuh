@@ -95,23 +95,31 @@ __device__ __forceinline__ void q4_load(const WeightDev& w, size_t row, int it, 
 __device__ __forceinline__ void q4_int_dots(const Q4Regs& a, const Q4Regs& b, const XS& x, int k0, int& la, int& ha, int& lb, int& hb) {
     const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
     const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
-    int s[3][4];
+    // Half a 32-byte run at a time: the sixteen masked nibble words are made once and used against all three planes while
+    // they are live (the other order, plane by plane, makes the compiler mask the same words three times).
+    int s[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
-    for (int p = 0; p < 3; p++) {
-        uint32_t xw[16];
-        plane64(x, p, k0, xw);
-        int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    for (int h = 0; h < 2; h++) {
+        uint32_t al[4], ah[4], bl[4], bh[4];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            s0 = dp(qa[i] & 0x0F0F0F0Fu, xw[i], s0);
-            s1 = dp((qa[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s1);
-            s2 = dp(qb[i] & 0x0F0F0F0Fu, xw[i], s2);
-            s3 = dp((qb[i] >> 4) & 0x0F0F0F0Fu, xw[8 + i], s3);
+        for (int i = 0; i < 4; i++) {
+            al[i] = qa[4 * h + i] & 0x0F0F0F0Fu;
+            ah[i] = (qa[4 * h + i] >> 4) & 0x0F0F0F0Fu;
+            bl[i] = qb[4 * h + i] & 0x0F0F0F0Fu;
+            bh[i] = (qb[4 * h + i] >> 4) & 0x0F0F0F0Fu;
         }
-        s[p][0] = s0;
-        s[p][1] = s1;
-        s[p][2] = s2;
-        s[p][3] = s3;
+#pragma unroll
+        for (int p = 0; p < 3; p++) {
+            const uint4 lo = plane16(x, p, k0 + 16 * h), hi = plane16(x, p, k0 + 32 + 16 * h);
+            const uint32_t xl[4] = {lo.x, lo.y, lo.z, lo.w}, xh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                s[p][0] = dp(al[i], xl[i], s[p][0]);
+                s[p][1] = dp(ah[i], xh[i], s[p][1]);
+                s[p][2] = dp(bl[i], xl[i], s[p][2]);
+                s[p][3] = dp(bh[i], xh[i], s[p][3]);
+            }
+        }
     }
     la = planes3(s[0][0], s[1][0], s[2][0]);
     ha = planes3(s[0][1], s[1][1], s[2][1]);
