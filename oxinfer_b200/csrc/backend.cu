@@ -610,7 +610,7 @@ class Backend {
 
     // One grouped GEMM: rows of xg (f16, segments of whole 128-row tiles per expert) times the stacked matrices.
     int grouped_gemm(int fmt, const void* stacked, size_t experts, size_t n_out, size_t n_in, const void* xg, size_t rows, const int* tile_expert,
-                     float* out_dev) {
+                     float* out_dev, int m_halves = 1) {
         WeightDev w{};
         w.fmt = fmt;
         w.n_out = n_out;
@@ -618,7 +618,7 @@ class Backend {
         w.p0 = (const uint8_t*)stacked;
         GemmPlan* plan = nullptr;
         char msg[256] = {0};
-        cudaError_t e = gemm_tc_plan_create(w, xg, rows, out_dev, B2_F32, &plan, msg, sizeof msg, experts, tile_expert, 1);
+        cudaError_t e = gemm_tc_plan_create(w, xg, rows, out_dev, B2_F32, &plan, msg, sizeof msg, experts, tile_expert, m_halves);
         if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
         e = launch_gemm_tc(plan, w, rows, out_dev, B2_F32, gemm_status, sm_count, stream);
         launches++;
@@ -688,6 +688,7 @@ class Backend {
         if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe: unknown handle]");
         const Moe& m = it->second;
         if (t == 0 || k == 0) return B2_OK;
+        if (((uintptr_t)x_dev_ | (uintptr_t)y_dev_) & 15) return fail(B2_ERR_ARG, "[b200qmm: moe: x and y must be 16-byte aligned]");
         int rc = ensure_status();
         if (rc) return rc;
         std::vector<size_t> count(m.experts, 0);
@@ -696,7 +697,20 @@ class Backend {
             count[(size_t)ids[i]]++;
         }
         if (t * k <= 64 && !getenv("B2_MOE_NO_GEMV")) return moe_small(m, x_dev_, t, ids, rw, k, y_dev_);
-        const size_t TILE = 128;
+        // Token tiles of 128 or 256 rows. A tile costs about the same either way (the kernel is bound by the expansion of
+        // the tile's weights, which both heights share), so the taller tile wins as soon as it needs clearly fewer tiles:
+        // large batches, where the experts hold more than a tile's worth of tokens each.
+        size_t tiles128 = 0, tiles256 = 0;
+        for (size_t e = 0; e < m.experts; e++) {
+            tiles128 += (count[e] + 127) / 128;
+            tiles256 += (count[e] + 255) / 256;
+        }
+        static const int force_tile = [] {
+            const char* e = getenv("B2_MOE_TILE");
+            return e ? atoi(e) : 0;
+        }();
+        const size_t TILE = force_tile == 128 || force_tile == 256 ? (size_t)force_tile : (tiles256 * 10 <= tiles128 * 8 ? 256 : 128);
+        const int m_halves = (int)(TILE / 128);
         std::vector<size_t> off(m.experts, 0);
         std::vector<int32_t> tile_expert;
         size_t rows = 0;
@@ -738,12 +752,12 @@ class Backend {
         e = launch_moe_gather(x_dev_, d_src, rows, m.h, moe_xg.p, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_gather");
-        if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p))) return rc;
+        if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p, m_halves))) return rc;
         float* d_scale = (float*)((uint8_t*)moe_a.p + rows * m.inter * 2);  // one power-of-two scale per row
-        e = launch_moe_act((const float*)moe_g.p, rows, m.inter, moe_a.p, d_scale, stream);
+        e = launch_moe_act((const float*)moe_g.p, d_src, rows, m.inter, moe_a.p, d_scale, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_act");
-        if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p))) return rc;
+        if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p, m_halves))) return rc;
         e = launch_moe_combine((const float*)moe_o.p, d_scale, d_slots, d_w, t, k, m.h, y_dev_, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_combine");

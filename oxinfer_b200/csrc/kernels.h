@@ -140,7 +140,7 @@ cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t t_pad, si
 // ---- moe.cu: the element-wise pieces of the routed-expert layer ------------------------------------
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st);
 cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, cudaStream_t st);
-cudaError_t launch_moe_act(const float* g, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
+cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
 // The same with the routes as kernel arguments (at most GEMV_BATCH_MAX pairs): slot of pair (i, j) = i k + j, no row scale.
 struct SmallRoutes {
     float w[GEMV_BATCH_MAX];
