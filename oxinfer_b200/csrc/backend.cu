@@ -339,7 +339,9 @@ class Backend {
     }
 
     // One token on the device over the prepared planes (FP8 weights read x itself).
-    int matvec_prepared(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
+    // `after_planes`: the product directly follows the plane kernel of its own vector in the stream, so it is launched as
+    // that kernel's dependent (it fetches its first weights while the planes are written, and waits for them on the device).
+    int matvec_prepared(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate, bool after_planes = false) {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
         bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
@@ -357,7 +359,7 @@ class Backend {
             if (prepared_k != w->dev.n_in) return fail(B2_ERR_ARG, "[b200qmm: matvec: no planes prepared for n_in = %zu (b2_prepare_x_dev)]", w->dev.n_in);
             xp = xplanes_at(xplanes.p, w->dev.n_in);
         }
-        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained);
+        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained || after_planes);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "gemv");
         return B2_OK;
@@ -366,11 +368,14 @@ class Backend {
     int matvec_dev(uint64_t h, uint64_t up, const float* x_dev_, float* y_dev_, int mode, const float* gate) {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
+        bool planes = false;
         if (w->dev.fmt != B2_FMT_F8E4M3 && gemv_supports(w->dev)) {
             int rc = prepare_x(x_dev_, w->dev.n_in);
             if (rc) return rc;
+            // measured: worth 3 % for Q6_K; the 4-bit formats would switch to their ring form, which loses when launched alone
+            planes = w->dev.fmt == B2_FMT_Q6_K || w->dev.fmt == B2_FMT_Q8_0;
         }
-        return matvec_prepared(h, up, x_dev_, y_dev_, mode, gate);
+        return matvec_prepared(h, up, x_dev_, y_dev_, mode, gate, planes);
     }
 
     int ensure_status() {
