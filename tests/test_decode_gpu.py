@@ -135,6 +135,33 @@ def test_generate_matches_host_loop_and_oracle(backend, token_kernel):
     plan.close()
 
 
+def test_planes_from_the_product_epilogue_are_the_same_bits(backend):
+    """The o and down products write the next product's planes and norm sums themselves (fewer launches); hidden states,
+    logits and cache rows must equal those of the plan that launches the separate split kernels, bit for bit."""
+    import os
+
+    cfg = dict(n_layers=3, h=512, nh=4, nkv=2, hd=128, inter=1024, vocab=512)
+    plans = {}
+    try:
+        for level in ("0", "1", "2"):   # none / residual-adding products / the gate-up pair too
+            os.environ["B2_PLAN_EPILOGUE"] = level
+            plans[level] = build(backend, cfg=cfg, seed=955, token_kernel=False)
+    finally:
+        os.environ.pop("B2_PLAN_EPILOGUE", None)
+    n = {k: v[0].launches_per_step() for k, v in plans.items()}
+    assert n["2"] < n["1"] < n["0"], n
+    rng = np.random.default_rng(12)
+    inv_freq = plans["0"][4]
+    for pos in range(5):
+        x = rng.standard_normal(cfg["h"]).astype(np.float32)
+        cs = O.rope_table(pos, inv_freq)
+        outs = {k: v[0].step(pos, x, cs) for k, v in plans.items()}
+        for k in ("1", "2"):
+            assert np.array_equal(outs[k][0], outs["0"][0]) and np.array_equal(outs[k][1], outs["0"][1]), (k, pos)
+    for v in plans.values():
+        v[0].close()
+
+
 def test_f16_cache_within_reduced_precision_bound(backend):
     plan, cpu, _, _, inv_freq, keep = build(backend, seed=930, kv_f16=True)
     prefill(plan, cpu, 150, 31)
