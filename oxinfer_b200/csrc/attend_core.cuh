@@ -121,7 +121,7 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
                                             const uint32_t max_splits, const uint32_t pos, const float* q,
                                             const T* kc, const T* vc, float* out, float* part,
                                             uint32_t* counters, DecAttn p, XPlanes xp, uint32_t* status,
-                                            unsigned long long* prof = nullptr) {
+                                            unsigned long long* prof = nullptr, const FusedRope* fr = nullptr, const uint32_t table_pos0 = 0) {
     const long long pt0 = clock64();
     auto stamp = [&](int i) {
         if (prof && tid == 0) prof[i] += (unsigned long long)(clock64() - pt0);
@@ -151,14 +151,46 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
     const float NEG = -INFINITY;
 
     const uint32_t t0 = split * per, t1 = min(tiles, t0 + per);
+    // FusedRope: the unit whose keys end at the token's position makes the token's key and value itself (thread d < HD
+    // owns dimension d), appends them to the caches and writes them into its last tile, whose copy leaves that row out.
+    const bool makes_row = fr != nullptr && t1 == tiles && pos < p.max_len;
+    auto rotate = [&](const float* head, int d) {  // dimension d of a head after RoPE (the arithmetic of rope_head)
+        const uint32_t hr = fr->r.half_rot;
+        float v = __ldcg(head + d);
+        if ((uint32_t)d < 2 * hr) {
+            const float* cs = fr->cs_table + (size_t)(pos - table_pos0) * fr->r.cs_stride + fr->r.cs_off;
+            if (fr->r.interleaved) {
+                const uint32_t j = (uint32_t)d >> 1;
+                const float c = cs[j], sn = cs[hr + j];
+                const float x1 = __ldcg(head + 2 * j), x2 = __ldcg(head + 2 * j + 1);
+                v = (d & 1) == 0 ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)) : __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+            } else {
+                const uint32_t j = (uint32_t)d < hr ? (uint32_t)d : (uint32_t)d - hr;
+                const float c = cs[j], sn = cs[hr + j];
+                const float x1 = __ldcg(head + j), x2 = __ldcg(head + j + hr);
+                v = (uint32_t)d < hr ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)) : __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+            }
+        }
+        return v;
+    };
+    T k_new = (T)0.0f, v_new = (T)0.0f;
+    if (makes_row && tid < HD) {
+        k_new = (T)rotate(fr->qkv + fr->r.k_off + (size_t)kvh * HD, tid);
+        v_new = (T)__ldcg(fr->qkv + fr->r.v_off + (size_t)kvh * HD + tid);
+        const size_t at = ((size_t)kvh * p.max_len + pos) * HD + tid;
+        const_cast<T*>(kc)[at] = k_new;
+        const_cast<T*>(vc)[at] = v_new;
+    }
     auto issue = [&](uint32_t t) {  // one thread: both copies of key tile t
-        const uint32_t j0 = lo + t * ATT_TILE, nv = min((uint32_t)ATT_TILE, len - j0);
+        const uint32_t j0 = lo + t * ATT_TILE;
+        uint32_t nv = min((uint32_t)ATT_TILE, len - j0);
+        if (makes_row && t == tiles - 1) nv--;  // the token's own row comes from this unit's registers
         const uint32_t bytes = nv * HD * (uint32_t)sizeof(T);
         const size_t at = ((size_t)kvh * p.max_len + j0) * HD;
-        bar_expect_tx(&bars[0], bytes);
-        bulk_load(Ks, kc + at, bytes, &bars[0]);
+        bar_expect_tx(&bars[0], bytes);  // with no bytes to wait for this alone completes the phase
+        if (bytes) bulk_load(Ks, kc + at, bytes, &bars[0]);
         bar_expect_tx(&bars[1], bytes);
-        bulk_load(Vs, vc + at, bytes, &bars[1]);
+        if (bytes) bulk_load(Vs, vc + at, bytes, &bars[1]);
     };
     if (tid == 0) {
         bar_init(&bars[0], 1);
@@ -168,7 +200,12 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         flags[0] = 0;
         flags[1] = 0;
     }
-    for (int i = tid; i < G * HD; i += ATT_THREADS) qs[i] = __ldcg(q + (size_t)h0 * HD + i) * p.scale;
+    if (fr) {
+        for (int i = tid; i < G * HD; i += ATT_THREADS)
+            qs[i] = rotate(fr->qkv + (size_t)(h0 + i / HD) * fr->r.q_stride, i % HD) * p.scale;
+    } else {
+        for (int i = tid; i < G * HD; i += ATT_THREADS) qs[i] = __ldcg(q + (size_t)h0 * HD + i) * p.scale;
+    }
     if (tid < G) {
         mrun[tid] = NEG;
         lrun[tid] = 0.0f;
@@ -191,6 +228,13 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         if (flags[0]) {
             ok = false;
             break;
+        }
+        if (makes_row && t == tiles - 1) {  // uniform over the unit's threads
+            if (tid < HD) {
+                Ks[(pos - j0) * HD + tid] = k_new;
+                Vs[(pos - j0) * HD + tid] = v_new;
+            }
+            group_sync(bar_id);
         }
         if (t == t0) stamp(0);
         // scores: eight lanes per key; a thread takes keys `slot` and `slot + 32` together so that one read of the

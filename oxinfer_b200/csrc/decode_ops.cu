@@ -114,13 +114,14 @@ __global__ void __launch_bounds__(256) glu_kernel(const float* __restrict__ g, c
 
 // ---- attention: grid (KV heads, splits), one unit per CTA (attend_core.cuh) --------------------------------
 template <int HD, int G, typename T>
-__global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
-                                                             float* __restrict__ out, float* part, uint32_t* counters,
-                                                             const uint32_t* __restrict__ sp, DecAttn p, XPlanes xp, uint32_t* status) {
+__global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __restrict__ q, T* kc, T* vc, float* __restrict__ out, float* part,
+                                                             uint32_t* counters, const uint32_t* __restrict__ sp, DecAttn p, XPlanes xp,
+                                                             uint32_t* status, FusedRope fr) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
-    attend_unit<HD, G, T>(smem, threadIdx.x, 0, blockIdx.x, blockIdx.y, gridDim.y, sp[0], q, kc, vc, out, part, counters, p, xp, status);
+    attend_unit<HD, G, T>(smem, threadIdx.x, 0, blockIdx.x, blockIdx.y, gridDim.y, sp[0], q, kc, vc, out, part, counters, p, xp, status, nullptr,
+                          fr.qkv ? &fr : nullptr, sp[1]);
 }
 
 // ---- greedy token ----------------------------------------------------------------------------------
@@ -331,8 +332,8 @@ bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd) {
 size_t attend_part_floats(uint32_t nh, uint32_t hd) { return (size_t)nh * ATT_MAX_SPLITS * (hd + 4); }
 
 template <int HD, int G, typename T>
-static cudaError_t attend_t(const float* q, const void* kc, const void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,
-                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
+static cudaError_t attend_t(const float* q, void* kc, void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,
+                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr) {
     constexpr size_t smem = attend_smem<HD, G, T>();
     static bool set = false;  // per instantiation; the attribute is per function and device-wide values are equal
     if (!set) {
@@ -344,31 +345,36 @@ static cudaError_t attend_t(const float* q, const void* kc, const void* vc, floa
     if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
     if (splits == 0) splits = 1;
     dim3 grid(p.nkv, splits);
-    return launch_k(attend_kernel<HD, G, T>, grid, dim3(ATT_THREADS), smem, st, pdl, q, (const T*)kc, (const T*)vc, out, part, counters, sp, p, xp,
-                    status);
+    return launch_k(attend_kernel<HD, G, T>, grid, dim3(ATT_THREADS), smem, st, pdl, q, (T*)kc, (T*)vc, out, part, counters, sp, p, xp, status, fr);
 }
 
 template <int HD, typename T>
-static cudaError_t attend_g(uint32_t g, const float* q, const void* kc, const void* vc, float* out, float* part, uint32_t* counters,
-                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
+static cudaError_t attend_g(uint32_t g, const float* q, void* kc, void* vc, float* out, float* part, uint32_t* counters,
+                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr) {
     switch (g) {
-        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
-        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
-        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
-        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
     }
     return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_attend(const float* q, const void* kc, const void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
-                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl) {
+cudaError_t launch_attend(const float* q, void* kc, void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope* frp) {
     if (!attend_supports(p.nh, p.nkv, p.hd)) return cudaErrorInvalidValue;
+    FusedRope fr{};
+    if (frp) {
+        fr = *frp;
+        if (fr.r.nh != p.nh || fr.r.nkv != p.nkv || fr.r.hd != p.hd || 2 * fr.r.half_rot > p.hd || fr.r.v_norm || fr.r.v_from_k)
+            return cudaErrorInvalidValue;
+    }
     const uint32_t g = p.nh / p.nkv;
     if (p.hd == 64)
-        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl)
-                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
-    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl)
-                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl);
+        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr)
+                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr)
+                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
 }
 
 cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st, bool pdl) {

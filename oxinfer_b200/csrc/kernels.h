@@ -182,9 +182,19 @@ cudaError_t launch_qk_rope(const float* qkv, float* qo, void* kc, void* vc, int 
                            const uint32_t* sp, const DecRope& p, cudaStream_t st, bool pdl = false);
 bool attend_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
 size_t attend_part_floats(uint32_t nh, uint32_t hd);  // scratch for the per-split partials
+// Attention that prepares its own inputs: with qkv set, the kernel applies RoPE to the token's query heads as it stages
+// them (`q` is not read), and the CTA whose keys end at the token's position rotates the token's key, appends key and value
+// to the caches and puts them into its tile; the arithmetic of launch_qk_rope, which is then not launched. Per-head norms
+// are not taken (r.* as for launch_qk_rope; qkv == nullptr: plain attention over q and the caches).
+struct FusedRope {
+    const float* qkv;
+    const float* cs_table;
+    DecRope r;
+};
 // counters: nkv zeroed words (left zero by every launch); status: set to 1 if a bounded wait gave up.
-cudaError_t launch_attend(const float* q, const void* kc, const void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
-                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl = false);
+cudaError_t launch_attend(const float* q, void* kc, void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl = false,
+                          const FusedRope* fr = nullptr);
 // Host-order rows [n][nkv][hd] f32 <-> cache rows pos0 .. pos0 + n - 1.
 cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, uint32_t nkv, uint32_t hd, uint32_t max_len, uint32_t pos0,
                            uint32_t n, cudaStream_t st);

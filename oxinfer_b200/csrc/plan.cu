@@ -19,6 +19,8 @@ namespace b2 {
 namespace {
 
 constexpr uint32_t OP_XPLANES = 100;
+constexpr int ATT_THREADS_HOST = 256;  // threads of an attention unit (a thread per head dimension makes the token's key row)
+static bool overlaps_f(const float* a, size_t na, const float* b, size_t nb) { return a && b && na && nb && a < b + nb && b < a + na; }
 constexpr uint32_t OP_NORM_DEFERRED = 101;  // internal: planes of x * w and per-block sums of squares; the products apply the factor  // internal: planes of a vector no producer kernel could write
 
 std::string fmt(const char* f, ...) {
@@ -131,8 +133,9 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         epi_level = atoi(e);
         p->epilogue_ = epi_level != 0;
     }
+    if (const char* e = getenv("B2_PLAN_FUSE_ROPE")) p->fuse_rope_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_TOKEN_KERNEL"))
-        if (atoi(e) != 0) p->epilogue_ = false;  // the token kernel's program is built from the unfused op list
+        if (atoi(e) != 0) p->epilogue_ = p->fuse_rope_ = false;  // the token kernel's program is built from the unfused op list
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -477,6 +480,44 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     PLAN_CUDA(cudaMalloc((void**)&p->planes_, std::max<size_t>(planes_total, 256)), "cudaMalloc(planes)");
     for (auto& [oi, r] : region_of_op) p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
 
+    // ---- RoPE inside the attention kernel ----------------------------------------------------------------------
+    // A QK_ROPE op without per-head norms whose rotated queries only the ATTEND op right behind it reads: the attention
+    // kernel rotates the queries as it stages them and the unit that holds the newest keys appends the token's key and
+    // value (FusedRope); one launch fewer per layer.
+    if (p->fuse_rope_) {
+        std::vector<Op> kept;
+        kept.reserve(p->ops_.size());
+        for (size_t b = 0; b < p->ops_.size(); b++) {
+            Op& at = p->ops_[b];
+            Op* rp = kept.empty() ? nullptr : &kept.back();
+            if (at.kind == B2_OP_ATTEND && rp && rp->kind == B2_OP_QK_ROPE && !rp->p0 && !rp->p1 && !rp->rope.v_norm && !rp->rope.v_from_k &&
+                rp->kv == at.kv && rp->y == at.x && rp->rope.nh == at.attn.nh && rp->rope.nkv == at.attn.nkv && rp->rope.hd == at.attn.hd &&
+                rp->rope.hd <= (uint32_t)ATT_THREADS_HOST) {
+                // nobody else may read the rotated queries: they are not written any more
+                bool other_reader = overlaps_f(rp->y, (size_t)rp->rope.nh * rp->rope.hd, p->hidden_, p->n_hidden_) ||
+                                    overlaps_f(rp->y, (size_t)rp->rope.nh * rp->rope.hd, p->logits_, p->n_logits_);
+                for (size_t c = 0; c < p->ops_.size() && !other_reader; c++) {
+                    if (c == b || &p->ops_[c] == &at) continue;
+                    const Op& o = p->ops_[c];
+                    if (o.kind == B2_OP_QK_ROPE) continue;  // writes it
+                    const float* q0 = rp->y;
+                    const size_t qn = (size_t)rp->rope.nh * rp->rope.hd;
+                    const size_t xn = o.kind == B2_OP_LINEAR ? o.w.n_in : o.kind == B2_OP_ATTEND ? (size_t)o.attn.nh * o.attn.hd
+                                      : (o.kind == B2_OP_NORM || o.kind == OP_NORM_DEFERRED) ? (size_t)(o.rows - 1) * o.norm.x_stride + o.norm.n : o.n;
+                    if (o.kind == B2_OP_ATTEND && o.x == q0) continue;  // another layer's attention over its own fused queries
+                    if (overlaps_f(q0, qn, o.x, xn) || overlaps_f(q0, qn, o.z, o.n ? o.n : 1)) other_reader = true;
+                }
+                if (!other_reader) {
+                    at.fr = FusedRope{rp->x, nullptr, rp->rope};  // the table's address is known at launch
+                    kept.back() = at;
+                    continue;
+                }
+            }
+            kept.push_back(at);
+        }
+        p->ops_ = std::move(kept);
+    }
+
     // ---- planes written by the product ahead ---------------------------------------------------------------------
     // A split kernel (deferred norm, or the planes of an MLP activation) that directly follows the 4-bit product which
     // wrote its whole input is dropped: that product's CTAs then own whole blocks of 32 rows and split each block once
@@ -578,7 +619,13 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
                 e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st, pdl);
                 break;
             case B2_OP_ATTEND:
-                e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st, pdl);
+                if (o.fr.qkv) {
+                    FusedRope fr = o.fr;
+                    fr.cs_table = rope_table_;
+                    e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st, pdl, &fr);
+                } else {
+                    e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_, o.attn, o.xp, status_, st, pdl);
+                }
                 break;
             case B2_OP_GLU: e = launch_glu(o.x, o.z, o.y, o.n, o.gelu, st, pdl); break;
             case B2_OP_EXCHANGE:

@@ -49,6 +49,7 @@ class DecodePlanImpl {
         size_t off = 0;  // EXCHANGE: offset of the vector in the activation block, in floats
         NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
+        FusedRope fr{};   // ATTEND: RoPE and the cache append done by the attention kernel (the QK_ROPE op ahead of it is dropped)
         EpiPlanes epi{};  // LINEAR: the planes of its output, written by its own last warps (the split kernel behind it is dropped)
     };
     DecodePlanImpl() = default;
@@ -72,6 +73,7 @@ class DecodePlanImpl {
     float* norm_partials_ = nullptr;
     bool fuse_ = true;  // q / k / v style products of one vector as one launch over concatenated rows (B2_PLAN_FUSE=0: off)
     std::vector<void*> fused_;  // device copies made for that
+    bool fuse_rope_ = true;  // RoPE inside the attention kernel where no per-head norm is asked for (B2_PLAN_FUSE_ROPE=0: separate kernels)
     bool epilogue_ = true;  // a 4-bit product writes the planes the next product reads (B2_PLAN_EPILOGUE=0: separate kernels)
     // one allocation each
     float* bufs_ = nullptr;
