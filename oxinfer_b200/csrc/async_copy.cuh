@@ -41,5 +41,20 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
+// Ask the L2 for `bytes` (a multiple of 16) at the 16-byte aligned global address `src`; nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// This CTA's slice of a range, in chunks of 16 KB, spread over the CTA's threads.
+__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* p, size_t n, unsigned cta, unsigned ctas, int tid, int nthreads) {
+    constexpr size_t CHUNK = 16384;
+    const size_t chunks = (n + CHUNK - 1) / CHUNK;
+    for (size_t c = (size_t)cta + (size_t)tid * ctas; c < chunks; c += (size_t)ctas * nthreads) {
+        const size_t at = c * CHUNK;
+        const size_t len = (n - at < CHUNK ? n - at : CHUNK) & ~(size_t)15;
+        if (len) bulk_prefetch_l2(p + at, (uint32_t)len);
+    }
+}
+
 }  // namespace acopy
 }  // namespace b2

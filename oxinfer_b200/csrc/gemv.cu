@@ -172,7 +172,7 @@ constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
 template <class F, bool PAIR, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 1)
 gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status,
-                  NormScale ns, EpiPlanes epi, int slots_per_warp) {
+                  NormScale ns, EpiPlanes epi, int slots_per_warp, NextWeights next) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bars[WARPS * RING_SLOTS_MAX];
     __shared__ uint64_t xbars[RING_X_STEPS];
@@ -199,6 +199,10 @@ gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         ring_prime<PAIR>(w, w2, ring, r_first, r_step, ni);
     }
+    if (next.p0) {  // behind this kernel's own first copies in the queue
+        acopy::prefetch_slice_l2(next.p0, next.n0, blockIdx.x, gridDim.x, threadIdx.x, THREADS);
+        if (next.p1) acopy::prefetch_slice_l2(next.p1, next.n1, blockIdx.x, gridDim.x, threadIdx.x, THREADS);
+    }
     pdl_wait();
     // the planes of x (written by the kernel ahead) -> shared memory, a set of bulk copies per 2048 k: the rows start once
     // the first set has landed
@@ -222,7 +226,7 @@ static int env_int(const char* name, int dflt) {
 
 template <class F, bool PAIR, int WARPS>
 cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, int slots) {
+                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, int slots, NextWeights next) {
     auto kern = gemv4_ring_kernel<F, PAIR, WARPS>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)WARPS * slots * RING_SLOT_BYTES;
     if (smem + 2048 > 227 * 1024) return cudaErrorInvalidValue;
@@ -240,25 +244,25 @@ cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, f
     if (WARPS != 8) per_sm = 1;  // the launch bounds of the wide form
     const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
     return launch_k(kern, dim3((unsigned)grid), dim3(WARPS * 32), smem, st, pdl, w, PAIR ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns, epi,
-                    slots);
+                    slots, next);
 }
 
 template <class F>
 cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, NextWeights next) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     if (epi.out.planes) {
         static const int warps = env_int("B2_EPI_WARPS", 16), slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_EPI_SLOTS", 3)));
         if (warps == 16) {
             const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)16 * slots * RING_SLOT_BYTES;
             if (smem + 2048 <= 227 * 1024)
-                return pair ? launch_ring_w<F, true, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots)
-                            : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots);
+                return pair ? launch_ring_w<F, true, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots, next)
+                            : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots, next);
         }
     }
     static const int plain_slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_RING_SLOTS", RING_SLOTS)));
-    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots)
-                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots);
+    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots, next)
+                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots, next);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -726,11 +730,11 @@ bool gemv_takes_epilogue(const WeightDev& w) {
 }
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, NextWeights next) {
     if (epi.out.planes) {  // only the ring form carries the epilogue, chained or not
         if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
     }
     // The tensor-core form of the 4-bit products is parity-green but not yet the faster one (14336 x 4096: 15.9 us against
     // 11.2; a decode token 2.52 ms against 2.37): its CTA-per-tile mapping leaves 896 tiles on 444 CTAs two or three rounds
@@ -749,8 +753,8 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
     if (ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
     }
     switch (w.fmt) {
         case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);

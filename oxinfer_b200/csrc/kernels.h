@@ -82,13 +82,23 @@ struct EpiPlanes {
     float* partial;
     float pre;
 };
+// The packed weights the NEXT product of a chain will stream (one or two matrices): the product kernel asks the L2 for them
+// (bulk prefetches, a slice per CTA, issued before the kernel waits for its predecessor), so that the next kernel's first
+// ring slots fill from L2 while this one, which is bound by instructions and not by DRAM, runs. p0 == nullptr: nothing.
+struct NextWeights {
+    const uint8_t* p0;
+    size_t n0;
+    const uint8_t* p1;
+    size_t n1;
+};
 // Whether launch_gemv takes an EpiPlanes for this matrix (the 4-bit formats whose planes and rings fit in shared memory).
 bool gemv_takes_epilogue(const WeightDev& w);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f},
-                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
+                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f},
+                        NextWeights next = NextWeights{nullptr, 0, nullptr, 0});
 // A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
 // of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
 // bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),

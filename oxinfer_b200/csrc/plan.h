@@ -50,6 +50,7 @@ class DecodePlanImpl {
         NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
         FusedRope fr{};   // ATTEND: RoPE and the cache append done by the attention kernel (the QK_ROPE op ahead of it is dropped)
+        NextWeights next{};  // LINEAR: the weights of the next product, prefetched into L2 by this one
         EpiPlanes epi{};  // LINEAR: the planes of its output, written by its own last warps (the split kernel behind it is dropped)
     };
     DecodePlanImpl() = default;
