@@ -519,7 +519,7 @@ def run_b200(args, rank, world, local_rank):
         print(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}), flush=True)
         return
     if args.section == "decode":
-        d = decode_extras(be, peaks, args.tokens, 2048, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
+        d = decode_extras(be, peaks, args.tokens, args.context, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
         if rank == 0:
             print(json.dumps({"extra": {"decode": d}}), flush=True)
         if world > 1:
@@ -682,6 +682,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--context", type=int, default=2048, help="with --section decode: tokens in the KV cache before the first decoded token")
     ap.add_argument("--case", default=None, help="with --section gemv: only the cases whose name contains this text")
     ap.add_argument("--no-graph", action="store_true", help="with --section gemv: host-launched kernels instead of a CUDA graph (profiling)")
     ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")

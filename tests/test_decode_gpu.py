@@ -149,7 +149,8 @@ def test_planes_from_the_product_epilogue_are_the_same_bits(backend):
     finally:
         os.environ.pop("B2_PLAN_EPILOGUE", None)
     n = {k: v[0].launches_per_step() for k, v in plans.items()}
-    assert n["2"] < n["1"] < n["0"], n
+    switched_off = any(os.environ.get(k) == "0" for k in ("B2_PLAN_PDL", "B2_PLAN_DEFER_NORM", "B2_GEMV_RING"))
+    assert n["2"] <= n["1"] <= n["0"] and (switched_off or n["2"] < n["1"] < n["0"]), n
     rng = np.random.default_rng(12)
     inv_freq = plans["0"][4]
     for pos in range(5):
