@@ -130,7 +130,7 @@ def run_reference(args, rank):
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
@@ -504,24 +504,28 @@ def run_b200(args, rank, world, local_rank):
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    if world > 1:
+        # Row shards fill half the SMs or less: K runs in two halves per tile (see gemm_tc_plan_create). The shards' rows then
+        # differ from the one-GPU rows by f32 reassociation (the default, unsplit, keeps them bit-identical).
+        os.environ.setdefault("B2_GEMM_SPLIT_K", "2")
     be = ob.Backend(local_rank)
     stream = torch.cuda.current_stream()
     be.set_stream(stream.cuda_stream)
 
     if args.section == "gemv":
-        print(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}), flush=True)
+        emit(json.dumps({"extra": {"gemv": gemv_extras(be, torch, peaks, args.steps, args.case, not args.no_graph)}}))
         return
     if args.section in ("moe", "fp8"):
         fn = moe_extras if args.section == "moe" else fp8_extras
-        print(json.dumps({"extra": {args.section: fn(be, torch, peaks)}}), flush=True)
+        emit(json.dumps({"extra": {args.section: fn(be, torch, peaks)}}))
         return
     if args.section == "refcuda":
-        print(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}), flush=True)
+        emit(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}))
         return
     if args.section == "decode":
         d = decode_extras(be, peaks, args.tokens, args.context, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
         if rank == 0:
-            print(json.dumps({"extra": {"decode": d}}), flush=True)
+            emit(json.dumps({"extra": {"decode": d}}))
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -637,7 +641,8 @@ def run_b200(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": (f"tp{world}: weight rows sharded, y stays sharded by columns on the ranks; an NCCL all-gather of the f32 y "
+            "config": {"workload": WORKLOAD, "split_k": int(os.environ.get("B2_GEMM_SPLIT_K", "1")) if world > 1 else 1,
+                       "parallelism": (f"tp{world}: weight rows sharded, y stays sharded by columns on the ranks; an NCCL all-gather of the f32 y "
                                        f"({M_TOK * N_OUT * 4 / 1e6:.0f} MB) measured apart takes {gather_ms:.3f} ms") if world > 1 else "single GPU",
                        "l2": f"inputs larger than L2: rotating over {copies} weight copies ({copies * shard_bytes / 1e6:.0f} MB) and {ycopies} outputs",
                        "step": "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel" + (" on this rank's rows" if world > 1 else "")},
@@ -670,13 +675,34 @@ def run_b200(args, rank, world, local_rank):
                     line["extra"][name + "_error"] = str(e)
         if dec_tp is not None:
             line["extra"] = {"decode": dec_tp}
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_OUT = None
+
+
+def emit(text: str) -> None:
+    """The result line goes to the process's original standard output; everything libraries print to file descriptor 1
+    (NCCL's version banner, for one) is sent to standard error, so that standard output holds the JSON line alone."""
+    global _OUT
+    if _OUT is None:
+        _OUT = sys.stdout
+    _OUT.write(text + "\n")
+    _OUT.flush()
+
+
+def _keep_stdout_clean() -> None:
+    global _OUT
+    sys.stdout.flush()
+    _OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
 def main():
+    _keep_stdout_clean()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

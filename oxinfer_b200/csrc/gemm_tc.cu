@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
                    int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg,
-                   const int* __restrict__ tile_expert, F8Scales f8) {
+                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits) {
     // A "raw block" is what one weight copy brings per row: a 144-byte 4-bit block (256 k, four pipeline
     // stages) or 128 e4m3 bytes (128 k = one column of FP8 scale blocks, two stages).
     constexpr int RAW_ROW = FMT == B2_FMT_F8E4M3 ? 128 : 144;
@@ -182,7 +182,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     Shared* sh = (Shared*)(raw + RAW_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nsb = K / (64 * RAW_ST), nks = nsb * RAW_ST;
+    // K may be divided between the CTAs of blockIdx.z (k_splits of them, whole super-blocks each): every CTA accumulates
+    // its share and the epilogue adds the shares into a zeroed y (TMA reduce). sb0: this CTA's first super-block.
+    const int nsb = K / (64 * RAW_ST) / k_splits, nks = nsb * RAW_ST;
+    const int sb0 = (int)blockIdx.z * nsb;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
     // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
@@ -226,7 +229,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     mbar_arrive(&sh->a_full[s]);
                 } else {
                     mbar_arrive_expect_tx(&sh->a_full[s], a_bytes);
-                    tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], ks * STAGE_K, m0);
+                    tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], (sb0 * RAW_ST + ks) * STAGE_K, m0);
                     a_issued = ks + 1;
                 }
             }
@@ -250,7 +253,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     continue;
                 }
                 mbar_arrive_expect_tx(&sh->raw_full, w_bytes);
-                tma_load_2d(raw, &tmap_w, &sh->raw_full, sb * RAW_ROW, w_row0 + n0);
+                tma_load_2d(raw, &tmap_w, &sh->raw_full, (sb0 + sb) * RAW_ROW, w_row0 + n0);
                 w_issued = sb + 1;
             }
             if (sh->abort_flag && w_issued > 0)
@@ -321,7 +324,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->raw_empty);
                     float scale = 1.0f;
-                    if (f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb);
+                    if (f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb0 + sb);
                     const __half2 sc2 = __float2half2_rn(scale * f8.pre);
                     const int ks = sb * 2 + set;
                     const int s = ks % STAGES;
@@ -479,9 +482,14 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         fence_proxy_async();
                         __syncwarp();
                         if (lane == 0 && !(dbg & 8)) {
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
-                                         "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
-                                         : "memory");
+                            if (k_splits > 1)
+                                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
+                                             "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
+                                             : "memory");
+                            else
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
+                                             "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
+                                             : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
@@ -501,7 +509,11 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         int n = n0 + cc;
                         if (y_dtype == B2_F32) {
                             float* o = (float*)y + (size_t)token * n_out + n;
-                            if (n + 16 <= n_out && (n_out & 3) == 0) {
+                            if (k_splits > 1) {  // this CTA's share of K: added to the other share (y starts at zero)
+#pragma unroll
+                                for (int i = 0; i < 16; i++)
+                                    if (n + i < n_out) atomicAdd(o + i, __uint_as_float(v[i]));
+                            } else if (n + 16 <= n_out && (n_out & 3) == 0) {
 #pragma unroll
                                 for (int i = 0; i < 4; i++)
                                     ((float4*)o)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
@@ -601,11 +613,18 @@ struct GemmPlan {
     int y_dtype;
     size_t t, K, n_out;
     int tile_n, m_halves, n_tiles, m_tiles;
+    int k_splits = 1;
+    int split_asked = 1;  // B2_GEMM_SPLIT_K when the plan was made (a cached plan is reused only under the same setting)
 };
 
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
     if (w.fmt == B2_FMT_F8E4M3) return w.n_in % 128 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0 && (w.p1 == nullptr || w.bs_cols == 128);
     return (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
+}
+
+static int split_k_asked() {
+    const char* e = getenv("B2_GEMM_SPLIT_K");
+    return e ? atoi(e) : 1;
 }
 
 // Tile width (weight rows per CTA): the multiple of 16 up to MAX_TILE_N that minimizes the time of the
@@ -654,6 +673,26 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count);
+    // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
+    // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
+    // with its width, so a grid that fills half the SMs or less runs nearly twice as fast as twice as many CTAs of half
+    // the depth. Two shares only: their sum does not depend on the order the two reductions land in. f32 output, dense.
+    {
+        const int want = split_k_asked();
+        p->split_asked = want;
+        const int sb_k = w.fmt == B2_FMT_F8E4M3 ? 128 : 256;
+        const size_t nsb_all = w.n_in / sb_k;
+        if (want == 2 && y_dtype == B2_F32 && !tile_expert && nsb_all % 2 == 0 && nsb_all >= 8) {
+            const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count);
+            const size_t tiles1 = (w.n_out + p->tile_n - 1) / p->tile_n * (size_t)p->m_tiles;
+            const size_t tiles2 = (w.n_out + tn2 - 1) / tn2 * (size_t)p->m_tiles * 2;
+            const size_t waves1 = (tiles1 + sm_count - 1) / sm_count, waves2 = (tiles2 + sm_count - 1) / sm_count;
+            if (waves2 <= waves1) {  // the split grid is no deeper in waves: half the stages per CTA
+                p->k_splits = 2;
+                p->tile_n = tn2;
+            }
+        }
+    }
     p->n_tiles = (int)((w.n_out + p->tile_n - 1) / p->tile_n);
     {
         cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)t};
@@ -706,7 +745,8 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
 void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
 
 bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype) {
-    return p && p->experts == 1 && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out;
+    return p && p->experts == 1 && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
+           p->split_asked == split_k_asked();
 }
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
@@ -719,11 +759,15 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles);
+    dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles, (unsigned)p->k_splits);
+    if (p->k_splits > 1) {  // the shares are added into y
+        cudaError_t e = cudaMemsetAsync(y, 0, t * w.n_out * sizeof(float), st);
+        if (e != cudaSuccess) return e;
+    }
     auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : w.fmt == B2_FMT_F8E4M3 ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
     F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
-                                                status_dev, debug_switches(), p->tile_expert, f8);
+                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits);
     return cudaGetLastError();
 }
 

@@ -139,3 +139,32 @@ def test_fp8_matmul_matches_oracle(backend, shape):
         ys = np.zeros((t, n_out - 128), np.float32)
         assert backend.matmul(x, [ob.Job(sh, ys)])
         assert np.array_equal(ys, y[:, 128:])
+
+
+def test_split_k_adds_two_shares(backend):
+    """B2_GEMM_SPLIT_K=2: grids that fill half the SMs or less run K in two halves whose sums are added into a zeroed y
+    (two shares only, so the result does not depend on which lands first). Same bound against the f64 definition, and
+    within f32 reassociation of the unsplit result; a wide matrix (more CTAs than half the SMs) is not split and keeps its bits."""
+    import os
+
+    if os.environ.get("B2_GEMM_SPLIT_K"):
+        pytest.skip("the split is switched on for the whole run: nothing to compare it with")
+    for n_out, n_in, t, split_expected in ((1792, 4096, 512, True), (1000, 2048, 300, True), (14336, 1024, 64, False)):
+        ref, m = make_pair("q4_k", n_out, n_in, 770 + n_out)
+        dev = backend.upload(ref, n_out, n_in)
+        x = synth.activations(t, n_in, 771)
+        exact = m.matmul_f64(x)
+        y1 = np.full((t, n_out), np.nan, np.float32)
+        assert backend.matmul(x, [ob.Job(dev, y1)])
+        os.environ["B2_GEMM_SPLIT_K"] = "2"
+        try:
+            y2 = np.full((t, n_out), np.nan, np.float32)
+            assert backend.matmul(x, [ob.Job(dev, y2)])
+            y3 = np.full((t, n_out), np.nan, np.float32)
+            assert backend.matmul(x, [ob.Job(dev, y3)])
+        finally:
+            os.environ.pop("B2_GEMM_SPLIT_K", None)
+        assert np.isfinite(y2).all() and np.array_equal(y2, y3)          # the same bits run after run
+        assert row_err(y1, exact) < 1e-3 and row_err(y2, exact) < 1e-3
+        assert row_err(y2, y1.astype(np.float64)) < 1e-5
+        assert np.array_equal(y1, y2) == (not split_expected)
