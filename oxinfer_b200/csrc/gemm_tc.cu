@@ -162,7 +162,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
-template <int FMT>
+template <int FMT, bool SPLIT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
@@ -184,8 +184,9 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // K may be divided between the CTAs of blockIdx.z (k_splits of them, whole super-blocks each): every CTA accumulates
     // its share and the epilogue adds the shares into a zeroed y (TMA reduce). sb0: this CTA's first super-block.
-    const int nsb = K / (64 * RAW_ST) / k_splits, nks = nsb * RAW_ST;
-    const int sb0 = (int)blockIdx.z * nsb;
+    // (SPLIT is a template parameter so that the unsplit kernel carries none of this.)
+    const int nsb = SPLIT ? K / (64 * RAW_ST) / k_splits : K / (64 * RAW_ST), nks = nsb * RAW_ST;
+    const int sb0 = SPLIT ? (int)blockIdx.z * nsb : 0;
     const int n0 = blockIdx.x * tile_n;
     const int m0 = blockIdx.y * 128 * m_halves;
     // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
@@ -482,7 +483,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         fence_proxy_async();
                         __syncwarp();
                         if (lane == 0 && !(dbg & 8)) {
-                            if (k_splits > 1)
+                            if (SPLIT)
                                 asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
                                              "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
                                              : "memory");
@@ -509,7 +510,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         int n = n0 + cc;
                         if (y_dtype == B2_F32) {
                             float* o = (float*)y + (size_t)token * n_out + n;
-                            if (k_splits > 1) {  // this CTA's share of K: added to the other share (y starts at zero)
+                            if (SPLIT) {  // this CTA's share of K: added to the other share (y starts at zero)
 #pragma unroll
                                 for (int i = 0; i < 16; i++)
                                     if (n + i < n_out) atomicAdd(o + i, __uint_as_float(v[i]));
@@ -753,9 +754,12 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
                            cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
@@ -764,7 +768,10 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         cudaError_t e = cudaMemsetAsync(y, 0, t * w.n_out * sizeof(float), st);
         if (e != cudaSuccess) return e;
     }
-    auto kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4> : w.fmt == B2_FMT_F8E4M3 ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3> : gemm_q4k_tc_kernel<B2_FMT_Q4_K>;
+    const bool split = p->k_splits > 1;
+    auto kern = w.fmt == B2_FMT_MLX4     ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false>)
+                : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>)
+                                         : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>);
     F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
                                                 status_dev, debug_switches(), p->tile_expert, f8, p->k_splits);
