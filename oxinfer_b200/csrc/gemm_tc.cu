@@ -628,20 +628,24 @@ static int split_k_asked() {
     return e ? atoi(e) : 1;
 }
 
-// Tile width (weight rows per CTA): the multiple of 16 up to MAX_TILE_N that minimizes the time of the
-// slowest SM, i.e. waves * tile_n, over the grid ceil(n_out / tile_n) * m_tiles.
-static int pick_tile_n(size_t n_out, int m_tiles, int sm_count) {
+// Tile width (weight rows per CTA): the multiple of 16 up to MAX_TILE_N that minimizes the time of the slowest SM,
+// waves x (time of one CTA), over the grid ceil(n_out / tile_n) * m_tiles. A CTA's time is mostly its k loop, whose stage
+// time hardly depends on the width (1108 cycles per stage at 208 rows, 1152 at 104), plus an epilogue that grows with
+// the width; in units of rows the measurements fit (tile_n + 13 per k stage), with widths above 208 costing about five
+// times as much per extra row (58-60 us at 240 against 54 at 208 for 64 stages). So the count of waves decides first.
+static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K) {
     // B2_GEMM_TILE_N forces a width (tests and tuning sweeps).
     if (const char* env = getenv("B2_GEMM_TILE_N")) {
         int v = atoi(env);
         if (v >= 16 && v <= MAX_TILE_N && v % 16 == 0) return v;
     }
+    const double per_cta = 24.0 + 13.0 * (double)(K / 64);
     int best = MAX_TILE_N;
     double best_cost = 1e30;
     for (int tn = MAX_TILE_N; tn >= 64; tn -= 16) {
         size_t tiles = (n_out + tn - 1) / tn * (size_t)m_tiles;
         size_t waves = (tiles + sm_count - 1) / sm_count;
-        double cost = (double)waves * (tn + 24);  // + fixed per-tile overhead, in units of rows
+        double cost = (double)waves * (tn + per_cta + (tn > 208 ? 4.0 * (tn - 208) : 0.0));
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
             best = tn;
@@ -673,7 +677,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     int sm_count = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count);
+    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in);
     // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
     // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
     // with its width, so a grid that fills half the SMs or less runs nearly twice as fast as twice as many CTAs of half
@@ -684,7 +688,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         const int sb_k = w.fmt == B2_FMT_F8E4M3 ? 128 : 256;
         const size_t nsb_all = w.n_in / sb_k;
         if (want == 2 && y_dtype == B2_F32 && !tile_expert && nsb_all % 2 == 0 && nsb_all >= 8) {
-            const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count);
+            const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count, w.n_in / 2);
             const size_t tiles1 = (w.n_out + p->tile_n - 1) / p->tile_n * (size_t)p->m_tiles;
             const size_t tiles2 = (w.n_out + tn2 - 1) / tn2 * (size_t)p->m_tiles * 2;
             const size_t waves1 = (tiles1 + sm_count - 1) / sm_count, waves2 = (tiles2 + sm_count - 1) / sm_count;
