@@ -25,7 +25,18 @@ def build(backend, cfg=CFG, seed=900, max_len=512, kv_f16=False, interleaved=Tru
     """`token_kernel`: the persistent one-launch-per-token kernel (the default), else the graph of one launch per op."""
     import os
 
-    os.environ["B2_PLAN_TOKEN_KERNEL"] = "1" if token_kernel else "0"
+    before = os.environ.get("B2_PLAN_TOKEN_KERNEL")
+    os.environ["B2_PLAN_TOKEN_KERNEL"] = "1" if token_kernel else "0"   # read when the plan is made; put back below
+    try:
+        return _build(backend, cfg, seed, max_len, kv_f16, interleaved)
+    finally:
+        if before is None:
+            os.environ.pop("B2_PLAN_TOKEN_KERNEL", None)
+        else:
+            os.environ["B2_PLAN_TOKEN_KERNEL"] = before
+
+
+def _build(backend, cfg, seed, max_len, kv_f16, interleaved):
     layers, final_norm, head, embed, shapes = synth.llama_weights(seed=seed, **cfg)
     dev_layers, cpu_layers = [], []
     for L in layers:

@@ -16,7 +16,8 @@ ROOT = Path(__file__).resolve().parent.parent
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="tensor-parallel decode needs two GPUs")
 def test_two_ranks_match_single_gpu_bitwise():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = {k: v for k, v in os.environ.items() if not k.startswith("B2_")}   # no switches left over from other tests
+    env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29641",
            str(ROOT / "tests" / "tp_decode_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
