@@ -386,6 +386,9 @@ class Backend {
         return B2_OK;
     }
 
+    // Formats whose many-token products run through the multi-row matrix-vector kernel (no tensor-core kernel for them).
+    static bool rows_path(const WeightDev& w) { return (w.fmt == B2_FMT_Q6_K || w.fmt == B2_FMT_Q8_0) && gemv_supports(w); }
+
     // t tokens on the device through the tensor-core GEMM (or token by token through the GEMV).
     int matmul_dev(uint64_t h, const void* x, int x_dtype, size_t t, void* y, int y_dtype) {
         Weight* w = find(h);
@@ -397,6 +400,37 @@ class Backend {
             for (size_t i = 0; i < t; i++) {
                 int rc = matvec_dev(h, 0, (const float*)x + i * K, (float*)y + i * w->dev.n_out, B2_MODE_STORE, nullptr);
                 if (rc) return rc;
+            }
+            return B2_OK;
+        }
+        if (rows_path(w->dev) && x_dtype == B2_F32 && y_dtype == B2_F32) {
+            // Q6_K / Q8_0 have no tensor-core kernel yet: the tokens go four at a time through the multi-row matrix-vector
+            // kernel (the weights are read once per four tokens; every row equals its one-token result bit for bit).
+            const size_t stride = (xplanes_bytes(K) + 255) / 256 * 256;
+            cudaError_t e = xplanes.reserve(t * stride);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
+            e = launch_xplanes_rows((const float*)x, t, K, (uint8_t*)xplanes.p, stride, stream);
+            launches++;
+            prepared_k = 0;  // the scratch holds many rows' planes now
+            if (e != cudaSuccess) return cuda_fail(e, "xplanes (rows)");
+            const size_t n_out = w->dev.n_out;
+            for (size_t i = 0; i < t; i += 4) {
+                const size_t nt = std::min<size_t>(4, t - i);
+                const float* xi = (const float*)x + i * K;
+                float* yi = (float*)y + i * n_out;
+                uint8_t* pi = (uint8_t*)xplanes.p + i * stride;
+                e = nt > 1 ? launch_gemv_multi(w->dev, nullptr, xi, K, xplanes_at(pi, K), stride, yi, n_out, (int)nt, B2_MODE_STORE, sm_count, stream)
+                           : cudaErrorInvalidValue;
+                if (e == cudaErrorInvalidValue) {  // one row, or the rows' planes do not fit in shared memory together
+                    for (size_t r = 0; r < nt; r++) {
+                        e = launch_gemv(w->dev, nullptr, xi + r * K, xplanes_at(pi + r * stride, K), yi + r * n_out, B2_MODE_STORE, nullptr, sm_count, stream);
+                        launches++;
+                        if (e != cudaSuccess) return cuda_fail(e, "gemv");
+                    }
+                } else {
+                    launches++;
+                    if (e != cudaSuccess) return cuda_fail(e, "gemv (several rows)");
+                }
             }
             return B2_OK;
         }
@@ -464,7 +498,7 @@ class Backend {
             if (w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
                 return fail(B2_ERR_ARG, "[b200qmm: matmul: job %zu does not match its weight's shape]", j);
             bool small = t <= 8 && gemv_supports(w->dev);
-            if (!small && !gemm_tc_supports(w->dev, t)) return fail(B2_DECLINED, "[b200qmm: matmul: job %zu has no kernel at t = %zu]", j, t);
+            if (!small && !gemm_tc_supports(w->dev, t) && !rows_path(w->dev)) return fail(B2_DECLINED, "[b200qmm: matmul: job %zu has no kernel at t = %zu]", j, t);
             max_out = std::max(max_out, jobs[j].n_out);
         }
         auto t0 = clk::now();

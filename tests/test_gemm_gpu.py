@@ -94,13 +94,36 @@ def test_q4k_matmul_full_size_config(backend):
     assert row_err(y3, 0.5 * y[:256].astype(np.float64) + 0.25 * y[256:].astype(np.float64)) < 5e-4
 
 
-def test_matmul_declines_formats_without_a_tensor_core_kernel(backend):
+@pytest.mark.parametrize("fmt", ["q6_k", "q8_0"])
+@pytest.mark.parametrize("shape", [(256, 512, 64), (1000, 2048, 9), (4099, 4096, 131)])
+def test_many_tokens_for_formats_without_a_tensor_core_kernel(backend, fmt, shape):
+    """Q6_K and Q8_0 at t > 8: the tokens run four at a time through the multi-row matrix-vector kernel, so the bound is the
+    matrix-vector one and every row equals its one-token result bit for bit (ragged token and row counts included)."""
+    n_out, n_in, t = shape
+    ref, m = make_pair(fmt, n_out, n_in, 440 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 441)
+    y = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert np.isfinite(y).all()
+    assert row_err(y, m.matmul_f64(x)) < 2e-5
+    for i in (0, t // 2, t - 1):
+        y1 = np.zeros((1, n_out), np.float32)
+        assert backend.matmul(x[i:i + 1], [ob.Job(dev, y1)])
+        assert np.array_equal(y1[0], y[i])
+
+
+def test_matmul_declines_what_it_cannot_take(backend):
+    """A shape outside every kernel (n_in not a multiple of the block size is refused at upload; here: bf16 activations for a
+    format that only has the f32 matrix-vector path) is declined with nothing written (src/gpu.rs:158-160)."""
     n_out, n_in, t = 256, 512, 64
     ref, _ = make_pair("q6_k", n_out, n_in, 440)
     dev = backend.upload(ref, n_out, n_in)
-    y = np.full((t, n_out), 7.0, np.float32)
-    assert backend.matmul(synth.activations(t, n_in, 441), [ob.Job(dev, y)]) is False
-    assert (y == 7.0).all()  # declined: nothing written (src/gpu.rs:158-160)
+    x = torch.from_numpy(synth.activations(t, n_in, 441)).cuda().to(torch.bfloat16)
+    y = torch.full((t, n_out), 7.0, device="cuda", dtype=torch.float32)
+    assert backend.matmul_dev(dev, x, y) is False
+    torch.cuda.synchronize()
+    assert bool((y == 7.0).all())
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 9), (4096, 4096, 64), (1536, 2048, 100), (2048, 768, 257), (1000, 1024, 512)])
