@@ -94,6 +94,13 @@ int b2_set_stream(b2_ctx* ctx, void* cuda_stream);
  * it reads the vector or writes its output, so results are unchanged. Meant for a caller that queues a token's
  * products back to back (the decode plan does this by itself). Off by default. */
 int b2_set_chained(b2_ctx* ctx, int on);
+/* The boundary's exactness switch, `gpu::set_exact` / `exact()` (src/gpu.rs:313-338: "no reduced-precision matrix units").
+ * Off (the default), a many-token matmul rounds activations and expanded weights to f16 operands once: results within 1e-3
+ * of the f64 product per output row (FP8: 2e-3). On, the tensor-core GEMM takes every f32 / bf16 activation as two f16
+ * terms and, for Q4_K, every weight as two f16 terms too (the other 4-bit and 8-bit formats' values need no second term):
+ * results within 1e-4 per output row, the bound the reference holds its own f32 CUDA kernels to (src/cuda.rs:1684), at two to
+ * four times the tensor-core work. Matrix-vector products (t <= 8) carry 21-bit activations either way. */
+int b2_set_exact(b2_ctx* ctx, int on);
 /* `Backend::stats`, src/cuda.rs:1120-1132: cumulative copy-in / kernel / copy-out time as text. */
 const char* b2_stats(b2_ctx* ctx);
 /* Count of kernel launches issued by this context since it was opened. */
@@ -106,9 +113,19 @@ int b2_wants(b2_ctx* ctx, size_t n_out, size_t n_in, size_t t);
 
 /* `Backend::upload` for WeightRef::Q4 with offsets, src/cuda.rs:640-699, taking the MLX triple as
  * it is on disk (src/safetensors.rs:767-853): w `[n_out][n_in/8]` u32, scales and biases
- * `[n_out][n_in/group]` bf16 bits. group must be 64; n_in a multiple of 256. Repacked on the device into Q4_K-shaped blocks. */
+ * `[n_out][n_in/group]` bf16 bits. group must be 64; n_in a multiple of 256. Repacked on the device into Q4_K-shaped blocks
+ * that carry from_mlx_q4's values (d = f16(scale), offset = bf16(bias + 8 scale), src/quant.rs:518-563). */
 int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in,
                    size_t group, b2_weight* out);
+/* `Backend::upload` for WeightRef::Q4(&Q4Matrix) (src/gpu.rs:15-21, src/cuda.rs:640-699), the layout a backend is actually
+ * handed (src/quant.rs:427-440; on the device the reference keeps it as DW{q, s, o, gpr, gk}, src/cuda_decode.cu:27):
+ * q `[n_out][n_in/2]` in Q4_0 order (byte j of a 32-block = element j low nibble, element j+16 high), scales
+ * `[n_out][n_in/32]` f16 bits, offsets `[n_out][n_in/group]` bf16 bits (Offsets, the affine term from_mlx_q4 adds,
+ * src/quant.rs:518-563). group a multiple of 64, n_in a multiple of 256. Gives the same device blocks, bit for bit,
+ * as b2_upload_mlx4 gives for the MLX triple the matrix was made from. Declined (> 0): offsets == NULL (plain Q4 has a
+ * scale per 32 weights), or a matrix whose 64-groups do not share one scale. */
+int b2_upload_q4(b2_ctx* ctx, const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in,
+                 b2_weight* out);
 /* `Backend::upload` for WeightRef::Gguf (declined by the reference at src/cuda.rs:642): raw GGUF
  * rows of `fmt` (B2_FMT_Q4_K / Q6_K / Q8_0 / F8E4M3). For F8E4M3, `block_scales` is
  * `[ceil(n_out/bs_rows)][ceil(n_in/bs_cols)]` f32 (BlockScales, src/ggml.rs:250-256), else NULL. */

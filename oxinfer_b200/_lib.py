@@ -86,11 +86,13 @@ _SIGNATURES = {
     "b2_last_error": (C.c_char_p, [C.c_void_p]),
     "b2_open_error": (C.c_char_p, []),
     "b2_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b2_set_exact": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_set_chained": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_stats": (C.c_char_p, [C.c_void_p]),
     "b2_launch_count": (C.c_uint64, [C.c_void_p]),
     "b2_wants": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
     "b2_upload_mlx4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_upload_q4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
     "b2_upload_gguf": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
     "b2_shard_rows": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
     "b2_free_weight": (C.c_int, [C.c_void_p, C.c_uint64]),

@@ -35,6 +35,16 @@ class MlxQ4:
 
 
 @dataclass
+class Q4Matrix:
+    """``WeightRef::Q4(&Q4Matrix)`` as a backend receives it (``src/gpu.rs:15-21``, ``src/quant.rs:427-440``): Q4_0-order
+    nibbles, an f16 scale per 32 weights and, for MLX checkpoints, a bf16 offset per group."""
+    q: np.ndarray               # uint8 [n_out, n_in/2]
+    scales: np.ndarray          # uint16 (f16 bits) [n_out, n_in/32]
+    offsets: np.ndarray | None  # uint16 (bf16 bits) [n_out, n_in/group]
+    group: int = 64
+
+
+@dataclass
 class Gguf:
     """``WeightRef::Gguf``: raw rows of a GGUF block format, FP8 with its block scales."""
     kind: int            # FMT_Q4_K / FMT_Q6_K / FMT_Q8_0 / FMT_F8E4M3
@@ -168,6 +178,10 @@ class Backend:
         """Device-resident matrix-vector calls launch as a dependent chain (each kernel may start while the one ahead drains)."""
         self._check(self._L.b2_set_chained(self._ctx, int(on)))
 
+    def set_exact(self, on: bool) -> None:
+        """``gpu::set_exact`` (``src/gpu.rs:313-338``): many-token matmuls with two-term f16 operands, within 1e-4 per row."""
+        self._check(self._L.b2_set_exact(self._ctx, int(on)))
+
     def check_status(self) -> None:
         self._check(self._L.b2_check_status(self._ctx))
 
@@ -175,9 +189,15 @@ class Backend:
     def wants(self, n_out: int, n_in: int, t: int) -> bool:
         return bool(self._L.b2_wants(self._ctx, n_out, n_in, t))
 
-    def upload(self, w: MlxQ4 | Gguf, n_out: int, n_in: int) -> DeviceWeight | None:
+    def upload(self, w: "MlxQ4 | Q4Matrix | Gguf", n_out: int, n_in: int) -> DeviceWeight | None:
         h = C.c_uint64()
-        if isinstance(w, MlxQ4):
+        if isinstance(w, Q4Matrix):
+            assert w.q.dtype == np.uint8 and w.scales.dtype == np.uint16 and w.q.size == n_out * n_in // 2 and w.scales.size == n_out * n_in // 32
+            assert w.offsets is None or (w.offsets.dtype == np.uint16 and w.offsets.size == n_out * n_in // w.group)
+            rc = self._L.b2_upload_q4(self._ctx, _ptr(w.q), _ptr(w.scales), None if w.offsets is None else _ptr(w.offsets), w.group, n_out, n_in,
+                                      C.byref(h))
+            fmt = FMT_MLX4
+        elif isinstance(w, MlxQ4):
             assert w.w.dtype == np.uint32 and w.scales.dtype == np.uint16 and w.biases.dtype == np.uint16
             assert w.w.size == n_out * n_in // 8 and w.scales.size == n_out * n_in // w.group == w.biases.size
             rc = self._L.b2_upload_mlx4(self._ctx, _ptr(w.w), _ptr(w.scales), _ptr(w.biases), n_out, n_in, w.group, C.byref(h))

@@ -60,6 +60,7 @@ class Backend {
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     bool chained = false;  // b2_set_chained
+    bool exact = false;    // b2_set_exact
     std::mutex mu;  // calls serialize, like the staging lock of src/cuda.rs:430,1443
     std::string err;
     std::string stats_text;
@@ -151,6 +152,49 @@ class Backend {
         wt.dev.n_out = n_out;
         wt.dev.n_in = n_in;
         wt.dev.group = group;
+        wt.dev.p0 = (const uint8_t*)blocks;
+        wt.bytes = nb * 144;
+        *out = next_handle++;
+        weights[*out] = std::move(wt);
+        return B2_OK;
+    }
+
+    // ---- Backend::upload for WeightRef::Q4(&Q4Matrix) with offsets (src/gpu.rs:15-21, src/cuda.rs:640-699): the layout the
+    // reference's loader hands a backend (src/quant.rs:427-440), i.e. what from_mlx_q4 made of an MLX checkpoint. Produces the
+    // same device blocks as upload_mlx4 does from the on-disk triple.
+    int upload_q4(const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in, uint64_t* out) {
+        if (!q || !scales || !out) return fail(B2_ERR_ARG, "[b200qmm: upload_q4: null argument]");
+        if (!offsets) return fail(B2_DECLINED, "[b200qmm: upload_q4: a Q4 matrix without offsets (plain --quant q4) has one scale per 32 weights; no device format for it]");
+        if (group == 0 || group % 64 != 0 || n_in % 256 != 0 || n_in % group != 0 || n_out == 0)
+            return fail(B2_DECLINED, "[b200qmm: upload_q4: the offsets' group must be a multiple of 64 dividing n_in, and n_in a multiple of 256]");
+        Weight wt;
+        std::vector<void*> tmp;
+        void *p0, *p1, *p2, *flag, *blocks;
+        int rc;
+        const size_t nb = n_out * (n_in / 256);
+        if ((rc = alloc_copy(q, n_out * n_in / 2, &p0, tmp)) || (rc = alloc_copy(scales, n_out * (n_in / 32) * 2, &p1, tmp)) ||
+            (rc = alloc_copy(offsets, n_out * (n_in / group) * 2, &p2, tmp)) || (rc = alloc_copy(nullptr, 4, &flag, tmp)) ||
+            (rc = alloc_copy(nullptr, nb * 144, &blocks, wt.owned))) {
+            drop(tmp);
+            drop(wt.owned);
+            return rc;
+        }
+        int mismatch = 0;
+        cudaError_t e = cudaMemsetAsync(flag, 0, 4, stream);
+        if (e == cudaSuccess) e = launch_repack_q4a((const uint8_t*)p0, (const uint16_t*)p1, (const uint16_t*)p2, n_out, n_in, group, (uint8_t*)blocks, (int*)flag, stream);
+        launches++;
+        if (e == cudaSuccess) e = cudaMemcpyAsync(&mismatch, flag, 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        drop(tmp);
+        if (e != cudaSuccess || mismatch) {
+            drop(wt.owned);
+            if (e != cudaSuccess) return cuda_fail(e, "repack_q4a");
+            return fail(B2_DECLINED, "[b200qmm: upload_q4: the two 32-blocks of a 64-group differ in scale (not a matrix from_mlx_q4 made)]");
+        }
+        wt.dev.fmt = B2_FMT_MLX4;
+        wt.dev.n_out = n_out;
+        wt.dev.n_in = n_in;
+        wt.dev.group = 64;
         wt.dev.p0 = (const uint8_t*)blocks;
         wt.bytes = nb * 144;
         *out = next_handle++;
@@ -419,17 +463,16 @@ class Backend {
                 const float* xi = (const float*)x + i * K;
                 float* yi = (float*)y + i * n_out;
                 uint8_t* pi = (uint8_t*)xplanes.p + i * stride;
-                e = nt > 1 ? launch_gemv_multi(w->dev, nullptr, xi, K, xplanes_at(pi, K), stride, yi, n_out, (int)nt, B2_MODE_STORE, sm_count, stream)
-                           : cudaErrorInvalidValue;
-                if (e == cudaErrorInvalidValue) {  // one row, or the rows' planes do not fit in shared memory together
-                    for (size_t r = 0; r < nt; r++) {
-                        e = launch_gemv(w->dev, nullptr, xi + r * K, xplanes_at(pi + r * stride, K), yi + r * n_out, B2_MODE_STORE, nullptr, sm_count, stream);
-                        launches++;
-                        if (e != cudaSuccess) return cuda_fail(e, "gemv");
-                    }
-                } else {
+                if (nt > 1 && gemv_multi_fits(w->dev, (int)nt)) {
+                    e = launch_gemv_multi(w->dev, nullptr, xi, K, xplanes_at(pi, K), stride, yi, n_out, (int)nt, B2_MODE_STORE, sm_count, stream);
                     launches++;
                     if (e != cudaSuccess) return cuda_fail(e, "gemv (several rows)");
+                    continue;
+                }
+                for (size_t r = 0; r < nt; r++) {  // one row, or the rows' planes do not fit in shared memory together
+                    e = launch_gemv(w->dev, nullptr, xi + r * K, xplanes_at(pi + r * stride, K), yi + r * n_out, B2_MODE_STORE, nullptr, sm_count, stream);
+                    launches++;
+                    if (e != cudaSuccess) return cuda_fail(e, "gemv");
                 }
             }
             return B2_OK;
@@ -438,19 +481,30 @@ class Backend {
         int rc = ensure_status();
         if (rc) return rc;
         cudaError_t e;
-        const void* xh = x;  // f16 activations are used where they lie (16-byte aligned rows)
+        const void* xh = x;  // f16 activations are used where they lie (16-byte aligned rows): in f16's range by definition
+        const float* unscale = nullptr;
+        size_t lo_row0 = 0;
+        // exact: 128-token tiles for any t, so that the activations go in as two f16 terms, and two-term weights where the
+        // format's values do not fit f16 (Q4_K): f32-like results, several times the tensor-core work
+        const int w_terms = exact ? 2 : 1;
         if (x_dtype != B2_F16 || ((uintptr_t)x & 15)) {
-            e = x16.reserve(t * K * 2);
+            // f32 / bf16 rows -> f16 with a power-of-two factor per token row that the GEMM's epilogue takes out again
+            // (up to 128 tokens, where a CTA's tile has room for it, as two f16 terms: 22 bits of every activation)
+            lo_row0 = exact ? (t + 127) / 128 * 128 : (t <= 128 ? 128 : 0);
+            const size_t x16_bytes = ((lo_row0 + t) * K * 2 + 255) / 256 * 256;
+            e = x16.reserve(x16_bytes + t * 4);
             if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(x16)");
-            e = launch_to_f16(x, x_dtype, t, t, K, x16.p, stream);
+            float* us = (float*)((uint8_t*)x16.p + x16_bytes);
+            e = launch_to_f16(x, x_dtype, t, K, x16.p, us, stream, lo_row0);
             launches++;
             if (e != cudaSuccess) return cuda_fail(e, "to_f16");
             xh = x16.p;
+            unscale = us;
         }
         // Tensor maps (activations + packed weights) are cached per (weights, activations, t).
         GemmPlan* plan = nullptr;
         for (GemmPlan* p : plans)
-            if (gemm_tc_plan_matches(p, w->dev, xh, t, y, y_dtype)) {
+            if (gemm_tc_plan_matches(p, w->dev, xh, t, y, y_dtype, lo_row0, w_terms, lo_row0 ? 1 : 0)) {
                 plan = p;
                 break;
             }
@@ -460,11 +514,11 @@ class Backend {
                 plans.clear();
             }
             char msg[256] = {0};
-            e = gemm_tc_plan_create(w->dev, xh, t, y, y_dtype, &plan, msg, sizeof msg);
+            e = gemm_tc_plan_create(w->dev, xh, t, y, y_dtype, &plan, msg, sizeof msg, 1, nullptr, lo_row0 ? 1 : 0, lo_row0, w_terms);
             if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
             plans.push_back(plan);
         }
-        e = launch_gemm_tc(plan, w->dev, t, y, y_dtype, gemm_status, sm_count, stream);
+        e = launch_gemm_tc(plan, w->dev, t, y, y_dtype, gemm_status, sm_count, stream, unscale);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "gemm_tc");
         return B2_OK;
@@ -476,7 +530,9 @@ class Backend {
         GemmStatus s{};
         cudaError_t e = cudaMemcpy(&s, gemm_status, sizeof s, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return cuda_fail(e, "status read");
+#ifdef B2_DEBUG
         if (getenv("B2_GEMM_DEBUG") && (atoi(getenv("B2_GEMM_DEBUG")) & 32768)) fprintf(stderr, "[gemm debug] mma loop cycles %u over %u stages; stamps: loop start %u, loop end %u, acc seen %u, epilogue done %u, all done %u; mma thread waited %u on activations, %u on weights\n", s.where, s.iter, s.t[0], s.t[1], s.t[2], s.t[3], s.t[4], s.t[5], s.t[6]);
+#endif
         if (s.code) {
             cudaMemset(gemm_status, 0, sizeof s);
             return fail(B2_ERR_TIMEOUT, "[b200qmm: gemm: a device wait gave up (wait %u, cta %u, k-stage %u)]", s.where, s.cta, s.iter);
@@ -491,7 +547,6 @@ class Backend {
     int matmul(const float* x, size_t t, size_t n_in, b2_job* jobs, size_t n_jobs) {
         if (t == 0 || n_jobs == 0) return B2_OK;
         if (!x || !jobs) return fail(B2_ERR_ARG, "[b200qmm: matmul: null argument]");
-        size_t max_out = 0;
         for (size_t j = 0; j < n_jobs; j++) {
             Weight* w = find(jobs[j].w);
             if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul: unknown weight in job %zu]", j);
@@ -499,29 +554,40 @@ class Backend {
                 return fail(B2_ERR_ARG, "[b200qmm: matmul: job %zu does not match its weight's shape]", j);
             bool small = t <= 8 && gemv_supports(w->dev);
             if (!small && !gemm_tc_supports(w->dev, t) && !rows_path(w->dev)) return fail(B2_DECLINED, "[b200qmm: matmul: job %zu has no kernel at t = %zu]", j, t);
-            max_out = std::max(max_out, jobs[j].n_out);
         }
         auto t0 = clk::now();
+        // every job's result is staged on the device and all jobs run before any result goes back: a job that fails leaves
+        // every y untouched ("nothing written unless 0")
+        std::vector<size_t> y_off(n_jobs);
+        size_t y_total = 0;
+        for (size_t j = 0; j < n_jobs; j++) {
+            y_off[j] = y_total;
+            y_total += (t * jobs[j].n_out * 4 + 255) / 256 * 256;
+        }
         cudaError_t e = x_dev.reserve(t * n_in * 4);
-        if (e == cudaSuccess) e = y_dev.reserve(t * max_out * 4);
+        if (e == cudaSuccess) e = y_dev.reserve(y_total);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
         e = cudaMemcpyAsync(x_dev.p, x, t * n_in * 4, cudaMemcpyHostToDevice, stream);
         if (e != cudaSuccess) return cuda_fail(e, "copy-in");
         ns_in += since(t0);
+        auto t1 = clk::now();
         for (size_t j = 0; j < n_jobs; j++) {
-            auto t1 = clk::now();
-            int rc = matmul_dev(jobs[j].w, x_dev.p, B2_F32, t, y_dev.p, B2_F32);
-            if (rc) return rc;
-            e = cudaStreamSynchronize(stream);
-            if (e != cudaSuccess) return cuda_fail(e, "matmul kernels");
-            if ((rc = check_gemm_status())) return rc;
-            ns_gpu += since(t1);
-            auto t2 = clk::now();
-            e = cudaMemcpyAsync(jobs[j].y, y_dev.p, t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
-            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-            if (e != cudaSuccess) return cuda_fail(e, "copy-out");
-            ns_out += since(t2);
+            int rc = matmul_dev(jobs[j].w, x_dev.p, B2_F32, t, (uint8_t*)y_dev.p + y_off[j], B2_F32);
+            if (rc) {
+                cudaStreamSynchronize(stream);
+                return rc;
+            }
         }
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "matmul kernels");
+        if (int rc = check_gemm_status()) return rc;
+        ns_gpu += since(t1);
+        auto t2 = clk::now();
+        for (size_t j = 0; j < n_jobs && e == cudaSuccess; j++)
+            e = cudaMemcpyAsync(jobs[j].y, (uint8_t*)y_dev.p + y_off[j], t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-out");
+        ns_out += since(t2);
         calls++;
         return B2_OK;
     }
@@ -531,66 +597,75 @@ class Backend {
         if (t == 0 || n_jobs == 0) return B2_OK;
         if (t > 4) return fail(B2_DECLINED, "[b200qmm: matvec_rows: at most 4 rows]");
         if (!x || !jobs) return fail(B2_ERR_ARG, "[b200qmm: matvec_rows: null argument]");
-        size_t max_out = 0;
+        std::vector<size_t> y_off(n_jobs);
+        size_t y_total = 0;
         for (size_t j = 0; j < n_jobs; j++) {
             Weight* w = find(jobs[j].w);
             if (!w || w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
                 return fail(B2_ERR_ARG, "[b200qmm: matvec_rows: job %zu does not match its weight]", j);
             if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec_rows: job %zu has no kernel]", j);
-            max_out = std::max(max_out, jobs[j].n_out);
+            if (jobs[j].up) {
+                Weight* u = find(jobs[j].up);
+                if (!u || u->dev.fmt != w->dev.fmt || u->dev.n_in != w->dev.n_in || u->dev.n_out != w->dev.n_out)
+                    return fail(B2_DECLINED, "[b200qmm: matvec_rows: the pair's matrices differ in shape or format]");
+            }
+            y_off[j] = y_total;
+            y_total += (t * jobs[j].n_out * 4 + 255) / 256 * 256;
         }
         auto t0 = clk::now();
         cudaError_t e = x_dev.reserve(t * n_in * 4);
-        if (e == cudaSuccess) e = y_dev.reserve(t * max_out * 4);
+        if (e == cudaSuccess) e = y_dev.reserve(y_total);  // all jobs run before any result goes back to the host
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
         e = cudaMemcpyAsync(x_dev.p, x, t * n_in * 4, cudaMemcpyHostToDevice, stream);
         if (e != cudaSuccess) return cuda_fail(e, "copy-in");
         ns_in += since(t0);
+        auto t1 = clk::now();
+        // The planes of this call's rows are computed at most once, by the first job that reads them; a job that takes the
+        // row-by-row route writes one vector's planes into the same scratch, after which they must be computed again.
+        bool planes_ready = false;
+        const size_t stride = (xplanes_bytes(n_in) + 255) / 256 * 256;
         for (size_t j = 0; j < n_jobs; j++) {
-            auto t1 = clk::now();
-            // two to four rows: one launch that reads the weights once (each row's result is the one-row result bit for bit);
-            // falls back to a launch per row when the rows' vectors do not fit in shared memory together
-            bool done = false;
-            // (FP8 rows go one by one: their single-row kernel is the tensor-core one, and the rows must match it bit for bit)
-            if (t > 1 && find(jobs[j].w)->dev.fmt != B2_FMT_F8E4M3) {
-                Weight* w = find(jobs[j].w);
-                Weight* u = jobs[j].up ? find(jobs[j].up) : nullptr;
-                if (jobs[j].up && (!u || u->dev.fmt != w->dev.fmt || u->dev.n_in != w->dev.n_in || u->dev.n_out != w->dev.n_out))
-                    return fail(B2_DECLINED, "[b200qmm: matvec_rows: the pair's matrices differ in shape or format]");
-                const bool f8 = w->dev.fmt == B2_FMT_F8E4M3;
-                const size_t stride = (xplanes_bytes(n_in) + 255) / 256 * 256;
-                XPlanes xp0{};
-                e = cudaSuccess;
-                if (!f8) {
+            Weight* w = find(jobs[j].w);
+            Weight* u = jobs[j].up ? find(jobs[j].up) : nullptr;
+            float* yj = (float*)((uint8_t*)y_dev.p + y_off[j]);
+            const int mode = jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE;
+            // Two to four rows: one launch that reads the weights once (each row's result is the one-row result bit for bit),
+            // when the rows' vectors fit in shared memory together. FP8 rows go one by one: their single-row kernel is the
+            // tensor-core one, and the rows must match it bit for bit.
+            if (t > 1 && w->dev.fmt != B2_FMT_F8E4M3 && gemv_multi_fits(w->dev, (int)t)) {
+                if (!planes_ready) {
                     e = xplanes.reserve(t * stride);
                     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
-                    if (j == 0 || prepared_k != 0) {
-                        e = launch_xplanes_rows((const float*)x_dev.p, t, n_in, (uint8_t*)xplanes.p, stride, stream);
-                        launches++;
-                        prepared_k = 0;  // the scratch now holds several rows' planes, not one prepared vector
-                    }
-                    xp0 = xplanes_at(xplanes.p, n_in);
-                }
-                if (e == cudaSuccess)
-                    e = launch_gemv_multi(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, xp0, stride, (float*)y_dev.p, jobs[j].n_out, (int)t,
-                                          jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE, sm_count, stream);
-                if (e == cudaSuccess) {
+                    e = launch_xplanes_rows((const float*)x_dev.p, t, n_in, (uint8_t*)xplanes.p, stride, stream);
                     launches++;
-                    done = true;
-                } else if (e != cudaErrorInvalidValue) {
-                    return cuda_fail(e, "gemv (several rows)");
+                    if (e != cudaSuccess) return cuda_fail(e, "xplanes (rows)");
+                    prepared_k = 0;  // the scratch now holds several rows' planes, not one prepared vector
+                    planes_ready = true;
+                }
+                e = launch_gemv_multi(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, xplanes_at(xplanes.p, n_in), stride, yj, jobs[j].n_out,
+                                      (int)t, mode, sm_count, stream);
+                launches++;
+                if (e != cudaSuccess) return cuda_fail(e, "gemv (several rows)");
+                continue;
+            }
+            for (size_t i = 0; i < t; i++) {
+                if (w->dev.fmt != B2_FMT_F8E4M3) planes_ready = false;  // matvec_dev overwrites the planes scratch
+                int rc = matvec_dev(jobs[j].w, jobs[j].up, (const float*)x_dev.p + i * n_in, yj + i * jobs[j].n_out, mode, nullptr);
+                if (rc) {
+                    cudaStreamSynchronize(stream);
+                    return rc;
                 }
             }
-            for (size_t i = 0; i < t && !done; i++) {
-                int rc = matvec_dev(jobs[j].w, jobs[j].up, (const float*)x_dev.p + i * n_in, (float*)y_dev.p + i * jobs[j].n_out,
-                                    jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE, nullptr);
-                if (rc) return rc;
-            }
-            e = cudaMemcpyAsync(jobs[j].y, y_dev.p, t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
-            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-            if (e != cudaSuccess) return cuda_fail(e, "matvec_rows");
-            ns_gpu += since(t1);
         }
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "matvec_rows kernels");
+        ns_gpu += since(t1);
+        auto t2 = clk::now();
+        for (size_t j = 0; j < n_jobs && e == cudaSuccess; j++)
+            e = cudaMemcpyAsync(jobs[j].y, (uint8_t*)y_dev.p + y_off[j], t * jobs[j].n_out * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "copy-out");
+        ns_out += since(t2);
         calls++;
         return B2_OK;
     }
@@ -649,7 +724,7 @@ class Backend {
 
     // One grouped GEMM: rows of xg (f16, segments of whole 128-row tiles per expert) times the stacked matrices.
     int grouped_gemm(int fmt, const void* stacked, size_t experts, size_t n_out, size_t n_in, const void* xg, size_t rows, const int* tile_expert,
-                     float* out_dev, int m_halves = 1) {
+                     float* out_dev, int m_halves, const float* row_unscale, size_t a_lo_row0) {
         WeightDev w{};
         w.fmt = fmt;
         w.n_out = n_out;
@@ -657,9 +732,9 @@ class Backend {
         w.p0 = (const uint8_t*)stacked;
         GemmPlan* plan = nullptr;
         char msg[256] = {0};
-        cudaError_t e = gemm_tc_plan_create(w, xg, rows, out_dev, B2_F32, &plan, msg, sizeof msg, experts, tile_expert, m_halves);
+        cudaError_t e = gemm_tc_plan_create(w, xg, rows, out_dev, B2_F32, &plan, msg, sizeof msg, experts, tile_expert, m_halves, a_lo_row0, a_lo_row0 ? 2 : 1);
         if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
-        e = launch_gemm_tc(plan, w, rows, out_dev, B2_F32, gemm_status, sm_count, stream);
+        e = launch_gemm_tc(plan, w, rows, out_dev, B2_F32, gemm_status, sm_count, stream, row_unscale);
         launches++;
         gemm_tc_plan_destroy(plan);  // the tensor maps were copied into the launch's parameters
         if (e != cudaSuccess) return cuda_fail(e, "grouped gemm");
@@ -722,6 +797,12 @@ class Backend {
         return B2_OK;
     }
 
+    static size_t rows_for(const std::vector<size_t>& count, size_t tile) {
+        size_t rows = 0;
+        for (size_t c : count) rows += (c + tile - 1) / tile * tile;
+        return rows;
+    }
+
     int moe_dev(uint64_t handle, const float* x_dev_, size_t t, const int32_t* ids, const float* rw, size_t k, float* y_dev_) {
         auto it = moes.find(handle);
         if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe: unknown handle]");
@@ -748,11 +829,17 @@ class Backend {
             const char* e = getenv("B2_MOE_TILE");
             return e ? atoi(e) : 0;
         }();
-        const size_t TILE = force_tile == 128 || force_tile == 256 ? (size_t)force_tile : (tiles256 * 10 <= tiles128 * 8 ? 256 : 128);
+        // Q4_K experts always take the 128-row tile: with it the activations of both projections go in as two f16 terms (22
+        // bits), which the 256-row tile has no room for, and Q4_K values round harder to f16 than MLX-4's: the two roundings
+        // together leave the layer above 1e-3 per output row.
+        const size_t TILE = force_tile == 128 || force_tile == 256 ? (size_t)force_tile
+                            : (m.fmt != B2_FMT_Q4_K && tiles256 * 10 <= tiles128 * 8) ? 256 : 128;
         const int m_halves = (int)(TILE / 128);
+        const size_t lo_row0 = TILE == 128 ? rows_for(count, 128) : 0;  // two-term activations with the 128-row tile
         std::vector<size_t> off(m.experts, 0);
         std::vector<int32_t> tile_expert;
         size_t rows = 0;
+        const size_t terms = lo_row0 ? 2 : 1;
         for (size_t e = 0; e < m.experts; e++) {
             off[e] = rows;
             size_t tiles = (count[e] + TILE - 1) / TILE;
@@ -771,9 +858,9 @@ class Backend {
         // index block on the device: src | slots | tile_expert | route weights
         const size_t n_idx = rows + t * k + tile_expert.size();
         cudaError_t e = moe_idx.reserve(n_idx * 4 + t * k * 4);
-        if (e == cudaSuccess) e = moe_xg.reserve(rows * m.h * 2);
+        if (e == cudaSuccess) e = moe_xg.reserve(terms * rows * m.h * 2 + rows * 4);
         if (e == cudaSuccess) e = moe_g.reserve(rows * 2 * m.inter * 4);
-        if (e == cudaSuccess) e = moe_a.reserve(rows * m.inter * 2 + rows * 4);
+        if (e == cudaSuccess) e = moe_a.reserve(terms * rows * m.inter * 2 + rows * 4);
         if (e == cudaSuccess) e = moe_o.reserve(rows * m.h * 4);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(moe scratch)");
         int32_t* d_src = (int32_t*)moe_idx.p;
@@ -788,16 +875,17 @@ class Backend {
         if (e == cudaSuccess) e = cudaMemcpyAsync(d_w, rw, t * k * 4, cudaMemcpyHostToDevice, stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(stream);  // the host vectors go out of scope
         if (e != cudaSuccess) return cuda_fail(e, "moe index upload");
-        e = launch_moe_gather(x_dev_, d_src, rows, m.h, moe_xg.p, stream);
+        float* x_unscale = (float*)((uint8_t*)moe_xg.p + terms * rows * m.h * 2);
+        float* a_unscale = (float*)((uint8_t*)moe_a.p + terms * rows * m.inter * 2);
+        e = launch_moe_gather(x_dev_, d_src, rows, m.h, moe_xg.p, x_unscale, lo_row0, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_gather");
-        if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p, m_halves))) return rc;
-        float* d_scale = (float*)((uint8_t*)moe_a.p + rows * m.inter * 2);  // one power-of-two scale per row
-        e = launch_moe_act((const float*)moe_g.p, d_src, rows, m.inter, moe_a.p, d_scale, stream);
+        if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p, m_halves, x_unscale, lo_row0))) return rc;
+        e = launch_moe_act((const float*)moe_g.p, d_src, rows, m.inter, moe_a.p, a_unscale, lo_row0, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_act");
-        if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p, m_halves))) return rc;
-        e = launch_moe_combine((const float*)moe_o.p, d_scale, d_slots, d_w, t, k, m.h, y_dev_, stream);
+        if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p, m_halves, a_unscale, lo_row0))) return rc;
+        e = launch_moe_combine((const float*)moe_o.p, d_slots, d_w, t, k, m.h, y_dev_, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_combine");
         return B2_OK;
@@ -1025,6 +1113,12 @@ B2_EXPORT int b2_set_chained(b2_ctx* ctx, int on) {
     return B2_OK;
 }
 
+B2_EXPORT int b2_set_exact(b2_ctx* ctx, int on) {
+    LOCKED(ctx);
+    ctx->be.exact = on != 0;
+    return B2_OK;
+}
+
 B2_EXPORT int b2_set_stream(b2_ctx* ctx, void* s) {
     LOCKED(ctx);
     ctx->be.stream = (cudaStream_t)s;
@@ -1045,6 +1139,12 @@ B2_EXPORT int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* sca
                              size_t group, b2_weight* out) {
     LOCKED(ctx);
     return ctx->be.upload_mlx4(w, scales, biases, n_out, n_in, group, out);
+}
+
+B2_EXPORT int b2_upload_q4(b2_ctx* ctx, const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in,
+                           b2_weight* out) {
+    LOCKED(ctx);
+    return ctx->be.upload_q4(q, scales, offsets, group, n_out, n_in, out);
 }
 
 B2_EXPORT int b2_upload_gguf(b2_ctx* ctx, int fmt, const uint8_t* data, size_t n_out, size_t n_in, const float* block_scales,

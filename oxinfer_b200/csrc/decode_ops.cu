@@ -335,12 +335,7 @@ template <int HD, int G, typename T>
 static cudaError_t attend_t(const float* q, void* kc, void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,
                             const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr) {
     constexpr size_t smem = attend_smem<HD, G, T>();
-    static bool set = false;  // per instantiation; the attribute is per function and device-wide values are equal
-    if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(attend_kernel<HD, G, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        set = true;
-    }
+    if (cudaError_t e = ensure_dynamic_smem((const void*)attend_kernel<HD, G, T>, smem, 0); e != cudaSuccess) return e;
     uint32_t splits = (p.max_len + ATT_TILE - 1) / ATT_TILE;
     if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
     if (splits == 0) splits = 1;

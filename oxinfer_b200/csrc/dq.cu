@@ -51,15 +51,41 @@ __global__ void repack_mlx4_kernel(const uint32_t* __restrict__ w, const uint16_
     size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // block b = 256 consecutive weights of the row-major matrix
     if (b >= nblocks) return;
     uint8_t* o = out + b * 144;
-    for (int g = 0; g < 4; g++) {
-        ((uint16_t*)o)[g] = scales[b * 4 + g];
-        ((uint16_t*)o)[4 + g] = biases[b * 4 + g];
+    for (int g = 0; g < 4; g++) {  // from_mlx_q4 (src/quant.rs:518-563): d = f16(scale), offset = bf16(bias + 8 scale)
+        const float s = bf16_bits_to_f32(scales[b * 4 + g]), bias = bf16_bits_to_f32(biases[b * 4 + g]);
+        ((uint16_t*)o)[g] = __half_as_ushort(__float2half_rn(s));
+        ((uint16_t*)o)[4 + g] = (uint16_t)f32_to_bf16_bits(__fadd_rn(bias, __fmul_rn(8.0f, s)));
     }
     const uint32_t* words = w + b * 32;
     for (int j = 0; j < 4; j++)
         for (int l = 0; l < 32; l++) {
             int e0 = 64 * j + l, e1 = e0 + 32;
             uint32_t n0 = (words[e0 / 8] >> (4 * (e0 % 8))) & 15, n1 = (words[e1 / 8] >> (4 * (e1 % 8))) & 15;
+            o[16 + 32 * j + l] = (uint8_t)(n0 | (n1 << 4));
+        }
+}
+
+// The reference's Q4Matrix with offsets (src/quant.rs:427-440: q in Q4_0 order, byte j of a 32-block = element j low,
+// element j + 16 high; one f16 scale per 32-block; one bf16 offset per group) -> the same blocks. The device block has one
+// scale per 64-group: *mismatch is set when the two 32-blocks of a group differ in scale (a matrix from_mlx_q4 did not make).
+__global__ void repack_q4a_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales, const uint16_t* __restrict__ offsets,
+                                  size_t nblocks, size_t blocks_per_row, size_t group, uint8_t* __restrict__ out, int* __restrict__ mismatch) {
+    size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    uint8_t* o = out + b * 144;
+    const size_t row = b / blocks_per_row, k0 = (b % blocks_per_row) * 256, gpr = blocks_per_row * 256 / group;
+    for (int g = 0; g < 4; g++) {
+        const uint16_t d0 = scales[b * 8 + 2 * g], d1 = scales[b * 8 + 2 * g + 1];
+        if (d0 != d1) *mismatch = 1;
+        ((uint16_t*)o)[g] = d0;
+        ((uint16_t*)o)[4 + g] = offsets[row * gpr + (k0 + 64 * g) / group];
+    }
+    const uint8_t* src = q + b * 128;  // eight 32-blocks of 16 bytes
+    for (int j = 0; j < 4; j++)
+        for (int l = 0; l < 32; l++) {
+            const uint8_t* b0 = src + (2 * j) * 16;      // elements 64 j .. 64 j + 31
+            const uint8_t* b1 = src + (2 * j + 1) * 16;  // elements 64 j + 32 .. 64 j + 63
+            const uint32_t n0 = l < 16 ? (b0[l] & 15u) : (b0[l - 16] >> 4), n1 = l < 16 ? (b1[l] & 15u) : (b1[l - 16] >> 4);
             o[16 + 32 * j + l] = (uint8_t)(n0 | (n1 << 4));
         }
 }
@@ -100,6 +126,13 @@ cudaError_t launch_repack_mlx4(const uint32_t* w, const uint16_t* scales, const 
                                cudaStream_t st) {
     size_t nb = n_out * (n_in / 256);
     repack_mlx4_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(w, scales, biases, nb, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repack_q4a(const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t n_out, size_t n_in, size_t group,
+                              uint8_t* out, int* mismatch, cudaStream_t st) {
+    size_t nb = n_out * (n_in / 256);
+    repack_q4a_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(q, scales, offsets, nb, n_in / 256, group, out, mismatch);
     return cudaGetLastError();
 }
 

@@ -13,13 +13,12 @@ __device__ __forceinline__ void dequant8(const WeightDev& w, size_t r, size_t e0
     if constexpr (FMT == B2_FMT_MLX4) {
         // dequantize_rows_q4 over from_mlx_q4's repack (src/quant.rs:518-563, 586-606):
         // d = f16(scale), offset = bf16(bias + 8 scale), value = (nib - 8) * d + offset.
-        // Device blocks (repack_mlx4_kernel): 4 bf16 scales, 4 bf16 biases, 128 nibble bytes in Q4_K order.
+        // Device blocks (repack_mlx4_kernel / repack_q4a_kernel): the four f16 d and the four bf16 offsets of the block's
+        // 64-groups (the fields of the reference's Q4Matrix), then 128 nibble bytes in Q4_K order.
         const uint8_t* blk = w.p0 + (r * (K / 256) + e0 / 256) * 144;
         int e = (int)(e0 % 256), j = e / 64, h = (e % 64) / 32, l = e % 32;
-        float s = bf16_bits_to_f32(((const uint16_t*)blk)[j]);
-        float b = bf16_bits_to_f32(((const uint16_t*)blk)[4 + j]);
-        float d = __half2float(__float2half_rn(s));
-        float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(b, __fmul_rn(8.0f, s))));
+        float d = f16_bits_to_f32(((const uint16_t*)blk)[j]);
+        float off = bf16_bits_to_f32(((const uint16_t*)blk)[4 + j]);
         const uint8_t* q = blk + 16 + 32 * j + l;
 #pragma unroll
         for (int k = 0; k < 8; k++) v[k] = __fadd_rn(__fmul_rn((float)((int)((q[k] >> (4 * h)) & 0xF) - 8), d), off);

@@ -1,8 +1,9 @@
 // Device-side layouts of the weight formats and the scalar decoders shared by every kernel.
 //
 // Device layouts (all 16-byte aligned per row for n_in a multiple of 256):
-//   MLX4   : repacked at upload into Q4_K-shaped blocks of 256 weights, 144 bytes: 4 bf16 scales @0,
-//            4 bf16 biases @8 (one per 64-group), qs[128] @16 with Q4_K's nibble order (byte l of
+//   MLX4   : repacked at upload into Q4_K-shaped blocks of 256 weights, 144 bytes: 4 f16 d @0, 4 bf16 offsets @8
+//            (one per 64-group; d = f16(scale), offset = bf16(bias + 8 scale), the fields of the reference's
+//            Q4Matrix, src/quant.rs:427-440,518-563), qs[128] @16 with Q4_K's nibble order (byte l of
 //            64-group j = element 64j+l low, 64j+32+l high), so that every 4-bit kernel is shared
 //   Q4_K   : raw GGUF super-blocks, 144 bytes per 256 weights: d f16 @0, dmin f16 @2,
 //            scales[12] @4, qs[128] @16                       (unchanged)

@@ -166,12 +166,24 @@ template <int FMT, bool SPLIT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
-                   int tile_n, int m_halves, void* __restrict__ y, int y_dtype, GemmStatus* __restrict__ status, int dbg,
-                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits) {
+                   int tile_n, int m_halves, void* __restrict__ y, int y_dtype_arg, GemmStatus* __restrict__ status, int dbg_arg,
+                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits, const float* __restrict__ row_unscale, int a_lo_row0, int w_terms) {
+    // The timing switches (see debug_switches below) exist only in builds made with -DB2_DEBUG: a production library
+    // must not change its results because of an environment variable.
+#ifdef B2_DEBUG
+    const int dbg = dbg_arg;
+#else
+    constexpr int dbg = 0;
+    (void)dbg_arg;
+#endif
     // A "raw block" is what one weight copy brings per row: a 144-byte 4-bit block (256 k, four pipeline
     // stages) or 128 e4m3 bytes (128 k = one column of FP8 scale blocks, two stages).
     constexpr int RAW_ROW = FMT == B2_FMT_F8E4M3 ? 128 : 144;
     constexpr int RAW_ST = FMT == B2_FMT_F8E4M3 ? 2 : 4;
+    // bit 8 of the output type: f32 rows that are not 16-byte multiples (n_out % 4 != 0) cannot be described to the copy
+    // engine; the epilogue then stores them directly
+    const int y_dtype = y_dtype_arg & 0xff;
+    const bool y_direct = (y_dtype_arg & 0x100) != 0;
     const long long dbg_k0 = clock64();
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
     extern __shared__ uint8_t smem_raw[];
@@ -192,7 +204,13 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
     // belongs to one expert
     const int w_row0 = tile_expert ? tile_expert[blockIdx.y] * n_out : 0;
-    const int set_warps = (tile_n + 31) / 32;  // live warps in each of the two dequantizer sets
+    // w_terms == 2 (Q4_K, tile_n <= 112): every weight goes into the B operand as two f16 terms, hi in rows 0 .. tile_n - 1 of
+    // the stage and lo (what the rounding of hi left of the exact f32 value) in rows 128 .. 128 + tile_n - 1; both are
+    // multiplied by the activations into the same accumulator. In each dequantizer set warps 0..3 then write the hi terms of
+    // rows 0..127 and warps 4..7 the lo terms of the same rows.
+    const bool w2 = w_terms == 2;
+    const int row_warps = (tile_n + 31) / 32;
+    const int set_warps = w2 ? 2 * row_warps : row_warps;  // live warps in each of the two dequantizer sets
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -220,7 +238,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         // ---------------- TMA producers: warp 0 streams the activations, warp 18 the packed weights ----------------
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
-            const uint32_t a_bytes = (uint32_t)(128 * m_halves * 128);
+            // a_lo_row0 > 0 (128-token tiles only): the activations come as two f16 terms, x = hi + lo, with the lo rows stored
+            // a_lo_row0 rows below the hi rows; both halves of the stage are filled and both feed the same accumulator, so the
+            // activations enter the product with 22 significant bits instead of 11.
+            const uint32_t a_bytes = (uint32_t)(128 * (a_lo_row0 > 0 ? 2 : m_halves) * 128);
             int a_issued = 0;
             for (int ks = 0; ks < nks; ks++) {
                 const int s = ks % STAGES;
@@ -231,6 +252,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 } else {
                     mbar_arrive_expect_tx(&sh->a_full[s], a_bytes);
                     tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], (sb0 * RAW_ST + ks) * STAGE_K, m0);
+                    if (a_lo_row0 > 0)
+                        tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES + 128 * 128, &tmap_x, &sh->a_full[s], (sb0 * RAW_ST + ks) * STAGE_K, a_lo_row0 + m0);
                     a_issued = ks + 1;
                 }
             }
@@ -285,6 +308,11 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     if (!(dbg & 4)) {
                         mma_f16(tmem_base, adesc0 + 2 * kk, bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
                         if (m_halves == 2) mma_f16(tmem_base + 256u, adesc0 + 2 * kk + ((128 * 128) >> 4), bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                        if (a_lo_row0 > 0) mma_f16(tmem_base, adesc0 + 2 * kk + ((128 * 128) >> 4), bdesc0 + 2 * kk, idesc, 1u);
+                        if (w2) {  // the weights' lo terms against the activations' hi terms (lo x lo is below f32's own rounding)
+                            mma_f16(tmem_base, adesc0 + 2 * kk, bdesc0 + 2 * kk + ((128 * 128) >> 4), idesc, 1u);
+                            if (m_halves == 2) mma_f16(tmem_base + 256u, adesc0 + 2 * kk + ((128 * 128) >> 4), bdesc0 + 2 * kk + ((128 * 128) >> 4), idesc, 1u);
+                        }
                     }
                 }
                 mma_commit(&sh->empty[s]);
@@ -301,11 +329,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const int dq_warp = warp - 2;
         const int dt = threadIdx.x - 64;
         const int set = dt >> 8;
-        const int r = dt & 255;  // weight row of the tile
+        const int r = w2 ? (dt & 127) : (dt & 255);  // weight row of the tile
+        const bool is_lo = w2 && (dt & 128);
         bool ok = true;
-        if ((dq_warp & 7) < set_warps) {
+        if ((w2 ? (dq_warp & 3) : (dq_warp & 7)) < row_warps) {
             const bool in_tile = r < tile_n;
-            const uint32_t row_off = (uint32_t)r * 128u;
+            const uint32_t row_off = (uint32_t)(r + (is_lo ? 128 : 0)) * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
             const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * RAW_ROW);
             for (int sb = 0; sb < nsb && ok; sb++) {
@@ -381,9 +410,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     __half2 dmul, c1lo, c2lo, c1hi, c2hi, addlo, addhi;
                     if constexpr (FMT == B2_FMT_MLX4) {
                         const uint32_t sw = (j & 2) ? hdr.y : hdr.x, bw = (j & 2) ? hdr.w : hdr.z;
-                        const float sc = bf16_bits_to_f32((sw >> (16 * (j & 1))) & 0xffffu), bb = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
-                        const float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, sc))));
-                        dmul = __float2half2_rn(sc);
+                        const float off = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
+                        dmul = __half2half2(__ushort_as_half((unsigned short)((sw >> (16 * (j & 1))) & 0xffffu)));
                         c1lo = __float2half2_rn(1.0f);
                         c2lo = __float2half2_rn(-1032.0f);
                         c1hi = __float2half2_rn(0.0625f);
@@ -416,6 +444,34 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         hi[2 * i] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h0), c1hi, c2hi), dmul, addhi));
                         hi[2 * i + 1] = h2_bits(__hfma2(__hfma2(*reinterpret_cast<__half2*>(&h1), c1hi, c2hi), dmul, addhi));
                     }
+                    if constexpr (FMT == B2_FMT_Q4_K) {
+                        if (is_lo) {
+                            // the second term: the exact f32 weight of the reference's decode, d1 * q - m1 with both roundings
+                            // (src/ggml.rs:750-773), minus the f16 the hi warps wrote (the same arithmetic as above)
+                            uint32_t sc0, mn0, sc1, mn1;
+                            q4k_scale_min(2 * j, hdr.y, hdr.z, hdr.w, sc0, mn0);
+                            q4k_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, sc1, mn1);
+                            const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
+                            const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                            const float d1l = __fmul_rn(d, (float)sc0), m1l = __fmul_rn(dmin, (float)mn0);
+                            const float d1h = __fmul_rn(d, (float)sc1), m1h = __fmul_rn(dmin, (float)mn1);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {  // bytes 4i + 2e, 4i + 2e + 1 of the group
+                                    const uint32_t b0 = (qw[i] >> (16 * e)) & 0xffu, b1 = (qw[i] >> (16 * e + 8)) & 0xffu;
+                                    const float2 hl = __half22float2(*reinterpret_cast<const __half2*>(&lo[2 * i + e]));
+                                    const float2 hh = __half22float2(*reinterpret_cast<const __half2*>(&hi[2 * i + e]));
+                                    const float vl0 = __fsub_rn(__fmul_rn(d1l, __uint_as_float(0x4B000000u | (b0 & 15u)) - 8388608.0f), m1l);
+                                    const float vl1 = __fsub_rn(__fmul_rn(d1l, __uint_as_float(0x4B000000u | (b1 & 15u)) - 8388608.0f), m1l);
+                                    const float vh0 = __fsub_rn(__fmul_rn(d1h, __uint_as_float(0x4B000000u | (b0 >> 4)) - 8388608.0f), m1h);
+                                    const float vh1 = __fsub_rn(__fmul_rn(d1h, __uint_as_float(0x4B000000u | (b1 >> 4)) - 8388608.0f), m1h);
+                                    lo[2 * i + e] = h2_bits(__floats2half2_rn(vl0 - hl.x, vl1 - hl.y));
+                                    hi[2 * i + e] = h2_bits(__floats2half2_rn(vh0 - hh.x, vh1 - hh.y));
+                                }
+                            }
+                        }
+                    }
                     if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
                         break;
@@ -445,12 +501,15 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             if (dbg_cta && threadIdx.x == 64) status->t[2] = (uint32_t)(clock64() - dbg_k0);
             if (acc_ok) {
                 tc_fence_after();
-                const float out_scale = FMT == B2_FMT_F8E4M3 ? 1.0f / f8.pre : 1.0f;
                 const int token0 = m0 + half * 128 + quarter * 32;
                 const int token = token0 + lane;
+                // the activations of a token row may have been scaled by a power of two on their way to f16 (to_f16_rows):
+                // its results are scaled back here, exactly
+                const bool scaled = FMT == B2_FMT_F8E4M3 || row_unscale != nullptr;
+                const float out_scale = (FMT == B2_FMT_F8E4M3 ? 1.0f / f8.pre : 1.0f) * ((row_unscale && token < t) ? __ldg(row_unscale + token) : 1.0f);
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
                 int c0 = cpar * 32;
-                if (y_dtype == B2_F32 && !(dbg & 64)) {
+                if (y_dtype == B2_F32 && !y_direct && !(dbg & 64)) {
                     // f32 output through shared memory and TMA stores: each warp owns two 4 KB staging tiles
                     // (32 tokens x 32 columns, 128-byte swizzle) in the now idle pipeline buffers, fills one
                     // from TMEM, and lets the copy engine write it out while it fills the other. The tensor
@@ -466,7 +525,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         uint32_t v[16], u[16];
                         tmem_ld16(taddr0 + (uint32_t)c0, v);
                         tmem_ld16(taddr0 + (uint32_t)c0 + 16u, u);
-                        if (FMT == B2_FMT_F8E4M3) {
+                        if (scaled) {
 #pragma unroll
                             for (int i = 0; i < 16; i++) {
                                 v[i] = __float_as_uint(__uint_as_float(v[i]) * out_scale);
@@ -497,12 +556,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     // a 16-column tail (tile_n not a multiple of 32) goes to the warps whose turn it would be
                     c0 = ((tile_n & 31) && ((tile_n >> 5) & 1) == cpar) ? (tile_n & ~31) : tile_n;
                 }
-                const int step = (y_dtype == B2_F32 && !(dbg & 64)) ? tile_n : 64;
+                const int step = (y_dtype == B2_F32 && !y_direct && !(dbg & 64)) ? tile_n : 64;
                 for (; c0 < tile_n; c0 += step) {
                   for (int cc = c0; cc < min(c0 + 32, tile_n); cc += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr0 + (uint32_t)cc, v);
-                    if (FMT == B2_FMT_F8E4M3) {
+                    if (scaled) {
 #pragma unroll
                         for (int i = 0; i < 16; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * out_scale);
                     }
@@ -561,21 +620,49 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     }
 }
 
+// One token row to f16 operands, scaled by a power of two so that its largest magnitude lands in [2^14, 2^15): rows
+// of any magnitude (the reference's own tests use rows scaled by 1e-3 .. 2e5, src/cuda.rs:1579-1700) neither overflow
+// f16 nor sink into its subnormals, and since the factor is a power of two the rounding is the same relative rounding
+// at every magnitude. unscale[row] = 1 / factor is what the GEMM's epilogue multiplies the row's results by (exact).
+// lo_off > 0: the remainder x * factor - f16(x * factor) is written lo_off elements behind each value (two-term activations).
+// One CTA per row; NaN elements stay NaN, a row with an infinity is passed through unscaled.
+__device__ __forceinline__ float load_as_float(const float* p) { return *p; }
+__device__ __forceinline__ float load_as_float(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float load_as_float(const __half* p) { return __half2float(*p); }
+
 template <typename T>
-__global__ void to_f16_kernel(const T* __restrict__ x, size_t n, __half* __restrict__ out) {
-    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i + 4 <= n) {
-        float f[4];
+__global__ void __launch_bounds__(256) to_f16_rows_kernel(const T* __restrict__ x, int K, __half* __restrict__ out, float* __restrict__ unscale,
+                                                          size_t lo_off) {
+    __shared__ float red[8];
+    const T* xr = x + (size_t)blockIdx.x * K;
+    __half* o = out + (size_t)blockIdx.x * K;
+    float mx = 0.0f;
+    for (int i = threadIdx.x; i < K; i += 256) mx = fmaxf(mx, fabsf(load_as_float(xr + i)));
 #pragma unroll
-        for (int k = 0; k < 4; k++) f[k] = (float)x[i + k];
-        __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
-        uint2 o;
-        o.x = *reinterpret_cast<uint32_t*>(&a);
-        o.y = *reinterpret_cast<uint32_t*>(&b);
-        *(uint2*)(out + i) = o;
-    } else {
-        for (; i < n; i++) out[i] = __float2half_rn((float)x[i]);
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    float s = 1.0f, inv = 1.0f;
+    if (mx > 0.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);                       // mx = m 2^e, m in [0.5, 1)
+        const int up = min(100, max(-100, 15 - e));
+        s = ldexpf(1.0f, up);
+        inv = ldexpf(1.0f, -up);
     }
+    for (int i = threadIdx.x * 2; i < K; i += 512) {  // K is even (a multiple of 64)
+        const float a = load_as_float(xr + i) * s, b = load_as_float(xr + i + 1) * s;
+        const __half2 h = __floats2half2_rn(a, b);
+        *(__half2*)(o + i) = h;
+        if (lo_off) {  // the second term: what the rounding to f16 left over (exact in f32, rounded once more)
+            const float2 hf = __half22float2(h);
+            *(__half2*)(o + lo_off + i) = __floats2half2_rn(a - hf.x, b - hf.y);
+        }
+    }
+    if (threadIdx.x == 0) unscale[blockIdx.x] = inv;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -593,13 +680,18 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// B2_GEMM_DEBUG: diagnostic switches for timing experiments (the results are WRONG when any of the
-// first five is set): 1 skip the dequantizers' shared-memory stores, 2 skip the weight copies, 4 skip
-// the MMAs, 8 skip the epilogue's stores, 16 skip the activation copies; 64 epilogue by direct stores
-// instead of TMA stores; 32768 make CTA (1, 0) write cycle stamps of its phases into the status word.
+// Only in builds made with -DB2_DEBUG (make EXTRA=-DB2_DEBUG), B2_GEMM_DEBUG selects diagnostic switches for timing
+// experiments (the results are WRONG when any of the first five is set): 1 skip the dequantizers' shared-memory
+// stores, 2 skip the weight copies, 4 skip the MMAs, 8 skip the epilogue's stores, 16 skip the activation copies;
+// 64 epilogue by direct stores instead of TMA stores; 32768 make CTA (1, 0) write cycle stamps of its phases into the
+// status word. The shipped library ignores the variable.
 int debug_switches() {
+#ifdef B2_DEBUG
     const char* e = getenv("B2_GEMM_DEBUG");
     return e ? atoi(e) : 0;
+#else
+    return 0;
+#endif
 }
 
 }  // namespace
@@ -615,6 +707,9 @@ struct GemmPlan {
     size_t t, K, n_out;
     int tile_n, m_halves, n_tiles, m_tiles;
     int k_splits = 1;
+    bool y_direct = false;  // f32 output whose rows the copy engine cannot take (stride not a multiple of 16 bytes)
+    int w_terms = 1;       // 2: two-term weights (Q4_K, tile_n <= 112)
+    size_t a_lo_row0 = 0;  // two-term activations: the lo rows start this many rows below the hi rows (0: one term)
     int split_asked = 1;  // B2_GEMM_SPLIT_K when the plan was made (a cached plan is reused only under the same setting)
 };
 
@@ -633,16 +728,16 @@ static int split_k_asked() {
 // time hardly depends on the width (1108 cycles per stage at 208 rows, 1152 at 104), plus an epilogue that grows with
 // the width; in units of rows the measurements fit (tile_n + 13 per k stage), with widths above 208 costing about five
 // times as much per extra row (58-60 us at 240 against 54 at 208 for 64 stages). So the count of waves decides first.
-static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K) {
+static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K, int widest = MAX_TILE_N) {
     // B2_GEMM_TILE_N forces a width (tests and tuning sweeps).
     if (const char* env = getenv("B2_GEMM_TILE_N")) {
         int v = atoi(env);
-        if (v >= 16 && v <= MAX_TILE_N && v % 16 == 0) return v;
+        if (v >= 16 && v <= widest && v % 16 == 0) return v;
     }
     const double per_cta = 24.0 + 13.0 * (double)(K / 64);
-    int best = MAX_TILE_N;
+    int best = widest;
     double best_cost = 1e30;
-    for (int tn = MAX_TILE_N; tn >= 64; tn -= 16) {
+    for (int tn = widest; tn >= 64; tn -= 16) {
         size_t tiles = (n_out + tn - 1) / tn * (size_t)m_tiles;
         size_t waves = (tiles + sm_count - 1) / sm_count;
         double cost = (double)waves * (tn + per_cta + (tn > 208 ? 4.0 * (tn - 208) : 0.0));
@@ -655,7 +750,7 @@ static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K) {
 }
 
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen, size_t experts, const int* tile_expert, int force_m_halves) {
+                                size_t errlen, size_t experts, const int* tile_expert, int force_m_halves, size_t a_lo_row0, int w_terms) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) {
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
@@ -672,12 +767,20 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     p->experts = experts;
     p->tile_expert = tile_expert;
     p->m_halves = force_m_halves ? force_m_halves : (t > 128 ? 2 : 1);
+    p->a_lo_row0 = a_lo_row0;
+    if (a_lo_row0 && (p->m_halves != 1 || a_lo_row0 % 128 || a_lo_row0 < t)) {
+        snprintf(err, errlen, "two-term activations need 128-token tiles and the lo rows on a 128-row boundary behind the hi rows");
+        delete p;
+        return cudaErrorInvalidValue;
+    }
     int tm = 128 * p->m_halves;
     p->m_tiles = (int)((t + tm - 1) / tm);
     int sm_count = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in);
+    if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;  // the other formats' weights round to f16 far below the bound
+    p->w_terms = w_terms;
+    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? 112 : MAX_TILE_N);
     // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
     // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
     // with its width, so a grid that fills half the SMs or less runs nearly twice as fast as twice as many CTAs of half
@@ -687,7 +790,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         p->split_asked = want;
         const int sb_k = w.fmt == B2_FMT_F8E4M3 ? 128 : 256;
         const size_t nsb_all = w.n_in / sb_k;
-        if (want == 2 && y_dtype == B2_F32 && !tile_expert && nsb_all % 2 == 0 && nsb_all >= 8) {
+        if (want == 2 && y_dtype == B2_F32 && !a_lo_row0 && w_terms == 1 && !tile_expert && nsb_all % 2 == 0 && nsb_all >= 8) {
             const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count, w.n_in / 2);
             const size_t tiles1 = (w.n_out + p->tile_n - 1) / p->tile_n * (size_t)p->m_tiles;
             const size_t tiles2 = (w.n_out + tn2 - 1) / tn2 * (size_t)p->m_tiles * 2;
@@ -700,7 +803,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     }
     p->n_tiles = (int)((w.n_out + p->tile_n - 1) / p->tile_n);
     {
-        cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)t};
+        cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)(a_lo_row0 ? a_lo_row0 + t : t)};
         cuuint64_t strides[1] = {(cuuint64_t)w.n_in * 2};
         cuuint32_t box[2] = {(cuuint32_t)STAGE_K, (cuuint32_t)tm};
         cuuint32_t estr[2] = {1, 1};
@@ -729,7 +832,8 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         }
     }
     p->tmap_y = p->tmap_x;  // placeholder when the epilogue stores directly (bf16 output)
-    if (y_dtype == B2_F32) {
+    p->y_direct = y_dtype == B2_F32 && (w.n_out % 4 != 0 || ((uintptr_t)y & 15) != 0);
+    if (y_dtype == B2_F32 && !p->y_direct) {
         // the f32 output [t][n_out]; one box = a warp's 32 tokens x 32 columns staging tile
         cuuint64_t dims[2] = {(cuuint64_t)w.n_out, (cuuint64_t)t};
         cuuint64_t strides[1] = {(cuuint64_t)w.n_out * 4};
@@ -749,23 +853,21 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
 
 void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
 
-bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype) {
-    return p && p->experts == 1 && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
+bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype, size_t a_lo_row0,
+                          int w_terms, int m_halves) {
+    if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;
+    return p && p->experts == 1 && p->a_lo_row0 == a_lo_row0 && p->w_terms == w_terms && (m_halves == 0 || p->m_halves == m_halves) && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
            p->split_asked == split_k_asked();
 }
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
-                           cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_MLX4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
+                           cudaStream_t st, const float* row_unscale) {
+    {
+        const void* kerns[6] = {(const void*)gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>,   (const void*)gemm_q4k_tc_kernel<B2_FMT_MLX4, false>,
+                                (const void*)gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>, (const void*)gemm_q4k_tc_kernel<B2_FMT_Q4_K, true>,
+                                (const void*)gemm_q4k_tc_kernel<B2_FMT_MLX4, true>,    (const void*)gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true>};
+        for (const void* k : kerns)
+            if (cudaError_t e = ensure_dynamic_smem(k, GEMM_SMEM); e != cudaSuccess) return e;
     }
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles, (unsigned)p->k_splits);
     if (p->k_splits > 1) {  // the shares are added into y
@@ -777,20 +879,20 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
                 : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>)
                                          : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>);
     F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype,
-                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype | (p->y_direct ? 0x100 : 0),
+                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms);
     return cudaGetLastError();
 }
 
-cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t /*t_pad*/, size_t K, void* x16, cudaStream_t st) {
-    size_t n = t * K;
-    unsigned grid = (unsigned)((n / 4 + 256) / 256);
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0) {
+    if (t == 0 || K % 2) return cudaErrorInvalidValue;
+    const size_t lo_off = lo_row0 * K;
     if (x_dtype == B2_F32)
-        to_f16_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, (__half*)x16);
+        to_f16_rows_kernel<float><<<(unsigned)t, 256, 0, st>>>((const float*)x, (int)K, (__half*)x16, unscale, lo_off);
     else if (x_dtype == B2_BF16)
-        to_f16_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, n, (__half*)x16);
+        to_f16_rows_kernel<__nv_bfloat16><<<(unsigned)t, 256, 0, st>>>((const __nv_bfloat16*)x, (int)K, (__half*)x16, unscale, lo_off);
     else if (x_dtype == B2_F16)
-        return cudaMemcpyAsync(x16, x, n * 2, cudaMemcpyDeviceToDevice, st);
+        to_f16_rows_kernel<__half><<<(unsigned)t, 256, 0, st>>>((const __half*)x, (int)K, (__half*)x16, unscale, lo_off);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();

@@ -172,7 +172,7 @@ constexpr size_t RING_BYTES = (size_t)GEMV_WARPS * RING_SLOTS * RING_SLOT_BYTES;
 template <class F, bool PAIR, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 1)
 gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, uint32_t* status,
-                  NormScale ns, EpiPlanes epi, int slots_per_warp, NextWeights next) {
+                  NormScale ns, EpiPlanes epi, int slots_per_warp) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t bars[WARPS * RING_SLOTS_MAX];
     __shared__ uint64_t xbars[RING_X_STEPS];
@@ -199,10 +199,6 @@ gemv4_ring_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         ring_prime<PAIR>(w, w2, ring, r_first, r_step, ni);
     }
-    if (next.p0) {  // behind this kernel's own first copies in the queue
-        acopy::prefetch_slice_l2(next.p0, next.n0, blockIdx.x, gridDim.x, threadIdx.x, THREADS);
-        if (next.p1) acopy::prefetch_slice_l2(next.p1, next.n1, blockIdx.x, gridDim.x, threadIdx.x, THREADS);
-    }
     pdl_wait();
     // the planes of x (written by the kernel ahead) -> shared memory, a set of bulk copies per 2048 k: the rows start once
     // the first set has landed
@@ -226,16 +222,11 @@ static int env_int(const char* name, int dflt) {
 
 template <class F, bool PAIR, int WARPS>
 cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, int slots, NextWeights next) {
+                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, int slots) {
     auto kern = gemv4_ring_kernel<F, PAIR, WARPS>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)WARPS * slots * RING_SLOT_BYTES;
     if (smem + 2048 > 227 * 1024) return cudaErrorInvalidValue;
-    static size_t smem_set = 48 * 1024;  // per instantiation
-    if (smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set = smem;
-    }
+    if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
     const size_t rows_per_cta = epi.out.planes ? 32 : (size_t)WARPS * (PAIR ? 1 : 2);
     const size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
     size_t per_sm = (size_t)(224 * 1024) / (smem + 2048);
@@ -244,25 +235,25 @@ cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, f
     if (WARPS != 8) per_sm = 1;  // the launch bounds of the wide form
     const size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
     return launch_k(kern, dim3((unsigned)grid), dim3(WARPS * 32), smem, st, pdl, w, PAIR ? *up : w, xp, y, mode, gate, (uint32_t*)nullptr, ns, epi,
-                    slots, next);
+                    slots);
 }
 
 template <class F>
 cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, NextWeights next) {
+                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     if (epi.out.planes) {
         static const int warps = env_int("B2_EPI_WARPS", 16), slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_EPI_SLOTS", 3)));
         if (warps == 16) {
             const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)16 * slots * RING_SLOT_BYTES;
             if (smem + 2048 <= 227 * 1024)
-                return pair ? launch_ring_w<F, true, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots, next)
-                            : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots, next);
+                return pair ? launch_ring_w<F, true, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots)
+                            : launch_ring_w<F, false, 16>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, slots);
         }
     }
     static const int plain_slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_RING_SLOTS", RING_SLOTS)));
-    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots, next)
-                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots, next);
+    return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots)
+                : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -398,207 +389,13 @@ static bool f8_mma_ok(const WeightDev& w, int mode) {
 
 static cudaError_t launch_f8_mma(const WeightDev& w, const float* x, float* y, int mode, const float* gate, int sm_count, cudaStream_t st, bool pdl) {
     const size_t smem = w.n_in * 4;  // two f16 copies of x
-    static size_t smem_set = 40 * 1024;  // the kernel also has static shared memory: ask early
-    if (smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_f8_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set = smem;
-    }
+    // the kernel also has static shared memory: ask early
+    if (cudaError_t e = ensure_dynamic_smem((const void*)gemv_f8_mma_kernel, smem, 40 * 1024); e != cudaSuccess) return e;
     const size_t tiles = (w.n_out + 15) / 16;
     size_t per_sm = (size_t)(220 * 1024) / (smem + 2048);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     const size_t grid = tiles < (size_t)sm_count * per_sm ? tiles : (size_t)sm_count * per_sm;
     return launch_k(gemv_f8_mma_kernel, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, x, y, mode, gate);
-}
-
-// ---- the 4-bit formats on the tensor cores -------------------------------------------------------------------------
-// The integer dot products of gemv_kernel cost 0.75 dp4a per weight plus as much again in nibble extraction, plane
-// loads and combining (3.2 instructions per weight all told, above what the SMs can issue per weight at the HBM rate).
-// Here the products run as mma.sync m16n8k32 (s8 x s8 -> s32): a warp owns 16 weight rows, A is a sub-block's 32
-// nibbles (masked out of the packed bytes, which already are four weights per word in k order). B's eight columns hold
-// (plane 0, plane 1) four times over in a first product and (plane 2, nothing) in a second, so every lane of a quad
-// ends up with all three sums of its two rows and no lane has to ask another; lane t keeps the sums of group t and
-// applies that group's scales (FmtQ4K / FmtMLX4::tail, the same arithmetic as gemv_kernel, bit for bit), so the four
-// lanes of a quad share the float work. A lane's share of the summation index is permuted (bytes 8 t .. 8 t + 7 of the
-// 32-byte group) so that weights and planes come in 8-byte reads.
-// A CTA owns one 16-row tile at a time; its warps split K by super-blocks and bring their rows' blocks (16 copies
-// of 144 bytes per step) into per-warp rings; the warps' partial sums meet in shared memory in warp order.
-// Measured: 8.7 M warp instructions at 14336 x 4096 against 5.9 M of gemv_kernel (the waits, the per-tile CTA barriers
-// and the address arithmetic outweigh what the MMAs save) and 15.5 us against 10.7, so it stays behind B2_GEMV_MMA4.
-__device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
-                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-
-constexpr int M4_SLOTS = 3;
-constexpr int M4_SLOT_BYTES = 16 * 144;
-
-template <class F, bool PAIR>
-__global__ void __launch_bounds__(GEMV_THREADS, 3)
-gemv4_mma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode, const float* __restrict__ gate, NormScale ns) {
-    using namespace acopy;
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t bars[GEMV_WARPS * M4_SLOTS];
-    __shared__ float part[2][GEMV_WARPS][16];
-    pdl_launch_dependents();
-    const int K = (int)w.n_in, nblk = K / 256;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const size_t n_out = w.n_out, row_bytes = (size_t)nblk * 144;
-    const size_t planes_bytes = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
-    uint8_t* slots = smem + planes_bytes + (size_t)warp * M4_SLOTS * M4_SLOT_BYTES;
-    uint64_t* wbars = bars + warp * M4_SLOTS;
-    uint32_t phases = 0;
-    // this warp's super-blocks of every tile: [kb0, kb1)
-    const int kb0 = (int)((long long)nblk * warp / GEMV_WARPS), kb1 = (int)((long long)nblk * (warp + 1) / GEMV_WARPS);
-    const int per_tile = (kb1 - kb0) * (PAIR ? 2 : 1);  // steps per tile (a pair runs the second matrix after the first)
-    const size_t tiles = (n_out + 15) / 16;
-    const size_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t T = (uint32_t)(my_tiles * (size_t)per_tile);
-    // step s of this warp: tile, matrix, block
-    auto issue = [&](uint32_t s) {  // whole warp: lanes 0..15 copy one row's block each
-        const size_t tile = blockIdx.x + (size_t)(s / (uint32_t)per_tile) * gridDim.x;
-        uint32_t r = s % (uint32_t)per_tile;
-        const bool second = PAIR && r >= (uint32_t)(kb1 - kb0);
-        if (second) r -= (uint32_t)(kb1 - kb0);
-        const int slot = (int)(s % M4_SLOTS);
-        if (lane == 0) bar_expect_tx(&wbars[slot], 16 * 144);
-        __syncwarp();
-        if (lane < 16) {
-            const size_t row = min(tile * 16 + lane, n_out - 1);
-            const uint8_t* src = (second ? w2.p0 : w.p0) + row * row_bytes + (size_t)(kb0 + (int)r) * 144;
-            bulk_load(slots + slot * M4_SLOT_BYTES + lane * 144, src, 144, &wbars[slot]);
-        }
-    };
-    if (lane == 0)
-        for (int sl = 0; sl < M4_SLOTS; sl++) bar_init(&wbars[sl], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncwarp();
-    for (uint32_t s = 0; s + 1 < M4_SLOTS && s < T; s++) issue(s);  // the weights do not depend on the kernel ahead
-    pdl_wait();
-    xplanes_stage(xp, K, smem, threadIdx.x, GEMV_THREADS);
-    __syncthreads();
-    const float2* sx = (const float2*)(smem + 3 * (size_t)K);
-    const uint8_t* plane01 = smem + (size_t)(g & 1) * K;  // the plane this lane feeds as column g of the first product
-    const uint8_t* plane2 = smem + 2 * (size_t)K;
-    const float kscale = norm_scale_factor(ns, lane);
-    const uint32_t M = 0x0F0F0F0Fu;
-    uint32_t s = 0;
-    bool ok = true;
-    for (size_t ti = 0; ti < my_tiles && ok; ti++) {
-        const size_t tile = blockIdx.x + ti * gridDim.x;
-        float res[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [matrix][row g | row g + 8]
-#pragma unroll
-        for (int mat = 0; mat < (PAIR ? 2 : 1); mat++) {
-            float accA = 0.0f, accB = 0.0f;
-            for (int kb = kb0; kb < kb1; kb++, s++) {
-                __syncwarp();  // every lane is done with the slot that is refilled now
-                if (s + M4_SLOTS - 1 < T) issue(s + M4_SLOTS - 1);
-                const int slot = (int)(s % M4_SLOTS);
-                if (!bar_wait(&wbars[slot], (phases >> slot) & 1u, RING_WAIT_LIMIT)) {
-                    ok = false;
-                    break;
-                }
-                phases ^= 1u << slot;
-                const uint8_t* blkA = slots + slot * M4_SLOT_BYTES + g * 144;
-                const uint8_t* blkB = blkA + 8 * 144;
-                int mine[4] = {0, 0, 0, 0};  // this lane's group (j == t): lo / hi sums of rows g and g + 8
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint2 wa = *(const uint2*)(blkA + 16 + 32 * j + 8 * t);
-                    const uint2 wb = *(const uint2*)(blkB + 16 + 32 * j + 8 * t);
-                    const int k0 = kb * 256 + 64 * j + 8 * t;
-                    // first product: columns (plane 0, plane 1) four times over, so every lane of a quad holds both sums of
-                    // its two rows; second: (plane 2, nothing). No lane has to ask another for a part of a sum.
-                    const size_t at_lo = ((size_t)swz(k0 >> 4) << 4) + (k0 & 15), at_hi = ((size_t)swz((k0 + 32) >> 4) << 4) + (k0 & 15);
-                    const uint2 b01lo = *(const uint2*)(plane01 + at_lo), b01hi = *(const uint2*)(plane01 + at_hi);
-                    uint2 b2lo = make_uint2(0, 0), b2hi = make_uint2(0, 0);
-                    if ((g & 1) == 0) {
-                        b2lo = *(const uint2*)(plane2 + at_lo);
-                        b2hi = *(const uint2*)(plane2 + at_hi);
-                    }
-                    const uint32_t al0 = wa.x & M, al1 = wb.x & M, al2 = wa.y & M, al3 = wb.y & M;
-                    const uint32_t ah0 = (wa.x >> 4) & M, ah1 = (wb.x >> 4) & M, ah2 = (wa.y >> 4) & M, ah3 = (wb.y >> 4) & M;
-                    int cl[4], chh[4], cl2[4], ch2[4];
-                    mma_s8_16832(cl, al0, al1, al2, al3, b01lo.x, b01lo.y);
-                    mma_s8_16832(cl2, al0, al1, al2, al3, b2lo.x, b2lo.y);
-                    mma_s8_16832(chh, ah0, ah1, ah2, ah3, b01hi.x, b01hi.y);
-                    mma_s8_16832(ch2, ah0, ah1, ah2, ah3, b2hi.x, b2hi.y);
-                    if (t == j) {
-                        mine[0] = cl[0] + (cl[1] << 7) + (cl2[0] << 14);
-                        mine[1] = chh[0] + (chh[1] << 7) + (ch2[0] << 14);
-                        mine[2] = cl[2] + (cl[3] << 7) + (cl2[2] << 14);
-                        mine[3] = chh[2] + (chh[3] << 7) + (ch2[2] << 14);
-                    }
-                }
-                // the scales of group t of rows g and g + 8
-                Q4Regs ra, rb;
-                ra.hdr = *(const uint4*)blkA;
-                rb.hdr = *(const uint4*)blkB;
-                const float4 sxv = *(const float4*)(sx + (kb * 8 + 2 * t));
-                F::tail(ra, t, sxv, mine[0], mine[1], accA);
-                F::tail(rb, t, sxv, mine[2], mine[3], accB);
-            }
-            // the quad's four groups
-            accA += __shfl_xor_sync(0xffffffffu, accA, 1);
-            accA += __shfl_xor_sync(0xffffffffu, accA, 2);
-            accB += __shfl_xor_sync(0xffffffffu, accB, 1);
-            accB += __shfl_xor_sync(0xffffffffu, accB, 2);
-            res[mat][0] = accA;
-            res[mat][1] = accB;
-        }
-        if (!ok) break;
-        if (t == 0) {
-#pragma unroll
-            for (int mat = 0; mat < (PAIR ? 2 : 1); mat++) {
-                part[mat][warp][g] = res[mat][0];
-                part[mat][warp][g + 8] = res[mat][1];
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x < 16) {
-            const size_t r = tile * 16 + threadIdx.x;
-            if (r < n_out) {
-                float a = 0.0f, b = 0.0f;
-#pragma unroll
-                for (int wv = 0; wv < GEMV_WARPS; wv++) {
-                    a += part[0][wv][threadIdx.x];
-                    if (PAIR) b += part[1][wv][threadIdx.x];
-                }
-                a *= kscale;
-                b *= kscale;
-                float* o = y + r;
-                if (PAIR)
-                    *o = (mode == B2_MODE_SILU_PAIR ? silu(a) : gelu_tanh(a)) * b;
-                else if (mode == B2_MODE_STORE)
-                    *o = a;
-                else if (mode == B2_MODE_ADD)
-                    *o += a;
-                else
-                    *o += a * (1.0f / (1.0f + __expf(-gate[0])));
-            }
-        }
-        __syncthreads();
-    }
-}
-
-template <class F>
-cudaError_t launch_mma4(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count, cudaStream_t st,
-                        bool pdl, NormScale ns) {
-    const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
-    auto kern = pair ? gemv4_mma_kernel<F, true> : gemv4_mma_kernel<F, false>;
-    const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 + (size_t)GEMV_WARPS * M4_SLOTS * M4_SLOT_BYTES;
-    static size_t smem_set[2] = {40 * 1024, 40 * 1024};
-    if (smem > smem_set[pair]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set[pair] = smem;
-    }
-    const size_t tiles = (w.n_out + 15) / 16;
-    size_t per_sm = (size_t)(224 * 1024) / (smem + 3072);
-    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
-    const size_t grid = tiles < (size_t)sm_count * per_sm ? tiles : (size_t)sm_count * per_sm;
-    return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, gate, ns);
 }
 
 template <class F, bool XF32, int NT = 1>
@@ -607,12 +404,7 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     size_t smem = (((XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128) * NT;
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, XF32, NT> : gemv_kernel<F, false, XF32, NT>;
-    static size_t smem_set[2] = {48 * 1024, 48 * 1024};  // largest size asked for so far, per kernel: later launches (and captures) skip the call
-    if (smem > smem_set[pair]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set[pair] = smem;
-    }
+    if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
     const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
     size_t groups = (w.n_out + rows_per_cta - 1) / rows_per_cta;
     size_t per_sm = (size_t)(220 * 1024) / (smem + 1024);
@@ -660,10 +452,7 @@ static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, c
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, false, 1> : gemv_kernel<F, false, false, 1>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-    }
+    if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
     const size_t rows_per_cta = (size_t)GEMV_WARPS * (pair ? 1 : 2);
     size_t gx = (w.n_out + rows_per_cta - 1) / rows_per_cta;
     const size_t cap = std::max<size_t>(1, (size_t)sm_count * 3 / batch);  // about three CTAs per SM over the whole batch
@@ -696,11 +485,15 @@ static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, cons
     }
 }
 
+bool gemv_multi_fits(const WeightDev& w, int nt) {
+    const size_t per = ((w.fmt == B2_FMT_F8E4M3 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128;
+    return nt >= 1 && nt <= 4 && gemv_supports(w) && per * (size_t)nt <= 200 * 1024;
+}
+
 cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, XPlanes xp, size_t xp_stride, float* y,
                               size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st) {
     const bool f8 = w.fmt == B2_FMT_F8E4M3;
-    const size_t per = (((f8 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128);
-    if (nt < 1 || nt > 4 || per * nt > 200 * 1024) return cudaErrorInvalidValue;
+    if (!gemv_multi_fits(w, nt)) return cudaErrorInvalidValue;
     const GemvMulti m{f8 ? x_stride : xp_stride, y_stride};
     switch (nt) {
         case 1: return launch_multi_nt<1>(w, up, x, xp, y, mode, sm_count, st, m);
@@ -724,37 +517,21 @@ static bool ring_enabled() { return ring_level() != 0; }
 static bool ring_fits(const WeightDev& w) {
     return (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && xplanes_bytes(w.n_in) + RING_BYTES + 4096 <= 224 * 1024 && w.n_in <= 2048 * RING_X_STEPS;
 }
-bool gemv_takes_epilogue(const WeightDev& w) {
-    const char* m = getenv("B2_GEMV_MMA4");
-    return ring_enabled() && ring_fits(w) && w.n_out % 32 == 0 && !(m && atoi(m) != 0);
-}
+bool gemv_takes_epilogue(const WeightDev& w) { return ring_enabled() && ring_fits(w) && w.n_out % 32 == 0; }
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, NextWeights next) {
+                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     if (epi.out.planes) {  // only the ring form carries the epilogue, chained or not
         if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
-    }
-    // The tensor-core form of the 4-bit products is parity-green but not yet the faster one (14336 x 4096: 15.9 us against
-    // 11.2; a decode token 2.52 ms against 2.37): its CTA-per-tile mapping leaves 896 tiles on 444 CTAs two or three rounds
-    // deep and small products are bound by the prologue either way. It stays selectable (B2_GEMV_MMA4: 1 everywhere,
-    // 2 only in dependent-launch chains) until tiles are handed out dynamically.
-    static const int mma4 = [] {
-        const char* e = getenv("B2_GEMV_MMA4");
-        return e ? atoi(e) : 0;
-    }();
-    if (mma4 && (mma4 == 1 || pdl) && (w.fmt == B2_FMT_MLX4 || w.fmt == B2_FMT_Q4_K) && w.n_in >= 256 * GEMV_WARPS &&
-        xplanes_bytes(w.n_in) + (size_t)GEMV_WARPS * M4_SLOTS * M4_SLOT_BYTES + 4096 <= 224 * 1024) {
-        if (w.fmt == B2_FMT_MLX4) return launch_mma4<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
-        return launch_mma4<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }
     // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
     if (ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, next);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }
     switch (w.fmt) {
         case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);

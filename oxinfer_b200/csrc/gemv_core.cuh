@@ -157,8 +157,8 @@ struct FmtQ4K {
     }
 };
 
-// MLX affine 4-bit, repacked at upload into Q4_K-shaped blocks: header = 4 bf16 scales + 4 bf16 biases
-// (one per 64-group), then the 128 nibble bytes in the order above.
+// MLX affine 4-bit, repacked at upload into Q4_K-shaped blocks: header = 4 f16 d + 4 bf16 offsets
+// (one per 64-group: the fields of the reference's Q4Matrix), then the 128 nibble bytes in the order above.
 struct FmtMLX4 {
     static constexpr int ITER_K = 2048;
     using Regs = Q4Regs;
@@ -168,9 +168,8 @@ struct FmtMLX4 {
     // w = (nib - 8) d + offset = nib d + (offset - 8 d).
     __device__ static __forceinline__ void tail(const Regs& r, int j, float4 sx, int lo, int hi, float& acc) {
         const uint32_t sw = (j & 2) ? r.hdr.y : r.hdr.x, bw = (j & 2) ? r.hdr.w : r.hdr.z;
-        const float s = bf16_bits_to_f32((sw >> (16 * (j & 1))) & 0xffffu), bb = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
-        const float d = __half2float(__float2half_rn(s));
-        const float off = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(bb, __fmul_rn(8.0f, s))));
+        const float d = __half2float(__ushort_as_half((unsigned short)((sw >> (16 * (j & 1))) & 0xffffu)));
+        const float off = bf16_bits_to_f32((bw >> (16 * (j & 1))) & 0xffffu);
         const float dots = fmaf(sx.z, (float)hi, sx.x * (float)lo);
         acc = fmaf(d, dots, acc);
         acc = fmaf(off - 8.0f * d, sx.y + sx.w, acc);

@@ -1,8 +1,31 @@
 // Host-callable launchers of the CUDA kernels (one translation unit per kernel family).
 #pragma once
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "formats.cuh"
 
 namespace b2 {
+
+// A kernel that wants more dynamic shared memory than the default must be told so with cudaFuncSetAttribute, and that
+// setting belongs to the (kernel, device) pair: a process may hold contexts on several GPUs (b2_open per ordinal), and
+// each of them needs its own call. Remembers the largest size asked so far per pair, so that the common launch costs a
+// map lookup. `dflt`: what the kernel may use without asking (less than 48 KB where it also has static shared memory).
+inline cudaError_t ensure_dynamic_smem(const void* kern, size_t bytes, size_t dflt = 48 * 1024) {
+    if (bytes <= dflt) return cudaSuccess;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> asked;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& cur = asked[std::make_pair(kern, dev)];
+    if (bytes <= cur) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) cur = bytes;
+    return e;
+}
 
 // Launch with or without the programmatic-dependent-launch attribute. With it the kernel may begin while the
 // kernel ahead of it in the stream is still running; every kernel launched this way calls pdl_wait() (xplanes.cuh)
@@ -32,6 +55,10 @@ cudaError_t launch_repack_q6k(const uint8_t* raw, size_t n_out, size_t n_in, uin
                               cudaStream_t st);
 cudaError_t launch_repack_mlx4(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, size_t n_out, size_t n_in, uint8_t* out,
                                cudaStream_t st);
+// Q4Matrix with offsets (q in Q4_0 order, f16 scale per 32, bf16 offset per `group`, a multiple of 64) -> the same blocks
+// launch_repack_mlx4 makes; *mismatch (device, zeroed by the caller) is set if a 64-group's two scales differ.
+cudaError_t launch_repack_q4a(const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t n_out, size_t n_in, size_t group,
+                              uint8_t* out, int* mismatch, cudaStream_t st);
 cudaError_t launch_repack_q8_0(const uint8_t* raw, size_t n_out, size_t n_in, int8_t* qs, uint16_t* d, cudaStream_t st);
 
 // ---- gemv.cu: one-token dequant matrix-vector products ---------------------------------------
@@ -82,23 +109,13 @@ struct EpiPlanes {
     float* partial;
     float pre;
 };
-// The packed weights the NEXT product of a chain will stream (one or two matrices): the product kernel asks the L2 for them
-// (bulk prefetches, a slice per CTA, issued before the kernel waits for its predecessor), so that the next kernel's first
-// ring slots fill from L2 while this one, which is bound by instructions and not by DRAM, runs. p0 == nullptr: nothing.
-struct NextWeights {
-    const uint8_t* p0;
-    size_t n0;
-    const uint8_t* p1;
-    size_t n1;
-};
 // Whether launch_gemv takes an EpiPlanes for this matrix (the 4-bit formats whose planes and rings fit in shared memory).
 bool gemv_takes_epilogue(const WeightDev& w);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
 // FP8 kernel reads `x` (f32) directly and ignores `xp`.
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f},
-                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f},
-                        NextWeights next = NextWeights{nullptr, 0, nullptr, 0});
+                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
 // A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
 // of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
 // bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),
@@ -135,29 +152,41 @@ bool gemm_tc_supports(const WeightDev& w, size_t t);
 // y[t][n_out] (f32 or bf16) = x[t][n_in] (f16, row-major, t padded by the caller to a multiple of
 // 256 rows in `x16`) * W^T. `tmap_x` is the host-encoded tensor map of x16 (see make_tmap_x).
 struct GemmPlan;
+// a_lo_row0 > 0 (128-token tiles only): x16 holds two-term activations, the lo rows a_lo_row0 rows below the hi rows; both
+// terms feed the same accumulator, so the activations enter with 22 significant bits.
+// w_terms == 2 (Q4_K only; other formats ignore it): every weight enters as two f16 terms, hi + lo = the reference's f32
+// value to about 22 bits; tiles are then at most 112 rows wide.
 // `experts` > 1 makes a grouped plan: w.p0 holds `experts` stacked matrices of w.n_out rows, x16 / y hold the
 // token rows of all experts in segments that are multiples of 128 * m_halves rows, and tile_expert[i]
 // (device) names the expert of token tile i.
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0);
+                                size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0, size_t a_lo_row0 = 0, int w_terms = 1);
 void gemm_tc_plan_destroy(GemmPlan* p);
-bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype);
+bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype, size_t a_lo_row0 = 0,
+                          int w_terms = 1, int m_halves = 0);
+// row_unscale (device, [t], may be null): factor the epilogue multiplies token row i's results by (launch_to_f16).
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int sm_count,
-                           cudaStream_t st);
-// x (f32 / bf16 / f16, [t][K]) -> f16 [t_pad][K], pad rows zeroed.
-cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t t_pad, size_t K, void* x16, cudaStream_t st);
+                           cudaStream_t st, const float* row_unscale = nullptr);
+// x (f32 / bf16 / f16, [t][K]) -> f16 [t][K], every row multiplied by a power of two that brings its largest magnitude
+// into [2^14, 2^15) (no overflow, no subnormals, same relative rounding at every magnitude); unscale[row] = 1 / factor.
+// lo_row0 > 0: two-term activations, x * factor = hi + lo; the lo rows go lo_row0 rows below the hi rows of x16.
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0 = 0);
+// Whether nt (1..4) token rows' vectors fit in shared memory together for launch_gemv_multi.
+bool gemv_multi_fits(const WeightDev& w, int nt);
 
 // ---- moe.cu: the element-wise pieces of the routed-expert layer ------------------------------------
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st);
-cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, cudaStream_t st);
-cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a_f16, float* row_scale, cudaStream_t st);
+// Rows to f16 operands for the grouped GEMM, each multiplied by a power of two (its largest magnitude into [2^14, 2^15));
+// unscale[row] = 1 / factor is handed to the GEMM, whose epilogue multiplies the row's results by it. lo_row0 > 0: two-term
+// rows, the second term lo_row0 rows below the first (see launch_to_f16).
+cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, float* unscale, size_t lo_row0, cudaStream_t st);
+cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a_f16, float* unscale, size_t lo_row0, cudaStream_t st);
 // The same with the routes as kernel arguments (at most GEMV_BATCH_MAX pairs): slot of pair (i, j) = i k + j, no row scale.
 struct SmallRoutes {
     float w[GEMV_BATCH_MAX];
 };
 cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
-cudaError_t launch_moe_combine(const float* o, const float* row_scale, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y,
-                               cudaStream_t st);
+cudaError_t launch_moe_combine(const float* o, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
 
 // ---- decode_ops.cu: the non-matmul ops of one decode token -------------------------------------------
 // Every kernel reads the step words `sp` on the device: sp[0] position of the token, sp[1] position of row 0

@@ -51,40 +51,111 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int t, int n
     if (lane < k) w[(size_t)tok * k + lane] = mine / sum;
 }
 
-// xg[row][h] (f16) = x[src[row]][h] (f32), zeros where src[row] < 0. One CTA per row.
-__global__ void moe_gather_kernel(const float* __restrict__ x, const int* __restrict__ src, int h, __half* __restrict__ xg) {
-    const int row = blockIdx.x;
-    const int s = src[row];
-    uint2* o = (uint2*)(xg + (size_t)row * h);  // four halves at a time (h is a multiple of 256)
-    if (s < 0) {
-        for (int i = threadIdx.x; i < h / 4; i += blockDim.x) o[i] = make_uint2(0u, 0u);
-        return;
+// A power of two that brings a row's largest magnitude mx into [2^14, 2^15) (1 for an all-zero or non-finite row), and
+// its inverse: f16 operands then neither overflow nor sink into subnormals, whatever the row's magnitude.
+__device__ __forceinline__ void row_factor(float mx, float& s, float& inv) {
+    s = inv = 1.0f;
+    if (mx > 0.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);
+        const int up = min(100, max(-100, 15 - e));
+        s = ldexpf(1.0f, up);
+        inv = ldexpf(1.0f, -up);
     }
-    const float4* in = (const float4*)(x + (size_t)s * h);
-    for (int i = threadIdx.x; i < h / 4; i += blockDim.x) {
-        const float4 v = in[i];
-        const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-        o[i] = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+}
+__device__ __forceinline__ float cta_max_256(float mx, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    return mx;
+}
+// Four values times a power of two -> four f16 (hi) and, with lo, the f16 of what that rounding left over.
+__device__ __forceinline__ void store_terms(float4 v, float f, __half* hi, __half* lo) {
+    v.x *= f; v.y *= f; v.z *= f; v.w *= f;
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *(uint2*)hi = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+    if (lo) {
+        const float2 fa = __half22float2(a), fb = __half22float2(b);
+        const __half2 c = __floats2half2_rn(v.x - fa.x, v.y - fa.y), d = __floats2half2_rn(v.z - fb.x, v.w - fb.y);
+        *(uint2*)lo = make_uint2(*(const uint32_t*)&c, *(const uint32_t*)&d);
     }
 }
 
-// a[row][inter] (f16) = silu(g[row][c]) * g[row][inter + c] / scale[row] over the fused gate_up output
-// g [rows][2 inter] (f32). scale[row] is a power of two (1 unless the row would leave f16's range) that the
-// combine step multiplies back, so the down projection sees operands it can represent. src[row] < 0 marks a padding row
-// (src may be null: no padding). One CTA per row; the row is read
-// once (a thread keeps its products in registers between the maximum and the store) when inter <= 256 * 4 * ACT_KEEP.
+// xg[row][h] (f16) = x[src[row]][h] (f32) * factor[row], zeros where src[row] < 0; unscale[row] = 1 / factor, which the
+// GEMM's epilogue multiplies the row's results by. lo_off > 0: two-term rows (see launch_to_f16), the second term
+// lo_off elements behind the first. One CTA of 256 threads per row; h is a multiple of 256 and at most 8192.
+constexpr int GATHER_KEEP = 8;
+__global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict__ x, const int* __restrict__ src, int h, __half* __restrict__ xg,
+                                                         float* __restrict__ unscale, size_t lo_off) {
+    __shared__ float red[8];
+    const int row = blockIdx.x;
+    const int s = src[row];
+    __half* o = xg + (size_t)row * h;
+    if (s < 0) {
+        for (int c = threadIdx.x * 4; c < h; c += 1024) {
+            *(uint2*)(o + c) = make_uint2(0u, 0u);
+            if (lo_off) *(uint2*)(o + lo_off + c) = make_uint2(0u, 0u);
+        }
+        if (threadIdx.x == 0) unscale[row] = 1.0f;
+        return;
+    }
+    const float4* in = (const float4*)(x + (size_t)s * h);
+    float4 v[GATHER_KEEP];
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < GATHER_KEEP; j++) {
+        const int i = j * 256 + threadIdx.x;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < h / 4) {
+            v[j] = in[i];
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+        }
+    }
+    mx = cta_max_256(mx, red);
+    float f, inv;
+    row_factor(mx, f, inv);
+#pragma unroll
+    for (int j = 0; j < GATHER_KEEP; j++) {
+        const int i = j * 256 + threadIdx.x;
+        if (i < h / 4) store_terms(v[j], f, o + 4 * i, lo_off ? o + lo_off + 4 * i : nullptr);
+    }
+    if (threadIdx.x == 0) unscale[row] = inv;
+}
+
+// a[row][inter] (f16) = silu(g[row][c]) * g[row][inter + c] * factor[row] over the fused gate_up output g [rows][2 inter]
+// (f32); factor[row] is the power of two of row_factor and unscale[row] = 1 / factor is what the down projection's epilogue
+// multiplies the row's results by. lo_off as for the gather. src[row] < 0 marks a padding row (src may be null: no
+// padding). One CTA per row; the row is read once (a thread keeps its products in registers between the maximum and the
+// store) when inter <= 256 * 4 * ACT_KEEP.
 constexpr int ACT_KEEP = 2;
 __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ g, const int* __restrict__ src, int inter, __half* __restrict__ a,
-                                                      float* __restrict__ scale) {
+                                                      float* __restrict__ unscale, size_t lo_off) {
     __shared__ float red[8];
     const size_t row = blockIdx.x;
+    __half* ar = a + row * inter;
     if (src && src[row] < 0) {  // a padding row of an expert's last tile: its products are zero, nothing to read
-        for (int c = threadIdx.x * 4; c < inter; c += 256 * 4) *(uint2*)(a + row * inter + c) = make_uint2(0u, 0u);
-        if (threadIdx.x == 0) scale[row] = 1.0f;
+        for (int c = threadIdx.x * 4; c < inter; c += 256 * 4) {
+            *(uint2*)(ar + c) = make_uint2(0u, 0u);
+            if (lo_off) *(uint2*)(ar + lo_off + c) = make_uint2(0u, 0u);
+        }
+        if (threadIdx.x == 0) unscale[row] = 1.0f;
         return;
     }
     const float* gr = g + row * 2 * (size_t)inter;
     const bool keep = inter <= 256 * 4 * ACT_KEEP;  // inter is a multiple of 256: whole float4 per thread
+    auto act4 = [&](int c) {
+        const float4 gate = *(const float4*)(gr + c), up = *(const float4*)(gr + inter + c);
+        float4 r;
+        r.x = gate.x / (1.0f + expf(-gate.x)) * up.x;
+        r.y = gate.y / (1.0f + expf(-gate.y)) * up.y;
+        r.z = gate.z / (1.0f + expf(-gate.z)) * up.z;
+        r.w = gate.w / (1.0f + expf(-gate.w)) * up.w;
+        return r;
+    };
     float4 v[ACT_KEEP];
     float mx = 0.0f;
     if (keep) {
@@ -93,63 +164,46 @@ __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ 
             const int c = (j * 256 + threadIdx.x) * 4;
             v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (c < inter) {
-                const float4 gate = *(const float4*)(gr + c), up = *(const float4*)(gr + inter + c);
-                v[j].x = gate.x / (1.0f + expf(-gate.x)) * up.x;
-                v[j].y = gate.y / (1.0f + expf(-gate.y)) * up.y;
-                v[j].z = gate.z / (1.0f + expf(-gate.z)) * up.z;
-                v[j].w = gate.w / (1.0f + expf(-gate.w)) * up.w;
+                v[j] = act4(c);
                 mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
             }
         }
     } else {
-        for (int c = threadIdx.x; c < inter; c += 256) {
-            float gate = gr[c], up = gr[inter + c];
-            mx = fmaxf(mx, fabsf(gate / (1.0f + expf(-gate)) * up));
+        for (int c = threadIdx.x * 4; c < inter; c += 256 * 4) {
+            const float4 r = act4(c);
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(r.x), fabsf(r.y))), fmaxf(fabsf(r.z), fabsf(r.w)));
         }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    mx = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
-    float sc = 1.0f;
-    if (mx > 32768.0f && mx < INFINITY) sc = exp2f(ceilf(log2f(mx * (1.0f / 32768.0f))));
-    const float inv = 1.0f / sc;  // exact: a power of two
+    mx = cta_max_256(mx, red);
+    float f, inv;
+    row_factor(mx, f, inv);
     if (keep) {
 #pragma unroll
         for (int j = 0; j < ACT_KEEP; j++) {
             const int c = (j * 256 + threadIdx.x) * 4;
-            if (c < inter) {
-                const __half2 lo = __floats2half2_rn(v[j].x * inv, v[j].y * inv), hi = __floats2half2_rn(v[j].z * inv, v[j].w * inv);
-                *(uint2*)(a + row * inter + c) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
-            }
+            if (c < inter) store_terms(v[j], f, ar + c, lo_off ? ar + lo_off + c : nullptr);
         }
     } else {
-        for (int c = threadIdx.x; c < inter; c += 256) {
-            float gate = gr[c], up = gr[inter + c];
-            a[row * inter + c] = __float2half_rn(gate / (1.0f + expf(-gate)) * up * inv);
-        }
+        for (int c = threadIdx.x * 4; c < inter; c += 256 * 4) store_terms(act4(c), f, ar + c, lo_off ? ar + lo_off + c : nullptr);
     }
-    if (threadIdx.x == 0) scale[row] = sc;
+    if (threadIdx.x == 0) unscale[row] = inv;
 }
 
 // y[tok][c] += sum over the token's k routes, in order, of w * o[slot][c].
-__global__ void moe_combine_kernel(const float* __restrict__ o, const float* __restrict__ scale, const int* __restrict__ slots,
-                                   const float* __restrict__ w, int k, int h, float* __restrict__ y) {
+__global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ slots, const float* __restrict__ w, int k, int h,
+                                   float* __restrict__ y) {
     const int tok = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;  // four columns per thread (h is a multiple of 256)
     if (c >= h) return;
     float4 acc = *(const float4*)(y + (size_t)tok * h + c);
     for (int j = 0; j < k; j++) {
         const int slot = slots[(size_t)tok * k + j];
-        const float wj = w[(size_t)tok * k + j], sc = scale[slot];
+        const float wj = w[(size_t)tok * k + j];
         const float4 v = *(const float4*)(o + (size_t)slot * h + c);
-        acc.x = __fadd_rn(acc.x, __fmul_rn(wj, v.x * sc));
-        acc.y = __fadd_rn(acc.y, __fmul_rn(wj, v.y * sc));
-        acc.z = __fadd_rn(acc.z, __fmul_rn(wj, v.z * sc));
-        acc.w = __fadd_rn(acc.w, __fmul_rn(wj, v.w * sc));
+        acc.x = __fadd_rn(acc.x, __fmul_rn(wj, v.x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(wj, v.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(wj, v.z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(wj, v.w));
     }
     *(float4*)(y + (size_t)tok * h + c) = acc;
 }
@@ -182,20 +236,21 @@ cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k,
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg, cudaStream_t st) {
-    moe_gather_kernel<<<(unsigned)rows, 256, 0, st>>>(x, src, (int)h, (__half*)xg);
+cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg, float* unscale, size_t lo_row0, cudaStream_t st) {
+    if (h % 256 || h > (size_t)GATHER_KEEP * 1024) return cudaErrorInvalidValue;
+    moe_gather_kernel<<<(unsigned)rows, 256, 0, st>>>(x, src, (int)h, (__half*)xg, unscale, lo_row0 * h);
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* scale, cudaStream_t st) {
-    moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, scale);
+cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* unscale, size_t lo_row0, cudaStream_t st) {
+    if (inter % 256) return cudaErrorInvalidValue;
+    moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter);
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_combine(const float* o, const float* scale, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y,
-                               cudaStream_t st) {
+cudaError_t launch_moe_combine(const float* o, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y, cudaStream_t st) {
     dim3 grid((unsigned)((h / 4 + 255) / 256), (unsigned)t);
-    moe_combine_kernel<<<grid, 256, 0, st>>>(o, scale, slots, w, (int)k, (int)h, y);
+    moe_combine_kernel<<<grid, 256, 0, st>>>(o, slots, w, (int)k, (int)h, y);
     return cudaGetLastError();
 }
 

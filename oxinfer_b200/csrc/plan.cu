@@ -102,7 +102,7 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.v) cudaFree(k.v);
     }
     for (void* m : peer_maps_) cudaIpcCloseMemHandle(m);
-    void* frees[] = {norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_, prog_dev_, tk_ctl_, tk_prof_};
+    void* frees[] = {norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -134,8 +134,6 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         p->epilogue_ = epi_level != 0;
     }
     if (const char* e = getenv("B2_PLAN_FUSE_ROPE")) p->fuse_rope_ = atoi(e) != 0;
-    if (const char* e = getenv("B2_PLAN_TOKEN_KERNEL"))
-        if (atoi(e) != 0) p->epilogue_ = p->fuse_rope_ = false;  // the token kernel's program is built from the unfused op list
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -542,26 +540,6 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         p->ops_ = std::move(kept);
     }
 
-    // ---- the next product's weights into L2 (NextWeights) ---------------------------------------------------------
-    {
-        size_t cap_mb = 0;  // off: measured slower (2.39 ms per token with every next product prefetched, 2.27 with those up to 16 MB, 2.26 without)
-        if (const char* e = getenv("B2_PLAN_PREFETCH_MB")) cap_mb = (size_t)atoi(e);
-        auto packed = [](const WeightDev& w) { return (size_t)w.n_out * (w.n_in / 256) * 144; };
-        auto four_bit = [](const WeightDev& w) { return w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4; };
-        for (size_t a = 0; a < p->ops_.size() && cap_mb; a++) {
-            Op& cur = p->ops_[a];
-            if (cur.kind != B2_OP_LINEAR || !four_bit(cur.w)) continue;
-            for (size_t b = a + 1; b < p->ops_.size(); b++) {
-                const Op& nx = p->ops_[b];
-                if (nx.kind != B2_OP_LINEAR) continue;
-                const size_t bytes = packed(nx.w) * (nx.pair ? 2 : 1);
-                if (four_bit(nx.w) && bytes <= cap_mb * 1024 * 1024)
-                    cur.next = NextWeights{nx.w.p0, packed(nx.w), nx.pair ? nx.w2.p0 : nullptr, nx.pair ? packed(nx.w2) : 0};
-                break;
-            }
-        }
-    }
-
     // ---- scratch ------------------------------------------------------------------------------------
     if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, attend_part_floats(max_nh, max_hd) * sizeof(float)), "cudaMalloc(attention partials)");
     size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1);
@@ -599,26 +577,6 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     if (rc) return rc;
     rc = p->capture(p->cap_stream_, false, &p->step_exec_, err);
     if (rc) return rc;
-    // The persistent token kernel is built on request (B2_PLAN_TOKEN_KERNEL=1): at the sizes measured so far the graph of
-    // one launch per op is the faster of the two (grid barriers and per-CTA staging cost what the launches saved).
-    const char* tk = getenv("B2_PLAN_TOKEN_KERNEL");
-    if (tk && atoi(tk) != 0) {
-        p->build_program();
-        if (p->tk_ok_) {
-            PLAN_CUDA(cudaMalloc((void**)&p->prog_dev_, p->prog_.size() * sizeof(TokOp)), "cudaMalloc(program)");
-            PLAN_CUDA(cudaMemcpy(p->prog_dev_, p->prog_.data(), p->prog_.size() * sizeof(TokOp), cudaMemcpyHostToDevice), "cudaMemcpy(program)");
-            PLAN_CUDA(cudaMalloc((void**)&p->tk_ctl_, 64), "cudaMalloc(token kernel words)");
-            // one token through the kernel now: a launch that cannot be placed (shared memory, residency) shows here, and the plan
-            // then keeps to the graph
-            PLAN_CUDA(launch_set_step(p->sp_, 0, 0, 0, nullptr, 0, p->cap_stream_), "set_step");
-            std::string e2;
-            if (p->run_token_kernel(p->cap_stream_, false, 0, nullptr, 0, 0, 1, e2) != B2_OK || cudaStreamSynchronize(p->cap_stream_) != cudaSuccess ||
-                p->check_status(e2) != B2_OK) {
-                cudaGetLastError();
-                p->tk_ok_ = false;
-            }
-        }
-    }
     *out = p.release();
     return B2_OK;
 }
@@ -634,7 +592,7 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
             case B2_OP_NORM: e = launch_norm(o.x, o.y, o.p0, o.norm, o.rows, o.xp, st, pdl); break;
             case OP_XPLANES: e = launch_xplanes(o.x, o.n, o.xp, st, pdl); break;
             case OP_NORM_DEFERRED: e = launch_norm_planes(o.x, o.p0, o.norm.pre, o.norm.n, o.xp, const_cast<float*>(o.ns.partial), st, pdl); break;
-            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl, o.ns, o.epi, pdl ? o.next : NextWeights{nullptr, 0, nullptr, 0}); break;
+            case B2_OP_LINEAR: e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, o.x, o.xp, o.y, o.mode, o.z, sm_count_, st, pdl, o.ns, o.epi); break;
             case B2_OP_QK_ROPE:
                 e = launch_qk_rope(o.x, o.y, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st, pdl);
                 break;
@@ -690,16 +648,6 @@ int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* ou
 int DecodePlanImpl::check_status(std::string& err) {
     uint32_t s = 0;
     PLAN_CUDA(cudaMemcpy(&s, status_, 4, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
-    uint32_t tks[3] = {0, 0, 0};
-    if (tk_ctl_) PLAN_CUDA(cudaMemcpy(tks, tk_ctl_, 12, cudaMemcpyDeviceToHost), "cudaMemcpy(token kernel words)");
-    if (tks[2]) {
-        cudaMemset(att_counters_, 0, 4 * (kv_.empty() ? 1 : kv_.size()));
-        err = tks[2] == 2   ? "[b200qmm: plan: a grid barrier of the token kernel ran into its time limit]"
-              : tks[2] == 3 ? "[b200qmm: plan: a weight copy of the token kernel did not arrive within its time limit]"
-                            : "[b200qmm: plan: an attention wait of the token kernel ran into its time limit]";
-        cudaMemset(tk_ctl_, 0, 12);
-        return B2_ERR_TIMEOUT;
-    }
     if (s) {
         cudaMemset(status_, 0, 4);
         cudaMemset(att_counters_, 0, 4 * kv_.size());  // a CTA that gave up never counted itself
@@ -730,12 +678,7 @@ int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const floa
     PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos, (uint32_t)pos, 0, nullptr, 0, st), "set_step");
     PLAN_CUDA(cudaMemcpyAsync(input_, x, n_input_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(x)");
     if (cs_stride_) PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs, cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
-    if (tk_ok_) {
-        int rc = run_token_kernel(st, false, 0, nullptr, 0, pos, 1, err);
-        if (rc) return rc;
-    } else {
-        PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
-    }
+    PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
     PLAN_CUDA(cudaMemcpyAsync(hidden, hidden_, n_hidden_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(hidden)");
     if (logits) PLAN_CUDA(cudaMemcpyAsync(logits, logits_, n_logits_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(logits)");
     PLAN_CUDA(cudaStreamSynchronize(st), "step");
@@ -798,19 +741,6 @@ int DecodePlanImpl::generate(cudaStream_t st, uint64_t embed_handle, const Weigh
     if (embed.n_in != n_input_ || first_token < 0 || (size_t)first_token >= embed.n_out) {
         err = "[b200qmm: plan generate: the embedding matrix does not match the graph's input, or the token is outside it]";
         return B2_ERR_ARG;
-    }
-    if (tk_ok_) {
-        gen_embed_ = embed_handle;
-        if (cs_stride_)
-            PLAN_CUDA(cudaMemcpyAsync(rope_table_, rope_cs_table, n_tokens * cs_stride_ * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpy(rope)");
-        PLAN_CUDA(cudaEventRecord(ev0_, st), "cudaEventRecord");
-        int rc = run_token_kernel(st, true, embed_handle, &embed, first_token, pos0, n_tokens, err);
-        if (rc) return rc;
-        PLAN_CUDA(cudaEventRecord(ev1_, st), "cudaEventRecord");
-        PLAN_CUDA(cudaMemcpyAsync(out_tokens, out_tokens_, n_tokens * sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpy(tokens)");
-        PLAN_CUDA(cudaStreamSynchronize(st), "generate");
-        if (elapsed_ms) PLAN_CUDA(cudaEventElapsedTime(elapsed_ms, ev0_, ev1_), "cudaEventElapsedTime");
-        return check_status(err);
     }
     if (!gen_exec_ || gen_embed_ != embed_handle || gen_embed_dev_.p0 != embed.p0) {
         if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
@@ -919,231 +849,6 @@ int DecodePlanImpl::attach_peers(uint32_t rank, uint32_t world, const void* hand
     if (step_exec_) cudaGraphExecDestroy(step_exec_);
     step_exec_ = nullptr;
     return capture(cap_stream_, false, &step_exec_, err);
-}
-
-// ---- the persistent token kernel -----------------------------------------------------------------------------
-// The program: ops_ in order, a planes-staging step in front of every product whose vector is not the one already in
-// shared memory, and a grid barrier wherever an op touches memory that an op since the last barrier wrote (or writes
-// memory that one read).
-void DecodePlanImpl::build_program() {
-    struct Range {
-        const char *b, *e;
-    };
-    auto rng = [](const void* p, size_t bytes) { return Range{(const char*)p, (const char*)p + bytes}; };
-    auto hits = [](const Range& r, const std::vector<Range>& v) {
-        for (const Range& o : v)
-            if (r.b < o.e && o.b < r.e) return true;
-        return false;
-    };
-    std::vector<Range> W, R;
-    prog_.clear();
-    tk_barriers_ = 0;
-    const float* staged_ptr = nullptr;   // the vector whose planes are in shared memory
-    const float* gplanes_ptr = nullptr;  // the vector whose planes are in global memory (gplanes)
-    XPlanes gplanes{};
-    size_t staged_n = 0, gplanes_n = 0, max_k = 0, att_smem = 0;
-    auto emit = [&](const TokOp& op, const std::vector<Range>& reads, const std::vector<Range>& writes) {
-        bool barrier = false;
-        for (const Range& r : reads) barrier = barrier || hits(r, W);
-        for (const Range& w : writes) barrier = barrier || hits(w, W) || hits(w, R);
-        if (barrier) {
-            TokOp b{};
-            b.kind = TK_BARRIER;
-            prog_.push_back(b);
-            tk_barriers_++;
-            W.clear();
-            R.clear();
-        }
-        prog_.push_back(op);
-        R.insert(R.end(), reads.begin(), reads.end());
-        W.insert(W.end(), writes.begin(), writes.end());
-        for (const Range& w : writes) {
-            if (staged_ptr && hits(w, {rng(staged_ptr, staged_n * 4)})) staged_ptr = nullptr;
-            if (gplanes_ptr && hits(w, {rng(gplanes_ptr, gplanes_n * 4)})) gplanes_ptr = nullptr;
-        }
-    };
-    const size_t esz = kv_f16_ ? 2 : 4;
-    for (const Op& o : ops_) {
-        TokOp t{};
-        switch (o.kind) {
-            case OP_XPLANES: {
-                // a long vector (the MLP's activations): its planes are computed once, spread over the grid, and copied
-                // by every CTA; a short one is split by every CTA for itself (TK_STAGE below) and saves the barrier
-                if (o.n < 8192) break;
-                t.kind = TK_XPLANES;
-                t.x = o.x;
-                t.n = o.n;
-                t.xp = o.xp;
-                emit(t, {rng(o.x, (size_t)o.n * 4)}, {rng(o.xp.planes, xplanes_bytes(o.n))});
-                gplanes_ptr = o.x;
-                gplanes_n = o.n;
-                gplanes = o.xp;
-                break;
-            }
-            case B2_OP_NORM:
-            case OP_NORM_DEFERRED: {  // the token kernel normalizes in full per CTA either way (its products apply no factor)
-                if (o.rows != 1 || o.norm.n % 32 || o.norm.n > TOKEN_KERNEL_MAX_NORM || o.norm.add) return;
-                t.kind = TK_NORM_STAGE;
-                t.x = o.x;
-                t.y = o.y;
-                t.p0 = o.p0;
-                t.norm = o.norm;
-                emit(t, {rng(o.x, o.norm.n * 4)}, {rng(o.y, o.norm.n * 4)});
-                staged_ptr = o.y;
-                staged_n = o.norm.n;
-                max_k = std::max<size_t>(max_k, o.norm.n);
-                break;
-            }
-            case B2_OP_LINEAR: {
-                if (o.w.fmt == B2_FMT_F8E4M3) return;
-                if (staged_ptr != o.x || staged_n != o.w.n_in) {
-                    TokOp s{};
-                    s.x = o.x;
-                    s.n = (uint32_t)o.w.n_in;
-                    if (gplanes_ptr == o.x && gplanes_n == o.w.n_in) {
-                        s.kind = TK_COPY;
-                        s.xp = gplanes;
-                        emit(s, {rng(gplanes.planes, xplanes_bytes(s.n))}, {});
-                    } else {
-                        s.kind = TK_STAGE;
-                        emit(s, {rng(o.x, o.w.n_in * 4)}, {});
-                    }
-                    staged_ptr = o.x;
-                    staged_n = o.w.n_in;
-                }
-                max_k = std::max(max_k, o.w.n_in);
-                t.kind = TK_GEMV;
-                t.mode = (uint32_t)o.mode;
-                t.pair = o.pair ? 1 : 0;
-                t.y = o.y;
-                t.z = o.z;
-                t.w = o.w;
-                t.w2 = o.w2;
-                std::vector<Range> reads;
-                if (o.mode == B2_MODE_ADD || o.mode == B2_MODE_ADD_GATED) reads.push_back(rng(o.y, o.w.n_out * 4));
-                if (o.z) reads.push_back(rng(o.z, 4));
-                emit(t, reads, {rng(o.y, o.w.n_out * 4)});
-                break;
-            }
-            case B2_OP_QK_ROPE: {
-                t.kind = TK_ROPE;
-                t.x = o.x;
-                t.y = o.y;
-                t.p0 = o.p0;
-                t.p1 = o.p1;
-                t.kc = kv_[o.kv].k;
-                t.vc = kv_[o.kv].v;
-                t.kv_f16 = (uint32_t)kv_f16_;
-                t.rope = o.rope;
-                const size_t cache = (size_t)o.rope.nkv * max_len_ * o.rope.hd * esz;
-                const size_t qkv_n = std::max({(size_t)(o.rope.nh - 1) * o.rope.q_stride + o.rope.hd, (size_t)o.rope.k_off + (size_t)o.rope.nkv * o.rope.hd,
-                                               (size_t)o.rope.v_off + (size_t)o.rope.nkv * o.rope.hd});
-                emit(t, {rng(o.x, qkv_n * 4)}, {rng(o.y, (size_t)o.rope.nh * o.rope.hd * 4), rng(t.kc, cache), rng(t.vc, cache)});
-                break;
-            }
-            case B2_OP_ATTEND: {
-                if (!token_kernel_attend_ok(o.attn.nh, o.attn.nkv, o.attn.hd)) return;
-                t.kind = TK_ATTEND;
-                t.x = o.x;
-                t.y = o.y;
-                t.kc = kv_[o.kv].k;
-                t.vc = kv_[o.kv].v;
-                t.kv_f16 = (uint32_t)kv_f16_;
-                t.attn = o.attn;  // with planes: the CTA that combines a KV head's splits writes the planes of its outputs
-                t.xp = o.xp;
-                const size_t cache = (size_t)o.attn.nkv * max_len_ * o.attn.hd * esz, qn = (size_t)o.attn.nh * o.attn.hd * 4;
-                std::vector<Range> writes{rng(o.y, qn), rng(part_, attend_part_floats(o.attn.nh, o.attn.hd) * 4), rng(att_counters_, 4 * o.attn.nkv)};
-                if (o.attn.planes) writes.push_back(rng(o.xp.planes, xplanes_bytes((size_t)o.attn.nh * o.attn.hd)));
-                emit(t, {rng(o.x, qn), rng(t.kc, cache), rng(t.vc, cache)}, writes);
-                staged_ptr = nullptr;  // the attention tiles use the planes' shared memory
-                if (o.attn.planes) {
-                    gplanes_ptr = o.y;
-                    gplanes_n = (size_t)o.attn.nh * o.attn.hd;
-                    gplanes = o.xp;
-                }
-                att_smem = std::max(att_smem, token_kernel_smem(0, o.attn.hd, o.attn.nh / o.attn.nkv, kv_f16_));
-                break;
-            }
-            case B2_OP_GLU: {
-                t.kind = TK_GLU;
-                t.x = o.x;
-                t.z = o.z;
-                t.y = o.y;
-                t.n = o.n;
-                t.gelu = (uint32_t)o.gelu;
-                emit(t, {rng(o.x, o.n * 4), rng(o.z, o.n * 4)}, {rng(o.y, o.n * 4)});
-                break;
-            }
-            default: return;
-        }
-    }
-    // the most ring slots per warp that fit beside the planes
-    const size_t limit = 226 * 1024;
-    tk_ring_offset_ = (uint32_t)token_kernel_ring_offset(max_k);
-    tk_ring_slots_ = 0;
-    for (uint32_t sl = 4; sl >= 2; sl--)
-        if (token_kernel_fixed_bytes() + tk_ring_offset_ + token_kernel_ring_bytes(sl) <= limit) {
-            tk_ring_slots_ = sl;
-            break;
-        }
-    if (!tk_ring_slots_) return;
-    tk_smem_ = std::max(att_smem, token_kernel_fixed_bytes() + tk_ring_offset_ + token_kernel_ring_bytes(tk_ring_slots_));
-    if (tk_smem_ > limit) return;
-    tk_ok_ = true;
-}
-
-int DecodePlanImpl::run_token_kernel(cudaStream_t st, bool with_head, uint64_t, const WeightDev* embed, int32_t first_token, size_t pos0,
-                                     size_t n_tokens, std::string& err) {
-    TokenArgs a{};
-    a.prog = prog_dev_;
-    a.n_ops = (uint32_t)prog_.size();
-    a.n_tokens = (uint32_t)n_tokens;
-    a.pos0 = (uint32_t)pos0;
-    a.table_pos0 = (uint32_t)pos0;
-    a.with_head = with_head ? 1 : 0;
-    a.n_logits = n_logits_;
-    a.max_splits = std::min<uint32_t>(64, (max_len_ + 63) / 64);
-    a.first_token = (uint32_t)first_token;
-    a.ring_slots = tk_ring_slots_;
-    a.ring_offset = tk_ring_offset_;
-    a.cs_table = rope_table_;
-    a.input = input_;
-    a.logits = logits_;
-    a.part = part_;
-    a.att_counters = att_counters_;
-    a.ctl = tk_ctl_;
-    a.argmax_val = argmax_val_;
-    a.argmax_idx = argmax_idx_;
-    a.token = token_;
-    a.out_tokens = out_tokens_;
-    if (embed) a.embed = *embed;
-    if (getenv("B2_TK_PROF")) {
-        if (!tk_prof_) {
-            PLAN_CUDA(cudaMalloc((void**)&tk_prof_, 96 * 8), "cudaMalloc(profile)");
-        }
-        PLAN_CUDA(cudaMemsetAsync(tk_prof_, 0, 96 * 8, st), "cudaMemset(profile)");
-        a.prof = tk_prof_;
-    }
-    PLAN_CUDA(cudaMemsetAsync(tk_ctl_, 0, 64, st), "cudaMemset(token kernel words)");
-    PLAN_CUDA(launch_token_kernel(a, tk_smem_, sm_count_, st), "token kernel");
-    if (a.prof) {  // diagnostics: CTA 0's cycles per op kind, per token
-        unsigned long long h[96];
-        PLAN_CUDA(cudaStreamSynchronize(st), "token kernel");
-        PLAN_CUDA(cudaMemcpy(h, tk_prof_, sizeof h, cudaMemcpyDeviceToHost), "cudaMemcpy(profile)");
-        static const char* names[16] = {"", "norm_stage", "stage", "gemv", "rope", "attend", "glu", "barrier", "xplanes", "copy", "", "", "", "", "", ""};
-        for (int k = 1; k < 10; k++)
-            if (h[16 + k])
-                fprintf(stderr, "[b200qmm token kernel] %-10s %6llu ops/token  %9.0f cycles/token  %7.0f cycles/op\n", names[k],
-                        h[16 + k] / (unsigned long long)n_tokens, (double)h[k] / n_tokens, (double)h[k] / h[16 + k]);
-        for (size_t pc = 0; pc < 32 && pc < prog_.size(); pc++)
-            fprintf(stderr, "[b200qmm token kernel] op %2zu %-10s %8.0f cycles\n", pc, names[prog_[pc].kind & 15], (double)h[32 + pc] / n_tokens);
-        if (h[17]) fprintf(stderr, "[b200qmm token kernel] norm_stage: loads done %.0f, sum done %.0f (cycles from its start)\n", (double)h[64] / h[17], (double)h[65] / h[17]);
-        if (h[21])
-            fprintf(stderr, "[b200qmm token kernel] attend unit (CTA 0, group 0), cycles from its start: keys in %.0f, scores %.0f, values in %.0f, loop done %.0f, counted %.0f, combined %.0f (%llu combines)\n",
-                    (double)h[72] / h[21], (double)h[73] / h[21], (double)h[74] / h[21], (double)h[75] / h[21], (double)h[76] / h[21],
-                    h[78] ? (double)h[77] / h[78] : 0.0, h[78]);
-    }
-    return B2_OK;
 }
 
 }  // namespace b2

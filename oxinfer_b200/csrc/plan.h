@@ -7,7 +7,6 @@
 
 #include "../../include/b200qmm.h"
 #include "kernels.h"
-#include "token_kernel.h"
 
 namespace b2 {
 
@@ -26,8 +25,7 @@ class DecodePlanImpl {
                  const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err);
     int export_handle(void* out128, std::string& err);
     int attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err);
-    uint64_t launches_per_step() const { return tk_ok_ ? 1 : (uint64_t)ops_.size(); }
-    bool token_kernel() const { return tk_ok_; }
+    uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
     bool uses_weight(uint64_t h) const;
 
   private:
@@ -50,16 +48,12 @@ class DecodePlanImpl {
         NormScale ns{};      // LINEAR: the deferred norm factor of its vector; deferred NORM: where its partial sums go
         XPlanes xp{};  // planes this op writes (norm, attend, xplanes) or reads (linear)
         FusedRope fr{};   // ATTEND: RoPE and the cache append done by the attention kernel (the QK_ROPE op ahead of it is dropped)
-        NextWeights next{};  // LINEAR: the weights of the next product, prefetched into L2 by this one
         EpiPlanes epi{};  // LINEAR: the planes of its output, written by its own last warps (the split kernel behind it is dropped)
     };
     DecodePlanImpl() = default;
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
     int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err);
     int check_status(std::string& err);
-    void build_program();  // the token kernel's program from ops_, if every op is one it takes
-    int run_token_kernel(cudaStream_t st, bool with_head, uint64_t embed_handle, const WeightDev* embed, int32_t first_token, size_t pos0,
-                         size_t n_tokens, std::string& err);
 
     std::vector<Op> ops_;
     std::vector<uint64_t> weight_handles_;
@@ -111,15 +105,6 @@ class DecodePlanImpl {
     uint64_t gen_embed_ = 0;
     WeightDev gen_embed_dev_{};
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
-    // the persistent token kernel (B2_PLAN_TOKEN_KERNEL=0 keeps to the one-launch-per-op graph)
-    bool tk_ok_ = false;
-    std::vector<TokOp> prog_;
-    TokOp* prog_dev_ = nullptr;
-    uint32_t* tk_ctl_ = nullptr;
-    size_t tk_smem_ = 0;
-    uint32_t tk_ring_slots_ = 0, tk_ring_offset_ = 0;
-    uint32_t tk_barriers_ = 0;
-    unsigned long long* tk_prof_ = nullptr;  // B2_TK_PROF: per-op-kind cycle counts of CTA 0
 };
 
 }  // namespace b2

@@ -21,19 +21,8 @@ pytestmark = pytest.mark.gpu
 CFG = dict(n_layers=2, h=256, nh=4, nkv=2, hd=64, inter=512, vocab=1024)
 
 
-def build(backend, cfg=CFG, seed=900, max_len=512, kv_f16=False, interleaved=True, token_kernel=True):
-    """`token_kernel`: the persistent one-launch-per-token kernel (the default), else the graph of one launch per op."""
-    import os
-
-    before = os.environ.get("B2_PLAN_TOKEN_KERNEL")
-    os.environ["B2_PLAN_TOKEN_KERNEL"] = "1" if token_kernel else "0"   # read when the plan is made; put back below
-    try:
-        return _build(backend, cfg, seed, max_len, kv_f16, interleaved)
-    finally:
-        if before is None:
-            os.environ.pop("B2_PLAN_TOKEN_KERNEL", None)
-        else:
-            os.environ["B2_PLAN_TOKEN_KERNEL"] = before
+def build(backend, cfg=CFG, seed=900, max_len=512, kv_f16=False, interleaved=True):
+    return _build(backend, cfg, seed, max_len, kv_f16, interleaved)
 
 
 def _build(backend, cfg, seed, max_len, kv_f16, interleaved):
@@ -72,11 +61,10 @@ def prefill(plan, cpu, n, seed):
         plan.kv_write(li, 0, k, v)
 
 
-@pytest.mark.parametrize("token_kernel", [True, False])
 @pytest.mark.parametrize("interleaved", [True, False])
-def test_steps_match_oracle_across_tile_edges(backend, interleaved, token_kernel):
-    plan, cpu, _, cpu_embed, inv_freq, keep = build(backend, interleaved=interleaved, token_kernel=token_kernel)
-    assert (plan.launches_per_step() == 1) == token_kernel
+def test_steps_match_oracle_across_tile_edges(backend, interleaved):
+    plan, cpu, _, cpu_embed, inv_freq, keep = build(backend, interleaved=interleaved)
+    assert plan.launches_per_step() > 1
     rng = np.random.default_rng(5)
     # positions 0 (one key), then a prefilled context whose length crosses the 64-key tile edges
     x = rng.standard_normal(CFG["h"]).astype(np.float32)
@@ -118,9 +106,8 @@ def test_consecutive_steps_build_the_cache(backend):
     plan.close()
 
 
-@pytest.mark.parametrize("token_kernel", [True, False])
-def test_generate_matches_host_loop_and_oracle(backend, token_kernel):
-    plan, cpu, dembed, cpu_embed, inv_freq, keep = build(backend, seed=920, token_kernel=token_kernel)
+def test_generate_matches_host_loop_and_oracle(backend):
+    plan, cpu, dembed, cpu_embed, inv_freq, keep = build(backend, seed=920)
     n0, n = 37, 24
     prefill(plan, cpu, n0, 77)
     table = np.stack([O.rope_table(n0 + i, inv_freq) for i in range(n)])
@@ -156,7 +143,7 @@ def test_planes_from_the_product_epilogue_are_the_same_bits(backend):
     try:
         for level in ("0", "1", "2"):   # none / residual-adding products / the gate-up pair too
             os.environ["B2_PLAN_EPILOGUE"] = level
-            plans[level] = build(backend, cfg=cfg, seed=955, token_kernel=False)
+            plans[level] = build(backend, cfg=cfg, seed=955)
     finally:
         os.environ.pop("B2_PLAN_EPILOGUE", None)
     n = {k: v[0].launches_per_step() for k, v in plans.items()}
@@ -190,7 +177,6 @@ def test_grouped_heads_and_long_context(backend):
     """8 query heads per KV head, head dim 128, and more key tiles than CTAs per KV head (several tiles per CTA)."""
     cfg = dict(n_layers=1, h=1024, nh=8, nkv=1, hd=128, inter=512, vocab=512)
     plan, cpu, _, _, inv_freq, keep = build(backend, cfg=cfg, seed=940, max_len=4500)
-    assert plan.launches_per_step() > 1   # 8 heads per KV head: outside the token kernel, the graph takes it
     n = 4300
     prefill(plan, cpu, n, 41)
     rng = np.random.default_rng(9)
@@ -202,10 +188,9 @@ def test_grouped_heads_and_long_context(backend):
     plan.close()
 
 
-def test_token_kernel_long_context_several_tiles_per_unit(backend):
+def test_long_context_two_consecutive_positions(backend):
     cfg = dict(n_layers=1, h=512, nh=4, nkv=1, hd=128, inter=512, vocab=512)
     plan, cpu, _, _, inv_freq, keep = build(backend, cfg=cfg, seed=945, max_len=4500)
-    assert plan.launches_per_step() == 1
     n = 4300
     prefill(plan, cpu, n, 43)
     rng = np.random.default_rng(10)

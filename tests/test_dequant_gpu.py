@@ -56,6 +56,33 @@ def test_gpu_dequant_bit_exact_with_oracle(backend, fmt, shape):
     assert np.array_equal(backend.dequantize_rows(sh), want[r0:])
 
 
+@pytest.mark.parametrize("shape", [(8, 256), (136, 768), (300, 2048)])
+def test_q4matrix_upload_gives_the_same_device_values_as_the_mlx_triple(backend, shape):
+    """b2_upload_q4 takes the layout a backend is actually handed, WeightRef::Q4(&Q4Matrix) (src/gpu.rs:15-21,
+    src/quant.rs:427-440): what from_mlx_q4 made of the MLX triple. Both uploads must dequantize to the same bits (and to
+    dequantize_rows_q4's), and multiply to the same bits."""
+    import torch
+
+    n_out, n_in = shape
+    ref, m = make_pair("mlx4", n_out, n_in, 230 + n_out)
+    q, sc, off, group = m.q4_parts()
+    dev_a = backend.upload(ref, n_out, n_in)
+    dev_b = backend.upload(ob.Q4Matrix(q, sc, off, group), n_out, n_in)
+    assert dev_b is not None, backend.last_declined
+    want = m.dequantize_rows()
+    a, b = backend.dequantize_rows(dev_a), backend.dequantize_rows(dev_b)
+    assert np.array_equal(a.view(np.uint32), want.view(np.uint32)) and np.array_equal(b.view(np.uint32), want.view(np.uint32))
+    x = synth.activations(1, n_in, 231)
+    ya, yb = np.zeros((1, n_out), np.float32), np.zeros((1, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev_a, ya)]) and backend.matvec_rows(x, [ob.RowsJob(dev_b, yb)])
+    assert np.array_equal(ya, yb)
+    # plain Q4 (no offsets: a scale per 32 weights) and a matrix whose 64-groups do not share a scale are declined
+    assert backend.upload(ob.Q4Matrix(q, sc, None, group), n_out, n_in) is None
+    sc2 = sc.copy()
+    sc2[1] ^= 1
+    assert backend.upload(ob.Q4Matrix(q, sc2, off, group), n_out, n_in) is None and "differ in scale" in backend.last_declined
+
+
 def test_gpu_dequant_golden(backend):
     from pathlib import Path
 

@@ -32,6 +32,51 @@ def test_q4k_matmul_matches_oracle(backend, shape):
     assert row_err(y, m.matmul_cpu(x)) < TOL  # the reference CPU path's own f32 result
 
 
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4", "f8_e4m3"])
+@pytest.mark.parametrize("t", [12, 100, 300])
+def test_matmul_rows_of_very_different_magnitude(backend, fmt, t):
+    """Token rows scaled by 1e-3, 1, 300 and 2e5, the magnitudes of the reference's input() (src/cuda.rs:1579-1700): a row
+    of 2e5 would overflow f16 and a row of 1e-3 would lose bits to its subnormals, so every row is multiplied by a power
+    of two on its way to f16 and its results are scaled back in the epilogue. The reference holds its f32 kernels to
+    1e-4 there; f16 operands give 1e-3 (2e-3 for FP8), the bound this engine states, at every magnitude alike."""
+    n_out, n_in = 640, 1024
+    ref, m = make_pair(fmt, n_out, n_in, 440 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 441) * np.array([1e-3, 1.0, 300.0, 2e5], np.float32)[np.arange(t) % 4, None]
+    y = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert np.isfinite(y).all()
+    exact = m.matmul_f64(x)
+    errs = [row_err(y[i::4], exact[i::4]) for i in range(4)]
+    print(f"{fmt} t={t}: row errors by magnitude 1e-3 / 1 / 300 / 2e5: " + " ".join(f"{e:.2e}" for e in errs))
+    assert max(errs) < (2e-3 if fmt == "f8_e4m3" else TOL), errs
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
+@pytest.mark.parametrize("shape", [(640, 1024, 100), (1000, 2048, 300), (333, 512, 9)])
+def test_exact_switch_meets_the_reference_kernels_bound(backend, fmt, shape):
+    """b2_set_exact (gpu::set_exact, src/gpu.rs:313-338): activations as two f16 terms and, for Q4_K, weights as two f16 terms.
+    The reference holds its f32 CUDA kernels to row_err < 1e-4 against the f64 product on rows scaled by 1e-3, 1, 300 and 2e5
+    (src/cuda.rs:1579-1700); with the switch on this engine's tensor-core GEMM meets the same bound on the same kind of rows."""
+    n_out, n_in, t = shape
+    ref, m = make_pair(fmt, n_out, n_in, 450 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 451) * np.array([1e-3, 1.0, 300.0, 2e5], np.float32)[np.arange(t) % 4, None]
+    exact = m.matmul_f64(x)
+    y = np.full((t, n_out), np.nan, np.float32)
+    backend.set_exact(True)
+    try:
+        assert backend.matmul(x, [ob.Job(dev, y)])
+    finally:
+        backend.set_exact(False)
+    err = row_err(y, exact)
+    print(f"exact switch, {fmt} {shape}: row error {err:.2e}")
+    assert err < 1e-4, err
+    y1 = np.zeros_like(y)
+    assert backend.matmul(x, [ob.Job(dev, y1)])      # and the default path afterwards is the default path again
+    assert row_err(y1, exact) < TOL
+
+
 def test_q4k_matmul_two_jobs_share_x_and_stats(backend):
     n_in, t = 1024, 96
     refs = [make_pair("q4_k", n, n_in, 410 + n) for n in (384, 640)]

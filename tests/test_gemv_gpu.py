@@ -101,6 +101,25 @@ def test_matvec_zero_and_extreme_inputs(backend):
     assert backend.matvec_rows(x, [ob.RowsJob(dev, y)]) and not y.any()
 
 
+def test_matvec_rows_job_list_of_mixed_formats(backend):
+    """A job list whose first job is FP8 (its rows go one by one and never touch the integer planes) followed by 4-, 6- and
+    8-bit jobs, called twice with different x: every job must see the planes of THIS call's rows, whatever an earlier job
+    or an earlier call left in the scratch."""
+    n_in = 1024
+    fmts = ["f8_e4m3", "q4_k", "q6_k", "f8_e4m3", "q8_0", "mlx4"]
+    pairs = [make_pair(f, 96 + 32 * i, n_in, 360 + i) for i, f in enumerate(fmts)]
+    devs = [backend.upload(r, 96 + 32 * i, n_in) for i, (r, _) in enumerate(pairs)]
+    for seed in (370, 371):
+        x = synth.activations(3, n_in, seed)
+        ys = [np.full((3, 96 + 32 * i), np.nan, np.float32) for i in range(len(fmts))]
+        assert backend.matvec_rows(x, [ob.RowsJob(d, y) for d, y in zip(devs, ys)])
+        for (_, m), y in zip(pairs, ys):
+            assert row_err(y, m.matmul_f64(x)) < TIGHT
+        # a one-row call in between leaves a single vector's planes behind
+        y1 = np.zeros((1, 128), np.float32)
+        assert backend.matvec_rows(x[:1] * np.float32(3.0), [ob.RowsJob(devs[1], y1)])
+
+
 def test_matmul_small_t_uses_gemv_for_every_format(backend):
     for fmt in FORMATS:
         n_out, n_in = 200, 512
@@ -114,9 +133,9 @@ def test_matmul_small_t_uses_gemv_for_every_format(backend):
 
 @pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
 @pytest.mark.parametrize("shape", [(1000, 2048), (4099, 4096), (520, 14336)])
-def test_tensor_core_path_modes_and_pairs(backend, fmt, shape):
-    """K >= 2048: the 4-bit products run on the tensor cores (mma.sync over nibbles and planes). Store / add / gated add and
-    the SiLU / GELU pairs, ragged row counts (the last 16-row tile is partial), against the f64 definition."""
+def test_four_bit_modes_and_pairs_at_large_k(backend, fmt, shape):
+    """The 4-bit products at K >= 2048, up to the K = 14336 whose planes need more than 48 KB of shared memory: store /
+    add / gated add and the SiLU / GELU pairs, ragged row counts, against the f64 definition."""
     n_out, n_in = shape
     ref_g, mg = make_pair(fmt, n_out, n_in, 350)
     ref_u, mu = make_pair(fmt, n_out, n_in, 351)

@@ -14,6 +14,7 @@ import pytest
 import torch
 
 import oxinfer_b200 as ob
+from oracle import oracle as O
 from oxinfer_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -59,6 +60,33 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(backend):
         assert np.abs(got2.cpu().numpy() - want2.cpu().numpy()).max() <= TOL * np.abs(want2.cpu().numpy()).max()
     finally:
         backend.set_stream(0)
+
+
+@pytest.mark.parametrize("n_out,n_in", [(1000, 4096), (515, 14336), (259, 16384)])
+def test_noalloc_matches_the_cpu_oracle_and_leaves_device_memory_alone(n_out, n_in):
+    """Against the f64 product over the bit-exact dequantized weights (not against this library's other entry point),
+    with a ragged row count, up to the largest n_in the built-in scratch takes; from 14080 inputs on the kernel needs
+    more than the default 48 KB of shared memory. Free device memory, as the driver reports it, is the same before
+    and after two calls: nothing was allocated on the way (what the callers of this entry point rely on)."""
+    ref = synth.q4_k(n_out, n_in, 910 + n_out)
+    m = O.Matrix.gguf(O.Q4_K, ref.data, n_out, n_in)
+    w_dev = torch.from_numpy(ref.data).cuda()
+    xs = [synth.activations(1, n_in, 920 + i) for i in range(2)]
+    xd = [torch.from_numpy(x[0]).cuda() for x in xs]
+    got = [torch.full((n_out,), float("nan"), device="cuda") for _ in range(2)]
+    rc, msg = _call(w_dev, n_out, n_in, xd[0], got[0])   # the first call on a device does the one-time set-up
+    assert rc == ob.OK, msg
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for i in range(2):
+        rc, msg = _call(w_dev, n_out, n_in, xd[i], got[i])
+        assert rc == ob.OK, msg
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    for i in range(2):
+        want = m.matmul_f64(xs[i])
+        assert O.row_err(got[i].cpu().numpy()[None], want) < TOL
 
 
 def test_noalloc_refuses_sizes_beyond_its_scratch():
