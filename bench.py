@@ -9,11 +9,12 @@ activations M = 512 tokens x K = 4096 (bf16, N(0,1)), weights N = 14336 x K = 40
 (f16 d and dmin ~ |N(0, 0.01)|, uniform 6-bit scales / mins, uniform 4-bit quants), f32 output.
 One step = one pass of that matmul over the 512-token batch. Seeded synthetic data.
 
-On N > 1 GPUs the weight rows are sharded (tensor parallel, N / world rows per rank), every rank
-multiplies the same activations by its shard and keeps its columns of the output (what a row-parallel
-layer behind a sharded projection consumes; the cost of an NCCL all-gather of the full f32 output is timed
-apart and reported in `config.parallelism`): total work is fixed, so scaling is "strong". Timing is on the device (CUDA events on the launching stream,
-barrier + synchronize on both sides, max over ranks).
+On N > 1 GPUs the weight rows are sharded (tensor parallel, N / world rows per rank): every rank multiplies the same
+activations by its shard and the ranks then all-gather the output over NVLink (NCCL), both inside the timed step; total
+work is fixed, so scaling is "strong". Before timing, every rank checks that its shard's output equals the same rows of
+the unsharded product bit for bit (`config.parity`). Timing is on the device (CUDA events on the launching stream,
+barrier + synchronize on both sides, max over ranks); the block of --steps steps is repeated until the timed region
+holds at least 0.3 s of device time (`repeats`), and `ms_per_step` is the mean over all of them.
 
 Prints ONE JSON line on rank 0. `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the
 same metric through the host-buffer call of the C ABI (b2_matmul: pinned f32 x in, f32 y out, both
@@ -39,9 +40,24 @@ FLOP_PER_STEP = 2.0 * M_TOK * K_IN * N_OUT
 WORKLOAD = "gguf_q4_k_prefill_gemm M=512 K=4096 N=14336 (bf16 activations, f32 output)"
 METRIC = "prefill dequant-GEMM throughput (Q4_K, M=512 K=4096 N=14336)"
 L2_BYTES = 126 * 1024 * 1024
-# DRAM bytes of one gemm_q4k_tc_kernel launch at this shape, from the ncu capture summarised in
-# profiles/gemm_q4k_tc_M512_K4096_N14336.txt (37.26 MB read + 1.35 MB written; the f32 output stays in L2).
-GEMM_DRAM_TRAFFIC_BYTES = 37_259_520 + 1_354_496
+
+def profiled_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel, read from the ncu summary committed under
+    profiles/ (lines `dram__bytes_read.sum: N` / `dram__bytes_write.sum: N`, and `captured at: <commit>`); None when the
+    file or the fields are missing."""
+    import re
+
+    f = ROOT / "profiles" / name
+    if not f.exists():
+        return None, None
+    text = f.read_text()
+    r = re.search(r"dram__bytes_read\.sum:\s*([0-9][0-9,_]*)", text)
+    w = re.search(r"dram__bytes_write\.sum:\s*([0-9][0-9,_]*)", text)
+    c = re.search(r"captured at:\s*(\S+)", text)
+    if not r or not w:
+        return None, None
+    num = lambda m: int(m.group(1).replace(",", "").replace("_", ""))
+    return num(r) + num(w), (c.group(1) if c else None)
 
 
 def measured_peaks():
@@ -111,22 +127,29 @@ def cpu_prefill_tflops(threads: int, steps: int, warmup: int):
     return times
 
 
+def base_config(world: int) -> dict:
+    """The `config` both arms print (same keys, same values)."""
+    return {"workload": WORKLOAD,
+            "parallelism": f"tp{world}: weight rows sharded, NCCL all-gather of y inside the step" if world > 1 else "single GPU",
+            "l2": "inputs larger than L2: rotating over weight copies of more than twice the L2 size"}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
     from oracle import oracle as O
 
     threads = O.cpu_threads()
-    steps = max(1, min(args.steps, 10))
-    warm = max(1, min(args.warmup, 2))
+    steps, warm = max(1, args.steps), max(1, args.warmup)
     times = cpu_prefill_tflops(threads, steps, warm)
     ms = 1e3 * sum(times) / len(times)
     v = FLOP_PER_STEP / (ms * 1e-3) / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "path": "CPU: dequantize 8 rows + 8x8 f32 FMA tiles (oracle port of the reference's AVX2 prefill path)"},
-        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": "full workload per step"},
+        "config": base_config(args.gpus),
+        "path": "CPU: dequantize 8 rows + 8x8 f32 FMA tiles (oracle port of the reference's AVX2 prefill path, src/kernels.rs:1998-2038)",
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": "full workload (512 tokens x 14336 rows) per step"},
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -185,6 +208,46 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
         algo = wbytes + 4 * n_in + 4 * n_out
         out[name] = {"us_per_gemv": us, "bytes": algo, "gbs": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peaks["hbm_gbs"],
                      "launches_per_gemv": 1 if fmt == "f8_e4m3" else 2, "timing": timing}
+        traffic, commit = profiled_traffic(f"gemv_{name}.txt")
+        out[name]["roofline"] = {"kernel": "gemv_f8_mma_kernel" if fmt == "f8_e4m3" else "xplanes_kernel + gemv_kernel (one matrix-vector product)",
+                                 "bound": "hbm", "achieved": algo / us / 1e3, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": algo / us / 1e3 / peaks["hbm_gbs"], "frac_of_nominal_8000": algo / us / 1e3 / 8000.0, "traffic": traffic,
+                                 "traffic_unit": f"bytes per product, from profiles/gemv_{name}.txt" + (f" captured at {commit}" if commit else ""),
+                                 "bytes_per_launch": algo, "peak_source": f"copy bandwidth, {peaks['source']}"}
+        if name.startswith("mlx4") or name.startswith("q4_k"):
+            # the same product through the host-buffer call (Backend::matvec_rows): pinned x in, y out, synchronous
+            xh = torch.randn((1, n_in), dtype=torch.float32).pin_memory()
+            yh = torch.empty((1, n_out), dtype=torch.float32).pin_memory()
+            import oxinfer_b200 as ob
+
+            for i in range(3):
+                assert be.matvec_rows(xh.numpy(), [ob.RowsJob(devs[i % copies], yh.numpy())])
+            torch.cuda.synchronize()
+            ev[0].record()
+            for i in range(n):
+                be.matvec_rows(xh.numpy(), [ob.RowsJob(devs[i % copies], yh.numpy())])
+            ev[1].record()
+            torch.cuda.synchronize()
+            us_e = ev[0].elapsed_time(ev[1]) * 1e3 / n
+            out[name]["e2e"] = {"value": algo / us_e / 1e3, "unit": "GB/s", "us_per_gemv": us_e, "h2d_bytes_per_step": 4 * n_in, "d2h_bytes_per_step": 4 * n_out,
+                                "call": "b2_matvec_rows (Backend::matvec_rows): host f32 x in, f32 y out, synchronous"}
+            # the reference's CPU decode path for this product (int8 activations, oracle port), all host threads
+            try:
+                from oracle import oracle as O
+
+                m = O.matrix_of(ref, n_out, n_in)
+                xc = xh.numpy()
+                m.matmul_cpu(xc)
+                reps_c, t0 = 0, time.perf_counter()
+                while time.perf_counter() - t0 < 1.0:
+                    m.matmul_cpu(xc)
+                    reps_c += 1
+                us_c = (time.perf_counter() - t0) / reps_c * 1e6
+                out[name]["cpu_baseline"] = {"value": algo / us_c / 1e3, "unit": "GB/s", "cores": O.cpu_threads(), "kind": "port",
+                                             "sample": f"{reps_c} products in 1 s (one matrix: it stays in the CPU's cache, which favours the CPU)",
+                                             "path": O.decode_kernel_name()}
+            except Exception as e:
+                out[name]["cpu_baseline_error"] = str(e)
         # The GEMV kernel alone, over planes prepared once (what a decode plan sees when one vector feeds
         # several products): a second graph with n GEMV launches and no plane kernels.
         if use_graph and fmt != "f8_e4m3":
@@ -399,7 +462,8 @@ def fp8_extras(be, torch, peaks):
     return out
 
 
-def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0, rank=0, world=1, dist=None):
+def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, cpu_tokens=0, rank=0, world=1, dist=None, check_tokens=0,
+                  e2e_tokens=0):
     """Config 2: greedy decode tok/s of a Llama-style decoder (hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab
     128256; Q4_K body, Q6_K head, Q8_0 embeddings) after a `ctx`-token cache, batch 1, through the decode plan
     (one CUDA graph launch per token, embedding lookup and argmax on the device). Random-init weights; every layer
@@ -421,6 +485,7 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     dembed = be.upload(embed, cfg["vocab"], cfg["h"])
     lc = D.LlamaConfig(eps=1e-5, rope_theta=500000.0, rope_interleaved=True, **cfg)
     head_bytes = dhead.bytes()
+    full_layers = dev_layers
     if world > 1:   # tensor parallel: this rank's row shards, activations exchanged by peer stores
         dev_layers, dhead_r = D.shard_llama(be, dev_layers, dhead, lc, rank, world)
         g = D.llama_graph(lc, dev_layers, final_norm, dhead_r, rank, world)
@@ -438,15 +503,35 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     row = cfg["nkv"] * cfg["hd"]
     per = row // world
     kv_rows = []
+    # N > 1: rank 0 also holds the one-GPU plan over the unsharded weights (the shards are views into the same uploads) and
+    # decodes a few tokens with it from the same cache: the tensor-parallel plan must produce the same tokens
+    single = None
+    if world > 1 and check_tokens and rank == 0:
+        single = D.decode_plan(be, D.llama_graph(lc, full_layers, final_norm, dhead), ctx + check_tokens, kv_f16=kv_f16)
     for li in range(n_layers):   # the prefilled cache: unit-variance keys and values (a rank keeps its KV heads' columns)
         k = rng.standard_normal((ctx, row), dtype=np.float32)
         v = rng.standard_normal((ctx, row), dtype=np.float32)
         plan.kv_write(li, 0, np.ascontiguousarray(k[:, rank * per:(rank + 1) * per]), np.ascontiguousarray(v[:, rank * per:(rank + 1) * per]))
+        if single is not None:
+            single.kv_write(li, 0, k, v)
         if cpu_tokens and li == 0:
             kv_rows = [k, v]
     inv_freq = D.rope_inv_freq(cfg["hd"], lc.rope_theta)
     table = np.stack([D.rope_table(ctx + i, inv_freq) for i in range(n_tokens)])
-    plan.generate(dembed, 1, ctx, min(8, n_tokens), table[: min(8, n_tokens)])    # warm-up (captures the graph)
+    warm_toks, _ = plan.generate(dembed, 1, ctx, min(8, n_tokens), table[: min(8, n_tokens)])    # warm-up (captures the graph)
+    parity = None
+    if world > 1 and check_tokens:
+        nchk = min(check_tokens, 8, n_tokens)
+        flag = 1
+        if single is not None:
+            ref_toks, _ = single.generate(dembed, 1, ctx, nchk, table[:nchk])
+            flag = int(np.array_equal(ref_toks[:nchk], warm_toks[:nchk]))
+            single.close()
+        import torch
+
+        ft = torch.tensor([flag], device="cuda", dtype=torch.int32)
+        dist.all_reduce(ft, op=dist.ReduceOp.MIN)
+        parity = f"first {nchk} greedy tokens equal the one-GPU plan's" if int(ft.item()) == 1 else "TOKEN MISMATCH against the one-GPU plan"
     times = []
     for _ in range(3):
         if world > 1:
@@ -469,6 +554,28 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
            "bytes_per_token": int(algo), "gbs": algo / (ms / n_tokens * 1e-3) / 1e9,
            "frac_of_hbm_peak": algo / (ms / n_tokens * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
            "distinct_tokens": int(len(set(toks.tolist()))), "timing": "CUDA events around the token loop, median of 3"}
+    if parity is not None:
+        out["parity"] = parity
+    gbs = algo / (ms / n_tokens * 1e-3) / 1e9
+    out["roofline"] = {"kernel": "one decode token: the plan's whole launch list (products, attention, norms)", "bound": "hbm", "achieved": gbs,
+                       "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
+                       "frac_of_nominal_8000": gbs / (8000.0 * world), "traffic": None, "bytes_per_launch": int(algo),
+                       "peak_source": f"copy bandwidth, {peaks['source']}"}
+    if e2e_tokens and world == 1:
+        # end to end through DecodePlan::step (b2_plan_step): per token the host hands over x and the RoPE row and reads the
+        # hidden state and all logits back, takes the argmax and looks the next row up in a host table (as the reference's
+        # generate loop does between steps, src/generate.rs)
+        xs = np.random.default_rng(11).standard_normal((64, cfg["h"])).astype(np.float32)
+        tok = 1
+        plan.step(ctx, xs[0], table[0])
+        t0 = time.perf_counter()
+        for i in range(e2e_tokens):
+            _, logits = plan.step(ctx + i, xs[tok % 64], table[i])
+            tok = int(np.argmax(logits))
+        dt = time.perf_counter() - t0
+        out["e2e"] = {"value": e2e_tokens / dt, "unit": "tok/s", "tokens": e2e_tokens,
+                      "h2d_bytes_per_step": int(4 * (cfg["h"] + table.shape[1])), "d2h_bytes_per_step": int(4 * (cfg["h"] + cfg["vocab"])),
+                      "call": "b2_plan_step (DecodePlan::step): host x and RoPE row in, hidden + logits out, argmax on the host"}
     if cpu_tokens:
         # the reference's CPU decode path (oracle port) on the same model: a few tokens at the same context
         from oracle import oracle as O
@@ -504,10 +611,6 @@ def run_b200(args, rank, world, local_rank):
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
-    if world > 1:
-        # Row shards fill half the SMs or less: K runs in two halves per tile (see gemm_tc_plan_create). The shards' rows then
-        # differ from the one-GPU rows by f32 reassociation (the default, unsplit, keeps them bit-identical).
-        os.environ.setdefault("B2_GEMM_SPLIT_K", "2")
     be = ob.Backend(local_rank)
     stream = torch.cuda.current_stream()
     be.set_stream(stream.cuda_stream)
@@ -523,7 +626,8 @@ def run_b200(args, rank, world, local_rank):
         emit(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}))
         return
     if args.section == "decode":
-        d = decode_extras(be, peaks, args.tokens, args.context, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None)
+        d = decode_extras(be, peaks, args.tokens, args.context, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None,
+                          check_tokens=8 if world > 1 else 0, e2e_tokens=32 if world == 1 else 0)
         if rank == 0:
             emit(json.dumps({"extra": {"decode": d}}))
         if world > 1:
@@ -532,7 +636,9 @@ def run_b200(args, rank, world, local_rank):
         return
     assert N_OUT % world == 0
     n_local = N_OUT // world
-    ref = synth.q4_k(n_local, K_IN, 1 + rank)
+    full = synth.q4_k(N_OUT, K_IN, 1)        # the same matrix on every rank; a rank multiplies by its rows
+    row_bytes = K_IN // 256 * 144
+    ref = ob.Gguf(ob.FMT_Q4_K, np.ascontiguousarray(full.data[rank * n_local * row_bytes:(rank + 1) * n_local * row_bytes]))
     shard_bytes = ref.data.size
     copies = max(8, -(-2 * L2_BYTES // shard_bytes))  # rotate through > 2 x L2 of weights: every step streams from HBM
     devs = [be.upload(ref, n_local, K_IN) for _ in range(copies)]
@@ -543,10 +649,30 @@ def run_b200(args, rank, world, local_rank):
     ys = [torch.empty((M_TOK, n_local), device="cuda", dtype=torch.float32) for _ in range(ycopies)]
     y_full = torch.empty((world, M_TOK, n_local), device="cuda", dtype=torch.float32) if world > 1 else None
 
-    def step(i):
+    # ---- N > 1: before anything is timed, this rank's shard against the same rows of the unsharded product ----
+    parity = None
+    if world > 1:
+        dfull = be.upload(full, N_OUT, K_IN)
+        y_all = torch.empty((M_TOK, N_OUT), device="cuda", dtype=torch.float32)
+        assert be.matmul_dev(dfull, x_bf16, y_all) and be.matmul_dev(devs[0], x_bf16, ys[0])
+        torch.cuda.synchronize()
+        be.check_status()
+        same = torch.equal(y_all[:, rank * n_local:(rank + 1) * n_local].contiguous().view(torch.int32), ys[0].view(torch.int32))
+        dist.all_gather_into_tensor(y_full, ys[0])
+        torch.cuda.synchronize()
+        same = same and torch.equal(y_full.permute(1, 0, 2).reshape(M_TOK, N_OUT).view(torch.int32), y_all.view(torch.int32))
+        flag = torch.tensor([1 if same else 0], device="cuda", dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = "bit-identical" if int(flag.item()) == 1 else "MISMATCH"
+        dfull.free()
+        del y_all
+
+    def step(i, gather=True):
         y = ys[i % ycopies]
         ok = be.matmul_dev(devs[i % copies], x_bf16, y)
         assert ok
+        if world > 1 and gather:
+            dist.all_gather_into_tensor(y_full, y)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -554,40 +680,38 @@ def run_b200(args, rank, world, local_rank):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for i in range(max(3, args.warmup)):
+    def timed(n, gather=True):
+        """Device milliseconds of n steps, barrier + synchronize on both sides."""
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            step(i, gather)
+        b.record()
+        sync_all()
+        return a.elapsed_time(b)
+
+    warm = max(3, args.warmup)
+    for i in range(warm):
         step(i)
     sync_all()
     be.check_status()
+    # how many times the block of --steps steps must repeat for the timed region to hold 0.3 s of device time
+    est_ms = timed(args.steps) / args.steps
+    repeats = torch.tensor([max(1, int(-(-args.min_time_ms // (est_ms * args.steps))))], device="cuda", dtype=torch.int32)
+    if world > 1:
+        dist.all_reduce(repeats, op=dist.ReduceOp.MAX)
+    repeats = int(repeats.item())
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
-    sync_all()
     launches0 = be.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    sync_all()
-    ms_total = e0.elapsed_time(e1)
-    launches = be.launch_count() - launches0
+    ms_total = timed(args.steps * repeats)
+    launches = (be.launch_count() - launches0) // repeats
     be.check_status()
-    # N > 1: y stays sharded by rows of W (columns of y) on the ranks, the way the row-parallel layer that follows a
-    # sharded projection consumes it. What a full copy of y on every rank would cost (NCCL all-gather) is timed apart.
-    gather_ms = None
-    if world > 1:
-        for _ in range(2):
-            dist.all_gather_into_tensor(y_full, ys[0])
-        sync_all()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(5):
-            dist.all_gather_into_tensor(y_full, ys[0])
-        g1.record()
-        sync_all()
-        gather_ms = g0.elapsed_time(g1) / 5
+    ms_compute = timed(args.steps * repeats, gather=False) if world > 1 else ms_total
 
     # ---- the GEMM kernel alone (f16 activations are used in place: one launch per call) ----
     n_k = max(args.steps, 20)
@@ -620,42 +744,51 @@ def run_b200(args, rank, world, local_rank):
     e2e_ms_total = e2.elapsed_time(e3)
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms_total, e2e_ms_total, kern_ms], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms_total, e2e_ms_total, kern_ms, ms_compute], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total, kern_ms = (float(v) for v in t.cpu())
+    ms_total, e2e_ms_total, kern_ms, ms_compute = (float(v) for v in t.cpu())
 
     dec_tp = None
     if world > 1 and args.section == "all":   # collective: every rank runs the tensor-parallel decode plan
         try:
-            dec_tp = decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist)
+            dec_tp = decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist, check_tokens=8)
         except Exception as e:
             dec_tp = {"error": str(e)}
     if rank == 0:
-        ms = ms_total / args.steps
+        n_timed = args.steps * repeats
+        ms = ms_total / n_timed
         value = FLOP_PER_STEP / (ms * 1e-3) / 1e12
         e2e_ms = e2e_ms_total / e2e_steps
         kern_flop = FLOP_PER_STEP / world
         achieved = kern_flop / (kern_ms * 1e-3) / 1e12
+        traffic, traffic_commit = profiled_traffic("gemm_q4k_tc_M512_K4096_N14336.txt") if world == 1 else (None, None)
+        cfg = base_config(world)
+        if parity is not None:
+            cfg["parity"] = parity
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD, "split_k": int(os.environ.get("B2_GEMM_SPLIT_K", "1")) if world > 1 else 1,
-                       "parallelism": (f"tp{world}: weight rows sharded, y stays sharded by columns on the ranks; an NCCL all-gather of the f32 y "
-                                       f"({M_TOK * N_OUT * 4 / 1e6:.0f} MB) measured apart takes {gather_ms:.3f} ms") if world > 1 else "single GPU",
-                       "l2": f"inputs larger than L2: rotating over {copies} weight copies ({copies * shard_bytes / 1e6:.0f} MB) and {ycopies} outputs",
-                       "step": "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel" + (" on this rank's rows" if world > 1 else "")},
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "repeats": repeats,
+            "timed_region_ms": ms_total, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 operands, f32 accumulate", "data": "synthetic", "config": cfg,
+            "step": ("x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel on this rank's rows + NCCL all-gather of the f32 y "
+                     f"({M_TOK * N_OUT * 4 / 1e6:.0f} MB) into rank-major blocks" if world > 1 else
+                     "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel"),
+            "inputs": f"{copies} weight copies ({copies * shard_bytes / 1e6:.0f} MB) and {ycopies} outputs in rotation",
             "e2e": {"value": FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(xh.numel() * 4), "d2h_bytes_per_step": int(yh.numel() * 4) * world,
                     "call": "b2_matmul (Backend::matmul): pinned host f32 x in, f32 y out, synchronous"},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"kernel": "gemm_q4k_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": GEMM_DRAM_TRAFFIC_BYTES / world if world == 1 else None,
-                         "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture of this kernel at this shape)", "us_per_launch": kern_ms * 1e3,
-                         "flop_per_launch": kern_flop, "peak_source": f"bf16 burst, {peaks['source']}"},
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": traffic,
+                         "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) read from profiles/gemm_q4k_tc_M512_K4096_N14336.txt"
+                                         + (f", captured at {traffic_commit}" if traffic_commit else ""),
+                         "us_per_launch": kern_ms * 1e3, "flop_per_launch": kern_flop, "peak_source": f"bf16 burst, {peaks['source']}"},
         }
+        if world > 1:
+            ms_c = ms_compute / n_timed
+            line["compute_only"] = {"value": FLOP_PER_STEP / (ms_c * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_c,
+                                    "note": "the same steps without the all-gather (y left sharded by columns on the ranks)"}
         if world == 1 and args.section == "all":
             from oracle import oracle as O
 
@@ -663,22 +796,49 @@ def run_b200(args, rank, world, local_rank):
             times = cpu_prefill_tflops(threads, 2, 1)
             line["cpu_baseline"] = {"value": FLOP_PER_STEP / min(times) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": "full workload (512 tokens x 14336 rows), best of 2 after 1 warm-up"}
-            try:
-                line["extra"] = {"gemv": gemv_extras(be, torch, peaks, 40)}
-            except Exception as e:  # the headline line must still print
-                line["extra"] = {"gemv_error": str(e)}
-            for name, fn in (("moe", lambda: moe_extras(be, torch, peaks)), ("fp8", lambda: fp8_extras(be, torch, peaks)),
-                             ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2)), ("reference_cuda", lambda: ref_cuda_extras(be, torch))):
+            line["extra"] = {}
+            for name, fn in (("gemv", lambda: gemv_extras(be, torch, peaks, 40)), ("moe", lambda: moe_extras(be, torch, peaks)),
+                             ("fp8", lambda: fp8_extras(be, torch, peaks)), ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2, e2e_tokens=32)),
+                             ("reference_cuda", lambda: ref_cuda_extras(be, torch))):
                 try:
                     line["extra"][name] = fn()
-                except Exception as e:
+                except Exception as e:  # the headline line must still print
                     line["extra"][name + "_error"] = str(e)
         if dec_tp is not None:
             line["extra"] = {"decode": dec_tp}
+        line["summary"] = summarize(line)
         emit(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def summarize(line: dict) -> dict:
+    """The three parts of the metric in a few numbers, printed last so that the end of the line shows them."""
+    out = {"gemm_tflops": round(line["value"], 1), "gemm_kernel_frac_of_bf16_peak": round(line["roofline"]["frac"], 3),
+           "gemm_e2e_tflops": round(line["e2e"]["value"], 1)}
+    ex = line.get("extra") or {}
+    g = ex.get("gemv") or {}
+    for key, short in (("mlx4_4096x4096", "gemv_cfg0_mlx4"), ("q4_k_14336x4096", "gemv_q4_k"), ("q6_k_32064x4096", "gemv_q6_k")):
+        if key in g and "roofline" in g[key]:
+            out[short + "_gbs"] = round(g[key]["roofline"]["achieved"], 0)
+            out[short + "_frac_of_hbm"] = round(g[key]["roofline"]["frac"], 3)
+    d = ex.get("decode") or {}
+    if "tok_s" in d:
+        out["decode_tok_s"] = round(d["tok_s"], 1)
+        out["decode_frac_of_hbm"] = round(d["frac_of_hbm_peak"], 3)
+        if "e2e" in d:
+            out["decode_e2e_tok_s"] = round(d["e2e"]["value"], 1)
+        if "parity" in d:
+            out["decode_parity"] = d["parity"]
+    m = ex.get("moe") or {}
+    for k in ("t1", "t64", "t512", "t4096"):
+        if k in m:
+            out["moe_" + k + "_us"] = round(m[k]["us"], 1)
+    f = ex.get("fp8") or {}
+    if "m8192" in f:
+        out["fp8_m8192_tflops"] = round(f["m8192"]["tflops"], 0)
+    return out
 
 
 _OUT = None
@@ -708,6 +868,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--min-time-ms", type=float, default=300.0,
+                    help="the block of --steps steps is repeated until the timed region holds this much device time (power / clock steady state)")
     ap.add_argument("--context", type=int, default=2048, help="with --section decode: tokens in the KV cache before the first decoded token")
     ap.add_argument("--case", default=None, help="with --section gemv: only the cases whose name contains this text")
     ap.add_argument("--no-graph", action="store_true", help="with --section gemv: host-launched kernels instead of a CUDA graph (profiling)")

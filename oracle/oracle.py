@@ -209,6 +209,19 @@ class Matrix:
         return y
 
 
+def matrix_of(ref, n_out: int, n_in: int) -> Matrix:
+    """The oracle's matrix for a synthetic weight reference: an MLX triple (fields ``w scales biases group``) or raw GGUF
+    rows (fields ``kind data block_scales bs_rows bs_cols``)."""
+    if hasattr(ref, "w"):
+        return Matrix.from_mlx_q4(ref.w.reshape(-1), ref.scales.reshape(-1), ref.biases.reshape(-1), n_out, n_in, ref.group)
+    return Matrix.gguf(ref.kind, ref.data, n_out, n_in, ref.block_scales, ref.bs_rows, ref.bs_cols)
+
+
+def decode_kernel_name() -> str:
+    """Which restatement of the reference's int8-activation decode kernels ``matmul_cpu`` runs at up to 7 rows."""
+    return "scalar restatement of the int8-activation decode kernels (src/kernels_x86.rs:476-536, src/kernels_ggml_x86.rs:389-431)"
+
+
 def mlx_dequant_row(w: np.ndarray, scales: np.ndarray, biases: np.ndarray, group: int, n: int) -> np.ndarray:
     out = np.zeros(n, dtype=np.float32)
     lib().orc_mlx_dequant_row(_p(w), _p(scales), _p(biases), group, _p(out), n)

@@ -829,13 +829,15 @@ class Backend {
             const char* e = getenv("B2_MOE_TILE");
             return e ? atoi(e) : 0;
         }();
-        // Q4_K experts always take the 128-row tile: with it the activations of both projections go in as two f16 terms (22
-        // bits), which the 256-row tile has no room for, and Q4_K values round harder to f16 than MLX-4's: the two roundings
-        // together leave the layer above 1e-3 per output row.
-        const size_t TILE = force_tile == 128 || force_tile == 256 ? (size_t)force_tile
-                            : (m.fmt != B2_FMT_Q4_K && tiles256 * 10 <= tiles128 * 8) ? 256 : 128;
+        // Two-term operands (activations of both projections as two f16 terms, Q4_K weights as two f16 terms) need the
+        // 128-row tile. Q4_K experts always take them: Q4_K values round harder to f16 than MLX-4's, and one-term operands
+        // through two chained projections leave that layer above 1e-3 per output row (MLX-4 stays near 3e-4 with one term).
+        const bool two_term = m.fmt == B2_FMT_Q4_K || exact;
+        const size_t TILE = two_term ? 128
+                            : force_tile == 128 || force_tile == 256 ? (size_t)force_tile
+                            : tiles256 * 10 <= tiles128 * 8 ? 256 : 128;
         const int m_halves = (int)(TILE / 128);
-        const size_t lo_row0 = TILE == 128 ? rows_for(count, 128) : 0;  // two-term activations with the 128-row tile
+        const size_t lo_row0 = two_term ? rows_for(count, 128) : 0;
         std::vector<size_t> off(m.experts, 0);
         std::vector<int32_t> tile_expert;
         size_t rows = 0;

@@ -162,12 +162,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
-template <int FMT, bool SPLIT>
+// TT: the instantiation that takes two-term operands (a_lo_row_arg, w_terms); the one-term kernel carries none of that code.
+template <int FMT, bool SPLIT, bool TT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
                    int tile_n, int m_halves, void* __restrict__ y, int y_dtype_arg, GemmStatus* __restrict__ status, int dbg_arg,
-                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits, const float* __restrict__ row_unscale, int a_lo_row0, int w_terms) {
+                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits, const float* __restrict__ row_unscale, int a_lo_row_arg, int w_terms) {
+    const int a_lo_row0 = TT ? a_lo_row_arg : 0;
     // The timing switches (see debug_switches below) exist only in builds made with -DB2_DEBUG: a production library
     // must not change its results because of an environment variable.
 #ifdef B2_DEBUG
@@ -208,7 +210,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // the stage and lo (what the rounding of hi left of the exact f32 value) in rows 128 .. 128 + tile_n - 1; both are
     // multiplied by the activations into the same accumulator. In each dequantizer set warps 0..3 then write the hi terms of
     // rows 0..127 and warps 4..7 the lo terms of the same rows.
-    const bool w2 = w_terms == 2;
+    const bool w2 = TT && w_terms == 2;
     const int row_warps = (tile_n + 31) / 32;
     const int set_warps = w2 ? 2 * row_warps : row_warps;  // live warps in each of the two dequantizer sets
 
@@ -862,22 +864,24 @@ bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
                            cudaStream_t st, const float* row_unscale) {
-    {
-        const void* kerns[6] = {(const void*)gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>,   (const void*)gemm_q4k_tc_kernel<B2_FMT_MLX4, false>,
-                                (const void*)gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>, (const void*)gemm_q4k_tc_kernel<B2_FMT_Q4_K, true>,
-                                (const void*)gemm_q4k_tc_kernel<B2_FMT_MLX4, true>,    (const void*)gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true>};
-        for (const void* k : kerns)
-            if (cudaError_t e = ensure_dynamic_smem(k, GEMM_SMEM); e != cudaSuccess) return e;
-    }
+    const bool split = p->k_splits > 1;
+    const bool tt = p->a_lo_row0 > 0 || p->w_terms == 2;
+    using Kern = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, void*, int, GemmStatus*, int, const int*, F8Scales, int, const float*,
+                          int, int);
+    Kern kern;
+    if (tt)  // two-term operands never come with a K split
+        kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4, false, true>
+               : w.fmt == B2_FMT_F8E4M3 ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, true>;
+    else
+        kern = w.fmt == B2_FMT_MLX4     ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true, false> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false>)
+               : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true, false> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false, false>)
+                                        : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true, false> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, false>);
+    if (cudaError_t e = ensure_dynamic_smem((const void*)kern, GEMM_SMEM); e != cudaSuccess) return e;
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles, (unsigned)p->k_splits);
     if (p->k_splits > 1) {  // the shares are added into y
         cudaError_t e = cudaMemsetAsync(y, 0, t * w.n_out * sizeof(float), st);
         if (e != cudaSuccess) return e;
     }
-    const bool split = p->k_splits > 1;
-    auto kern = w.fmt == B2_FMT_MLX4     ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false>)
-                : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false>)
-                                         : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false>);
     F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype | (p->y_direct ? 0x100 : 0),
                                                 status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms);
