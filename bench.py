@@ -458,6 +458,53 @@ def fp8_extras(be, torch, peaks):
         out[f"m{t}"] = {"us": us, "tflops": flop / us / 1e6, "frac_of_bf16_peak": flop / us / 1e6 / peaks["bf16_tflops"],
                         "weight_gbs": n_out * n_in / us / 1e3, "frac_of_hbm_peak": n_out * n_in / us / 1e3 / peaks["hbm_gbs"]}
         del xd, y
+    # ---- FP8 on both sides (b2_set_fp8_activations): activations quantized per token and per 128 k to e4m3, tcgen05 kind::f8f6f4,
+    # bf16 output, as the configuration states it. The FP8 peak is measured here: an 8192^3 e4m3 x e4m3 torch._scaled_mm.
+    try:
+        a8 = torch.randn((8192, 8192), device="cuda").to(torch.float8_e4m3fn)
+        b8 = torch.randn((8192, 8192), device="cuda").to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device="cuda")
+        for _ in range(3):
+            torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        best = 1e9
+        for _ in range(10):
+            e0.record()
+            torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        fp8_peak = 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+        del a8, b8
+    except Exception as e:   # no FP8 library GEMM in this torch: twice the bf16 figure as a labelled stand-in
+        fp8_peak = None
+        out["fp8_peak_error"] = str(e)
+    out["fp8_peak_tflops"] = fp8_peak
+    out["fp8_peak_source"] = "torch._scaled_mm 8192^3 e4m3 x e4m3, best of 10, measured in this run" if fp8_peak else "2 x the measured bf16 burst (stand-in)"
+    peak8 = fp8_peak or 2.0 * peaks["bf16_tflops"]
+    be.set_fp8_activations(True)
+    try:
+        for t in (128, 8192):
+            xd = torch.randn((t, n_in), device="cuda", dtype=torch.bfloat16)
+            y = torch.empty((t, n_out), device="cuda", dtype=torch.bfloat16)
+            for _ in range(2):
+                be.matmul_dev(dev, xd, y)
+            torch.cuda.synchronize()
+            be.check_status()
+            n = 5
+            e0.record()
+            for _ in range(n):
+                be.matmul_dev(dev, xd, y)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / n
+            flop = 2.0 * t * n_in * n_out
+            out[f"w8a8_m{t}"] = {"us": us, "tflops": flop / us / 1e6, "frac_of_fp8_peak": flop / us / 1e6 / peak8,
+                                 "frac_of_bf16_peak": flop / us / 1e6 / peaks["bf16_tflops"], "weight_gbs": n_out * n_in / us / 1e3,
+                                 "frac_of_hbm_peak": n_out * n_in / us / 1e3 / peaks["hbm_gbs"],
+                                 "kernels": "quantize_act_e4m3_kernel + gemm_f8_tc_kernel (tcgen05 kind::f8f6f4), bf16 output"}
+            del xd, y
+    finally:
+        be.set_fp8_activations(False)
     dev.free()
     return out
 
@@ -838,6 +885,9 @@ def summarize(line: dict) -> dict:
     f = ex.get("fp8") or {}
     if "m8192" in f:
         out["fp8_m8192_tflops"] = round(f["m8192"]["tflops"], 0)
+    if "w8a8_m8192" in f:
+        out["fp8_w8a8_m8192_tflops"] = round(f["w8a8_m8192"]["tflops"], 0)
+        out["fp8_w8a8_m8192_frac_of_fp8_peak"] = round(f["w8a8_m8192"]["frac_of_fp8_peak"], 3)
     return out
 
 

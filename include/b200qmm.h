@@ -101,6 +101,14 @@ int b2_set_chained(b2_ctx* ctx, int on);
  * results within 1e-4 per output row, the bound the reference holds its own f32 CUDA kernels to (src/cuda.rs:1684), at two to
  * four times the tensor-core work. Matrix-vector products (t <= 8) carry 21-bit activations either way. */
 int b2_set_exact(b2_ctx* ctx, int on);
+/* No counterpart in the reference, whose FP8 matrices multiply unquantized activations (src/ggml.rs:433-443; that stays the
+ * default here and is what the 2e-3 parity bound refers to). On: b2_matmul / b2_matmul_dev over F8E4M3 weights with 128 x 128
+ * scale blocks quantize the activations per token and per 128 k to e4m3 (scale = amax / 448, round to nearest even) and run
+ * FP8 x FP8 on the tensor cores (tcgen05 kind::f8f6f4), every 128-k partial sum scaled by both scales and added in f32: the
+ * large-projection form in which both operands stay 8 bits wide. The result equals the f64 product of the dequantized
+ * weights with the DEQUANTIZED quantized activations to about 1e-6 per row; against unquantized activations it carries
+ * e4m3's quantization noise (about 2e-2 per row). b2_set_exact takes precedence. */
+int b2_set_fp8_activations(b2_ctx* ctx, int on);
 /* `Backend::stats`, src/cuda.rs:1120-1132: cumulative copy-in / kernel / copy-out time as text. */
 const char* b2_stats(b2_ctx* ctx);
 /* Count of kernel launches issued by this context since it was opened. */

@@ -182,6 +182,10 @@ class Backend:
         """``gpu::set_exact`` (``src/gpu.rs:313-338``): many-token matmuls with two-term f16 operands, within 1e-4 per row."""
         self._check(self._L.b2_set_exact(self._ctx, int(on)))
 
+    def set_fp8_activations(self, on: bool) -> None:
+        """FP8 weights x FP8 activations (``b2_set_fp8_activations``): activations quantized per token and per 128 k to e4m3."""
+        self._check(self._L.b2_set_fp8_activations(self._ctx, int(on)))
+
     def check_status(self) -> None:
         self._check(self._L.b2_check_status(self._ctx))
 

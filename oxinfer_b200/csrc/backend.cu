@@ -61,6 +61,7 @@ class Backend {
     cudaStream_t stream = nullptr;
     bool chained = false;  // b2_set_chained
     bool exact = false;    // b2_set_exact
+    bool fp8_act = false;  // b2_set_fp8_activations
     std::mutex mu;  // calls serialize, like the staging lock of src/cuda.rs:430,1443
     std::string err;
     std::string stats_text;
@@ -71,7 +72,7 @@ class Backend {
     uint64_t next_handle = 1;
     uint64_t launches = 0;
     // staging for the host-buffer entry points
-    Scratch x_dev, y_dev, x16, xplanes, pair_tmp;
+    Scratch x_dev, y_dev, x16, x8, xplanes, pair_tmp;
     GemmStatus* gemm_status = nullptr;  // device
     // cached tensor maps of the tensor-core GEMM (see matmul_dev)
     std::vector<GemmPlan*> plans;
@@ -440,7 +441,7 @@ class Backend {
         if (t == 0) return B2_OK;
         if (y_dtype != B2_F32 && y_dtype != B2_BF16) return fail(B2_ERR_ARG, "[b200qmm: matmul: y must be f32 or bf16]");
         size_t K = w->dev.n_in;
-        if (t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev)) {
+        if (t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev) && !(fp8_act && w->dev.fmt == B2_FMT_F8E4M3)) {
             for (size_t i = 0; i < t; i++) {
                 int rc = matvec_dev(h, 0, (const float*)x + i * K, (float*)y + i * w->dev.n_out, B2_MODE_STORE, nullptr);
                 if (rc) return rc;
@@ -475,6 +476,24 @@ class Backend {
                     if (e != cudaSuccess) return cuda_fail(e, "gemv");
                 }
             }
+            return B2_OK;
+        }
+        if (fp8_act && !exact && gemm_f8_supports(w->dev, t)) {
+            // FP8 on both sides: the activations are quantized per token and per 128 k to e4m3, and the tensor cores multiply
+            // e4m3 by e4m3 (kind::f8f6f4); partial sums of every 128 k are scaled by both scales and added in f32
+            int rc8 = ensure_status();
+            if (rc8) return rc8;
+            cudaError_t e8 = x8.reserve(gemm_f8_scratch_bytes(t, K));
+            if (e8 != cudaSuccess) return cuda_fail(e8, "cudaMalloc(x8)");
+            uint8_t* q = (uint8_t*)x8.p;
+            float* sx = (float*)(q + (t * K + 255) / 256 * 256);
+            e8 = launch_quantize_act_e4m3(x, x_dtype, t, K, q, sx, stream);
+            launches++;
+            if (e8 != cudaSuccess) return cuda_fail(e8, "quantize_act_e4m3");
+            char msg[256] = {0};
+            e8 = launch_gemm_f8(w->dev, q, sx, t, y, y_dtype, gemm_status, stream, msg, sizeof msg);
+            launches++;
+            if (e8 != cudaSuccess) return msg[0] ? fail(B2_ERR_CUDA, "[b200qmm: %s]", msg) : cuda_fail(e8, "gemm_f8");
             return B2_OK;
         }
         if (!gemm_tc_supports(w->dev, t)) return fail(B2_DECLINED, "[b200qmm: matmul: no tensor-core kernel for this format / shape]");
@@ -1032,6 +1051,7 @@ class Backend {
         x_dev.release();
         y_dev.release();
         x16.release();
+        x8.release();
         xplanes.release();
         pair_tmp.release();
         if (gemm_status) cudaFree(gemm_status);
@@ -1118,6 +1138,12 @@ B2_EXPORT int b2_set_chained(b2_ctx* ctx, int on) {
 B2_EXPORT int b2_set_exact(b2_ctx* ctx, int on) {
     LOCKED(ctx);
     ctx->be.exact = on != 0;
+    return B2_OK;
+}
+
+B2_EXPORT int b2_set_fp8_activations(b2_ctx* ctx, int on) {
+    LOCKED(ctx);
+    ctx->be.fp8_act = on != 0;
     return B2_OK;
 }
 

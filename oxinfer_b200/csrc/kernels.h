@@ -174,6 +174,18 @@ cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* 
 // Whether nt (1..4) token rows' vectors fit in shared memory together for launch_gemv_multi.
 bool gemv_multi_fits(const WeightDev& w, int nt);
 
+// ---- gemm_f8.cu: FP8 weights x FP8 activations (tcgen05 kind::f8f6f4), 128 x 128 weight scale blocks, activations quantized
+// per token and per 128 k -----------------------------------------------------------------------------------------------
+bool gemm_f8_supports(const WeightDev& w, size_t t);
+// Bytes of scratch for t rows of K: the e4m3 activations [t][K], then (256-byte aligned) their scales f32 [t][K / 128].
+size_t gemm_f8_scratch_bytes(size_t t, size_t K);
+// x (f32 / bf16 / f16, [t][K]) -> q e4m3 [t][K] and sx f32 [t][K / 128]: scale = amax / 448 per block of 128 (1 for a zero
+// block), q = RNE(x / scale) saturating at +-448.
+cudaError_t launch_quantize_act_e4m3(const void* x, int x_dtype, size_t t, size_t K, uint8_t* q, float* sx, cudaStream_t st);
+// y[t][n_out] (f32 or bf16) = sum over 128-k blocks of sx * sw * (qx . qw).
+cudaError_t launch_gemm_f8(const WeightDev& w, const uint8_t* qx, const float* sx, size_t t, void* y, int y_dtype, GemmStatus* status_dev,
+                           cudaStream_t st, char* err, size_t errlen);
+
 // ---- moe.cu: the element-wise pieces of the routed-expert layer ------------------------------------
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st);
 // Rows to f16 operands for the grouped GEMM, each multiplied by a power of two (its largest magnitude into [2^14, 2^15));
