@@ -410,6 +410,42 @@ def moe_extras(be, torch, peaks):
         out[f"t{t}"] = {"us": us, "tflops": flop / us / 1e6, "experts_touched": int(len(np.unique(ids))), "weight_gbs": touched / us / 1e3,
                         "frac_of_hbm_peak": touched / us / 1e3 / peaks["hbm_gbs"], "frac_of_bf16_peak": flop / us / 1e6 / peaks["bf16_tflops"]}
     out["note"] = "b2_moe_dev per call: host segment building + gather, grouped tensor-core GEMM (gate_up), SiLU, grouped GEMM (down), combine"
+    # The reference's own CUDA kernels for the same layer on the same device (moe_gather, a gemm_q4a per touched expert and
+    # projection, moe_act, moe_combine: the launch sequence of CudaBackend::moe_run, src/cuda.rs:798-966), device time only
+    # (its host-side segment building and its three PCIe copies per call are left out, which favours it).
+    try:
+        from oracle import oracle as O
+
+        L = O.ref_cuda()
+        if L is None:
+            out["reference_cuda"] = {"unavailable": "oracle/_ref/libref_cuda.so was not built"}
+        else:
+            pm = [(O.matrix_of(g, 2 * I, H), O.matrix_of(d, H, I)) for g, d in protos]
+            rm = O.RefMoe([pm[e % 8][0] for e in range(E)], [pm[e % 8][1] for e in range(E)], H, I)
+            refs = {}
+            rng = np.random.default_rng(3)
+            bias = rng.standard_normal(E).astype(np.float32)
+            for t in (1, 64, 512, 4096):
+                logits = rng.standard_normal((t, E)).astype(np.float32) + bias
+                ids = np.argsort(-logits, axis=1, kind="stable")[:, :K].astype(np.int32)
+                top = np.take_along_axis(logits, ids, axis=1)
+                w = np.exp(top - top[:, :1])
+                w = (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
+                x = torch.randn((t, H), device="cuda", dtype=torch.float32)
+                y_ref = torch.zeros((t, H), device="cuda", dtype=torch.float32)
+                O.ref_moe_q4a(L, rm, x, ids, w, y_ref, iters=0)
+                y = torch.zeros((t, H), device="cuda", dtype=torch.float32)
+                be.moe_dev(x, ids, w, moe, y)
+                torch.cuda.synchronize()
+                diff = float((y - y_ref).abs().max() / y_ref.abs().max())
+                scratch = torch.zeros((t, H), device="cuda", dtype=torch.float32)
+                ms = O.ref_moe_q4a(L, rm, x, ids, w, scratch, iters=3 if t >= 512 else 10)
+                refs[f"t{t}"] = {"reference_us": ms * 1e3, "this_us": out[f"t{t}"]["us"], "speedup": ms * 1e3 / out[f"t{t}"]["us"],
+                                 "max_abs_difference_over_max": diff}
+            refs["note"] = "same routing distribution and experts; the reference sequence is 2 + 2 x (touched experts) + 1 launches per layer"
+            out["reference_cuda"] = refs
+    except Exception as e:
+        out["reference_cuda_error"] = str(e)
     return out
 
 

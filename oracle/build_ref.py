@@ -19,7 +19,13 @@ OUT = HERE / "_ref"
 LIB = OUT / "libref_cuda.so"
 
 
-def build(reference: Path = Path("/root/reference"), verbose: bool = False) -> Path | None:
+def build(reference: Path | None = None, verbose: bool = False) -> Path | None:
+    """``reference``: the root of the reference's source tree; by default the OXINFER_REFERENCE environment variable, else the
+    ``reference`` folder beside this repository."""
+    import os
+
+    if reference is None:
+        reference = Path(os.environ.get("OXINFER_REFERENCE", str(HERE.parent.parent / "reference")))
     rs, cu = reference / "src" / "cuda.rs", reference / "src" / "cuda_decode.cu"
     if not rs.exists() or not cu.exists():
         return LIB if LIB.exists() else None

@@ -488,6 +488,153 @@ float dot_row_q4(const Matrix& m, size_t r, const QAct& x, size_t c, const float
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same two decode kernels with the reference's AVX2 instructions (the form the reference runs on x86 and the one timed
+// as its CPU baseline): src/kernels_x86.rs:476-519 (q4_dot_rows_tc_avx2: maddubs of unsigned nibbles with int8 x, madd to
+// eight i32 lanes, one FMA per block into eight f32 lanes, hsum, the -8 * sum correction) and src/kernels_ggml_x86.rs:120-431
+// (unpack a block to int8 in registers, maddubs / madd for the 16-element integer sums). The reference's own invariant is
+// that these give the bits of the portable kernels (src/kernels_ggml_x86.rs:576-624); tests/test_oracle_pins.py holds
+// these to the scalar restatements above bit for bit. The float arithmetic over a block's 16 sums stays in the portable
+// kernel's order, which is what makes the bits equal.
+// ---------------------------------------------------------------------------------------------
+static bool g_decode_scalar = false;  // orc_set_decode_scalar: force the scalar restatements (the bit-identity tests)
+
+static inline float hsum256(__m256 v) {  // src/kernels_x86.rs:96-103
+    __m128 lo = _mm256_castps256_ps128(v), hi = _mm256_extractf128_ps(v, 1);
+    __m128 t = _mm_add_ps(lo, hi);
+    t = _mm_add_ps(t, _mm_movehl_ps(t, t));
+    t = _mm_add_ss(t, _mm_shuffle_ps(t, t, 1));
+    return _mm_cvtss_f32(t);
+}
+
+// R = 2 rows against one activation row, as q4_rows_t1 pairs them (src/kernels_x86.rs:522-536): y[0], y[1]; rows == 1 for
+// the last row of an odd range.
+void dot_rows_q4_avx2(const Matrix& m, size_t r, int rows, const QAct& x, size_t c, const float* gsums, float* y) {
+    const size_t n_in = m.n_in, bpr = n_in / 32;
+    const int8_t* xq = x.q.data() + c * n_in;
+    const float* xs = x.scales.data() + c * bpr;
+    const int32_t* xsums = x.sums.data() + c * bpr;
+    const __m256i ones = _mm256_set1_epi16(1);
+    const __m128i m0f = _mm_set1_epi8(0x0F);
+    __m256 acc[2] = {_mm256_setzero_ps(), _mm256_setzero_ps()};
+    float corr[2] = {0.0f, 0.0f};
+    for (size_t b = 0; b < bpr; b++) {
+        const __m256i xv = _mm256_loadu_si256((const __m256i*)(xq + b * 32));
+        for (int i = 0; i < rows; i++) {
+            const __m128i bytes = _mm_loadu_si128((const __m128i*)(m.q.data() + (r + i) * n_in / 2 + b * 16));
+            const __m128i lo = _mm_and_si128(bytes, m0f), hi = _mm_and_si128(_mm_srli_epi16(bytes, 4), m0f);
+            const __m256i wv = _mm256_set_m128i(hi, lo);
+            const float d = f16_to_f32(m.scales[(r + i) * bpr + b]);
+            const __m256i p32 = _mm256_madd_epi16(_mm256_maddubs_epi16(wv, xv), ones);
+            const float sc = d * xs[b];
+            acc[i] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(p32), _mm256_set1_ps(sc), acc[i]);
+            corr[i] += sc * (float)xsums[b];
+        }
+    }
+    for (int i = 0; i < rows; i++) {
+        float v = hsum256(acc[i]) - 8.0f * corr[i];
+        if (!m.offsets.empty()) {  // src/kernels.rs:1284-1297
+            const size_t gpr = n_in / m.group;
+            const uint16_t* o = m.offsets.data() + (r + i) * gpr;
+            float a8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (size_t g = 0; g < gpr; g++) a8[g % 8] = std::fmaf(bf16_to_f32(o[g]), gsums[g], a8[g % 8]);
+            float t = 0.0f;
+            for (int k = 0; k < 8; k++) t += a8[k];
+            v += t;
+        }
+        y[i] = v;
+    }
+}
+
+// The int8 values of one block, unpacked with 256-bit operations into q (32-byte aligned); the scales / offsets come from
+// the scalar decode_i8 arithmetic (16 values per block).
+static inline void unpack_q_avx2(int kind, const uint8_t* b, int8_t* q) {
+    const __m256i m4 = _mm256_set1_epi8(0x0F);
+    if (kind == K_Q8_0) {
+        _mm256_store_si256((__m256i*)q, _mm256_loadu_si256((const __m256i*)(b + 2)));
+    } else if (kind == K_Q4_K) {
+        const __m256i eight = _mm256_set1_epi8(8);
+        for (int j = 0; j < 4; j++) {
+            const __m256i v = _mm256_loadu_si256((const __m256i*)(b + 16 + 32 * j));
+            _mm256_store_si256((__m256i*)(q + 64 * j), _mm256_sub_epi8(_mm256_and_si256(v, m4), eight));
+            _mm256_store_si256((__m256i*)(q + 64 * j + 32), _mm256_sub_epi8(_mm256_and_si256(_mm256_srli_epi16(v, 4), m4), eight));
+        }
+    } else {  // Q6_K
+        const __m256i m2 = _mm256_set1_epi8(3), off = _mm256_set1_epi8(32);
+        for (int n = 0; n < 2; n++) {
+            const __m256i la = _mm256_loadu_si256((const __m256i*)(b + 64 * n)), lb = _mm256_loadu_si256((const __m256i*)(b + 64 * n + 32));
+            const __m256i h = _mm256_loadu_si256((const __m256i*)(b + 128 + 32 * n));
+            const __m256i h0 = _mm256_slli_epi16(_mm256_and_si256(h, m2), 4);
+            const __m256i h1 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 2), m2), 4);
+            const __m256i h2 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 4), m2), 4);
+            const __m256i h3 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 6), m2), 4);
+            int8_t* o = q + 128 * n;
+            _mm256_store_si256((__m256i*)o, _mm256_sub_epi8(_mm256_or_si256(_mm256_and_si256(la, m4), h0), off));
+            _mm256_store_si256((__m256i*)(o + 32), _mm256_sub_epi8(_mm256_or_si256(_mm256_and_si256(lb, m4), h1), off));
+            _mm256_store_si256((__m256i*)(o + 64), _mm256_sub_epi8(_mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(la, 4), m4), h2), off));
+            _mm256_store_si256((__m256i*)(o + 96), _mm256_sub_epi8(_mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(lb, 4), m4), h3), off));
+        }
+    }
+}
+
+// The block's scales (and offsets) alone: decode_i8 without its element loop.
+static inline bool block_scales(int kind, const uint8_t* b, float* s, float* m) {
+    if (kind == K_Q8_0) {
+        s[0] = s[1] = f16at(b, 0);
+        return false;
+    }
+    if (kind == K_Q4_K) {
+        const float d = f16at(b, 0), mn = f16at(b, 2);
+        for (int i = 0; i < 8; i++) {
+            uint8_t sc, mm;
+            scale_min_k4(i, b + 4, &sc, &mm);
+            s[2 * i] = s[2 * i + 1] = d * (float)sc;
+            const float a = 8.0f * s[2 * i], c = mn * (float)mm;
+            m[2 * i] = m[2 * i + 1] = a - c;
+        }
+        return true;
+    }
+    const float d = f16at(b, 208);
+    for (int g = 0; g < 16; g++) s[g] = d * (float)(int8_t)b[192 + g];
+    return false;
+}
+
+float dot_row_gguf_avx2(int kind, const uint8_t* row, size_t n_in, const QAct& x, size_t c) {
+    const size_t bs = block_size(kind), ts = type_size(kind);
+    alignas(32) int8_t q[256];
+    alignas(32) int32_t lanes[8];
+    float s[16], m[16];
+    const __m256i ones = _mm256_set1_epi16(1);
+    float acc = 0.0f;
+    for (size_t bi = 0; bi < n_in / bs; bi++) {
+        const uint8_t* b = row + bi * ts;
+        unpack_q_avx2(kind, b, q);
+        const bool has_min = block_scales(kind, b, s, m);
+        const size_t e0 = bi * bs;
+        const int8_t* xq = x.q.data() + c * n_in + e0;
+        const float* xs = x.scales.data() + c * n_in / 32 + e0 / 32;
+        float sum = 0.0f;
+        for (size_t g2 = 0; g2 < bs / 32; g2++) {  // two 16-element groups per 256-bit step
+            const __m256i qv = _mm256_load_si256((const __m256i*)(q + 32 * g2));
+            const __m256i xv = _mm256_loadu_si256((const __m256i*)(xq + 32 * g2));
+            // maddubs wants an unsigned first operand: |q| times x with q's sign (|q| <= 128, |x| <= 127: no saturation)
+            const __m256i p32 = _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_abs_epi8(qv), _mm256_sign_epi8(xv, qv)), ones);
+            _mm256_store_si256((__m256i*)lanes, p32);
+            const int i0 = lanes[0] + lanes[1] + lanes[2] + lanes[3], i1 = lanes[4] + lanes[5] + lanes[6] + lanes[7];
+            const float a0 = s[2 * g2] * xs[g2];
+            sum += a0 * (float)i0;
+            const float a1 = s[2 * g2 + 1] * xs[g2];
+            sum += a1 * (float)i1;
+        }
+        if (has_min) {
+            const float* xh = x.hsums.data() + c * n_in / 16 + e0 / 16;
+            for (size_t g = 0; g < bs / 16; g++) sum += m[g] * xh[g];
+        }
+        acc += sum;
+    }
+    return acc;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Prefill (t > 7, and every t for dense formats): dequantize 8 rows, then an 8 x 8 outer-product
 // FMA tile with ONE accumulator per output and k in ascending order
 // (src/kernels.rs:1998-2038, src/kernels_x86.rs:296-324). The value of each output is therefore
@@ -583,11 +730,29 @@ void matmul_quant(const Matrix& m, const float* x, size_t t, float* y, int threa
             }
     }
     size_t rb = m.format == 1 ? row_bytes(m.kind, n_in) : 0;
+    const bool scalar = g_decode_scalar;
     parallel_for(blocks.size(), threads, [&](size_t b) {
-        for (size_t r = blocks[b].first; r < blocks[b].second; r++)
-            for (size_t c = 0; c < t; c++)
-                y[c * n_out + r] = m.format == 0 ? dot_row_q4(m, r, xa, c, gs.empty() ? nullptr : gs.data() + c * gpr)
-                                                 : dot_row_gguf(m.kind, m.data.data() + r * rb, n_in, xa, c);
+        const size_t r0 = blocks[b].first, r1 = blocks[b].second;
+        if (scalar) {
+            for (size_t r = r0; r < r1; r++)
+                for (size_t c = 0; c < t; c++)
+                    y[c * n_out + r] = m.format == 0 ? dot_row_q4(m, r, xa, c, gs.empty() ? nullptr : gs.data() + c * gpr)
+                                                     : dot_row_gguf(m.kind, m.data.data() + r * rb, n_in, xa, c);
+            return;
+        }
+        if (m.format == 0) {
+            for (size_t r = r0; r < r1; r += 2) {
+                const int rows = r + 2 <= r1 ? 2 : 1;
+                for (size_t c = 0; c < t; c++) {
+                    float o[2];
+                    dot_rows_q4_avx2(m, r, rows, xa, c, gs.empty() ? nullptr : gs.data() + c * gpr, o);
+                    for (int i = 0; i < rows; i++) y[c * n_out + r + i] = o[i];
+                }
+            }
+        } else {
+            for (size_t r = r0; r < r1; r++)
+                for (size_t c = 0; c < t; c++) y[c * n_out + r] = dot_row_gguf_avx2(m.kind, m.data.data() + r * rb, n_in, xa, c);
+        }
     });
 }
 
@@ -754,6 +919,8 @@ ORC_API void orc_mlx_dequant_row(const uint32_t* w, const uint16_t* scales, cons
 }
 
 // The CPU path's own result: decode kernels for t <= 7, f32 GEMM otherwise (matmul_quant above).
+// 1: the decode path (t <= 7) runs the scalar restatements; 0 (default): the AVX2 kernels. Same bits either way.
+ORC_API void orc_set_decode_scalar(int on) { g_decode_scalar = on != 0; }
 ORC_API void orc_matmul_cpu(void* m, const float* x, size_t t, float* y, int threads) { matmul_quant(*(Matrix*)m, x, t, y, threads); }
 
 // The prefill (f32 GEMM) arithmetic at any t (what a GPU GEMM result is compared with).

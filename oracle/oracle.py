@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
             "orc_matrix_q4_parts": (i32, [vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(vp), C.POINTER(sz), C.POINTER(vp), C.POINTER(sz), C.POINTER(sz)]),
             "orc_matrix_dequantize_rows": (None, [vp, sz, sz, vp]),
             "orc_mlx_dequant_row": (None, [vp, vp, vp, sz, vp, sz]),
+            "orc_set_decode_scalar": (None, [i32]),
             "orc_matmul_cpu": (None, [vp, vp, sz, vp, i32]),
             "orc_matmul_prefill": (None, [vp, vp, sz, vp, i32]),
             "orc_matmul_f64": (None, [vp, vp, sz, vp, i32]),
@@ -217,9 +218,14 @@ def matrix_of(ref, n_out: int, n_in: int) -> Matrix:
     return Matrix.gguf(ref.kind, ref.data, n_out, n_in, ref.block_scales, ref.bs_rows, ref.bs_cols)
 
 
+def set_decode_scalar(on: bool) -> None:
+    """``matmul_cpu`` at up to 7 rows: the scalar restatements of the decode kernels instead of the AVX2 ones (same bits)."""
+    lib().orc_set_decode_scalar(int(on))
+
+
 def decode_kernel_name() -> str:
     """Which restatement of the reference's int8-activation decode kernels ``matmul_cpu`` runs at up to 7 rows."""
-    return "scalar restatement of the int8-activation decode kernels (src/kernels_x86.rs:476-536, src/kernels_ggml_x86.rs:389-431)"
+    return "AVX2 int8-activation decode kernels (maddubs / madd; src/kernels_x86.rs:476-536, src/kernels_ggml_x86.rs:120-431)"
 
 
 def mlx_dequant_row(w: np.ndarray, scales: np.ndarray, biases: np.ndarray, group: int, n: int) -> np.ndarray:
@@ -391,7 +397,8 @@ def ref_cuda():
                        ("ref_qk_rope", [vp] * 10 + [u] * 5 + [f, vp]),
                        ("ref_attend", [vp] * 6 + [u, u, u, f, u, C.c_int, C.POINTER(f), vp]),
                        ("ref_glu", [vp, vp, vp, u, u, vp]),
-                       ("ref_gemm_q4a", [vp, vp, vp, u, u, vp, vp, u, u, u, C.c_int, C.POINTER(f), vp])):
+                       ("ref_gemm_q4a", [vp, vp, vp, u, u, vp, vp, u, u, u, C.c_int, C.POINTER(f), vp]),
+                       ("ref_moe_q4a", [vp] * 6 + [u, u, u, u, vp, u, u, vp, vp, vp, vp, u, vp, vp, vp, vp, vp, C.c_int, C.POINTER(f), vp])):
         fn = getattr(L, name)
         fn.restype, fn.argtypes = C.c_int, args
     return L
@@ -456,4 +463,63 @@ def ref_dmv_q4a(L, m: Matrix, x, y, iters: int = 1, stream: int = 0) -> float:
                        C.byref(ms), stream)
     if rc != 0:
         raise RuntimeError(f"the reference kernel failed with CUDA error {rc}")
+    return ms.value
+
+
+class RefMoe:
+    """The experts of one MoE layer as the reference's CUDA backend holds them (per expert the Q4Matrix arrays of the fused
+    gate_up and of the down projection on the device), for ``ref_moe_q4a``. ``gate_up`` / ``down``: oracle matrices made by
+    ``Matrix.from_mlx_q4``."""
+
+    def __init__(self, gate_up: list, down: list, h: int, inter: int):
+        import torch
+
+        self.h, self.inter, self.n = h, inter, len(gate_up)
+        self.keep, tabs = [], [[] for _ in range(6)]
+        self.group = None
+        for e in range(self.n):
+            for base, m in ((0, gate_up[e]), (3, down[e])):
+                q, s, o, group = m.q4_parts()
+                self.group = group
+                for j, a in enumerate((q, s.view(np.int16), o.view(np.int16))):
+                    d = torch.from_numpy(a).cuda()
+                    self.keep.append(d)
+                    tabs[base + j].append(d.data_ptr())
+        self.tabs = [(C.c_void_p * self.n)(*t) for t in tabs]
+
+
+def ref_moe_q4a(L, rm: RefMoe, x, route_ids: np.ndarray, route_w: np.ndarray, y, iters: int = 0) -> float:
+    """One routed-expert layer with the reference's own kernels in the sequence of CudaBackend::moe_run
+    (src/cuda.rs:798-966): segments per expert padded to its 64-row GEMM tile, built here on the host as moe_run builds
+    them. ``x``, ``y``: torch CUDA f32 [t][h]; y is added to once per run of the sequence (1 + iters runs). Returns the
+    mean device milliseconds of one sequence."""
+    import torch
+
+    t, k = route_ids.shape
+    TILE = 64
+    count = np.bincount(route_ids.reshape(-1), minlength=rm.n)
+    seg_len = ((count + TILE - 1) // TILE * TILE).astype(np.uint32)
+    seg_start = np.concatenate([[0], np.cumsum(seg_len)[:-1]]).astype(np.uint32)
+    rows = int(seg_len.sum())
+    src = np.full(rows, t, np.uint32)
+    slots = np.zeros(2 * t * k, np.uint32)
+    fill = seg_start.astype(np.int64).copy()
+    wbits = np.ascontiguousarray(route_w, dtype=np.float32).view(np.uint32)
+    for i in range(t):
+        for j in range(k):
+            e = int(route_ids[i, j])
+            r = fill[e]
+            fill[e] += 1
+            src[r] = i
+            slots[2 * (i * k + j)] = r
+            slots[2 * (i * k + j) + 1] = wbits[i, j]
+    dsrc, dslots = torch.from_numpy(src.view(np.int32)).cuda(), torch.from_numpy(slots.view(np.int32)).cuda()
+    xs = torch.empty((rows, rm.h), device="cuda")
+    gu = torch.empty((rows, 2 * rm.inter), device="cuda")
+    a = torch.empty((rows, rm.inter), device="cuda")
+    o = torch.empty((rows, rm.h), device="cuda")
+    ms = C.c_float()
+    _ref_rc(L.ref_moe_q4a(*rm.tabs, rm.n, rm.h, rm.inter, rm.group, x.data_ptr(), t, k, dsrc.data_ptr(), dslots.data_ptr(),
+                          seg_start.ctypes.data, seg_len.ctypes.data, rows, xs.data_ptr(), gu.data_ptr(), a.data_ptr(), o.data_ptr(), y.data_ptr(),
+                          iters, C.byref(ms), None))
     return ms.value

@@ -174,3 +174,53 @@ REF_API int ref_gemm_q4a(const void* q, const void* scales, const void* offsets,
     if (e == cudaSuccess) e = cudaGetLastError();
     return (int)e;
 }
+
+// One routed-expert layer with the reference's own kernels, launched as CudaBackend::moe_run launches them
+// (src/cuda.rs:798-966): moe_gather over per-expert segments padded to the GEMM's 64-row tile, one gemm_q4a per touched
+// expert for the fused gate_up projection, moe_act (SiLU), one gemm_q4a per touched expert for the down projection,
+// moe_combine in route order. The caller builds the segment tables the way moe_run does (host arrays seg_start / seg_len in
+// rows, device arrays src [rows] and slots [2 t k] = (row, weight bits) pairs) and passes the experts' Q4Matrix arrays as
+// host tables of device pointers. Scratch (device): xs [rows][h], gu [rows][2 mi], a [rows][mi], o [rows][h] f32.
+// y [t][h] is added to (the caller resets it between calls if it wants one layer's result). Runs the sequence `iters`
+// times after one warm-up and returns the mean device time of one sequence.
+REF_API int ref_moe_q4a(const void* const* gu_q, const void* const* gu_s, const void* const* gu_o, const void* const* dn_q, const void* const* dn_s,
+                        const void* const* dn_o, unsigned int n_experts, unsigned int h, unsigned int mi, unsigned int group, const float* x,
+                        unsigned int t, unsigned int k, const unsigned int* src, const unsigned int* slots, const unsigned int* seg_start,
+                        const unsigned int* seg_len, unsigned int rows, float* xs, float* gu, float* a, float* o, float* y, int iters,
+                        float* ms_per_iter, void* stream) {
+    if (h % 64 || mi % 64 || (2 * mi) % 64 || h % 32 || mi % 32) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned int cols = (h + 255) / 256 < 64 ? (h + 255) / 256 : 64;
+    auto once = [&]() {
+        moe_gather<<<dim3(cols, rows), 256, 0, st>>>(x, src, xs, h, t);
+        for (unsigned int e = 0; e < n_experts; e++) {
+            if (!seg_len[e]) continue;
+            gemm_q4a<<<dim3(2 * mi / 64, seg_len[e] / 64), 256, 0, st>>>((const unsigned char*)gu_q[e], (const unsigned short*)gu_s[e],
+                                                                          xs + (size_t)seg_start[e] * h, gu + (size_t)seg_start[e] * 2 * mi, 2 * mi, h,
+                                                                          (const unsigned short*)gu_o[e], h / group, group / 32);
+        }
+        moe_act<<<(unsigned int)(((size_t)rows * mi + 255) / 256), 256, 0, st>>>(gu, a, rows, mi, 0u, 0u, 0.0f);
+        for (unsigned int e = 0; e < n_experts; e++) {
+            if (!seg_len[e]) continue;
+            gemm_q4a<<<dim3(h / 64, seg_len[e] / 64), 256, 0, st>>>((const unsigned char*)dn_q[e], (const unsigned short*)dn_s[e],
+                                                                     a + (size_t)seg_start[e] * mi, o + (size_t)seg_start[e] * h, h, mi,
+                                                                     (const unsigned short*)dn_o[e], mi / group, group / 32);
+        }
+        moe_combine<<<dim3(cols, t), 256, 0, st>>>(o, slots, y, h, k);
+    };
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    once();
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < iters; i++) once();
+    cudaEventRecord(e1, st);
+    cudaError_t e = cudaStreamSynchronize(st);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (ms_per_iter) *ms_per_iter = iters > 0 ? ms / iters : 0.0f;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return (int)e;
+}

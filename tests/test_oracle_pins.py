@@ -190,3 +190,26 @@ def test_golden_vectors():
         assert O.fnv_f32(m.dequantize_rows()) == int(g[f"{fmt}_deq_fnv"])
         assert np.array_equal(m.matmul_prefill(x), g[f"{fmt}_y_prefill"])
         assert np.array_equal(m.matmul_f64(x), g[f"{fmt}_y_f64"])
+
+
+def test_avx2_decode_kernels_give_the_bits_of_the_scalar_restatements():
+    """The reference's own invariant (src/kernels_ggml_x86.rs:576-624; src/kernels_x86.rs tests): its AVX2 decode kernels
+    equal the portable ones bit for bit. The oracle's AVX2 kernels (the ones timed as the CPU baseline) are held to its
+    scalar restatements the same way, for every format, one to seven rows, odd row counts and several thread counts."""
+    from oxinfer_b200 import synth
+
+    from util import oracle_matrix
+
+    for fmt, n_out, n_in in [("mlx4", 77, 1024), ("q4_k", 50, 768), ("q6_k", 33, 512), ("q8_0", 41, 256)]:
+        ref = synth.make(fmt, n_out, n_in, 60)
+        m = oracle_matrix(ref, n_out, n_in)
+        for t in (1, 2, 7):
+            x = synth.activations(t, n_in, 61 + t) * np.float32(1.7)
+            O.set_decode_scalar(True)
+            try:
+                want = m.matmul_cpu(x, 3)
+            finally:
+                O.set_decode_scalar(False)
+            for threads in (1, 4):
+                got = m.matmul_cpu(x, threads)
+                assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (fmt, t, threads)
