@@ -177,6 +177,16 @@ int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float* x_dev, fl
  * copied into two stacked device buffers; the per-expert handles may be freed afterwards. h and inter
  * must be multiples of 256. The activation is SiLU (MoeAct::Silu, src/gpu.rs:36-54). */
 int b2_upload_moe(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* down, size_t experts, size_t h, size_t inter, b2_moe_handle* out);
+/* The full `Backend::upload_moe` (src/gpu.rs:200-215): with `up` != NULL, gate_up[e] is the gate projection [inter][h] and
+ * up[e] the up projection [inter][h] (GGUF files store them apart); `act` is the layer's gated activation (MoeAct,
+ * src/gpu.rs:36-54), act_limit the clamp of B2_ACT_SILU_CLAMP. Activations the reference's own CUDA backend keeps on the CPU
+ * (SwigluOai, SiTU: src/cuda.rs:900-906) are declined here too. `upload_moe_transient` (src/gpu.rs:217-231) is this call
+ * followed by b2_free_moe when the pass over the streamed experts is done. */
+#define B2_ACT_SILU 0       /* MoeAct::Silu */
+#define B2_ACT_GELU_TANH 1  /* MoeAct::GeluTanh */
+#define B2_ACT_SILU_CLAMP 2 /* MoeAct::SiluClamp(limit) */
+int b2_upload_moe_ex(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* up, const b2_weight* down, size_t experts, size_t h, size_t inter,
+                     int act, float act_limit, b2_moe_handle* out);
 int b2_free_moe(b2_ctx* ctx, b2_moe_handle m);
 /* `Backend::moe`, src/gpu.rs:232-248 / src/cuda.rs:798-966: token i of x [t][h] goes through its k routes
  * (route_ids[i k + j], route_w[i k + j]) and y[i] += sum_j w_ij down(silu(gate x_i) * up x_i), added in
@@ -303,6 +313,30 @@ int b2_plan_launches(b2_ctx* ctx, b2_plan plan, uint64_t* per_step);
 #define B2_PLAN_HANDLE_BYTES 128
 int b2_plan_export(b2_ctx* ctx, b2_plan plan, void* handle_out);
 int b2_plan_attach_peers(b2_ctx* ctx, b2_plan plan, uint32_t rank, uint32_t world, const void* handles);
+
+/* ---- several GPUs: one process per GPU, collectives over NCCL (no counterpart in the reference, which drives one device) ----
+ * The library opens libnccl.so.2 itself with dlopen on the first of these calls (nothing is linked at build time; without
+ * NCCL they return B2_DECLINED). Rank 0 makes an id with b2_comm_unique_id and hands its B2_COMM_ID_BYTES bytes to the other
+ * processes by any host channel; then every process calls b2_comm_init on its own context (ncclCommInitRank on that
+ * context's device). The calls below are collective: every rank makes them in the same order, on its context's stream. */
+#define B2_COMM_ID_BYTES 128
+int b2_comm_unique_id(void* id_out);
+int b2_comm_init(b2_ctx* ctx, int world, int rank, const void* id);
+int b2_comm_free(b2_ctx* ctx);
+/* Tensor-parallel dense matmul: the rows of W are sharded over the ranks in equal contiguous parts and `w_shard` is this
+ * rank's part [n_local][n_in] (an upload of its rows, or b2_shard_rows of a full upload); x_dev [t][n_in] is the same on
+ * every rank; y_dev [t][world * n_local] f32 receives the FULL product on every rank (the shard's product, one
+ * ncclAllGather, a copy of the ranks' blocks into their columns). Bit-identical to the unsharded b2_matmul_dev: every
+ * column is computed by the kernel that computes it on one GPU. Not synchronized. */
+int b2_matmul_sharded(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float* y_dev);
+/* Expert-parallel `Backend::moe`: the layer's n_experts_global experts are sharded over the ranks in equal contiguous parts
+ * and `m` holds this rank's (b2_upload_moe over them, local numbering); x_dev / y_dev [t][h] are THIS rank's tokens,
+ * route_ids [t][k] (host) are global expert numbers, route_w [t][k] (host) their weights. Every (token, route) pair goes to
+ * the rank that owns its expert and its result comes back (counts by ncclAllGather, rows by grouped ncclSend / ncclRecv),
+ * then y[i] += sum_j w_ij o_ij in route order: bit-identical to b2_moe_dev over all experts on one GPU. Synchronizes the
+ * stream (the route tables are host arrays). */
+int b2_moe_ep(b2_ctx* ctx, b2_moe_handle m, size_t n_experts_global, const float* x_dev, size_t t, const int32_t* route_ids,
+              const float* route_w, size_t k, float* y_dev);
 
 /* No counterpart in the reference (its CUDA backend allocates staging and arena memory freely,
  * src/cuda.rs:572-699). One Q4_K matrix-vector product, y[n_out] = W x, that allocates nothing, for

@@ -34,6 +34,7 @@ class View(C.Structure):
 
 OP_NORM, OP_LINEAR, OP_QK_ROPE, OP_ATTEND, OP_GLU, OP_EXCHANGE = 1, 2, 3, 4, 5, 6
 PLAN_HANDLE_BYTES = 128
+COMM_ID_BYTES = 128
 
 
 class Op(C.Structure):
@@ -106,6 +107,8 @@ _SIGNATURES = {
     "b2_matvec_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "b2_check_status": (C.c_int, [C.c_void_p]),
     "b2_upload_moe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_upload_moe_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_float,
+                         C.POINTER(C.c_uint64)]),
     "b2_free_moe": (C.c_int, [C.c_void_p, C.c_uint64]),
     "b2_moe": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b2_moe_dev": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -122,6 +125,11 @@ _SIGNATURES = {
     "b2_plan_launches": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64)]),
     "b2_plan_export": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "b2_plan_attach_peers": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "b2_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "b2_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "b2_comm_free": (C.c_int, [C.c_void_p]),
+    "b2_matmul_sharded": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
+    "b2_moe_ep": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b2_matvec_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
 }
 

@@ -261,13 +261,16 @@ class Backend:
                                                  _ptr(gate) if gate is not None else None))
 
     # -- routed experts ---------------------------------------------------------------------------
-    def upload_moe(self, gate_up: list, down: list, h: int, inter: int) -> "MoeWeights | None":
-        """``Backend::upload_moe`` (``src/gpu.rs:200-215``): per-expert weights already uploaded with ``upload``."""
+    def upload_moe(self, gate_up: list, down: list, h: int, inter: int, up: list | None = None, act: int = 0, act_limit: float = 0.0) -> "MoeWeights | None":
+        """``Backend::upload_moe`` (``src/gpu.rs:200-215``): per-expert weights already uploaded with ``upload``. With ``up`` the gate
+        and up projections come apart; ``act``: 0 SiLU, 1 tanh GELU, 2 SiLU clamped at ``act_limit`` (``MoeAct``)."""
         n = len(gate_up)
         gu = (C.c_uint64 * n)(*[d.handle for d in gate_up])
         dn = (C.c_uint64 * n)(*[d.handle for d in down])
+        up_arr = (C.c_uint64 * n)(*[d.handle for d in up]) if up is not None else None
         hd = C.c_uint64()
-        if not self._check(self._L.b2_upload_moe(self._ctx, C.cast(gu, C.c_void_p), C.cast(dn, C.c_void_p), n, h, inter, C.byref(hd))):
+        if not self._check(self._L.b2_upload_moe_ex(self._ctx, C.cast(gu, C.c_void_p), C.cast(up_arr, C.c_void_p) if up_arr is not None else None,
+                                                    C.cast(dn, C.c_void_p), n, h, inter, act, act_limit, C.byref(hd))):
             return None
         return MoeWeights(self, hd.value, n, h, inter)
 
@@ -290,6 +293,37 @@ class Backend:
     def route_topk_dev(self, logits, k: int, ids, w) -> bool:
         t, n = logits.shape
         return self._check(self._L.b2_route_topk_dev(self._ctx, _ptr(logits), t, n, k, _ptr(ids), _ptr(w)))
+
+    # -- several GPUs (one process per GPU; collectives over NCCL, opened by the library itself) ----------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """Rank 0 makes the id; the other processes receive its bytes by any host channel."""
+        buf = C.create_string_buffer(_lib.COMM_ID_BYTES)
+        rc = _lib.lib().b2_comm_unique_id(buf)
+        if rc != OK:
+            raise BackendError(rc, "b2_comm_unique_id: NCCL is not available")
+        return buf.raw
+
+    def comm_init(self, world: int, rank: int, comm_id: bytes) -> bool:
+        assert len(comm_id) == _lib.COMM_ID_BYTES
+        self.world, self.rank = world, rank
+        return self._check(self._L.b2_comm_init(self._ctx, world, rank, comm_id))
+
+    def comm_free(self) -> None:
+        self._check(self._L.b2_comm_free(self._ctx))
+
+    def matmul_sharded(self, shard: DeviceWeight, x, y) -> bool:
+        """``y[t][world * n_local]`` (f32, full on every rank) from this rank's row shard; collective."""
+        t = x.shape[0]
+        assert x.shape[1] == shard.n_in and y.shape[0] == t and y.is_cuda and x.is_cuda
+        return self._check(self._L.b2_matmul_sharded(self._ctx, shard.handle, _ptr(x), _dtype_code(x), t, _ptr(y)))
+
+    def moe_ep(self, x, routes_ids: np.ndarray, routes_w: np.ndarray, dev: "MoeWeights", n_experts_global: int, y) -> bool:
+        """Expert-parallel ``moe``: ``dev`` holds this rank's experts, the routes name global experts; collective."""
+        ids = np.ascontiguousarray(routes_ids, dtype=np.int32)
+        w = np.ascontiguousarray(routes_w, dtype=np.float32)
+        t, k = ids.shape
+        return self._check(self._L.b2_moe_ep(self._ctx, dev.handle, n_experts_global, _ptr(x), t, _ptr(ids), _ptr(w), k, _ptr(y)))
 
     def prepare_x_dev(self, x) -> bool:
         """Splits a device vector into the integer planes the GEMV kernels read (once per vector)."""

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "kernels.h"
+#include "nccl_dyn.h"
 #include "plan.h"
 
 namespace b2 {
@@ -29,6 +30,8 @@ struct Weight {
 struct Moe {
     int fmt = 0;
     size_t experts = 0, h = 0, inter = 0;
+    int act = B2_ACT_SILU;   // MoeAct
+    float act_limit = 0.0f;  // SiluClamp's limit
     void* gate_up = nullptr;  // [experts][2 inter][h / 256][144]
     void* down = nullptr;     // [experts][h][inter / 256][144]
     size_t bytes = 0;
@@ -69,6 +72,10 @@ class Backend {
     std::unordered_map<uint64_t, Moe> moes;
     std::unordered_map<uint64_t, DecodePlanImpl*> decode_plans;
     Scratch moe_idx, moe_xg, moe_g, moe_a, moe_o;
+    // tensor / expert parallel (b2_comm_init): this process's rank in a group of `world` processes, one GPU each
+    NcclComm comm = nullptr;
+    int world = 1, rank = 0;
+    Scratch tp_stage, tp_gather, ep_idx, ep_send, ep_recv, ep_out, ep_back;
     uint64_t next_handle = 1;
     uint64_t launches = 0;
     // staging for the host-buffer entry points
@@ -692,21 +699,29 @@ class Backend {
     // ---- Backend::upload_moe (src/gpu.rs:200-215, src/cuda.rs:777-796): the experts were uploaded one by
     // one with b2_upload_*; their blocks are copied into two stacked buffers the grouped GEMM indexes by
     // expert, after which the caller may free the per-expert handles.
-    int upload_moe(const uint64_t* gate_up, const uint64_t* down, size_t experts, size_t h, size_t inter, uint64_t* out) {
+    // `up` == nullptr: gate_up[e] is the fused projection [2 inter][h]; else gate_up[e] is the gate projection [inter][h] and up[e]
+    // the up projection [inter][h] (GGUF files store them apart, src/gpu.rs:200-215): they are stacked into the fused layout here.
+    int upload_moe(const uint64_t* gate_up, const uint64_t* up, const uint64_t* down, size_t experts, size_t h, size_t inter, int act, float limit,
+                   uint64_t* out) {
         if (!gate_up || !down || !out || experts == 0) return fail(B2_ERR_ARG, "[b200qmm: upload_moe: null argument]");
         if (h % 256 || inter % 256) return fail(B2_DECLINED, "[b200qmm: upload_moe: h and inter must be multiples of 256]");
+        if (act != B2_ACT_SILU && act != B2_ACT_GELU_TANH && act != B2_ACT_SILU_CLAMP)
+            return fail(B2_DECLINED, "[b200qmm: upload_moe: activation %d is not run on the device (SwigluOai and SiTU stay on the CPU, as in the reference)]", act);
         Moe m;
+        m.act = act;
+        m.act_limit = limit;
         m.experts = experts;
         m.h = h;
         m.inter = inter;
         const size_t gu_bytes = 2 * inter * (h / 256) * 144, dn_bytes = h * (inter / 256) * 144;
         for (size_t e = 0; e < experts; e++) {
-            Weight *g = find(gate_up[e]), *d = find(down[e]);
-            if (!g || !d) return fail(B2_ERR_ARG, "[b200qmm: upload_moe: unknown weight for expert %zu]", e);
+            Weight *g = find(gate_up[e]), *d = find(down[e]), *u = up ? find(up[e]) : nullptr;
+            if (!g || !d || (up && !u)) return fail(B2_ERR_ARG, "[b200qmm: upload_moe: unknown weight for expert %zu]", e);
             if (e == 0) m.fmt = g->dev.fmt;
-            if ((m.fmt != B2_FMT_MLX4 && m.fmt != B2_FMT_Q4_K) || g->dev.fmt != m.fmt || d->dev.fmt != m.fmt)
+            if ((m.fmt != B2_FMT_MLX4 && m.fmt != B2_FMT_Q4_K) || g->dev.fmt != m.fmt || d->dev.fmt != m.fmt || (u && u->dev.fmt != m.fmt))
                 return fail(B2_DECLINED, "[b200qmm: upload_moe: experts must all be MLX-4 or all Q4_K]");
-            if (g->dev.n_out != 2 * inter || g->dev.n_in != h || d->dev.n_out != h || d->dev.n_in != inter)
+            if (g->dev.n_out != (up ? inter : 2 * inter) || g->dev.n_in != h || d->dev.n_out != h || d->dev.n_in != inter ||
+                (u && (u->dev.n_out != inter || u->dev.n_in != h)))
                 return fail(B2_ERR_ARG, "[b200qmm: upload_moe: expert %zu has the wrong shape]", e);
         }
         cudaError_t e1 = cudaMalloc(&m.gate_up, gu_bytes * experts), e2 = cudaSuccess;
@@ -716,7 +731,12 @@ class Backend {
             return cuda_fail(e1 != cudaSuccess ? e1 : e2, "cudaMalloc(moe)");
         }
         for (size_t e = 0; e < experts; e++) {
-            cudaMemcpyAsync((uint8_t*)m.gate_up + e * gu_bytes, find(gate_up[e])->dev.p0, gu_bytes, cudaMemcpyDeviceToDevice, stream);
+            if (up) {  // gate rows, then up rows
+                cudaMemcpyAsync((uint8_t*)m.gate_up + e * gu_bytes, find(gate_up[e])->dev.p0, gu_bytes / 2, cudaMemcpyDeviceToDevice, stream);
+                cudaMemcpyAsync((uint8_t*)m.gate_up + e * gu_bytes + gu_bytes / 2, find(up[e])->dev.p0, gu_bytes / 2, cudaMemcpyDeviceToDevice, stream);
+            } else {
+                cudaMemcpyAsync((uint8_t*)m.gate_up + e * gu_bytes, find(gate_up[e])->dev.p0, gu_bytes, cudaMemcpyDeviceToDevice, stream);
+            }
             cudaMemcpyAsync((uint8_t*)m.down + e * dn_bytes, find(down[e])->dev.p0, dn_bytes, cudaMemcpyDeviceToDevice, stream);
         }
         cudaError_t e = cudaStreamSynchronize(stream);
@@ -807,7 +827,8 @@ class Backend {
         b2.x_stride = sa;
         b2.y_stride = m.h;
         b2.planes = (uint8_t*)moe_a.p;
-        if (e == cudaSuccess) e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, B2_MODE_SILU_PAIR, sm_count, stream);
+        if (e == cudaSuccess)
+            e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, m.act == B2_ACT_GELU_TANH ? B2_MODE_GELU_PAIR : B2_MODE_SILU_PAIR, sm_count, stream);
         if (e == cudaSuccess) e = launch_xplanes_rows((const float*)moe_g.p, R, m.inter, (uint8_t*)moe_a.p, sa, stream);
         if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, sm_count, stream);
         if (e == cudaSuccess) e = launch_moe_combine_small((const float*)moe_o.p, routes, t, k, m.h, y_dev_, stream);
@@ -835,7 +856,8 @@ class Backend {
             if (ids[i] < 0 || (size_t)ids[i] >= m.experts) return fail(B2_ERR_ARG, "[b200qmm: moe: expert index out of range]");
             count[(size_t)ids[i]]++;
         }
-        if (t * k <= 64 && !getenv("B2_MOE_NO_GEMV")) return moe_small(m, x_dev_, t, ids, rw, k, y_dev_);
+        // (the clamped SiLU has no fused pair mode in the matrix-vector kernels: those layers take the GEMM path at any batch)
+        if (t * k <= 64 && m.act != B2_ACT_SILU_CLAMP && !getenv("B2_MOE_NO_GEMV")) return moe_small(m, x_dev_, t, ids, rw, k, y_dev_);
         // Token tiles of 128 or 256 rows. A tile costs about the same either way (the kernel is bound by the expansion of
         // the tile's weights, which both heights share), so the taller tile wins as soon as it needs clearly fewer tiles:
         // large batches, where the experts hold more than a tile's worth of tokens each.
@@ -902,7 +924,7 @@ class Backend {
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_gather");
         if ((rc = grouped_gemm(m.fmt, m.gate_up, m.experts, 2 * m.inter, m.h, moe_xg.p, rows, d_tiles, (float*)moe_g.p, m_halves, x_unscale, lo_row0))) return rc;
-        e = launch_moe_act((const float*)moe_g.p, d_src, rows, m.inter, moe_a.p, a_unscale, lo_row0, stream);
+        e = launch_moe_act((const float*)moe_g.p, d_src, rows, m.inter, moe_a.p, a_unscale, lo_row0, stream, m.act, m.act_limit);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "moe_act");
         if ((rc = grouped_gemm(m.fmt, m.down, m.experts, m.h, m.inter, moe_a.p, rows, d_tiles, (float*)moe_o.p, m_halves, a_unscale, lo_row0))) return rc;
@@ -939,6 +961,168 @@ class Backend {
         cudaError_t e = launch_route_topk(logits_dev, t, n, k, ids_dev, w_dev, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "route_topk");
+        return B2_OK;
+    }
+
+    // ---- tensor parallel / expert parallel over NCCL (no counterpart in the reference, which has one device) ----
+    int nccl_fail(int rc, const char* what) { return fail(B2_ERR_CUDA, "[b200qmm: %s: %s]", what, nccl_api().GetErrorString ? nccl_api().GetErrorString(rc) : "NCCL error"); }
+
+    int comm_init(int world_, int rank_, const void* id) {
+        const NcclApi& n = nccl_api();
+        if (!n.ok) return fail(B2_DECLINED, "[b200qmm: comm_init: libnccl.so.2 was not found]");
+        if (!id || world_ < 1 || rank_ < 0 || rank_ >= world_) return fail(B2_ERR_ARG, "[b200qmm: comm_init: bad world / rank / id]");
+        if (comm) return fail(B2_ERR_ARG, "[b200qmm: comm_init: this context already has a communicator]");
+        NcclId uid;
+        std::memcpy(&uid, id, sizeof uid);
+        int rc = n.CommInitRank(&comm, world_, uid, rank_);
+        if (rc) {
+            comm = nullptr;
+            return nccl_fail(rc, "ncclCommInitRank");
+        }
+        world = world_;
+        rank = rank_;
+        return B2_OK;
+    }
+    int comm_free() {
+        if (comm) {
+            cudaStreamSynchronize(stream);
+            nccl_api().CommDestroy(comm);
+        }
+        comm = nullptr;
+        world = 1;
+        rank = 0;
+        return B2_OK;
+    }
+
+    // y[t][world * n_local] (f32, on every rank) = x[t][n_in] W^T for a W whose rows are sharded in equal contiguous parts over the
+    // ranks (w = this rank's shard): the shard's product into a staging buffer, one all-gather of the ranks' [t][n_local]
+    // blocks, and a copy that puts each block into its columns. Every column is computed by the kernel that computes it on one
+    // GPU, so the result equals the unsharded product bit for bit.
+    int matmul_sharded(uint64_t h, const void* x, int x_dtype, size_t t, float* y) {
+        Weight* w = find(h);
+        if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul_sharded: unknown weight]");
+        if (!comm) return fail(B2_ERR_ARG, "[b200qmm: matmul_sharded: no communicator (b2_comm_init)]");
+        if (t == 0) return B2_OK;
+        const size_t nl = w->dev.n_out, block = t * nl;
+        cudaError_t e = tp_stage.reserve(block * 4);
+        if (e == cudaSuccess) e = tp_gather.reserve(block * 4 * (size_t)world);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
+        int rc = matmul_dev(h, x, x_dtype, t, tp_stage.p, B2_F32);
+        if (rc) return rc;
+        int nrc = nccl_api().AllGather(tp_stage.p, tp_gather.p, block, NCCL_FLOAT32, comm, stream);
+        if (nrc) return nccl_fail(nrc, "ncclAllGather");
+        e = launch_scatter_blocks((const float*)tp_gather.p, (size_t)world, t, nl, y, stream);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "scatter_blocks");
+        return B2_OK;
+    }
+
+    // Expert-parallel routed experts: the layer's experts are sharded in equal contiguous parts over the ranks (`handle` holds
+    // this rank's, n_experts_global / world of them), the tokens x [t][h] are this rank's own, route_ids are GLOBAL expert
+    // numbers. Every (token, route) pair travels to the rank that owns its expert and its result travels back:
+    //   1. all-gather of every rank's per-expert pair counts (one small copy back to the host: the only synchronization);
+    //   2. the pairs' token rows, grouped by destination rank, then by expert, token order kept, sent with one grouped
+    //      send / receive (a receiver knows each row's expert from the counts alone, so no ids travel);
+    //   3. the local experts over the received rows (moe_dev with one route of weight 1 per row);
+    //   4. the results back the same way, and the combine y[i] += sum_j w_ij o_ij in route order.
+    // Each pair runs the kernels it runs on one GPU with the same inputs, and the combine keeps the route order: bit-identical
+    // to the single-GPU layer.
+    int moe_ep(uint64_t handle, size_t n_experts_global, const float* x_dev_, size_t t, const int32_t* ids, const float* rw, size_t k, float* y_dev_) {
+        auto it = moes.find(handle);
+        if (it == moes.end()) return fail(B2_ERR_ARG, "[b200qmm: moe_ep: unknown handle]");
+        if (!comm) return fail(B2_ERR_ARG, "[b200qmm: moe_ep: no communicator (b2_comm_init)]");
+        const size_t E = n_experts_global, W = (size_t)world, per = it->second.experts, hdim = it->second.h;
+        if (E != per * W) return fail(B2_ERR_ARG, "[b200qmm: moe_ep: this rank must hold n_experts_global / world experts]");
+        const NcclApi& n = nccl_api();
+        const size_t P = t * k;
+        for (size_t i = 0; i < P; i++)
+            if (ids[i] < 0 || (size_t)ids[i] >= E) return fail(B2_ERR_ARG, "[b200qmm: moe_ep: expert index out of range]");
+        // 1. counts
+        std::vector<int32_t> mine(E, 0), all(E * W, 0);
+        for (size_t i = 0; i < P; i++) mine[(size_t)ids[i]]++;
+        cudaError_t e = ep_idx.reserve((E + E * W) * 4 + (2 * P + 16) * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(ep index)");
+        int32_t* d_mine = (int32_t*)ep_idx.p;
+        int32_t* d_all = d_mine + E;
+        int32_t* d_order = d_all + E * W;   // [P] token of the i-th sent row
+        int32_t* d_slots = d_order + P;     // [P] position of pair (i, j) in the returned rows
+        e = cudaMemcpyAsync(d_mine, mine.data(), E * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "ep counts upload");
+        int nrc = n.AllGather(d_mine, d_all, E, NCCL_INT32, comm, stream);
+        if (nrc) return nccl_fail(nrc, "ncclAllGather(counts)");
+        e = cudaMemcpyAsync(all.data(), d_all, E * W * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return cuda_fail(e, "ep counts");
+        // 2. send order: by expert (hence by owner rank), token order kept
+        std::vector<size_t> start(E + 1, 0);
+        for (size_t x = 0; x < E; x++) start[x + 1] = start[x] + (size_t)mine[x];
+        std::vector<int32_t> order(P), slots(P);
+        {
+            std::vector<size_t> fill(start.begin(), start.end() - 1);
+            for (size_t i = 0; i < t; i++)
+                for (size_t j = 0; j < k; j++) {
+                    const size_t pos = fill[(size_t)ids[i * k + j]]++;
+                    order[pos] = (int32_t)i;
+                    slots[i * k + j] = (int32_t)pos;
+                }
+        }
+        std::vector<size_t> send_rows(W, 0), recv_rows(W, 0);
+        size_t n_recv = 0;
+        for (size_t r = 0; r < W; r++) {
+            for (size_t x = r * per; x < (r + 1) * per; x++) send_rows[r] += (size_t)mine[x];
+            for (size_t x = (size_t)rank * per; x < ((size_t)rank + 1) * per; x++) recv_rows[r] += (size_t)all[r * E + x];
+            n_recv += recv_rows[r];
+        }
+        e = ep_send.reserve(std::max<size_t>(P, 1) * hdim * 4);
+        if (e == cudaSuccess) e = ep_recv.reserve(std::max<size_t>(n_recv, 1) * hdim * 4);
+        if (e == cudaSuccess) e = ep_out.reserve(std::max<size_t>(n_recv, 1) * hdim * 4);
+        if (e == cudaSuccess) e = ep_back.reserve(std::max<size_t>(P, 1) * hdim * 4);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(ep rows)");
+        if (P) {
+            e = cudaMemcpyAsync(d_order, order.data(), P * 4, cudaMemcpyHostToDevice, stream);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(d_slots, slots.data(), P * 4, cudaMemcpyHostToDevice, stream);
+            if (e == cudaSuccess) e = launch_gather_rows(x_dev_, d_order, P, hdim, (float*)ep_send.p, stream);
+            launches++;
+            if (e != cudaSuccess) return cuda_fail(e, "ep gather");
+        }
+        auto exchange = [&](const float* sendbuf, const std::vector<size_t>& srows, float* recvbuf, const std::vector<size_t>& rrows) -> int {
+            int rc = n.GroupStart();
+            size_t so = 0, ro = 0;
+            for (size_t r = 0; r < W && !rc; r++) {
+                if (srows[r]) rc = n.Send(sendbuf + so * hdim, srows[r] * hdim, NCCL_FLOAT32, (int)r, comm, stream);
+                if (!rc && rrows[r]) rc = n.Recv(recvbuf + ro * hdim, rrows[r] * hdim, NCCL_FLOAT32, (int)r, comm, stream);
+                so += srows[r];
+                ro += rrows[r];
+            }
+            int rc2 = n.GroupEnd();
+            return rc ? rc : rc2;
+        };
+        nrc = exchange((const float*)ep_send.p, send_rows, (float*)ep_recv.p, recv_rows);
+        if (nrc) return nccl_fail(nrc, "dispatch (ncclSend / ncclRecv)");
+        // 3. the local experts: rows from rank r arrive sorted by expert with the counts every rank now knows
+        if (n_recv) {
+            std::vector<int32_t> lid(n_recv);
+            std::vector<float> one(n_recv, 1.0f);
+            size_t at = 0;
+            for (size_t r = 0; r < W; r++)
+                for (size_t x = 0; x < per; x++)
+                    for (int32_t c = 0; c < all[r * E + (size_t)rank * per + x]; c++) lid[at++] = (int32_t)x;
+            e = cudaMemsetAsync(ep_out.p, 0, n_recv * hdim * 4, stream);
+            if (e != cudaSuccess) return cuda_fail(e, "ep memset");
+            int rc = moe_dev(handle, (const float*)ep_recv.p, n_recv, lid.data(), one.data(), 1, (float*)ep_out.p);
+            if (rc) return rc;
+        }
+        // 4. back, and the combine in route order
+        nrc = exchange((const float*)ep_out.p, recv_rows, (float*)ep_back.p, send_rows);
+        if (nrc) return nccl_fail(nrc, "combine (ncclSend / ncclRecv)");
+        if (P) {
+            float* d_w = (float*)(d_slots + P);
+            e = cudaMemcpyAsync(d_w, rw, P * 4, cudaMemcpyHostToDevice, stream);
+            if (e == cudaSuccess) e = launch_moe_combine((const float*)ep_back.p, d_slots, d_w, t, k, hdim, y_dev_, stream);
+            launches++;
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);  // the host vectors above go out of scope
+            if (e != cudaSuccess) return cuda_fail(e, "ep combine");
+        }
         return B2_OK;
     }
 
@@ -1043,6 +1227,8 @@ class Backend {
             cudaFree(kv.second.down);
         }
         moes.clear();
+        comm_free();
+        for (Scratch* sc : {&tp_stage, &tp_gather, &ep_idx, &ep_send, &ep_recv, &ep_out, &ep_back}) sc->release();
         moe_idx.release();
         moe_xg.release();
         moe_g.release();
@@ -1230,7 +1416,13 @@ B2_EXPORT int b2_matvec_dev(b2_ctx* ctx, b2_weight w, b2_weight up, const float*
 
 B2_EXPORT int b2_upload_moe(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* down, size_t experts, size_t h, size_t inter, b2_moe_handle* out) {
     LOCKED(ctx);
-    return ctx->be.upload_moe(gate_up, down, experts, h, inter, out);
+    return ctx->be.upload_moe(gate_up, nullptr, down, experts, h, inter, B2_ACT_SILU, 0.0f, out);
+}
+
+B2_EXPORT int b2_upload_moe_ex(b2_ctx* ctx, const b2_weight* gate_up, const b2_weight* up, const b2_weight* down, size_t experts, size_t h, size_t inter,
+                               int act, float act_limit, b2_moe_handle* out) {
+    LOCKED(ctx);
+    return ctx->be.upload_moe(gate_up, up, down, experts, h, inter, act, act_limit, out);
 }
 
 B2_EXPORT int b2_free_moe(b2_ctx* ctx, b2_moe_handle m) {
@@ -1270,6 +1462,37 @@ B2_EXPORT int b2_matvec_prepared_dev(b2_ctx* ctx, b2_weight w, b2_weight up, con
 B2_EXPORT int b2_check_status(b2_ctx* ctx) {
     LOCKED(ctx);
     return ctx->be.check_gemm_status();
+}
+
+B2_EXPORT int b2_comm_unique_id(void* id_out) {
+    const b2::NcclApi& n = b2::nccl_api();
+    if (!id_out) return B2_ERR_ARG;
+    if (!n.ok) return B2_DECLINED;
+    b2::NcclId id;
+    if (n.GetUniqueId(&id)) return B2_ERR_CUDA;
+    std::memcpy(id_out, &id, sizeof id);
+    return B2_OK;
+}
+
+B2_EXPORT int b2_comm_init(b2_ctx* ctx, int world, int rank, const void* id) {
+    LOCKED(ctx);
+    return ctx->be.comm_init(world, rank, id);
+}
+
+B2_EXPORT int b2_comm_free(b2_ctx* ctx) {
+    LOCKED(ctx);
+    return ctx->be.comm_free();
+}
+
+B2_EXPORT int b2_matmul_sharded(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float* y_dev) {
+    LOCKED(ctx);
+    return ctx->be.matmul_sharded(w_shard, x_dev, x_dtype, t, y_dev);
+}
+
+B2_EXPORT int b2_moe_ep(b2_ctx* ctx, b2_moe_handle m, size_t n_experts_global, const float* x_dev, size_t t, const int32_t* route_ids,
+                        const float* route_w, size_t k, float* y_dev) {
+    LOCKED(ctx);
+    return ctx->be.moe_ep(m, n_experts_global, x_dev, t, route_ids, route_w, k, y_dev);
 }
 
 B2_EXPORT int b2_decode_plan(b2_ctx* ctx, const b2_graph* graph, b2_plan* out) {

@@ -192,13 +192,20 @@ cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k,
 // unscale[row] = 1 / factor is handed to the GEMM, whose epilogue multiplies the row's results by it. lo_row0 > 0: two-term
 // rows, the second term lo_row0 rows below the first (see launch_to_f16).
 cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg_f16, float* unscale, size_t lo_row0, cudaStream_t st);
-cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a_f16, float* unscale, size_t lo_row0, cudaStream_t st);
+// kind: B2_ACT_* (0 SiLU, 1 tanh GELU, 2 SiLU with clamp `limit`).
+cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a_f16, float* unscale, size_t lo_row0, cudaStream_t st,
+                           int kind = 0, float limit = 0.0f);
 // The same with the routes as kernel arguments (at most GEMV_BATCH_MAX pairs): slot of pair (i, j) = i k + j, no row scale.
 struct SmallRoutes {
     float w[GEMV_BATCH_MAX];
 };
 cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
 cudaError_t launch_moe_combine(const float* o, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
+
+// out[r][h] = x[idx[r]][h] (f32), h a multiple of 4; and an all-gather's rank-major blocks g [world][t][n_local] into the
+// column blocks of y [t][world * n_local] (the tensor- and expert-parallel entry points).
+cudaError_t launch_gather_rows(const float* x, const int* idx, size_t rows, size_t h, float* out, cudaStream_t st);
+cudaError_t launch_scatter_blocks(const float* gathered, size_t world, size_t t, size_t n_local, float* y, cudaStream_t st);
 
 // ---- decode_ops.cu: the non-matmul ops of one decode token -------------------------------------------
 // Every kernel reads the step words `sp` on the device: sp[0] position of the token, sp[1] position of row 0

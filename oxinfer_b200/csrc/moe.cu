@@ -7,6 +7,8 @@
 //                  (moe_act, src/cuda.rs:300-316; SiLU with expf as on the reference's GPU path)
 //   moe_combine  : y[t] += sum_j w_j * o[slot(t, j)] in route order, multiply and add unfused
 //                  (moe_combine, src/cuda.rs:319-330)
+#include <algorithm>
+
 #include "kernels.h"
 
 namespace b2 {
@@ -132,8 +134,22 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict
 // padding). One CTA per row; the row is read once (a thread keeps its products in registers between the maximum and the
 // store) when inter <= 256 * 4 * ACT_KEEP.
 constexpr int ACT_KEEP = 2;
+// kind (MoeAct, src/gpu.rs:36-54; the arithmetic of the reference's moe_act, src/cuda.rs:300-316): 0 SiLU, 1 tanh GELU
+// written as g * sigmoid(1.5957692 (g + 0.044715 g^3)), 2 SiLU with the clamp silu(min(g, l)) * clamp(u, -l, l).
+__device__ __forceinline__ float gated_act(float g, float u, int kind, float limit) {
+    if (kind == 1) {
+        const float k = 1.5957692f * (g + 0.044715f * g * g * g);
+        return g / (1.0f + expf(-k)) * u;
+    }
+    if (kind == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ g, const int* __restrict__ src, int inter, __half* __restrict__ a,
-                                                      float* __restrict__ unscale, size_t lo_off) {
+                                                      float* __restrict__ unscale, size_t lo_off, int kind, float limit) {
     __shared__ float red[8];
     const size_t row = blockIdx.x;
     __half* ar = a + row * inter;
@@ -150,10 +166,10 @@ __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ 
     auto act4 = [&](int c) {
         const float4 gate = *(const float4*)(gr + c), up = *(const float4*)(gr + inter + c);
         float4 r;
-        r.x = gate.x / (1.0f + expf(-gate.x)) * up.x;
-        r.y = gate.y / (1.0f + expf(-gate.y)) * up.y;
-        r.z = gate.z / (1.0f + expf(-gate.z)) * up.z;
-        r.w = gate.w / (1.0f + expf(-gate.w)) * up.w;
+        r.x = gated_act(gate.x, up.x, kind, limit);
+        r.y = gated_act(gate.y, up.y, kind, limit);
+        r.z = gated_act(gate.z, up.z, kind, limit);
+        r.w = gated_act(gate.w, up.w, kind, limit);
         return r;
     };
     float4 v[ACT_KEEP];
@@ -221,7 +237,38 @@ __global__ void moe_combine_small_kernel(const float* __restrict__ o, SmallRoute
     y[(size_t)tok * h + c] = acc;
 }
 
+// out[r][h] = x[idx[r]][h] (f32 rows gathered by index), and the all-gather's rank-major blocks into column blocks.
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx, int h, float* __restrict__ out) {
+    const size_t r = blockIdx.x;
+    const float4* in = (const float4*)(x + (size_t)idx[r] * h);
+    float4* o = (float4*)(out + r * h);
+    for (int i = threadIdx.x; i < h / 4; i += blockDim.x) o[i] = in[i];
+}
+__global__ void scatter_blocks_kernel(const float* __restrict__ g, int t, size_t nl, size_t world, float* __restrict__ y) {
+    // g [world][t][nl] -> y [t][world * nl]
+    const size_t n = (size_t)world * t * nl;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / ((size_t)t * nl), rem = i - r * (size_t)t * nl, tok = rem / nl, c = rem - tok * nl;
+        y[tok * world * nl + r * nl + c] = g[i];
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_gather_rows(const float* x, const int* idx, size_t rows, size_t h, float* out, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    if (h % 4) return cudaErrorInvalidValue;
+    gather_rows_kernel<<<(unsigned)rows, 256, 0, st>>>(x, idx, (int)h, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_blocks(const float* gathered, size_t world, size_t t, size_t n_local, float* y, cudaStream_t st) {
+    const size_t n = world * t * n_local;
+    if (n == 0) return cudaSuccess;
+    const unsigned grid = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 16);
+    scatter_blocks_kernel<<<grid, 256, 0, st>>>(gathered, (int)t, n_local, world, y);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st) {
     if (t * k > GEMV_BATCH_MAX) return cudaErrorInvalidValue;
@@ -242,9 +289,10 @@ cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* unscale, size_t lo_row0, cudaStream_t st) {
+cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* unscale, size_t lo_row0, cudaStream_t st,
+                           int kind, float limit) {
     if (inter % 256) return cudaErrorInvalidValue;
-    moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter);
+    moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter, kind, limit);
     return cudaGetLastError();
 }
 

@@ -94,6 +94,44 @@ def test_moe_rows_of_very_different_magnitude(backend, fmt):
     assert row_err(y, O.moe_forward(gu, dn, h, inter, x, ids, w, exact=True)) < TOL
 
 
+def _layer_f64(gate, up, down, x, ids, w, act, limit):
+    """y[i] = sum_j w_ij down_e(act(gate_e x_i) * up_e x_i) in f64 over the bit-exact dequantized weights (MoeAct, src/gpu.rs:36-54)."""
+    t, k = ids.shape
+    y = np.zeros((t, down[0].n_out), np.float64)
+    for i in range(t):
+        for j in range(k):
+            e = int(ids[i, j])
+            g, u = gate[e].matmul_f64(x[i : i + 1])[0], up[e].matmul_f64(x[i : i + 1])[0]
+            if act == 1:
+                a = g / (1.0 + np.exp(-1.5957692 * (g + 0.044715 * g**3))) * u
+            else:
+                if act == 2:
+                    g, u = np.minimum(g, limit), np.clip(u, -limit, limit)
+                a = g / (1.0 + np.exp(-g)) * u
+            y[i] += float(w[i, j]) * (down[e].dequantize_rows().astype(np.float64) @ a)
+    return y
+
+
+@pytest.mark.parametrize("act,limit", [(0, 0.0), (1, 0.0), (2, 7.0)])
+@pytest.mark.parametrize("t", [3, 90])
+def test_separate_up_matrices_and_the_other_activations(backend, act, limit, t):
+    """upload_moe with the gate and up projections apart (GGUF checkpoints store them so, src/gpu.rs:200-215) and the gated
+    activations the reference's CUDA backend runs besides SiLU: tanh GELU and the clamped SiLU (src/cuda.rs:300-316, 896-906)."""
+    n_experts, k, h, inter = 6, 2, 512, 256
+    refs = [(synth.mlx4(inter, h, 760 + 3 * e), synth.mlx4(inter, h, 761 + 3 * e), synth.mlx4(h, inter, 762 + 3 * e)) for e in range(n_experts)]
+    devs = [[backend.upload(r[i], *(s)) for r in refs] for i, s in enumerate([(inter, h), (inter, h), (h, inter)])]
+    moe = backend.upload_moe(devs[0], devs[2], h, inter, up=devs[1], act=act, act_limit=limit)
+    assert moe is not None, backend.last_declined
+    mats = [[oracle_matrix(r[i], *(s)) for r in refs] for i, s in enumerate([(inter, h), (inter, h), (h, inter)])]
+    _, ids, w = routes(t, n_experts, k, 763 + t)
+    x = synth.activations(t, h, 764) * np.float32(0.25)    # gate values around the clamp, not far beyond it
+    y = np.zeros((t, h), np.float32)
+    assert backend.moe(x, ids, w, moe, y)
+    assert row_err(y, _layer_f64(mats[0], mats[1], mats[2], x, ids, w, act, limit)) < TOL
+    # an activation the device does not run is declined, as the reference's backend declines it
+    assert backend.upload_moe(devs[0], devs[2], h, inter, up=devs[1], act=3) is None
+
+
 def test_route_topk_matches_oracle(backend):
     t, n, k = 70, 128, 8
     logits, ids, w = routes(t, n, k, 720)
