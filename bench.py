@@ -449,6 +449,81 @@ def moe_extras(be, torch, peaks):
     return out
 
 
+def moe_ep_extras(be, torch, dist, rank, world):
+    """Config 3 expert-parallel across the ranks (one process per GPU): 128 experts in equal contiguous shares, the token batch
+    split evenly over the ranks, every (token, route) pair sent to the rank that owns its expert and back (b2_moe_ep: NCCL
+    all-gather of the counts, grouped send / receive of the rows, local experts, ordered combine). Times one layer call at
+    512 and 4096 tokens (whole batch over all ranks), slowest rank; before timing, rank 0's rows are checked against the
+    one-GPU layer over all experts (bit for bit)."""
+    import numpy as np
+
+    import oxinfer_b200 as ob
+    from oxinfer_b200 import synth
+
+    E, K, H, I = 128, 8, 2048, 768
+    assert E % world == 0
+    box = [ob.Backend.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    be.comm_init(world, rank, box[0])
+    protos = [(synth.mlx4(2 * I, H, 900 + i), synth.mlx4(H, I, 950 + i)) for i in range(8)]
+    pe = E // world
+    gu = [be.upload(protos[e % 8][0], 2 * I, H) for e in range(rank * pe, (rank + 1) * pe)]
+    dn = [be.upload(protos[e % 8][1], H, I) for e in range(rank * pe, (rank + 1) * pe)]
+    local = be.upload_moe(gu, dn, H, I)
+    for d in gu + dn:
+        d.free()
+    full = None
+    if rank == 0:
+        agu = [be.upload(protos[e % 8][0], 2 * I, H) for e in range(E)]
+        adn = [be.upload(protos[e % 8][1], H, I) for e in range(E)]
+        full = be.upload_moe(agu, adn, H, I)
+        for d in agu + adn:
+            d.free()
+    out = {}
+    rng = np.random.default_rng(3)
+    bias = rng.standard_normal(E).astype(np.float32)
+    for t in (512, 4096):
+        logits = rng.standard_normal((t, E)).astype(np.float32) + bias
+        ids = np.argsort(-logits, axis=1, kind="stable")[:, :K].astype(np.int32)
+        top = np.take_along_axis(logits, ids, axis=1)
+        w = np.exp(top - top[:, :1])
+        w = (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
+        xs = synth.activations(t, H, 77 + t)
+        share = t // world
+        t0, t1 = rank * share, (rank + 1) * share
+        x = torch.from_numpy(xs[t0:t1]).cuda()
+        y = torch.zeros((share, H), device="cuda")
+        be.moe_ep(x, ids[t0:t1], w[t0:t1], local, E, y)
+        torch.cuda.synchronize()
+        same = 1
+        if rank == 0:
+            want = torch.zeros((share, H), device="cuda")
+            be.moe_dev(x, ids[t0:t1], w[t0:t1], full, want)
+            torch.cuda.synchronize()
+            same = int(torch.equal(want.view(torch.int32), y.view(torch.int32)))
+        flag = torch.tensor([same], device="cuda", dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        n = 5
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            be.moe_ep(x, ids[t0:t1], w[t0:t1], local, E, y)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / n], device="cuda", dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        us = float(ms.item()) * 1e3
+        flop = 6.0 * t * K * H * I
+        out[f"t{t}"] = {"us": us, "tflops": flop / us / 1e6, "tokens_per_rank": share,
+                        "parity": "bit-identical to the one-GPU layer (rank 0's rows)" if int(flag.item()) == 1 else "MISMATCH"}
+    out["note"] = (f"ep{world}: {pe} experts per rank; per call an all-gather of counts (one host read), two grouped send / receive exchanges of "
+                   "f32 rows, the local grouped-expert kernels, the ordered combine")
+    be.comm_free()
+    return out
+
+
 def fp8_extras(be, torch, peaks):
     """Config 4: FP8 e4m3 128x128-block-scaled weights N=28672 x K=12288, f16 activations on the device, M = 128 and 8192
     through the tensor-core GEMM (M = 1 is the f8 case of extra.gemv at another shape). FP8 keeps the reference's
@@ -838,6 +913,12 @@ def run_b200(args, rank, world, local_rank):
             dec_tp = decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist, check_tokens=8)
         except Exception as e:
             dec_tp = {"error": str(e)}
+    ep = None
+    if world > 1 and args.section == "all" and 128 % world == 0:   # collective: the expert-parallel MoE layer
+        try:
+            ep = moe_ep_extras(be, torch, dist, rank, world)
+        except Exception as e:
+            ep = {"error": str(e)}
     if rank == 0:
         n_timed = args.steps * repeats
         ms = ms_total / n_timed
@@ -889,6 +970,8 @@ def run_b200(args, rank, world, local_rank):
                     line["extra"][name + "_error"] = str(e)
         if dec_tp is not None:
             line["extra"] = {"decode": dec_tp}
+        if ep is not None:
+            line.setdefault("extra", {})["moe_ep"] = ep
         line["summary"] = summarize(line)
         emit(json.dumps(line))
     if world > 1:
@@ -918,6 +1001,11 @@ def summarize(line: dict) -> dict:
     for k in ("t1", "t64", "t512", "t4096"):
         if k in m:
             out["moe_" + k + "_us"] = round(m[k]["us"], 1)
+    mep = ex.get("moe_ep") or {}
+    for k in ("t512", "t4096"):
+        if k in mep:
+            out["moe_ep_" + k + "_us"] = round(mep[k]["us"], 1)
+            out["moe_ep_parity"] = mep[k]["parity"]
     f = ex.get("fp8") or {}
     if "m8192" in f:
         out["fp8_m8192_tflops"] = round(f["m8192"]["tflops"], 0)

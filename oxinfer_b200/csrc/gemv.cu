@@ -300,8 +300,28 @@ gemv_f8_mma_kernel(WeightDev w, const float* __restrict__ x, float* __restrict__
     const int kb0 = (int)((long long)nblk * warp / GEMV_WARPS), kb1 = (int)((long long)nblk * (warp + 1) / GEMV_WARPS);
     const int ch0 = 2 * kb0, ch1 = 2 * kb1;  // chunks of 64 k
     pdl_wait();
+    // x times a power of two that brings its largest magnitude into [2^14, 2^15): vectors of any magnitude stay inside f16's
+    // range and out of its subnormals; the results are scaled back (exactly) when they are written
+    float mx = 0.0f;
+    for (int i = threadIdx.x; i < K; i += GEMV_THREADS) mx = fmaxf(mx, fabsf(x[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) part[warp][0] = mx;
+    __syncthreads();
+    mx = part[0][0];
+#pragma unroll
+    for (int i = 1; i < GEMV_WARPS; i++) mx = fmaxf(mx, part[i][0]);
+    __syncthreads();
+    float xscale = 1.0f, xinv = 1.0f;
+    if (mx > 0.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);
+        const int up = min(100, max(-100, 15 - e));
+        xscale = ldexpf(1.0f, up);
+        xinv = ldexpf(1.0f, -up);
+    }
     for (int i = threadIdx.x; i < K; i += GEMV_THREADS) {
-        const float v = x[i];
+        const float v = x[i] * xscale;
         const __half h = __float2half_rn(v);
         xh[i] = h;
         xl[i] = __float2half_rn(v - __half2float(h));
@@ -367,6 +387,7 @@ gemv_f8_mma_kernel(WeightDev w, const float* __restrict__ x, float* __restrict__
                 float v = 0.0f;
 #pragma unroll
                 for (int wv = 0; wv < GEMV_WARPS; wv++) v += part[wv][threadIdx.x];
+                v *= xinv;
                 float* o = y + r;
                 if (mode == B2_MODE_STORE)
                     *o = v;

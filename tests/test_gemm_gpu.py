@@ -33,7 +33,7 @@ def test_q4k_matmul_matches_oracle(backend, shape):
 
 
 @pytest.mark.parametrize("fmt", ["q4_k", "mlx4", "f8_e4m3"])
-@pytest.mark.parametrize("t", [12, 100, 300])
+@pytest.mark.parametrize("t", [4, 12, 100, 300])
 def test_matmul_rows_of_very_different_magnitude(backend, fmt, t):
     """Token rows scaled by 1e-3, 1, 300 and 2e5, the magnitudes of the reference's input() (src/cuda.rs:1579-1700): a row
     of 2e5 would overflow f16 and a row of 1e-3 would lose bits to its subnormals, so every row is multiplied by a power
