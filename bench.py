@@ -308,6 +308,45 @@ def gemv_extras(be, torch, peaks, steps, only=None, use_graph=True):
                 out[name]["reference_cuda_kernel_error"] = str(e)
         for d in devs:
             d.free()
+    if not only or "other" in only:
+        out["other_formats"] = other_format_gemv(be, torch, peaks, steps)
+    return out
+
+
+def other_format_gemv(be, torch, peaks, steps):
+    """The generic (untuned) matrix-vector kernel of the other GGUF block formats at 8192 x 4096: algorithmic bytes / CUDA-event
+    time over rotating weight copies larger than L2, host-launched back to back."""
+    from oxinfer_b200 import synth
+
+    out = {}
+    n_out, n_in = 8192, 4096
+    x = torch.randn(n_in, device="cuda", dtype=torch.float32)
+    y = torch.empty(n_out, device="cuda", dtype=torch.float32)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for kind, name in synth.OTHER_NAMES.items():
+        ref = synth.other_blocks(kind, n_out, n_in, 9)
+        dev0 = be.upload(ref, n_out, n_in)
+        if dev0 is None:
+            out[name] = {"declined": be.last_declined}
+            continue
+        wbytes = dev0.bytes()
+        copies = max(2, min(48, -(-2 * L2_BYTES // wbytes)))
+        devs = [dev0] + [be.upload(ref, n_out, n_in) for _ in range(copies - 1)]
+        n = max(steps, 2 * copies)
+        for i in range(3):
+            be.matvec_dev(devs[i % copies], x, y)
+        torch.cuda.synchronize()
+        ev[0].record()
+        for i in range(n):
+            be.matvec_dev(devs[i % copies], x, y)
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) * 1e3 / n
+        algo = wbytes + 4 * n_in + 4 * n_out
+        out[name] = {"us_per_gemv": us, "bytes": algo, "gbs": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peaks["hbm_gbs"],
+                     "kernel": "gemv_other_kernel", "shape": f"{n_out}x{n_in}"}
+        for d in devs:
+            d.free()
     return out
 
 

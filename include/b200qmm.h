@@ -41,6 +41,19 @@ extern "C" {
 #define B2_FMT_Q4_K 12     /* GGUF Q4_K  (src/ggml.rs:750-773) */
 #define B2_FMT_Q6_K 14     /* GGUF Q6_K  (src/ggml.rs:774-793) */
 #define B2_FMT_F8E4M3 4096 /* FP8 e4m3fn + f32 block scales (src/ggml.rs:240-293,433-443) */
+/* The other GGUF block formats b2_upload_gguf takes (ids of src/ggml.rs:42-93; decode arms src/ggml.rs:665-706, 713-773,
+ * 915-960): kept as raw GGUF rows on the device, dequantized bit-exactly, multiplied by one generic (untuned) matrix-vector
+ * kernel at any number of tokens, f32 activations and results; no MoE / decode-plan use. */
+#define B2_FMT_Q4_0 2
+#define B2_FMT_Q4_1 3
+#define B2_FMT_Q5_0 6
+#define B2_FMT_Q5_1 7
+#define B2_FMT_Q2_K 10
+#define B2_FMT_Q3_K 11
+#define B2_FMT_Q5_K 13
+#define B2_FMT_IQ4_NL 20
+#define B2_FMT_IQ4_XS 23
+#define B2_FMT_MXFP4 39
 
 /* Element types of device-resident activations / results. */
 #define B2_F32 0
@@ -135,7 +148,7 @@ int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const
 int b2_upload_q4(b2_ctx* ctx, const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in,
                  b2_weight* out);
 /* `Backend::upload` for WeightRef::Gguf (declined by the reference at src/cuda.rs:642): raw GGUF
- * rows of `fmt` (B2_FMT_Q4_K / Q6_K / Q8_0 / F8E4M3). For F8E4M3, `block_scales` is
+ * rows of `fmt` (B2_FMT_Q4_K / Q6_K / Q8_0 / F8E4M3, or one of the other block formats above). For F8E4M3, `block_scales` is
  * `[ceil(n_out/bs_rows)][ceil(n_in/bs_cols)]` f32 (BlockScales, src/ggml.rs:250-256), else NULL. */
 int b2_upload_gguf(b2_ctx* ctx, int fmt, const uint8_t* data, size_t n_out, size_t n_in, const float* block_scales, size_t bs_rows,
                    size_t bs_cols, b2_weight* out);

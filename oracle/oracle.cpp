@@ -122,11 +122,23 @@ void parallel_for(size_t n, int threads, const std::function<void(size_t)>& f) {
 // ---------------------------------------------------------------------------------------------
 // GGUF kinds (ids of src/ggml.rs:42-93).
 // ---------------------------------------------------------------------------------------------
-enum Kind : int { K_F32 = 0, K_F16 = 1, K_Q8_0 = 8, K_Q4_K = 12, K_Q6_K = 14, K_BF16 = 30, K_F8E4M3 = 0x1000 };
+enum Kind : int {
+    K_F32 = 0, K_F16 = 1, K_Q4_0 = 2, K_Q4_1 = 3, K_Q5_0 = 6, K_Q5_1 = 7, K_Q8_0 = 8, K_Q2_K = 10, K_Q3_K = 11, K_Q4_K = 12, K_Q5_K = 13,
+    K_Q6_K = 14, K_IQ4_NL = 20, K_IQ4_XS = 23, K_BF16 = 30, K_MXFP4 = 39, K_F8E4M3 = 0x1000
+};
+// The block kinds whose matrix products this file runs through the f32 route only (decoded bit-exactly here).
+inline bool other_block_kind(int kind) {
+    switch (kind) {
+        case K_Q4_0: case K_Q4_1: case K_Q5_0: case K_Q5_1: case K_Q2_K: case K_Q3_K: case K_Q5_K: case K_IQ4_NL: case K_IQ4_XS: case K_MXFP4: return true;
+        default: return false;
+    }
+}
 
 inline size_t block_size(int kind) {  // src/ggml.rs:173-185
     switch (kind) {
+        case K_Q4_0: case K_Q4_1: case K_Q5_0: case K_Q5_1: case K_IQ4_NL: case K_MXFP4:
         case K_Q8_0: return 32;
+        case K_Q2_K: case K_Q3_K: case K_Q5_K: case K_IQ4_XS:
         case K_Q4_K:
         case K_Q6_K: return 256;
         default: return 1;
@@ -138,6 +150,15 @@ inline size_t type_size(int kind) {  // src/ggml.rs:187-215
         case K_F16:
         case K_BF16: return 2;
         case K_Q8_0: return 34;
+        case K_Q4_0: case K_IQ4_NL: return 18;
+        case K_Q4_1: return 20;
+        case K_Q5_0: return 22;
+        case K_Q5_1: return 24;
+        case K_Q2_K: return 84;
+        case K_Q3_K: return 110;
+        case K_Q5_K: return 176;
+        case K_IQ4_XS: return 136;
+        case K_MXFP4: return 17;
         case K_Q4_K: return 144;
         case K_Q6_K: return 210;
         case K_F8E4M3: return 1;
@@ -158,6 +179,31 @@ inline void scale_min_k4(int j, const uint8_t* q, uint8_t* sc, uint8_t* m) {
         *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
     }
 }
+
+inline uint32_t u32at(const uint8_t* b, size_t i) { return (uint32_t)b[i] | ((uint32_t)b[i + 1] << 8) | ((uint32_t)b[i + 2] << 16) | ((uint32_t)b[i + 3] << 24); }
+
+// src/ggml.rs:466-474 (e8m0_half): 2^(e - 128), the subnormal cases from their bit patterns.
+inline float e8m0_half(uint8_t e) { return bits_f32(e < 2 ? (0x00200000u << e) : (((uint32_t)e - 1) << 23)); }
+
+// src/ggml.rs:511-530 (q3k_scales): sixteen 6-bit scales from 12 bytes, still offset by 32.
+inline void q3k_scales(const uint8_t* s, int8_t* out) {
+    const uint32_t k1 = 0x03030303u, k2 = 0x0f0f0f0fu;
+    const uint32_t a0 = u32at(s, 0), a1 = u32at(s, 4), tmp = u32at(s, 8);
+    const uint32_t aux[4] = {(a0 & k2) | ((tmp & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4), ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4),
+                             ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)};
+    for (int i = 0; i < 4; i++)
+        for (int j = 0; j < 4; j++) out[4 * i + j] = (int8_t)(uint8_t)(aux[i] >> (8 * j));
+}
+
+// src/ggml.rs:544-547 (iq4xs_scale)
+inline int iq4xs_scale(const uint8_t* b, int ib) {
+    const uint32_t sh = (uint32_t)b[2] | ((uint32_t)b[3] << 8);
+    return (int)(((b[4 + ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+}
+
+// ggml's published code books: the non-linear 4-bit values of IQ4_NL / IQ4_XS and the doubled E2M1 values of MXFP4.
+const int8_t KV_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+const int8_t KV_MXFP4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
 
 // src/ggml.rs:258-271
 inline float e4m3_to_f32(uint8_t b) {
@@ -194,10 +240,102 @@ void dequantize_row(int kind, const uint8_t* src, float* out, size_t n) {
         if (kind == K_Q8_0) {  // src/ggml.rs:707-712
             float d = f16at(b, 0);
             for (int j = 0; j < 32; j++) y[j] = (float)(int8_t)b[2 + j] * d;
-        } else if (kind == K_Q4_K) {  // src/ggml.rs:750-773
+        } else if (kind == K_Q4_0) {  // src/ggml.rs:673-679
+            float d = f16at(b, 0);
+            for (int j = 0; j < 16; j++) {
+                y[j] = (float)((int)(b[2 + j] & 0xF) - 8) * d;
+                y[j + 16] = (float)((int)(b[2 + j] >> 4) - 8) * d;
+            }
+        } else if (kind == K_Q4_1) {  // src/ggml.rs:680-686
+            float d = f16at(b, 0), m = f16at(b, 2);
+            for (int j = 0; j < 16; j++) {
+                float p0 = (float)(b[4 + j] & 0xF) * d, p1 = (float)(b[4 + j] >> 4) * d;
+                y[j] = p0 + m;
+                y[j + 16] = p1 + m;
+            }
+        } else if (kind == K_Q5_0 || kind == K_Q5_1) {  // src/ggml.rs:687-706
+            const bool one = kind == K_Q5_1;
+            float d = f16at(b, 0), m = one ? f16at(b, 2) : 0.0f;
+            const uint32_t qh = u32at(b, one ? 4 : 2);
+            const uint8_t* qs = b + (one ? 8 : 6);
+            for (int j = 0; j < 16; j++) {
+                const uint32_t h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
+                const int v0 = (int)((qs[j] & 0xF) | h0), v1 = (int)((qs[j] >> 4) | h1);
+                if (one) {
+                    float p0 = (float)v0 * d, p1 = (float)v1 * d;
+                    y[j] = p0 + m;
+                    y[j + 16] = p1 + m;
+                } else {
+                    y[j] = (float)(v0 - 16) * d;
+                    y[j + 16] = (float)(v1 - 16) * d;
+                }
+            }
+        } else if (kind == K_Q2_K) {  // src/ggml.rs:713-729
+            float d = f16at(b, 80), mn = f16at(b, 82);
+            const uint8_t* sc = b;
+            const uint8_t* qs = b + 16;
+            for (int nn = 0; nn < 2; nn++) {
+                const uint8_t* q = qs + 32 * nn;
+                for (int j = 0; j < 4; j++)
+                    for (int h = 0; h < 2; h++) {
+                        const uint8_t s = sc[8 * nn + 2 * j + h];
+                        float dl = d * (float)(s & 0xF), ml = mn * (float)(s >> 4);
+                        float* o = y + 128 * nn + 32 * j + 16 * h;
+                        for (int l = 0; l < 16; l++) {
+                            float p = dl * (float)((q[16 * h + l] >> (2 * j)) & 3);
+                            o[l] = p - ml;
+                        }
+                    }
+            }
+        } else if (kind == K_Q3_K) {  // src/ggml.rs:730-749
+            float d = f16at(b, 108);
+            const uint8_t* hm = b;
+            const uint8_t* qs = b + 32;
+            int8_t sc[16];
+            q3k_scales(b + 96, sc);
+            for (int nn = 0; nn < 2; nn++) {
+                const uint8_t* q = qs + 32 * nn;
+                for (int j = 0; j < 4; j++) {
+                    const uint8_t msk = (uint8_t)(1u << (4 * nn + j));
+                    for (int h = 0; h < 2; h++) {
+                        float dl = d * (float)((int)sc[8 * nn + 2 * j + h] - 32);
+                        float* o = y + 128 * nn + 32 * j + 16 * h;
+                        for (int l = 0; l < 16; l++) {
+                            const int i = 16 * h + l;
+                            const int v = (int)((q[i] >> (2 * j)) & 3) - ((hm[i] & msk) ? 0 : 4);
+                            o[l] = dl * (float)v;
+                        }
+                    }
+                }
+            }
+        } else if (kind == K_IQ4_NL) {  // src/ggml.rs:915-921
+            float d = f16at(b, 0);
+            for (int j = 0; j < 16; j++) {
+                y[j] = d * (float)KV_IQ4NL[b[2 + j] & 0xF];
+                y[j + 16] = d * (float)KV_IQ4NL[b[2 + j] >> 4];
+            }
+        } else if (kind == K_MXFP4) {  // src/ggml.rs:922-928
+            float d = e8m0_half(b[0]);
+            for (int j = 0; j < 16; j++) {
+                y[j] = d * (float)KV_MXFP4[b[1 + j] & 0xF];
+                y[j + 16] = d * (float)KV_MXFP4[b[1 + j] >> 4];
+            }
+        } else if (kind == K_IQ4_XS) {  // src/ggml.rs:948-958
+            float d = f16at(b, 0);
+            for (int ib = 0; ib < 8; ib++) {
+                float dl = d * (float)iq4xs_scale(b, ib);
+                const uint8_t* q = b + 8 + 16 * ib;
+                for (int j = 0; j < 16; j++) {
+                    y[32 * ib + j] = dl * (float)KV_IQ4NL[q[j] & 0xF];
+                    y[32 * ib + j + 16] = dl * (float)KV_IQ4NL[q[j] >> 4];
+                }
+            }
+        } else if (kind == K_Q4_K || kind == K_Q5_K) {  // src/ggml.rs:750-773
+            const bool five = kind == K_Q5_K;
             float d = f16at(b, 0), mn = f16at(b, 2);
             const uint8_t* sc = b + 4;
-            const uint8_t* qs = b + 16;
+            const uint8_t* qh = b + 16;
+            const uint8_t* qs = b + (five ? 48 : 16);
             for (int j = 0; j < 4; j++) {
                 const uint8_t* q = qs + 32 * j;
                 for (int h = 0; h < 2; h++) {
@@ -207,6 +345,7 @@ void dequantize_row(int kind, const uint8_t* src, float* out, size_t n) {
                     float* o = y + 64 * j + 32 * h;
                     for (int l = 0; l < 32; l++) {
                         uint8_t v = (q[l] >> (4 * h)) & 0xF;
+                        if (five && (qh[l] & (1 << (2 * j + h)))) v += 16;
                         float p = d1 * (float)v;
                         o[l] = p - m1;
                     }
@@ -267,7 +406,10 @@ struct Matrix {
         return format == 0 ? q.size() + scales.size() * 2 + offsets.size() * 2 : data.size();
     }
     // "dense" formats take the f32 path at every token count (src/ggml.rs:220-225).
-    bool dense() const { return format == 1 && (kind == K_F8E4M3 || kind == K_F32 || kind == K_F16 || kind == K_BF16); }
+    // The other block kinds also take it here: the reference multiplies them through an int8 block decode
+    // (src/ggml.rs:965-1130) that this file does not restate; their products are checked against the f64 product of the
+    // bit-exactly decoded weights.
+    bool dense() const { return format == 1 && (kind == K_F8E4M3 || kind == K_F32 || kind == K_F16 || kind == K_BF16 || other_block_kind(kind)); }
 };
 
 // src/quant.rs:586-606
@@ -792,7 +934,7 @@ ORC_API uint64_t orc_fnv_f32(const float* v, size_t n) {
     return h;
 }
 
-// src/ggml.rs:1446-1496 (random_blocks), arms F32 / F16 / BF16 / Q4_K / Q6_K / Q8_0.
+// src/ggml.rs:1446-1496 (random_blocks), the arms of every kind this file decodes.
 ORC_API void orc_random_blocks(int kind, size_t nb, uint64_t* seed, uint8_t* v) {
     size_t ts = type_size(kind);
     for (size_t i = 0; i < nb * ts; i++) v[i] = (uint8_t)lcg(seed);
@@ -823,13 +965,27 @@ ORC_API void orc_random_blocks(int kind, size_t nb, uint64_t* seed, uint8_t* v) 
                 b[1] = (uint8_t)(h >> 8);
                 break;
             }
+            case K_Q4_1:
+            case K_Q5_1: {
+                put_f16(b, 0, rnd(false));
+                put_f16(b, 2, rnd(true) * 8.0f);
+                break;
+            }
+            case K_Q2_K: {
+                put_f16(b, 80, rnd(false));
+                put_f16(b, 82, rnd(false));
+                break;
+            }
+            case K_Q3_K: put_f16(b, 108, rnd(true)); break;
+            case K_Q5_K:
             case K_Q4_K: {
                 put_f16(b, 0, rnd(false));
                 put_f16(b, 2, rnd(false));
                 break;
             }
             case K_Q6_K: put_f16(b, 208, rnd(true)); break;
-            default: put_f16(b, 0, rnd(true)); break;  // Q8_0
+            case K_MXFP4: b[0] = (uint8_t)(118 + lcg(seed) % 7); break;
+            default: put_f16(b, 0, rnd(true)); break;  // Q8_0, Q4_0, Q5_0, IQ4_NL, IQ4_XS
         }
     }
 }

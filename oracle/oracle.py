@@ -21,6 +21,10 @@ _LIB_PATH = _HERE / "liboracle.so"
 
 # GGUF type ids (src/ggml.rs:42-93)
 F32, F16, Q8_0, Q4_K, Q6_K, BF16, F8E4M3 = 0, 1, 8, 12, 14, 30, 0x1000
+Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS, MXFP4 = 2, 3, 6, 7, 10, 11, 13, 20, 23, 39
+OTHER_KINDS = (Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS, MXFP4)
+KIND_NAMES = {Q4_0: "q4_0", Q4_1: "q4_1", Q5_0: "q5_0", Q5_1: "q5_1", Q2_K: "q2_k", Q3_K: "q3_k", Q5_K: "q5_k", IQ4_NL: "iq4_nl",
+              IQ4_XS: "iq4_xs", MXFP4: "mxfp4", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
 
 # FNV-1a-64 of the f32 bits of dequantize_row(kind, fixture(kind)), from src/ggml.rs:1547-1577.
 REF_HASHES = {
@@ -30,6 +34,16 @@ REF_HASHES = {
     Q4_K: 0xDE4DA39C1D9096B2,
     Q6_K: 0x20A51CC0FEAAE638,
     Q8_0: 0x3199BE3DEDDF5C1A,
+    Q4_0: 0xC2AC60F0D9D22BC8,
+    Q4_1: 0x8A49B60459C03FA2,
+    Q5_0: 0x46640E791FEAF19F,
+    Q5_1: 0xB0FD98E61B74D61D,
+    Q2_K: 0x44B0A081C4B9C71C,
+    Q3_K: 0x0C8FA80FD8589B8A,
+    Q5_K: 0x4BE2F59B66CC7042,
+    IQ4_NL: 0x9DE348F3E6E39671,
+    IQ4_XS: 0xF26FD3824913AF96,
+    MXFP4: 0xF64D0292F050737D,
 }
 FIXTURE_ELEMS = 1024  # src/ggml.rs:1535
 

@@ -16,6 +16,9 @@ HEADER = PKG_DIR.parent / "include" / "b200qmm.h"
 
 OK, DECLINED, ERR_CUDA, ERR_ARG, ERR_NOMEM, ERR_TIMEOUT = 0, 1, -1, -2, -3, -4
 FMT_MLX4, FMT_Q8_0, FMT_Q4_K, FMT_Q6_K, FMT_F8E4M3 = 1, 8, 12, 14, 4096
+# the other GGUF block formats (raw rows on the device, one generic matrix-vector kernel)
+FMT_Q4_0, FMT_Q4_1, FMT_Q5_0, FMT_Q5_1, FMT_Q2_K, FMT_Q3_K, FMT_Q5_K, FMT_IQ4_NL, FMT_IQ4_XS, FMT_MXFP4 = 2, 3, 6, 7, 10, 11, 13, 20, 23, 39
+OTHER_FORMATS = (FMT_Q4_0, FMT_Q4_1, FMT_Q5_0, FMT_Q5_1, FMT_Q2_K, FMT_Q3_K, FMT_Q5_K, FMT_IQ4_NL, FMT_IQ4_XS, FMT_MXFP4)
 F32, BF16, F16 = 0, 1, 2
 MODE_STORE, MODE_ADD, MODE_SILU_PAIR, MODE_GELU_PAIR, MODE_ADD_GATED = 0, 1, 2, 3, 4
 

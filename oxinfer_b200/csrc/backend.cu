@@ -12,6 +12,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "dq_other.cuh"
 #include "kernels.h"
 #include "nccl_dyn.h"
 #include "plan.h"
@@ -295,6 +296,13 @@ class Backend {
                 wt.dev.bs_ncb = ncb;
                 wt.bytes += ncb * nrb * 4;
             }
+        } else if (fmt_is_other(fmt)) {
+            // the other GGUF block formats stay as they are in the file (raw rows) and run through the generic kernels
+            if (n_in % other_block_size(fmt) || n_in % 32) return fail(B2_DECLINED, "[b200qmm: format %d needs n_in to be a multiple of its block size]", fmt);
+            void* p;
+            wt.bytes = n_out * other_row_bytes(fmt, n_in);
+            if ((rc = alloc_copy(data, wt.bytes, &p, wt.owned))) return rc;
+            wt.dev.p0 = (const uint8_t*)p;
         } else {
             return fail(B2_DECLINED, "[b200qmm: format %d has no device kernels]", fmt);
         }
@@ -329,6 +337,9 @@ class Backend {
                 s.dev.p0 += r0 * K;
                 s.dev.bs_row0 += r0;
                 break;
+            default:
+                if (fmt_is_other(w->dev.fmt)) s.dev.p0 += r0 * other_row_bytes(w->dev.fmt, K);
+                break;
         }
         s.bytes = w->bytes / w->dev.n_out * (r1 - r0);
         *out = next_handle++;
@@ -353,7 +364,7 @@ class Backend {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: unknown weight]");
         if (r0 > r1 || r1 > w->dev.n_out) return fail(B2_ERR_ARG, "[b200qmm: dequantize_rows: bad row range]");
-        cudaError_t e = launch_dequantize(w->dev, r0, r1 - r0, out_dev, stream);
+        cudaError_t e = fmt_is_other(w->dev.fmt) ? launch_dequantize_other(w->dev, r0, r1 - r0, out_dev, stream) : launch_dequantize(w->dev, r0, r1 - r0, out_dev, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "dequantize");
         return B2_OK;
@@ -405,6 +416,13 @@ class Backend {
                 return fail(B2_DECLINED, "[b200qmm: matvec: the pair's matrices differ in shape or format]");
         }
         if (mode < 0 || mode > 4 || (mode == B2_MODE_ADD_GATED && !gate)) return fail(B2_ERR_ARG, "[b200qmm: matvec: bad mode]");
+        if (fmt_is_other(w->dev.fmt)) {  // the generic kernel reads x itself
+            if (!gemv_other_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec: shape not supported for this format]");
+            cudaError_t eo = launch_gemv_other(w->dev, u ? &u->dev : nullptr, x_dev_, 0, y_dev_, 0, 1, mode, gate, sm_count, stream, chained);
+            launches++;
+            if (eo != cudaSuccess) return cuda_fail(eo, "gemv (generic)");
+            return B2_OK;
+        }
         if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec: shape not supported by the GEMV kernels]");
         XPlanes xp{};
         if (w->dev.fmt != B2_FMT_F8E4M3) {
@@ -421,7 +439,7 @@ class Backend {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: matvec: unknown weight]");
         bool planes = false;
-        if (w->dev.fmt != B2_FMT_F8E4M3 && gemv_supports(w->dev)) {
+        if (w->dev.fmt != B2_FMT_F8E4M3 && !fmt_is_other(w->dev.fmt) && gemv_supports(w->dev)) {
             int rc = prepare_x(x_dev_, w->dev.n_in);
             if (rc) return rc;
             // measured: worth 3 % for Q6_K; the 4-bit formats would switch to their ring form, which loses when launched alone
@@ -448,6 +466,19 @@ class Backend {
         if (t == 0) return B2_OK;
         if (y_dtype != B2_F32 && y_dtype != B2_BF16) return fail(B2_ERR_ARG, "[b200qmm: matmul: y must be f32 or bf16]");
         size_t K = w->dev.n_in;
+        if (fmt_is_other(w->dev.fmt)) {
+            // no tensor-core kernel for these formats: four tokens at a time through the generic matrix-vector kernel (the weights
+            // are read once per four tokens; every row equals its one-token row bit for bit)
+            if (x_dtype != B2_F32 || y_dtype != B2_F32 || !gemv_other_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matmul: this format takes f32 activations and results]");
+            for (size_t i = 0; i < t; i += 4) {
+                const int nt = (int)std::min<size_t>(4, t - i);
+                cudaError_t eo = launch_gemv_other(w->dev, nullptr, (const float*)x + i * K, K, (float*)y + i * w->dev.n_out, w->dev.n_out, nt, B2_MODE_STORE, nullptr,
+                                                   sm_count, stream);
+                launches++;
+                if (eo != cudaSuccess) return cuda_fail(eo, "gemv (generic, several rows)");
+            }
+            return B2_OK;
+        }
         if (t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev) && !(fp8_act && w->dev.fmt == B2_FMT_F8E4M3)) {
             for (size_t i = 0; i < t; i++) {
                 int rc = matvec_dev(h, 0, (const float*)x + i * K, (float*)y + i * w->dev.n_out, B2_MODE_STORE, nullptr);
@@ -578,7 +609,7 @@ class Backend {
             if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul: unknown weight in job %zu]", j);
             if (w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
                 return fail(B2_ERR_ARG, "[b200qmm: matmul: job %zu does not match its weight's shape]", j);
-            bool small = t <= 8 && gemv_supports(w->dev);
+            bool small = (t <= 8 && gemv_supports(w->dev)) || gemv_other_supports(w->dev);
             if (!small && !gemm_tc_supports(w->dev, t) && !rows_path(w->dev)) return fail(B2_DECLINED, "[b200qmm: matmul: job %zu has no kernel at t = %zu]", j, t);
         }
         auto t0 = clk::now();
@@ -629,7 +660,7 @@ class Backend {
             Weight* w = find(jobs[j].w);
             if (!w || w->dev.n_in != n_in || w->dev.n_out != jobs[j].n_out || !jobs[j].y)
                 return fail(B2_ERR_ARG, "[b200qmm: matvec_rows: job %zu does not match its weight]", j);
-            if (!gemv_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec_rows: job %zu has no kernel]", j);
+            if (!gemv_supports(w->dev) && !gemv_other_supports(w->dev)) return fail(B2_DECLINED, "[b200qmm: matvec_rows: job %zu has no kernel]", j);
             if (jobs[j].up) {
                 Weight* u = find(jobs[j].up);
                 if (!u || u->dev.fmt != w->dev.fmt || u->dev.n_in != w->dev.n_in || u->dev.n_out != w->dev.n_out)
@@ -655,6 +686,12 @@ class Backend {
             Weight* u = jobs[j].up ? find(jobs[j].up) : nullptr;
             float* yj = (float*)((uint8_t*)y_dev.p + y_off[j]);
             const int mode = jobs[j].up ? B2_MODE_SILU_PAIR : B2_MODE_STORE;
+            if (fmt_is_other(w->dev.fmt)) {
+                e = launch_gemv_other(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, yj, jobs[j].n_out, (int)t, mode, nullptr, sm_count, stream);
+                launches++;
+                if (e != cudaSuccess) return cuda_fail(e, "gemv (generic)");
+                continue;
+            }
             // Two to four rows: one launch that reads the weights once (each row's result is the one-row result bit for bit),
             // when the rows' vectors fit in shared memory together. FP8 rows go one by one: their single-row kernel is the
             // tensor-core one, and the rows must match it bit for bit.

@@ -140,6 +140,14 @@ cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const flo
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 
+// ---- gemv_other.cu: the other GGUF block formats (dq_other.cuh), raw rows, one generic kernel ---------------------------
+bool gemv_other_supports(const WeightDev& w);
+cudaError_t launch_dequantize_other(const WeightDev& w, size_t r0, size_t nrows, float* out, cudaStream_t st, const int* row_dev = nullptr,
+                                    bool pdl = false);
+// nt (1..4) tokens: token i's f32 vector at x + i * x_stride, its outputs at y + i * y_stride; the five output modes and the pair.
+cudaError_t launch_gemv_other(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, float* y, size_t y_stride, int nt, int mode,
+                              const float* gate, int sm_count, cudaStream_t st, bool pdl = false);
+
 // ---- gemm_tc.cu: prefill dequant-GEMM on tcgen05 ------------------------------------------------
 struct GemmStatus {   // written by the kernel when a bounded wait gives up
     uint32_t code;    // 0 = ok

@@ -96,6 +96,39 @@ def f8_e4m3(n_out: int, n_in: int, seed: int, bs_rows: int = 128, bs_cols: int =
     return Gguf(FMT_F8E4M3, np.ascontiguousarray(out.reshape(-1)), scales, bs_rows, bs_cols)
 
 
+# The other GGUF block formats: (block elements, block bytes, [(offset of an f16 field, magnitude, signed)]); MXFP4's first
+# byte is an E8M0 exponent instead (src/ggml.rs:173-215 for the sizes, src/ggml.rs:665-773, 915-960 for the fields).
+OTHER_BLOCKS = {
+    2: (32, 18, [(0, 0.01, True)]),                      # Q4_0
+    3: (32, 20, [(0, 0.01, False), (2, 0.05, True)]),    # Q4_1
+    6: (32, 22, [(0, 0.01, True)]),                      # Q5_0
+    7: (32, 24, [(0, 0.01, False), (2, 0.05, True)]),    # Q5_1
+    10: (256, 84, [(80, 0.01, False), (82, 0.01, False)]),   # Q2_K
+    11: (256, 110, [(108, 0.002, True)]),                # Q3_K
+    13: (256, 176, [(0, 0.01, False), (2, 0.01, False)]),    # Q5_K
+    20: (32, 18, [(0, 0.001, True)]),                    # IQ4_NL
+    23: (256, 136, [(0, 0.0001, True)]),                 # IQ4_XS
+    39: (32, 17, []),                                    # MXFP4
+}
+OTHER_NAMES = {2: "q4_0", 3: "q4_1", 6: "q5_0", 7: "q5_1", 10: "q2_k", 11: "q3_k", 13: "q5_k", 20: "iq4_nl", 23: "iq4_xs", 39: "mxfp4"}
+
+
+def other_blocks(kind: int, n_out: int, n_in: int, seed: int) -> Gguf:
+    """Uniform random block bytes of one of the other GGUF formats with its f16 scale fields drawn as |N(0, magnitude)|
+    (signed where the format's scale is) and MXFP4's exponent byte in 118 .. 124."""
+    bs, ts, fields = OTHER_BLOCKS[kind]
+    rng = np.random.default_rng(seed)
+    nb = n_out * (n_in // bs)
+    blk = rng.integers(0, 256, size=(nb, ts), dtype=np.uint16).astype(np.uint8)
+    for off, mag, signed in fields:
+        v = mag * rng.standard_normal(nb)
+        d = _f16_bits(v if signed else np.abs(v))
+        blk[:, off], blk[:, off + 1] = d & 0xFF, d >> 8
+    if kind == 39:
+        blk[:, 0] = rng.integers(118, 125, size=nb, dtype=np.uint16).astype(np.uint8)
+    return Gguf(kind, np.ascontiguousarray(blk.reshape(-1)))
+
+
 def make(fmt: str, n_out: int, n_in: int, seed: int):
     return {"mlx4": mlx4, "q4_k": q4_k, "q6_k": q6_k, "q8_0": q8_0, "f8_e4m3": f8_e4m3}[fmt](n_out, n_in, seed)
 

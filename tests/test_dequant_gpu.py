@@ -96,6 +96,6 @@ def test_gpu_dequant_golden(backend):
 
 def test_upload_rejects_bad_shapes(backend):
     assert backend.upload(ob.Gguf(ob.FMT_Q4_K, np.zeros(144, np.uint8)), 1, 128) is None  # n_in not a multiple of 256
-    assert backend.upload(ob.Gguf(2, np.zeros(18, np.uint8)), 1, 32) is None              # Q4_0: no device kernels
+    assert backend.upload(ob.Gguf(9, np.zeros(36, np.uint8)), 1, 32) is None              # Q8_1: no device kernels
     with pytest.raises(ob.BackendError):
         backend.dequantize_rows(ob.DeviceWeight(backend, 99999, 1, 256, ob.FMT_Q4_K))

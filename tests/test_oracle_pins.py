@@ -2,7 +2,8 @@
 
 Sources of truth, all from the reference tree:
   - REF_HASHES (src/ggml.rs:1547-1577) over fixture(kind) = random_blocks(kind, 1024 / block, 1000 + id)
-    (src/ggml.rs:1437-1496, 1535-1541): the dequantized values of Q4_K, Q6_K, Q8_0, F16, BF16, F32.
+    (src/ggml.rs:1437-1496, 1535-1541): the dequantized values of Q4_K, Q6_K, Q8_0, F16, BF16, F32 and of
+    Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS, MXFP4.
   - e4m3: the closed form of src/ggml.rs:258-271 for all 256 bytes (test e4m3_scaled_matches_the_table).
   - f16 / bf16 conversions: IEEE round-to-nearest-even (crate half 2.7.1), checked against numpy for
     every f16 value (the reference's f16c_matches_software_conversion, src/kernels_x86.rs:592-606).
@@ -20,7 +21,7 @@ from oxinfer_b200 import synth
 from util import FORMATS, make_pair, row_err
 
 
-@pytest.mark.parametrize("kind", [O.Q4_K, O.Q6_K, O.Q8_0, O.F16, O.BF16, O.F32])
+@pytest.mark.parametrize("kind", [O.Q4_K, O.Q6_K, O.Q8_0, O.F16, O.BF16, O.F32, *O.OTHER_KINDS])
 def test_dequantization_matches_reference_hashes(kind):
     d = O.dequantize_row(kind, O.fixture(kind), O.FIXTURE_ELEMS)
     assert O.fnv_f32(d) == O.REF_HASHES[kind]
