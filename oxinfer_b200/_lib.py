@@ -91,6 +91,7 @@ _SIGNATURES = {
     "b2_open_error": (C.c_char_p, []),
     "b2_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_set_exact": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_set_fast_planes": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_set_fp8_activations": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_set_chained": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_stats": (C.c_char_p, [C.c_void_p]),

@@ -178,6 +178,10 @@ class Backend:
         """Device-resident matrix-vector calls launch as a dependent chain (each kernel may start while the one ahead drains)."""
         self._check(self._L.b2_set_chained(self._ctx, int(on)))
 
+    def set_fast_planes(self, on: bool) -> None:
+        """Matrix-vector products over 16 of the activations' 21 bits (no counterpart in the reference; off by default)."""
+        self._check(self._L.b2_set_fast_planes(self._ctx, int(on)))
+
     def set_exact(self, on: bool) -> None:
         """``gpu::set_exact`` (``src/gpu.rs:313-338``): many-token matmuls with two-term f16 operands, within 1e-4 per row."""
         self._check(self._L.b2_set_exact(self._ctx, int(on)))

@@ -65,6 +65,7 @@ class Backend {
     cudaStream_t stream = nullptr;
     bool chained = false;  // b2_set_chained
     bool exact = false;    // b2_set_exact
+    bool fast_planes = false;  // b2_set_fast_planes
     bool fp8_act = false;  // b2_set_fp8_activations
     std::mutex mu;  // calls serialize, like the staging lock of src/cuda.rs:430,1443
     std::string err;
@@ -113,6 +114,14 @@ class Backend {
     // only conditions are the kernels' shape rules.
     bool wants(size_t n_out, size_t n_in, size_t t) const { return t >= 1 && n_out >= 1 && n_in % 32 == 0; }
 
+    // The planes record at `base` as the products of this context read it: all three planes, or the upper two under
+    // b2_set_fast_planes (never under the exactness switch).
+    int planes_read() const { return fast_planes && !exact ? 2 : 3; }
+    XPlanes planes_at(void* base, size_t K) const {
+        XPlanes p = xplanes_at(base, K);
+        p.np = planes_read();
+        return p;
+    }
     int alloc_copy(const void* host, size_t bytes, void** out, std::vector<void*>& owned) {
         void* p = nullptr;
         cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
@@ -301,7 +310,12 @@ class Backend {
             if (n_in % other_block_size(fmt) || n_in % 32) return fail(B2_DECLINED, "[b200qmm: format %d needs n_in to be a multiple of its block size]", fmt);
             void* p;
             wt.bytes = n_out * other_row_bytes(fmt, n_in);
-            if ((rc = alloc_copy(data, wt.bytes, &p, wt.owned))) return rc;
+            // 16 bytes of room after the last row: the matrix-vector kernel reads whole aligned 16-byte words
+            if ((rc = alloc_copy(nullptr, wt.bytes + 16, &p, wt.owned))) return rc;
+            if ((e = cudaMemcpyAsync(p, data, wt.bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess || (e = cudaStreamSynchronize(stream)) != cudaSuccess) {
+                drop(wt.owned);
+                return cuda_fail(e, "upload copy");
+            }
             wt.dev.p0 = (const uint8_t*)p;
         } else {
             return fail(B2_DECLINED, "[b200qmm: format %d has no device kernels]", fmt);
@@ -394,7 +408,7 @@ class Backend {
         if (!x_dev_ || n_in == 0 || n_in % 32) return fail(B2_ERR_ARG, "[b200qmm: prepare_x: n_in must be a positive multiple of 32]");
         cudaError_t e = xplanes.reserve(xplanes_bytes(n_in));
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
-        e = launch_xplanes(x_dev_, n_in, xplanes_at(xplanes.p, n_in), stream, chained);
+        e = launch_xplanes(x_dev_, n_in, planes_at(xplanes.p, n_in), stream, chained);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "xplanes");
         prepared_k = n_in;
@@ -427,7 +441,7 @@ class Backend {
         XPlanes xp{};
         if (w->dev.fmt != B2_FMT_F8E4M3) {
             if (prepared_k != w->dev.n_in) return fail(B2_ERR_ARG, "[b200qmm: matvec: no planes prepared for n_in = %zu (b2_prepare_x_dev)]", w->dev.n_in);
-            xp = xplanes_at(xplanes.p, w->dev.n_in);
+            xp = planes_at(xplanes.p, w->dev.n_in);
         }
         cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained || after_planes);
         launches++;
@@ -503,13 +517,13 @@ class Backend {
                 float* yi = (float*)y + i * n_out;
                 uint8_t* pi = (uint8_t*)xplanes.p + i * stride;
                 if (nt > 1 && gemv_multi_fits(w->dev, (int)nt)) {
-                    e = launch_gemv_multi(w->dev, nullptr, xi, K, xplanes_at(pi, K), stride, yi, n_out, (int)nt, B2_MODE_STORE, sm_count, stream);
+                    e = launch_gemv_multi(w->dev, nullptr, xi, K, planes_at(pi, K), stride, yi, n_out, (int)nt, B2_MODE_STORE, sm_count, stream);
                     launches++;
                     if (e != cudaSuccess) return cuda_fail(e, "gemv (several rows)");
                     continue;
                 }
                 for (size_t r = 0; r < nt; r++) {  // one row, or the rows' planes do not fit in shared memory together
-                    e = launch_gemv(w->dev, nullptr, xi + r * K, xplanes_at(pi + r * stride, K), yi + r * n_out, B2_MODE_STORE, nullptr, sm_count, stream);
+                    e = launch_gemv(w->dev, nullptr, xi + r * K, planes_at(pi + r * stride, K), yi + r * n_out, B2_MODE_STORE, nullptr, sm_count, stream);
                     launches++;
                     if (e != cudaSuccess) return cuda_fail(e, "gemv");
                 }
@@ -705,7 +719,7 @@ class Backend {
                     prepared_k = 0;  // the scratch now holds several rows' planes, not one prepared vector
                     planes_ready = true;
                 }
-                e = launch_gemv_multi(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, xplanes_at(xplanes.p, n_in), stride, yj, jobs[j].n_out,
+                e = launch_gemv_multi(w->dev, u ? &u->dev : nullptr, (const float*)x_dev.p, n_in, planes_at(xplanes.p, n_in), stride, yj, jobs[j].n_out,
                                       (int)t, mode, sm_count, stream);
                 launches++;
                 if (e != cudaSuccess) return cuda_fail(e, "gemv (several rows)");
@@ -865,9 +879,9 @@ class Backend {
         b2.y_stride = m.h;
         b2.planes = (uint8_t*)moe_a.p;
         if (e == cudaSuccess)
-            e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, m.act == B2_ACT_GELU_TANH ? B2_MODE_GELU_PAIR : B2_MODE_SILU_PAIR, sm_count, stream);
+            e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, m.act == B2_ACT_GELU_TANH ? B2_MODE_GELU_PAIR : B2_MODE_SILU_PAIR, planes_read(), sm_count, stream);
         if (e == cudaSuccess) e = launch_xplanes_rows((const float*)moe_g.p, R, m.inter, (uint8_t*)moe_a.p, sa, stream);
-        if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, sm_count, stream);
+        if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, planes_read(), sm_count, stream);
         if (e == cudaSuccess) e = launch_moe_combine_small((const float*)moe_o.p, routes, t, k, m.h, y_dev_, stream);
         launches += 5;
         if (e != cudaSuccess) return cuda_fail(e, "moe (batched matrix-vector path)");
@@ -1182,7 +1196,7 @@ class Backend {
                 Weight* w = find(h);
                 return w ? &w->dev : nullptr;
             },
-            sm_count, &p, e);
+            sm_count, planes_read(), &p, e);
         if (rc) {
             err = e;
             return rc;
@@ -1358,6 +1372,11 @@ B2_EXPORT int b2_set_chained(b2_ctx* ctx, int on) {
     return B2_OK;
 }
 
+B2_EXPORT int b2_set_fast_planes(b2_ctx* ctx, int on) {
+    if (!ctx) return B2_ERR_ARG;
+    ctx->be.fast_planes = on != 0;
+    return B2_OK;
+}
 B2_EXPORT int b2_set_exact(b2_ctx* ctx, int on) {
     LOCKED(ctx);
     ctx->be.exact = on != 0;

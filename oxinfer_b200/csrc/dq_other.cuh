@@ -40,8 +40,14 @@ __host__ __device__ inline size_t other_row_bytes(int fmt, size_t n_in) { return
 // ggml's non-linear 4-bit code book (kvalues_iq4nl) and the doubled E2M1 values of MXFP4 (kvalues_mxfp4).
 static __constant__ int8_t K_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 static __constant__ int8_t K_MXFP4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
-__device__ __forceinline__ float iq4nl_value(uint32_t i) { return (float)K_IQ4NL[i & 15]; }
-__device__ __forceinline__ float mxfp4_value(uint32_t i) { return (float)K_MXFP4[i & 15]; }
+// The kernels copy the code book of their format into 16 floats of shared memory (lanes index it differently, which a
+// constant-memory table would serialize; 16 words sit in 16 banks): lut_fill by the first 16 threads, then a barrier.
+template <int FMT>
+__device__ __forceinline__ void lut_fill(float* lut, int tid) {
+    if (tid < 16) lut[tid] = (FMT == B2_FMT_MXFP4) ? (float)K_MXFP4[tid] : (float)K_IQ4NL[tid];
+}
+// A small non-negative integer as a float through the mantissa of 2^23 (exact; keeps the conversion unit out of the loop).
+__device__ __forceinline__ float uint_to_f32(uint32_t n) { return __uint_as_float(0x4B000000u | n) - 8388608.0f; }
 __device__ __forceinline__ float f16_at(const uint8_t* b, int i) { return f16_bits_to_f32((uint16_t)(b[i] | (b[i + 1] << 8))); }
 __device__ __forceinline__ uint32_t u32_at(const uint8_t* b, int i) { return b[i] | (b[i + 1] << 8) | (b[i + 2] << 16) | ((uint32_t)b[i + 3] << 24); }
 // Half the value of an E8M0 scale byte, 2^(e - 128) (src/ggml.rs:466-474).
@@ -49,20 +55,20 @@ __device__ __forceinline__ float e8m0_half(uint32_t e) { return __uint_as_float(
 
 // v[0..32) = weights 32 sub .. 32 sub + 31 of the block at `b`.
 template <int FMT>
-__device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float (&v)[32]) {
+__device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float (&v)[32], const float* lut) {
     if constexpr (FMT == B2_FMT_Q4_0) {
         const float d = f16_at(b, 0);
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            v[j] = __fmul_rn((float)((int)(b[2 + j] & 0xF) - 8), d);
-            v[j + 16] = __fmul_rn((float)((int)(b[2 + j] >> 4) - 8), d);
+            v[j] = __fmul_rn((uint_to_f32(b[2 + j] & 0xF) - 8.0f), d);
+            v[j + 16] = __fmul_rn((uint_to_f32(b[2 + j] >> 4) - 8.0f), d);
         }
     } else if constexpr (FMT == B2_FMT_Q4_1) {
         const float d = f16_at(b, 0), m = f16_at(b, 2);
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            v[j] = __fadd_rn(__fmul_rn((float)(b[4 + j] & 0xF), d), m);
-            v[j + 16] = __fadd_rn(__fmul_rn((float)(b[4 + j] >> 4), d), m);
+            v[j] = __fadd_rn(__fmul_rn(uint_to_f32(b[4 + j] & 0xF), d), m);
+            v[j + 16] = __fadd_rn(__fmul_rn(uint_to_f32(b[4 + j] >> 4), d), m);
         }
     } else if constexpr (FMT == B2_FMT_Q5_0 || FMT == B2_FMT_Q5_1) {
         constexpr bool ONE = FMT == B2_FMT_Q5_1;
@@ -74,26 +80,26 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
             const uint32_t h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
             const uint32_t lo = (q[j] & 0xF) | h0, hi = (q[j] >> 4) | h1;
             if (ONE) {
-                v[j] = __fadd_rn(__fmul_rn((float)lo, d), m);
-                v[j + 16] = __fadd_rn(__fmul_rn((float)hi, d), m);
+                v[j] = __fadd_rn(__fmul_rn(uint_to_f32(lo), d), m);
+                v[j + 16] = __fadd_rn(__fmul_rn(uint_to_f32(hi), d), m);
             } else {
-                v[j] = __fmul_rn((float)((int)lo - 16), d);
-                v[j + 16] = __fmul_rn((float)((int)hi - 16), d);
+                v[j] = __fmul_rn((uint_to_f32(lo) - 16.0f), d);
+                v[j + 16] = __fmul_rn((uint_to_f32(hi) - 16.0f), d);
             }
         }
     } else if constexpr (FMT == B2_FMT_IQ4_NL) {
         const float d = f16_at(b, 0);
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            v[j] = __fmul_rn(d, iq4nl_value(b[2 + j] & 0xF));
-            v[j + 16] = __fmul_rn(d, iq4nl_value(b[2 + j] >> 4));
+            v[j] = __fmul_rn(d, lut[b[2 + j] & 0xF]);
+            v[j + 16] = __fmul_rn(d, lut[b[2 + j] >> 4]);
         }
     } else if constexpr (FMT == B2_FMT_MXFP4) {
         const float d = e8m0_half(b[0]);
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            v[j] = __fmul_rn(d, mxfp4_value(b[1 + j] & 0xF));
-            v[j + 16] = __fmul_rn(d, mxfp4_value(b[1 + j] >> 4));
+            v[j] = __fmul_rn(d, lut[b[1 + j] & 0xF]);
+            v[j + 16] = __fmul_rn(d, lut[b[1 + j] >> 4]);
         }
     } else if constexpr (FMT == B2_FMT_Q2_K) {
         // scales b[0..16), quants b[16..80), d @80, min @82; chunk sub = 4 n + j covers h = 0, 1 (src/ggml.rs:713-730)
@@ -105,7 +111,7 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
             const uint32_t s = b[8 * n + 2 * j + h];
             const float dl = __fmul_rn(d, (float)(s & 0xF)), ml = __fmul_rn(mn, (float)(s >> 4));
 #pragma unroll
-            for (int l = 0; l < 16; l++) v[16 * h + l] = __fsub_rn(__fmul_rn(dl, (float)((q[16 * h + l] >> (2 * j)) & 3)), ml);
+            for (int l = 0; l < 16; l++) v[16 * h + l] = __fsub_rn(__fmul_rn(dl, uint_to_f32((q[16 * h + l] >> (2 * j)) & 3)), ml);
         }
     } else if constexpr (FMT == B2_FMT_Q3_K) {
         // high-bit mask b[0..32), quants b[32..96), 12 scale bytes @96, d @108 (src/ggml.rs:731-749, q3k_scales :513-531)
@@ -124,8 +130,8 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
 #pragma unroll
             for (int l = 0; l < 16; l++) {
                 const int i = 16 * h + l;
-                const int val = (int)((q[i] >> (2 * j)) & 3) - ((b[i] & m) ? 0 : 4);
-                v[16 * h + l] = __fmul_rn(dl, (float)val);
+                const float val = uint_to_f32((q[i] >> (2 * j)) & 3) - ((b[i] & m) ? 0.0f : 4.0f);
+                v[16 * h + l] = __fmul_rn(dl, val);
             }
         }
     } else if constexpr (FMT == B2_FMT_Q5_K) {
@@ -141,7 +147,7 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
         for (int l = 0; l < 32; l++) {
             uint32_t val = (q[l] >> (4 * h)) & 0xF;
             if (qh[l] & (1u << sub)) val += 16;
-            v[l] = __fsub_rn(__fmul_rn(d1, (float)val), m1);
+            v[l] = __fsub_rn(__fmul_rn(d1, uint_to_f32(val)), m1);
         }
     } else {  // IQ4_XS: d @0, high scale bits u16 @2, low scale nibbles b[4..8), quants @8 + 16 ib (src/ggml.rs:948-958, :544-547)
         const float d = f16_at(b, 0);
@@ -151,8 +157,8 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
         const uint8_t* q = b + 8 + 16 * sub;
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            v[j] = __fmul_rn(dl, iq4nl_value(q[j] & 0xF));
-            v[j + 16] = __fmul_rn(dl, iq4nl_value(q[j] >> 4));
+            v[j] = __fmul_rn(dl, lut[q[j] & 0xF]);
+            v[j + 16] = __fmul_rn(dl, lut[q[j] >> 4]);
         }
     }
 }

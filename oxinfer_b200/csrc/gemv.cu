@@ -239,8 +239,8 @@ cudaError_t launch_ring_w(const WeightDev& w, const WeightDev* up, XPlanes xp, f
 }
 
 template <class F>
-cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
-                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+cudaError_t launch_ring_f(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
+                          cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     if (epi.out.planes) {
         static const int warps = env_int("B2_EPI_WARPS", 16), slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_EPI_SLOTS", 3)));
@@ -254,6 +254,14 @@ cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, flo
     static const int plain_slots = std::min(RING_SLOTS_MAX, std::max(2, env_int("B2_RING_SLOTS", RING_SLOTS)));
     return pair ? launch_ring_w<F, true, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots)
                 : launch_ring_w<F, false, 8>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi, plain_slots);
+}
+
+// FT<3> reads all three planes of x, FT<2> the upper two (XPlanes::np).
+template <template <int> class FT>
+cudaError_t launch_ring(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, const float* gate, int sm_count,
+                        cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+    return xp.np == 2 ? launch_ring_f<FT<2>>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi)
+                      : launch_ring_f<FT<3>>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
 }
 
 // ---- FP8 e4m3 weights on the tensor cores ---------------------------------------------------------------------
@@ -419,9 +427,9 @@ static cudaError_t launch_f8_mma(const WeightDev& w, const float* x, float* y, i
     return launch_k(gemv_f8_mma_kernel, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, x, y, mode, gate);
 }
 
-template <class F, bool XF32, int NT = 1>
-cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                       int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi = GemvMulti{0, 0}) {
+template <class F, bool XF32, int NT>
+cudaError_t launch_fmt_f(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
+                         int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi) {
     size_t smem = (((XF32 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128) * NT;
     bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, XF32, NT> : gemv_kernel<F, false, XF32, NT>;
@@ -432,6 +440,13 @@ cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, 
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
     size_t grid = groups < (size_t)sm_count * per_sm ? groups : (size_t)sm_count * per_sm;
     return launch_k(kern, dim3((unsigned)grid), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, x, xp, y, mode, gate, ns, GemvBatch{}, multi);
+}
+
+template <template <int> class FT, bool XF32, int NT = 1>
+cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
+                       int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi = GemvMulti{0, 0}) {
+    if (XF32 || xp.np != 2) return launch_fmt_f<FT<3>, XF32, NT>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns, multi);
+    return launch_fmt_f<FT<XF32 ? 3 : 2>, XF32, NT>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns, multi);
 }
 
 }  // namespace
@@ -484,11 +499,13 @@ static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, c
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
+cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int np, int sm_count,
                                 cudaStream_t st) {
     if (batch == 0 || batch > GEMV_BATCH_MAX || (size_t)b.n != batch || !gemv_supports(w)) return cudaErrorInvalidValue;
-    if (w.fmt == B2_FMT_MLX4) return launch_batched_fmt<FmtMLX4>(w, up, b, batch, y, mode, sm_count, st);
-    if (w.fmt == B2_FMT_Q4_K) return launch_batched_fmt<FmtQ4K>(w, up, b, batch, y, mode, sm_count, st);
+    if (w.fmt == B2_FMT_MLX4)
+        return np == 2 ? launch_batched_fmt<FmtMLX4_T<2>>(w, up, b, batch, y, mode, sm_count, st) : launch_batched_fmt<FmtMLX4_T<3>>(w, up, b, batch, y, mode, sm_count, st);
+    if (w.fmt == B2_FMT_Q4_K)
+        return np == 2 ? launch_batched_fmt<FmtQ4K_T<2>>(w, up, b, batch, y, mode, sm_count, st) : launch_batched_fmt<FmtQ4K_T<3>>(w, up, b, batch, y, mode, sm_count, st);
     return cudaErrorInvalidValue;
 }
 
@@ -497,11 +514,11 @@ static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, cons
                                    cudaStream_t st, GemvMulti m) {
     const NormScale none{nullptr, 0, 0.0f, 0.0f};
     switch (w.fmt) {
-        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_F8E4M3: return launch_fmt<FmtF8, true, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_F8E4M3: return launch_fmt<FmtF8_T, true, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -544,28 +561,28 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
                         int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
     if (epi.out.planes) {  // only the ring form carries the epilogue, chained or not
         if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }
     // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
     if (ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
-        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
-        return launch_ring<FmtQ4K>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
+        return launch_ring<FmtQ4K_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }
     switch (w.fmt) {
-        case B2_FMT_MLX4: return launch_fmt<FmtMLX4, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
-        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
-        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
-        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4_T, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K_T, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K_T, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0_T, false>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
         case B2_FMT_F8E4M3: {
             static const bool mma = [] {
                 const char* e = getenv("B2_GEMV_F8_MMA");
                 return !e || atoi(e) != 0;
             }();
             if (mma && !ns.partial && f8_mma_ok(w, mode)) return launch_f8_mma(w, x, y, mode, gate, sm_count, st, pdl);
-            return launch_fmt<FmtF8, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
+            return launch_fmt<FmtF8_T, true>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns);
         }
         default: return cudaErrorInvalidValue;
     }

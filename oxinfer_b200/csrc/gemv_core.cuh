@@ -45,7 +45,19 @@ __device__ __forceinline__ void plane64(const XS& x, int p, int k0, uint32_t (&w
 }
 
 __device__ __forceinline__ int dp(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
-__device__ __forceinline__ int planes3(int a0, int a1, int a2) { return a0 + (a1 << 7) + (a2 << 14); }
+// unsigned weight bytes (0 .. 255) times signed plane bytes
+__device__ __forceinline__ int dp_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// The integer sum over a run of k of w * q from the per-plane sums (q = q0 + 32 q1 + 8192 q2). NP = 2 leaves q0 out. The
+// partial terms may wrap; the total fits 32 bits and unsigned arithmetic keeps it.
+template <int NP>
+__device__ __forceinline__ int planes_sum(int a0, int a1, int a2) {
+    const uint32_t hi = ((uint32_t)a1 << 5) + ((uint32_t)a2 << 13);
+    return (int)(NP == 3 ? hi + (uint32_t)a0 : hi);
+}
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {  // streamed once: keep it out of L1
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -91,7 +103,8 @@ __device__ __forceinline__ void q4_load(const WeightDev& w, size_t row, int it, 
     r.q0 = ldg_stream(blk + 16 + 32 * (lane & 3));
     r.q1 = ldg_stream(blk + 32 + 32 * (lane & 3));
 }
-// Integer dot products of the low / high nibbles of two rows' 64-groups with the three planes.
+// Integer dot products of the low / high nibbles of two rows' 64-groups with the planes.
+template <int NP>
 __device__ __forceinline__ void q4_int_dots(const Q4Regs& a, const Q4Regs& b, const XS& x, int k0, int& la, int& ha, int& lb, int& hb) {
     const uint32_t qa[8] = {a.q0.x, a.q0.y, a.q0.z, a.q0.w, a.q1.x, a.q1.y, a.q1.z, a.q1.w};
     const uint32_t qb[8] = {b.q0.x, b.q0.y, b.q0.z, b.q0.w, b.q1.x, b.q1.y, b.q1.z, b.q1.w};
@@ -104,30 +117,36 @@ __device__ __forceinline__ void q4_int_dots(const Q4Regs& a, const Q4Regs& b, co
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             al[i] = qa[4 * h + i] & 0x0F0F0F0Fu;
-            ah[i] = (qa[4 * h + i] >> 4) & 0x0F0F0F0Fu;
+            ah[i] = NP == 3 ? (qa[4 * h + i] >> 4) & 0x0F0F0F0Fu : qa[4 * h + i] & 0xF0F0F0F0u;  // NP 2: 16 x the nibble, no shift
             bl[i] = qb[4 * h + i] & 0x0F0F0F0Fu;
-            bh[i] = (qb[4 * h + i] >> 4) & 0x0F0F0F0Fu;
+            bh[i] = NP == 3 ? (qb[4 * h + i] >> 4) & 0x0F0F0F0Fu : qb[4 * h + i] & 0xF0F0F0F0u;
         }
 #pragma unroll
-        for (int p = 0; p < 3; p++) {
+        for (int p = 3 - NP; p < 3; p++) {
             const uint4 lo = plane16(x, p, k0 + 16 * h), hi = plane16(x, p, k0 + 32 + 16 * h);
             const uint32_t xl[4] = {lo.x, lo.y, lo.z, lo.w}, xh[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 s[p][0] = dp(al[i], xl[i], s[p][0]);
-                s[p][1] = dp(ah[i], xh[i], s[p][1]);
+                s[p][1] = NP == 3 ? dp(ah[i], xh[i], s[p][1]) : dp_us(ah[i], xh[i], s[p][1]);
                 s[p][2] = dp(bl[i], xl[i], s[p][2]);
-                s[p][3] = dp(bh[i], xh[i], s[p][3]);
+                s[p][3] = NP == 3 ? dp(bh[i], xh[i], s[p][3]) : dp_us(bh[i], xh[i], s[p][3]);
             }
         }
     }
-    la = planes3(s[0][0], s[1][0], s[2][0]);
-    ha = planes3(s[0][1], s[1][1], s[2][1]);
-    lb = planes3(s[0][2], s[1][2], s[2][2]);
-    hb = planes3(s[0][3], s[1][3], s[2][3]);
+    la = planes_sum<NP>(s[0][0], s[1][0], s[2][0]);
+    lb = planes_sum<NP>(s[0][2], s[1][2], s[2][2]);
+    if (NP == 3) {
+        ha = planes_sum<3>(s[0][1], s[1][1], s[2][1]);
+        hb = planes_sum<3>(s[0][3], s[1][3], s[2][3]);
+    } else {  // the high sums carry a factor of 16 (exactly): 32 q1 + 8192 q2 over 16 = 2 q1 + 512 q2
+        ha = (int)(((uint32_t)s[1][1] << 1) + ((uint32_t)s[2][1] << 9));
+        hb = (int)(((uint32_t)s[1][3] << 1) + ((uint32_t)s[2][3] << 9));
+    }
 }
 
-struct FmtQ4K {
+template <int NP>
+struct FmtQ4K_T {
     static constexpr int ITER_K = 2048;
     using Regs = Q4Regs;
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
@@ -150,7 +169,7 @@ struct FmtQ4K {
         const int j = lane & 3;
         const int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
         int la, ha, lb, hb;
-        q4_int_dots(a, b, x, k0, la, ha, lb, hb);
+        q4_int_dots<NP>(a, b, x, k0, la, ha, lb, hb);
         const float4 sx = *(const float4*)(x.sx + (k0 >> 5));  // {xs, xsum} of the two blocks of 32
         tail(a, j, sx, la, ha, accA);
         tail(b, j, sx, lb, hb, accB);
@@ -159,7 +178,8 @@ struct FmtQ4K {
 
 // MLX affine 4-bit, repacked at upload into Q4_K-shaped blocks: header = 4 f16 d + 4 bf16 offsets
 // (one per 64-group: the fields of the reference's Q4Matrix), then the 128 nibble bytes in the order above.
-struct FmtMLX4 {
+template <int NP>
+struct FmtMLX4_T {
     static constexpr int ITER_K = 2048;
     using Regs = Q4Regs;
     __device__ static __forceinline__ bool active(int K, int it, int lane) { return it * 8 + (lane >> 2) < K / 256; }
@@ -178,14 +198,15 @@ struct FmtMLX4 {
         const int j = lane & 3;
         const int k0 = (it * 8 + (lane >> 2)) * 256 + 64 * j;
         int la, ha, lb, hb;
-        q4_int_dots(a, b, x, k0, la, ha, lb, hb);
+        q4_int_dots<NP>(a, b, x, k0, la, ha, lb, hb);
         const float4 sx = *(const float4*)(x.sx + (k0 >> 5));
         tail(a, j, sx, la, ha, accA);
         tail(b, j, sx, lb, hb, accB);
     }
 };
 
-struct FmtQ6K {
+template <int NP>
+struct FmtQ6K_T {
     static constexpr int ITER_K = 2048;  // 8 blocks of 256, 4 lanes each (64 elements per lane)
     struct Regs {
         uint4 qh, qa, qb;
@@ -225,9 +246,9 @@ struct FmtQ6K {
                 qb[i] = (lo & 0x0F0F0F0Fu) | (hb & 0x30303030u);
             }
             const int k0 = kb + 32 * k4;
-            int sa[3], sb[3];
+            int sa[3] = {0, 0, 0}, sb[3] = {0, 0, 0};
 #pragma unroll
-            for (int p = 0; p < 3; p++) {
+            for (int p = 3 - NP; p < 3; p++) {
                 uint4 xv = plane16(x, p, k0);
                 int t = dp(qa[0], xv.x, 0);
                 t = dp(qa[1], xv.y, t);
@@ -242,13 +263,14 @@ struct FmtQ6K {
             const float xs = x.sx[k0 >> 5].x;
             const float scale_a = int8_to_float((uint32_t)(sca >> (8 * (u + 2 * k4))));
             const float scale_b = int8_to_float((uint32_t)(scb >> (8 * (u + 2 * k4))));
-            accA = fmaf((da * scale_a) * xs, (float)(planes3(sa[0], sa[1], sa[2]) - off32), accA);
-            accB = fmaf((db * scale_b) * xs, (float)(planes3(sb[0], sb[1], sb[2]) - off32), accB);
+            accA = fmaf((da * scale_a) * xs, (float)(planes_sum<NP>(sa[0], sa[1], sa[2]) - off32), accA);
+            accB = fmaf((db * scale_b) * xs, (float)(planes_sum<NP>(sb[0], sb[1], sb[2]) - off32), accB);
         }
     }
 };
 
-struct FmtQ8_0 {
+template <int NP>
+struct FmtQ8_0_T {
     static constexpr int ITER_K = 512;  // 16 bytes = 16 weights per lane
     struct Regs {
         uint4 q;
@@ -262,9 +284,9 @@ struct FmtQ8_0 {
     }
     __device__ static __forceinline__ void dot2(const Regs& a, const Regs& b, const XS& x, int it, int lane, float& accA, float& accB) {
         const int k0 = it * 512 + lane * 16;
-        int sa[3], sb[3];
+        int sa[3] = {0, 0, 0}, sb[3] = {0, 0, 0};
 #pragma unroll
-        for (int p = 0; p < 3; p++) {
+        for (int p = 3 - NP; p < 3; p++) {
             uint4 xv = plane16(x, p, k0);
             int t = dp(a.q.x, xv.x, 0);
             t = dp(a.q.y, xv.y, t);
@@ -276,12 +298,13 @@ struct FmtQ8_0 {
             sb[p] = dp(b.q.w, xv.w, t);
         }
         const float xs = x.sx[k0 >> 5].x;
-        accA = fmaf(__half2float(__ushort_as_half((unsigned short)a.d)) * xs, (float)planes3(sa[0], sa[1], sa[2]), accA);
-        accB = fmaf(__half2float(__ushort_as_half((unsigned short)b.d)) * xs, (float)planes3(sb[0], sb[1], sb[2]), accB);
+        accA = fmaf(__half2float(__ushort_as_half((unsigned short)a.d)) * xs, (float)planes_sum<NP>(sa[0], sa[1], sa[2]), accA);
+        accB = fmaf(__half2float(__ushort_as_half((unsigned short)b.d)) * xs, (float)planes_sum<NP>(sb[0], sb[1], sb[2]), accB);
     }
 };
 
-struct FmtF8 {
+template <int NP>  // reads the f32 vector, not the planes: NP is ignored and every use names 3
+struct FmtF8_T {
     static constexpr int ITER_K = 512;  // 16 e4m3 bytes per lane
     struct Regs {
         uint4 q;

@@ -62,8 +62,8 @@ cudaError_t launch_repack_q4a(const uint8_t* q, const uint16_t* scales, const ui
 cudaError_t launch_repack_q8_0(const uint8_t* raw, size_t n_out, size_t n_in, int8_t* qs, uint16_t* d, cudaStream_t st);
 
 // ---- gemv.cu: one-token dequant matrix-vector products ---------------------------------------
-// Activation vector split into three int8 planes per block of 32 (x ~= xs * (q0 + 128 q1 + 16384 q2),
-// 21 significant bits per block), plus block scales and sums. The record in global memory is the image the product
+// Activation vector split into three int8 planes per block of 32 (x ~= xs * (q0 + 32 q1 + 8192 q2),
+// 21 significant bits per block; q1 and q2 alone carry 16), plus block scales and sums. The record in global memory is the image the product
 // kernels keep in shared memory, so staging it is a plain copy (bulk copies in the ring form). For n_in = K, in bytes:
 //   planes 3K | sx 8K/32 | v16 4K/16
 // Element k of plane p sits at p * K + 16 * xplanes_slot(k / 16) + k % 16: the 16-byte slots of each 64 bytes are
@@ -72,6 +72,7 @@ struct XPlanes {
     int8_t* planes;   // [3][K], slots permuted
     float2* sx;       // [K/32]  (block scale, scale * sum of the block's integers = the quantized block sum)
     int32_t* v16;     // [K/16]  integer sums of each 16 elements
+    int np;           // planes a product reads: 2 = the upper two (16 bits), anything else = all three (21 bits, the default)
 };
 // Slot g -> g with its low two bits xor-ed by bits 3 and 4: lanes L = 0..7 of a phase that read slots 4 L + i (a 64-byte
 // stride) then cover all eight 16-byte bank groups for every i.
@@ -83,6 +84,7 @@ __host__ __device__ inline XPlanes xplanes_at(void* base, size_t K) {
     p.planes = (int8_t*)b;
     p.sx = (float2*)(b + 3 * K);
     p.v16 = (int32_t*)(b + 3 * K + 8 * (K / 32));
+    p.np = 0;
     return p;
 }
 cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false);
@@ -128,7 +130,7 @@ struct GemvBatch {
     size_t w_stride, x_stride, y_stride;
     uint8_t* planes;
 };
-cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
+cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int np, int sm_count,
                                 cudaStream_t st);
 // Planes of `rows` vectors of K values (row r at x + r * K) into blocks `stride` bytes apart.
 cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st);

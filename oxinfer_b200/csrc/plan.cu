@@ -113,8 +113,8 @@ bool DecodePlanImpl::uses_weight(uint64_t h) const {
     return h != 0 && h == gen_embed_;
 }
 
-int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, DecodePlanImpl** out,
-                           std::string& err) {
+int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes,
+                           DecodePlanImpl** out, std::string& err) {
     if (!g || !g->bufs || !g->ops || g->n_bufs == 0 || g->n_ops == 0 || !out) {
         err = "[b200qmm: decode_plan: empty graph]";
         return B2_ERR_ARG;
@@ -476,7 +476,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         planes_total += align_up(xplanes_bytes(region_k[r]), 256);
     }
     PLAN_CUDA(cudaMalloc((void**)&p->planes_, std::max<size_t>(planes_total, 256)), "cudaMalloc(planes)");
-    for (auto& [oi, r] : region_of_op) p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
+    for (auto& [oi, r] : region_of_op) {
+        p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
+        p->ops_[oi].xp.np = planes;
+    }
 
     // ---- RoPE inside the attention kernel ----------------------------------------------------------------------
     // A QK_ROPE op without per-head norms whose rotated queries only the ATTEND op right behind it reads: the attention

@@ -14,7 +14,8 @@ class DecodePlanImpl {
   public:
     // `resolve` maps a weight handle to its device description (nullptr: unknown handle).
     // Returns B2_OK, B2_DECLINED or an error code; `err` gets the reason.
-    static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, DecodePlanImpl** out,
+    // `planes`: how many planes of the activation split the plan's products read (2: the upper two, 16 bits; otherwise all three, 21 bits).
+    static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, DecodePlanImpl** out,
                       std::string& err);
     ~DecodePlanImpl();
 

@@ -12,7 +12,11 @@ namespace b2 {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-constexpr float XQ_MAX = 1040000.0f;  // |q0 + 128 q1 + 16384 q2| <= 63 + 128*63 + 16384*63 = 1040319
+// The block's integers q = round(x / s) have 21 significant bits, |q| <= XQ_MAX, and are stored as three signed digits
+// q = q0 + 32 (q1 + 256 q2): q0 in [-16, 15], q1 in [-128, 127], |q2| <= 127. The product kernels read all three (exact to
+// 21 bits, the default) or, on request, only q1 and q2 (the nearest multiple of 32: 16 bits, an error of at most 1.6e-5
+// of the block's largest element per element) and save a third of their integer dot products.
+constexpr float XQ_MAX = 1040000.0f;
 
 // One block of 32 values split by a warp (one value per lane, all 32 lanes call it): the lane's three plane bytes,
 // the block scale, the integer sums of the lane's half block and of the block.
@@ -27,10 +31,10 @@ __device__ __forceinline__ XSplit xplanes_split(float v) {
     r.s = a / XQ_MAX;
     int q = a > 0.0f ? __float2int_rn(v * (XQ_MAX / a)) : 0;
     q = max(-(int)XQ_MAX, min((int)XQ_MAX, q));
-    r.q0 = ((q + 64) & 127) - 64;
-    int r1 = (q - r.q0) >> 7;
-    r.q1 = ((r1 + 64) & 127) - 64;
-    r.q2 = (r1 - r.q1) >> 7;
+    r.q0 = ((q + 16) & 31) - 16;
+    int r1 = (q - r.q0) >> 5;
+    r.q1 = ((r1 + 128) & 255) - 128;
+    r.q2 = (r1 - r.q1) >> 8;
     const unsigned half = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;  // the lane's half warp
     r.sum16 = __reduce_add_sync(half, q);
     r.sum32 = __reduce_add_sync(0xffffffffu, q);

@@ -166,3 +166,36 @@ def test_four_bit_modes_and_pairs_at_large_k(backend, fmt, shape):
     torch.cuda.synchronize()
     gelu = 0.5 * g * (1 + np.tanh(0.7978845608 * (g + 0.044715 * g**3)))
     assert row_err(y.cpu().numpy()[None], (gelu * u)[None]) < 1e-4
+
+
+@pytest.mark.parametrize("fmt", ["mlx4", "q4_k", "q6_k", "q8_0"])
+def test_fast_planes_switch_reads_sixteen_bits(backend, fmt):
+    """b2_set_fast_planes: the products read the upper two of the three activation planes. Inside the stated 1e-3, outside
+    the default's 2e-5 on some rows, every row still equal to its one-token row bit for bit; off again, the default's bits
+    come back; the exactness switch overrides it."""
+    n_out, n_in = 1000, 2048
+    ref, m = make_pair(fmt, n_out, n_in, 77)
+    dev = backend.upload(ref, n_out, n_in)
+    x = (synth.activations(3, n_in, 78) * np.float32(1.2345)).astype(np.float32)
+    want = m.matmul_f64(x)
+    y3 = np.zeros((3, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev, y3)])
+    try:
+        backend.set_fast_planes(True)
+        y2 = np.zeros((3, n_out), np.float32)
+        assert backend.matvec_rows(x, [ob.RowsJob(dev, y2)])
+        e3, e2 = row_err(y3, want), row_err(y2, want)
+        assert e3 < TIGHT and e2 < TOL and e2 > e3, (e3, e2)
+        one = np.zeros((1, n_out), np.float32)
+        assert backend.matvec_rows(x[1:2], [ob.RowsJob(dev, one)])
+        assert np.array_equal(one[0], y2[1])
+        backend.set_exact(True)
+        ye = np.zeros((3, n_out), np.float32)
+        assert backend.matvec_rows(x, [ob.RowsJob(dev, ye)])
+        assert np.array_equal(ye, y3)
+    finally:
+        backend.set_exact(False)
+        backend.set_fast_planes(False)
+    again = np.zeros((3, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev, again)])
+    assert np.array_equal(again, y3)
