@@ -758,6 +758,7 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
                        "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
                        "frac_of_nominal_8000": gbs / (8000.0 * world), "traffic": None, "bytes_per_launch": int(algo),
                        "peak_source": f"copy bandwidth, {peaks['source']}"}
+    e2e_tokens = min(e2e_tokens, n_tokens)
     if e2e_tokens and world == 1:
         # end to end through DecodePlan::step (b2_plan_step): per token the host hands over x and the RoPE row and reads the
         # hidden state and all logits back, takes the argmax and looks the next row up in a host table (as the reference's

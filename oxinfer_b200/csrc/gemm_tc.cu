@@ -57,12 +57,22 @@ struct F8Scales {  // block scales of an FP8 matrix (formats.cuh); s == nullptr 
                 // epilogue multiplies the outputs by 1 / pre
 };
 
+// The CTA-pair form (cta_group::2): two CTAs of a cluster share every weight tile. Each expands half of its rows (at most
+// 128) and keeps 256 tokens of its own; one thread of the even CTA issues M = 256 instructions that read A from both CTAs
+// and B half from each, so a CTA's shared memory is read for half a B tile per instruction instead of a whole one, and a
+// weight is expanded once per 512 tokens instead of once per 256. Stages are 32 KB (A) + 16 KB (B): four of them fit.
+constexpr int PAIR_STAGES = 4;
+constexpr int PAIR_MAX_TILE_N = 240;                       // the pair's tile; a CTA expands half of it
+constexpr int PAIR_B_STAGE_BYTES = PAIR_MAX_TILE_N / 2 * 128;
+constexpr int PAIR_RAW_BYTES = PAIR_MAX_TILE_N / 2 * 144;  // one of two staging buffers (the copy of super-block sb + 2 flies while sb + 1 is expanded)
+constexpr int MAX_STAGES = 4;
+
 struct __align__(8) Shared {
-    uint64_t a_full[STAGES];
-    uint64_t b_full[STAGES];
-    uint64_t empty[STAGES];
-    uint64_t raw_full;
-    uint64_t raw_empty;
+    uint64_t a_full[MAX_STAGES];
+    uint64_t b_full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t raw_full[2];
+    uint64_t raw_empty[2];
     uint64_t acc_full;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
@@ -70,6 +80,8 @@ struct __align__(8) Shared {
 
 constexpr size_t GEMM_SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + RAW_BYTES + sizeof(Shared);
 static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
+constexpr size_t PAIR_SMEM = 1024 + (size_t)PAIR_STAGES * (A_STAGE_BYTES + PAIR_B_STAGE_BYTES) + 2 * PAIR_RAW_BYTES + sizeof(Shared);
+static_assert(PAIR_SMEM <= 227 * 1024, "shared memory budget (pair form)");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -93,16 +105,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same test with acquire semantics at cluster scope: for barriers that a peer CTA's threads or copies complete.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// The address, in the cluster's shared window, of the CTA of rank `cta`'s copy of a shared-memory object of this CTA.
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of both CTAs
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Bounded wait. Returns false when the CTA is aborting or the limit passed (in which case it records
 // `where` and raises the abort flag). `heed_abort` = false is for the teardown waits. The limit is
 // counted on the SM's own cycle counter (a cheap register read; the global nanosecond timer costs
 // about a microsecond per read, as long as a whole pipeline stage).
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
                                           bool heed_abort = true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto test = [&] { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (test()) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (test()) return true;
         if ((spin & 255) == 0) {
             if (heed_abort && sh->abort_flag) return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
@@ -129,6 +171,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         : "memory");
 }
 
+// The copy of a CTA pair: the data lands in this CTA's shared memory, the bytes are counted on the barrier at the cluster
+// address `cluster_bar` (the even CTA's: its MMA thread waits for both CTAs' tiles on one barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
 // K-major operand tile, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     uint64_t d = 0;
@@ -147,6 +198,20 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// M = 256 over a CTA pair: A rows 0..127 and B rows 0..N/2-1 from the even CTA's shared memory, the rest from the odd CTA's
+// (same offsets in both), accumulator rows 0..127 in the even CTA's tensor memory, 128..255 in the odd CTA's.
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives, when the pair's instructions issued so far have completed, on the barrier at cluster address `cluster_bar`
+// (issued once per CTA of the pair: each CTA's producers and epilogue wait on their own copy of the barrier).
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -163,7 +228,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
 // TT: the instantiation that takes two-term operands (a_lo_row_arg, w_terms); the one-term kernel carries none of that code.
-template <int FMT, bool SPLIT, bool TT>
+// PAIR: the CTA-pair form (4-bit formats, one-term operands, no K split, dense launches of an even number of 256-token
+// tiles): launched as clusters of two CTAs along x = the token tiles; tile_n is then the pair's tile width.
+template <int FMT, bool SPLIT, bool TT, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
@@ -187,13 +254,23 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const int y_dtype = y_dtype_arg & 0xff;
     const bool y_direct = (y_dtype_arg & 0x100) != 0;
     const long long dbg_k0 = clock64();
-    const bool dbg_cta = (dbg & 32768) && blockIdx.x == 1 && blockIdx.y == 0;
+    const bool dbg_cta = (dbg & 32768) && blockIdx.x == (PAIR ? 0 : 1) && blockIdx.y == (PAIR ? 1 : 0);
+    static_assert(!PAIR || (!SPLIT && !TT && FMT != B2_FMT_F8E4M3), "the pair form takes one-term 4-bit operands without a K split");
+    constexpr int STAGES = PAIR ? PAIR_STAGES : b2::STAGES;
+    constexpr int B_STAGE_BYTES = PAIR ? PAIR_B_STAGE_BYTES : b2::B_STAGE_BYTES;
+    constexpr int RAW_BYTES = PAIR ? PAIR_RAW_BYTES : b2::RAW_BYTES;
+    constexpr int NRAW = PAIR ? 2 : 1;  // staging buffers of packed weights
+    // dequantizer sets: groups of warps that take the pipeline stages in turn, one thread per weight row of the CTA's tile
+    constexpr int NSETS = PAIR ? 4 : 2, SET_THREADS = 512 / NSETS, SET_WARPS = SET_THREADS / 32;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + (size_t)STAGES * A_STAGE_BYTES;
     uint8_t* raw = b_tiles + (size_t)STAGES * B_STAGE_BYTES;
-    Shared* sh = (Shared*)(raw + RAW_BYTES);
+    Shared* sh = (Shared*)(raw + NRAW * RAW_BYTES);
+    // pair form: this CTA's rank in its pair (the even CTA issues the instructions) and the rows of the pair's tile it expands
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
+    const int my_rows = PAIR ? tile_n / 2 : tile_n;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // K may be divided between the CTAs of blockIdx.z (k_splits of them, whole super-blocks each): every CTA accumulates
@@ -201,8 +278,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // (SPLIT is a template parameter so that the unsplit kernel carries none of this.)
     const int nsb = SPLIT ? K / (64 * RAW_ST) / k_splits : K / (64 * RAW_ST), nks = nsb * RAW_ST;
     const int sb0 = SPLIT ? (int)blockIdx.z * nsb : 0;
-    const int n0 = blockIdx.x * tile_n;
-    const int m0 = blockIdx.y * 128 * m_halves;
+    // (pair form: the two CTAs of a pair are neighbours in x, the dimension a CTA pair is formed along, so there the token
+    // tiles run along x and the weight tiles along y)
+    const int n0 = (PAIR ? blockIdx.y : blockIdx.x) * tile_n;
+    const int m0 = (PAIR ? blockIdx.x : blockIdx.y) * 128 * m_halves;
     // grouped (MoE) launches: the weights of all experts are stacked, n_out rows each, and every token tile
     // belongs to one expert
     const int w_row0 = tile_expert ? tile_expert[blockIdx.y] * n_out : 0;
@@ -211,28 +290,39 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // multiplied by the activations into the same accumulator. In each dequantizer set warps 0..3 then write the hi terms of
     // rows 0..127 and warps 4..7 the lo terms of the same rows.
     const bool w2 = TT && w_terms == 2;
-    const int row_warps = (tile_n + 31) / 32;
-    const int set_warps = w2 ? 2 * row_warps : row_warps;  // live warps in each of the two dequantizer sets
+    const int row_warps = (my_rows + 31) / 32;
+    const int set_warps = w2 ? 2 * row_warps : row_warps;  // live warps in each dequantizer set
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&sh->a_full[s], 1);
-            mbar_init(&sh->b_full[s], (uint32_t)set_warps);
+            mbar_init(&sh->b_full[s], (uint32_t)(PAIR ? 2 * set_warps : set_warps));  // pair form: both CTAs' warps arrive on the even CTA's
             mbar_init(&sh->empty[s], 1);
         }
-        mbar_init(&sh->raw_full, 1);
-        mbar_init(&sh->raw_empty, (uint32_t)(2 * set_warps));
+        for (int b = 0; b < NRAW; b++) {
+            mbar_init(&sh->raw_full[b], 1);
+            mbar_init(&sh->raw_empty[b], (uint32_t)(NSETS * set_warps));
+        }
         mbar_init(&sh->acc_full, 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {  // the same warp of both CTAs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
+    else
+        __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
 
@@ -248,10 +338,17 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             for (int ks = 0; ks < nks; ks++) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
-                if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)ks)) break;
+                if (!mbar_wait<PAIR>(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)ks)) break;
                 if (dbg & 16) {
                     mbar_arrive(&sh->a_full[s]);
                 } else {
+                    if constexpr (PAIR) {
+                        // both CTAs' tiles are counted on the even CTA's barrier, which expects the bytes of both
+                        if (rank == 0) mbar_arrive_expect_tx(&sh->a_full[s], 2 * a_bytes);
+                        tma_load_2d_pair(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, cluster_addr(&sh->a_full[s], 0), ks * STAGE_K, m0);
+                        a_issued = ks + 1;
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&sh->a_full[s], a_bytes);
                     tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &tmap_x, &sh->a_full[s], (sb0 * RAW_ST + ks) * STAGE_K, m0);
                     if (a_lo_row0 > 0)
@@ -259,36 +356,40 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     a_issued = ks + 1;
                 }
             }
-            if (sh->abort_flag) {
-                // Let the copies still in flight land before the CTA's shared memory is released.
+            if (sh->abort_flag && (!PAIR || rank == 0)) {
+                // Let the copies still in flight land before the CTA's shared memory is released. (Pair form: the odd CTA's
+                // copies are counted on the even CTA's barriers; both CTAs meet at the cluster barrier of the teardown, which
+                // the even CTA reaches only after these waits.)
                 for (int ks = max(0, a_issued - STAGES); ks < a_issued; ks++)
-                    mbar_wait(&sh->a_full[ks % STAGES], (uint32_t)((ks / STAGES) & 1), sh, status, 2, (uint32_t)ks, false);
+                    mbar_wait<PAIR>(&sh->a_full[ks % STAGES], (uint32_t)((ks / STAGES) & 1), sh, status, 2, (uint32_t)ks, false);
             }
         }
     } else if (warp == 18) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
-            const uint32_t w_bytes = (uint32_t)(tile_n * RAW_ROW);
+            const uint32_t w_bytes = (uint32_t)(my_rows * RAW_ROW);
             int w_issued = 0;
             for (int sb = 0; sb < nsb; sb++) {
                 // the staging buffer is free once every dequant warp has taken its copy of super-block sb - 1,
                 // which they do at the start of that super-block: this copy runs a whole super-block ahead
-                if (!mbar_wait(&sh->raw_empty, (uint32_t)((sb & 1) ^ 1), sh, status, 8, (uint32_t)sb)) break;
+                const int rb = sb % NRAW;
+                if (!mbar_wait(&sh->raw_empty[rb], (uint32_t)(((sb / NRAW) & 1) ^ 1), sh, status, 8, (uint32_t)sb)) break;
                 if (dbg & 2) {
-                    mbar_arrive(&sh->raw_full);
+                    mbar_arrive(&sh->raw_full[rb]);
                     continue;
                 }
-                mbar_arrive_expect_tx(&sh->raw_full, w_bytes);
-                tma_load_2d(raw, &tmap_w, &sh->raw_full, (sb0 + sb) * RAW_ROW, w_row0 + n0);
+                mbar_arrive_expect_tx(&sh->raw_full[rb], w_bytes);
+                tma_load_2d(raw + (size_t)rb * RAW_BYTES, &tmap_w, &sh->raw_full[rb], (sb0 + sb) * RAW_ROW, w_row0 + n0 + (int)rank * my_rows);
                 w_issued = sb + 1;
             }
-            if (sh->abort_flag && w_issued > 0)
-                mbar_wait(&sh->raw_full, (uint32_t)((w_issued - 1) & 1), sh, status, 9, (uint32_t)w_issued, false);
+            if (sh->abort_flag)
+                for (int sb = max(0, w_issued - NRAW); sb < w_issued; sb++)
+                    mbar_wait(&sh->raw_full[sb % NRAW], (uint32_t)((sb / NRAW) & 1), sh, status, 9, (uint32_t)sb, false);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(tile_n >> 3) << 17) | ((128u >> 4) << 24);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(tile_n >> 3) << 17) | (((PAIR ? 256u : 128u) >> 4) << 24);
             bool ok = true;
             const long long dbg_t0 = clock64();
             long long dbg_wa = 0, dbg_wb = 0;
@@ -297,14 +398,29 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 int s = ks % STAGES;
                 uint32_t ph = (uint32_t)((ks / STAGES) & 1);
                 const long long w0 = dbg_cta ? clock64() : 0;
-                if (!mbar_wait(&sh->a_full[s], ph, sh, status, 3, (uint32_t)ks)) { ok = false; break; }
+                if (!mbar_wait<PAIR>(&sh->a_full[s], ph, sh, status, 3, (uint32_t)ks)) { ok = false; break; }
                 const long long w1 = dbg_cta ? clock64() : 0;
-                if (!mbar_wait(&sh->b_full[s], ph, sh, status, 4, (uint32_t)ks)) { ok = false; break; }
-                if (dbg_cta) { dbg_wa += w1 - w0; dbg_wb += clock64() - w1; }
+                if (!mbar_wait<PAIR>(&sh->b_full[s], ph, sh, status, 4, (uint32_t)ks)) { ok = false; break; }
+                const bool dbg_alt = dbg_cta && (dbg & 16384);  // report the issue / commit time instead of the two waits
+                if (dbg_cta && !dbg_alt) { dbg_wa += w1 - w0; dbg_wb += clock64() - w1; }
+                const long long i0 = dbg_alt ? clock64() : 0;
                 tc_fence_after();
                 // descriptors differ from the stage-0 ones only in the start-address field (units of 16 bytes)
                 const uint64_t adesc0 = a_desc_base + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
                 const uint64_t bdesc0 = b_desc_base + (uint64_t)((uint32_t)s * (B_STAGE_BYTES >> 4));
+                if constexpr (PAIR) {
+#pragma unroll
+                    for (int kk = 0; kk < STAGE_K / 16; kk++) {
+                        if (dbg & 4) break;
+                        mma_f16_pair(tmem_base, adesc0 + 2 * kk, bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                        mma_f16_pair(tmem_base + 256u, adesc0 + 2 * kk + ((128 * 128) >> 4), bdesc0 + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    const long long i1 = dbg_alt ? clock64() : 0;
+                    mma_commit_pair(cluster_addr(&sh->empty[s], 0));
+                    mma_commit_pair(cluster_addr(&sh->empty[s], 1));
+                    if (dbg_alt) { dbg_wa += i1 - i0; dbg_wb += clock64() - i1; }
+                    continue;
+                }
 #pragma unroll
                 for (int kk = 0; kk < STAGE_K / 16; kk++) {
                     if (!(dbg & 4)) {
@@ -317,9 +433,16 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                         }
                     }
                 }
+                const long long i1 = dbg_alt ? clock64() : 0;
                 mma_commit(&sh->empty[s]);
+                if (dbg_alt) { dbg_wa += i1 - i0; dbg_wb += clock64() - i1; }
             }
-            mma_commit(&sh->acc_full);
+            if constexpr (PAIR) {
+                mma_commit_pair(cluster_addr(&sh->acc_full, 0));
+                mma_commit_pair(cluster_addr(&sh->acc_full, 1));
+            } else {
+                mma_commit(&sh->acc_full);
+            }
             if (dbg_cta) { status->where = (uint32_t)(clock64() - dbg_t0); status->iter = (uint32_t)nks; status->t[0] = (uint32_t)(dbg_t0 - dbg_k0); status->t[1] = (uint32_t)(clock64() - dbg_k0); status->t[5] = (uint32_t)dbg_wa; status->t[6] = (uint32_t)dbg_wb; }
             if (!ok) mbar_wait(&sh->acc_full, 0, sh, status, 5, 0, false);  // drain what was issued before teardown
         }
@@ -330,19 +453,22 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         // "expand 64 weights, wait for the slot, store, fence, arrive", and half as many waits per weight.
         const int dq_warp = warp - 2;
         const int dt = threadIdx.x - 64;
-        const int set = dt >> 8;
-        const int r = w2 ? (dt & 127) : (dt & 255);  // weight row of the tile
+        const int set = dt / SET_THREADS;
+        const int r = w2 ? (dt & 127) : (dt & (SET_THREADS - 1));  // weight row of this CTA's tile
         const bool is_lo = w2 && (dt & 128);
         bool ok = true;
-        if ((w2 ? (dq_warp & 3) : (dq_warp & 7)) < row_warps) {
-            const bool in_tile = r < tile_n;
+        if ((w2 ? (dq_warp & 3) : (dq_warp & (SET_WARPS - 1))) < row_warps) {
+            const bool in_tile = r < my_rows;
+            const uint32_t b_full_even = PAIR ? cluster_addr(&sh->b_full[0], 0) : 0u;  // the even CTA's b_full[0]
             const uint32_t row_off = (uint32_t)(r + (is_lo ? 128 : 0)) * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
-            const uint4* my_raw = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * RAW_ROW);
+            const uint4* my_raw0 = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * RAW_ROW);
             for (int sb = 0; sb < nsb && ok; sb++) {
+                const int rb = sb % NRAW;
+                const uint4* my_raw = (const uint4*)((const uint8_t*)my_raw0 + (size_t)rb * RAW_BYTES);
                 // this row's packed super-block: staging buffer -> registers (only the two 64-groups this set
                 // expands), then release the buffer
-                if (!mbar_wait(&sh->raw_full, (uint32_t)(sb & 1), sh, status, 10, (uint32_t)sb)) {
+                if (!mbar_wait(&sh->raw_full[rb], (uint32_t)((sb / NRAW) & 1), sh, status, 10, (uint32_t)sb)) {
                     ok = false;
                     break;
                 }
@@ -354,7 +480,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 #pragma unroll
                     for (int c = 0; c < 4; c++) qb[c] = my_raw[((uint32_t)(4 * set + c)) ^ swz];
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->raw_empty);
+                    if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
                     float scale = 1.0f;
                     if (f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb0 + sb);
                     const __half2 sc2 = __float2half2_rn(scale * f8.pre);
@@ -373,7 +499,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                             o[8 * c + 2 * i + 1] = h2_bits(__hmul2(*reinterpret_cast<__half2*>(&h23), sc2));
                         }
                     }
-                    if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
+                    if (!mbar_wait<PAIR>(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
                         break;
                     }
@@ -389,17 +515,17 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     continue;
                 }
                 const uint4 hdr = my_raw[0];
-                uint4 q[4];
+                uint4 q[2 * (4 / NSETS)];
 #pragma unroll
-                for (int jj = 0; jj < 2; jj++) {
-                    q[2 * jj] = my_raw[1 + 2 * (set + 2 * jj)];
-                    q[2 * jj + 1] = my_raw[2 + 2 * (set + 2 * jj)];
+                for (int jj = 0; jj < 4 / NSETS; jj++) {
+                    q[2 * jj] = my_raw[1 + 2 * (set + NSETS * jj)];
+                    q[2 * jj + 1] = my_raw[2 + 2 * (set + NSETS * jj)];
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->raw_empty);
+                if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
 #pragma unroll
-                for (int jj = 0; jj < 2; jj++) {
-                    const int j = set + 2 * jj;
+                for (int jj = 0; jj < 4 / NSETS; jj++) {
+                    const int j = set + NSETS * jj;
                     const int ks = sb * 4 + j;
                     const int s = ks % STAGES;
                     const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
@@ -474,7 +600,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                             }
                         }
                     }
-                    if (!mbar_wait(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
+                    if (!mbar_wait<PAIR>(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
                         ok = false;
                         break;
                     }
@@ -488,7 +614,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     }
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->b_full[s]);
+                    if (lane == 0) {
+                        if constexpr (PAIR)
+                            mbar_arrive_cluster(b_full_even + (uint32_t)s * 8u);
+                        else
+                            mbar_arrive(&sh->b_full[s]);
+                    }
                 }
             }
         }
@@ -498,7 +629,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const int half = (dq_warp >> 2) & 1;
         const int cpar = dq_warp >> 3;
         if (half < m_halves) {
-            bool acc_ok = mbar_wait(&sh->acc_full, 0, sh, status, 7, 0) && !sh->abort_flag;
+            bool acc_ok = mbar_wait<PAIR>(&sh->acc_full, 0, sh, status, 7, 0) && !sh->abort_flag;
             acc_ok = __all_sync(0xffffffffu, acc_ok);
             if (dbg_cta && threadIdx.x == 64) status->t[2] = (uint32_t)(clock64() - dbg_k0);
             if (acc_ok) {
@@ -614,11 +745,17 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 
     if (dbg_cta && threadIdx.x == 64) status->t[3] = (uint32_t)(clock64() - dbg_k0);
     tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync_all();  // neither CTA's shared or tensor memory goes away while the other may still signal or read it
+    else
+        __syncthreads();
     if (dbg_cta && threadIdx.x == 64) status->t[4] = (uint32_t)(clock64() - dbg_k0);
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -710,6 +847,8 @@ struct GemmPlan {
     int tile_n, m_halves, n_tiles, m_tiles;
     int k_splits = 1;
     bool y_direct = false;  // f32 output whose rows the copy engine cannot take (stride not a multiple of 16 bytes)
+    bool pair = false;     // the CTA-pair form: clusters of two CTAs along the token tiles, tile_n the pair's width
+    bool pair_asked = false;  // B2_GEMM_PAIR when the plan was made (a cached plan is reused only under the same setting)
     int w_terms = 1;       // 2: two-term weights (Q4_K, tile_n <= 112)
     size_t a_lo_row0 = 0;  // two-term activations: the lo rows start this many rows below the hi rows (0: one term)
     int split_asked = 1;  // B2_GEMM_SPLIT_K when the plan was made (a cached plan is reused only under the same setting)
@@ -718,6 +857,13 @@ struct GemmPlan {
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
     if (w.fmt == B2_FMT_F8E4M3) return w.n_in % 128 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0 && (w.p1 == nullptr || w.bs_cols == 128);
     return (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
+}
+
+// B2_GEMM_PAIR=1 selects the CTA-pair form where a launch qualifies. It is off by default: at the benchmark shape it
+// measures 60.7 us against 57.2 us for the single-CTA form (same build), with bit-identical results.
+static bool pair_form_enabled() {
+    const char* e = getenv("B2_GEMM_PAIR");
+    return e && atoi(e) != 0;
 }
 
 static int split_k_asked() {
@@ -803,6 +949,15 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
             }
         }
     }
+    // The CTA-pair form: dense one-term 4-bit launches of more than one 256-token tile. The token tiles are rounded up to an
+    // even count (a CTA whose tokens are all out of range multiplies zeros and stores nothing).
+    p->pair_asked = pair_form_enabled();
+    p->pair = p->pair_asked && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && !tile_expert && experts == 1 && !a_lo_row0 && w_terms == 1 &&
+              p->k_splits == 1 && p->m_halves == 2 && p->m_tiles >= 2;
+    if (p->pair) {
+        p->m_tiles = (p->m_tiles + 1) / 2 * 2;
+        p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, PAIR_MAX_TILE_N);
+    }
     p->n_tiles = (int)((w.n_out + p->tile_n - 1) / p->tile_n);
     {
         cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)(a_lo_row0 ? a_lo_row0 + t : t)};
@@ -823,7 +978,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         size_t row_bytes = f8 ? w.n_in : w.n_in / 256 * 144;
         cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(w.n_out * experts)};
         cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-        cuuint32_t box[2] = {f8 ? 128u : 144u, (cuuint32_t)p->tile_n};
+        cuuint32_t box[2] = {f8 ? 128u : 144u, (cuuint32_t)(p->pair ? p->tile_n / 2 : p->tile_n)};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = enc(&p->tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.p0, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          f8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -859,7 +1014,7 @@ bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16
                           int w_terms, int m_halves) {
     if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;
     return p && p->experts == 1 && p->a_lo_row0 == a_lo_row0 && p->w_terms == w_terms && (m_halves == 0 || p->m_halves == m_halves) && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
-           p->split_asked == split_k_asked();
+           p->split_asked == split_k_asked() && p->pair_asked == pair_form_enabled();
 }
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
@@ -876,13 +1031,32 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         kern = w.fmt == B2_FMT_MLX4     ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true, false> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false>)
                : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true, false> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false, false>)
                                         : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true, false> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, false>);
+    F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
+    if (p->pair) {
+        kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, false, true>;
+        if (cudaError_t e = ensure_dynamic_smem((const void*)kern, PAIR_SMEM); e != cudaSuccess) return e;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)p->m_tiles, (unsigned)p->n_tiles, 1);
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = PAIR_SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
+                                  y_dtype | (p->y_direct ? 0x100 : 0), status_dev, debug_switches(), (const int*)nullptr, f8, 1, row_unscale, 0, 1);
+        return le;
+    }
     if (cudaError_t e = ensure_dynamic_smem((const void*)kern, GEMM_SMEM); e != cudaSuccess) return e;
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->m_tiles, (unsigned)p->k_splits);
     if (p->k_splits > 1) {  // the shares are added into y
         cudaError_t e = cudaMemsetAsync(y, 0, t * w.n_out * sizeof(float), st);
         if (e != cudaSuccess) return e;
     }
-    F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype | (p->y_direct ? 0x100 : 0),
                                                 status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms);
     return cudaGetLastError();

@@ -236,3 +236,30 @@ def test_split_k_adds_two_shares(backend):
         assert row_err(y1, exact) < 1e-3 and row_err(y2, exact) < 1e-3
         assert row_err(y2, y1.astype(np.float64)) < 1e-5
         assert np.array_equal(y1, y2) == (not split_expected)
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
+@pytest.mark.parametrize("shape", [(48, 256, 300), (1000, 512, 700), (3000, 1024, 1024), (14336, 4096, 512)])
+def test_cta_pair_form_equals_the_single_cta_form(backend, fmt, shape):
+    """B2_GEMM_PAIR=1: more than 256 tokens of a dense 4-bit product run as pairs of CTAs that share each weight tile (one
+    M = 256 instruction over both CTAs' tokens, tcgen05 cta_group::2). Every output is the same k-ordered accumulation as in
+    the single-CTA form: the results must be equal bit for bit, ragged token and row counts included, and within the bound
+    of the f64 product on a sample of rows."""
+    import os
+
+    n_out, n_in, t = shape
+    ref, m = make_pair(fmt, n_out, n_in, 470 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 471)
+    y1 = np.full((t, n_out), np.nan, np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y1)])
+    os.environ["B2_GEMM_PAIR"] = "1"
+    try:
+        y = np.full((t, n_out), np.nan, np.float32)
+        assert backend.matmul(x, [ob.Job(dev, y)])
+    finally:
+        del os.environ["B2_GEMM_PAIR"]
+    assert np.isfinite(y).all()
+    rows = np.unique(np.concatenate([np.arange(0, t, 37), [t - 1, 255, 256]]))
+    assert row_err(y[rows], m.matmul_f64(x[rows])) < TOL
+    assert np.array_equal(y, y1)
