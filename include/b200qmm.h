@@ -150,8 +150,9 @@ int b2_upload_mlx4(b2_ctx* ctx, const uint32_t* w, const uint16_t* scales, const
  * q `[n_out][n_in/2]` in Q4_0 order (byte j of a 32-block = element j low nibble, element j+16 high), scales
  * `[n_out][n_in/32]` f16 bits, offsets `[n_out][n_in/group]` bf16 bits (Offsets, the affine term from_mlx_q4 adds,
  * src/quant.rs:518-563). group a multiple of 64, n_in a multiple of 256. Gives the same device blocks, bit for bit,
- * as b2_upload_mlx4 gives for the MLX triple the matrix was made from. Declined (> 0): offsets == NULL (plain Q4 has a
- * scale per 32 weights), or a matrix whose 64-groups do not share one scale. */
+ * as b2_upload_mlx4 gives for the MLX triple the matrix was made from. offsets == NULL: a plain Q4 matrix (one scale per 32
+ * weights, w = (nibble - 8) * scale; group is ignored, n_in a multiple of 32): what GGUF Q4_0 blocks hold, so it becomes a
+ * B2_FMT_Q4_0 weight on the generic kernels. Declined (> 0): an affine matrix whose 64-groups do not share one scale. */
 int b2_upload_q4(b2_ctx* ctx, const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in,
                  b2_weight* out);
 /* `Backend::upload` for WeightRef::Gguf (declined by the reference at src/cuda.rs:642): raw GGUF

@@ -204,7 +204,7 @@ class Backend:
             assert w.offsets is None or (w.offsets.dtype == np.uint16 and w.offsets.size == n_out * n_in // w.group)
             rc = self._L.b2_upload_q4(self._ctx, _ptr(w.q), _ptr(w.scales), None if w.offsets is None else _ptr(w.offsets), w.group, n_out, n_in,
                                       C.byref(h))
-            fmt = FMT_MLX4
+            fmt = FMT_MLX4 if w.offsets is not None else 2  # plain Q4 becomes a Q4_0 weight
         elif isinstance(w, MlxQ4):
             assert w.w.dtype == np.uint32 and w.scales.dtype == np.uint16 and w.biases.dtype == np.uint16
             assert w.w.size == n_out * n_in // 8 and w.scales.size == n_out * n_in // w.group == w.biases.size

@@ -182,7 +182,19 @@ class Backend {
     // same device blocks as upload_mlx4 does from the on-disk triple.
     int upload_q4(const uint8_t* q, const uint16_t* scales, const uint16_t* offsets, size_t group, size_t n_out, size_t n_in, uint64_t* out) {
         if (!q || !scales || !out) return fail(B2_ERR_ARG, "[b200qmm: upload_q4: null argument]");
-        if (!offsets) return fail(B2_DECLINED, "[b200qmm: upload_q4: a Q4 matrix without offsets (plain --quant q4) has one scale per 32 weights; no device format for it]");
+        if (!offsets) {
+            // A plain Q4 matrix (--quant q4: one f16 scale per 32 weights, w = (nibble - 8) * scale, src/quant.rs:427-440) holds
+            // what GGUF Q4_0 blocks hold, in two arrays: interleaved into 18-byte blocks it runs through the generic kernels.
+            if (n_in % 32 != 0 || n_out == 0) return fail(B2_DECLINED, "[b200qmm: upload_q4: n_in must be a multiple of 32]");
+            const size_t nb32 = n_out * (n_in / 32);
+            std::vector<uint8_t> blocks(nb32 * 18);
+            for (size_t b = 0; b < nb32; b++) {
+                blocks[b * 18] = (uint8_t)(scales[b] & 0xff);
+                blocks[b * 18 + 1] = (uint8_t)(scales[b] >> 8);
+                std::memcpy(&blocks[b * 18 + 2], q + b * 16, 16);
+            }
+            return upload_gguf(B2_FMT_Q4_0, blocks.data(), n_out, n_in, nullptr, 0, 0, out);
+        }
         if (group == 0 || group % 64 != 0 || n_in % 256 != 0 || n_in % group != 0 || n_out == 0)
             return fail(B2_DECLINED, "[b200qmm: upload_q4: the offsets' group must be a multiple of 64 dividing n_in, and n_in a multiple of 256]");
         Weight wt;

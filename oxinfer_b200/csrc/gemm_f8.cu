@@ -24,7 +24,9 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -33,6 +35,12 @@ namespace b2 {
 namespace {
 
 constexpr int F8_STAGES = 4;
+// The CTA-pair form (cta_group::2): two CTAs of a cluster compute 256 tokens x 256 weight rows. Each keeps 128 tokens (its
+// own partial accumulators, promotion and epilogue) and copies HALF of the weight tile; one thread of the even CTA issues
+// M = 256 instructions that read A from both CTAs and half of B from each. Per 128-k block a CTA then moves 32 KB through
+// shared memory instead of 48 KB, and six stages fit.
+constexpr int F8_PAIR_STAGES = 6;
+constexpr int F8_MAX_STAGES = 6;
 constexpr int F8_TM = 128;    // tokens per CTA
 constexpr int F8_TN = 256;    // weight rows per CTA
 constexpr int F8_BK = 128;    // k per stage = one scale block = one 128-byte swizzle row
@@ -42,8 +50,8 @@ constexpr int F8_THREADS = 384;  // warps 0..3: copies, MMAs (two idle); warps 4
 constexpr long long F8_WAIT_LIMIT = 4000000000ll;
 
 struct __align__(8) F8Shared {
-    uint64_t full[F8_STAGES];
-    uint64_t empty[F8_STAGES];
+    uint64_t full[F8_MAX_STAGES];
+    uint64_t empty[F8_MAX_STAGES];
     uint64_t pfull[2];
     uint64_t pfree[2];
     uint32_t tmem_base;
@@ -51,6 +59,8 @@ struct __align__(8) F8Shared {
 };
 constexpr size_t F8_SMEM = 1024 + (size_t)F8_STAGES * (F8_A_BYTES + F8_B_BYTES) + sizeof(F8Shared);
 static_assert(F8_SMEM <= 227 * 1024, "shared memory budget");
+constexpr size_t F8_PAIR_SMEM = 1024 + (size_t)F8_PAIR_STAGES * (F8_A_BYTES + F8_B_BYTES / 2) + sizeof(F8Shared);
+static_assert(F8_PAIR_SMEM <= 227 * 1024, "shared memory budget (pair form)");
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
@@ -70,12 +80,40 @@ __device__ __forceinline__ bool bar_try(uint64_t* bar, uint32_t parity) {
                  : "memory");
     return ok != 0;
 }
+// The same test with acquire semantics at cluster scope: for barriers that the peer CTA's threads, copies or instructions complete.
+__device__ __forceinline__ bool bar_try_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(s32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// The address, in the cluster's shared window, of CTA `cta`'s copy of a shared-memory object of this CTA.
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(s32(p)), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of both CTAs
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, F8Shared* sh, GemmStatus* status, uint32_t where, uint32_t iter,
                                          bool heed_abort = true) {
-    if (bar_try(bar, parity)) return true;
+    auto test = [&] { return CLUSTER ? bar_try_cluster(bar, parity) : bar_try(bar, parity); };
+    if (test()) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1;; spin++) {
-        if (bar_try(bar, parity)) return true;
+        if (test()) return true;
         if ((spin & 255) == 0) {
             if (heed_abort && sh->abort_flag) return false;
             if (clock64() - t0 > F8_WAIT_LIMIT) {
@@ -95,6 +133,13 @@ __device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, uint64
                  "r"(s32(bar)), "r"(x), "r"(y)
                  : "memory");
 }
+// The copy of a CTA pair: the data lands in this CTA's shared memory, the bytes are counted on the barrier at the cluster
+// address `cluster_bar` (the even CTA's: its MMA thread waits for both CTAs' tiles on one barrier). No multicast.
+__device__ __forceinline__ void tma_2d_pair(void* dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(s32(dst)),
+                 "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+                 : "memory");
+}
 // K-major operand tile, 128-byte swizzle: rows 128 bytes apart, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
     uint64_t d = 0;
@@ -111,6 +156,19 @@ __device__ __forceinline__ void mma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// M = 256 over a CTA pair: A rows 0..127 and B rows 0..N/2-1 from the even CTA's shared memory, the others from the odd
+// CTA's (same offsets), accumulator rows 0..127 in the even CTA's tensor memory, 128..255 in the odd CTA's.
+__device__ __forceinline__ void mma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at cluster address `cluster_bar` when the pair's instructions issued so far have completed.
+__device__ __forceinline__ void commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
@@ -149,10 +207,14 @@ __device__ __forceinline__ void tile_of(int id, int m_tiles, int n_tiles, int& m
     m = panel * PM + r - n * pm;
 }
 
+// PAIR: launched as clusters of two CTAs (neighbours in x); m_tiles then counts 256-token tiles of the pair.
+template <bool PAIR>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, int K, int n_out, int t, int m_tiles,
                   int n_tiles, const float* __restrict__ sx, const float* __restrict__ sw, int sw_ncb, int sw_row0, void* __restrict__ y, int y_dtype,
                   GemmStatus* __restrict__ status) {
+    constexpr int F8_STAGES = PAIR ? F8_PAIR_STAGES : b2::F8_STAGES;
+    constexpr int F8_B_BYTES = PAIR ? b2::F8_B_BYTES / 2 : b2::F8_B_BYTES;  // bytes of B this CTA holds per stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
@@ -160,6 +222,9 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     F8Shared* sh = (F8Shared*)(b_tiles + (size_t)F8_STAGES * F8_B_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = K / F8_BK;
+    // pair form: this CTA's rank in its pair; the pair takes the tiles (of 256 tokens) first_tile, first_tile + tile_step, ...
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
+    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     // Persistent: CTA c takes tiles c, c + gridDim.x, ... ; the k-block counter `it` runs on across a CTA's tiles, so the ring
     // and the two partial accumulators keep alternating and the next tile's copies and MMAs start under this tile's epilogue.
     const int total_tiles = m_tiles * n_tiles;
@@ -171,17 +236,25 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         }
         for (int i = 0; i < 2; i++) {
             bar_init(&sh->pfull[i], 1);
-            bar_init(&sh->pfree[i], 8);  // the eight promotion warps
+            bar_init(&sh->pfree[i], PAIR ? 16 : 8);  // the eight promotion warps (pair form: of both CTAs, on the even CTA's barrier)
         }
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh->tmem_base)), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {  // the same warp of both CTAs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh->tmem_base)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh->tmem_base)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
+    else
+        __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sh->tmem_base;
 
@@ -195,44 +268,65 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
             int it = 0;
             bool ok = true;
-            for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += (int)gridDim.x) {
+            for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
                 int mt, nt;
                 tile_of(tile, m_tiles, n_tiles, mt, nt);
                 for (int b = 0; b < nb; b++, it++) {
                     const int s = it % F8_STAGES;
                     const uint32_t ph = (uint32_t)((it / F8_STAGES) & 1);
-                    if (!bar_wait(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)it)) { ok = false; break; }
-                    bar_expect(&sh->full[s], (uint32_t)(F8_A_BYTES + F8_B_BYTES));
-                    tma_2d(a_tiles + (size_t)s * F8_A_BYTES, &tmap_x, &sh->full[s], b * F8_BK, mt * F8_TM);
-                    tma_2d(b_tiles + (size_t)s * F8_B_BYTES, &tmap_w, &sh->full[s], b * F8_BK, nt * F8_TN);
+                    if (!bar_wait<PAIR>(&sh->empty[s], ph ^ 1u, sh, status, 1, (uint32_t)it)) { ok = false; break; }
+                    if constexpr (PAIR) {
+                        // both CTAs' tiles are counted on the even CTA's barrier, which expects the bytes of both
+                        const uint32_t bar0 = cluster_addr(&sh->full[s], 0);
+                        if (rank == 0) bar_expect(&sh->full[s], (uint32_t)(2 * (F8_A_BYTES + F8_B_BYTES)));
+                        tma_2d_pair(a_tiles + (size_t)s * F8_A_BYTES, &tmap_x, bar0, b * F8_BK, mt * 2 * F8_TM + (int)rank * F8_TM);
+                        tma_2d_pair(b_tiles + (size_t)s * F8_B_BYTES, &tmap_w, bar0, b * F8_BK, nt * F8_TN + (int)rank * (F8_TN / 2));
+                    } else {
+                        bar_expect(&sh->full[s], (uint32_t)(F8_A_BYTES + F8_B_BYTES));
+                        tma_2d(a_tiles + (size_t)s * F8_A_BYTES, &tmap_x, &sh->full[s], b * F8_BK, mt * F8_TM);
+                        tma_2d(b_tiles + (size_t)s * F8_B_BYTES, &tmap_w, &sh->full[s], b * F8_BK, nt * F8_TN);
+                    }
                 }
             }
-            if (sh->abort_flag)  // let the copies still in flight land before the shared memory is released
+            // let the copies still in flight land before the shared memory is released (pair form: the odd CTA's copies are
+            // counted on the even CTA's barriers, and both CTAs meet at the cluster barrier of the teardown after these waits)
+            if (sh->abort_flag && rank == 0)
                 for (int j = max(0, it - F8_STAGES); j < it; j++)
-                    bar_wait(&sh->full[j % F8_STAGES], (uint32_t)((j / F8_STAGES) & 1), sh, status, 2, (uint32_t)j, false);
+                    bar_wait<PAIR>(&sh->full[j % F8_STAGES], (uint32_t)((j / F8_STAGES) & 1), sh, status, 2, (uint32_t)j, false);
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             // D f32 (bit 4), A and B e4m3 (format code 0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(F8_TN >> 3) << 17) | ((uint32_t)(F8_TM >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(F8_TN >> 3) << 17) | ((uint32_t)((PAIR ? 2 * F8_TM : F8_TM) >> 4) << 24);
             const uint64_t a_base = desc_sw128(s32(a_tiles)), b_base = desc_sw128(s32(b_tiles));
             bool ok = true;
             int n_mine = 0;
-            for (int tile = (int)blockIdx.x; tile < total_tiles; tile += (int)gridDim.x) n_mine++;
+            for (int tile = first_tile; tile < total_tiles; tile += tile_step) n_mine++;
             const int n_it = n_mine * nb;
             for (int it = 0; it < n_it && ok; it++) {
                 const int s = it % F8_STAGES, buf = it & 1;
-                if (!bar_wait(&sh->full[s], (uint32_t)((it / F8_STAGES) & 1), sh, status, 3, (uint32_t)it)) { ok = false; break; }
+                if (!bar_wait<PAIR>(&sh->full[s], (uint32_t)((it / F8_STAGES) & 1), sh, status, 3, (uint32_t)it)) { ok = false; break; }
                 // the partial accumulator `buf` was last used by block it - 2: wait until its promotion has read it
-                if (it >= 2 && !bar_wait(&sh->pfree[buf], (uint32_t)(((it >> 1) - 1) & 1), sh, status, 4, (uint32_t)it)) { ok = false; break; }
+                if (it >= 2 && !bar_wait<PAIR>(&sh->pfree[buf], (uint32_t)(((it >> 1) - 1) & 1), sh, status, 4, (uint32_t)it)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t ad = a_base + (uint64_t)((uint32_t)s * (F8_A_BYTES >> 4));
                 const uint64_t bd = b_base + (uint64_t)((uint32_t)s * (F8_B_BYTES >> 4));
 #pragma unroll
-                for (int kk = 0; kk < F8_BK / 32; kk++)  // 32 bytes of k per instruction: the descriptors advance by 2 x 16 bytes
-                    mma_f8(tmem_base + (uint32_t)(buf * F8_TN), ad + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
-                commit(&sh->empty[s]);
-                commit(&sh->pfull[buf]);
+                for (int kk = 0; kk < F8_BK / 32; kk++) {  // 32 bytes of k per instruction: the descriptors advance by 2 x 16 bytes
+                    if constexpr (PAIR)
+                        mma_f8_pair(tmem_base + (uint32_t)(buf * F8_TN), ad + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+                    else
+                        mma_f8(tmem_base + (uint32_t)(buf * F8_TN), ad + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+                }
+                if constexpr (PAIR) {  // each CTA's producer and promotion warps wait on their own copies of the barriers
+                    commit_pair(cluster_addr(&sh->empty[s], 0));
+                    commit_pair(cluster_addr(&sh->empty[s], 1));
+                    commit_pair(cluster_addr(&sh->pfull[buf], 0));
+                    commit_pair(cluster_addr(&sh->pfull[buf], 1));
+                } else {
+                    commit(&sh->empty[s]);
+                    commit(&sh->pfull[buf]);
+                }
             }
         }
       }
@@ -245,10 +339,11 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         float acc[128];
         bool ok = true;
         int it = 0;
-        for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += (int)gridDim.x) {
+        const uint32_t pfree_even = PAIR ? cluster_addr(&sh->pfree[0], 0) : 0u;  // the even CTA's pfree[0]
+        for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
             int mt, nt;
             tile_of(tile, m_tiles, n_tiles, mt, nt);
-            const int m0 = mt * F8_TM, n0 = nt * F8_TN;
+            const int m0 = PAIR ? mt * 2 * F8_TM + (int)rank * F8_TM : mt * F8_TM, n0 = nt * F8_TN;
             const int token = m0 + quarter * 32 + lane;
             const int tok_c = min(token, t - 1);
             const float* sx_row = sx + (size_t)tok_c * nb;
@@ -261,7 +356,7 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 const int buf = it & 1;
                 const float c = c_next;
                 if (b + 1 < nb) c_next = __ldg(sx_row + b + 1) * (sw_row ? __ldg(sw_row + b + 1) : 1.0f);
-                if (!bar_wait(&sh->pfull[buf], (uint32_t)((it >> 1) & 1), sh, status, 5, (uint32_t)it)) { ok = false; break; }
+                if (!bar_wait<PAIR>(&sh->pfull[buf], (uint32_t)((it >> 1) & 1), sh, status, 5, (uint32_t)it)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * F8_TN + chalf * 128);
                 // two loads in flight: the next 32 columns travel while this chunk's multiply-adds issue
@@ -278,7 +373,12 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 tmem_ld_wait();
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) bar_arrive(&sh->pfree[buf]);   // the partial is in registers: the MMAs of block it + 2 may overwrite it
+                if (lane == 0) {  // the partial is in registers: the MMAs of block it + 2 may overwrite it
+                    if constexpr (PAIR)
+                        bar_arrive_cluster(pfree_even + (uint32_t)buf * 8u);
+                    else
+                        bar_arrive(&sh->pfree[buf]);
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i++) acc[64 + i] = fmaf(__uint_as_float(va[i]), c, acc[64 + i]);
 #pragma unroll
@@ -321,10 +421,16 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync_all();  // neither CTA's shared or tensor memory goes away while the other may still signal or read it
+    else
+        __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -401,6 +507,11 @@ cudaError_t launch_gemm_f8(const WeightDev& w, const uint8_t* qx, const float* s
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
         return cudaErrorNotSupported;
     }
+    // B2_F8_PAIR=1 selects the CTA-pair form for more than one 128-token tile. Off by default: with two partial accumulators
+    // the MMA -> promotion -> MMA chain of a block crosses SMs twice in that form, and it measures 6.8 ms against 3.2 ms at
+    // 8192 x 12288 x 28672 (bit-identical results).
+    const char* pe = getenv("B2_F8_PAIR");
+    const bool pair = t > (size_t)F8_TM && pe && atoi(pe) != 0;
     CUtensorMap tx, tw;
     cuuint32_t estr[2] = {1, 1};
     {
@@ -417,7 +528,7 @@ cudaError_t launch_gemm_f8(const WeightDev& w, const uint8_t* qx, const float* s
     {
         cuuint64_t dims[2] = {(cuuint64_t)w.n_in, (cuuint64_t)w.n_out};
         cuuint64_t strides[1] = {(cuuint64_t)w.n_in};
-        cuuint32_t box[2] = {(cuuint32_t)F8_BK, (cuuint32_t)F8_TN};
+        cuuint32_t box[2] = {(cuuint32_t)F8_BK, (cuuint32_t)(pair ? F8_TN / 2 : F8_TN)};
         CUresult r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.p0, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) {
@@ -425,12 +536,33 @@ cudaError_t launch_gemm_f8(const WeightDev& w, const uint8_t* qx, const float* s
             return cudaErrorInvalidValue;
         }
     }
-    if (cudaError_t e = ensure_dynamic_smem((const void*)gemm_f8_tc_kernel, F8_SMEM, 0); e != cudaSuccess) return e;
-    const int m_tiles = (int)((t + F8_TM - 1) / F8_TM), n_tiles = (int)((w.n_out + F8_TN - 1) / F8_TN);
+    const int n_tiles = (int)((w.n_out + F8_TN - 1) / F8_TN);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (pair) {
+        auto kern = gemm_f8_tc_kernel<true>;
+        if (cudaError_t e = ensure_dynamic_smem((const void*)kern, F8_PAIR_SMEM, 0); e != cudaSuccess) return e;
+        const int pm_tiles = (int)((t + 2 * F8_TM - 1) / (2 * F8_TM));
+        const int pairs = std::min(pm_tiles * n_tiles, sms / 2);  // persistent: one CTA per SM, two SMs per pair
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(2 * pairs));
+        cfg.blockDim = dim3(F8_THREADS);
+        cfg.dynamicSmemBytes = F8_PAIR_SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;  // a CTA pair is formed along x
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, kern, tx, tw, (int)w.n_in, (int)w.n_out, (int)t, pm_tiles, n_tiles, sx, (const float*)w.p1, (int)w.bs_ncb,
+                                  (int)w.bs_row0, y, y_dtype, status_dev);
+    }
+    if (cudaError_t e = ensure_dynamic_smem((const void*)gemm_f8_tc_kernel<false>, F8_SMEM, 0); e != cudaSuccess) return e;
+    const int m_tiles = (int)((t + F8_TM - 1) / F8_TM);
     const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;  // persistent: one CTA per SM
-    gemm_f8_tc_kernel<<<(unsigned)grid, F8_THREADS, F8_SMEM, st>>>(tx, tw, (int)w.n_in, (int)w.n_out, (int)t, m_tiles, n_tiles, sx,
+    gemm_f8_tc_kernel<false><<<(unsigned)grid, F8_THREADS, F8_SMEM, st>>>(tx, tw, (int)w.n_in, (int)w.n_out, (int)t, m_tiles, n_tiles, sx,
                                                                                    (const float*)w.p1, (int)w.bs_ncb, (int)w.bs_row0, y, y_dtype,
                                                                                    status_dev);
     return cudaGetLastError();

@@ -76,8 +76,18 @@ def test_q4matrix_upload_gives_the_same_device_values_as_the_mlx_triple(backend,
     ya, yb = np.zeros((1, n_out), np.float32), np.zeros((1, n_out), np.float32)
     assert backend.matvec_rows(x, [ob.RowsJob(dev_a, ya)]) and backend.matvec_rows(x, [ob.RowsJob(dev_b, yb)])
     assert np.array_equal(ya, yb)
-    # plain Q4 (no offsets: a scale per 32 weights) and a matrix whose 64-groups do not share a scale are declined
-    assert backend.upload(ob.Q4Matrix(q, sc, None, group), n_out, n_in) is None
+    # plain Q4 (no offsets: a scale per 32 weights, w = (nibble - 8) * scale, src/quant.rs:586-606) is what Q4_0 blocks hold
+    # and runs through the generic kernels: bit-exact values, products within the matrix-vector bound
+    dev_p = backend.upload(ob.Q4Matrix(q, sc, None, group), n_out, n_in)
+    assert dev_p is not None, backend.last_declined
+    nib = np.stack([q.reshape(n_out, n_in // 32, 16) & 0xF, q.reshape(n_out, n_in // 32, 16) >> 4], axis=2).reshape(n_out, n_in // 32, 32)
+    plain = ((nib.astype(np.float32) - 8.0) * sc.view(np.float16).astype(np.float32).reshape(n_out, n_in // 32, 1)).reshape(n_out, n_in)
+    assert np.array_equal(backend.dequantize_rows(dev_p).view(np.uint32), plain.view(np.uint32))
+    yp = np.zeros((1, n_out), np.float32)
+    assert backend.matvec_rows(x, [ob.RowsJob(dev_p, yp)])
+    from util import row_err
+    assert row_err(yp, x.astype(np.float64) @ plain.astype(np.float64).T) < 2e-5
+    # a matrix whose 64-groups do not share a scale is declined
     sc2 = sc.copy()
     sc2[1] ^= 1
     assert backend.upload(ob.Q4Matrix(q, sc2, off, group), n_out, n_in) is None and "differ in scale" in backend.last_declined

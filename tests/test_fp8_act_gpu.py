@@ -86,3 +86,29 @@ def test_default_keeps_the_reference_definition(backend):
     y = np.zeros((t, n_out), np.float32)
     assert backend.matmul(x, [ob.Job(dev, y)])
     assert row_err(y, m.matmul_f64(x)) < 2e-3
+
+
+@pytest.mark.parametrize("shape", [(1000, 2048, 700), (2304, 4096, 1024), (256, 256, 129)])
+def test_fp8_cta_pair_form_equals_the_single_cta_form(fp8_backend, shape):
+    """B2_F8_PAIR=1: more than 128 tokens run as pairs of CTAs that share each weight tile (M = 256 instructions, tcgen05
+    cta_group::2). Each output is the same sequence of 128-k partial sums promoted in the same order: the results must be
+    equal to the single-CTA form's bit for bit, ragged token and row counts included."""
+    import os
+
+    n_out, n_in, t = shape
+    ref, m = make_pair("f8_e4m3", n_out, n_in, 520 + t)
+    dev = fp8_backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 521)
+    y1 = np.full((t, n_out), np.nan, np.float32)
+    assert fp8_backend.matmul(x, [ob.Job(dev, y1)])
+    os.environ["B2_F8_PAIR"] = "1"
+    try:
+        y = np.full((t, n_out), np.nan, np.float32)
+        assert fp8_backend.matmul(x, [ob.Job(dev, y)])
+    finally:
+        del os.environ["B2_F8_PAIR"]
+    assert np.isfinite(y).all()
+    assert np.array_equal(y, y1)
+    rows = np.unique(np.concatenate([np.arange(0, t, 53), [t - 1, 127, 128]]))
+    want, _ = oracle_fp8_act(m, x[rows])
+    assert row_err(y[rows], want) < 1e-5
