@@ -128,6 +128,50 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict
     if (threadIdx.x == 0) unscale[row] = inv;
 }
 
+// The same with a warp per row (eight rows per CTA, no CTA barrier): h = 128 * VPL, a lane keeps VPL float4. A CTA per row
+// costs more in CTA launches than in bytes once there are tens of thousands of rows.
+__device__ __forceinline__ float warp_max(float mx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    return mx;
+}
+template <int VPL>
+__global__ void __launch_bounds__(256) moe_gather_warp_kernel(const float* __restrict__ x, const int* __restrict__ src, int rows, __half* __restrict__ xg,
+                                                              float* __restrict__ unscale, size_t lo_off) {
+    constexpr int H = 128 * VPL;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int s = src[row];
+    __half* o = xg + (size_t)row * H;
+    if (s < 0) {
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            const int c = (j * 32 + lane) * 4;
+            *(uint2*)(o + c) = make_uint2(0u, 0u);
+            if (lo_off) *(uint2*)(o + lo_off + c) = make_uint2(0u, 0u);
+        }
+        if (lane == 0) unscale[row] = 1.0f;
+        return;
+    }
+    const float4* in = (const float4*)(x + (size_t)s * H);
+    float4 v[VPL];
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        v[j] = in[j * 32 + lane];
+        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+    }
+    mx = warp_max(mx);
+    float f, inv;
+    row_factor(mx, f, inv);
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int c = (j * 32 + lane) * 4;
+        store_terms(v[j], f, o + c, lo_off ? o + lo_off + c : nullptr);
+    }
+    if (lane == 0) unscale[row] = inv;
+}
+
 // a[row][inter] (f16) = silu(g[row][c]) * g[row][inter + c] * factor[row] over the fused gate_up output g [rows][2 inter]
 // (f32); factor[row] is the power of two of row_factor and unscale[row] = 1 / factor is what the down projection's epilogue
 // multiplies the row's results by. lo_off as for the gather. src[row] < 0 marks a padding row (src may be null: no
@@ -203,6 +247,48 @@ __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ 
         for (int c = threadIdx.x * 4; c < inter; c += 256 * 4) store_terms(act4(c), f, ar + c, lo_off ? ar + lo_off + c : nullptr);
     }
     if (threadIdx.x == 0) unscale[row] = inv;
+}
+
+// The same with a warp per row (eight rows per CTA): inter = 128 * VPL, a lane keeps its VPL float4 of products.
+template <int VPL>
+__global__ void __launch_bounds__(256) moe_act_warp_kernel(const float* __restrict__ g, const int* __restrict__ src, int rows, __half* __restrict__ a,
+                                                           float* __restrict__ unscale, size_t lo_off, int kind, float limit) {
+    constexpr int INTER = 128 * VPL;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    __half* ar = a + (size_t)row * INTER;
+    if (src && src[row] < 0) {
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            const int c = (j * 32 + lane) * 4;
+            *(uint2*)(ar + c) = make_uint2(0u, 0u);
+            if (lo_off) *(uint2*)(ar + lo_off + c) = make_uint2(0u, 0u);
+        }
+        if (lane == 0) unscale[row] = 1.0f;
+        return;
+    }
+    const float* gr = g + (size_t)row * 2 * INTER;
+    float4 v[VPL];
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int c = (j * 32 + lane) * 4;
+        const float4 gate = *(const float4*)(gr + c), up = *(const float4*)(gr + INTER + c);
+        v[j].x = gated_act(gate.x, up.x, kind, limit);
+        v[j].y = gated_act(gate.y, up.y, kind, limit);
+        v[j].z = gated_act(gate.z, up.z, kind, limit);
+        v[j].w = gated_act(gate.w, up.w, kind, limit);
+        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+    }
+    mx = warp_max(mx);
+    float f, inv;
+    row_factor(mx, f, inv);
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int c = (j * 32 + lane) * 4;
+        store_terms(v[j], f, ar + c, lo_off ? ar + lo_off + c : nullptr);
+    }
+    if (lane == 0) unscale[row] = inv;
 }
 
 // y[tok][c] += sum over the token's k routes, in order, of w * o[slot][c].
@@ -285,14 +371,27 @@ cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k,
 
 cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_t h, void* xg, float* unscale, size_t lo_row0, cudaStream_t st) {
     if (h % 256 || h > (size_t)GATHER_KEEP * 1024) return cudaErrorInvalidValue;
-    moe_gather_kernel<<<(unsigned)rows, 256, 0, st>>>(x, src, (int)h, (__half*)xg, unscale, lo_row0 * h);
+    if (rows == 0) return cudaSuccess;
+    const unsigned wgrid = (unsigned)((rows + 7) / 8);
+    switch (rows >= 1024 ? h / 128 : 0) {  // many rows of a common width: a warp per row
+        case 8: moe_gather_warp_kernel<8><<<wgrid, 256, 0, st>>>(x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h); break;
+        case 16: moe_gather_warp_kernel<16><<<wgrid, 256, 0, st>>>(x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h); break;
+        default: moe_gather_kernel<<<(unsigned)rows, 256, 0, st>>>(x, src, (int)h, (__half*)xg, unscale, lo_row0 * h);
+    }
     return cudaGetLastError();
 }
 
 cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* unscale, size_t lo_row0, cudaStream_t st,
                            int kind, float limit) {
     if (inter % 256) return cudaErrorInvalidValue;
-    moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+    if (rows == 0) return cudaSuccess;
+    const unsigned wgrid = (unsigned)((rows + 7) / 8);
+    switch (rows >= 1024 ? inter / 128 : 0) {  // many rows of a common width: a warp per row
+        case 4: moe_act_warp_kernel<4><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
+        case 6: moe_act_warp_kernel<6><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
+        case 8: moe_act_warp_kernel<8><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
+        default: moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+    }
     return cudaGetLastError();
 }
 
