@@ -130,7 +130,8 @@ def cpu_prefill_tflops(threads: int, steps: int, warmup: int):
 def base_config(world: int) -> dict:
     """The `config` both arms print (same keys, same values)."""
     return {"workload": WORKLOAD,
-            "parallelism": f"tp{world}: weight rows sharded, NCCL all-gather of y inside the step" if world > 1 else "single GPU",
+            "parallelism": (f"tp{world}: weight rows sharded, every rank ends each step with the whole y (gathered by the GEMM epilogue's peer stores "
+                            "over NVLink, or by an NCCL all-gather where that path is declined)") if world > 1 else "single GPU",
             "l2": "inputs larger than L2: rotating over weight copies of more than twice the L2 size"}
 
 
@@ -501,9 +502,11 @@ def moe_ep_extras(be, torch, dist, rank, world):
 
     E, K, H, I = 128, 8, 2048, 768
     assert E % world == 0
-    box = [ob.Backend.comm_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
-    be.comm_init(world, rank, box[0])
+    if not getattr(be, "comm_ready", False):
+        box = [ob.Backend.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        be.comm_init(world, rank, box[0])
+        be.comm_ready = True
     protos = [(synth.mlx4(2 * I, H, 900 + i), synth.mlx4(H, I, 950 + i)) for i in range(8)]
     pe = E // world
     gu = [be.upload(protos[e % 8][0], 2 * I, H) for e in range(rank * pe, (rank + 1) * pe)]
@@ -872,6 +875,7 @@ def run_b200(args, rank, world, local_rank):
 
     # ---- N > 1: before anything is timed, this rank's shard against the same rows of the unsharded product ----
     parity = None
+    peer_ok, peer_note = [False], [None]
     if world > 1:
         dfull = be.upload(full, N_OUT, K_IN)
         y_all = torch.empty((M_TOK, N_OUT), device="cuda", dtype=torch.float32)
@@ -882,6 +886,26 @@ def run_b200(args, rank, world, local_rank):
         dist.all_gather_into_tensor(y_full, ys[0])
         torch.cuda.synchronize()
         same = same and torch.equal(y_full.permute(1, 0, 2).reshape(M_TOK, N_OUT).view(torch.int32), y_all.view(torch.int32))
+        # the gather done by the GEMM's own epilogue (b2_matmul_sharded_peer): the library's communicator carries the buffers'
+        # handles once; the result must equal the unsharded product bit for bit too
+        try:
+            box = [ob.Backend.comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            be.comm_init(world, rank, box[0])
+            be.comm_ready = True
+            for i in range(3):
+                yp = be.matmul_sharded_peer(devs[i % copies], x_bf16)
+                if yp is None:
+                    break
+                torch.cuda.synchronize()
+                be.check_status()
+                same = same and torch.equal(yp.view(torch.int32), y_all.view(torch.int32)) if i == 0 else same
+            peer_ok[0] = yp is not None
+        except Exception as e:   # no NCCL, no peer access: the NCCL-through-torch gather stays
+            peer_note[0] = str(e)
+        agree = torch.tensor([1 if peer_ok[0] else 0], device="cuda", dtype=torch.int32)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        peer_ok[0] = int(agree.item()) == 1
         flag = torch.tensor([1 if same else 0], device="cuda", dtype=torch.int32)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         parity = "bit-identical" if int(flag.item()) == 1 else "MISMATCH"
@@ -889,6 +913,11 @@ def run_b200(args, rank, world, local_rank):
         del y_all
 
     def step(i, gather=True):
+        """gather: True = the fastest available way to leave the whole y on every rank, "nccl" = the library collective,
+        False = none (y stays sharded)."""
+        if world > 1 and gather is True and peer_ok[0]:
+            assert be.matmul_sharded_peer(devs[i % copies], x_bf16) is not None
+            return
         y = ys[i % ycopies]
         ok = be.matmul_dev(devs[i % copies], x_bf16, y)
         assert ok
@@ -948,6 +977,7 @@ def run_b200(args, rank, world, local_rank):
     launches = (be.launch_count() - launches0) // repeats
     be.check_status()
     ms_compute = timed(args.steps * repeats, gather=False) if world > 1 else ms_total
+    ms_nccl = timed(args.steps * repeats, gather="nccl") if world > 1 and peer_ok[0] else ms_total
 
     # ---- end to end through the host-buffer call (b2_matmul): pinned x in, y out, every step ----
     xh = torch.from_numpy(x_host).pin_memory()
@@ -966,10 +996,10 @@ def run_b200(args, rank, world, local_rank):
     e2e_ms_total = e2.elapsed_time(e3)
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms_total, e2e_ms_total, kern_ms, ms_compute], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms_total, e2e_ms_total, kern_ms, ms_compute, ms_nccl], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total, kern_ms, ms_compute = (float(v) for v in t.cpu())
+    ms_total, e2e_ms_total, kern_ms, ms_compute, ms_nccl = (float(v) for v in t.cpu())
 
     dec_tp = None
     if world > 1 and args.section == "all":   # collective: every rank runs the tensor-parallel decode plan
@@ -998,8 +1028,11 @@ def run_b200(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "repeats": repeats,
             "timed_region_ms": ms_total, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 operands, f32 accumulate", "data": "synthetic", "config": cfg,
-            "step": ("x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel on this rank's rows + NCCL all-gather of the f32 y "
-                     f"({M_TOK * N_OUT * 4 / 1e6:.0f} MB) into rank-major blocks" if world > 1 else
+            "step": (("x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel on this rank's rows whose epilogue stores every tile into "
+                      f"every rank's y ({M_TOK * N_OUT * 4 / 1e6:.0f} MB, bulk tensor stores over NVLink) + the ranks' meeting kernel"
+                      if peer_ok[0] else
+                      "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel on this rank's rows + NCCL all-gather of the f32 y "
+                      f"({M_TOK * N_OUT * 4 / 1e6:.0f} MB) into rank-major blocks") if world > 1 else
                      "x bf16 -> f16 conversion kernel + tcgen05 dequant-GEMM kernel"),
             "inputs": f"{copies} weight copies ({copies * shard_bytes / 1e6:.0f} MB) and {ycopies} outputs in rotation",
             "e2e": {"value": FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
@@ -1017,6 +1050,12 @@ def run_b200(args, rank, world, local_rank):
             ms_c = ms_compute / n_timed
             line["compute_only"] = {"value": FLOP_PER_STEP / (ms_c * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_c,
                                     "note": "the same steps without the all-gather (y left sharded by columns on the ranks)"}
+            if peer_ok[0]:
+                ms_n = ms_nccl / n_timed
+                line["nccl_gather"] = {"value": FLOP_PER_STEP / (ms_n * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_n,
+                                       "note": "the same steps with the GEMM's result gathered by an NCCL all-gather instead of the epilogue's peer stores"}
+            elif peer_note[0]:
+                line["peer_store_unavailable"] = peer_note[0]
         if world == 1 and args.section == "all":
             from oracle import oracle as O
 

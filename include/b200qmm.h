@@ -350,6 +350,16 @@ int b2_comm_free(b2_ctx* ctx);
  * ncclAllGather, a copy of the ranks' blocks into their columns). Bit-identical to the unsharded b2_matmul_dev: every
  * column is computed by the kernel that computes it on one GPU. Not synchronized. */
 int b2_matmul_sharded(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float* y_dev);
+/* The same product with the all-gather done by the GEMM kernel itself (no library collective in the step): every rank keeps a
+ * result buffer that the other ranks map (CUDA IPC, exchanged once through the communicator when the buffer is first made or
+ * grows: that part is collective and synchronizes); the tensor-core GEMM's epilogue stores each finished tile into this
+ * rank's columns of its own buffer and of every peer's buffer with bulk tensor stores over NVLink, and a one-CTA kernel then
+ * makes the ranks meet (flags in the peers' buffers, bounded polling: a missing rank gives B2_ERR_TIMEOUT from
+ * b2_check_status, not a hang). *y_full_dev is this rank's buffer [t][world * n_local] f32: complete once the stream reaches
+ * the end of the call, valid until the call after the next one (two areas alternate). Bit-identical to b2_matmul_sharded.
+ * Declined (> 0): up to 8 tokens, formats without a tensor-core kernel, FP8 x FP8 mode, n_local % 4 != 0, more than 8 ranks:
+ * use b2_matmul_sharded then. 2 to 8 ranks of one NVLink domain, one process per GPU. */
+int b2_matmul_sharded_peer(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float** y_full_dev);
 /* Expert-parallel `Backend::moe`: the layer's n_experts_global experts are sharded over the ranks in equal contiguous parts
  * and `m` holds this rank's (b2_upload_moe over them, local numbering); x_dev / y_dev [t][h] are THIS rank's tokens,
  * route_ids [t][k] (host) are global expert numbers, route_w [t][k] (host) their weights. Every (token, route) pair goes to

@@ -133,6 +133,7 @@ _SIGNATURES = {
     "b2_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "b2_comm_free": (C.c_int, [C.c_void_p]),
     "b2_matmul_sharded": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
+    "b2_matmul_sharded_peer": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
     "b2_moe_ep": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b2_matvec_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
 }

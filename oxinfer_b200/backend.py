@@ -117,6 +117,20 @@ def _ptr(a) -> int:
     return a.data_ptr()
 
 
+class _DeviceArray:
+    """A raw device pointer with a shape, as torch reads it (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, shape: tuple):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def _device_f32_tensor(ptr: int, shape: tuple, device):
+    """An f32 torch tensor over device memory the library owns (no copy)."""
+    import torch
+
+    return torch.as_tensor(_DeviceArray(ptr, shape), device=device)
+
+
 _TORCH_DTYPES = None
 
 
@@ -321,6 +335,18 @@ class Backend:
         t = x.shape[0]
         assert x.shape[1] == shard.n_in and y.shape[0] == t and y.is_cuda and x.is_cuda
         return self._check(self._L.b2_matmul_sharded(self._ctx, shard.handle, _ptr(x), _dtype_code(x), t, _ptr(y)))
+
+    def matmul_sharded_peer(self, shard: DeviceWeight, x):
+        """The same with the gather done by the GEMM's epilogue (peer stores over NVLink): returns this rank's full ``y`` as a
+        torch tensor over the library's buffer (valid until the call after the next one), or None when declined; collective."""
+        import torch
+
+        t = x.shape[0]
+        assert x.shape[1] == shard.n_in and x.is_cuda
+        out = C.c_void_p()
+        if not self._check(self._L.b2_matmul_sharded_peer(self._ctx, shard.handle, _ptr(x), _dtype_code(x), t, C.byref(out))):
+            return None
+        return _device_f32_tensor(out.value, (t, shard.n_out * self.world), x.device)
 
     def moe_ep(self, x, routes_ids: np.ndarray, routes_w: np.ndarray, dev: "MoeWeights", n_experts_global: int, y) -> bool:
         """Expert-parallel ``moe``: ``dev`` holds this rank's experts, the routes name global experts; collective."""

@@ -486,12 +486,16 @@ class Backend {
     static bool rows_path(const WeightDev& w) { return (w.fmt == B2_FMT_Q6_K || w.fmt == B2_FMT_Q8_0) && gemv_supports(w); }
 
     // t tokens on the device through the tensor-core GEMM (or token by token through the GEMV).
-    int matmul_dev(uint64_t h, const void* x, int x_dtype, size_t t, void* y, int y_dtype) {
+    // peer_y (matmul_sharded_peer): the result goes, tile by tile from the GEMM's epilogue, to this rank's columns of its own y and
+    // of the peers' copies; only the tensor-core GEMM takes it, every other route declines.
+    int matmul_dev(uint64_t h, const void* x, int x_dtype, size_t t, void* y, int y_dtype, const GemmPeerY* peer_y = nullptr) {
         Weight* w = find(h);
         if (!w) return fail(B2_ERR_ARG, "[b200qmm: matmul: unknown weight]");
         if (t == 0) return B2_OK;
         if (y_dtype != B2_F32 && y_dtype != B2_BF16) return fail(B2_ERR_ARG, "[b200qmm: matmul: y must be f32 or bf16]");
         size_t K = w->dev.n_in;
+        if (peer_y && (t <= 8 || y_dtype != B2_F32 || !gemm_tc_supports(w->dev, t) || (fp8_act && !exact && w->dev.fmt == B2_FMT_F8E4M3)))
+            return fail(B2_DECLINED, "[b200qmm: matmul_sharded_peer: only the tensor-core GEMM with f32 results stores to peers (more than 8 tokens)]");
         if (fmt_is_other(w->dev.fmt)) {
             // no tensor-core kernel for these formats: four tokens at a time through the generic matrix-vector kernel (the weights
             // are read once per four tokens; every row equals its one-token row bit for bit)
@@ -587,7 +591,7 @@ class Backend {
         // Tensor maps (activations + packed weights) are cached per (weights, activations, t).
         GemmPlan* plan = nullptr;
         for (GemmPlan* p : plans)
-            if (gemm_tc_plan_matches(p, w->dev, xh, t, y, y_dtype, lo_row0, w_terms, lo_row0 ? 1 : 0)) {
+            if (gemm_tc_plan_matches(p, w->dev, xh, t, y, y_dtype, lo_row0, w_terms, lo_row0 ? 1 : 0, peer_y)) {
                 plan = p;
                 break;
             }
@@ -597,7 +601,7 @@ class Backend {
                 plans.clear();
             }
             char msg[256] = {0};
-            e = gemm_tc_plan_create(w->dev, xh, t, y, y_dtype, &plan, msg, sizeof msg, 1, nullptr, lo_row0 ? 1 : 0, lo_row0, w_terms);
+            e = gemm_tc_plan_create(w->dev, xh, t, y, y_dtype, &plan, msg, sizeof msg, 1, nullptr, lo_row0 ? 1 : 0, lo_row0, w_terms, peer_y);
             if (e != cudaSuccess) return fail(B2_ERR_CUDA, "[b200qmm: %s]", msg);
             plans.push_back(plan);
         }
@@ -1049,6 +1053,7 @@ class Backend {
     int comm_free() {
         if (comm) {
             cudaStreamSynchronize(stream);
+            tp_sym_release();
             nccl_api().CommDestroy(comm);
         }
         comm = nullptr;
@@ -1077,6 +1082,103 @@ class Backend {
         e = launch_scatter_blocks((const float*)tp_gather.p, (size_t)world, t, nl, y, stream);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "scatter_blocks");
+        return B2_OK;
+    }
+
+    // ---- the same product with the all-gather done by the GEMM's own epilogue -------------------------------------------------
+    // Every rank keeps a buffer of the same size, mapped into the other ranks (CUDA IPC): 1 KB of flag words, then two result
+    // areas used in turn. A rank's GEMM stores each finished tile into its columns of ITS OWN area and of EVERY PEER's area
+    // (bulk tensor stores through NVLink), then the ranks meet (flags written into the peers' buffers with system-scope
+    // release, bounded polling of the own ones): past that point on the stream, the area holds the whole y. The areas
+    // alternate so that a call never writes what a peer may still be reading from the call before.
+    struct TpSym {
+        uint8_t* local = nullptr;
+        size_t half = 0;  // bytes of one result area
+        uint8_t* peer[8] = {};
+        uint32_t calls = 0;
+    } tp_sym;
+    static constexpr size_t TP_SYM_HEADER = 1024;
+
+    void tp_sym_release() {
+        for (int p = 0; p < 8; p++)
+            if (tp_sym.peer[p]) cudaIpcCloseMemHandle(tp_sym.peer[p]);
+        if (tp_sym.local) cudaFree(tp_sym.local);
+        tp_sym = TpSym{};
+    }
+    // Collective (every rank calls it with the same size): makes the buffers at least `bytes` per area.
+    int tp_sym_reserve(size_t bytes) {
+        if (tp_sym.half >= bytes) return B2_OK;
+        const NcclApi& n = nccl_api();
+        cudaError_t e = tp_stage.reserve(64 + 64 * (size_t)world);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(handle exchange)");
+        // 1. nobody maps an old buffer any more before anybody frees one
+        for (int p = 0; p < 8; p++)
+            if (tp_sym.peer[p]) {
+                cudaIpcCloseMemHandle(tp_sym.peer[p]);
+                tp_sym.peer[p] = nullptr;
+            }
+        int nrc = n.AllGather(tp_stage.p, (uint8_t*)tp_stage.p + 64, 16, NCCL_FLOAT32, comm, stream);
+        if (nrc) return nccl_fail(nrc, "ncclAllGather(barrier)");
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return cuda_fail(e, "synchronize");
+        if (tp_sym.local) cudaFree(tp_sym.local);
+        tp_sym = TpSym{};
+        // 2. the new buffer, its flags cleared, and its handle to everybody
+        const size_t half = (bytes + ((size_t)1 << 20) - 1) >> 20 << 20;
+        if ((e = cudaMalloc((void**)&tp_sym.local, TP_SYM_HEADER + 2 * half)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(result buffer)");
+        cudaIpcMemHandle_t mine;
+        static_assert(sizeof mine == 64, "handle size");
+        if ((e = cudaMemsetAsync(tp_sym.local, 0, TP_SYM_HEADER, stream)) != cudaSuccess || (e = cudaIpcGetMemHandle(&mine, tp_sym.local)) != cudaSuccess ||
+            (e = cudaMemcpyAsync(tp_stage.p, &mine, 64, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+            return cuda_fail(e, "cudaIpcGetMemHandle");
+        nrc = n.AllGather(tp_stage.p, (uint8_t*)tp_stage.p + 64, 16, NCCL_FLOAT32, comm, stream);
+        if (nrc) return nccl_fail(nrc, "ncclAllGather(handles)");
+        std::vector<cudaIpcMemHandle_t> all((size_t)world);
+        if ((e = cudaMemcpyAsync(all.data(), (uint8_t*)tp_stage.p + 64, 64 * (size_t)world, cudaMemcpyDeviceToHost, stream)) != cudaSuccess ||
+            (e = cudaStreamSynchronize(stream)) != cudaSuccess)
+            return cuda_fail(e, "handle exchange");
+        for (int p = 0; p < world; p++) {
+            if (p == rank) continue;
+            void* m = nullptr;
+            if ((e = cudaIpcOpenMemHandle(&m, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle(peer result buffer)");
+            tp_sym.peer[p] = (uint8_t*)m;
+        }
+        tp_sym.half = half;
+        return B2_OK;
+    }
+
+    // y_out: this rank's copy of y [t][world * n_local] (f32), inside the library's buffer, complete once the stream reaches the
+    // end of this call and valid until the call after the next one. Bit-identical to matmul_sharded.
+    int matmul_sharded_peer(uint64_t h, const void* x, int x_dtype, size_t t, float** y_out) {
+        Weight* w = find(h);
+        if (!w || !y_out) return fail(B2_ERR_ARG, "[b200qmm: matmul_sharded_peer: unknown weight or null result pointer]");
+        if (!comm || world < 2 || world > 8) return fail(B2_DECLINED, "[b200qmm: matmul_sharded_peer: needs a communicator of 2 to 8 ranks (b2_comm_init)]");
+        const size_t nl = w->dev.n_out, N = nl * (size_t)world;
+        if (t <= 8 || nl % 4 || !gemm_tc_supports(w->dev, t) || (fp8_act && !exact && w->dev.fmt == B2_FMT_F8E4M3))
+            return fail(B2_DECLINED, "[b200qmm: matmul_sharded_peer: only the tensor-core GEMM with f32 results stores to peers (more than 8 tokens, n_out %% 4 == 0)]");
+        int rc = tp_sym_reserve(t * N * 4);
+        if (rc) return rc;
+        if ((rc = ensure_status())) return rc;
+        const size_t area = TP_SYM_HEADER + (size_t)(tp_sym.calls & 1) * tp_sym.half;
+        float* mine = (float*)(tp_sym.local + area);
+        GemmPeerY py;
+        py.ld = N;
+        PeerSet ps{};
+        ps.rank = (uint32_t)rank;
+        ps.world = (uint32_t)world;
+        for (int p = 0; p < world; p++) {
+            uint8_t* base = p == rank ? tp_sym.local : tp_sym.peer[p];
+            ps.base[p] = (float*)(base + area);
+            ps.flags[p] = (uint32_t*)base;
+            if (p != rank) py.more[py.n_more++] = (float*)(base + area) + (size_t)rank * nl;
+        }
+        rc = matmul_dev(h, x, x_dtype, t, mine + (size_t)rank * nl, B2_F32, &py);
+        if (rc) return rc;
+        // the ranks meet: every rank's tiles have landed in every buffer (the kernel waited for its stores before it ended)
+        cudaError_t e = launch_exchange(ps, 0, 0, (uint32_t*)tp_sym.local, &gemm_status->code, stream, false, false);
+        launches++;
+        if (e != cudaSuccess) return cuda_fail(e, "peer barrier");
+        tp_sym.calls++;
+        *y_out = mine;
         return B2_OK;
     }
 
@@ -1555,6 +1657,11 @@ B2_EXPORT int b2_comm_free(b2_ctx* ctx) {
 B2_EXPORT int b2_matmul_sharded(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float* y_dev) {
     LOCKED(ctx);
     return ctx->be.matmul_sharded(w_shard, x_dev, x_dtype, t, y_dev);
+}
+
+B2_EXPORT int b2_matmul_sharded_peer(b2_ctx* ctx, b2_weight w_shard, const void* x_dev, int x_dtype, size_t t, float** y_full_dev) {
+    LOCKED(ctx);
+    return ctx->be.matmul_sharded_peer(w_shard, x_dev, x_dtype, t, y_full_dev);
 }
 
 B2_EXPORT int b2_moe_ep(b2_ctx* ctx, b2_moe_handle m, size_t n_experts_global, const float* x_dev, size_t t, const int32_t* route_ids,

@@ -235,7 +235,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, int K, int n_out, int t,
                    int tile_n, int m_halves, void* __restrict__ y, int y_dtype_arg, GemmStatus* __restrict__ status, int dbg_arg,
-                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits, const float* __restrict__ row_unscale, int a_lo_row_arg, int w_terms) {
+                   const int* __restrict__ tile_expert, F8Scales f8, int k_splits, const float* __restrict__ row_unscale, int a_lo_row_arg, int w_terms,
+                   const CUtensorMap* __restrict__ y_more, int n_more) {
+    // y_more[0 .. n_more): tensor maps (in global memory) of the other ranks' copies of y, for a row-sharded product whose
+    // result every rank wants whole: each staging tile is stored once per destination.
     const int a_lo_row0 = TT ? a_lo_row_arg : 0;
     // The timing switches (see debug_switches below) exist only in builds made with -DB2_DEBUG: a production library
     // must not change its results because of an environment variable.
@@ -683,6 +686,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                                 asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&tmap_y),
                                              "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
                                              : "memory");
+                            for (int d = 0; d < n_more; d++)  // the same tile into the peers' y, through their mapped memory
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(y_more + d),
+                                             "r"(smem_u32(buf)), "r"(n0 + c0), "r"(token0)
+                                             : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
@@ -847,6 +854,10 @@ struct GemmPlan {
     int tile_n, m_halves, n_tiles, m_tiles;
     int k_splits = 1;
     bool y_direct = false;  // f32 output whose rows the copy engine cannot take (stride not a multiple of 16 bytes)
+    CUtensorMap* y_more = nullptr;  // device array of n_more tensor maps: the peers' copies of y (GemmPeerY)
+    int n_more = 0;
+    size_t y_ld = 0;
+    float* more_ptr[7] = {};
     bool pair = false;     // the CTA-pair form: clusters of two CTAs along the token tiles, tile_n the pair's width
     bool pair_asked = false;  // B2_GEMM_PAIR when the plan was made (a cached plan is reused only under the same setting)
     int w_terms = 1;       // 2: two-term weights (Q4_K, tile_n <= 112)
@@ -876,16 +887,16 @@ static int split_k_asked() {
 // time hardly depends on the width (1108 cycles per stage at 208 rows, 1152 at 104), plus an epilogue that grows with
 // the width; in units of rows the measurements fit (tile_n + 13 per k stage), with widths above 208 costing about five
 // times as much per extra row (58-60 us at 240 against 54 at 208 for 64 stages). So the count of waves decides first.
-static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K, int widest = MAX_TILE_N) {
+static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K, int widest = MAX_TILE_N, int step = 16) {
     // B2_GEMM_TILE_N forces a width (tests and tuning sweeps).
     if (const char* env = getenv("B2_GEMM_TILE_N")) {
         int v = atoi(env);
-        if (v >= 16 && v <= widest && v % 16 == 0) return v;
+        if (v >= 16 && v <= widest && v % step == 0) return v;
     }
     const double per_cta = 24.0 + 13.0 * (double)(K / 64);
     int best = widest;
     double best_cost = 1e30;
-    for (int tn = widest; tn >= 64; tn -= 16) {
+    for (int tn = widest; tn >= 64; tn -= step) {
         size_t tiles = (n_out + tn - 1) / tn * (size_t)m_tiles;
         size_t waves = (tiles + sm_count - 1) / sm_count;
         double cost = (double)waves * (tn + per_cta + (tn > 208 ? 4.0 * (tn - 208) : 0.0));
@@ -898,8 +909,15 @@ static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K, int wi
 }
 
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen, size_t experts, const int* tile_expert, int force_m_halves, size_t a_lo_row0, int w_terms) {
+                                size_t errlen, size_t experts, const int* tile_expert, int force_m_halves, size_t a_lo_row0, int w_terms,
+                                const GemmPeerY* peer_y) {
     EncodeTiledFn enc = encode_tiled_fn();
+    const bool gathered = peer_y && peer_y->ld != 0;
+    if (gathered && (y_dtype != B2_F32 || experts != 1 || tile_expert || peer_y->n_more < 0 || peer_y->n_more > 7 || peer_y->ld < w.n_out ||
+                     peer_y->ld % 4 || w.n_out % 4 || ((uintptr_t)y & 15))) {
+        snprintf(err, errlen, "a gathered product needs a dense f32 result with 16-byte aligned column blocks");
+        return cudaErrorInvalidValue;
+    }
     if (!enc) {
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
         return cudaErrorNotSupported;
@@ -928,7 +946,8 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;  // the other formats' weights round to f16 far below the bound
     p->w_terms = w_terms;
-    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? 112 : MAX_TILE_N);
+    // (a gathered product stores every tile through the copy engine, whose staging tiles are 32 columns wide)
+    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? (gathered ? 96 : 112) : (gathered ? 224 : MAX_TILE_N), gathered ? 32 : 16);
     // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
     // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
     // with its width, so a grid that fills half the SMs or less runs nearly twice as fast as twice as many CTAs of half
@@ -938,7 +957,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         p->split_asked = want;
         const int sb_k = w.fmt == B2_FMT_F8E4M3 ? 128 : 256;
         const size_t nsb_all = w.n_in / sb_k;
-        if (want == 2 && y_dtype == B2_F32 && !a_lo_row0 && w_terms == 1 && !tile_expert && nsb_all % 2 == 0 && nsb_all >= 8) {
+        if (want == 2 && y_dtype == B2_F32 && !a_lo_row0 && w_terms == 1 && !tile_expert && !gathered && nsb_all % 2 == 0 && nsb_all >= 8) {
             const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count, w.n_in / 2);
             const size_t tiles1 = (w.n_out + p->tile_n - 1) / p->tile_n * (size_t)p->m_tiles;
             const size_t tiles2 = (w.n_out + tn2 - 1) / tn2 * (size_t)p->m_tiles * 2;
@@ -952,7 +971,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     // The CTA-pair form: dense one-term 4-bit launches of more than one 256-token tile. The token tiles are rounded up to an
     // even count (a CTA whose tokens are all out of range multiplies zeros and stores nothing).
     p->pair_asked = pair_form_enabled();
-    p->pair = p->pair_asked && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && !tile_expert && experts == 1 && !a_lo_row0 && w_terms == 1 &&
+    p->pair = p->pair_asked && !gathered && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && !tile_expert && experts == 1 && !a_lo_row0 && w_terms == 1 &&
               p->k_splits == 1 && p->m_halves == 2 && p->m_tiles >= 2;
     if (p->pair) {
         p->m_tiles = (p->m_tiles + 1) / 2 * 2;
@@ -989,11 +1008,13 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         }
     }
     p->tmap_y = p->tmap_x;  // placeholder when the epilogue stores directly (bf16 output)
-    p->y_direct = y_dtype == B2_F32 && (w.n_out % 4 != 0 || ((uintptr_t)y & 15) != 0);
+    p->y_direct = y_dtype == B2_F32 && !gathered && (w.n_out % 4 != 0 || ((uintptr_t)y & 15) != 0);
     if (y_dtype == B2_F32 && !p->y_direct) {
-        // the f32 output [t][n_out]; one box = a warp's 32 tokens x 32 columns staging tile
+        // the f32 output [t][n_out] (a gathered product: this shard's n_out columns of rows `ld` apart); one box = a warp's
+        // 32 tokens x 32 columns staging tile
+        const size_t ld = gathered ? peer_y->ld : w.n_out;
         cuuint64_t dims[2] = {(cuuint64_t)w.n_out, (cuuint64_t)t};
-        cuuint64_t strides[1] = {(cuuint64_t)w.n_out * 4};
+        cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
         cuuint32_t box[2] = {32, 32};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = enc(&p->tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1003,16 +1024,46 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
             delete p;
             return cudaErrorInvalidValue;
         }
+        if (gathered && peer_y->n_more > 0) {
+            CUtensorMap maps[7];
+            for (int d = 0; d < peer_y->n_more; d++) {
+                if (((uintptr_t)peer_y->more[d] & 15) != 0) r = CUDA_ERROR_INVALID_VALUE;
+                if (r == CUDA_SUCCESS)
+                    r = enc(&maps[d], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, peer_y->more[d], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                p->more_ptr[d] = peer_y->more[d];
+            }
+            cudaError_t ce = r == CUDA_SUCCESS ? cudaMalloc((void**)&p->y_more, sizeof(CUtensorMap) * peer_y->n_more) : cudaErrorInvalidValue;
+            if (ce == cudaSuccess) ce = cudaMemcpy(p->y_more, maps, sizeof(CUtensorMap) * peer_y->n_more, cudaMemcpyHostToDevice);
+            if (ce != cudaSuccess) {
+                snprintf(err, errlen, "tensor maps of the peers' y could not be made (CUresult %d, %s)", (int)r, cudaGetErrorString(ce));
+                if (p->y_more) cudaFree(p->y_more);
+                delete p;
+                return cudaErrorInvalidValue;
+            }
+            p->n_more = peer_y->n_more;
+        }
+        p->y_ld = gathered ? ld : 0;
     }
     *out = p;
     return cudaSuccess;
 }
 
-void gemm_tc_plan_destroy(GemmPlan* p) { delete p; }
+void gemm_tc_plan_destroy(GemmPlan* p) {
+    if (p && p->y_more) cudaFree(p->y_more);
+    delete p;
+}
 
 bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype, size_t a_lo_row0,
-                          int w_terms, int m_halves) {
+                          int w_terms, int m_halves, const GemmPeerY* peer_y) {
     if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;
+    if (p) {  // the same destinations
+        const size_t ld = peer_y ? peer_y->ld : 0;
+        const int nm = peer_y && peer_y->ld ? peer_y->n_more : 0;
+        if (p->y_ld != ld || p->n_more != nm) return false;
+        for (int d = 0; d < nm; d++)
+            if (p->more_ptr[d] != peer_y->more[d]) return false;
+    }
     return p && p->experts == 1 && p->a_lo_row0 == a_lo_row0 && p->w_terms == w_terms && (m_halves == 0 || p->m_halves == m_halves) && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
            p->split_asked == split_k_asked() && p->pair_asked == pair_form_enabled();
 }
@@ -1022,7 +1073,7 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
     const bool split = p->k_splits > 1;
     const bool tt = p->a_lo_row0 > 0 || p->w_terms == 2;
     using Kern = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, void*, int, GemmStatus*, int, const int*, F8Scales, int, const float*,
-                          int, int);
+                          int, int, const CUtensorMap*, int);
     Kern kern;
     if (tt)  // two-term operands never come with a K split
         kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4, false, true>
@@ -1048,7 +1099,7 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
-                                  y_dtype | (p->y_direct ? 0x100 : 0), status_dev, debug_switches(), (const int*)nullptr, f8, 1, row_unscale, 0, 1);
+                                  y_dtype | (p->y_direct ? 0x100 : 0), status_dev, debug_switches(), (const int*)nullptr, f8, 1, row_unscale, 0, 1, (const CUtensorMap*)nullptr, 0);
         return le;
     }
     if (cudaError_t e = ensure_dynamic_smem((const void*)kern, GEMM_SMEM); e != cudaSuccess) return e;
@@ -1058,7 +1109,8 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         if (e != cudaSuccess) return e;
     }
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype | (p->y_direct ? 0x100 : 0),
-                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms);
+                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms,
+                                                (const CUtensorMap*)p->y_more, p->n_more);
     return cudaGetLastError();
 }
 

@@ -169,11 +169,20 @@ struct GemmPlan;
 // `experts` > 1 makes a grouped plan: w.p0 holds `experts` stacked matrices of w.n_out rows, x16 / y hold the
 // token rows of all experts in segments that are multiples of 128 * m_halves rows, and tile_expert[i]
 // (device) names the expert of token tile i.
+// Where a row-sharded product's f32 result goes when every rank is to end up with the whole y [t][ld]: this rank's columns
+// of its own y (`y` of the call, already offset to them) and of n_more peers' copies (device pointers mapped from the
+// peers, offset the same way). The GEMM's epilogue then issues each staging tile's bulk store once per destination, so the
+// all-gather happens tile by tile from the kernel that computes the tiles.
+struct GemmPeerY {
+    size_t ld = 0;        // row stride of the destinations in elements (0: not a gathered product, the stride is n_out)
+    int n_more = 0;       // peers' destinations
+    float* more[7] = {};
+};
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
-                                size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0, size_t a_lo_row0 = 0, int w_terms = 1);
+                                size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0, size_t a_lo_row0 = 0, int w_terms = 1, const GemmPeerY* peer_y = nullptr);
 void gemm_tc_plan_destroy(GemmPlan* p);
 bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16, size_t t, const void* y, int y_dtype, size_t a_lo_row0 = 0,
-                          int w_terms = 1, int m_halves = 0);
+                          int w_terms = 1, int m_halves = 0, const GemmPeerY* peer_y = nullptr);
 // row_unscale (device, [t], may be null): factor the epilogue multiplies token row i's results by (launch_to_f16).
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int sm_count,
                            cudaStream_t st, const float* row_unscale = nullptr);

@@ -1,9 +1,10 @@
 """One rank of the C-ABI tensor- / expert-parallel test (launched by test_comm_gpu.py through torch.distributed.run, which here
 only starts the processes and carries the NCCL id between them on the host: gloo). Everything on the GPUs goes through
-b2_comm_init, b2_matmul_sharded and b2_moe_ep, i.e. the library's own NCCL use, as a non-Python host would drive it.
+b2_comm_init, b2_matmul_sharded, b2_matmul_sharded_peer and b2_moe_ep, i.e. the library's own NCCL use, as a non-Python host would drive it.
 
 Checks, against the single-GPU calls on rank 0's device over the unsharded matrix / all experts and tokens:
-  * the row-sharded dense matmul gives the full y on every rank, bit for bit;
+  * the row-sharded dense matmul gives the full y on every rank, bit for bit, through the library collective and through the
+    GEMM epilogue's own peer stores;
   * the expert-parallel layer gives every rank's token rows bit for bit (ragged token shards, an expert nobody routes to).
 """
 import os
@@ -48,6 +49,21 @@ def main():
     if not torch.equal(y.view(torch.int32), want.view(torch.int32)):
         print(f"rank {rank}: sharded matmul differs from the unsharded product", flush=True)
         ok = False
+
+    # ---- the same with the gather done by the GEMM's epilogue (peer stores): several calls in a row (the two result areas
+    # alternate), a larger product afterwards (the buffers are made again, collectively), ragged token counts ----
+    for (tt, seed) in ((100, 801), (300, 802), (300, 803), (300, 804), (777, 805)):
+        xx = torch.from_numpy(synth.activations(tt, n_in, seed)).cuda()
+        ww = torch.empty((tt, n_out), device="cuda")
+        assert be.matmul_dev(dfull, xx, ww)
+        got = be.matmul_sharded_peer(shard, xx)
+        assert got is not None, be.last_declined
+        torch.cuda.synchronize()
+        be.check_status()
+        if got.shape != ww.shape or not torch.equal(got.view(torch.int32), ww.view(torch.int32)):
+            print(f"rank {rank}: peer-store sharded matmul differs from the unsharded product at t = {tt}", flush=True)
+            ok = False
+    assert be.matmul_sharded_peer(shard, x[:4]) is None    # the matrix-vector routes do not store to peers: declined
 
     # ---- expert parallel ----
     E, K, H, I, T = 4 * world, 3, 512, 256, 157
