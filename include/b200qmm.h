@@ -54,6 +54,8 @@ extern "C" {
 #define B2_FMT_IQ4_NL 20
 #define B2_FMT_IQ4_XS 23
 #define B2_FMT_MXFP4 39
+#define B2_FMT_NVFP4 40 /* blocks of 64 E2M1 values, an unsigned E4M3 scale per 16 (src/ggml.rs:79-83, 936-947); block_scales may
+                          carry the tensor's global scale (one value for the whole matrix: bs_rows >= n_out, bs_cols >= n_in) */
 
 /* Element types of device-resident activations / results. */
 #define B2_F32 0

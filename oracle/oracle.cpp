@@ -124,12 +124,12 @@ void parallel_for(size_t n, int threads, const std::function<void(size_t)>& f) {
 // ---------------------------------------------------------------------------------------------
 enum Kind : int {
     K_F32 = 0, K_F16 = 1, K_Q4_0 = 2, K_Q4_1 = 3, K_Q5_0 = 6, K_Q5_1 = 7, K_Q8_0 = 8, K_Q2_K = 10, K_Q3_K = 11, K_Q4_K = 12, K_Q5_K = 13,
-    K_Q6_K = 14, K_IQ4_NL = 20, K_IQ4_XS = 23, K_BF16 = 30, K_MXFP4 = 39, K_F8E4M3 = 0x1000
+    K_Q6_K = 14, K_IQ4_NL = 20, K_IQ4_XS = 23, K_BF16 = 30, K_MXFP4 = 39, K_NVFP4 = 40, K_F8E4M3 = 0x1000
 };
 // The block kinds whose matrix products this file runs through the f32 route only (decoded bit-exactly here).
 inline bool other_block_kind(int kind) {
     switch (kind) {
-        case K_Q4_0: case K_Q4_1: case K_Q5_0: case K_Q5_1: case K_Q2_K: case K_Q3_K: case K_Q5_K: case K_IQ4_NL: case K_IQ4_XS: case K_MXFP4: return true;
+        case K_Q4_0: case K_Q4_1: case K_Q5_0: case K_Q5_1: case K_Q2_K: case K_Q3_K: case K_Q5_K: case K_IQ4_NL: case K_IQ4_XS: case K_MXFP4: case K_NVFP4: return true;
         default: return false;
     }
 }
@@ -138,6 +138,7 @@ inline size_t block_size(int kind) {  // src/ggml.rs:173-185
     switch (kind) {
         case K_Q4_0: case K_Q4_1: case K_Q5_0: case K_Q5_1: case K_IQ4_NL: case K_MXFP4:
         case K_Q8_0: return 32;
+        case K_NVFP4: return 64;
         case K_Q2_K: case K_Q3_K: case K_Q5_K: case K_IQ4_XS:
         case K_Q4_K:
         case K_Q6_K: return 256;
@@ -159,6 +160,7 @@ inline size_t type_size(int kind) {  // src/ggml.rs:187-215
         case K_Q5_K: return 176;
         case K_IQ4_XS: return 136;
         case K_MXFP4: return 17;
+        case K_NVFP4: return 36;
         case K_Q4_K: return 144;
         case K_Q6_K: return 210;
         case K_F8E4M3: return 1;
@@ -184,6 +186,15 @@ inline uint32_t u32at(const uint8_t* b, size_t i) { return (uint32_t)b[i] | ((ui
 
 // src/ggml.rs:466-474 (e8m0_half): 2^(e - 128), the subnormal cases from their bit patterns.
 inline float e8m0_half(uint8_t e) { return bits_f32(e < 2 ? (0x00200000u << e) : (((uint32_t)e - 1) << 23)); }
+
+// src/ggml.rs:477-491 (ue4m3_half): half the value of an unsigned E4M3 scale byte; 0 and 0x7f give 0.
+inline float ue4m3_half(uint8_t x) {
+    if (x == 0 || x == 0x7F) return 0.0f;
+    const int e = (x >> 3) & 0xF;
+    const float m = (float)(x & 7);
+    const float raw = e == 0 ? m * std::ldexp(1.0f, -9) : (1.0f + m / 8.0f) * std::ldexp(1.0f, e - 7);
+    return raw * 0.5f;
+}
 
 // src/ggml.rs:511-530 (q3k_scales): sixteen 6-bit scales from 12 bytes, still offset by 32.
 inline void q3k_scales(const uint8_t* s, int8_t* out) {
@@ -320,6 +331,15 @@ void dequantize_row(int kind, const uint8_t* src, float* out, size_t n) {
                 y[j] = d * (float)KV_MXFP4[b[1 + j] & 0xF];
                 y[j + 16] = d * (float)KV_MXFP4[b[1 + j] >> 4];
             }
+        } else if (kind == K_NVFP4) {  // src/ggml.rs:936-947
+            for (int sb = 0; sb < 4; sb++) {
+                float d = ue4m3_half(b[sb]);
+                const uint8_t* q = b + 4 + 8 * sb;
+                for (int j = 0; j < 8; j++) {
+                    y[16 * sb + j] = d * (float)KV_MXFP4[q[j] & 0xF];
+                    y[16 * sb + j + 8] = d * (float)KV_MXFP4[q[j] >> 4];
+                }
+            }
         } else if (kind == K_IQ4_XS) {  // src/ggml.rs:948-958
             float d = f16at(b, 0);
             for (int ib = 0; ib < 8; ib++) {
@@ -449,6 +469,11 @@ void dequantize_rows_gguf(const Matrix& m, size_t r0, size_t r1, float* out) {
             }
         } else {
             dequantize_row(m.kind, w, o, n);
+            if (!m.bscales.empty()) {  // scales on top of what the kind decodes (NVFP4's global scale), src/ggml.rs:420-432
+                size_t ncb = (n + m.bs_cols - 1) / m.bs_cols;
+                const float* srow = m.bscales.data() + (r / m.bs_rows) * ncb;
+                for (size_t c = 0; c < n; c++) o[c] *= srow[c / m.bs_cols];
+            }
         }
     }
 }

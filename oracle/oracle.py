@@ -22,9 +22,10 @@ _LIB_PATH = _HERE / "liboracle.so"
 # GGUF type ids (src/ggml.rs:42-93)
 F32, F16, Q8_0, Q4_K, Q6_K, BF16, F8E4M3 = 0, 1, 8, 12, 14, 30, 0x1000
 Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS, MXFP4 = 2, 3, 6, 7, 10, 11, 13, 20, 23, 39
+NVFP4 = 40  # no known-answer hash in the reference (src/ggml.rs:1547-1577 has none): pinned to the closed form in the tests
 OTHER_KINDS = (Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS, MXFP4)
 KIND_NAMES = {Q4_0: "q4_0", Q4_1: "q4_1", Q5_0: "q5_0", Q5_1: "q5_1", Q2_K: "q2_k", Q3_K: "q3_k", Q5_K: "q5_k", IQ4_NL: "iq4_nl",
-              IQ4_XS: "iq4_xs", MXFP4: "mxfp4", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
+              IQ4_XS: "iq4_xs", MXFP4: "mxfp4", NVFP4: "nvfp4", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
 
 # FNV-1a-64 of the f32 bits of dequantize_row(kind, fixture(kind)), from src/ggml.rs:1547-1577.
 REF_HASHES = {

@@ -328,6 +328,22 @@ class Backend {
                 drop(wt.owned);
                 return cuda_fail(e, "upload copy");
             }
+            if (bscales) {  // NVFP4's global scale: one value for the whole matrix
+                if (fmt != B2_FMT_NVFP4 || bs_rows < n_out || bs_cols < n_in) {
+                    drop(wt.owned);
+                    return fail(B2_DECLINED, "[b200qmm: upload_gguf: block scales on this format must be one scale for the whole NVFP4 matrix]");
+                }
+                void* gs;
+                if ((rc = alloc_copy(bscales, 4, &gs, wt.owned))) {
+                    drop(wt.owned);
+                    return rc;
+                }
+                if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) {
+                    drop(wt.owned);
+                    return cuda_fail(e, "upload copy");
+                }
+                wt.dev.p1 = (const uint8_t*)gs;
+            }
             wt.dev.p0 = (const uint8_t*)p;
         } else {
             return fail(B2_DECLINED, "[b200qmm: format %d has no device kernels]", fmt);

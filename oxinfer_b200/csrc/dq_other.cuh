@@ -13,12 +13,12 @@ namespace b2 {
 __host__ __device__ inline bool fmt_is_other(int fmt) {
     switch (fmt) {
         case B2_FMT_Q4_0: case B2_FMT_Q4_1: case B2_FMT_Q5_0: case B2_FMT_Q5_1: case B2_FMT_Q2_K: case B2_FMT_Q3_K: case B2_FMT_Q5_K:
-        case B2_FMT_IQ4_NL: case B2_FMT_IQ4_XS: case B2_FMT_MXFP4: return true;
+        case B2_FMT_IQ4_NL: case B2_FMT_IQ4_XS: case B2_FMT_MXFP4: case B2_FMT_NVFP4: return true;
         default: return false;
     }
 }
 __host__ __device__ inline int other_block_size(int fmt) {  // src/ggml.rs:173-185
-    return (fmt == B2_FMT_Q2_K || fmt == B2_FMT_Q3_K || fmt == B2_FMT_Q5_K || fmt == B2_FMT_IQ4_XS) ? 256 : 32;
+    return (fmt == B2_FMT_Q2_K || fmt == B2_FMT_Q3_K || fmt == B2_FMT_Q5_K || fmt == B2_FMT_IQ4_XS) ? 256 : fmt == B2_FMT_NVFP4 ? 64 : 32;
 }
 __host__ __device__ inline int other_type_size(int fmt) {  // src/ggml.rs:187-215
     switch (fmt) {
@@ -32,6 +32,7 @@ __host__ __device__ inline int other_type_size(int fmt) {  // src/ggml.rs:187-21
         case B2_FMT_IQ4_NL: return 18;
         case B2_FMT_IQ4_XS: return 136;
         case B2_FMT_MXFP4: return 17;
+        case B2_FMT_NVFP4: return 36;
         default: return 0;
     }
 }
@@ -44,7 +45,7 @@ static __constant__ int8_t K_MXFP4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3
 // constant-memory table would serialize; 16 words sit in 16 banks): lut_fill by the first 16 threads, then a barrier.
 template <int FMT>
 __device__ __forceinline__ void lut_fill(float* lut, int tid) {
-    if (tid < 16) lut[tid] = (FMT == B2_FMT_MXFP4) ? (float)K_MXFP4[tid] : (float)K_IQ4NL[tid];
+    if (tid < 16) lut[tid] = (FMT == B2_FMT_MXFP4 || FMT == B2_FMT_NVFP4) ? (float)K_MXFP4[tid] : (float)K_IQ4NL[tid];
 }
 // A small non-negative integer as a float through the mantissa of 2^23 (exact; keeps the conversion unit out of the loop).
 __device__ __forceinline__ float uint_to_f32(uint32_t n) { return __uint_as_float(0x4B000000u | n) - 8388608.0f; }
@@ -52,6 +53,15 @@ __device__ __forceinline__ float f16_at(const uint8_t* b, int i) { return f16_bi
 __device__ __forceinline__ uint32_t u32_at(const uint8_t* b, int i) { return b[i] | (b[i + 1] << 8) | (b[i + 2] << 16) | ((uint32_t)b[i + 3] << 24); }
 // Half the value of an E8M0 scale byte, 2^(e - 128) (src/ggml.rs:466-474).
 __device__ __forceinline__ float e8m0_half(uint32_t e) { return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1) << 23)); }
+
+// Half the value of an unsigned E4M3 scale byte (src/ggml.rs:477-491): 0 and 0x7f give 0; every product below is exact.
+__device__ __forceinline__ float ue4m3_half(uint32_t x) {
+    if (x == 0 || x == 0x7F) return 0.0f;
+    const uint32_t e = (x >> 3) & 0xF;
+    const float m = (float)(x & 7);
+    const float raw = e == 0 ? m * 0.001953125f : (1.0f + m * 0.125f) * __uint_as_float((e + 120u) << 23);  // 2^-9; 2^(e - 7)
+    return raw * 0.5f;
+}
 
 // v[0..32) = weights 32 sub .. 32 sub + 31 of the block at `b`.
 template <int FMT>
@@ -100,6 +110,20 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
         for (int j = 0; j < 16; j++) {
             v[j] = __fmul_rn(d, lut[b[1 + j] & 0xF]);
             v[j + 16] = __fmul_rn(d, lut[b[1 + j] >> 4]);
+        }
+    } else if constexpr (FMT == B2_FMT_NVFP4) {
+        // four scale bytes, then per 16-value sub-block 8 bytes holding elements j (low nibble) and j + 8 (high); chunk `sub`
+        // covers sub-blocks 2 sub and 2 sub + 1 (src/ggml.rs:936-947)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int s = 2 * sub + h;
+            const float d = ue4m3_half(b[s]);
+            const uint8_t* q = b + 4 + 8 * s;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                v[16 * h + j] = __fmul_rn(d, lut[q[j] & 0xF]);
+                v[16 * h + j + 8] = __fmul_rn(d, lut[q[j] >> 4]);
+            }
         }
     } else if constexpr (FMT == B2_FMT_Q2_K) {
         // scales b[0..16), quants b[16..80), d @80, min @82; chunk sub = 4 n + j covers h = 0, 1 (src/ggml.rs:713-730)
@@ -181,6 +205,7 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* b, int sub, float
         B2_OTHER_CASE(B2_FMT_IQ4_NL, expr)    \
         B2_OTHER_CASE(B2_FMT_IQ4_XS, expr)    \
         B2_OTHER_CASE(B2_FMT_MXFP4, expr)     \
+        B2_OTHER_CASE(B2_FMT_NVFP4, expr)     \
         default: return cudaErrorInvalidValue; \
     }
 

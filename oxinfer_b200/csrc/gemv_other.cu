@@ -31,10 +31,17 @@ __global__ void __launch_bounds__(128) dq_other_kernel(WeightDev w, size_t r0, s
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nrows * per_row) return;
     const size_t r = r0 + i / per_row, c = i % per_row;
-    constexpr int BS = (FMT == B2_FMT_Q2_K || FMT == B2_FMT_Q3_K || FMT == B2_FMT_Q5_K || FMT == B2_FMT_IQ4_XS) ? 256 : 32;
+    constexpr int BS = (FMT == B2_FMT_Q2_K || FMT == B2_FMT_Q3_K || FMT == B2_FMT_Q5_K || FMT == B2_FMT_IQ4_XS) ? 256 : FMT == B2_FMT_NVFP4 ? 64 : 32;
     const uint8_t* blk = w.p0 + r * other_row_bytes(FMT, K) + (c * 32 / BS) * other_type_size(FMT);
     float v[32];
     dequant32_other<FMT>(blk, (int)(c % (BS / 32)), v, lut);
+    if constexpr (FMT == B2_FMT_NVFP4) {  // the tensor's global scale on top of what the blocks decode (src/ggml.rs:420-432)
+        if (w.p1) {
+            const float gs = __ldg((const float*)w.p1);
+#pragma unroll
+            for (int k = 0; k < 32; k++) v[k] = __fmul_rn(v[k], gs);
+        }
+    }
     float4* o = (float4*)(out + (i / per_row) * K + c * 32);
 #pragma unroll
     for (int k = 0; k < 8; k++) o[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
@@ -45,8 +52,8 @@ constexpr int STAGE = 800;  // bytes of a warp's staging run: the largest run (3
 
 template <int FMT>
 struct OtherShape {
-    static constexpr int BS = (FMT == B2_FMT_Q2_K || FMT == B2_FMT_Q3_K || FMT == B2_FMT_Q5_K || FMT == B2_FMT_IQ4_XS) ? 256 : 32;
-    static constexpr int TS = FMT == B2_FMT_Q4_0 ? 18 : FMT == B2_FMT_Q4_1 ? 20 : FMT == B2_FMT_Q5_0 ? 22 : FMT == B2_FMT_Q5_1 ? 24 : FMT == B2_FMT_Q2_K ? 84
+    static constexpr int BS = (FMT == B2_FMT_Q2_K || FMT == B2_FMT_Q3_K || FMT == B2_FMT_Q5_K || FMT == B2_FMT_IQ4_XS) ? 256 : FMT == B2_FMT_NVFP4 ? 64 : 32;
+    static constexpr int TS = FMT == B2_FMT_NVFP4 ? 36 : FMT == B2_FMT_Q4_0 ? 18 : FMT == B2_FMT_Q4_1 ? 20 : FMT == B2_FMT_Q5_0 ? 22 : FMT == B2_FMT_Q5_1 ? 24 : FMT == B2_FMT_Q2_K ? 84
                               : FMT == B2_FMT_Q3_K ? 110 : FMT == B2_FMT_Q5_K ? 176 : FMT == B2_FMT_IQ4_NL ? 18 : FMT == B2_FMT_IQ4_XS ? 136 : 17;
     static constexpr int RUN = 1024 / BS * TS;  // bytes of 1024 weights
     static_assert(RUN + 15 <= STAGE, "staging run");
@@ -130,6 +137,14 @@ __global__ void __launch_bounds__(OW * 32, 3) gemv_other_kernel(WeightDev w, Wei
                     const uint8_t* blk = stage_all[warp][m] + ((uintptr_t)gm & 15) + (lane * 32 / S::BS) * S::TS;
                     float v[32];
                     dequant32_other<FMT>(blk, (int)(c % (S::BS / 32)), v, lut);
+                    if constexpr (FMT == B2_FMT_NVFP4) {  // the global scale multiplies the decoded values, as in the bit-exact rows
+                        const WeightDev& wm = m ? w2 : w;
+                        if (wm.p1) {
+                            const float gs = __ldg((const float*)wm.p1);
+#pragma unroll
+                            for (int k = 0; k < 32; k++) v[k] = __fmul_rn(v[k], gs);
+                        }
+                    }
 #pragma unroll
                     for (int tk = 0; tk < NT; tk++) {
                         const float4* xv = (const float4*)xsm + (size_t)tk * (K / 4) + c * 8;

@@ -43,11 +43,13 @@ def test_one_rank_communicator_is_the_single_gpu_call(backend):
         backend.comm_free()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_through_the_c_abi_match_single_gpu_bitwise():
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_ranks_through_the_c_abi_match_single_gpu_bitwise(ranks):
+    if torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
     env = {k: v for k, v in os.environ.items() if not k.startswith("B2_")}
     env["NCCL_NVLS_ENABLE"] = "0"
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29651",
-           str(ROOT / "tests" / "comm_worker.py")]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr", "127.0.0.1", "--master-port",
+           str(29651 + ranks), str(ROOT / "tests" / "comm_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert r.returncode == 0 and "COMM_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

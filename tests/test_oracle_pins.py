@@ -214,3 +214,29 @@ def test_avx2_decode_kernels_give_the_bits_of_the_scalar_restatements():
             for threads in (1, 4):
                 got = m.matmul_cpu(x, threads)
                 assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (fmt, t, threads)
+
+
+def test_nvfp4_decode_matches_its_closed_form():
+    """NVFP4 has no known-answer hash in the reference; the decode arm (src/ggml.rs:936-947, ue4m3_half :477-491) is a closed form:
+    value = ue4m3(scale byte) / 2 * (doubled E2M1 value), checked here for all 256 scale bytes x 16 codes, with the layout
+    of a block (four scale bytes, then eight bytes per 16 values: element j in the low nibble, j + 8 in the high one)."""
+    kv = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float64)
+    scale = np.zeros(256)
+    for x in range(256):
+        if x in (0, 0x7F):
+            continue
+        e, m = (x >> 3) & 0xF, x & 7
+        scale[x] = (m * 2.0**-9 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7)) * 0.5
+    blocks = np.zeros((64, 36), np.uint8)       # block i: scale bytes 4 i .. 4 i + 3, codes cycling so every pair occurs
+    for i in range(64):
+        blocks[i, :4] = np.arange(4 * i, 4 * i + 4)
+        blocks[i, 4:] = (np.arange(32) * 37 + 11 * i) % 256
+    got = O.dequantize_row(O.NVFP4, blocks.reshape(-1), 64 * 64).reshape(64, 4, 16)
+    for i in range(64):
+        for s in range(4):
+            q = blocks[i, 4 + 8 * s: 12 + 8 * s]
+            want = np.concatenate([kv[q & 0xF], kv[q >> 4]]) * scale[4 * i + s]
+            assert np.array_equal(got[i, s].astype(np.float64), want), (i, s)
+    # a global scale on top (BlockScales over the whole matrix, src/ggml.rs:420-432)
+    m = O.Matrix.gguf(O.NVFP4, blocks.reshape(-1), 4, 1024, np.array([[0.37]], np.float32), 4, 1024)
+    assert np.array_equal(m.dequantize_rows(), (got.reshape(4, 1024) * np.float32(0.37)).astype(np.float32))

@@ -102,3 +102,29 @@ def test_formats_without_a_device_path_are_declined(backend):
     ref, _ = blocks(O.Q4_0, 256, 256, 1)
     dev = backend.upload(ref, 256, 256)
     assert backend.upload_moe([dev], [dev], 256, 256) is None
+
+
+@pytest.mark.parametrize("gscale", [None, 0.0371])
+def test_nvfp4_rows_and_products(backend, gscale):
+    """NVFP4 (blocks of 64, an unsigned E4M3 scale per 16, optionally the tensor's global scale): rows bit-exact with the oracle
+    (which is pinned to the closed form on the CPU; the reference holds no hash for this type), products within the bound."""
+    n_out, n_in = 300, 2048
+    data, _ = O.random_blocks(O.NVFP4, n_out * n_in // 64, 4040)
+    bs = None if gscale is None else np.array([[gscale]], np.float32)
+    ref = ob.Gguf(O.NVFP4, data, bs, n_out, n_in)
+    m = O.Matrix.gguf(O.NVFP4, data, n_out, n_in, bs, n_out, n_in)
+    dev = backend.upload(ref, n_out, n_in)
+    assert dev is not None, backend.last_declined
+    want = m.dequantize_rows()
+    assert np.array_equal(backend.dequantize_rows(dev).view(np.uint32), want.view(np.uint32))
+    sh = backend.shard_rows(dev, 101, n_out)
+    assert np.array_equal(backend.dequantize_rows(sh), want[101:])
+    x = synth.activations(5, n_in, 41)
+    y = np.zeros((5, n_out), np.float32)
+    assert backend.matmul(x, [ob.Job(dev, y)])
+    assert row_err(y, x.astype(np.float64) @ want.astype(np.float64).T) < 2e-5
+    y1 = np.zeros((1, n_out), np.float32)
+    assert backend.matmul(x[4:5], [ob.Job(dev, y1)])
+    assert np.array_equal(y1[0].view(np.uint32), y[4].view(np.uint32))
+    # scale blocks that are not one value for the whole matrix are declined
+    assert backend.upload(ob.Gguf(O.NVFP4, data, np.ones((3, 16), np.float32), 128, 128), n_out, n_in) is None
