@@ -1,5 +1,5 @@
-// The decode attention of one (KV head, key split) unit by a group of 256 threads, shared by the stand-alone
-// attention kernel (decode_ops.cu) and the persistent token kernel (token_kernel.cu).
+// The decode attention of one (KV head, key split) unit by a group of 256 threads: the body of the attention kernel
+// (decode_ops.cu).
 #pragma once
 #include <cuda_fp16.h>
 
@@ -112,9 +112,8 @@ __host__ __device__ constexpr size_t attend_smem() {
            + 4 * (size_t)G * 4 + 16;
 }
 
-// A group of 256 threads (a CTA of the stand-alone kernel, a third of the token kernel's CTA; `bar_id` names its
-// barrier) as unit (kvh, split): it runs the G query heads of KV head kvh over its share of the key tiles with
-// an online softmax, writes the unnormalized partial (o, m, l) of each head, and the last CTA of a KV head
+// A group of 256 threads (a CTA of the attention kernel; `bar_id` names its barrier) as unit (kvh, split): it runs the G
+// query heads of KV head kvh over its share of the key tiles with an online softmax, writes the unnormalized partial (o, m, l) of each head, and the last CTA of a KV head
 // to finish (a counter, no waiting) combines the partials, writes `out` and, if asked, the planes of `out`.
 template <int HD, int G, typename T>
 __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const int bar_id, const int kvh, const int split,

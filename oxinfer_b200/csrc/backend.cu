@@ -1190,7 +1190,8 @@ class Backend {
         rc = matmul_dev(h, x, x_dtype, t, mine + (size_t)rank * nl, B2_F32, &py);
         if (rc) return rc;
         // the ranks meet: every rank's tiles have landed in every buffer (the kernel waited for its stores before it ended)
-        cudaError_t e = launch_exchange(ps, 0, 0, (uint32_t*)tp_sym.local, &gemm_status->code, stream, false, false);
+        // (the ranks' hosts are not in lockstep: a peer may be a few launches behind; four seconds of polling before giving up)
+        cudaError_t e = launch_exchange(ps, 0, 0, (uint32_t*)tp_sym.local, &gemm_status->code, stream, false, false, 8000000000ll);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "peer barrier");
         tp_sym.calls++;

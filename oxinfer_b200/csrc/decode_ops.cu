@@ -231,7 +231,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 constexpr long long EXCHANGE_WAIT_LIMIT = 1000000000LL;  // cycles (about half a second)
 
-__device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, int bank, uint32_t epoch, int* ok_s) {
+__device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, int bank, uint32_t epoch, int* ok_s,
+                                           long long limit = EXCHANGE_WAIT_LIMIT) {
     const uint32_t tid = threadIdx.x;
     if (tid == 0) *ok_s = 1;
     __syncthreads();
@@ -240,7 +241,7 @@ __device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, 
         const long long t0 = clock64();
         uint32_t spin = 0;
         while ((int32_t)(ld_acquire_sys(lflags + bank + tid) - epoch) < 0) {
-            if ((++spin & 15) == 0 && clock64() - t0 > EXCHANGE_WAIT_LIMIT) {
+            if ((++spin & 15) == 0 && clock64() - t0 > limit) {
                 *ok_s = 0;
                 break;
             }
@@ -250,7 +251,8 @@ __device__ __forceinline__ bool peers_meet(const PeerSet& ps, uint32_t* lflags, 
     return *ok_s != 0;
 }
 
-__global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, uint32_t n, uint32_t* lflags, uint32_t* status, int meet_first) {
+__global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, uint32_t n, uint32_t* lflags, uint32_t* status, int meet_first,
+                                                        long long limit) {
     __shared__ int ok_s;
     __shared__ uint32_t epoch_s;
     pdl_launch_dependents();
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, 
     const uint32_t epoch = epoch_s;
     // The first meeting is left out where the plan has shown that no kernel between the previous exchange and this one
     // reads the other ranks' parts of the vector (a peer can be at most one exchange ahead).
-    bool ok = meet_first ? peers_meet(ps, lflags, 8, epoch, &ok_s) : true;
+    bool ok = meet_first ? peers_meet(ps, lflags, 8, epoch, &ok_s, limit) : true;
     if (ok) {
         const uint32_t part = n / ps.world;  // a multiple of 4 (checked on the host)
         const float4* src = (const float4*)(ps.base[ps.rank] + off + (size_t)ps.rank * part);
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(1024) exchange_kernel(PeerSet ps, size_t off, 
             for (uint32_t i = threadIdx.x; i < part / 4; i += blockDim.x) dst[i] = __ldcg(src + i);
         }
         __threadfence_system();
-        ok = peers_meet(ps, lflags, 16, epoch, &ok_s);
+        ok = peers_meet(ps, lflags, 16, epoch, &ok_s, limit);
     }
     if (threadIdx.x == 0) {
         lflags[0] = epoch;
@@ -296,9 +298,10 @@ cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, 
 }
 
 cudaError_t launch_exchange(const PeerSet& ps, size_t off_floats, uint32_t n, uint32_t* lflags, uint32_t* status, cudaStream_t st, bool pdl,
-                            bool meet_first) {
+                            bool meet_first, long long wait_limit_cycles) {
     if (ps.world < 2 || ps.world > 8 || n % (4 * ps.world)) return cudaErrorInvalidValue;
-    return launch_k(exchange_kernel, dim3(1), dim3(1024), 0, st, pdl, ps, off_floats, n, lflags, status, meet_first ? 1 : 0);
+    const long long limit = wait_limit_cycles > 0 ? wait_limit_cycles : EXCHANGE_WAIT_LIMIT;
+    return launch_k(exchange_kernel, dim3(1), dim3(1024), 0, st, pdl, ps, off_floats, n, lflags, status, meet_first ? 1 : 0, limit);
 }
 
 cudaError_t launch_set_step(uint32_t* sp, uint32_t pos, uint32_t table_pos0, uint32_t count, int* token, int tok, cudaStream_t st) {

@@ -1,6 +1,6 @@
 // Bit-exact decode of eight consecutive weights of a row, per device format: the arithmetic of the reference's
 // dequantize functions with explicit round-to-nearest multiplies and adds (see dq.cu). Shared by the
-// dequantization kernels and the embedding lookup of the persistent token kernel.
+// dequantization kernels and the decode plan's embedding lookup.
 #pragma once
 #include "kernels.h"
 

@@ -1,6 +1,6 @@
-// Device code shared by the stand-alone GEMV kernels (gemv.cu) and the persistent token kernel
-// (token_kernel.cu): the shared-memory view of the activation planes, and per weight format the loads of one
-// step of a row pair and its integer dot products (see the design notes at the top of gemv.cu).
+// Device code shared by the matrix-vector kernels (gemv.cu: register-load, ring and generic forms): the shared-memory
+// view of the activation planes, and per weight format the loads of one step of a row pair and its integer dot
+// products (see the design notes at the top of gemv.cu).
 #pragma once
 #include <cuda_fp8.h>
 

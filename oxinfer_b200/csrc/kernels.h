@@ -251,8 +251,9 @@ struct PeerSet {
 };
 // All-gather of the n-value vector at `off_floats` inside the activation block (equal contiguous parts, rank order).
 // meet_first: also meet before writing (needed when a kernel since the previous exchange reads other ranks' parts).
+// wait_limit_cycles: how long a rank polls for its peers before it gives up and sets the status word (0: about half a second).
 cudaError_t launch_exchange(const PeerSet& ps, size_t off_floats, uint32_t n, uint32_t* lflags, uint32_t* status, cudaStream_t st,
-                            bool pdl = false, bool meet_first = true);
+                            bool pdl = false, bool meet_first = true, long long wait_limit_cycles = 0);
 cudaError_t launch_norm(const float* x, float* out, const float* w, const DecNorm& p, uint32_t rows, XPlanes xp, cudaStream_t st, bool pdl = false);
 // KV caches are [nkv][max_len][hd], f32 or (kv_f16) f16.
 cudaError_t launch_qk_rope(const float* qkv, float* qo, void* kc, void* vc, int kv_f16, const float* qn, const float* kn, const float* cs_table,

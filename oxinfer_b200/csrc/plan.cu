@@ -559,7 +559,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     size_t table = (size_t)std::max<uint32_t>(p->cs_stride_, 1) * g->max_len;
     PLAN_CUDA(cudaMalloc((void**)&p->rope_table_, table * sizeof(float)), "cudaMalloc(rope table)");
     PLAN_CUDA(cudaMemset(p->rope_table_, 0, table * sizeof(float)), "cudaMemset(rope table)");
-    const size_t n_partials = std::max(128, sm_count);  // one per CTA of the argmax kernel / of the token kernel
+    const size_t n_partials = std::max(128, sm_count);  // one per CTA of the argmax kernel
     PLAN_CUDA(cudaMalloc((void**)&p->argmax_val_, n_partials * sizeof(float)), "cudaMalloc(argmax)");
     PLAN_CUDA(cudaMalloc((void**)&p->argmax_idx_, n_partials * sizeof(int)), "cudaMalloc(argmax)");
     PLAN_CUDA(cudaMalloc((void**)&p->token_, sizeof(int)), "cudaMalloc(token)");
