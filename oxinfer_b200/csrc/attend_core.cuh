@@ -120,7 +120,8 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
                                             const uint32_t max_splits, const uint32_t pos, const float* q,
                                             const T* kc, const T* vc, float* out, float* part,
                                             uint32_t* counters, DecAttn p, XPlanes xp, uint32_t* status,
-                                            unsigned long long* prof = nullptr, const FusedRope* fr = nullptr, const uint32_t table_pos0 = 0) {
+                                            unsigned long long* prof = nullptr, const FusedRope* fr = nullptr, const uint32_t table_pos0 = 0,
+                                            const bool wait_inside = false) {
     const long long pt0 = clock64();
     auto stamp = [&](int i) {
         if (prof && tid == 0) prof[i] += (unsigned long long)(clock64() - pt0);
@@ -172,14 +173,9 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         }
         return v;
     };
-    T k_new = (T)0.0f, v_new = (T)0.0f;
-    if (makes_row && tid < HD) {
-        k_new = (T)rotate(fr->qkv + fr->r.k_off + (size_t)kvh * HD, tid);
-        v_new = (T)__ldcg(fr->qkv + fr->r.v_off + (size_t)kvh * HD + tid);
-        const size_t at = ((size_t)kvh * p.max_len + pos) * HD + tid;
-        const_cast<T*>(kc)[at] = k_new;
-        const_cast<T*>(vc)[at] = v_new;
-    }
+    // Without FusedRope the token's row was appended by the kernel ahead: the tile that holds it (the last one) is copied
+    // only after the wait.
+    const bool late_first = wait_inside && fr == nullptr && t0 == tiles - 1;
     auto issue = [&](uint32_t t) {  // one thread: both copies of key tile t
         const uint32_t j0 = lo + t * ATT_TILE;
         uint32_t nv = min((uint32_t)ATT_TILE, len - j0);
@@ -195,9 +191,23 @@ __device__ __forceinline__ void attend_unit(uint8_t* smem, const int tid, const 
         bar_init(&bars[0], 1);
         bar_init(&bars[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        issue(t0);  // the first tile is on its way while the queries are staged
+        if (!late_first) issue(t0);  // the first tile is on its way while the queries are staged
         flags[0] = 0;
         flags[1] = 0;
+    }
+    // wait_inside: the caller has not yet waited for the kernel ahead of it in the stream (programmatic dependent launch).
+    // The rows of the caches that this unit copies were written by earlier steps (a step is one graph launch, and the
+    // token's own row is left out of the copy), so the first tile's copy starts before the wait; the queries, and the
+    // token's key and value, come from the kernel ahead and are read after it.
+    if (wait_inside) pdl_wait();
+    if (tid == 0 && late_first) issue(t0);
+    T k_new = (T)0.0f, v_new = (T)0.0f;
+    if (makes_row && tid < HD) {
+        k_new = (T)rotate(fr->qkv + fr->r.k_off + (size_t)kvh * HD, tid);
+        v_new = (T)__ldcg(fr->qkv + fr->r.v_off + (size_t)kvh * HD + tid);
+        const size_t at = ((size_t)kvh * p.max_len + pos) * HD + tid;
+        const_cast<T*>(kc)[at] = k_new;
+        const_cast<T*>(vc)[at] = v_new;
     }
     if (fr) {
         for (int i = tid; i < G * HD; i += ATT_THREADS)

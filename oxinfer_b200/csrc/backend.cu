@@ -911,10 +911,13 @@ class Backend {
         b2.y_stride = m.h;
         b2.planes = (uint8_t*)moe_a.p;
         if (e == cudaSuccess)
-            e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, m.act == B2_ACT_GELU_TANH ? B2_MODE_GELU_PAIR : B2_MODE_SILU_PAIR, planes_read(), sm_count, stream);
-        if (e == cudaSuccess) e = launch_xplanes_rows((const float*)moe_g.p, R, m.inter, (uint8_t*)moe_a.p, sa, stream);
-        if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, planes_read(), sm_count, stream);
-        if (e == cudaSuccess) e = launch_moe_combine_small((const float*)moe_o.p, routes, t, k, m.h, y_dev_, stream);
+            e = launch_gemv_batched(gate, &up, b1, R, (float*)moe_g.p, m.act == B2_ACT_GELU_TANH ? B2_MODE_GELU_PAIR : B2_MODE_SILU_PAIR, planes_read(), sm_count, stream,
+                                    true);
+        // (the five kernels are a chain of dependent launches: each may start while the one ahead drains and waits for it
+        // before it reads what that one wrote)
+        if (e == cudaSuccess) e = launch_xplanes_rows((const float*)moe_g.p, R, m.inter, (uint8_t*)moe_a.p, sa, stream, true);
+        if (e == cudaSuccess) e = launch_gemv_batched(down, nullptr, b2, R, (float*)moe_o.p, B2_MODE_STORE, planes_read(), sm_count, stream, true);
+        if (e == cudaSuccess) e = launch_moe_combine_small((const float*)moe_o.p, routes, t, k, m.h, y_dev_, stream, true);
         launches += 5;
         if (e != cudaSuccess) return cuda_fail(e, "moe (batched matrix-vector path)");
         return B2_OK;

@@ -119,9 +119,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __rest
                                                              uint32_t* status, FusedRope fr) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
-    pdl_wait();
+    // the step words (position, RoPE table base) were written before this step's graph was launched
     attend_unit<HD, G, T>(smem, threadIdx.x, 0, blockIdx.x, blockIdx.y, gridDim.y, sp[0], q, kc, vc, out, part, counters, p, xp, status, nullptr,
-                          fr.qkv ? &fr : nullptr, sp[1]);
+                          fr.qkv ? &fr : nullptr, sp[1], true);
 }
 
 // ---- greedy token ----------------------------------------------------------------------------------

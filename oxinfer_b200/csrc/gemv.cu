@@ -468,6 +468,8 @@ cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t s
 }
 
 __global__ void __launch_bounds__(256) xplanes_rows_kernel(const float* __restrict__ x, int rows, int K, uint8_t* planes, size_t stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int per_row = K / 32;
     if (warp >= rows * per_row) return;
@@ -475,16 +477,15 @@ __global__ void __launch_bounds__(256) xplanes_rows_kernel(const float* __restri
     xplanes_block(x[(size_t)r * K + blk * 32 + lane], blk, lane, K, xplanes_at(planes + (size_t)r * stride, (size_t)K));
 }
 
-cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st) {
+cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st, bool pdl) {
     if (rows == 0 || K % 32) return cudaErrorInvalidValue;
     const unsigned warps = (unsigned)(rows * (K / 32));
-    xplanes_rows_kernel<<<(warps + 7) / 8, 256, 0, st>>>(x, (int)rows, (int)K, planes, stride);
-    return cudaGetLastError();
+    return launch_k(xplanes_rows_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, (int)rows, (int)K, planes, stride);
 }
 
 template <class F>
 static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int sm_count,
-                                      cudaStream_t st) {
+                                      cudaStream_t st, bool pdl) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     auto kern = pair ? gemv_kernel<F, true, false, 1> : gemv_kernel<F, false, false, 1>;
     const size_t smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
@@ -494,18 +495,17 @@ static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, c
     const size_t cap = std::max<size_t>(1, (size_t)sm_count * 3 / batch);  // about three CTAs per SM over the whole batch
     if (gx > cap) gx = cap;
     XPlanes none{};
-    kern<<<dim3((unsigned)gx, (unsigned)batch), GEMV_THREADS, smem, st>>>(w, pair ? *up : w, nullptr, none, y, mode, nullptr,
-                                                                         NormScale{nullptr, 0, 0.0f, 0.0f}, b, GemvMulti{0, 0});
-    return cudaGetLastError();
+    return launch_k(kern, dim3((unsigned)gx, (unsigned)batch), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, (const float*)nullptr, none, y, mode,
+                    (const float*)nullptr, NormScale{nullptr, 0, 0.0f, 0.0f}, b, GemvMulti{0, 0});
 }
 
 cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int np, int sm_count,
-                                cudaStream_t st) {
+                                cudaStream_t st, bool pdl) {
     if (batch == 0 || batch > GEMV_BATCH_MAX || (size_t)b.n != batch || !gemv_supports(w)) return cudaErrorInvalidValue;
     if (w.fmt == B2_FMT_MLX4)
-        return np == 2 ? launch_batched_fmt<FmtMLX4_T<2>>(w, up, b, batch, y, mode, sm_count, st) : launch_batched_fmt<FmtMLX4_T<3>>(w, up, b, batch, y, mode, sm_count, st);
+        return np == 2 ? launch_batched_fmt<FmtMLX4_T<2>>(w, up, b, batch, y, mode, sm_count, st, pdl) : launch_batched_fmt<FmtMLX4_T<3>>(w, up, b, batch, y, mode, sm_count, st, pdl);
     if (w.fmt == B2_FMT_Q4_K)
-        return np == 2 ? launch_batched_fmt<FmtQ4K_T<2>>(w, up, b, batch, y, mode, sm_count, st) : launch_batched_fmt<FmtQ4K_T<3>>(w, up, b, batch, y, mode, sm_count, st);
+        return np == 2 ? launch_batched_fmt<FmtQ4K_T<2>>(w, up, b, batch, y, mode, sm_count, st, pdl) : launch_batched_fmt<FmtQ4K_T<3>>(w, up, b, batch, y, mode, sm_count, st, pdl);
     return cudaErrorInvalidValue;
 }
 

@@ -131,9 +131,9 @@ struct GemvBatch {
     uint8_t* planes;
 };
 cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int np, int sm_count,
-                                cudaStream_t st);
+                                cudaStream_t st, bool pdl = false);
 // Planes of `rows` vectors of K values (row r at x + r * K) into blocks `stride` bytes apart.
-cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st);
+cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st, bool pdl = false);
 // nt (1..4) tokens in one launch, the weights read once: token i's f32 vector at x + i * x_stride (FP8 weights) or planes
 // at xp + i * xp_stride bytes (the other formats), outputs at y + i * y_stride. Each token's result equals its
 // single-token result bit for bit. cudaErrorInvalidValue if the tokens' vectors do not fit in shared memory together.
@@ -218,7 +218,7 @@ cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t i
 struct SmallRoutes {
     float w[GEMV_BATCH_MAX];
 };
-cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
+cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st, bool pdl = false);
 cudaError_t launch_moe_combine(const float* o, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y, cudaStream_t st);
 
 // out[r][h] = x[idx[r]][h] (f32), h a multiple of 4; and an all-gather's rank-major blocks g [world][t][n_local] into the

@@ -10,6 +10,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "xplanes.cuh"
 
 namespace b2 {
 
@@ -312,6 +313,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
 
 // y[tok][c] += sum over the token's k routes, in order, of w * o[tok k + j][c]; the weights are kernel arguments.
 __global__ void moe_combine_small_kernel(const float* __restrict__ o, SmallRoutes r, int k, int h, float* __restrict__ y) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int tok = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= h) return;
@@ -356,11 +359,10 @@ cudaError_t launch_scatter_blocks(const float* gathered, size_t world, size_t t,
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st) {
+cudaError_t launch_moe_combine_small(const float* o, const SmallRoutes& r, size_t t, size_t k, size_t h, float* y, cudaStream_t st, bool pdl) {
     if (t * k > GEMV_BATCH_MAX) return cudaErrorInvalidValue;
     dim3 grid((unsigned)((h + 255) / 256), (unsigned)t);
-    moe_combine_small_kernel<<<grid, 256, 0, st>>>(o, r, (int)k, (int)h, y);
-    return cudaGetLastError();
+    return launch_k(moe_combine_small_kernel, grid, dim3(256), 0, st, pdl, o, r, (int)k, (int)h, y);
 }
 
 cudaError_t launch_route_topk(const float* logits, size_t t, size_t n, size_t k, int* ids, float* w, cudaStream_t st) {
