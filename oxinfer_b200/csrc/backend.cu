@@ -471,7 +471,8 @@ class Backend {
             if (prepared_k != w->dev.n_in) return fail(B2_ERR_ARG, "[b200qmm: matvec: no planes prepared for n_in = %zu (b2_prepare_x_dev)]", w->dev.n_in);
             xp = planes_at(xplanes.p, w->dev.n_in);
         }
-        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained || after_planes);
+        cudaError_t e = launch_gemv(w->dev, u ? &u->dev : nullptr, x_dev_, xp, y_dev_, mode, gate, sm_count, stream, chained || after_planes,
+                                    NormScale{nullptr, 0, 0.0f, 0.0f}, EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f}, after_planes && !chained);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "gemv");
         return B2_OK;
@@ -484,8 +485,9 @@ class Backend {
         if (w->dev.fmt != B2_FMT_F8E4M3 && !fmt_is_other(w->dev.fmt) && gemv_supports(w->dev)) {
             int rc = prepare_x(x_dev_, w->dev.n_in);
             if (rc) return rc;
-            // measured: worth 3 % for Q6_K; the 4-bit formats would switch to their ring form, which loses when launched alone
-            planes = w->dev.fmt == B2_FMT_Q6_K || w->dev.fmt == B2_FMT_Q8_0;
+            // the product is launched as the plane kernel's dependent, in its register-load form (the 4-bit ring form loses when
+            // launched alone): its first weights travel while the planes are made
+            planes = true;
         }
         return matvec_prepared(h, up, x_dev_, y_dev_, mode, gate, planes);
     }

@@ -558,7 +558,7 @@ static bool ring_fits(const WeightDev& w) {
 bool gemv_takes_epilogue(const WeightDev& w) { return ring_enabled() && ring_fits(w) && w.n_out % 32 == 0; }
 
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi) {
+                        int sm_count, cudaStream_t st, bool pdl, NormScale ns, EpiPlanes epi, bool plain_form) {
     if (epi.out.planes) {  // only the ring form carries the epilogue, chained or not
         if (!gemv_takes_epilogue(w)) return cudaErrorInvalidValue;
         if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
@@ -567,7 +567,7 @@ cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x,
     // In a chain of dependent launches (a decode step) the ring form wins: its copies start while the kernel ahead still
     // runs. Launched alone, the register-load form's shorter prologue makes it the faster one (measured at 14336 x 4096:
     // 11.2 us against 12.5), so plain launches keep it.
-    if (ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
+    if (!plain_form && ring_enabled() && (pdl || ring_level() >= 2) && ring_fits(w)) {
         if (w.fmt == B2_FMT_MLX4) return launch_ring<FmtMLX4_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
         return launch_ring<FmtQ4K_T>(w, up, xp, y, mode, gate, sm_count, st, pdl, ns, epi);
     }

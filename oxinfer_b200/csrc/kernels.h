@@ -114,10 +114,12 @@ struct EpiPlanes {
 // Whether launch_gemv takes an EpiPlanes for this matrix (the 4-bit formats whose planes and rings fit in shared memory).
 bool gemv_takes_epilogue(const WeightDev& w);
 // y[n_out] = mode(W x [, U x]). `xp` holds the planes of x (launch_xplanes); the
-// FP8 kernel reads `x` (f32) directly and ignores `xp`.
+// FP8 kernel reads `x` (f32) directly and ignores `xp`. plain_form: never the ring form (a lone product behind its own plane
+// kernel: launched as that kernel's dependent, the register-load form fetches its first weights while the planes are made).
 cudaError_t launch_gemv(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
                         int sm_count, cudaStream_t st, bool pdl = false, NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f},
-                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f});
+                        EpiPlanes epi = EpiPlanes{XPlanes{nullptr, nullptr, nullptr}, nullptr, nullptr, 1.0f},
+                        bool plain_form = false);
 // A batch of products in one launch (the routed experts of a few tokens): entry b multiplies matrix expert[b] of a stack
 // of equally shaped 4-bit matrices (w describes matrix 0; w_stride bytes apart) by the planes block xrow[b] (x_stride
 // bytes apart, laid out as xplanes_at) into y + b * y_stride. The tables travel as kernel arguments (up to 64 entries),
