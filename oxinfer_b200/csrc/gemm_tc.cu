@@ -240,6 +240,11 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // y_more[0 .. n_more): tensor maps (in global memory) of the other ranks' copies of y, for a row-sharded product whose
     // result every rank wants whole: each staging tile is stored once per destination.
     const int a_lo_row0 = TT ? a_lo_row_arg : 0;
+    // Programmatic dependent launch: the kernel behind this one in the stream may start launching now, and this kernel may
+    // itself have started before the kernel ahead of it finished. What that kernel wrote is the activations (and their row
+    // factors, which the epilogue reads after every activation tile has been consumed): only the activation producer waits
+    // for it; the barriers, the tensor memory, the packed weights and their expansion do not depend on it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // The timing switches (see debug_switches below) exist only in builds made with -DB2_DEBUG: a production library
     // must not change its results because of an environment variable.
 #ifdef B2_DEBUG
@@ -338,6 +343,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             // activations enter the product with 22 significant bits instead of 11.
             const uint32_t a_bytes = (uint32_t)(128 * (a_lo_row0 > 0 ? 2 : m_halves) * 128);
             int a_issued = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations are complete (see the top of the kernel)
             for (int ks = 0; ks < nks; ks++) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
@@ -780,6 +786,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) to_f16_rows_kernel(const T* __restrict__ x, int K, __half* __restrict__ out, float* __restrict__ unscale,
                                                           size_t lo_off) {
     __shared__ float red[8];
+    // (a dependent launch: the GEMM behind it may set itself up meanwhile; the GEMM ahead of it may still be reading `out`)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const T* xr = x + (size_t)blockIdx.x * K;
     __half* o = out + (size_t)blockIdx.x * K;
     float mx = 0.0f;
@@ -1091,13 +1100,15 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         cfg.blockDim = dim3(GEMM_THREADS);
         cfg.dynamicSmemBytes = PAIR_SMEM;
         cfg.stream = st;
-        cudaLaunchAttribute attr{};
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
+        cudaLaunchAttribute attr[2] = {};
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
         cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
                                   y_dtype | (p->y_direct ? 0x100 : 0), status_dev, debug_switches(), (const int*)nullptr, f8, 1, row_unscale, 0, 1, (const CUtensorMap*)nullptr, 0);
         return le;
@@ -1108,21 +1119,21 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         cudaError_t e = cudaMemsetAsync(y, 0, t * w.n_out * sizeof(float), st);
         if (e != cudaSuccess) return e;
     }
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y, y_dtype | (p->y_direct ? 0x100 : 0),
-                                                status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms,
-                                                (const CUtensorMap*)p->y_more, p->n_more);
-    return cudaGetLastError();
+    // (a dependent launch: see the top of the kernel)
+    return launch_k(kern, grid, dim3(GEMM_THREADS), GEMM_SMEM, st, true, p->tmap_x, p->tmap_w, p->tmap_y, (int)w.n_in, (int)w.n_out, (int)t, p->tile_n, p->m_halves, y,
+                    y_dtype | (p->y_direct ? 0x100 : 0), status_dev, debug_switches(), p->tile_expert, f8, p->k_splits, row_unscale, (int)p->a_lo_row0, p->w_terms,
+                    (const CUtensorMap*)p->y_more, p->n_more);
 }
 
 cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0) {
     if (t == 0 || K % 2) return cudaErrorInvalidValue;
     const size_t lo_off = lo_row0 * K;
     if (x_dtype == B2_F32)
-        to_f16_rows_kernel<float><<<(unsigned)t, 256, 0, st>>>((const float*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<float>, dim3((unsigned)t), dim3(256), 0, st, true, (const float*)x, (int)K, (__half*)x16, unscale, lo_off);
     else if (x_dtype == B2_BF16)
-        to_f16_rows_kernel<__nv_bfloat16><<<(unsigned)t, 256, 0, st>>>((const __nv_bfloat16*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<__nv_bfloat16>, dim3((unsigned)t), dim3(256), 0, st, true, (const __nv_bfloat16*)x, (int)K, (__half*)x16, unscale, lo_off);
     else if (x_dtype == B2_F16)
-        to_f16_rows_kernel<__half><<<(unsigned)t, 256, 0, st>>>((const __half*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<__half>, dim3((unsigned)t), dim3(256), 0, st, true, (const __half*)x, (int)K, (__half*)x16, unscale, lo_off);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();
