@@ -222,6 +222,9 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     F8Shared* sh = (F8Shared*)(b_tiles + (size_t)F8_STAGES * F8_B_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = K / F8_BK;
+    // Programmatic dependent launch: the quantized activations and their scales come from the kernel ahead in the stream; the
+    // producer and the promotion warps wait for it before they read them, everything else (barriers, tensor memory) does not.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // pair form: this CTA's rank in its pair; the pair takes the tiles (of 256 tokens) first_tile, first_tile + tile_step, ...
     const uint32_t rank = PAIR ? cluster_rank() : 0u;
     const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -266,6 +269,7 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int it = 0;
             bool ok = true;
             for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
@@ -339,6 +343,7 @@ gemm_f8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         float acc[128];
         bool ok = true;
         int it = 0;
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations' scales (sx) come from the kernel ahead
         const uint32_t pfree_even = PAIR ? cluster_addr(&sh->pfree[0], 0) : 0u;  // the even CTA's pfree[0]
         for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
             int mt, nt;
@@ -442,6 +447,9 @@ __device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
 
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_act_e4m3_kernel(const T* __restrict__ x, size_t t, int K, uint8_t* __restrict__ q, float* __restrict__ sx) {
+    // (a dependent launch: the GEMM behind it may set itself up; the GEMM ahead of it may still be reading q and sx)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t blk = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int nb = K / 128;
@@ -490,11 +498,11 @@ cudaError_t launch_quantize_act_e4m3(const void* x, int x_dtype, size_t t, size_
     const size_t warps = t * (K / 128);
     const unsigned grid = (unsigned)((warps + 7) / 8);
     if (x_dtype == B2_F32)
-        quantize_act_e4m3_kernel<float><<<grid, 256, 0, st>>>((const float*)x, t, (int)K, q, sx);
+        return launch_k(quantize_act_e4m3_kernel<float>, dim3(grid), dim3(256), 0, st, true, (const float*)x, t, (int)K, q, sx);
     else if (x_dtype == B2_BF16)
-        quantize_act_e4m3_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, t, (int)K, q, sx);
+        return launch_k(quantize_act_e4m3_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, true, (const __nv_bfloat16*)x, t, (int)K, q, sx);
     else if (x_dtype == B2_F16)
-        quantize_act_e4m3_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, t, (int)K, q, sx);
+        return launch_k(quantize_act_e4m3_kernel<__half>, dim3(grid), dim3(256), 0, st, true, (const __half*)x, t, (int)K, q, sx);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();
@@ -562,10 +570,8 @@ cudaError_t launch_gemm_f8(const WeightDev& w, const uint8_t* qx, const float* s
     if (cudaError_t e = ensure_dynamic_smem((const void*)gemm_f8_tc_kernel<false>, F8_SMEM, 0); e != cudaSuccess) return e;
     const int m_tiles = (int)((t + F8_TM - 1) / F8_TM);
     const int grid = m_tiles * n_tiles < sms ? m_tiles * n_tiles : sms;  // persistent: one CTA per SM
-    gemm_f8_tc_kernel<false><<<(unsigned)grid, F8_THREADS, F8_SMEM, st>>>(tx, tw, (int)w.n_in, (int)w.n_out, (int)t, m_tiles, n_tiles, sx,
-                                                                                   (const float*)w.p1, (int)w.bs_ncb, (int)w.bs_row0, y, y_dtype,
-                                                                                   status_dev);
-    return cudaGetLastError();
+    return launch_k(gemm_f8_tc_kernel<false>, dim3((unsigned)grid), dim3(F8_THREADS), F8_SMEM, st, true, tx, tw, (int)w.n_in, (int)w.n_out, (int)t, m_tiles,
+                    n_tiles, sx, (const float*)w.p1, (int)w.bs_ncb, (int)w.bs_row0, y, y_dtype, status_dev);
 }
 
 }  // namespace b2

@@ -95,6 +95,8 @@ constexpr int GATHER_KEEP = 8;
 __global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict__ x, const int* __restrict__ src, int h, __half* __restrict__ xg,
                                                          float* __restrict__ unscale, size_t lo_off) {
     __shared__ float red[8];
+    pdl_launch_dependents();  // a dependent launch: the kernel behind may set itself up; nothing is read or written before the wait
+    pdl_wait();
     const int row = blockIdx.x;
     const int s = src[row];
     __half* o = xg + (size_t)row * h;
@@ -140,6 +142,8 @@ template <int VPL>
 __global__ void __launch_bounds__(256) moe_gather_warp_kernel(const float* __restrict__ x, const int* __restrict__ src, int rows, __half* __restrict__ xg,
                                                               float* __restrict__ unscale, size_t lo_off) {
     constexpr int H = 128 * VPL;
+    pdl_launch_dependents();  // a dependent launch: the kernel behind may set itself up; nothing is read or written before the wait
+    pdl_wait();
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     const int s = src[row];
@@ -196,6 +200,8 @@ __device__ __forceinline__ float gated_act(float g, float u, int kind, float lim
 __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ g, const int* __restrict__ src, int inter, __half* __restrict__ a,
                                                       float* __restrict__ unscale, size_t lo_off, int kind, float limit) {
     __shared__ float red[8];
+    pdl_launch_dependents();  // a dependent launch: the kernel behind may set itself up; nothing is read or written before the wait
+    pdl_wait();
     const size_t row = blockIdx.x;
     __half* ar = a + row * inter;
     if (src && src[row] < 0) {  // a padding row of an expert's last tile: its products are zero, nothing to read
@@ -255,6 +261,8 @@ template <int VPL>
 __global__ void __launch_bounds__(256) moe_act_warp_kernel(const float* __restrict__ g, const int* __restrict__ src, int rows, __half* __restrict__ a,
                                                            float* __restrict__ unscale, size_t lo_off, int kind, float limit) {
     constexpr int INTER = 128 * VPL;
+    pdl_launch_dependents();  // a dependent launch: the kernel behind may set itself up; nothing is read or written before the wait
+    pdl_wait();
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     __half* ar = a + (size_t)row * INTER;
@@ -295,6 +303,8 @@ __global__ void __launch_bounds__(256) moe_act_warp_kernel(const float* __restri
 // y[tok][c] += sum over the token's k routes, in order, of w * o[slot][c].
 __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ slots, const float* __restrict__ w, int k, int h,
                                    float* __restrict__ y) {
+    pdl_launch_dependents();  // a dependent launch: the kernel behind may set itself up; nothing is read or written before the wait
+    pdl_wait();
     const int tok = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;  // four columns per thread (h is a multiple of 256)
     if (c >= h) return;
@@ -376,11 +386,10 @@ cudaError_t launch_moe_gather(const float* x, const int* src, size_t rows, size_
     if (rows == 0) return cudaSuccess;
     const unsigned wgrid = (unsigned)((rows + 7) / 8);
     switch (rows >= 1024 ? h / 128 : 0) {  // many rows of a common width: a warp per row
-        case 8: moe_gather_warp_kernel<8><<<wgrid, 256, 0, st>>>(x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h); break;
-        case 16: moe_gather_warp_kernel<16><<<wgrid, 256, 0, st>>>(x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h); break;
-        default: moe_gather_kernel<<<(unsigned)rows, 256, 0, st>>>(x, src, (int)h, (__half*)xg, unscale, lo_row0 * h);
+        case 8: return launch_k(moe_gather_warp_kernel<8>, dim3(wgrid), dim3(256), 0, st, true, x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h);
+        case 16: return launch_k(moe_gather_warp_kernel<16>, dim3(wgrid), dim3(256), 0, st, true, x, src, (int)rows, (__half*)xg, unscale, lo_row0 * h);
+        default: return launch_k(moe_gather_kernel, dim3((unsigned)rows), dim3(256), 0, st, true, x, src, (int)h, (__half*)xg, unscale, lo_row0 * h);
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t inter, void* a, float* unscale, size_t lo_row0, cudaStream_t st,
@@ -389,18 +398,16 @@ cudaError_t launch_moe_act(const float* g, const int* src, size_t rows, size_t i
     if (rows == 0) return cudaSuccess;
     const unsigned wgrid = (unsigned)((rows + 7) / 8);
     switch (rows >= 1024 ? inter / 128 : 0) {  // many rows of a common width: a warp per row
-        case 4: moe_act_warp_kernel<4><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
-        case 6: moe_act_warp_kernel<6><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
-        case 8: moe_act_warp_kernel<8><<<wgrid, 256, 0, st>>>(g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit); break;
-        default: moe_act_kernel<<<(unsigned)rows, 256, 0, st>>>(g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+        case 4: return launch_k(moe_act_warp_kernel<4>, dim3(wgrid), dim3(256), 0, st, true, g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+        case 6: return launch_k(moe_act_warp_kernel<6>, dim3(wgrid), dim3(256), 0, st, true, g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+        case 8: return launch_k(moe_act_warp_kernel<8>, dim3(wgrid), dim3(256), 0, st, true, g, src, (int)rows, (__half*)a, unscale, lo_row0 * inter, kind, limit);
+        default: return launch_k(moe_act_kernel, dim3((unsigned)rows), dim3(256), 0, st, true, g, src, (int)inter, (__half*)a, unscale, lo_row0 * inter, kind, limit);
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_moe_combine(const float* o, const int* slots, const float* w, size_t t, size_t k, size_t h, float* y, cudaStream_t st) {
     dim3 grid((unsigned)((h / 4 + 255) / 256), (unsigned)t);
-    moe_combine_kernel<<<grid, 256, 0, st>>>(o, slots, w, (int)k, (int)h, y);
-    return cudaGetLastError();
+    return launch_k(moe_combine_kernel, grid, dim3(256), 0, st, true, o, slots, w, (int)k, (int)h, y);
 }
 
 }  // namespace b2
