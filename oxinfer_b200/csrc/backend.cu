@@ -1196,7 +1196,7 @@ class Backend {
         if (rc) return rc;
         // the ranks meet: every rank's tiles have landed in every buffer (the kernel waited for its stores before it ended)
         // (the ranks' hosts are not in lockstep: a peer may be a few launches behind; four seconds of polling before giving up)
-        cudaError_t e = launch_exchange(ps, 0, 0, (uint32_t*)tp_sym.local, &gemm_status->code, stream, false, false, 8000000000ll);
+        cudaError_t e = launch_exchange(ps, 0, 0, (uint32_t*)tp_sym.local, &gemm_status->code, stream, true, false, 8000000000ll);
         launches++;
         if (e != cudaSuccess) return cuda_fail(e, "peer barrier");
         tp_sym.calls++;
