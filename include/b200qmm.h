@@ -312,6 +312,23 @@ int b2_plan_free(b2_ctx* ctx, b2_plan plan);
  * rope_cs from the host, hidden [n_hidden] and (if not NULL) logits [n_logits] back to the host.
  * Synchronous. Nonzero: nothing valid was written. */
 int b2_plan_step(b2_ctx* ctx, b2_plan plan, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits);
+/* Backend::decode_plan_multi (src/gpu.rs:273-276): a plan whose steps take up to `tokens` tokens (speculative verification).
+ * `tokens` 1 .. B2_PLAN_MAX_TOKENS; more is declined. A tensor-parallel graph (B2_OP_EXCHANGE) is declined for tokens > 1.
+ * The plan is exact in the sense of the reference's multi-token kernels (src/cuda_decode.cu:176-179): every token's hidden
+ * state, logits and cache rows equal those of one-token steps bit for bit; the products read their weights once for all
+ * tokens of the step. It also serves Backend::decode_plan_multi_fast (src/gpu.rs:281-283), whose default is the exact plan.
+ * All other plan calls (b2_plan_step, the KV calls, b2_plan_generate, b2_plan_free) take such a plan too. */
+#define B2_PLAN_MAX_TOKENS 4
+int b2_decode_plan_multi(b2_ctx* ctx, const b2_graph* graph, size_t tokens, b2_plan* out);
+/* DecodePlan::tokens (src/gpu_decode.rs:575-577): the most tokens of a step of this plan. */
+int b2_plan_tokens(b2_ctx* ctx, b2_plan plan, size_t* tokens);
+/* DecodePlan::step with Step::t = t tokens at positions pos .. pos + t - 1, each attending to the ones before it
+ * (src/gpu_decode.rs:538-570): x [t][n_input], hidden [t][n_hidden], logits [t][n_logits] or NULL, all on the host.
+ * rope_cs as Step::rope_cs: for each table of rope_halves, one after the other, t rows of cos[half] then sin[half].
+ * The step's keys and values are appended to the plan's caches at pos .. pos + t - 1; a caller that accepts only the first
+ * m tokens simply continues at pos + m (the rows behind are overwritten). Synchronous. Nonzero: nothing valid was written. */
+int b2_plan_step_multi(b2_ctx* ctx, b2_plan plan, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden,
+                       float* logits);
 /* Rows pos0 .. pos0+n-1 of KV cache `kv` from / to host arrays laid out [n][n_kv][hd] f32. */
 int b2_plan_kv_write(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v);
 int b2_plan_kv_read(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, float* k, float* v);

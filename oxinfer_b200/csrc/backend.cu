@@ -1322,7 +1322,7 @@ class Backend {
     }
 
     // ---- Backend::decode_plan (src/gpu.rs:262-289) and DecodePlan::step (src/gpu_decode.rs:538-587) ----
-    int decode_plan(const b2_graph* g, uint64_t* out) {
+    int decode_plan(const b2_graph* g, uint64_t* out, int tokens = 1) {
         if (!out) return fail(B2_ERR_ARG, "[b200qmm: decode_plan: null argument]");
         DecodePlanImpl* p = nullptr;
         std::string e;
@@ -1332,7 +1332,7 @@ class Backend {
                 Weight* w = find(h);
                 return w ? &w->dev : nullptr;
             },
-            sm_count, planes_read(), &p, e);
+            sm_count, planes_read(), tokens, &p, e);
         if (rc) {
             err = e;
             return rc;
@@ -1340,6 +1340,7 @@ class Backend {
         uint64_t h = next_handle++;
         decode_plans[h] = p;
         launches += p->launches_per_step();  // the eager first pass
+        for (int nt = 2; nt <= tokens; nt++) launches += p->launches_per_step((size_t)nt);
         *out = h;
         return B2_OK;
     }
@@ -1361,6 +1362,16 @@ class Backend {
         std::string e;
         int rc = p->step(stream, pos, x, rope_cs, hidden, logits, e);
         launches += p->launches_per_step() + 1;
+        calls++;
+        if (rc) err = e;
+        return rc;
+    }
+    int plan_step_multi(uint64_t h, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, float* logits) {
+        DecodePlanImpl* p = find_plan(h);
+        if (!p) return fail(B2_ERR_ARG, "[b200qmm: plan_step_multi: unknown plan]");
+        std::string e;
+        int rc = p->step_multi(stream, pos, t, x, rope_cs, hidden, logits, e);
+        launches += p->launches_per_step(t) + 1;
         calls++;
         if (rc) err = e;
         return rc;
@@ -1695,6 +1706,27 @@ B2_EXPORT int b2_moe_ep(b2_ctx* ctx, b2_moe_handle m, size_t n_experts_global, c
 B2_EXPORT int b2_decode_plan(b2_ctx* ctx, const b2_graph* graph, b2_plan* out) {
     LOCKED(ctx);
     return ctx->be.decode_plan(graph, out);
+}
+
+B2_EXPORT int b2_decode_plan_multi(b2_ctx* ctx, const b2_graph* graph, size_t tokens, b2_plan* out) {
+    LOCKED(ctx);
+    if (tokens == 0) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: decode_plan_multi: a step has at least one token]");
+    if (tokens > B2_PLAN_MAX_TOKENS) return ctx->be.fail(B2_DECLINED, "[b200qmm: decode_plan_multi: steps of at most four tokens are taken]");
+    return ctx->be.decode_plan(graph, out, (int)tokens);
+}
+
+B2_EXPORT int b2_plan_step_multi(b2_ctx* ctx, b2_plan plan, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden,
+                                 float* logits) {
+    LOCKED(ctx);
+    return ctx->be.plan_step_multi(plan, pos, t, x, rope_cs, hidden, logits);
+}
+
+B2_EXPORT int b2_plan_tokens(b2_ctx* ctx, b2_plan plan, size_t* out) {
+    LOCKED(ctx);
+    b2::DecodePlanImpl* p = ctx->be.find_plan(plan);
+    if (!p || !out) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: plan_tokens: unknown plan or null argument]");
+    *out = (size_t)p->tokens();
+    return B2_OK;
 }
 
 B2_EXPORT int b2_plan_free(b2_ctx* ctx, b2_plan plan) {

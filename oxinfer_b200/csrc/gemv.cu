@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(256) norm_planes_kernel(const float* __restric
 // (floats for the f32 vector, bytes for the planes), its outputs multi.y_stride floats after.
 struct GemvMulti {
     size_t x_stride, y_stride;
+    size_t ns_stride;  // floats between the tokens' blocks of norm partial sums (NormScale), when there is a factor
 };
 
 template <class F, bool PAIR, bool XF32, int NT>
@@ -124,7 +125,13 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
         }
     }
     __syncthreads();
-    const float kscale = norm_scale_factor(ns, lane);
+    float kscale[NT];
+#pragma unroll
+    for (int tk = 0; tk < NT; tk++) {
+        NormScale nt = ns;
+        if (nt.partial) nt.partial += (size_t)tk * multi.ns_stride;
+        kscale[tk] = norm_scale_factor(nt, lane);
+    }
     for (size_t r0 = r_first; r0 < n_out; r0 += r_step) {
         float accA[NT], accB[NT];
 #pragma unroll
@@ -137,7 +144,7 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
         }
 #pragma unroll
         for (int tk = 0; tk < NT; tk++) {
-            const float sa = warp_sum(accA[tk]) * kscale, sb = warp_sum(accB[tk]) * kscale;
+            const float sa = warp_sum(accA[tk]) * kscale[tk], sb = warp_sum(accB[tk]) * kscale[tk];
             float* yt = y + (size_t)tk * multi.y_stride;
             if (lane == 0) {
                 if (PAIR) {
@@ -444,7 +451,7 @@ cudaError_t launch_fmt_f(const WeightDev& w, const WeightDev* up, const float* x
 
 template <template <int> class FT, bool XF32, int NT = 1>
 cudaError_t launch_fmt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, const float* gate,
-                       int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi = GemvMulti{0, 0}) {
+                       int sm_count, cudaStream_t st, bool pdl, NormScale ns, GemvMulti multi = GemvMulti{0, 0, 0}) {
     if (XF32 || xp.np != 2) return launch_fmt_f<FT<3>, XF32, NT>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns, multi);
     return launch_fmt_f<FT<XF32 ? 3 : 2>, XF32, NT>(w, up, x, xp, y, mode, gate, sm_count, st, pdl, ns, multi);
 }
@@ -496,7 +503,7 @@ static cudaError_t launch_batched_fmt(const WeightDev& w, const WeightDev* up, c
     if (gx > cap) gx = cap;
     XPlanes none{};
     return launch_k(kern, dim3((unsigned)gx, (unsigned)batch), dim3(GEMV_THREADS), smem, st, pdl, w, pair ? *up : w, (const float*)nullptr, none, y, mode,
-                    (const float*)nullptr, NormScale{nullptr, 0, 0.0f, 0.0f}, b, GemvMulti{0, 0});
+                    (const float*)nullptr, NormScale{nullptr, 0, 0.0f, 0.0f}, b, GemvMulti{0, 0, 0});
 }
 
 cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const GemvBatch& b, size_t batch, float* y, int mode, int np, int sm_count,
@@ -511,14 +518,13 @@ cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const G
 
 template <int NT>
 static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, const float* x, XPlanes xp, float* y, int mode, int sm_count,
-                                   cudaStream_t st, GemvMulti m) {
-    const NormScale none{nullptr, 0, 0.0f, 0.0f};
+                                   cudaStream_t st, GemvMulti m, bool pdl, NormScale ns) {
     switch (w.fmt) {
-        case B2_FMT_MLX4: return launch_fmt<FmtMLX4_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
-        case B2_FMT_F8E4M3: return launch_fmt<FmtF8_T, true, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, false, none, m);
+        case B2_FMT_MLX4: return launch_fmt<FmtMLX4_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, pdl, ns, m);
+        case B2_FMT_Q4_K: return launch_fmt<FmtQ4K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, pdl, ns, m);
+        case B2_FMT_Q6_K: return launch_fmt<FmtQ6K_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, pdl, ns, m);
+        case B2_FMT_Q8_0: return launch_fmt<FmtQ8_0_T, false, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, pdl, ns, m);
+        case B2_FMT_F8E4M3: return launch_fmt<FmtF8_T, true, NT>(w, up, x, xp, y, mode, nullptr, sm_count, st, pdl, ns, m);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -529,15 +535,15 @@ bool gemv_multi_fits(const WeightDev& w, int nt) {
 }
 
 cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, XPlanes xp, size_t xp_stride, float* y,
-                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st) {
+                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st, bool pdl, NormScale ns, size_t ns_stride) {
     const bool f8 = w.fmt == B2_FMT_F8E4M3;
-    if (!gemv_multi_fits(w, nt)) return cudaErrorInvalidValue;
-    const GemvMulti m{f8 ? x_stride : xp_stride, y_stride};
+    if (!gemv_multi_fits(w, nt) || mode == B2_MODE_ADD_GATED) return cudaErrorInvalidValue;  // no gate pointer travels here
+    const GemvMulti m{f8 ? x_stride : xp_stride, y_stride, ns_stride};
     switch (nt) {
-        case 1: return launch_multi_nt<1>(w, up, x, xp, y, mode, sm_count, st, m);
-        case 2: return launch_multi_nt<2>(w, up, x, xp, y, mode, sm_count, st, m);
-        case 3: return launch_multi_nt<3>(w, up, x, xp, y, mode, sm_count, st, m);
-        default: return launch_multi_nt<4>(w, up, x, xp, y, mode, sm_count, st, m);
+        case 1: return launch_multi_nt<1>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);
+        case 2: return launch_multi_nt<2>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);
+        case 3: return launch_multi_nt<3>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);
+        default: return launch_multi_nt<4>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);
     }
 }
 

@@ -138,9 +138,11 @@ cudaError_t launch_gemv_batched(const WeightDev& w, const WeightDev* up, const G
 cudaError_t launch_xplanes_rows(const float* x, size_t rows, size_t K, uint8_t* planes, size_t stride, cudaStream_t st, bool pdl = false);
 // nt (1..4) tokens in one launch, the weights read once: token i's f32 vector at x + i * x_stride (FP8 weights) or planes
 // at xp + i * xp_stride bytes (the other formats), outputs at y + i * y_stride. Each token's result equals its
-// single-token result bit for bit. cudaErrorInvalidValue if the tokens' vectors do not fit in shared memory together.
+// single-token result bit for bit. cudaErrorInvalidValue if the tokens' vectors do not fit in shared memory together, or for
+// the gated mode. `ns`: token 0's deferred norm factor (see NormScale), token i's partial sums ns_stride floats further.
 cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const float* x, size_t x_stride, XPlanes xp, size_t xp_stride, float* y,
-                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st);
+                              size_t y_stride, int nt, int mode, int sm_count, cudaStream_t st, bool pdl = false,
+                              NormScale ns = NormScale{nullptr, 0, 0.0f, 0.0f}, size_t ns_stride = 0);
 // Whether launch_gemv handles this format and shape.
 bool gemv_supports(const WeightDev& w);
 

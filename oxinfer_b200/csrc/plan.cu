@@ -93,6 +93,8 @@ cudaError_t fuse_rows(const std::vector<const WeightDev*>& parts, WeightDev* out
 DecodePlanImpl::~DecodePlanImpl() {
     for (void* p : fused_) cudaFree(p);
     if (step_exec_) cudaGraphExecDestroy(step_exec_);
+    for (cudaGraphExec_t e : multi_exec_)
+        if (e) cudaGraphExecDestroy(e);
     if (gen_exec_) cudaGraphExecDestroy(gen_exec_);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
@@ -113,18 +115,24 @@ bool DecodePlanImpl::uses_weight(uint64_t h) const {
     return h != 0 && h == gen_embed_;
 }
 
-int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes,
+int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, int tokens,
                            DecodePlanImpl** out, std::string& err) {
     if (!g || !g->bufs || !g->ops || g->n_bufs == 0 || g->n_ops == 0 || !out) {
         err = "[b200qmm: decode_plan: empty graph]";
         return B2_ERR_ARG;
     }
-    if (g->max_len == 0 || g->n_rope > 8) {
-        err = "[b200qmm: decode_plan: max_len must be positive and at most 8 RoPE tables are taken]";
+    if (g->max_len == 0 || g->n_rope > 8 || (tokens > 0 && g->max_len < (uint32_t)tokens)) {
+        err = "[b200qmm: decode_plan: max_len must be positive (and hold a whole step) and at most 8 RoPE tables are taken]";
         return B2_ERR_ARG;
+    }
+    if (tokens < 1 || tokens > 4) {
+        err = "[b200qmm: decode_plan: a plan takes steps of 1 to 4 tokens]";
+        return tokens > 4 ? B2_DECLINED : B2_ERR_ARG;
     }
     std::unique_ptr<DecodePlanImpl> p(new DecodePlanImpl());
     p->sm_count_ = sm_count;
+    p->tokens_ = tokens;
+    const size_t T = (size_t)tokens;
     if (const char* e = getenv("B2_PLAN_PDL")) p->pdl_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_FUSE")) p->fuse_ = atoi(e) != 0;
     if (const char* e = getenv("B2_PLAN_DEFER_NORM")) p->defer_norm_ = atoi(e) != 0;
@@ -144,8 +152,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         off[i] = total;
         total += align_up((size_t)g->bufs[i], 64);
     }
-    PLAN_CUDA(cudaMalloc((void**)&p->bufs_, std::max<size_t>(total, 64) * sizeof(float)), "cudaMalloc(buffers)");
-    PLAN_CUDA(cudaMemset(p->bufs_, 0, std::max<size_t>(total, 64) * sizeof(float)), "cudaMemset(buffers)");
+    total = std::max<size_t>(total, 64);
+    p->block_floats_ = total;
+    PLAN_CUDA(cudaMalloc((void**)&p->bufs_, T * total * sizeof(float)), "cudaMalloc(buffers)");
+    PLAN_CUDA(cudaMemset(p->bufs_, 0, T * total * sizeof(float)), "cudaMemset(buffers)");
     for (uint32_t i = 0; i < g->n_bufs; i++) {
         p->buf_ptr_.push_back(p->bufs_ + off[i]);
         p->buf_len_.push_back((size_t)g->bufs[i]);
@@ -163,6 +173,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     std::vector<uint32_t> cs_off(g->n_rope + 1, 0);
     for (uint32_t i = 0; i < g->n_rope; i++) cs_off[i + 1] = cs_off[i] + 2 * g->rope_halves[i];
     p->cs_stride_ = cs_off[g->n_rope];
+    p->cs_off_ = cs_off;
 
     // ---- KV caches --------------------------------------------------------------------------------
     const size_t esz = p->kv_f16_ ? 2 : 4;
@@ -375,6 +386,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                 break;
             }
             case B2_OP_EXCHANGE: {
+                if (tokens > 1) {
+                    err = "[b200qmm: decode_plan: a tensor-parallel graph runs one token per step]";
+                    return B2_DECLINED;
+                }
                 if (o.n == 0 || o.n % 32) {
                     err = "[b200qmm: decode_plan: an exchanged vector must be a positive multiple of 32 values]";
                     return B2_ERR_ARG;
@@ -460,9 +475,10 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
             norm_floats += (n / 32 + 63) / 64 * 64;
         }
     }
+    p->partial_block_ = norm_floats;
     if (norm_floats) {
-        PLAN_CUDA(cudaMalloc((void**)&p->norm_partials_, norm_floats * sizeof(float)), "cudaMalloc(norm partial sums)");
-        PLAN_CUDA(cudaMemset(p->norm_partials_, 0, norm_floats * sizeof(float)), "cudaMemset(norm partial sums)");
+        PLAN_CUDA(cudaMalloc((void**)&p->norm_partials_, T * norm_floats * sizeof(float)), "cudaMalloc(norm partial sums)");
+        PLAN_CUDA(cudaMemset(p->norm_partials_, 0, T * norm_floats * sizeof(float)), "cudaMemset(norm partial sums)");
         for (Op& o : p->ops_)
             if ((o.kind == OP_NORM_DEFERRED || o.kind == B2_OP_LINEAR) && o.ns.count)
                 o.ns.partial = p->norm_partials_ + (size_t)(uintptr_t)o.ns.partial;
@@ -475,7 +491,9 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         region_at[r] = planes_total;
         planes_total += align_up(xplanes_bytes(region_k[r]), 256);
     }
-    PLAN_CUDA(cudaMalloc((void**)&p->planes_, std::max<size_t>(planes_total, 256)), "cudaMalloc(planes)");
+    planes_total = std::max<size_t>(planes_total, 256);
+    p->planes_block_ = planes_total;
+    PLAN_CUDA(cudaMalloc((void**)&p->planes_, T * planes_total), "cudaMalloc(planes)");
     for (auto& [oi, r] : region_of_op) {
         p->ops_[oi].xp = xplanes_at(p->planes_ + region_at[r], region_k[r]);
         p->ops_[oi].xp.np = planes;
@@ -545,7 +563,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
 
     // ---- scratch ------------------------------------------------------------------------------------
     if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, attend_part_floats(max_nh, max_hd) * sizeof(float)), "cudaMalloc(attention partials)");
-    size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1);
+    size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1) + 4 * T;
     PLAN_CUDA(cudaMalloc((void**)&p->words_, n_words * 4), "cudaMalloc(step words)");
     PLAN_CUDA(cudaMemset(p->words_, 0, n_words * 4), "cudaMemset(step words)");
     if (p->has_exchange_) {
@@ -556,6 +574,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     p->status_ = p->words_ + 4;
     p->argmax_counter_ = p->words_ + 5;
     p->att_counters_ = p->words_ + 8;
+    p->sp_multi_ = p->words_ + 8 + std::max<uint32_t>(max_nkv, 1);
     size_t table = (size_t)std::max<uint32_t>(p->cs_stride_, 1) * g->max_len;
     PLAN_CUDA(cudaMalloc((void**)&p->rope_table_, table * sizeof(float)), "cudaMalloc(rope table)");
     PLAN_CUDA(cudaMemset(p->rope_table_, 0, table * sizeof(float)), "cudaMemset(rope table)");
@@ -580,6 +599,19 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     if (rc) return rc;
     rc = p->capture(p->cap_stream_, false, &p->step_exec_, err);
     if (rc) return rc;
+    // Steps of several tokens: the same eager pass and a graph per token count.
+    for (int nt = 2; nt <= tokens; nt++) {
+        uint32_t words[16] = {};
+        for (int tk = 0; tk < nt; tk++) words[4 * tk] = (uint32_t)tk;
+        PLAN_CUDA(cudaMemcpyAsync(p->sp_multi_, words, 16 * nt, cudaMemcpyHostToDevice, p->cap_stream_), "cudaMemcpy(step words)");
+        rc = p->run_ops_multi(p->cap_stream_, nt, err, false);
+        if (rc) return rc;
+        PLAN_CUDA(cudaStreamSynchronize(p->cap_stream_), "first pass (several tokens)");
+        rc = p->check_status(err);
+        if (rc) return rc;
+        rc = p->capture(p->cap_stream_, false, &p->multi_exec_[nt], err, nt);
+        if (rc) return rc;
+    }
     *out = p.release();
     return B2_OK;
 }
@@ -622,13 +654,115 @@ int DecodePlanImpl::run_ops(cudaStream_t st, std::string& err, bool chained, boo
     return B2_OK;
 }
 
+// The ops for nt tokens at once, op by op: a product reads its weights once for all tokens where the tokens' vectors fit in
+// shared memory together (launch_gemv_multi: each token's sums are its one-token sums), every other op runs once per token
+// on that token's blocks (activations, planes, norm sums, step words). Attention and RoPE are ordinary launches, not
+// dependent ones: token i's attention reads the keys the launches just ahead of it appended, and its first key tile is
+// fetched before the dependency wait.
+int DecodePlanImpl::run_ops_multi(cudaStream_t st, int nt, std::string& err, bool chained) {
+    auto A = [&](const float* p, int tk) -> float* { return p ? const_cast<float*>(p) + (size_t)tk * block_floats_ : nullptr; };
+    auto P = [&](XPlanes xp, int tk) {
+        if (!xp.planes) return xp;
+        const size_t off = (size_t)tk * planes_block_;
+        xp.planes = (int8_t*)((uint8_t*)xp.planes + off);
+        xp.sx = (float2*)((uint8_t*)xp.sx + off);
+        xp.v16 = (int32_t*)((uint8_t*)xp.v16 + off);
+        return xp;
+    };
+    auto N = [&](NormScale ns, int tk) {
+        if (ns.partial) ns.partial += (size_t)tk * partial_block_;
+        return ns;
+    };
+    bool first = true;
+    uint64_t count = 0;
+    auto pdl = [&]() {
+        const bool v = chained && !first;
+        first = false;
+        count++;
+        return v;
+    };
+    for (size_t i = 0; i < ops_.size(); i++) {
+        const Op& o = ops_[i];
+        cudaError_t e = cudaSuccess;
+        switch (o.kind) {
+            case B2_OP_NORM:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++)
+                    e = launch_norm(A(o.x, tk), A(o.y, tk), o.p0, o.norm, o.rows, P(o.xp, tk), st, pdl());
+                break;
+            case OP_XPLANES:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) e = launch_xplanes(A(o.x, tk), o.n, P(o.xp, tk), st, pdl());
+                break;
+            case OP_NORM_DEFERRED:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++)
+                    e = launch_norm_planes(A(o.x, tk), o.p0, o.norm.pre, o.norm.n, P(o.xp, tk), const_cast<float*>(N(o.ns, tk).partial), st, pdl());
+                break;
+            case B2_OP_LINEAR: {
+                // FP8 products go token by token: their one-token kernel is the tensor-core one, and the tokens must match it.
+                const bool together = o.mode != B2_MODE_ADD_GATED && o.w.fmt != B2_FMT_F8E4M3 && gemv_multi_fits(o.w, nt);
+                if (together) {
+                    e = launch_gemv_multi(o.w, o.pair ? &o.w2 : nullptr, o.x, block_floats_, o.xp, planes_block_, o.y, block_floats_, nt, o.mode,
+                                          sm_count_, st, pdl(), o.ns, partial_block_);
+                    // the split the one-token product does in its epilogue (the same bits as the kernels of their own)
+                    for (int tk = 0; tk < nt && e == cudaSuccess && o.epi.out.planes; tk++) {
+                        if (o.epi.partial)
+                            e = launch_norm_planes(A(o.y, tk), o.epi.w, o.epi.pre, o.w.n_out, P(o.epi.out, tk),
+                                                   o.epi.partial + (size_t)tk * partial_block_, st, pdl());
+                        else
+                            e = launch_xplanes(A(o.y, tk), o.w.n_out, P(o.epi.out, tk), st, pdl());
+                    }
+                    break;
+                }
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) {
+                    EpiPlanes epi = o.epi;
+                    if (epi.out.planes) {
+                        epi.out = P(epi.out, tk);
+                        if (epi.partial) epi.partial += (size_t)tk * partial_block_;
+                    }
+                    e = launch_gemv(o.w, o.pair ? &o.w2 : nullptr, A(o.x, tk), P(o.xp, tk), A(o.y, tk), o.mode, A(o.z, tk), sm_count_, st, pdl(),
+                                    N(o.ns, tk), epi);
+                }
+                break;
+            }
+            case B2_OP_QK_ROPE:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) {
+                    e = launch_qk_rope(A(o.x, tk), A(o.y, tk), kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_multi_ + 4 * tk, o.rope, st,
+                                       false);
+                    first = false;
+                    count++;
+                }
+                break;
+            case B2_OP_ATTEND:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) {
+                    FusedRope fr = o.fr;
+                    fr.qkv = A(o.fr.qkv, tk);
+                    fr.cs_table = rope_table_;
+                    e = launch_attend(A(o.x, tk), kv_[o.kv].k, kv_[o.kv].v, kv_f16_, A(o.y, tk), part_, att_counters_, sp_multi_ + 4 * tk, o.attn,
+                                      P(o.xp, tk), status_, st, false, o.fr.qkv ? &fr : nullptr);
+                    first = false;
+                    count++;
+                }
+                break;
+            case B2_OP_GLU:
+                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) e = launch_glu(A(o.x, tk), A(o.z, tk), A(o.y, tk), o.n, o.gelu, st, pdl());
+                break;
+            default: e = cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) {
+            err = fmt("[b200qmm: plan: op %zu (kind %u) for %d tokens: %s]", i, o.kind, nt, cudaGetErrorString(e));
+            return B2_ERR_CUDA;
+        }
+    }
+    multi_launches_[nt] = count;
+    return B2_OK;
+}
+
 // Captures [embedding lookup,] ops [, argmax + advance] on `st` (not the legacy stream) into an executable graph.
-int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err) {
+int DecodePlanImpl::capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err, int nt) {
     PLAN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
     int rc = B2_OK;
     cudaError_t e = cudaSuccess;
     if (with_head) e = launch_dequantize(gen_embed_dev_, 0, 1, input_, st, token_);
-    if (e == cudaSuccess) rc = run_ops(st, err, pdl_, with_head);
+    if (e == cudaSuccess) rc = nt > 1 ? run_ops_multi(st, nt, err, pdl_) : run_ops(st, err, pdl_, with_head);
     if (e == cudaSuccess && rc == B2_OK && with_head)
         e = launch_argmax(logits_, n_logits_, argmax_val_, argmax_idx_, argmax_counter_, token_, out_tokens_, sp_, st, pdl_);
     cudaGraph_t graph = nullptr;
@@ -684,6 +818,49 @@ int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const floa
     PLAN_CUDA(cudaGraphLaunch(step_exec_, st), "cudaGraphLaunch");
     PLAN_CUDA(cudaMemcpyAsync(hidden, hidden_, n_hidden_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(hidden)");
     if (logits) PLAN_CUDA(cudaMemcpyAsync(logits, logits_, n_logits_ * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpy(logits)");
+    PLAN_CUDA(cudaStreamSynchronize(st), "step");
+    return check_status(err);
+}
+
+int DecodePlanImpl::step_multi(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, float* logits,
+                               std::string& err) {
+    if (t == 0 || t > (size_t)tokens_) {
+        err = fmt("[b200qmm: plan step: %zu tokens in a step of a plan made for %d]", t, tokens_);
+        return B2_ERR_ARG;
+    }
+    if (t == 1) return step(st, pos, x, rope_cs, hidden, logits, err);  // one row per table: the one-token layout
+    if (!x || (cs_stride_ && !rope_cs) || !hidden) {
+        err = "[b200qmm: plan step: x, rope_cs and hidden are required]";
+        return B2_ERR_ARG;
+    }
+    if (pos + t > max_len_) {
+        err = fmt("[b200qmm: plan step: positions %zu .. %zu are past the %u the caches hold]", pos, pos + t - 1, max_len_);
+        return B2_ERR_ARG;
+    }
+    if (logits && !n_logits_) {
+        err = "[b200qmm: plan step: the graph has no logits]";
+        return B2_ERR_ARG;
+    }
+    uint32_t words[16] = {};
+    for (size_t tk = 0; tk < t; tk++) {
+        words[4 * tk] = (uint32_t)(pos + tk);  // the token's position
+        words[4 * tk + 1] = (uint32_t)pos;     // the position of row 0 of the RoPE table
+    }
+    PLAN_CUDA(cudaMemcpyAsync(sp_multi_, words, 16 * t, cudaMemcpyHostToDevice, st), "cudaMemcpy(step words)");
+    PLAN_CUDA(cudaMemcpy2DAsync(input_, block_floats_ * 4, x, (size_t)n_input_ * 4, (size_t)n_input_ * 4, t, cudaMemcpyHostToDevice, st),
+              "cudaMemcpy(x)");
+    for (size_t i = 0; i + 1 < cs_off_.size(); i++) {  // table i: t rows of cos | sin, behind the rows of the tables ahead of it
+        const size_t row = (size_t)(cs_off_[i + 1] - cs_off_[i]) * 4;
+        if (row == 0) continue;
+        PLAN_CUDA(cudaMemcpy2DAsync(rope_table_ + cs_off_[i], (size_t)cs_stride_ * 4, rope_cs + t * cs_off_[i], row, row, t, cudaMemcpyHostToDevice, st),
+                  "cudaMemcpy(rope)");
+    }
+    PLAN_CUDA(cudaGraphLaunch(multi_exec_[t], st), "cudaGraphLaunch");
+    PLAN_CUDA(cudaMemcpy2DAsync(hidden, (size_t)n_hidden_ * 4, hidden_, block_floats_ * 4, (size_t)n_hidden_ * 4, t, cudaMemcpyDeviceToHost, st),
+              "cudaMemcpy(hidden)");
+    if (logits)
+        PLAN_CUDA(cudaMemcpy2DAsync(logits, (size_t)n_logits_ * 4, logits_, block_floats_ * 4, (size_t)n_logits_ * 4, t, cudaMemcpyDeviceToHost, st),
+                  "cudaMemcpy(logits)");
     PLAN_CUDA(cudaStreamSynchronize(st), "step");
     return check_status(err);
 }

@@ -15,11 +15,18 @@ class DecodePlanImpl {
     // `resolve` maps a weight handle to its device description (nullptr: unknown handle).
     // Returns B2_OK, B2_DECLINED or an error code; `err` gets the reason.
     // `planes`: how many planes of the activation split the plan's products read (2: the upper two, 16 bits; otherwise all three, 21 bits).
-    static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, DecodePlanImpl** out,
-                      std::string& err);
+    // `tokens` (1..4): the most tokens of a step (Backend::decode_plan_multi, src/gpu.rs:273-276). A plan of several tokens keeps
+    // one activation block, planes block and block of norm sums per token.
+    static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, int tokens,
+                      DecodePlanImpl** out, std::string& err);
     ~DecodePlanImpl();
 
     int step(cudaStream_t st, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err);
+    // t (1 .. tokens()) tokens at positions pos .. pos + t - 1, each attending to the ones before it: x [t][n_input],
+    // hidden [t][n_hidden], logits [t][n_logits] or null; rope_cs as the reference's Step::rope_cs (src/gpu_decode.rs:546-548):
+    // for each RoPE table in turn, t rows of cos then sin. Every token's results equal those of t one-token steps bit for bit.
+    int step_multi(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err);
+    int tokens() const { return tokens_; }
     int kv_write(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v, std::string& err);
     int kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err);
     int generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
@@ -27,6 +34,7 @@ class DecodePlanImpl {
     int export_handle(void* out128, std::string& err);
     int attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err);
     uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
+    uint64_t launches_per_step(size_t t) const { return t >= 2 && t <= 4 ? multi_launches_[t] : (uint64_t)ops_.size(); }
     bool uses_weight(uint64_t h) const;
 
   private:
@@ -53,10 +61,18 @@ class DecodePlanImpl {
     };
     DecodePlanImpl() = default;
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
-    int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err);
+    int run_ops_multi(cudaStream_t st, int nt, std::string& err, bool chained);
+    int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err, int nt = 1);
     int check_status(std::string& err);
 
     std::vector<Op> ops_;
+    // plans of several tokens: token i's activations, planes and norm sums sit these strides after token 0's
+    int tokens_ = 1;
+    size_t block_floats_ = 0, planes_block_ = 0, partial_block_ = 0;
+    uint32_t* sp_multi_ = nullptr;        // [tokens][4] step words, inside words_
+    std::vector<uint32_t> cs_off_;        // start of each RoPE table's values inside a row of the device table
+    cudaGraphExec_t multi_exec_[5] = {};  // [nt], nt = 2 .. tokens
+    uint64_t multi_launches_[5] = {};     // kernels of a step of nt tokens
     std::vector<uint64_t> weight_handles_;
     int sm_count_ = 148;
     bool pdl_ = true;  // programmatic dependent launch between the kernels of a step (B2_PLAN_PDL=0 switches it off)

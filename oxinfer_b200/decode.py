@@ -136,6 +136,26 @@ class DecodePlan:
                                                  logits.ctypes.data if logits is not None else None))
         return hidden, logits
 
+    def tokens(self) -> int:
+        """``DecodePlan::tokens`` (``src/gpu_decode.rs:575-577``): the most tokens of a step."""
+        n = C.c_size_t()
+        self._be._check(self._be._L.b2_plan_tokens(self._be._ctx, self.handle, C.byref(n)))
+        return n.value
+
+    def step_multi(self, pos: int, x: np.ndarray, rope_cs: np.ndarray, want_logits: bool = True):
+        """``t`` tokens at positions ``pos .. pos + t - 1`` (``Step::t``, ``src/gpu_decode.rs:538-570``): ``x`` is ``[t][n_input]``,
+        ``rope_cs`` holds, for each RoPE table in turn, ``t`` rows of cos then sin. Returns (hidden ``[t][n_hidden]``, logits
+        ``[t][n_logits]`` or None); every row equals the result of a one-token step, bit for bit."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        t = x.shape[0]
+        cs = np.ascontiguousarray(rope_cs, dtype=np.float32)
+        assert x.ndim == 2 and x.shape[1] == self.graph.n_input and cs.size == t * self.cs_stride
+        hidden = np.empty((t, self.graph.n_hidden), dtype=np.float32)
+        logits = np.empty((t, self.graph.logits[1]), dtype=np.float32) if want_logits and self.graph.logits else None
+        self._be._check(self._be._L.b2_plan_step_multi(self._be._ctx, self.handle, pos, t, x.ctypes.data, cs.ctypes.data, hidden.ctypes.data,
+                                                       logits.ctypes.data if logits is not None else None))
+        return hidden, logits
+
     def kv_write(self, kv: int, pos0: int, k: np.ndarray, v: np.ndarray) -> None:
         """Rows ``[n][n_kv][hd]`` f32 in the host cache's order into positions ``pos0 ..``."""
         k = np.ascontiguousarray(k, dtype=np.float32)
@@ -163,8 +183,9 @@ class DecodePlan:
         return out, ms.value
 
 
-def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False) -> DecodePlan | None:
-    """``Backend::decode_plan`` (``src/gpu.rs:262-289``): a plan, or ``None`` when the graph is declined."""
+def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False, tokens: int = 1) -> DecodePlan | None:
+    """``Backend::decode_plan`` (``src/gpu.rs:262-289``): a plan, or ``None`` when the graph is declined. ``tokens`` > 1:
+    ``Backend::decode_plan_multi`` (``src/gpu.rs:273-276``), steps of up to that many tokens."""
     bufs = (C.c_uint64 * len(g.bufs))(*g.bufs)
     ops = (_lib.Op * len(g.ops))(*g.ops)
     nkv = (C.c_uint32 * max(1, len(g.kv)))(*[k[0] for k in g.kv])
@@ -175,9 +196,16 @@ def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False) -> DecodePlan 
                           n_hidden=g.n_hidden, logits=lv.c(), n_logits=ln, kv_nkv=nkv, kv_hd=hd, n_kv=len(g.kv), rope_halves=halves,
                           n_rope=len(g.rope_halves), max_len=max_len, kv_f16=int(kv_f16))
     h = C.c_uint64()
-    if not be._check(be._L.b2_decode_plan(be._ctx, C.byref(desc), C.byref(h))):
+    rc = be._L.b2_decode_plan(be._ctx, C.byref(desc), C.byref(h)) if tokens == 1 else \
+        be._L.b2_decode_plan_multi(be._ctx, C.byref(desc), tokens, C.byref(h))
+    if not be._check(rc):
         return None
     return DecodePlan(be, h.value, g, max_len)
+
+
+def decode_plan_multi(be, g: Graph, max_len: int, tokens: int, kv_f16: bool = False) -> DecodePlan | None:
+    """``Backend::decode_plan_multi`` (``src/gpu.rs:273-276``); also what ``decode_plan_multi_fast`` gives (the exact plan)."""
+    return decode_plan(be, g, max_len, kv_f16=kv_f16, tokens=tokens)
 
 
 # ---- RoPE tables (src/kernels.rs:2277-2306) ---------------------------------------------------------
