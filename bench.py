@@ -795,6 +795,37 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
         out["cpu_baseline"] = {"value": cpu_tokens / dt, "unit": "tok/s", "cores": O.cpu_threads(), "kind": "port",
                                "sample": f"{cpu_tokens} tokens at context {ctx} (int8-activation decode kernels, f32 attention)"}
     if world == 1 and e2e_tokens:
+        # Steps of several tokens (Backend::decode_plan_multi: speculative verification), through b2_plan_step_multi with host
+        # buffers: t embeddings and RoPE rows in, t hidden states and t rows of logits out. Each step is first checked against
+        # one-token steps of the plan above (bit for bit), then timed by the host clock around the synchronous calls.
+        try:
+            many = D.decode_plan_multi(be, g, max_len, 4, kv_f16=kv_f16)
+            if many is None:
+                raise RuntimeError("declined: " + be.last_declined)
+            rng3 = np.random.default_rng(7)
+            for li in range(n_layers):
+                k = rng3.standard_normal((ctx, row), dtype=np.float32)
+                v = rng3.standard_normal((ctx, row), dtype=np.float32)
+                many.kv_write(li, 0, k, v)
+                plan.kv_write(li, 0, k, v)
+            xs = np.random.default_rng(12).standard_normal((4, cfg["h"])).astype(np.float32)
+            ones = [plan.step(ctx + i, xs[i], table[i]) for i in range(4)]
+            hm, lm = many.step_multi(ctx, xs, table[:4])
+            same = all(np.array_equal(hm[i], ones[i][0]) and np.array_equal(lm[i], ones[i][1]) for i in range(4))
+            res = {"parity": "4 tokens in one step: hidden states and logits equal four one-token steps bit for bit" if same
+                   else "MISMATCH against one-token steps", "steps_timed": 24}
+            for t in (1, 2, 3, 4):
+                many.step_multi(ctx, xs[:t], table[:t])
+                t0 = time.perf_counter()
+                for _ in range(24):
+                    many.step_multi(ctx, xs[:t], table[:t])
+                dt = (time.perf_counter() - t0) / 24
+                res[f"t{t}"] = {"ms_per_step": dt * 1e3, "tok_s": t / dt}
+            res["call"] = "b2_plan_step_multi: host x [t][h] and RoPE rows in, hidden [t][h] and logits [t][vocab] out, synchronous"
+            out["multi_token_steps"] = res
+            many.close()
+        except Exception as e:
+            out["multi_token_steps"] = {"error": str(e)}
         # the same model with the products reading 16 of the activations' 21 bits (b2_set_fast_planes; not the default)
         try:
             be.set_fast_planes(True)

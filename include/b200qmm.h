@@ -329,6 +329,17 @@ int b2_plan_tokens(b2_ctx* ctx, b2_plan plan, size_t* tokens);
  * m tokens simply continues at pos + m (the rows behind are overwritten). Synchronous. Nonzero: nothing valid was written. */
 int b2_plan_step_multi(b2_ctx* ctx, b2_plan plan, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden,
                        float* logits);
+/* Backend::decode_plan_prefill (src/gpu.rs:283-289): a plan whose steps take up to `tokens` tokens (1 .. B2_PREFILL_MAX_TOKENS)
+ * on batched kernels, the activations on the device for the whole step: every product is a tensor-core GEMM over all token
+ * rows (b2_matmul's kernel), attention a causal tensor-core kernel over the step's queries and the plan's KV cache. Its
+ * results differ from one-token steps in rounding (as the reference says of its own prefill plans). The graph is the decode
+ * graph without the head (n_logits == 0: the reference builds its prefill graph that way, src/model_gpu.rs:398-400); products
+ * need a format with a tensor-core kernel (Q4_K, MLX-4, FP8), otherwise B2_DECLINED. Steps go through b2_plan_step_multi
+ * (logits NULL); the KV calls, b2_plan_tokens and b2_plan_free apply. */
+#define B2_PREFILL_MAX_TOKENS 8192
+int b2_decode_plan_prefill(b2_ctx* ctx, const b2_graph* graph, size_t tokens, b2_plan* out);
+/* Device time in milliseconds of the kernels of the plan's last prefill step (between the host copies); 0 before one. */
+int b2_plan_last_step_ms(b2_ctx* ctx, b2_plan plan, float* ms);
 /* Rows pos0 .. pos0+n-1 of KV cache `kv` from / to host arrays laid out [n][n_kv][hd] f32. */
 int b2_plan_kv_write(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v);
 int b2_plan_kv_read(b2_ctx* ctx, b2_plan plan, uint32_t kv, size_t pos0, size_t n, float* k, float* v);

@@ -122,6 +122,8 @@ _SIGNATURES = {
     "b2_decode_plan": (C.c_int, [C.c_void_p, C.POINTER(GraphDesc), C.POINTER(C.c_uint64)]),
     "b2_decode_plan_multi": (C.c_int, [C.c_void_p, C.POINTER(GraphDesc), C.c_size_t, C.POINTER(C.c_uint64)]),
     "b2_plan_tokens": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_size_t)]),
+    "b2_decode_plan_prefill": (C.c_int, [C.c_void_p, C.POINTER(GraphDesc), C.c_size_t, C.POINTER(C.c_uint64)]),
+    "b2_plan_last_step_ms": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_float)]),
     "b2_plan_step_multi": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b2_plan_free": (C.c_int, [C.c_void_p, C.c_uint64]),
     "b2_plan_step": (C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -1322,7 +1322,7 @@ class Backend {
     }
 
     // ---- Backend::decode_plan (src/gpu.rs:262-289) and DecodePlan::step (src/gpu_decode.rs:538-587) ----
-    int decode_plan(const b2_graph* g, uint64_t* out, int tokens = 1) {
+    int decode_plan(const b2_graph* g, uint64_t* out, int tokens = 1, bool prefill = false) {
         if (!out) return fail(B2_ERR_ARG, "[b200qmm: decode_plan: null argument]");
         DecodePlanImpl* p = nullptr;
         std::string e;
@@ -1332,15 +1332,15 @@ class Backend {
                 Weight* w = find(h);
                 return w ? &w->dev : nullptr;
             },
-            sm_count, planes_read(), tokens, &p, e);
+            sm_count, planes_read(), tokens, prefill, &p, e);
         if (rc) {
             err = e;
             return rc;
         }
         uint64_t h = next_handle++;
         decode_plans[h] = p;
-        launches += p->launches_per_step();  // the eager first pass
-        for (int nt = 2; nt <= tokens; nt++) launches += p->launches_per_step((size_t)nt);
+        if (!prefill) launches += p->launches_per_step();  // the eager first pass
+        for (int nt = 2; nt <= tokens && !prefill; nt++) launches += p->launches_per_step((size_t)nt);
         *out = h;
         return B2_OK;
     }
@@ -1719,6 +1719,21 @@ B2_EXPORT int b2_plan_step_multi(b2_ctx* ctx, b2_plan plan, size_t pos, size_t t
                                  float* logits) {
     LOCKED(ctx);
     return ctx->be.plan_step_multi(plan, pos, t, x, rope_cs, hidden, logits);
+}
+
+B2_EXPORT int b2_decode_plan_prefill(b2_ctx* ctx, const b2_graph* graph, size_t tokens, b2_plan* out) {
+    LOCKED(ctx);
+    if (tokens == 0) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: decode_plan_prefill: a step has at least one token]");
+    if (tokens > B2_PREFILL_MAX_TOKENS) return ctx->be.fail(B2_DECLINED, "[b200qmm: decode_plan_prefill: steps of at most 8192 tokens are taken]");
+    return ctx->be.decode_plan(graph, out, (int)tokens, true);
+}
+
+B2_EXPORT int b2_plan_last_step_ms(b2_ctx* ctx, b2_plan plan, float* ms) {
+    LOCKED(ctx);
+    b2::DecodePlanImpl* p = ctx->be.find_plan(plan);
+    if (!p || !ms) return ctx->be.fail(B2_ERR_ARG, "[b200qmm: plan_last_step_ms: unknown plan or null argument]");
+    *ms = p->last_step_ms();
+    return B2_OK;
 }
 
 B2_EXPORT int b2_plan_tokens(b2_ctx* ctx, b2_plan plan, size_t* out) {

@@ -784,12 +784,12 @@ __device__ __forceinline__ float load_as_float(const __half* p) { return __half2
 
 template <typename T>
 __global__ void __launch_bounds__(256) to_f16_rows_kernel(const T* __restrict__ x, int K, __half* __restrict__ out, float* __restrict__ unscale,
-                                                          size_t lo_off) {
+                                                          size_t lo_off, size_t x_ld) {
     __shared__ float red[8];
     // (a dependent launch: the GEMM behind it may set itself up meanwhile; the GEMM ahead of it may still be reading `out`)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const T* xr = x + (size_t)blockIdx.x * K;
+    const T* xr = x + (size_t)blockIdx.x * x_ld;
     __half* o = out + (size_t)blockIdx.x * K;
     float mx = 0.0f;
     for (int i = threadIdx.x; i < K; i += 256) mx = fmaxf(mx, fabsf(load_as_float(xr + i)));
@@ -1125,15 +1125,16 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
                     (const CUtensorMap*)p->y_more, p->n_more);
 }
 
-cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0) {
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0, size_t x_ld) {
     if (t == 0 || K % 2) return cudaErrorInvalidValue;
     const size_t lo_off = lo_row0 * K;
+    if (x_ld == 0) x_ld = K;
     if (x_dtype == B2_F32)
-        return launch_k(to_f16_rows_kernel<float>, dim3((unsigned)t), dim3(256), 0, st, true, (const float*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<float>, dim3((unsigned)t), dim3(256), 0, st, true, (const float*)x, (int)K, (__half*)x16, unscale, lo_off, x_ld);
     else if (x_dtype == B2_BF16)
-        return launch_k(to_f16_rows_kernel<__nv_bfloat16>, dim3((unsigned)t), dim3(256), 0, st, true, (const __nv_bfloat16*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<__nv_bfloat16>, dim3((unsigned)t), dim3(256), 0, st, true, (const __nv_bfloat16*)x, (int)K, (__half*)x16, unscale, lo_off, x_ld);
     else if (x_dtype == B2_F16)
-        return launch_k(to_f16_rows_kernel<__half>, dim3((unsigned)t), dim3(256), 0, st, true, (const __half*)x, (int)K, (__half*)x16, unscale, lo_off);
+        return launch_k(to_f16_rows_kernel<__half>, dim3((unsigned)t), dim3(256), 0, st, true, (const __half*)x, (int)K, (__half*)x16, unscale, lo_off, x_ld);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();

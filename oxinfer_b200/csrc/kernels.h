@@ -193,7 +193,9 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
 // x (f32 / bf16 / f16, [t][K]) -> f16 [t][K], every row multiplied by a power of two that brings its largest magnitude
 // into [2^14, 2^15) (no overflow, no subnormals, same relative rounding at every magnitude); unscale[row] = 1 / factor.
 // lo_row0 > 0: two-term activations, x * factor = hi + lo; the lo rows go lo_row0 rows below the hi rows of x16.
-cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0 = 0);
+// x_ld: elements between the rows of x (0: K, the rows are contiguous).
+cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* x16, float* unscale, cudaStream_t st, size_t lo_row0 = 0,
+                          size_t x_ld = 0);
 // Whether nt (1..4) token rows' vectors fit in shared memory together for launch_gemv_multi.
 bool gemv_multi_fits(const WeightDev& w, int nt);
 
@@ -285,5 +287,20 @@ cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, i
 // pval / pidx: 128 words each; counter: one zeroed word.
 cudaError_t launch_argmax(const float* logits, uint32_t n, float* pval, int* pidx, uint32_t* counter, int* token, int* out_tokens, uint32_t* sp,
                           cudaStream_t st, bool pdl = false);
+
+// ---- prefill_ops.cu: the same ops over many token rows (row r of an activation `stride` floats behind row r - 1) -----------
+// Token row r is at position sp[0] + r; sp[1] is the position of row 0 of the RoPE table.
+cudaError_t launch_qk_rope_rows(const float* qkv, float* qo, size_t stride, uint32_t rows, void* kc, void* vc, int kv_f16, const float* qn,
+                                const float* kn, const float* cs_table, const uint32_t* sp, const DecRope& p, cudaStream_t st);
+bool attend_rows_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
+// Causal attention of `rows` query tokens over the cache (which already holds their keys and values): tensor-core products
+// over f16 roundings of q, k, v and the probabilities, f32 sums.
+cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16,
+                               const uint32_t* sp, const DecAttn& p, cudaStream_t st);
+cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
+                            uint32_t rows, int gelu, cudaStream_t st);
+// dst[r][i] (+)= src[r][i] for i < n (a multiple of 4; 16-byte aligned rows).
+cudaError_t launch_rows_op(float* dst, size_t dst_stride, const float* src, size_t src_stride, uint32_t n, uint32_t rows, bool add,
+                           cudaStream_t st);
 
 }  // namespace b2

@@ -104,7 +104,9 @@ DecodePlanImpl::~DecodePlanImpl() {
         if (k.v) cudaFree(k.v);
     }
     for (void* m : peer_maps_) cudaIpcCloseMemHandle(m);
-    void* frees[] = {norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
+    for (auto& kv : gemm_plans_)
+        for (GemmPlan* gp : kv.second) gemm_tc_plan_destroy(gp);
+    void* frees[] = {x16_, unscale_, tmp_a_, tmp_b_, gemm_status_, norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -116,7 +118,7 @@ bool DecodePlanImpl::uses_weight(uint64_t h) const {
 }
 
 int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, int tokens,
-                           DecodePlanImpl** out, std::string& err) {
+                           bool prefill, DecodePlanImpl** out, std::string& err) {
     if (!g || !g->bufs || !g->ops || g->n_bufs == 0 || g->n_ops == 0 || !out) {
         err = "[b200qmm: decode_plan: empty graph]";
         return B2_ERR_ARG;
@@ -125,9 +127,13 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         err = "[b200qmm: decode_plan: max_len must be positive (and hold a whole step) and at most 8 RoPE tables are taken]";
         return B2_ERR_ARG;
     }
-    if (tokens < 1 || tokens > 4) {
-        err = "[b200qmm: decode_plan: a plan takes steps of 1 to 4 tokens]";
-        return tokens > 4 ? B2_DECLINED : B2_ERR_ARG;
+    if (tokens < 1 || tokens > (prefill ? 8192 : 4)) {
+        err = prefill ? "[b200qmm: decode_plan: a prefill plan takes steps of 1 to 8192 tokens]" : "[b200qmm: decode_plan: a plan takes steps of 1 to 4 tokens]";
+        return tokens >= 1 ? B2_DECLINED : B2_ERR_ARG;
+    }
+    if (prefill && g->n_logits) {
+        err = "[b200qmm: decode_plan: a prefill plan ends at the hidden states (a graph without logits)]";
+        return B2_DECLINED;
     }
     std::unique_ptr<DecodePlanImpl> p(new DecodePlanImpl());
     p->sm_count_ = sm_count;
@@ -142,6 +148,12 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         p->epilogue_ = epi_level != 0;
     }
     if (const char* e = getenv("B2_PLAN_FUSE_ROPE")) p->fuse_rope_ = atoi(e) != 0;
+    if (prefill) {  // the one-token kernels' fusions do not apply: the products are GEMMs
+        p->prefill_ = true;
+        p->defer_norm_ = p->fuse_rope_ = p->epilogue_ = false;
+        const char* e = getenv("B2_PREFILL_ATTEND");
+        p->loop_attend_ = e && strcmp(e, "loop") == 0;
+    }
     p->max_len_ = g->max_len;
     p->kv_f16_ = g->kv_f16 ? 1 : 0;
 
@@ -253,8 +265,13 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                     err = fmt("[b200qmm: decode_plan: linear %u x %u does not match its weight %zu x %zu]", o.n_out, o.n_in, w->n_out, w->n_in);
                     return B2_ERR_ARG;
                 }
-                if (!gemv_supports(*w)) {
+                if (!prefill && !gemv_supports(*w)) {
                     err = "[b200qmm: decode_plan: a weight's shape is outside the matrix-vector kernels]";
+                    return B2_DECLINED;
+                }
+                if (prefill && (!gemm_tc_supports(*w, (size_t)tokens) || o.mode == B2_MODE_ADD_GATED || o.n_out % 4)) {
+                    err = "[b200qmm: decode_plan: a prefill plan takes products with a tensor-core kernel (Q4_K, MLX-4, FP8), rows in multiples of 4, "
+                          "and no gated mode]";
                     return B2_DECLINED;
                 }
                 op.w = *w;
@@ -303,7 +320,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                         i = j - 1;  // the fused ops are done
                     }
                 }
-                if (w->fmt != B2_FMT_F8E4M3) {
+                if (w->fmt != B2_FMT_F8E4M3 && !prefill) {
                     Key key{o.x.buf, o.x.off, o.n_in};
                     size_t region;
                     auto v = valid.find(key);
@@ -361,7 +378,11 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                     err = "[b200qmm: decode_plan: attend does not match its KV cache]";
                     return B2_ERR_ARG;
                 }
-                if (!attend_supports(o.nh, o.nkv, o.hd)) {
+                if (prefill && !attend_rows_supports(o.nh, o.nkv, o.hd)) {
+                    err = "[b200qmm: decode_plan: prefill attention takes head dimensions 64 and 128]";
+                    return B2_DECLINED;
+                }
+                if ((!prefill || p->loop_attend_) && !attend_supports(o.nh, o.nkv, o.hd)) {
                     err = fmt("[b200qmm: decode_plan: attention with %u heads over %u KV heads of %u is outside the kernel (head dim 64 / 128, "
                               "1 / 2 / 4 / 8 heads per KV head)]", o.nh, o.nkv, o.hd);
                     return B2_DECLINED;
@@ -589,6 +610,22 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     PLAN_CUDA(cudaEventCreate(&p->ev0_), "cudaEventCreate");
     PLAN_CUDA(cudaEventCreate(&p->ev1_), "cudaEventCreate");
 
+    if (prefill) {
+        size_t max_k = 64, max_n = 64;
+        for (const Op& o : p->ops_)
+            if (o.kind == B2_OP_LINEAR) {
+                max_k = std::max(max_k, o.w.n_in);
+                max_n = std::max(max_n, o.w.n_out);
+            }
+        PLAN_CUDA(cudaMalloc(&p->x16_, T * max_k * 2), "cudaMalloc(f16 activations)");
+        PLAN_CUDA(cudaMalloc((void**)&p->unscale_, T * sizeof(float)), "cudaMalloc(row factors)");
+        PLAN_CUDA(cudaMalloc((void**)&p->tmp_a_, T * max_n * sizeof(float)), "cudaMalloc(products)");
+        PLAN_CUDA(cudaMalloc((void**)&p->tmp_b_, T * max_n * sizeof(float)), "cudaMalloc(products)");
+        PLAN_CUDA(cudaMalloc((void**)&p->gemm_status_, sizeof(GemmStatus)), "cudaMalloc(GEMM status)");
+        PLAN_CUDA(cudaMemset(p->gemm_status_, 0, sizeof(GemmStatus)), "cudaMemset(GEMM status)");
+        *out = p.release();  // nothing is captured: a step launches its kernels (a few per op, whatever the token count)
+        return B2_OK;
+    }
     // One eager pass (loads every kernel outside a capture, and surfaces launch errors with their op),
     // then the step graph.
     PLAN_CUDA(launch_set_step(p->sp_, 0, 0, 0, nullptr, 0, p->cap_stream_), "set_step");
@@ -796,6 +833,7 @@ int DecodePlanImpl::check_status(std::string& err) {
 }
 
 int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err) {
+    if (prefill_) return step_multi(st, pos, 1, x, rope_cs, hidden, logits, err);
     if (!x || (cs_stride_ && !rope_cs) || !hidden) {
         err = "[b200qmm: plan step: x, rope_cs and hidden are required]";
         return B2_ERR_ARG;
@@ -824,6 +862,13 @@ int DecodePlanImpl::step(cudaStream_t st, size_t pos, const float* x, const floa
 
 int DecodePlanImpl::step_multi(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, float* logits,
                                std::string& err) {
+    if (prefill_) {
+        if (logits) {
+            err = "[b200qmm: plan step: a prefill plan has no logits]";
+            return B2_ERR_ARG;
+        }
+        return step_prefill(st, pos, t, x, rope_cs, hidden, err);
+    }
     if (t == 0 || t > (size_t)tokens_) {
         err = fmt("[b200qmm: plan step: %zu tokens in a step of a plan made for %d]", t, tokens_);
         return B2_ERR_ARG;
@@ -862,6 +907,169 @@ int DecodePlanImpl::step_multi(cudaStream_t st, size_t pos, size_t t, const floa
         PLAN_CUDA(cudaMemcpy2DAsync(logits, (size_t)n_logits_ * 4, logits_, block_floats_ * 4, (size_t)n_logits_ * 4, t, cudaMemcpyDeviceToHost, st),
                   "cudaMemcpy(logits)");
     PLAN_CUDA(cudaStreamSynchronize(st), "step");
+    return check_status(err);
+}
+
+// A prefill step's kernels for t token rows. A product = the rows to f16 (each multiplied by a power of two, taken out again
+// by the GEMM's epilogue), then the tensor-core GEMM: straight into the activation rows where it stores, into a scratch
+// matrix where it adds to the rows (a row-wise add follows) or is one of a gate / up pair (the activation kernel follows).
+int DecodePlanImpl::run_prefill(cudaStream_t st, size_t t, std::string& err) {
+    std::vector<GemmPlan*>& plans = gemm_plans_[t];
+    const bool build = plans.empty();
+    size_t slot = 0;
+    uint64_t count = 0;
+    const size_t ld = block_floats_;
+    const uint32_t rows = (uint32_t)t;
+    const float* x16_src = nullptr;  // the vector whose f16 rows the scratch holds
+    size_t x16_k = 0;
+    auto gemm = [&](const WeightDev& w, float* y, size_t y_ld) -> cudaError_t {
+        GemmPlan* gp = nullptr;
+        if (build) {
+            char msg[256] = {0};
+            GemmPeerY py;
+            py.ld = y_ld;
+            cudaError_t e = gemm_tc_plan_create(w, x16_, t, y, B2_F32, &gp, msg, sizeof msg, 1, nullptr, 0, 0, 1, y_ld != w.n_out ? &py : nullptr);
+            if (e != cudaSuccess) {
+                err = fmt("[b200qmm: prefill: %s]", msg);
+                return e;
+            }
+            plans.push_back(gp);
+        } else {
+            gp = plans[slot];
+        }
+        slot++;
+        count++;
+        return launch_gemm_tc(gp, w, t, y, B2_F32, gemm_status_, sm_count_, st, unscale_);
+    };
+    int rc = B2_OK;
+    for (size_t i = 0; i < ops_.size() && rc == B2_OK; i++) {
+        const Op& o = ops_[i];
+        cudaError_t e = cudaSuccess;
+        switch (o.kind) {
+            case B2_OP_NORM:
+                if (o.rows == 1) {
+                    DecNorm n = o.norm;
+                    n.x_stride = n.out_stride = (uint32_t)ld;
+                    e = launch_norm(o.x, o.y, o.p0, n, rows, XPlanes{}, st, false);
+                    count++;
+                } else {
+                    for (size_t tk = 0; tk < t && e == cudaSuccess; tk++, count++)
+                        e = launch_norm(o.x + tk * ld, o.y + tk * ld, o.p0, o.norm, o.rows, XPlanes{}, st, false);
+                }
+                if (overlaps_f(o.y, (size_t)(o.rows - 1) * o.norm.out_stride + o.norm.n, x16_src, x16_k)) x16_src = nullptr;
+                break;
+            case B2_OP_LINEAR: {
+                const size_t K = o.w.n_in, n_out = o.w.n_out;
+                if (!(x16_src == o.x && x16_k == K)) {
+                    e = launch_to_f16(o.x, B2_F32, t, K, x16_, unscale_, st, 0, ld);
+                    count++;
+                    x16_src = o.x;
+                    x16_k = K;
+                }
+                if (e != cudaSuccess) break;
+                if (o.pair) {
+                    e = gemm(o.w, tmp_a_, n_out);
+                    if (e == cudaSuccess) e = gemm(o.w2, tmp_b_, n_out);
+                    if (e == cudaSuccess) e = launch_glu_rows(tmp_a_, n_out, tmp_b_, n_out, o.y, ld, (uint32_t)n_out, rows, o.mode == B2_MODE_GELU_PAIR, st);
+                    count++;
+                } else if (o.mode == B2_MODE_STORE && ((uintptr_t)o.y & 15) == 0) {
+                    e = gemm(o.w, o.y, ld);
+                } else {
+                    e = gemm(o.w, tmp_a_, n_out);
+                    if (e == cudaSuccess) e = launch_rows_op(o.y, ld, tmp_a_, n_out, (uint32_t)n_out, rows, o.mode == B2_MODE_ADD, st);
+                    count++;
+                }
+                if (overlaps_f(o.y, n_out, x16_src, x16_k)) x16_src = nullptr;
+                break;
+            }
+            case B2_OP_QK_ROPE:
+                e = launch_qk_rope_rows(o.x, o.y, ld, rows, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_, o.rope, st);
+                count++;
+                if (overlaps_f(o.y, (size_t)o.rope.nh * o.rope.hd, x16_src, x16_k)) x16_src = nullptr;
+                break;
+            case B2_OP_ATTEND:
+                if (loop_attend_) {
+                    for (size_t tk = 0; tk < t && e == cudaSuccess; tk++, count++)
+                        e = launch_attend(o.x + tk * ld, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y + tk * ld, part_, att_counters_, sp_multi_ + 4 * tk, o.attn,
+                                          XPlanes{}, status_, st, false, nullptr);
+                } else {
+                    e = launch_attend_rows(o.x, o.y, ld, rows, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, sp_, o.attn, st);
+                    count++;
+                }
+                if (overlaps_f(o.y, (size_t)o.attn.nh * o.attn.hd, x16_src, x16_k)) x16_src = nullptr;
+                break;
+            case B2_OP_GLU:
+                if (o.n % 4 == 0 && (((uintptr_t)o.x | (uintptr_t)o.y | (uintptr_t)o.z) & 15) == 0) {
+                    e = launch_glu_rows(o.x, ld, o.z, ld, o.y, ld, o.n, rows, o.gelu, st);
+                    count++;
+                } else {
+                    for (size_t tk = 0; tk < t && e == cudaSuccess; tk++, count++)
+                        e = launch_glu(o.x + tk * ld, o.z + tk * ld, o.y + tk * ld, o.n, o.gelu, st, false);
+                }
+                if (overlaps_f(o.y, o.n, x16_src, x16_k)) x16_src = nullptr;
+                break;
+            default: e = cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) {
+            if (err.empty()) err = fmt("[b200qmm: prefill: op %zu (kind %u) for %zu tokens: %s]", i, o.kind, t, cudaGetErrorString(e));
+            rc = B2_ERR_CUDA;
+        }
+    }
+    if (rc != B2_OK && build) {  // a half-made list must not be found again
+        for (GemmPlan* gp : plans) gemm_tc_plan_destroy(gp);
+        gemm_plans_.erase(t);
+    }
+    prefill_launches_ = count;
+    return rc;
+}
+
+int DecodePlanImpl::step_prefill(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, std::string& err) {
+    if (!x || (cs_stride_ && !rope_cs) || !hidden) {
+        err = "[b200qmm: plan step: x, rope_cs and hidden are required]";
+        return B2_ERR_ARG;
+    }
+    if (t == 0 || t > (size_t)tokens_ || pos + t > max_len_) {
+        err = fmt("[b200qmm: plan step: %zu tokens from position %zu: the plan takes %d per step and its caches hold %u positions]", t, pos, tokens_,
+                  max_len_);
+        return B2_ERR_ARG;
+    }
+    err.clear();
+    PLAN_CUDA(launch_set_step(sp_, (uint32_t)pos, (uint32_t)pos, 0, nullptr, 0, st), "set_step");
+    if (loop_attend_) {
+        std::vector<uint32_t> words(4 * t, 0u);
+        for (size_t tk = 0; tk < t; tk++) {
+            words[4 * tk] = (uint32_t)(pos + tk);
+            words[4 * tk + 1] = (uint32_t)pos;
+        }
+        PLAN_CUDA(cudaMemcpyAsync(sp_multi_, words.data(), 16 * t, cudaMemcpyHostToDevice, st), "cudaMemcpy(step words)");
+        PLAN_CUDA(cudaStreamSynchronize(st), "step words");
+    }
+    PLAN_CUDA(cudaMemcpy2DAsync(input_, block_floats_ * 4, x, (size_t)n_input_ * 4, (size_t)n_input_ * 4, t, cudaMemcpyHostToDevice, st),
+              "cudaMemcpy(x)");
+    for (size_t i = 0; i + 1 < cs_off_.size(); i++) {
+        const size_t row = (size_t)(cs_off_[i + 1] - cs_off_[i]) * 4;
+        if (row == 0) continue;
+        PLAN_CUDA(cudaMemcpy2DAsync(rope_table_ + cs_off_[i], (size_t)cs_stride_ * 4, rope_cs + t * cs_off_[i], row, row, t, cudaMemcpyHostToDevice, st),
+                  "cudaMemcpy(rope)");
+    }
+    PLAN_CUDA(cudaEventRecord(ev0_, st), "cudaEventRecord");
+    int rc = run_prefill(st, t, err);
+    if (rc) {
+        cudaStreamSynchronize(st);
+        return rc;
+    }
+    PLAN_CUDA(cudaEventRecord(ev1_, st), "cudaEventRecord");
+    PLAN_CUDA(cudaMemcpy2DAsync(hidden, (size_t)n_hidden_ * 4, hidden_, block_floats_ * 4, (size_t)n_hidden_ * 4, t, cudaMemcpyDeviceToHost, st),
+              "cudaMemcpy(hidden)");
+    PLAN_CUDA(cudaStreamSynchronize(st), "step");
+    PLAN_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_), "cudaEventElapsedTime");
+    GemmStatus gs{};
+    PLAN_CUDA(cudaMemcpy(&gs, gemm_status_, sizeof gs, cudaMemcpyDeviceToHost), "cudaMemcpy(GEMM status)");
+    if (gs.code) {
+        cudaMemset(gemm_status_, 0, sizeof gs);
+        err = fmt("[b200qmm: prefill: a GEMM's bounded wait %u gave up in CTA %u]", gs.where, gs.cta);
+        return B2_ERR_TIMEOUT;
+    }
     return check_status(err);
 }
 

@@ -2,6 +2,7 @@
 // with the KV caches it owns. The role of CudaPlan in the reference (src/cuda_decode.rs:1233-1658).
 #pragma once
 #include <functional>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -17,8 +18,11 @@ class DecodePlanImpl {
     // `planes`: how many planes of the activation split the plan's products read (2: the upper two, 16 bits; otherwise all three, 21 bits).
     // `tokens` (1..4): the most tokens of a step (Backend::decode_plan_multi, src/gpu.rs:273-276). A plan of several tokens keeps
     // one activation block, planes block and block of norm sums per token.
+    // `prefill`: a prefill plan (Backend::decode_plan_prefill, src/gpu.rs:283-289): steps of up to `tokens` (1..8192) tokens on
+    // batched kernels (tensor-core GEMMs for the products, tensor-core causal attention), whose results differ from one-token
+    // steps in rounding. Such a plan takes no logits (the reference's prefill graph ends at the final norm).
     static int create(const b2_graph* g, const std::function<const WeightDev*(uint64_t)>& resolve, int sm_count, int planes, int tokens,
-                      DecodePlanImpl** out, std::string& err);
+                      bool prefill, DecodePlanImpl** out, std::string& err);
     ~DecodePlanImpl();
 
     int step(cudaStream_t st, size_t pos, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err);
@@ -27,6 +31,8 @@ class DecodePlanImpl {
     // for each RoPE table in turn, t rows of cos then sin. Every token's results equal those of t one-token steps bit for bit.
     int step_multi(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, float* logits, std::string& err);
     int tokens() const { return tokens_; }
+    bool is_prefill() const { return prefill_; }
+    float last_step_ms() const { return last_ms_; }  // device time of the last prefill step's kernels (without the copies)
     int kv_write(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, const float* k, const float* v, std::string& err);
     int kv_read(cudaStream_t st, uint32_t kv, size_t pos0, size_t n, float* k, float* v, std::string& err);
     int generate(cudaStream_t st, uint64_t embed_handle, const WeightDev& embed, int32_t first_token, size_t pos0, size_t n_tokens,
@@ -34,7 +40,7 @@ class DecodePlanImpl {
     int export_handle(void* out128, std::string& err);
     int attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err);
     uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
-    uint64_t launches_per_step(size_t t) const { return t >= 2 && t <= 4 ? multi_launches_[t] : (uint64_t)ops_.size(); }
+    uint64_t launches_per_step(size_t t) const { return prefill_ ? prefill_launches_ : t >= 2 && t <= 4 ? multi_launches_[t] : (uint64_t)ops_.size(); }
     bool uses_weight(uint64_t h) const;
 
   private:
@@ -62,6 +68,8 @@ class DecodePlanImpl {
     DecodePlanImpl() = default;
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
     int run_ops_multi(cudaStream_t st, int nt, std::string& err, bool chained);
+    int run_prefill(cudaStream_t st, size_t t, std::string& err);
+    int step_prefill(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, std::string& err);
     int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err, int nt = 1);
     int check_status(std::string& err);
 
@@ -73,6 +81,16 @@ class DecodePlanImpl {
     std::vector<uint32_t> cs_off_;        // start of each RoPE table's values inside a row of the device table
     cudaGraphExec_t multi_exec_[5] = {};  // [nt], nt = 2 .. tokens
     uint64_t multi_launches_[5] = {};     // kernels of a step of nt tokens
+    // prefill plans
+    bool prefill_ = false;
+    bool loop_attend_ = false;       // B2_PREFILL_ATTEND=loop: the one-token attention kernel token by token (for comparisons)
+    void* x16_ = nullptr;            // [tokens][largest n_in] f16: a product's activations
+    float* unscale_ = nullptr;       // [tokens] what the conversion to f16 multiplied each row by, inverted
+    float *tmp_a_ = nullptr, *tmp_b_ = nullptr;  // [tokens][largest n_out] products that are added or paired afterwards
+    GemmStatus* gemm_status_ = nullptr;
+    std::map<size_t, std::vector<GemmPlan*>> gemm_plans_;  // per token count: the products' tensor maps, in op order
+    uint64_t prefill_launches_ = 0;
+    float last_ms_ = 0.0f;
     std::vector<uint64_t> weight_handles_;
     int sm_count_ = 148;
     bool pdl_ = true;  // programmatic dependent launch between the kernels of a step (B2_PLAN_PDL=0 switches it off)

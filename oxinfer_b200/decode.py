@@ -156,6 +156,12 @@ class DecodePlan:
                                                        logits.ctypes.data if logits is not None else None))
         return hidden, logits
 
+    def last_step_ms(self) -> float:
+        """Device milliseconds of the kernels of the last prefill step (without the host copies)."""
+        ms = C.c_float()
+        self._be._check(self._be._L.b2_plan_last_step_ms(self._be._ctx, self.handle, C.byref(ms)))
+        return ms.value
+
     def kv_write(self, kv: int, pos0: int, k: np.ndarray, v: np.ndarray) -> None:
         """Rows ``[n][n_kv][hd]`` f32 in the host cache's order into positions ``pos0 ..``."""
         k = np.ascontiguousarray(k, dtype=np.float32)
@@ -183,7 +189,7 @@ class DecodePlan:
         return out, ms.value
 
 
-def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False, tokens: int = 1) -> DecodePlan | None:
+def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False, tokens: int = 1, prefill: bool = False) -> DecodePlan | None:
     """``Backend::decode_plan`` (``src/gpu.rs:262-289``): a plan, or ``None`` when the graph is declined. ``tokens`` > 1:
     ``Backend::decode_plan_multi`` (``src/gpu.rs:273-276``), steps of up to that many tokens."""
     bufs = (C.c_uint64 * len(g.bufs))(*g.bufs)
@@ -196,8 +202,12 @@ def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False, tokens: int = 
                           n_hidden=g.n_hidden, logits=lv.c(), n_logits=ln, kv_nkv=nkv, kv_hd=hd, n_kv=len(g.kv), rope_halves=halves,
                           n_rope=len(g.rope_halves), max_len=max_len, kv_f16=int(kv_f16))
     h = C.c_uint64()
-    rc = be._L.b2_decode_plan(be._ctx, C.byref(desc), C.byref(h)) if tokens == 1 else \
-        be._L.b2_decode_plan_multi(be._ctx, C.byref(desc), tokens, C.byref(h))
+    if prefill:
+        rc = be._L.b2_decode_plan_prefill(be._ctx, C.byref(desc), tokens, C.byref(h))
+    elif tokens == 1:
+        rc = be._L.b2_decode_plan(be._ctx, C.byref(desc), C.byref(h))
+    else:
+        rc = be._L.b2_decode_plan_multi(be._ctx, C.byref(desc), tokens, C.byref(h))
     if not be._check(rc):
         return None
     return DecodePlan(be, h.value, g, max_len)
@@ -206,6 +216,12 @@ def decode_plan(be, g: Graph, max_len: int, kv_f16: bool = False, tokens: int = 
 def decode_plan_multi(be, g: Graph, max_len: int, tokens: int, kv_f16: bool = False) -> DecodePlan | None:
     """``Backend::decode_plan_multi`` (``src/gpu.rs:273-276``); also what ``decode_plan_multi_fast`` gives (the exact plan)."""
     return decode_plan(be, g, max_len, kv_f16=kv_f16, tokens=tokens)
+
+
+def decode_plan_prefill(be, g: Graph, max_len: int, tokens: int, kv_f16: bool = False) -> DecodePlan | None:
+    """``Backend::decode_plan_prefill`` (``src/gpu.rs:283-289``): steps of up to ``tokens`` tokens on batched kernels; the graph
+    has no head. Steps go through ``DecodePlan.step_multi``."""
+    return decode_plan(be, g, max_len, kv_f16=kv_f16, tokens=tokens, prefill=True)
 
 
 # ---- RoPE tables (src/kernels.rs:2277-2306) ---------------------------------------------------------
@@ -242,7 +258,7 @@ class LlamaConfig:
         return float(np.float32(1.0) / np.sqrt(np.float32(self.hd)))
 
 
-def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, rank: int = 0, world: int = 1) -> Graph:
+def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, rank: int = 0, world: int = 1, prefill: bool = False) -> Graph:
     """``layers``: per layer a dict with device weights ``q k v o gate up down`` and f32 arrays ``ln_pre ln_post``.
     Ten ops per layer (norm, q, k, v, qk-rope, attend, o, norm, gate+up pair, down), then the final norm and the head.
 
@@ -250,7 +266,9 @@ def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, ra
     (``shard_rows``: q / k / v by head, o / gate / up / down / head by equal row ranges), activations are replicated,
     and an exchange follows every sharded product whose output the next op needs in full (attention outputs, both
     residual updates, the MLP activations, the logits). Every output row is computed by the same kernel over the
-    same inputs as on one GPU, so the results are bit-identical to the single-GPU plan."""
+    same inputs as on one GPU, so the results are bit-identical to the single-GPU plan.
+
+    ``prefill``: the graph of a prefill plan, which ends at the final norm (no head, no logits: ``src/model_gpu.rs:398-400``)."""
     g = Graph()
     h, hd = cfg.h, cfg.hd
     assert cfg.nh % world == 0 and cfg.nkv % world == 0 and h % (32 * world) == 0 and cfg.inter % (32 * world) == 0 and cfg.vocab % (32 * world) == 0
@@ -264,7 +282,7 @@ def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, ra
     act = g.buf(cfg.inter)
     act2 = g.buf(cfg.inter)
     hidden = g.buf(h)
-    logits = g.buf(cfg.vocab)
+    logits = g.buf(1 if prefill else cfg.vocab)   # a prefill graph has no head (src/model_gpu.rs:77)
     g.input, g.n_input = x, h
     g.hidden, g.n_hidden = hidden, h
     g.rope_halves = [hd // 2]
@@ -296,6 +314,8 @@ def llama_graph(cfg: LlamaConfig, layers: list, final_norm: np.ndarray, head, ra
         if world > 1:
             g.exchange(x, h)
     g.norm(x, hidden, final_norm, h, cfg.eps)
+    if prefill:
+        return g
     g.linear(head, hidden, logits.at(rank * vs))
     if world > 1:
         g.exchange(logits, cfg.vocab)
