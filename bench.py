@@ -852,6 +852,62 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     return out
 
 
+def prefill_extras(be, peaks, n_layers=32, tokens=2048, kv_f16=False):
+    """Prefill of the config-2 model (Backend::decode_plan_prefill): `tokens` tokens per step from an empty cache, through
+    b2_plan_step_multi with host buffers (embeddings and RoPE rows in, final-normed hidden states out). The device time is
+    the step's kernels between the copies (CUDA events inside the call); the end-to-end time is the host clock around it."""
+    import numpy as np
+
+    from oxinfer_b200 import decode as D
+    from oxinfer_b200 import synth
+
+    cfg = dict(n_layers=n_layers, h=4096, nh=32, nkv=8, hd=128, inter=14336, vocab=128256)
+    layers, final_norm, head, embed, shapes = synth.llama_weights(seed=0xB2000020, same_layers=True, **cfg)
+    dev_layers = []
+    for L in layers:
+        d = {name: be.upload(L[name], *shapes[name]) for name in shapes}
+        d["ln_pre"], d["ln_post"] = L["ln_pre"], L["ln_post"]
+        dev_layers.append(d)
+    dhead = be.upload(head, cfg["vocab"], cfg["h"])
+    lc = D.LlamaConfig(eps=1e-5, rope_theta=500000.0, rope_interleaved=True, **cfg)
+    inv_freq = D.rope_inv_freq(cfg["hd"], lc.rope_theta)
+    pt = tokens
+    pre = D.decode_plan_prefill(be, D.llama_graph(lc, dev_layers, final_norm, dhead, prefill=True), pt + 64, pt, kv_f16=kv_f16)
+    if pre is None:
+        raise RuntimeError("prefill plan declined: " + be.last_declined)
+    one = D.decode_plan(be, D.llama_graph(lc, dev_layers, final_norm, dhead), 64, kv_f16=kv_f16)
+    xs = np.random.default_rng(13).standard_normal((pt, cfg["h"])).astype(np.float32)
+    ptab = np.stack([D.rope_table(i, inv_freq) for i in range(pt)])
+    # parity first: 48 tokens through the prefill plan and through one-token steps of the decode plan
+    nchk = min(48, pt)
+    hp, _ = pre.step_multi(0, xs[:nchk], ptab[:nchk])
+    h1 = np.stack([one.step(i, xs[i], ptab[i], want_logits=False)[0] for i in range(nchk)])
+    one.close()
+    perr = float(np.max(np.max(np.abs(hp.astype(np.float64) - h1), axis=1) / np.maximum(np.max(np.abs(h1), axis=1), 1e-30)))
+    res = {"tokens": pt, "layers": n_layers,
+           "parity": f"{nchk} tokens: final hidden states within {perr:.2e} of one-token steps (row_err; bound 2e-3 per layer of depth)"}
+    params = sum(shapes[name][0] * shapes[name][1] for name in shapes) * n_layers
+    for t in sorted({pt, min(pt, 512), min(pt, 128)}, reverse=True):
+        pre.step_multi(0, xs[:t], ptab[:t])
+        dev, wall = [], []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            pre.step_multi(0, xs[:t], ptab[:t])
+            wall.append(time.perf_counter() - t0)
+            dev.append(pre.last_step_ms())
+        dms, wms = sorted(dev)[1], sorted(wall)[1] * 1e3
+        att = n_layers * cfg["nh"] * cfg["hd"] * 4 * (t * (t + 1) // 2)
+        res[f"t{t}"] = {"device_ms": dms, "tok_s": t / (dms * 1e-3), "e2e_ms": wms, "e2e_tok_s": t / (wms * 1e-3),
+                        "tflops": (2.0 * params * t + att) / (dms * 1e-3) / 1e12,
+                        "frac_of_bf16_sustained_peak": (2.0 * params * t + att) / (dms * 1e-3) / 1e12 / (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]),
+                        "flop_products": 2.0 * params * t, "flop_attention": float(att), "launches": pre.launches_per_step()}
+    res["call"] = "b2_plan_step_multi on a b2_decode_plan_prefill plan: x [t][h] and RoPE rows from the host, hidden [t][h] back"
+    res["h2d_bytes_per_step"] = int(4 * pt * (cfg["h"] + ptab.shape[1]))
+    res["d2h_bytes_per_step"] = int(4 * pt * cfg["h"])
+    pre.close()
+    return res
+
+
 def run_b200(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -879,6 +935,9 @@ def run_b200(args, rank, world, local_rank):
         return
     if args.section == "refcuda":
         emit(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}))
+        return
+    if args.section == "prefill":
+        emit(json.dumps({"extra": {"prefill_plan": prefill_extras(be, peaks, args.layers, min(args.tokens, 8192) if args.tokens != 256 else 2048, args.kv_f16)}}))
         return
     if args.section == "decode":
         d = decode_extras(be, peaks, args.tokens, args.context, args.layers, args.kv_f16, rank=rank, world=world, dist=dist if world > 1 else None,
@@ -1097,6 +1156,7 @@ def run_b200(args, rank, world, local_rank):
             line["extra"] = {}
             for name, fn in (("gemv", lambda: gemv_extras(be, torch, peaks, 40)), ("moe", lambda: moe_extras(be, torch, peaks)),
                              ("fp8", lambda: fp8_extras(be, torch, peaks)), ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2, e2e_tokens=32)),
+                             ("prefill_plan", lambda: prefill_extras(be, peaks)),
                              ("reference_cuda", lambda: ref_cuda_extras(be, torch))):
                 try:
                     line["extra"][name] = fn()
@@ -1131,6 +1191,13 @@ def summarize(line: dict) -> dict:
             out["decode_e2e_tok_s"] = round(d["e2e"]["value"], 1)
         if "parity" in d:
             out["decode_parity"] = d["parity"]
+    pf = ex.get("prefill_plan") or {}
+    if "t2048" in pf:
+        out["prefill_2048_tok_s"] = round(pf["t2048"]["tok_s"], 0)
+        out["prefill_2048_e2e_tok_s"] = round(pf["t2048"]["e2e_tok_s"], 0)
+    mt = (d.get("multi_token_steps") or {}).get("t4")
+    if mt:
+        out["verify_4_tokens_ms"] = round(mt["ms_per_step"], 2)
     m = ex.get("moe") or {}
     for k in ("t1", "t64", "t512", "t4096"):
         if k in m:
@@ -1184,7 +1251,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")
     ap.add_argument("--tokens", type=int, default=256, help="with --section decode: tokens to generate")
     ap.add_argument("--kv-f16", action="store_true", help="with --section decode: f16 KV caches instead of the reference's f32")
-    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "moe", "fp8", "refcuda"],
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "prefill", "moe", "fp8", "refcuda"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

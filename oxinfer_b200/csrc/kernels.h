@@ -294,9 +294,11 @@ cudaError_t launch_qk_rope_rows(const float* qkv, float* qo, size_t stride, uint
                                 const float* kn, const float* cs_table, const uint32_t* sp, const DecRope& p, cudaStream_t st);
 bool attend_rows_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
 // Causal attention of `rows` query tokens over the cache (which already holds their keys and values): tensor-core products
-// over f16 roundings of q, k, v and the probabilities, f32 sums.
-cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16,
-                               const uint32_t* sp, const DecAttn& p, cudaStream_t st);
+// over f16 roundings of q, k, v and the probabilities, f32 sums. `len`: positions the cache holds now (sp[0] + rows, as the
+// host knows it). f32 caches: `scratch` (attend_rows_scratch_bytes) receives an f16 copy of those rows first.
+size_t attend_rows_scratch_bytes(uint32_t nkv, uint32_t max_len, uint32_t hd, int kv_f16);
+cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16, void* scratch,
+                               uint32_t len, const uint32_t* sp, const DecAttn& p, cudaStream_t st);
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
                             uint32_t rows, int gelu, cudaStream_t st);
 // dst[r][i] (+)= src[r][i] for i < n (a multiple of 4; 16-byte aligned rows).

@@ -106,7 +106,7 @@ DecodePlanImpl::~DecodePlanImpl() {
     for (void* m : peer_maps_) cudaIpcCloseMemHandle(m);
     for (auto& kv : gemm_plans_)
         for (GemmPlan* gp : kv.second) gemm_tc_plan_destroy(gp);
-    void* frees[] = {x16_, unscale_, tmp_a_, tmp_b_, gemm_status_, norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
+    void* frees[] = {kv16_, x16_, unscale_, tmp_a_, tmp_b_, gemm_status_, norm_partials_, xflags_, bufs_, planes_, consts_, part_, words_, rope_table_, argmax_val_, argmax_idx_, token_, out_tokens_, stage_};
     for (void* p : frees)
         if (p) cudaFree(p);
 }
@@ -621,6 +621,9 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
         PLAN_CUDA(cudaMalloc((void**)&p->unscale_, T * sizeof(float)), "cudaMalloc(row factors)");
         PLAN_CUDA(cudaMalloc((void**)&p->tmp_a_, T * max_n * sizeof(float)), "cudaMalloc(products)");
         PLAN_CUDA(cudaMalloc((void**)&p->tmp_b_, T * max_n * sizeof(float)), "cudaMalloc(products)");
+        size_t kv16 = 0;
+        for (const Kv& k : p->kv_) kv16 = std::max(kv16, attend_rows_scratch_bytes(k.nkv, g->max_len, k.hd, p->kv_f16_));
+        if (kv16) PLAN_CUDA(cudaMalloc(&p->kv16_, kv16), "cudaMalloc(f16 cache rows)");
         PLAN_CUDA(cudaMalloc((void**)&p->gemm_status_, sizeof(GemmStatus)), "cudaMalloc(GEMM status)");
         PLAN_CUDA(cudaMemset(p->gemm_status_, 0, sizeof(GemmStatus)), "cudaMemset(GEMM status)");
         *out = p.release();  // nothing is captured: a step launches its kernels (a few per op, whatever the token count)
@@ -913,7 +916,7 @@ int DecodePlanImpl::step_multi(cudaStream_t st, size_t pos, size_t t, const floa
 // A prefill step's kernels for t token rows. A product = the rows to f16 (each multiplied by a power of two, taken out again
 // by the GEMM's epilogue), then the tensor-core GEMM: straight into the activation rows where it stores, into a scratch
 // matrix where it adds to the rows (a row-wise add follows) or is one of a gate / up pair (the activation kernel follows).
-int DecodePlanImpl::run_prefill(cudaStream_t st, size_t t, std::string& err) {
+int DecodePlanImpl::run_prefill(cudaStream_t st, size_t pos, size_t t, std::string& err) {
     std::vector<GemmPlan*>& plans = gemm_plans_[t];
     const bool build = plans.empty();
     size_t slot = 0;
@@ -993,8 +996,8 @@ int DecodePlanImpl::run_prefill(cudaStream_t st, size_t t, std::string& err) {
                         e = launch_attend(o.x + tk * ld, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y + tk * ld, part_, att_counters_, sp_multi_ + 4 * tk, o.attn,
                                           XPlanes{}, status_, st, false, nullptr);
                 } else {
-                    e = launch_attend_rows(o.x, o.y, ld, rows, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, sp_, o.attn, st);
-                    count++;
+                    e = launch_attend_rows(o.x, o.y, ld, rows, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, kv16_, (uint32_t)(pos + t), sp_, o.attn, st);
+                    count += kv_f16_ ? 1 : 3;
                 }
                 if (overlaps_f(o.y, (size_t)o.attn.nh * o.attn.hd, x16_src, x16_k)) x16_src = nullptr;
                 break;
@@ -1053,7 +1056,7 @@ int DecodePlanImpl::step_prefill(cudaStream_t st, size_t pos, size_t t, const fl
                   "cudaMemcpy(rope)");
     }
     PLAN_CUDA(cudaEventRecord(ev0_, st), "cudaEventRecord");
-    int rc = run_prefill(st, t, err);
+    int rc = run_prefill(st, pos, t, err);
     if (rc) {
         cudaStreamSynchronize(st);
         return rc;

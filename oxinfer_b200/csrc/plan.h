@@ -39,7 +39,7 @@ class DecodePlanImpl {
                  const float* rope_cs_table, int32_t* out_tokens, float* elapsed_ms, std::string& err);
     int export_handle(void* out128, std::string& err);
     int attach_peers(uint32_t rank, uint32_t world, const void* handles, std::string& err);
-    uint64_t launches_per_step() const { return (uint64_t)ops_.size(); }
+    uint64_t launches_per_step() const { return prefill_ ? prefill_launches_ : (uint64_t)ops_.size(); }
     uint64_t launches_per_step(size_t t) const { return prefill_ ? prefill_launches_ : t >= 2 && t <= 4 ? multi_launches_[t] : (uint64_t)ops_.size(); }
     bool uses_weight(uint64_t h) const;
 
@@ -68,7 +68,7 @@ class DecodePlanImpl {
     DecodePlanImpl() = default;
     int run_ops(cudaStream_t st, std::string& err, bool chained, bool first_chained);
     int run_ops_multi(cudaStream_t st, int nt, std::string& err, bool chained);
-    int run_prefill(cudaStream_t st, size_t t, std::string& err);
+    int run_prefill(cudaStream_t st, size_t pos, size_t t, std::string& err);
     int step_prefill(cudaStream_t st, size_t pos, size_t t, const float* x, const float* rope_cs, float* hidden, std::string& err);
     int capture(cudaStream_t st, bool with_head, cudaGraphExec_t* out, std::string& err, int nt = 1);
     int check_status(std::string& err);
@@ -88,6 +88,7 @@ class DecodePlanImpl {
     float* unscale_ = nullptr;       // [tokens] what the conversion to f16 multiplied each row by, inverted
     float *tmp_a_ = nullptr, *tmp_b_ = nullptr;  // [tokens][largest n_out] products that are added or paired afterwards
     GemmStatus* gemm_status_ = nullptr;
+    void* kv16_ = nullptr;           // f16 copy of one f32 cache's rows for the attention kernel
     std::map<size_t, std::vector<GemmPlan*>> gemm_plans_;  // per token count: the products' tensor maps, in op order
     uint64_t prefill_launches_ = 0;
     float last_ms_ = 0.0f;

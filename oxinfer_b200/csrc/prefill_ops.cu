@@ -3,12 +3,13 @@
 // kept on the device for the whole step"). Token row r of every activation sits `stride` floats behind row r - 1.
 //
 //   qk_rope_rows : per-head q / k norm, RoPE and cache append of every token (rope_head, the one-token arithmetic)
-//   attend_rows  : causal attention of a tile of 64 query tokens of one head over the cache, keys in tiles of 64:
-//                  S = Q K^T and O += P V on mma.sync m16n8k16 (f16 operands, f32 accumulators), softmax running in f32
-//                  registers. The reference's prefill attention is its f32 CPU kernel (attention_ext,
-//                  src/model.rs:2214-2309) or attention_cached on the device; this one rounds q, k, v and the
-//                  probabilities to f16, which the parity bound of the prefill plan covers.
-//   glu_rows, rows_add / rows_copy : the element-wise ops
+//   attend_rows  : causal attention of a tile of 64 query tokens of one or two query heads (of one KV head) over the cache,
+//                  keys in tiles of 64 brought in by cp.async two stages deep: S = Q K^T and O += P V on mma.sync m16n8k16
+//                  (f16 operands, f32 accumulators), softmax running in f32 registers. An f32 cache is first copied to f16.
+//                  The reference's prefill attention is its f32 CPU kernel (attention_ext, src/model.rs:2214-2309) or
+//                  attention_cached on the device; this one rounds q, k, v and the probabilities to f16, which the parity
+//                  bound of the prefill plan covers.
+//   glu_rows, rows_op : the element-wise ops
 #include <cuda_fp16.h>
 
 #include "attend_core.cuh"
@@ -69,7 +70,6 @@ __global__ void __launch_bounds__(256) rows_op_kernel(float* __restrict__ dst, s
 
 // ---- attention over many query tokens ------------------------------------------------------------------------------
 constexpr int PF_TILE = 64;      // query tokens per CTA, and keys per shared-memory tile
-constexpr int PF_THREADS = 128;  // four warps of 16 query rows
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -88,86 +88,123 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *(const uint32_t*)&h;
 }
-__device__ __forceinline__ uint2 to_h4(float4 v) { return make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w)); }
-__device__ __forceinline__ uint2 row4_as_half(const float* p) { return to_h4(*(const float4*)p); }
-__device__ __forceinline__ uint2 row4_as_half(const __half* p) { return *(const uint2*)p; }
+// 16 bytes global -> shared without passing through registers; `bytes` 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, uint32_t bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int HD>
-__host__ __device__ constexpr size_t attend_rows_smem() {
-    return (size_t)3 * PF_TILE * (HD + 8) * 2;
+// f32 cache rows [0, len) of every KV head -> an f16 copy with the same layout ([nkv][max_len][hd]).
+__global__ void __launch_bounds__(256) kv_rows_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst, uint32_t max_len, uint32_t len,
+                                                             uint32_t hd4) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;  // a group of 4 values of the head's first `len` rows
+    if (i >= len * hd4) return;
+    const size_t at = ((size_t)blockIdx.y * max_len * hd4 + i) * 4;
+    const float4 v = *(const float4*)(src + at);
+    *(uint2*)(dst + at) = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
 }
 
-// Grid (query tiles, heads). Token row r (position sp[0] + r) attends to the keys 0 .. sp[0] + r of its KV head's cache
-// (the keys of this step's tokens were appended by the RoPE kernel ahead), or to the last `window` of them.
-template <int HD, typename T>
-__global__ void __launch_bounds__(PF_THREADS) attend_rows_kernel(const float* __restrict__ q, float* __restrict__ out, size_t stride,
-                                                                 const T* __restrict__ kc, const T* __restrict__ vc,
-                                                                 const uint32_t* __restrict__ sp, DecAttn p, uint32_t rows) {
+template <int HD, int HEADS>
+__host__ __device__ constexpr size_t attend_rows_smem() {
+    return (size_t)(HEADS + 4) * PF_TILE * (HD + 8) * 2;  // the queries of HEADS heads, two stages of a key and a value tile
+}
+
+// Grid (query tiles, heads / HEADS). A CTA takes 64 query tokens of HEADS query heads that share a KV head (warp w: head
+// w / 4, rows 16 (w % 4) ..); token row r (position sp[0] + r) attends to the keys 0 .. sp[0] + r of the cache (the keys of
+// this step's tokens were appended by the RoPE kernel ahead), or to the last `window` of them. kc / vc: f16 rows. The key
+// and value tiles arrive by cp.async, the next tile's copies in flight while the current one is multiplied.
+template <int HD, int HEADS>
+__global__ void __launch_bounds__(HEADS * 128) attend_rows_kernel(const float* __restrict__ q, float* __restrict__ out, size_t stride,
+                                                                  const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                                  const uint32_t* __restrict__ sp, DecAttn p, uint32_t rows) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int P = HD + 8;  // halves per shared-memory row: rows 16 bytes apart modulo 128, so ldmatrix reads without conflicts
-    __half* Qs = (__half*)smem;
-    __half* Ks = Qs + PF_TILE * P;
-    __half* Vs = Ks + PF_TILE * P;
+    constexpr int THREADS = HEADS * 128;
+    __half* Qs = (__half*)smem;                 // [HEADS][64][P]
+    __half* KV = Qs + HEADS * PF_TILE * P;      // [stage][K | V][64][P]
     const uint32_t pos0 = sp[0];
     const uint32_t qt = gridDim.x - 1 - blockIdx.x;  // the tiles with the most keys first
-    const uint32_t head = blockIdx.y, kvh = head / (p.nh / p.nkv);
+    const uint32_t head0 = blockIdx.y * HEADS, kvh = head0 / (p.nh / p.nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const int wh = warp >> 2, wr = warp & 3;  // the warp's head within the CTA, and its block of 16 query rows
     const uint32_t r0 = qt * PF_TILE;
-    for (int i = tid; i < PF_TILE * (HD / 4); i += PF_THREADS) {
-        const int r = i / (HD / 4), d4 = i % (HD / 4);
+    const uint32_t last_row = min(r0 + PF_TILE, rows) - 1;
+    const uint32_t qp_first = pos0 + r0, qp_last = pos0 + last_row;
+    const uint32_t lo = (p.window != 0 && qp_first + 1 > p.window) ? qp_first + 1 - p.window : 0;
+    const uint32_t tile_first = lo / PF_TILE, tile_last = qp_last / PF_TILE;
+    auto issue = [&](uint32_t tk, int stage) {  // every thread: its share of the 2 x 64 rows of HD halves
+        const uint32_t j0 = tk * PF_TILE;
+        __half* Ks = KV + (size_t)stage * 2 * PF_TILE * P;
+        __half* Vs = Ks + PF_TILE * P;
+        for (int i = tid; i < PF_TILE * (HD / 8); i += THREADS) {
+            const int r = i / (HD / 8), d8 = i % (HD / 8);
+            const bool in = j0 + r <= qp_last;  // rows behind the last query's position: zeros (never a stale NaN under a zero weight)
+            const size_t at = ((size_t)kvh * p.max_len + (in ? j0 + r : 0)) * HD + d8 * 8;
+            cp_async_16(Ks + r * P + d8 * 8, kc + at, in ? 16u : 0u);
+            cp_async_16(Vs + r * P + d8 * 8, vc + at, in ? 16u : 0u);
+        }
+        cp_async_commit();
+    };
+    issue(tile_first, 0);
+    for (int i = tid; i < HEADS * PF_TILE * (HD / 4); i += THREADS) {
+        const int hh = i / (PF_TILE * (HD / 4)), r = (i / (HD / 4)) % PF_TILE, d4 = i % (HD / 4);
         uint2 h = make_uint2(0u, 0u);
-        if (r0 + r < rows) h = row4_as_half(q + (size_t)(r0 + r) * stride + head * HD + d4 * 4);
-        *(uint2*)(Qs + r * P + d4 * 4) = h;
+        if (r0 + r < rows) {
+            const float4 v = *(const float4*)(q + (size_t)(r0 + r) * stride + (head0 + hh) * HD + d4 * 4);
+            h = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
+        }
+        *(uint2*)(Qs + (hh * PF_TILE + r) * P + d4 * 4) = h;
     }
-    __syncthreads();
-    uint32_t qa[HD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ks++) ldsm_x4(qa[ks], Qs + (warp * 16 + (lane & 15)) * P + ks * 16 + (lane >> 4) * 8);
     float o[HD / 8][4];
 #pragma unroll
     for (int nb = 0; nb < HD / 8; nb++) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    const uint32_t last_row = min(r0 + PF_TILE, rows) - 1;
-    const uint32_t qp_first = pos0 + r0, qp_last = pos0 + last_row;
-    const uint32_t lo = (p.window != 0 && qp_first + 1 > p.window) ? qp_first + 1 - p.window : 0;
-    const uint32_t my_qp[2] = {pos0 + r0 + warp * 16 + g, pos0 + r0 + warp * 16 + g + 8};
-    for (uint32_t tk = lo / PF_TILE; tk <= qp_last / PF_TILE; tk++) {
-        const uint32_t j0 = tk * PF_TILE;
-        __syncthreads();  // every warp is done with the previous tile
-        for (int i = tid; i < PF_TILE * (HD / 4); i += PF_THREADS) {
-            const int r = i / (HD / 4), d4 = i % (HD / 4);
-            uint2 kh = make_uint2(0u, 0u), vh = make_uint2(0u, 0u);
-            if (j0 + r <= qp_last) {
-                const size_t at = ((size_t)kvh * p.max_len + j0 + r) * HD + d4 * 4;
-                kh = row4_as_half(kc + at);
-                vh = row4_as_half(vc + at);
-            }
-            *(uint2*)(Ks + r * P + d4 * 4) = kh;
-            *(uint2*)(Vs + r * P + d4 * 4) = vh;
+    const uint32_t my_qp[2] = {pos0 + r0 + wr * 16 + g, pos0 + r0 + wr * 16 + g + 8};
+    const __half* Qw = Qs + (wh * PF_TILE + wr * 16 + (lane & 15)) * P + (lane >> 4) * 8;
+    for (uint32_t tk = tile_first; tk <= tile_last; tk++) {
+        const int stage = (int)((tk - tile_first) & 1);
+        if (tk < tile_last) {
+            issue(tk + 1, stage ^ 1);  // (the barrier at the end of the previous round freed that stage)
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
+        const __half* Ks = KV + (size_t)stage * 2 * PF_TILE * P;
+        const __half* Vs = Ks + PF_TILE * P;
+        const uint32_t j0 = tk * PF_TILE;
         float s[PF_TILE / 8][4];
 #pragma unroll
         for (int nb = 0; nb < PF_TILE / 8; nb++) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t qa[4];
+            ldsm_x4(qa, Qw + ks * 16);
 #pragma unroll
             for (int nb2 = 0; nb2 < PF_TILE / 16; nb2++) {
                 uint32_t b[4];
                 ldsm_x4(b, Ks + (nb2 * 16 + (lane & 7) + 8 * (lane >> 4)) * P + ks * 16 + 8 * ((lane >> 3) & 1));
-                mma_16816(s[2 * nb2], qa[ks], b[0], b[1]);
-                mma_16816(s[2 * nb2 + 1], qa[ks], b[2], b[3]);
+                mma_16816(s[2 * nb2], qa, b[0], b[1]);
+                mma_16816(s[2 * nb2 + 1], qa, b[2], b[3]);
             }
         }
         float mx[2] = {-INFINITY, -INFINITY};
+        // only tiles that reach past the first query's position or start inside the window's edge need the mask
+        const bool masked = j0 + PF_TILE - 1 > qp_first || (p.window != 0 && j0 + p.window <= qp_last);
 #pragma unroll
         for (int nb = 0; nb < PF_TILE / 8; nb++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int row = e >> 1;
-                const uint32_t j = j0 + nb * 8 + 2 * c + (e & 1), qp = my_qp[row];
-                const bool ok = j <= qp && (p.window == 0 || j + p.window > qp);
-                const float v = ok ? s[nb][e] * p.scale : -INFINITY;
+                float v = s[nb][e] * p.scale;
+                if (masked) {
+                    const uint32_t j = j0 + nb * 8 + 2 * c + (e & 1), qp = my_qp[row];
+                    const bool ok = j <= qp && (p.window == 0 || j + p.window > qp);
+                    v = ok ? v : -INFINITY;
+                }
                 s[nb][e] = v;
                 mx[row] = fmaxf(mx[row], v);
             }
@@ -209,26 +246,27 @@ __global__ void __launch_bounds__(PF_THREADS) attend_rows_kernel(const float* __
                 mma_16816(o[2 * nb2 + 1], pa, b[2], b[3]);
             }
         }
+        __syncthreads();  // every warp is done with this stage before the next round's copies land in it
     }
 #pragma unroll
     for (int row = 0; row < 2; row++) {
         l[row] += __shfl_xor_sync(0xffffffffu, l[row], 1);
         l[row] += __shfl_xor_sync(0xffffffffu, l[row], 2);
-        const uint32_t r = r0 + warp * 16 + g + 8 * row;
+        const uint32_t r = r0 + wr * 16 + g + 8 * row;
         if (r >= rows) continue;
         const float inv = l[row] > 0.0f ? 1.0f / l[row] : 0.0f;
-        float* dst = out + (size_t)r * stride + head * HD + 2 * c;
+        float* dst = out + (size_t)r * stride + (head0 + wh) * HD + 2 * c;
 #pragma unroll
         for (int nb = 0; nb < HD / 8; nb++) *(float2*)(dst + nb * 8) = make_float2(o[nb][2 * row] * inv, o[nb][2 * row + 1] * inv);
     }
 }
 
-template <int HD, typename T>
-cudaError_t attend_rows_t(const float* q, float* out, size_t stride, const void* kc, const void* vc, const uint32_t* sp, const DecAttn& p,
+template <int HD, int HEADS>
+cudaError_t attend_rows_t(const float* q, float* out, size_t stride, const __half* kc, const __half* vc, const uint32_t* sp, const DecAttn& p,
                           uint32_t rows, cudaStream_t st) {
-    constexpr size_t smem = attend_rows_smem<HD>();
-    if (cudaError_t e = ensure_dynamic_smem((const void*)attend_rows_kernel<HD, T>, smem); e != cudaSuccess) return e;
-    attend_rows_kernel<HD, T><<<dim3((rows + PF_TILE - 1) / PF_TILE, p.nh), PF_THREADS, smem, st>>>(q, out, stride, (const T*)kc, (const T*)vc, sp, p, rows);
+    constexpr size_t smem = attend_rows_smem<HD, HEADS>();
+    if (cudaError_t e = ensure_dynamic_smem((const void*)attend_rows_kernel<HD, HEADS>, smem); e != cudaSuccess) return e;
+    attend_rows_kernel<HD, HEADS><<<dim3((rows + PF_TILE - 1) / PF_TILE, p.nh / HEADS), HEADS * 128, smem, st>>>(q, out, stride, kc, vc, sp, p, rows);
     return cudaGetLastError();
 }
 
@@ -247,12 +285,29 @@ cudaError_t launch_qk_rope_rows(const float* qkv, float* qo, size_t stride, uint
 
 bool attend_rows_supports(uint32_t nh, uint32_t nkv, uint32_t hd) { return nkv != 0 && nh % nkv == 0 && (hd == 64 || hd == 128); }
 
-cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16,
-                               const uint32_t* sp, const DecAttn& p, cudaStream_t st) {
-    if (!attend_rows_supports(p.nh, p.nkv, p.hd) || rows == 0 || stride % 4 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return cudaErrorInvalidValue;
-    if (p.hd == 64)
-        return kv_f16 ? attend_rows_t<64, __half>(q, out, stride, kc, vc, sp, p, rows, st) : attend_rows_t<64, float>(q, out, stride, kc, vc, sp, p, rows, st);
-    return kv_f16 ? attend_rows_t<128, __half>(q, out, stride, kc, vc, sp, p, rows, st) : attend_rows_t<128, float>(q, out, stride, kc, vc, sp, p, rows, st);
+size_t attend_rows_scratch_bytes(uint32_t nkv, uint32_t max_len, uint32_t hd, int kv_f16) {
+    return kv_f16 ? 0 : (size_t)2 * nkv * max_len * hd * 2;
+}
+
+cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16, void* scratch,
+                               uint32_t len, const uint32_t* sp, const DecAttn& p, cudaStream_t st) {
+    if (!attend_rows_supports(p.nh, p.nkv, p.hd) || rows == 0 || stride % 4 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || len > p.max_len)
+        return cudaErrorInvalidValue;
+    const __half *kh = (const __half*)kc, *vh = (const __half*)vc;
+    if (!kv_f16) {  // an f16 copy of the rows the step reads (the kernel's operands are f16 either way)
+        if (!scratch) return cudaErrorInvalidValue;
+        __half* k16 = (__half*)scratch;
+        __half* v16 = k16 + (size_t)p.nkv * p.max_len * p.hd;
+        const dim3 grid((len * (p.hd / 4) + 255) / 256, p.nkv);
+        kv_rows_to_f16_kernel<<<grid, 256, 0, st>>>((const float*)kc, k16, p.max_len, len, p.hd / 4);
+        kv_rows_to_f16_kernel<<<grid, 256, 0, st>>>((const float*)vc, v16, p.max_len, len, p.hd / 4);
+        if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+        kh = k16;
+        vh = v16;
+    }
+    const bool two = (p.nh / p.nkv) % 2 == 0;  // two query heads of a KV head share a CTA's key and value tiles
+    if (p.hd == 64) return two ? attend_rows_t<64, 2>(q, out, stride, kh, vh, sp, p, rows, st) : attend_rows_t<64, 1>(q, out, stride, kh, vh, sp, p, rows, st);
+    return two ? attend_rows_t<128, 2>(q, out, stride, kh, vh, sp, p, rows, st) : attend_rows_t<128, 1>(q, out, stride, kh, vh, sp, p, rows, st);
 }
 
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
