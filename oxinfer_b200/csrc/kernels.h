@@ -181,6 +181,7 @@ struct GemmPeerY {
     size_t ld = 0;        // row stride of the destinations in elements (0: not a gathered product, the stride is n_out)
     int n_more = 0;       // peers' destinations
     float* more[7] = {};
+    bool accumulate = false;  // the results are added to what y holds (the copy engine's reduce-add; no peers then): y += x W^T
 };
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
                                 size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0, size_t a_lo_row0 = 0, int w_terms = 1, const GemmPeerY* peer_y = nullptr);
@@ -299,6 +300,11 @@ bool attend_rows_supports(uint32_t nh, uint32_t nkv, uint32_t hd);
 size_t attend_rows_scratch_bytes(uint32_t nkv, uint32_t max_len, uint32_t hd, int kv_f16);
 cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32_t rows, const void* kc, const void* vc, int kv_f16, void* scratch,
                                uint32_t len, const uint32_t* sp, const DecAttn& p, cudaStream_t st);
+// RMS norm of `rows` rows (p.n values each, p.pre / p.eps / p.add as for launch_norm; the strides here replace p's). With
+// x16 / unscale the rows also leave as the f16 operands launch_to_f16 would make of the result (rows of p.n halves).
+bool norm_rows_supports(uint32_t n, const float* x, const float* out, const float* w, size_t x_stride, size_t out_stride);
+cudaError_t launch_norm_rows(const float* x, size_t x_stride, float* out, size_t out_stride, const float* w, const DecNorm& p, uint32_t rows,
+                             void* x16, float* unscale, cudaStream_t st);
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
                             uint32_t rows, int gelu, cudaStream_t st);
 // dst[r][i] (+)= src[r][i] for i < n (a multiple of 4; 16-byte aligned rows).

@@ -925,13 +925,14 @@ int DecodePlanImpl::run_prefill(cudaStream_t st, size_t pos, size_t t, std::stri
     const uint32_t rows = (uint32_t)t;
     const float* x16_src = nullptr;  // the vector whose f16 rows the scratch holds
     size_t x16_k = 0;
-    auto gemm = [&](const WeightDev& w, float* y, size_t y_ld) -> cudaError_t {
+    auto gemm = [&](const WeightDev& w, float* y, size_t y_ld, bool accumulate = false) -> cudaError_t {
         GemmPlan* gp = nullptr;
         if (build) {
             char msg[256] = {0};
             GemmPeerY py;
             py.ld = y_ld;
-            cudaError_t e = gemm_tc_plan_create(w, x16_, t, y, B2_F32, &gp, msg, sizeof msg, 1, nullptr, 0, 0, 1, y_ld != w.n_out ? &py : nullptr);
+            py.accumulate = accumulate;
+            cudaError_t e = gemm_tc_plan_create(w, x16_, t, y, B2_F32, &gp, msg, sizeof msg, 1, nullptr, 0, 0, 1, (y_ld != w.n_out || accumulate) ? &py : nullptr);
             if (e != cudaSuccess) {
                 err = fmt("[b200qmm: prefill: %s]", msg);
                 return e;
@@ -950,7 +951,18 @@ int DecodePlanImpl::run_prefill(cudaStream_t st, size_t pos, size_t t, std::stri
         cudaError_t e = cudaSuccess;
         switch (o.kind) {
             case B2_OP_NORM:
-                if (o.rows == 1) {
+                if (o.rows == 1 && norm_rows_supports(o.norm.n, o.x, o.y, o.p0, ld, ld)) {
+                    // a product right behind it that reads exactly this vector gets its f16 rows from the norm kernel
+                    const Op* nx = i + 1 < ops_.size() ? &ops_[i + 1] : nullptr;
+                    const bool feeds = nx && nx->kind == B2_OP_LINEAR && nx->x == o.y && nx->w.n_in == o.norm.n && o.norm.n % 8 == 0;
+                    e = launch_norm_rows(o.x, ld, o.y, ld, o.p0, o.norm, rows, feeds ? x16_ : nullptr, unscale_, st);
+                    count++;
+                    if (feeds) {
+                        x16_src = o.y;
+                        x16_k = o.norm.n;
+                        break;  // (the overlap check below would forget the rows just made)
+                    }
+                } else if (o.rows == 1) {
                     DecNorm n = o.norm;
                     n.x_stride = n.out_stride = (uint32_t)ld;
                     e = launch_norm(o.x, o.y, o.p0, n, rows, XPlanes{}, st, false);
@@ -975,8 +987,8 @@ int DecodePlanImpl::run_prefill(cudaStream_t st, size_t pos, size_t t, std::stri
                     if (e == cudaSuccess) e = gemm(o.w2, tmp_b_, n_out);
                     if (e == cudaSuccess) e = launch_glu_rows(tmp_a_, n_out, tmp_b_, n_out, o.y, ld, (uint32_t)n_out, rows, o.mode == B2_MODE_GELU_PAIR, st);
                     count++;
-                } else if (o.mode == B2_MODE_STORE && ((uintptr_t)o.y & 15) == 0) {
-                    e = gemm(o.w, o.y, ld);
+                } else if ((o.mode == B2_MODE_STORE || o.mode == B2_MODE_ADD) && ((uintptr_t)o.y & 15) == 0) {
+                    e = gemm(o.w, o.y, ld, o.mode == B2_MODE_ADD);  // adds through the copy engine's reduce
                 } else {
                     e = gemm(o.w, tmp_a_, n_out);
                     if (e == cudaSuccess) e = launch_rows_op(o.y, ld, tmp_a_, n_out, (uint32_t)n_out, rows, o.mode == B2_MODE_ADD, st);

@@ -12,6 +12,8 @@
 //   glu_rows, rows_op : the element-wise ops
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "attend_core.cuh"
 
 namespace b2 {
@@ -19,6 +21,11 @@ namespace b2 {
 using namespace attend_core;
 
 namespace {
+
+__device__ __forceinline__ uint32_t pack_h2f(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *(const uint32_t*)&h;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) qk_rope_rows_kernel(const float* __restrict__ qkv, float* __restrict__ qo, size_t stride, T* __restrict__ kc,
@@ -28,6 +35,130 @@ __global__ void __launch_bounds__(256) qk_rope_rows_kernel(const float* __restri
     __shared__ float red[32];
     const size_t off = (size_t)blockIdx.y * stride;
     rope_head<T>(blockIdx.x, threadIdx.x, sp[0] + blockIdx.y, sp[1], qkv + off, qo + off, kc, vc, qn, kn, cs_table, p, buf, red);
+}
+
+// RoPE and cache append without per-head norms: a warp per head of a token, lane l owning dimensions 4 l .. 4 l + 3 (and
+// 128 + 4 l .. for heads of 256). The rotation is rope_head's arithmetic (unfused multiplies and adds), so the rows that
+// reach the caches equal the one-token kernel's bit for bit. hd and half_rot are multiples of 4.
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) { *(float4*)p = v; }
+template <>
+__device__ __forceinline__ void store4<__half>(__half* p, float4 v) {
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *(uint2*)p = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_rope_fast_kernel(const float* __restrict__ qkv, float* __restrict__ qo, size_t stride, uint32_t rows,
+                                                           T* __restrict__ kc, T* __restrict__ vc, const float* __restrict__ cs_table,
+                                                           const uint32_t* __restrict__ sp, DecRope p) {
+    const uint32_t heads = p.nh + 2 * p.nkv;
+    const uint32_t unit = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= rows * heads) return;
+    const uint32_t tok = unit / heads, h = unit - tok * heads;
+    const uint32_t kind = h < p.nh ? 0 : (h < p.nh + p.nkv ? 1 : 2);
+    const uint32_t hh = kind == 0 ? h : (kind == 1 ? h - p.nh : h - p.nh - p.nkv);
+    const uint32_t pos = sp[0] + tok, hd = p.hd, hr = p.half_rot;
+    if (pos >= p.max_len) return;
+    const float* src = qkv + (size_t)tok * stride + (kind == 0 ? hh * p.q_stride : (kind == 1 || p.v_from_k) ? p.k_off + hh * hd : p.v_off + hh * hd);
+    const float* cs = cs_table + (size_t)(pos - sp[1]) * p.cs_stride + p.cs_off;
+    const size_t at = ((size_t)hh * p.max_len + pos) * hd;
+    for (uint32_t d0 = 4 * lane; d0 < hd; d0 += 128) {
+        float4 v = *(const float4*)(src + d0);
+        if (kind != 2 && d0 < 2 * hr) {
+            if (p.interleaved) {  // pairs (2 j, 2 j + 1): both in this lane
+                const uint32_t j = d0 >> 1;
+                const float c0 = cs[j], s0 = cs[hr + j], c1 = cs[j + 1], s1 = cs[hr + j + 1];
+                v = make_float4(__fsub_rn(__fmul_rn(v.x, c0), __fmul_rn(v.y, s0)), __fadd_rn(__fmul_rn(v.y, c0), __fmul_rn(v.x, s0)),
+                                __fsub_rn(__fmul_rn(v.z, c1), __fmul_rn(v.w, s1)), __fadd_rn(__fmul_rn(v.w, c1), __fmul_rn(v.z, s1)));
+            } else {  // pairs (j, j + hr): the partner's four values come from global memory again (L1)
+                const bool first = d0 < hr;
+                const uint32_t j = first ? d0 : d0 - hr;
+                const float4 o = *(const float4*)(src + (first ? d0 + hr : d0 - hr));
+                const float4 c = *(const float4*)(cs + j), s = *(const float4*)(cs + hr + j);
+                if (first)
+                    v = make_float4(__fsub_rn(__fmul_rn(v.x, c.x), __fmul_rn(o.x, s.x)), __fsub_rn(__fmul_rn(v.y, c.y), __fmul_rn(o.y, s.y)),
+                                    __fsub_rn(__fmul_rn(v.z, c.z), __fmul_rn(o.z, s.z)), __fsub_rn(__fmul_rn(v.w, c.w), __fmul_rn(o.w, s.w)));
+                else
+                    v = make_float4(__fadd_rn(__fmul_rn(v.x, c.x), __fmul_rn(o.x, s.x)), __fadd_rn(__fmul_rn(v.y, c.y), __fmul_rn(o.y, s.y)),
+                                    __fadd_rn(__fmul_rn(v.z, c.z), __fmul_rn(o.z, s.z)), __fadd_rn(__fmul_rn(v.w, c.w), __fmul_rn(o.w, s.w)));
+            }
+        }
+        if (kind == 0) *(float4*)(qo + (size_t)tok * stride + hh * hd + d0) = v;
+        else store4<T>((kind == 1 ? kc : vc) + at + d0, v);
+    }
+}
+
+// RMS norm of many rows, one CTA of 256 threads per row, the row in registers between the passes (n <= 8192). With x16 the
+// row also leaves as f16 operands of the GEMM behind it: multiplied by the power of two that brings its largest magnitude
+// into [2^14, 2^15), the inverse factor in unscale[row] (what to_f16_rows_kernel makes of the f32 row).
+constexpr int NORM_ROWS_V = 8;
+__global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict__ x, size_t x_stride, float* __restrict__ out, size_t out_stride,
+                                                        const float* __restrict__ w, uint32_t n, float pre, float eps, int add,
+                                                        __half* __restrict__ x16, float* __restrict__ unscale) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const float4* xr = (const float4*)(x + row * x_stride);
+    float4* o = (float4*)(out + row * out_stride);
+    const uint32_t n4 = n / 4;
+    float4 v[NORM_ROWS_V];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NORM_ROWS_V; j++) {
+        const uint32_t i = threadIdx.x + 256 * j;
+        v[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < n4) {
+            const float4 t = xr[i];
+            v[j] = make_float4(t.x * pre, t.y * pre, t.z * pre, t.w * pre);
+            s += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    const float k = 1.0f / sqrtf(block_sum(s, red) / (float)n + eps);
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NORM_ROWS_V; j++) {
+        const uint32_t i = threadIdx.x + 256 * j;
+        if (i < n4) {
+            float4 t = make_float4(v[j].x * k, v[j].y * k, v[j].z * k, v[j].w * k);
+            if (w) {
+                const float4 ww = ((const float4*)w)[i];
+                t = make_float4(t.x * ww.x, t.y * ww.y, t.z * ww.z, t.w * ww.w);
+            }
+            if (add) {
+                const float4 a = o[i];
+                t = make_float4(t.x + a.x, t.y + a.y, t.z + a.z, t.w + a.w);
+            }
+            o[i] = t;
+            v[j] = t;
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(t.x), fabsf(t.y))), fmaxf(fabsf(t.z), fabsf(t.w)));
+        }
+    }
+    if (!x16) return;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    __syncthreads();  // red is read by every thread in block_sum above
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    float sc = 1.0f, inv = 1.0f;
+    if (mx > 0.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);
+        const int up = min(100, max(-100, 15 - e));
+        sc = ldexpf(1.0f, up);
+        inv = ldexpf(1.0f, -up);
+    }
+    __half* h = x16 + row * n;
+#pragma unroll
+    for (int j = 0; j < NORM_ROWS_V; j++) {
+        const uint32_t i = threadIdx.x + 256 * j;
+        if (i < n4) *(uint2*)(h + 4 * (size_t)i) = make_uint2(pack_h2f(v[j].x * sc, v[j].y * sc), pack_h2f(v[j].z * sc, v[j].w * sc));
+    }
+    if (threadIdx.x == 0) unscale[row] = inv;
 }
 
 __global__ void __launch_bounds__(256) glu_rows_kernel(const float* __restrict__ g, size_t g_stride, const float* __restrict__ u, size_t u_stride,
@@ -275,6 +406,19 @@ cudaError_t attend_rows_t(const float* q, float* out, size_t stride, const __hal
 cudaError_t launch_qk_rope_rows(const float* qkv, float* qo, size_t stride, uint32_t rows, void* kc, void* vc, int kv_f16, const float* qn,
                                 const float* kn, const float* cs, const uint32_t* sp, const DecRope& p, cudaStream_t st) {
     if (p.hd > 256 || p.hd % 32 || 2 * p.half_rot > p.hd || rows == 0 || rows > 65535) return cudaErrorInvalidValue;
+    // (the fast kernel reads a rotation partner's values from the input again: input and output must not overlap)
+    const size_t in_extent = std::max<size_t>((size_t)(p.nh - 1) * p.q_stride + p.hd, std::max<size_t>(p.k_off, p.v_off) + (size_t)p.nkv * p.hd);
+    const bool apart = qo + (size_t)p.nh * p.hd <= qkv || qkv + in_extent <= qo;
+    if (apart && !qn && !kn && !p.v_norm && p.half_rot % 4 == 0 && stride % 4 == 0 && p.q_stride % 4 == 0 && p.k_off % 4 == 0 && p.v_off % 4 == 0 &&
+        p.cs_off % 4 == 0 && p.cs_stride % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)qo | (uintptr_t)cs) & 15) == 0) {
+        const size_t units = (size_t)rows * (p.nh + 2 * p.nkv);
+        const unsigned grid = (unsigned)((units + 7) / 8);
+        if (kv_f16)
+            qk_rope_fast_kernel<__half><<<grid, 256, 0, st>>>(qkv, qo, stride, rows, (__half*)kc, (__half*)vc, cs, sp, p);
+        else
+            qk_rope_fast_kernel<float><<<grid, 256, 0, st>>>(qkv, qo, stride, rows, (float*)kc, (float*)vc, cs, sp, p);
+        return cudaGetLastError();
+    }
     const dim3 grid(p.nh + 2 * p.nkv, rows);
     if (kv_f16)
         qk_rope_rows_kernel<__half><<<grid, p.hd, 0, st>>>(qkv, qo, stride, (__half*)kc, (__half*)vc, qn, kn, cs, sp, p);
@@ -308,6 +452,17 @@ cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32
     const bool two = (p.nh / p.nkv) % 2 == 0;  // two query heads of a KV head share a CTA's key and value tiles
     if (p.hd == 64) return two ? attend_rows_t<64, 2>(q, out, stride, kh, vh, sp, p, rows, st) : attend_rows_t<64, 1>(q, out, stride, kh, vh, sp, p, rows, st);
     return two ? attend_rows_t<128, 2>(q, out, stride, kh, vh, sp, p, rows, st) : attend_rows_t<128, 1>(q, out, stride, kh, vh, sp, p, rows, st);
+}
+
+bool norm_rows_supports(uint32_t n, const float* x, const float* out, const float* w, size_t x_stride, size_t out_stride) {
+    return n % 4 == 0 && n <= 1024 * NORM_ROWS_V && x_stride % 4 == 0 && out_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
+}
+
+cudaError_t launch_norm_rows(const float* x, size_t x_stride, float* out, size_t out_stride, const float* w, const DecNorm& p, uint32_t rows,
+                             void* x16, float* unscale, cudaStream_t st) {
+    if (!norm_rows_supports(p.n, x, out, w, x_stride, out_stride) || rows == 0 || (x16 && (p.n % 8 || ((uintptr_t)x16 & 15)))) return cudaErrorInvalidValue;
+    norm_rows_kernel<<<rows, 256, 0, st>>>(x, x_stride, out, out_stride, w, p.n, p.pre, p.eps, (int)p.add, (__half*)x16, unscale);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
