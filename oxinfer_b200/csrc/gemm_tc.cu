@@ -872,7 +872,6 @@ struct GemmPlan {
     int w_terms = 1;       // 2: two-term weights (Q4_K, tile_n <= 112)
     size_t a_lo_row0 = 0;  // two-term activations: the lo rows start this many rows below the hi rows (0: one term)
     int split_asked = 1;  // B2_GEMM_SPLIT_K when the plan was made (a cached plan is reused only under the same setting)
-    bool accumulate = false;  // GemmPeerY::accumulate
 };
 
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
@@ -928,10 +927,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         snprintf(err, errlen, "a gathered product needs a dense f32 result with 16-byte aligned column blocks");
         return cudaErrorInvalidValue;
     }
-    if (peer_y && peer_y->accumulate && (!gathered || peer_y->n_more != 0 || a_lo_row0 || w_terms == 2)) {
-        snprintf(err, errlen, "an accumulating product takes one-term operands, a row stride and no peers");
-        return cudaErrorInvalidValue;
-    }
+
     if (!enc) {
         snprintf(err, errlen, "cuTensorMapEncodeTiled is not available from the driver");
         return cudaErrorNotSupported;
@@ -1022,7 +1018,6 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         }
     }
     p->tmap_y = p->tmap_x;  // placeholder when the epilogue stores directly (bf16 output)
-    p->accumulate = peer_y && peer_y->accumulate;
     p->y_direct = y_dtype == B2_F32 && !gathered && (w.n_out % 4 != 0 || ((uintptr_t)y & 15) != 0);
     if (y_dtype == B2_F32 && !p->y_direct) {
         // the f32 output [t][n_out] (a gathered product: this shard's n_out columns of rows `ld` apart); one box = a warp's
@@ -1080,12 +1075,12 @@ bool gemm_tc_plan_matches(const GemmPlan* p, const WeightDev& w, const void* x16
             if (p->more_ptr[d] != peer_y->more[d]) return false;
     }
     return p && p->experts == 1 && p->a_lo_row0 == a_lo_row0 && p->w_terms == w_terms && (m_halves == 0 || p->m_halves == m_halves) && p->y == y && p->y_dtype == y_dtype && p->x16 == x16 && p->wptr == w.p0 && p->t == t && p->K == w.n_in && p->n_out == w.n_out &&
-           p->split_asked == split_k_asked() && p->pair_asked == pair_form_enabled() && p->accumulate == (peer_y && peer_y->accumulate);
+           p->split_asked == split_k_asked() && p->pair_asked == pair_form_enabled();
 }
 
 cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, int y_dtype, GemmStatus* status_dev, int /*sm_count*/,
                            cudaStream_t st, const float* row_unscale) {
-    const bool split = p->k_splits > 1 || p->accumulate;  // both add their results through the copy engine's reduce
+    const bool split = p->k_splits > 1;
     const bool tt = p->a_lo_row0 > 0 || p->w_terms == 2;
     using Kern = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, int, int, int, int, int, void*, int, GemmStatus*, int, const int*, F8Scales, int, const float*,
                           int, int, const CUtensorMap*, int);

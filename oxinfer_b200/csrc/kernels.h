@@ -181,7 +181,6 @@ struct GemmPeerY {
     size_t ld = 0;        // row stride of the destinations in elements (0: not a gathered product, the stride is n_out)
     int n_more = 0;       // peers' destinations
     float* more[7] = {};
-    bool accumulate = false;  // the results are added to what y holds (the copy engine's reduce-add; no peers then): y += x W^T
 };
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
                                 size_t errlen, size_t experts = 1, const int* tile_expert = nullptr, int force_m_halves = 0, size_t a_lo_row0 = 0, int w_terms = 1, const GemmPeerY* peer_y = nullptr);
