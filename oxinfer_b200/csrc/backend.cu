@@ -534,9 +534,10 @@ class Backend {
             }
             return B2_OK;
         }
-        if (rows_path(w->dev) && x_dtype == B2_F32 && y_dtype == B2_F32) {
-            // Q6_K / Q8_0 have no tensor-core kernel yet: the tokens go four at a time through the multi-row matrix-vector
-            // kernel (the weights are read once per four tokens; every row equals its one-token result bit for bit).
+        if (rows_path(w->dev) && x_dtype == B2_F32 && y_dtype == B2_F32 && (exact || !gemm_tc_supports(w->dev, t))) {
+            // Q6_K / Q8_0 under the exact switch (or at a shape the tensor-core kernel does not take): the tokens go four at a
+            // time through the multi-row matrix-vector kernel (the weights are read once per four tokens; every row equals its
+            // one-token result bit for bit).
             const size_t stride = (xplanes_bytes(K) + 255) / 256 * 256;
             cudaError_t e = xplanes.reserve(t * stride);
             if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(planes)");
@@ -596,6 +597,7 @@ class Backend {
             // f32 / bf16 rows -> f16 with a power-of-two factor per token row that the GEMM's epilogue takes out again
             // (up to 128 tokens, where a CTA's tile has room for it, as two f16 terms: 22 bits of every activation)
             lo_row0 = exact ? (t + 127) / 128 * 128 : (t <= 128 ? 128 : 0);
+            if (rows_path(w->dev)) lo_row0 = 0;  // the Q6_K / Q8_0 arms of the kernel take one-term operands
             const size_t x16_bytes = ((lo_row0 + t) * K * 2 + 255) / 256 * 256;
             e = x16.reserve(x16_bytes + t * 4);
             if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(x16)");

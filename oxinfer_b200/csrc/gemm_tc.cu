@@ -50,8 +50,10 @@ constexpr int RAW_BYTES = MAX_TILE_N * 144;  // one super-block column of the we
 constexpr int GEMM_THREADS = 608;          // activation producer, MMA issuer, 16 dequant / epilogue warps, weight producer
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds of SM clock
 
-struct F8Scales {  // block scales of an FP8 matrix (formats.cuh); s == nullptr for the 4-bit formats
+struct F8Scales {  // block scales of an FP8 matrix (formats.cuh); s == nullptr for the 4-bit formats.
+                   // Q8_0: s = the f16 block scales [n_out][ncb]. Q6_K: s = the i8 scales [n_out][K / 16], s2 = the f16 d [n_out][K / 256].
     const float* s;
+    const void* s2;
     int rows, ncb, row0;
     float pre;  // power of two folded into the f16 weights (keeps small scales out of f16's subnormals); the
                 // epilogue multiplies the outputs by 1 / pre
@@ -255,15 +257,19 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 #endif
     // A "raw block" is what one weight copy brings per row: a 144-byte 4-bit block (256 k, four pipeline
     // stages) or 128 e4m3 bytes (128 k = one column of FP8 scale blocks, two stages).
-    constexpr int RAW_ROW = FMT == B2_FMT_F8E4M3 ? 128 : 144;
-    constexpr int RAW_ST = FMT == B2_FMT_F8E4M3 ? 2 : 4;
+    // Q8_0 rows are 128 int8 per copy like the FP8 rows; a Q6_K copy brings a row's 128 bytes of low nibbles and, through a
+    // second tensor map (y_more[n_more]), its 64 bytes of high bit pairs (the planes of formats.cuh), 256 k = four stages.
+    constexpr bool BYTE_ROWS = FMT == B2_FMT_F8E4M3 || FMT == B2_FMT_Q8_0;
+    constexpr bool PRE_SCALED = BYTE_ROWS || FMT == B2_FMT_Q6_K;  // the f16 weights carry the factor f8.pre, the epilogue takes it out
+    constexpr int RAW_ROW = BYTE_ROWS ? 128 : (FMT == B2_FMT_Q6_K ? 192 : 144);
+    constexpr int RAW_ST = BYTE_ROWS ? 2 : 4;
     // bit 8 of the output type: f32 rows that are not 16-byte multiples (n_out % 4 != 0) cannot be described to the copy
     // engine; the epilogue then stores them directly
     const int y_dtype = y_dtype_arg & 0xff;
     const bool y_direct = (y_dtype_arg & 0x100) != 0;
     const long long dbg_k0 = clock64();
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == (PAIR ? 0 : 1) && blockIdx.y == (PAIR ? 1 : 0);
-    static_assert(!PAIR || (!SPLIT && !TT && FMT != B2_FMT_F8E4M3), "the pair form takes one-term 4-bit operands without a K split");
+    static_assert(!PAIR || (!SPLIT && !TT && (FMT == B2_FMT_Q4_K || FMT == B2_FMT_MLX4)), "the pair form takes one-term 4-bit operands without a K split");
     constexpr int STAGES = PAIR ? PAIR_STAGES : b2::STAGES;
     constexpr int B_STAGE_BYTES = PAIR ? PAIR_B_STAGE_BYTES : b2::B_STAGE_BYTES;
     constexpr int RAW_BYTES = PAIR ? PAIR_RAW_BYTES : b2::RAW_BYTES;
@@ -388,6 +394,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     continue;
                 }
                 mbar_arrive_expect_tx(&sh->raw_full[rb], w_bytes);
+                if constexpr (FMT == B2_FMT_Q6_K) {  // [rows][128] low nibbles, then [rows][64] high bit pairs
+                    tma_load_2d(raw, &tmap_w, &sh->raw_full[rb], (sb0 + sb) * 128, n0);
+                    tma_load_2d(raw + (size_t)my_rows * 128, y_more + n_more, &sh->raw_full[rb], (sb0 + sb) * 64, n0);
+                    w_issued = sb + 1;
+                    continue;
+                }
                 tma_load_2d(raw + (size_t)rb * RAW_BYTES, &tmap_w, &sh->raw_full[rb], (sb0 + sb) * RAW_ROW, w_row0 + n0 + (int)rank * my_rows);
                 w_issued = sb + 1;
             }
@@ -471,7 +483,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             const uint32_t b_full_even = PAIR ? cluster_addr(&sh->b_full[0], 0) : 0u;  // the even CTA's b_full[0]
             const uint32_t row_off = (uint32_t)(r + (is_lo ? 128 : 0)) * 128u;
             const uint32_t swz = (uint32_t)(r & 7);
-            const uint4* my_raw0 = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * RAW_ROW);
+            const uint4* my_raw0 = (const uint4*)(raw + (size_t)(in_tile ? r : 0) * (FMT == B2_FMT_Q6_K ? 128 : RAW_ROW));
             for (int sb = 0; sb < nsb && ok; sb++) {
                 const int rb = sb % NRAW;
                 const uint4* my_raw = (const uint4*)((const uint8_t*)my_raw0 + (size_t)rb * RAW_BYTES);
@@ -481,7 +493,67 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     ok = false;
                     break;
                 }
-                if constexpr (FMT == B2_FMT_F8E4M3) {
+                if constexpr (FMT == B2_FMT_Q6_K) {
+                    // Stage j of the super-block = elements 64 j .. 64 j + 63 = half n = j / 2 of the block, its low (j even) or
+                    // high (j odd) nibbles with bit pairs (0, 2) or (4, 6) of the half's 32 qh bytes (src/ggml.rs Q6_K decode):
+                    // element e < 32: ql[64 n + e] and qh[32 n + e] >> 4 odd; e >= 32: ql[64 n + e] and qh[32 n + e - 32] >> (4 odd + 2).
+                    // The staged tiles are swizzled by the copy engine: 16-byte chunk c of a ql row at c ^ (r & 7), of a qh row at
+                    // c ^ ((r >> 1) & 3). w = f16(d sc pre) * (q - 32), q - 32 exact in f16.
+                    const uint4* my_qh = (const uint4*)(raw + (size_t)my_rows * 128 + (size_t)(in_tile ? r : 0) * 64);
+                    const uint32_t swh = (uint32_t)((r >> 1) & 3);
+                    const size_t wrow = (size_t)(n0 + r);
+                    const bool live = in_tile && n0 + r < n_out;
+                    const float d = live ? __half2float(__ushort_as_half(__ldg((const unsigned short*)f8.s2 + wrow * (size_t)(K / 256) + sb0 + sb))) : 0.0f;
+#pragma unroll
+                    for (int jj = 0; jj < 2; jj++) {
+                        const int j = set + 2 * jj, n = j >> 1, odd = j & 1;
+                        uint4 ql4[4], qh4[2];
+#pragma unroll
+                        for (int c = 0; c < 4; c++) ql4[c] = my_raw[((uint32_t)(4 * n + c)) ^ swz];
+#pragma unroll
+                        for (int c = 0; c < 2; c++) qh4[c] = my_qh[((uint32_t)(2 * n + c)) ^ swh];
+                        if (jj == 1) {  // the row's last read of this super-block's staging buffer
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
+                        }
+                        const uint32_t sc4 = live ? __ldg((const uint32_t*)((const int8_t*)f8.s + wrow * (size_t)(K / 16) + (size_t)(sb0 + sb) * 16 + 4 * j)) : 0u;
+                        __half2 mul[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) mul[i] = __float2half2_rn(d * (float)(int8_t)(sc4 >> (8 * i)) * f8.pre);
+                        const int ks = sb * 4 + j;
+                        const int s = ks % STAGES;
+                        const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
+                        const uint32_t qlw[16] = {ql4[0].x, ql4[0].y, ql4[0].z, ql4[0].w, ql4[1].x, ql4[1].y, ql4[1].z, ql4[1].w,
+                                                  ql4[2].x, ql4[2].y, ql4[2].z, ql4[2].w, ql4[3].x, ql4[3].y, ql4[3].z, ql4[3].w};
+                        const uint32_t qhw[8] = {qh4[0].x, qh4[0].y, qh4[0].z, qh4[0].w, qh4[1].x, qh4[1].y, qh4[1].z, qh4[1].w};
+                        const __half2 bias = __float2half2_rn(1056.0f);  // 1024 (the exponent trick) + 32
+                        uint32_t o[32];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {  // word i: elements 4 i .. 4 i + 3 of the stage
+                            const uint32_t nib = odd ? (qlw[i] >> 4) & 0x0F0F0F0Fu : qlw[i] & 0x0F0F0F0Fu;
+                            const uint32_t hb = ((qhw[i & 7] >> (4 * odd + 2 * (i >> 3))) & 0x03030303u) << 4;
+                            const uint32_t q4 = nib | hb;
+                            uint32_t p0 = __byte_perm(q4, 0, 0x4140) | 0x64006400u, p1 = __byte_perm(q4, 0, 0x4342) | 0x64006400u;
+                            o[2 * i] = h2_bits(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), bias), mul[i >> 2]));
+                            o[2 * i + 1] = h2_bits(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), bias), mul[i >> 2]));
+                        }
+                        if (!mbar_wait<PAIR>(&sh->empty[s], ph ^ 1u, sh, status, 6, (uint32_t)ks)) {
+                            ok = false;
+                            break;
+                        }
+                        if (in_tile && !(dbg & 1)) {
+                            uint8_t* dst = b_tiles + (size_t)s * B_STAGE_BYTES + row_off;
+#pragma unroll
+                            for (int c = 0; c < 8; c++)
+                                *(uint4*)(dst + ((((uint32_t)c) ^ swz) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sh->b_full[s]);
+                    }
+                    continue;
+                }
+                if constexpr (BYTE_ROWS) {
                     // 64 e4m3 bytes of this set's stage (the raw tile is 128-byte swizzled: chunk c of row r sits
                     // at c ^ (r & 7)), the block scale of this row and k-block, then hardware e4m3x2 -> f16x2
                     // and one multiply by the scale per pair.
@@ -490,15 +562,37 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                     for (int c = 0; c < 4; c++) qb[c] = my_raw[((uint32_t)(4 * set + c)) ^ swz];
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
-                    float scale = 1.0f;
-                    if (f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb0 + sb);
-                    const __half2 sc2 = __float2half2_rn(scale * f8.pre);
                     const int ks = sb * 2 + set;
                     const int s = ks % STAGES;
                     const uint32_t ph = (uint32_t)((ks / STAGES) & 1);
                     uint32_t o[32];
+                    if constexpr (FMT == B2_FMT_Q8_0) {
+                        // 64 int8 of this set's stage = two blocks of 32 with an f16 scale each (src/ggml.rs Q8_0 decode): byte b ^ 0x80
+                        // under the exponent 0x64 is the f16 1024 + (q + 128), minus 1152 = q exactly, times f16(d pre)
+                        uint32_t d2 = 0u;
+                        if (in_tile && n0 + r < n_out)
+                            d2 = __ldg((const uint32_t*)((const unsigned short*)f8.s + (size_t)(n0 + r) * (size_t)f8.ncb + (size_t)(sb0 + sb) * 4 + set * 2));
+                        const __half2 m0 = __float2half2_rn(__half2float(__ushort_as_half((unsigned short)(d2 & 0xffffu))) * f8.pre);
+                        const __half2 m1 = __float2half2_rn(__half2float(__ushort_as_half((unsigned short)(d2 >> 16))) * f8.pre);
+                        const __half2 bias = __float2half2_rn(1152.0f);
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const uint32_t wds[4] = {qb[c].x, qb[c].y, qb[c].z, qb[c].w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const uint32_t u = wds[i] ^ 0x80808080u;
+                                uint32_t p0 = __byte_perm(u, 0, 0x4140) | 0x64006400u, p1 = __byte_perm(u, 0, 0x4342) | 0x64006400u;
+                                o[8 * c + 2 * i] = h2_bits(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), bias), c < 2 ? m0 : m1));
+                                o[8 * c + 2 * i + 1] = h2_bits(__hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), bias), c < 2 ? m0 : m1));
+                            }
+                        }
+                    }
+                    float scale = 1.0f;
+                    if (FMT == B2_FMT_F8E4M3 && f8.s && in_tile && n0 + r < n_out) scale = __ldg(f8.s + (size_t)((f8.row0 + n0 + r) / f8.rows) * f8.ncb + sb0 + sb);
+                    const __half2 sc2 = __float2half2_rn(scale * f8.pre);
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
+                        if (FMT != B2_FMT_F8E4M3) break;
                         const uint32_t wds[4] = {qb[c].x, qb[c].y, qb[c].z, qb[c].w};
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
@@ -647,8 +741,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 const int token = token0 + lane;
                 // the activations of a token row may have been scaled by a power of two on their way to f16 (to_f16_rows):
                 // its results are scaled back here, exactly
-                const bool scaled = FMT == B2_FMT_F8E4M3 || row_unscale != nullptr;
-                const float out_scale = (FMT == B2_FMT_F8E4M3 ? 1.0f / f8.pre : 1.0f) * ((row_unscale && token < t) ? __ldg(row_unscale + token) : 1.0f);
+                const bool scaled = PRE_SCALED || row_unscale != nullptr;
+                const float out_scale = (PRE_SCALED ? 1.0f / f8.pre : 1.0f) * ((row_unscale && token < t) ? __ldg(row_unscale + token) : 1.0f);
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
                 int c0 = cpar * 32;
                 if (y_dtype == B2_F32 && !y_direct && !(dbg & 64)) {
@@ -876,6 +970,8 @@ struct GemmPlan {
 
 bool gemm_tc_supports(const WeightDev& w, size_t t) {
     if (w.fmt == B2_FMT_F8E4M3) return w.n_in % 128 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0 && (w.p1 == nullptr || w.bs_cols == 128);
+    if (w.fmt == B2_FMT_Q8_0) return w.n_in % 128 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0 && ((uintptr_t)w.p1 & 3) == 0;
+    if (w.fmt == B2_FMT_Q6_K) return w.n_in % 256 == 0 && t >= 1 && (((uintptr_t)w.p0 | (uintptr_t)w.p1) & 15) == 0 && ((uintptr_t)w.p2 & 3) == 0;
     return (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && w.n_in % 256 == 0 && t >= 1 && ((uintptr_t)w.p0 & 15) == 0;
 }
 
@@ -915,6 +1011,16 @@ static int pick_tile_n(size_t n_out, int m_tiles, int sm_count, size_t K, int wi
         }
     }
     return best;
+}
+
+// Q6_K's qh plane [n_out][K / 4] bytes: boxes of 64 bytes x tile rows, 64-byte swizzle (conflict-free 16-byte reads by row).
+static CUresult encode_q6k_qh(EncodeTiledFn enc, CUtensorMap* m, const WeightDev& w, int tile_n) {
+    cuuint64_t dims[2] = {(cuuint64_t)(w.n_in / 4), (cuuint64_t)w.n_out};
+    cuuint64_t strides[1] = {(cuuint64_t)(w.n_in / 4)};
+    cuuint32_t box[2] = {64u, (cuuint32_t)tile_n};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.p1, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
 cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, void* y, int y_dtype, GemmPlan** out, char* err,
@@ -957,7 +1063,15 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     if (w_terms == 2 && w.fmt != B2_FMT_Q4_K) w_terms = 1;  // the other formats' weights round to f16 far below the bound
     p->w_terms = w_terms;
     // (a gathered product stores every tile through the copy engine, whose staging tiles are 32 columns wide)
-    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? (gathered ? 96 : 112) : (gathered ? 224 : MAX_TILE_N), gathered ? 32 : 16);
+    const bool new_fmt = w.fmt == B2_FMT_Q6_K || w.fmt == B2_FMT_Q8_0;
+    if (new_fmt && (experts != 1 || tile_expert || a_lo_row0 || w_terms == 2)) {
+        snprintf(err, errlen, "Q6_K / Q8_0 products are dense, with one-term operands");
+        delete p;
+        return cudaErrorInvalidValue;
+    }
+    // (a Q6_K row brings 192 packed bytes per super-block against Q4_K's 144: narrower tiles fit the same staging buffer)
+    const int widest = w.fmt == B2_FMT_Q6_K ? (gathered ? 160 : 176) : (gathered ? 224 : MAX_TILE_N);
+    p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? (gathered ? 96 : 112) : widest, gathered ? 32 : 16);
     // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
     // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
     // with its width, so a grid that fills half the SMs or less runs nearly twice as fast as twice as many CTAs of half
@@ -967,7 +1081,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         p->split_asked = want;
         const int sb_k = w.fmt == B2_FMT_F8E4M3 ? 128 : 256;
         const size_t nsb_all = w.n_in / sb_k;
-        if (want == 2 && y_dtype == B2_F32 && !a_lo_row0 && w_terms == 1 && !tile_expert && !gathered && nsb_all % 2 == 0 && nsb_all >= 8) {
+        if (want == 2 && !new_fmt && y_dtype == B2_F32 && !a_lo_row0 && w_terms == 1 && !tile_expert && !gathered && nsb_all % 2 == 0 && nsb_all >= 8) {
             const int tn2 = pick_tile_n(w.n_out, p->m_tiles * 2, sm_count, w.n_in / 2);
             const size_t tiles1 = (w.n_out + p->tile_n - 1) / p->tile_n * (size_t)p->m_tiles;
             const size_t tiles2 = (w.n_out + tn2 - 1) / tn2 * (size_t)p->m_tiles * 2;
@@ -1003,8 +1117,8 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
     }
     {
         // the packed weights as a byte matrix [n_out][row_bytes]; one box = one super-block column of the tile
-        const bool f8 = w.fmt == B2_FMT_F8E4M3;
-        size_t row_bytes = f8 ? w.n_in : w.n_in / 256 * 144;
+        const bool f8 = w.fmt == B2_FMT_F8E4M3 || new_fmt;  // rows of bytes, 128 per copy, swizzled
+        size_t row_bytes = w.fmt == B2_FMT_Q6_K ? w.n_in / 2 : f8 ? w.n_in : w.n_in / 256 * 144;
         cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(w.n_out * experts)};
         cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
         cuuint32_t box[2] = {f8 ? 128u : 144u, (cuuint32_t)(p->pair ? p->tile_n / 2 : p->tile_n)};
@@ -1035,7 +1149,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
             return cudaErrorInvalidValue;
         }
         if (gathered && peer_y->n_more > 0) {
-            CUtensorMap maps[7];
+            CUtensorMap maps[8];
             for (int d = 0; d < peer_y->n_more; d++) {
                 if (((uintptr_t)peer_y->more[d] & 15) != 0) r = CUDA_ERROR_INVALID_VALUE;
                 if (r == CUDA_SUCCESS)
@@ -1043,8 +1157,10 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
                 p->more_ptr[d] = peer_y->more[d];
             }
-            cudaError_t ce = r == CUDA_SUCCESS ? cudaMalloc((void**)&p->y_more, sizeof(CUtensorMap) * peer_y->n_more) : cudaErrorInvalidValue;
-            if (ce == cudaSuccess) ce = cudaMemcpy(p->y_more, maps, sizeof(CUtensorMap) * peer_y->n_more, cudaMemcpyHostToDevice);
+            const int extra = w.fmt == B2_FMT_Q6_K ? 1 : 0;  // the qh plane's map goes behind the peers'
+            if (extra && r == CUDA_SUCCESS) r = encode_q6k_qh(enc, &maps[peer_y->n_more], w, p->tile_n);
+            cudaError_t ce = r == CUDA_SUCCESS ? cudaMalloc((void**)&p->y_more, sizeof(CUtensorMap) * (peer_y->n_more + extra)) : cudaErrorInvalidValue;
+            if (ce == cudaSuccess) ce = cudaMemcpy(p->y_more, maps, sizeof(CUtensorMap) * (peer_y->n_more + extra), cudaMemcpyHostToDevice);
             if (ce != cudaSuccess) {
                 snprintf(err, errlen, "tensor maps of the peers' y could not be made (CUresult %d, %s)", (int)r, cudaGetErrorString(ce));
                 if (p->y_more) cudaFree(p->y_more);
@@ -1054,6 +1170,18 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
             p->n_more = peer_y->n_more;
         }
         p->y_ld = gathered ? ld : 0;
+    }
+    if (w.fmt == B2_FMT_Q6_K && !p->y_more) {  // the second weight plane's tensor map, read from global memory by the kernel
+        CUtensorMap m;
+        CUresult r = encode_q6k_qh(enc, &m, w, p->tile_n);
+        cudaError_t ce = r == CUDA_SUCCESS ? cudaMalloc((void**)&p->y_more, sizeof(CUtensorMap)) : cudaErrorInvalidValue;
+        if (ce == cudaSuccess) ce = cudaMemcpy(p->y_more, &m, sizeof m, cudaMemcpyHostToDevice);
+        if (ce != cudaSuccess) {
+            snprintf(err, errlen, "the tensor map of the Q6_K high-bit plane could not be made (CUresult %d, %s)", (int)r, cudaGetErrorString(ce));
+            if (p->y_more) cudaFree(p->y_more);
+            delete p;
+            return cudaErrorInvalidValue;
+        }
     }
     *out = p;
     return cudaSuccess;
@@ -1089,10 +1217,14 @@ cudaError_t launch_gemm_tc(GemmPlan* p, const WeightDev& w, size_t t, void* y, i
         kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4, false, true>
                : w.fmt == B2_FMT_F8E4M3 ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, true>;
     else
-        kern = w.fmt == B2_FMT_MLX4     ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true, false> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false>)
+        kern = w.fmt == B2_FMT_Q6_K     ? gemm_q4k_tc_kernel<B2_FMT_Q6_K, false, false>
+               : w.fmt == B2_FMT_Q8_0   ? gemm_q4k_tc_kernel<B2_FMT_Q8_0, false, false>
+               : w.fmt == B2_FMT_MLX4   ? (split ? gemm_q4k_tc_kernel<B2_FMT_MLX4, true, false> : gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false>)
                : w.fmt == B2_FMT_F8E4M3 ? (split ? gemm_q4k_tc_kernel<B2_FMT_F8E4M3, true, false> : gemm_q4k_tc_kernel<B2_FMT_F8E4M3, false, false>)
                                         : (split ? gemm_q4k_tc_kernel<B2_FMT_Q4_K, true, false> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, false>);
-    F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
+    F8Scales f8{w.fmt == B2_FMT_F8E4M3 ? (const float*)w.p1 : nullptr, nullptr, (int)w.bs_rows, (int)w.bs_ncb, (int)w.bs_row0, 256.0f};
+    if (w.fmt == B2_FMT_Q8_0) f8 = F8Scales{(const float*)w.p1, nullptr, 1, (int)(w.n_in / 32), 0, 256.0f};
+    if (w.fmt == B2_FMT_Q6_K) f8 = F8Scales{(const float*)w.p2, (const void*)w.p3, 1, 0, 0, 256.0f};
     if (p->pair) {
         kern = w.fmt == B2_FMT_MLX4 ? gemm_q4k_tc_kernel<B2_FMT_MLX4, false, false, true> : gemm_q4k_tc_kernel<B2_FMT_Q4_K, false, false, true>;
         if (cudaError_t e = ensure_dynamic_smem((const void*)kern, PAIR_SMEM); e != cudaSuccess) return e;

@@ -173,11 +173,13 @@ def q8_0_model(n_out: int, n_in: int, seed: int, sigma: float) -> Gguf:
     return Gguf(FMT_Q8_0, np.ascontiguousarray(blk.reshape(-1)))
 
 
-def llama_weights(n_layers: int, h: int, nh: int, nkv: int, hd: int, inter: int, vocab: int, seed: int, same_layers: bool = False):
+def llama_weights(n_layers: int, h: int, nh: int, nkv: int, hd: int, inter: int, vocab: int, seed: int, same_layers: bool = False,
+                  mixed: bool = False):
     """Random-init weights of a Llama-style decoder in the formats of a GGUF Q4_K_M-like checkpoint: Q4_K body,
     Q6_K head, Q8_0 embeddings, f32 norms. Returns (layers, final_norm, head, embed); each layer is a dict of
     ``Gguf`` refs ``q k v o gate up down`` plus f32 ``ln_pre ln_post``. ``same_layers`` reuses layer 0's bytes for
-    every layer (each still uploads to its own device memory): generation time only, the work per token is unchanged."""
+    every layer (each still uploads to its own device memory): generation time only, the work per token is unchanged.
+    ``mixed``: v and down in Q6_K (as Q4_K_M checkpoints keep them in half of their layers) and o in Q8_0."""
     rng = np.random.default_rng(seed)
     shapes = {"q": (nh * hd, h), "k": (nkv * hd, h), "v": (nkv * hd, h), "o": (h, nh * hd), "gate": (inter, h), "up": (inter, h),
               "down": (h, inter)}
@@ -188,7 +190,10 @@ def llama_weights(n_layers: int, h: int, nh: int, nkv: int, hd: int, inter: int,
             continue
         L = {}
         for j, (name, (n_out, n_in)) in enumerate(shapes.items()):
-            L[name] = q4_k_model(n_out, n_in, seed + 100 * li + j + 1, 1.0 / np.sqrt(n_in))
+            make = q4_k_model
+            if mixed:
+                make = {"v": q6_k_model, "down": q6_k_model, "o": q8_0_model}.get(name, q4_k_model)
+            L[name] = make(n_out, n_in, seed + 100 * li + j + 1, 1.0 / np.sqrt(n_in))
         L["ln_pre"] = (1.0 + 0.1 * rng.standard_normal(h)).astype(np.float32)
         L["ln_post"] = (1.0 + 0.1 * rng.standard_normal(h)).astype(np.float32)
         layers.append(L)

@@ -141,28 +141,62 @@ def test_q4k_matmul_full_size_config(backend):
 
 @pytest.mark.parametrize("fmt", ["q6_k", "q8_0"])
 @pytest.mark.parametrize("shape", [(256, 512, 64), (1000, 2048, 9), (4099, 4096, 131)])
-def test_many_tokens_for_formats_without_a_tensor_core_kernel(backend, fmt, shape):
-    """Q6_K and Q8_0 at t > 8: the tokens run four at a time through the multi-row matrix-vector kernel, so the bound is the
-    matrix-vector one and every row equals its one-token result bit for bit (ragged token and row counts included)."""
+def test_many_tokens_under_the_exact_switch_for_q6k_and_q8_0(backend, fmt, shape):
+    """Q6_K and Q8_0 at t > 8 with the exact switch on: the tokens run four at a time through the multi-row matrix-vector
+    kernel, so the bound is the matrix-vector one and every row equals its one-token result bit for bit (ragged token and row
+    counts included)."""
     n_out, n_in, t = shape
     ref, m = make_pair(fmt, n_out, n_in, 440 + t)
     dev = backend.upload(ref, n_out, n_in)
     x = synth.activations(t, n_in, 441)
     y = np.full((t, n_out), np.nan, np.float32)
+    backend.set_exact(True)
+    try:
+        assert backend.matmul(x, [ob.Job(dev, y)])
+        assert np.isfinite(y).all()
+        assert row_err(y, m.matmul_f64(x)) < 2e-5
+        for i in (0, t // 2, t - 1):
+            y1 = np.zeros((1, n_out), np.float32)
+            assert backend.matmul(x[i:i + 1], [ob.Job(dev, y1)])
+            assert np.array_equal(y1[0], y[i])
+    finally:
+        backend.set_exact(False)
+
+
+@pytest.mark.parametrize("fmt", ["q6_k", "q8_0"])
+@pytest.mark.parametrize("shape", [(256, 512, 64), (176, 256, 9), (1000, 2048, 130), (4099, 4096, 131), (4096, 768, 512), (32064, 4096, 300),
+                                   (2048, 14336, 257)])
+def test_q6k_and_q8_0_matmul_on_the_tensor_cores(backend, fmt, shape):
+    """Q6_K and Q8_0 prefill products (t > 8) on the tcgen05 kernel: the row planes come in through the copy engine
+    (128-byte rows of low nibbles / int8, Q6_K's 64-byte rows of high bit pairs through a second tensor map), are expanded to
+    f16 (w = f16(d sc) (q - 32) resp. f16(d) q, the integer exact) and multiplied like the 4-bit formats. The bound is the
+    prefill one: 1e-3 per row against the f64 product of the bit-exact weights; ragged row and token counts, rows that are not
+    a multiple of 4 (direct stores), the vocabulary-sized head and a long K included."""
+    n_out, n_in, t = shape
+    ref, m = make_pair(fmt, n_out, n_in, 470 + t)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(t, n_in, 471)
+    y = np.full((t, n_out), np.nan, np.float32)
+    launches0 = backend.launch_count()
     assert backend.matmul(x, [ob.Job(dev, y)])
+    assert backend.launch_count() - launches0 == 2          # the conversion to f16 and one GEMM, not t / 4 matrix-vector launches
     assert np.isfinite(y).all()
-    assert row_err(y, m.matmul_f64(x)) < 2e-5
-    for i in (0, t // 2, t - 1):
-        y1 = np.zeros((1, n_out), np.float32)
-        assert backend.matmul(x[i:i + 1], [ob.Job(dev, y1)])
-        assert np.array_equal(y1[0], y[i])
+    err = row_err(y, m.matmul_f64(x))
+    assert err < TOL, err
+    # device-resident bf16 activations and bf16 results take the same kernel
+    xd = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    yd = torch.zeros((t, n_out), device="cuda", dtype=torch.bfloat16)
+    assert backend.matmul_dev(dev, xd, yd)
+    torch.cuda.synchronize()
+    exact = m.matmul_f64(xd.float().cpu().numpy())
+    assert row_err(yd.float().cpu().numpy(), exact) < 6e-3   # bf16 results: 8 bits
 
 
 def test_matmul_declines_what_it_cannot_take(backend):
     """A shape outside every kernel (n_in not a multiple of the block size is refused at upload; here: bf16 activations for a
     format that only has the f32 matrix-vector path) is declined with nothing written (src/gpu.rs:158-160)."""
     n_out, n_in, t = 256, 512, 64
-    ref, _ = make_pair("q6_k", n_out, n_in, 440)
+    ref = synth.other_blocks(13, n_out, n_in, 440)   # Q5_K: the generic matrix-vector kernel only
     dev = backend.upload(ref, n_out, n_in)
     x = torch.from_numpy(synth.activations(t, n_in, 441)).cuda().to(torch.bfloat16)
     y = torch.full((t, n_out), 7.0, device="cuda", dtype=torch.float32)

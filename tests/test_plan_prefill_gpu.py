@@ -24,8 +24,8 @@ SMALL = dict(n_layers=2, h=256, nh=4, nkv=2, hd=64, inter=512, vocab=1024)
 WIDE = dict(n_layers=3, h=512, nh=8, nkv=2, hd=128, inter=1024, vocab=512)
 
 
-def plans(backend, cfg, seed, tokens, max_len=512, kv_f16=False, interleaved=True, with_cpu=False):
-    layers, final_norm, head, embed, shapes = synth.llama_weights(seed=seed, **cfg)
+def plans(backend, cfg, seed, tokens, max_len=512, kv_f16=False, interleaved=True, with_cpu=False, mixed=False):
+    layers, final_norm, head, embed, shapes = synth.llama_weights(seed=seed, mixed=mixed, **cfg)
     dev_layers, cpu_layers = [], []
     for L in layers:
         d = {name: backend.upload(L[name], n_out, n_in) for name, (n_out, n_in) in shapes.items()}
@@ -95,6 +95,23 @@ def test_prefill_steps_match_one_token_steps(backend, cfg, kv_f16):
         assert none is None
         assert row_err(hp, h1.astype(np.float64)) < bound, (pos, t, row_err(hp, h1.astype(np.float64)))
         assert cache_err(pre, one, cfg, pos, t) < bound, (pos, t)
+    one.close()
+    pre.close()
+
+
+def test_prefill_with_q6k_and_q8_0_products(backend):
+    """A body in the formats of a Q4_K_M checkpoint's heavier layers: v and down in Q6_K, o in Q8_0 (all three on the
+    tensor-core GEMM in the prefill plan, on the exact matrix-vector kernels in the one-token plan)."""
+    cfg = WIDE
+    one, pre, inv_freq, _, keep = plans(backend, cfg, seed=1305, tokens=160, mixed=True)
+    rng = np.random.default_rng(95)
+    pos, t = 45, 160
+    fill((one, pre), cfg, pos, 66)
+    xs = rng.standard_normal((t, cfg["h"])).astype(np.float32)
+    h1 = one_by_one(one, pos, xs, inv_freq)
+    hp, _ = pre.step_multi(pos, xs, rope_rows(pos, t, inv_freq))
+    assert row_err(hp, h1.astype(np.float64)) < 2e-3 * cfg["n_layers"]
+    assert cache_err(pre, one, cfg, pos, t) < 2e-3 * cfg["n_layers"]
     one.close()
     pre.close()
 
@@ -196,12 +213,14 @@ def test_declined_graphs_and_argument_errors(backend):
         pre.step_multi(40, x[:30], rope_rows(40, 30, inv_freq))
     h, _ = pre.step_multi(3, x[:30], rope_rows(3, 30, inv_freq))
     assert np.isfinite(h).all()
-    # a graph with the head is the decode graph, not a prefill graph; the Q6_K head has no tensor-core kernel either
+    # a graph with the head is the decode graph, not a prefill graph
     with_head = D.llama_graph(lc, dev_layers, final_norm, dhead)
     assert D.decode_plan_prefill(backend, with_head, 64, 32) is None and "without logits" in backend.last_declined
     assert D.decode_plan_prefill(backend, gp, 16384, 8193) is None and "8192" in backend.last_declined
+    # a product in a format without a tensor-core kernel (Q5_K runs on the generic matrix-vector kernel only)
     g2 = D.llama_graph(lc, dev_layers, final_norm, dhead, prefill=True)
-    g2.linear(dhead, g2.hidden, g2.hidden)   # a Q6_K product
+    q5 = backend.upload(synth.other_blocks(13, SMALL["h"], SMALL["h"], 9), SMALL["h"], SMALL["h"])
+    g2.linear(q5, g2.hidden, g2.input)
     assert D.decode_plan_prefill(backend, g2, 64, 32) is None and "tensor-core" in backend.last_declined
     one.close()
     pre.close()
