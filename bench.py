@@ -852,6 +852,36 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
     return out
 
 
+def gemm_format_extras(be, torch, peaks):
+    """The prefill product at config 1's shape (512 x 4096 x 14336) in every format with a tensor-core kernel: the GEMM kernel
+    alone (f16 activations used in place), weights larger than L2 (rotating copies), CUDA events around 20 launches."""
+    from oxinfer_b200 import synth
+
+    out = {}
+    x16 = torch.from_numpy(synth.activations(M_TOK, K_IN, 78)).cuda().to(torch.float16)
+    for fmt in ("q4_k", "mlx4", "q6_k", "q8_0", "f8_e4m3"):
+        ref = synth.make(fmt, N_OUT, K_IN, 91)
+        devs = [be.upload(ref, N_OUT, K_IN) for _ in range(6)]
+        wbytes = devs[0].bytes()
+        ys = [torch.empty((M_TOK, N_OUT), device="cuda") for _ in range(2)]
+        for i in range(3):
+            assert be.matmul_dev(devs[i % 6], x16, ys[i % 2])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(20):
+            be.matmul_dev(devs[i % 6], x16, ys[i % 2])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 20 * 1e3
+        out[fmt] = {"us": us, "tflops": FLOP_PER_STEP / us / 1e6, "frac_of_bf16_peak": FLOP_PER_STEP / us / 1e6 / peaks["bf16_tflops"],
+                    "weight_bytes": wbytes, "rotating_copies": 6}
+        for d in devs:
+            d.free()
+    be.check_status()
+    return out
+
+
 def prefill_extras(be, peaks, n_layers=32, tokens=2048, kv_f16=False):
     """Prefill of the config-2 model (Backend::decode_plan_prefill): `tokens` tokens per step from an empty cache, through
     b2_plan_step_multi with host buffers (embeddings and RoPE rows in, final-normed hidden states out). The device time is
@@ -935,6 +965,9 @@ def run_b200(args, rank, world, local_rank):
         return
     if args.section == "refcuda":
         emit(json.dumps({"extra": {"reference_cuda": ref_cuda_extras(be, torch)}}))
+        return
+    if args.section == "gemm_formats":
+        emit(json.dumps({"extra": {"gemm_formats": gemm_format_extras(be, torch, peaks)}}))
         return
     if args.section == "prefill":
         emit(json.dumps({"extra": {"prefill_plan": prefill_extras(be, peaks, args.layers, min(args.tokens, 8192) if args.tokens != 256 else 2048, args.kv_f16)}}))
@@ -1157,6 +1190,7 @@ def run_b200(args, rank, world, local_rank):
             for name, fn in (("gemv", lambda: gemv_extras(be, torch, peaks, 40)), ("moe", lambda: moe_extras(be, torch, peaks)),
                              ("fp8", lambda: fp8_extras(be, torch, peaks)), ("decode", lambda: decode_extras(be, peaks, cpu_tokens=2, e2e_tokens=32)),
                              ("prefill_plan", lambda: prefill_extras(be, peaks)),
+                             ("gemm_formats", lambda: gemm_format_extras(be, torch, peaks)),
                              ("reference_cuda", lambda: ref_cuda_extras(be, torch))):
                 try:
                     line["extra"][name] = fn()
@@ -1251,7 +1285,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="with --section decode: layers of the decoder (profiling runs use fewer)")
     ap.add_argument("--tokens", type=int, default=256, help="with --section decode: tokens to generate")
     ap.add_argument("--kv-f16", action="store_true", help="with --section decode: f16 KV caches instead of the reference's f32")
-    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "prefill", "moe", "fp8", "refcuda"],
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "gemv", "decode", "prefill", "gemm_formats", "moe", "fp8", "refcuda"],
                     help="gemm: only the headline GEMM loops (no CPU baseline, no GEMV extras); gemv: only the GEMV extras (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

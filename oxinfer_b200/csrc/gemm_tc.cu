@@ -68,6 +68,7 @@ constexpr int PAIR_MAX_TILE_N = 240;                       // the pair's tile; a
 constexpr int PAIR_B_STAGE_BYTES = PAIR_MAX_TILE_N / 2 * 128;
 constexpr int PAIR_RAW_BYTES = PAIR_MAX_TILE_N / 2 * 144;  // one of two staging buffers (the copy of super-block sb + 2 flies while sb + 1 is expanded)
 constexpr int MAX_STAGES = 4;
+constexpr int Q6K_MAX_TILE_N = 208;
 
 struct __align__(8) Shared {
     uint64_t a_full[MAX_STAGES];
@@ -271,8 +272,11 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const bool dbg_cta = (dbg & 32768) && blockIdx.x == (PAIR ? 0 : 1) && blockIdx.y == (PAIR ? 1 : 0);
     static_assert(!PAIR || (!SPLIT && !TT && (FMT == B2_FMT_Q4_K || FMT == B2_FMT_MLX4)), "the pair form takes one-term 4-bit operands without a K split");
     constexpr int STAGES = PAIR ? PAIR_STAGES : b2::STAGES;
-    constexpr int B_STAGE_BYTES = PAIR ? PAIR_B_STAGE_BYTES : b2::B_STAGE_BYTES;
-    constexpr int RAW_BYTES = PAIR ? PAIR_RAW_BYTES : b2::RAW_BYTES;
+    // (Q6_K: tiles of at most 208 rows, so that the three B stages leave room for 192 packed bytes per row)
+    constexpr int B_STAGE_BYTES = PAIR ? PAIR_B_STAGE_BYTES : (FMT == B2_FMT_Q6_K ? Q6K_MAX_TILE_N * 128 : b2::B_STAGE_BYTES);
+    constexpr int RAW_BYTES = PAIR ? PAIR_RAW_BYTES : (FMT == B2_FMT_Q6_K ? Q6K_MAX_TILE_N * 192 : b2::RAW_BYTES);
+    static_assert(1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + (PAIR ? 2 : 1) * RAW_BYTES + sizeof(Shared) <= (PAIR ? PAIR_SMEM : GEMM_SMEM),
+                  "the format's buffers fit the launch's shared memory");
     constexpr int NRAW = PAIR ? 2 : 1;  // staging buffers of packed weights
     // dequantizer sets: groups of warps that take the pipeline stages in turn, one thread per weight row of the CTA's tile
     constexpr int NSETS = PAIR ? 4 : 2, SET_THREADS = 512 / NSETS, SET_WARPS = SET_THREADS / 32;
@@ -1070,7 +1074,7 @@ cudaError_t gemm_tc_plan_create(const WeightDev& w, const void* x16, size_t t, v
         return cudaErrorInvalidValue;
     }
     // (a Q6_K row brings 192 packed bytes per super-block against Q4_K's 144: narrower tiles fit the same staging buffer)
-    const int widest = w.fmt == B2_FMT_Q6_K ? (gathered ? 160 : 176) : (gathered ? 224 : MAX_TILE_N);
+    const int widest = w.fmt == B2_FMT_Q6_K ? (gathered ? 192 : Q6K_MAX_TILE_N) : (gathered ? 224 : MAX_TILE_N);
     p->tile_n = pick_tile_n(w.n_out, p->m_tiles, sm_count, w.n_in, w_terms == 2 ? (gathered ? 96 : 112) : widest, gathered ? 32 : 16);
     // K in two halves (B2_GEMM_SPLIT_K=2; off by default because a row's bits then depend on whether its launch was
     // split, and row shards must equal the unsharded rows): a CTA's time goes with its number of k stages and hardly
