@@ -334,7 +334,7 @@ int b2_plan_step_multi(b2_ctx* ctx, b2_plan plan, size_t pos, size_t t, const fl
  * rows (b2_matmul's kernel), attention a causal tensor-core kernel over the step's queries and the plan's KV cache. Its
  * results differ from one-token steps in rounding (as the reference says of its own prefill plans). The graph is the decode
  * graph without the head (n_logits == 0: the reference builds its prefill graph that way, src/model_gpu.rs:398-400); products
- * need a format with a tensor-core kernel (Q4_K, MLX-4, FP8), otherwise B2_DECLINED. Steps go through b2_plan_step_multi
+ * need a format with a tensor-core kernel (Q4_K, MLX-4, Q6_K, Q8_0, FP8), otherwise B2_DECLINED. Steps go through b2_plan_step_multi
  * (logits NULL); the KV calls, b2_plan_tokens and b2_plan_free apply. */
 #define B2_PREFILL_MAX_TOKENS 8192
 int b2_decode_plan_prefill(b2_ctx* ctx, const b2_graph* graph, size_t tokens, b2_plan* out);

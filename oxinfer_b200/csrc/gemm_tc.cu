@@ -24,6 +24,9 @@
 // wave; the last tile may be ragged (TMA zero-fills rows past n_out, which dequantize to zeros).
 // Operands are f16 rather than bf16: Q4_K values carry more than 8 significant bits, and bf16
 // activations convert to f16 exactly in the range that matters.
+// The same kernel is instantiated for the repacked MLX 4-bit blocks, FP8 e4m3 with block scales, Q8_0 (int8 rows + f16
+// block scales) and Q6_K (rows of low nibbles and of high bit pairs + i8 scales + f16 d): only the weight copies and the
+// dequantizers' expansion differ (the arms of `if constexpr (FMT == ...)`).
 //
 // Every wait is bounded: a wait that exceeds its cycle limit records where it gave up in a status
 // word, raises a CTA-wide abort flag, and every role then falls through to the common teardown

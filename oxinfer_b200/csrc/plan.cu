@@ -270,7 +270,7 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
                     return B2_DECLINED;
                 }
                 if (prefill && (!gemm_tc_supports(*w, (size_t)tokens) || o.mode == B2_MODE_ADD_GATED || o.n_out % 4)) {
-                    err = "[b200qmm: decode_plan: a prefill plan takes products with a tensor-core kernel (Q4_K, MLX-4, FP8), rows in multiples of 4, "
+                    err = "[b200qmm: decode_plan: a prefill plan takes products with a tensor-core kernel (Q4_K, MLX-4, Q6_K, Q8_0, FP8), rows in multiples of 4, "
                           "and no gated mode]";
                     return B2_DECLINED;
                 }
