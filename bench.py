@@ -718,6 +718,8 @@ def decode_extras(be, peaks, n_tokens=256, ctx=2048, n_layers=32, kv_f16=False, 
             kv_rows = [k, v]
     inv_freq = D.rope_inv_freq(cfg["hd"], lc.rope_theta)
     table = np.stack([D.rope_table(ctx + i, inv_freq) for i in range(n_tokens)])
+    if world > 1:   # the ranks enter every collective step together (rank 0 has just built and filled a second plan)
+        dist.barrier()
     warm_toks, _ = plan.generate(dembed, 1, ctx, min(8, n_tokens), table[: min(8, n_tokens)])    # warm-up (captures the graph)
     parity = None
     if world > 1 and check_tokens:
@@ -950,7 +952,13 @@ def run_b200(args, rank, world, local_rank):
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # A rank that fails inside a collective section must end the run in minutes, not in the library's default half hour
+        # (10 minutes of collective timeout and 8 of its heartbeat monitor): rank 0 then still prints what it has.
+        import datetime
+
+        os.environ.setdefault("TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC", "60")
+        os.environ.setdefault("TORCH_NCCL_DUMP_ON_TIMEOUT", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=150))
     peaks = measured_peaks()
     be = ob.Backend(local_rank)
     stream = torch.cuda.current_stream()
@@ -1134,18 +1142,39 @@ def run_b200(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms_total, kern_ms, ms_compute, ms_nccl = (float(v) for v in t.cpu())
 
+    # The collective extras run in a worker thread with a deadline: if a rank fails inside one of them, the others would wait
+    # in a collective until the process group's timeout aborts the process, and rank 0 would print nothing. With the deadline
+    # the headline line is printed whatever happens to the extras, and the ranks then leave without the closing barrier.
+    stuck = []
+
+    def collective_section(name, fn, seconds=300):
+        box = {}
+
+        def work():
+            try:
+                torch.cuda.set_device(local_rank)
+                with torch.cuda.stream(stream):
+                    box["out"] = fn()
+            except Exception as e:
+                box["out"] = {"error": str(e)}
+                print(f"[bench rank {rank}] {name} failed: {e}", file=sys.stderr, flush=True)
+
+        th = threading.Thread(target=work, daemon=True)
+        th.start()
+        th.join(seconds)
+        if th.is_alive():
+            stuck.append(name)
+            print(f"[bench rank {rank}] {name} did not finish within {seconds} s", file=sys.stderr, flush=True)
+            return {"error": f"did not finish within {seconds} s (a rank failed inside a collective step)"}
+        return box["out"]
+
     dec_tp = None
     if world > 1 and args.section == "all":   # collective: every rank runs the tensor-parallel decode plan
-        try:
-            dec_tp = decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist, check_tokens=8)
-        except Exception as e:
-            dec_tp = {"error": str(e)}
+        dec_tp = collective_section("tensor-parallel decode",
+                                    lambda: decode_extras(be, peaks, 128, 2048, 32, False, rank=rank, world=world, dist=dist, check_tokens=8))
     ep = None
-    if world > 1 and args.section == "all" and 128 % world == 0:   # collective: the expert-parallel MoE layer
-        try:
-            ep = moe_ep_extras(be, torch, dist, rank, world)
-        except Exception as e:
-            ep = {"error": str(e)}
+    if world > 1 and args.section == "all" and 128 % world == 0 and not stuck:   # collective: the expert-parallel MoE layer
+        ep = collective_section("expert-parallel MoE", lambda: moe_ep_extras(be, torch, dist, rank, world))
     if rank == 0:
         n_timed = args.steps * repeats
         ms = ms_total / n_timed
@@ -1218,6 +1247,9 @@ def run_b200(args, rank, world, local_rank):
         line["summary"] = summarize(line)
         emit(json.dumps(line))
     if world > 1:
+        if stuck:   # a worker thread still sits in a collective: no closing barrier, no orderly teardown
+            sys.stdout.flush()
+            os._exit(0)
         dist.barrier()
         dist.destroy_process_group()
 
