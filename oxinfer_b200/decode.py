@@ -142,15 +142,17 @@ class DecodePlan:
         self._be._check(self._be._L.b2_plan_tokens(self._be._ctx, self.handle, C.byref(n)))
         return n.value
 
-    def step_multi(self, pos: int, x: np.ndarray, rope_cs: np.ndarray, want_logits: bool = True):
+    def step_multi(self, pos: int, x: np.ndarray, rope_cs: np.ndarray, want_logits: bool = True, hidden_out: np.ndarray | None = None):
         """``t`` tokens at positions ``pos .. pos + t - 1`` (``Step::t``, ``src/gpu_decode.rs:538-570``): ``x`` is ``[t][n_input]``,
         ``rope_cs`` holds, for each RoPE table in turn, ``t`` rows of cos then sin. Returns (hidden ``[t][n_hidden]``, logits
-        ``[t][n_logits]`` or None); every row equals the result of a one-token step, bit for bit."""
+        ``[t][n_logits]`` or None); every row equals the result of a one-token step, bit for bit (a prefill plan's: up to
+        rounding). ``hidden_out``: a caller's ``[t][n_hidden]`` f32 array to fill (page-locked memory makes the copies faster)."""
         x = np.ascontiguousarray(x, dtype=np.float32)
         t = x.shape[0]
         cs = np.ascontiguousarray(rope_cs, dtype=np.float32)
         assert x.ndim == 2 and x.shape[1] == self.graph.n_input and cs.size == t * self.cs_stride
-        hidden = np.empty((t, self.graph.n_hidden), dtype=np.float32)
+        hidden = np.empty((t, self.graph.n_hidden), dtype=np.float32) if hidden_out is None else hidden_out
+        assert hidden.dtype == np.float32 and hidden.flags["C_CONTIGUOUS"] and hidden.shape == (t, self.graph.n_hidden)
         logits = np.empty((t, self.graph.logits[1]), dtype=np.float32) if want_logits and self.graph.logits else None
         self._be._check(self._be._L.b2_plan_step_multi(self._be._ctx, self.handle, pos, t, x.ctypes.data, cs.ctypes.data, hidden.ctypes.data,
                                                        logits.ctypes.data if logits is not None else None))
