@@ -304,8 +304,10 @@ cudaError_t launch_attend_rows(const float* q, float* out, size_t stride, uint32
 bool norm_rows_supports(uint32_t n, const float* x, const float* out, const float* w, size_t x_stride, size_t out_stride);
 cudaError_t launch_norm_rows(const float* x, size_t x_stride, float* out, size_t out_stride, const float* w, const DecNorm& p, uint32_t rows,
                              void* x16, float* unscale, cudaStream_t st);
+// With x16 / unscale (glu_rows_f16_supports(n)) the rows also leave as the f16 operands launch_to_f16 would make of the result.
+bool glu_rows_f16_supports(uint32_t n);
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
-                            uint32_t rows, int gelu, cudaStream_t st);
+                            uint32_t rows, int gelu, cudaStream_t st, void* x16 = nullptr, float* unscale = nullptr);
 // dst[r][i] (+)= src[r][i] for i < n (a multiple of 4; 16-byte aligned rows).
 cudaError_t launch_rows_op(float* dst, size_t dst_stride, const float* src, size_t src_stride, uint32_t n, uint32_t rows, bool add,
                            cudaStream_t st);

@@ -987,8 +987,19 @@ int DecodePlanImpl::run_prefill(cudaStream_t st, size_t pos, size_t t, std::stri
                 if (o.pair) {
                     e = gemm(o.w, tmp_a_, n_out);
                     if (e == cudaSuccess) e = gemm(o.w2, tmp_b_, n_out);
-                    if (e == cudaSuccess) e = launch_glu_rows(tmp_a_, n_out, tmp_b_, n_out, o.y, ld, (uint32_t)n_out, rows, o.mode == B2_MODE_GELU_PAIR, st);
+                    // a product right behind the pair that reads exactly its output gets its f16 rows from the activation kernel
+                    // (both GEMMs above have read the scratch rows by then: the kernel is an ordinary launch behind them)
+                    const Op* nx = i + 1 < ops_.size() ? &ops_[i + 1] : nullptr;
+                    const bool feeds = nx && nx->kind == B2_OP_LINEAR && nx->x == o.y && nx->w.n_in == n_out && glu_rows_f16_supports((uint32_t)n_out);
+                    if (e == cudaSuccess)
+                        e = launch_glu_rows(tmp_a_, n_out, tmp_b_, n_out, o.y, ld, (uint32_t)n_out, rows, o.mode == B2_MODE_GELU_PAIR, st,
+                                            feeds ? x16_ : nullptr, unscale_);
                     count++;
+                    if (feeds && e == cudaSuccess) {
+                        x16_src = o.y;
+                        x16_k = n_out;
+                        break;  // (the overlap check below would forget the rows just made)
+                    }
                 } else if (o.mode == B2_MODE_STORE && ((uintptr_t)o.y & 15) == 0) {
                     e = gemm(o.w, o.y, ld);
                 } else {

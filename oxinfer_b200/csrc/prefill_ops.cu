@@ -184,6 +184,67 @@ __global__ void __launch_bounds__(256) glu_rows_kernel(const float* __restrict__
     *(float4*)(out + r * out_stride + i) = make_float4(o[0], o[1], o[2], o[3]);
 }
 
+// act(g) * u of a whole row by one CTA, the row in registers (n <= 16384): the f32 result and, with x16, the f16 operand
+// rows of the product behind it with their power-of-two row factor (what to_f16_rows_kernel makes of the f32 row), so that
+// product needs no conversion launch and the row is not read again.
+constexpr int GLU_ROW_V = 16;
+__global__ void __launch_bounds__(256) glu_rows_f16_kernel(const float* __restrict__ g, size_t g_stride, const float* __restrict__ u, size_t u_stride,
+                                                           float* __restrict__ out, size_t out_stride, uint32_t n, int gelu,
+                                                           __half* __restrict__ x16, float* __restrict__ unscale) {
+    __shared__ float red[8];
+    const size_t r = blockIdx.x;
+    const uint32_t n4 = n / 4;
+    float4 v[GLU_ROW_V];
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < GLU_ROW_V; j++) {
+        const uint32_t i = threadIdx.x + 256 * j;
+        v[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < n4) {
+            const float4 a4 = ((const float4*)(g + r * g_stride))[i], u4 = ((const float4*)(u + r * u_stride))[i];
+            const float a[4] = {a4.x, a4.y, a4.z, a4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {  // the arithmetic of glu_rows_kernel
+                float t;
+                if (gelu) {
+                    const float K2 = 2.0f * 0.7978846f;
+                    const float z = K2 * (a[e] + 0.044715f * a[e] * a[e] * a[e]);
+                    t = a[e] / (1.0f + expf(-z));
+                } else {
+                    t = a[e] / (1.0f + expf(-a[e]));
+                }
+                o[e] = t * uu[e];
+                mx = fmaxf(mx, fabsf(o[e]));
+            }
+            v[j] = make_float4(o[0], o[1], o[2], o[3]);
+            ((float4*)(out + r * out_stride))[i] = v[j];
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    float sc = 1.0f, inv = 1.0f;
+    if (mx > 0.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);
+        const int up = min(100, max(-100, 15 - e));
+        sc = ldexpf(1.0f, up);
+        inv = ldexpf(1.0f, -up);
+    }
+    __half* h = x16 + r * n;
+#pragma unroll
+    for (int j = 0; j < GLU_ROW_V; j++) {
+        const uint32_t i = threadIdx.x + 256 * j;
+        if (i < n4) *(uint2*)(h + 4 * (size_t)i) = make_uint2(pack_h2f(v[j].x * sc, v[j].y * sc), pack_h2f(v[j].z * sc, v[j].w * sc));
+    }
+    if (threadIdx.x == 0) unscale[r] = inv;
+}
+
 template <bool ADD>
 __global__ void __launch_bounds__(256) rows_op_kernel(float* __restrict__ dst, size_t dst_stride, const float* __restrict__ src, size_t src_stride,
                                                       uint32_t n) {
@@ -465,10 +526,17 @@ cudaError_t launch_norm_rows(const float* x, size_t x_stride, float* out, size_t
     return cudaGetLastError();
 }
 
+bool glu_rows_f16_supports(uint32_t n) { return n % 8 == 0 && n <= 1024 * GLU_ROW_V; }
+
 cudaError_t launch_glu_rows(const float* g, size_t g_stride, const float* u, size_t u_stride, float* out, size_t out_stride, uint32_t n,
-                            uint32_t rows, int gelu, cudaStream_t st) {
+                            uint32_t rows, int gelu, cudaStream_t st, void* x16, float* unscale) {
     if (n % 4 || g_stride % 4 || u_stride % 4 || out_stride % 4 || rows == 0 || rows > 65535 || (((uintptr_t)g | (uintptr_t)u | (uintptr_t)out) & 15))
         return cudaErrorInvalidValue;
+    if (x16) {
+        if (!glu_rows_f16_supports(n) || ((uintptr_t)x16 & 15)) return cudaErrorInvalidValue;
+        glu_rows_f16_kernel<<<rows, 256, 0, st>>>(g, g_stride, u, u_stride, out, out_stride, n, gelu, (__half*)x16, unscale);
+        return cudaGetLastError();
+    }
     glu_rows_kernel<<<dim3((n / 4 + 255) / 256, rows), 256, 0, st>>>(g, g_stride, u, u_stride, out, out_stride, n, gelu);
     return cudaGetLastError();
 }

@@ -224,3 +224,33 @@ def test_declined_graphs_and_argument_errors(backend):
     assert D.decode_plan_prefill(backend, g2, 64, 32) is None and "tensor-core" in backend.last_declined
     one.close()
     pre.close()
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("kv_f16", [False, True], ids=["f32cache", "f16cache"])
+def test_one_query_head_per_kv_head(backend, hd, kv_f16):
+    """No grouping (as many KV heads as query heads, three of them): the attention kernel's one-head-per-CTA form."""
+    nh = nkv = 3
+    nq = nh * hd
+    g = D.Graph()
+    bq, bo, ba = g.buf(3 * nq), g.buf(nq), g.buf(nq)
+    g.qk_rope(bq, bo, 0, nh, nkv, hd, hd // 2, nq, 2 * nq, False, 1e-6)
+    g.attend(bo, ba, 0, nh, nkv, hd, hd ** -0.5)
+    g.input, g.n_input, g.hidden, g.n_hidden = bq, 3 * nq, ba, nq
+    g.kv, g.rope_halves = [(nkv, hd)], [hd // 2]
+    one = D.decode_plan(backend, g, 400, kv_f16=kv_f16)
+    pre = D.decode_plan_prefill(backend, g, 400, 200, kv_f16=kv_f16)
+    assert one is not None and pre is not None, backend.last_declined
+    rng = np.random.default_rng(96 + hd)
+    inv = O.rope_inv_freq(hd, 1e4)
+    pos, t = 101, 133
+    k = rng.standard_normal((pos, nq)).astype(np.float32)
+    v = rng.standard_normal((pos, nq)).astype(np.float32)
+    one.kv_write(0, 0, k, v)
+    pre.kv_write(0, 0, k, v)
+    xs = rng.standard_normal((t, 3 * nq)).astype(np.float32)
+    h1 = one_by_one(one, pos, xs, inv)
+    hp, _ = pre.step_multi(pos, xs, rope_rows(pos, t, inv))
+    assert row_err(hp, h1.astype(np.float64)) < 2e-3
+    one.close()
+    pre.close()
