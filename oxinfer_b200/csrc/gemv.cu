@@ -168,6 +168,164 @@ gemv_kernel(WeightDev w, WeightDev w2, const float* __restrict__ x, XPlanes xp, 
     }
 }
 
+// ---- several tokens of a 4-bit product with the integer dots on the tensor cores -------------------------------------------
+// The exact products are bound by instruction issue: 0.75 dp4a per weight and token. mma.sync.m16n8k32 (u8 x s8 -> s32)
+// makes the same integer sums, which do not depend on the order of their terms: A = the nibbles of 16 weight rows over one
+// block of 32 k (a byte each), B = that block of the planes, column n = (token n / 2, plane n & 1) and, in a second
+// instruction, (token n / 2, the third plane) in the even columns. A lane (g, c) then holds, for rows g and g + 8 and token c,
+// the three plane sums of the block; the float tail per row, token and 64-group is the one-token kernel's own
+// (F::tail), fed the same integers, so the results keep their bits.
+// The one-token kernel gives the 64-group (block b, group j) to lane 4 (b % 8) + j of the row's warp, which adds its
+// groups in the order of b and then takes part in a butterfly sum. Here a CTA takes 16 rows and its warp w the blocks
+// b % 8 == w: it keeps the four accumulators 4 w + j of every (row, token) it holds, adding in the same order, and the 32
+// accumulators of a (row, token) meet in shared memory, where one thread adds them in the butterfly's order.
+__device__ __forceinline__ void imma_16832(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int IMMA_ROWS = 16, IMMA_THREADS = 256;
+
+template <class F, bool PAIR, int NT, int NP>
+__global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
+                                                                  NormScale ns, GemvMulti multi) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NM = PAIR ? 2 : 1;
+    pdl_launch_dependents();
+    const int K = (int)w.n_in, nblk = K / 256;
+    const size_t n_out = w.n_out;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const size_t row0 = (size_t)blockIdx.x * IMMA_ROWS;
+    const size_t rows_ld[2] = {min(row0 + g, n_out - 1), min(row0 + g + 8, n_out - 1)};  // rows past the end repeat the last one (never stored)
+    pdl_wait();
+    const size_t per_tok = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
+#pragma unroll
+    for (int tk = 0; tk < NT; tk++) {
+        const XPlanes xpt = tk == 0 ? xp : xplanes_at((uint8_t*)xp.planes + (size_t)tk * multi.x_stride, (size_t)K);
+        xplanes_stage(xpt, K, smem + (size_t)tk * per_tok, threadIdx.x, IMMA_THREADS);
+    }
+    float kscale[NT];
+#pragma unroll
+    for (int tk = 0; tk < NT; tk++) {
+        NormScale nt = ns;
+        if (nt.partial) nt.partial += (size_t)tk * multi.ns_stride;
+        kscale[tk] = norm_scale_factor(nt, lane);
+    }
+    __syncthreads();
+    // this lane's column of B: token g / 2, plane (g & 1) of the first instruction's two planes; the third plane in even columns
+    const bool bcol = (g >> 1) < NT;
+    const uint8_t* btok = smem + (size_t)min(g >> 1, NT - 1) * per_tok;
+    const uint8_t* bp1 = btok + (size_t)((NP == 3 ? 0 : 1) + (g & 1)) * K;
+    const uint8_t* bp2 = btok + (size_t)2 * K;
+    const bool b2col = bcol && (g & 1) == 0;
+    // this lane's token in the accumulators: c (lanes with c >= NT carry sums that are never stored)
+    const float2* sx_t = (const float2*)(smem + (size_t)min(c, NT - 1) * per_tok + 3 * (size_t)K);
+    float acc[NM][2][4];
+#pragma unroll
+    for (int m = 0; m < NM; m++)
+#pragma unroll
+        for (int r = 0; r < 2; r++) acc[m][r][0] = acc[m][r][1] = acc[m][r][2] = acc[m][r][3] = 0.0f;
+    for (int b = warp; b < nblk; b += 8) {
+        Q4Regs hd[NM][2];
+        const uint8_t* blk[NM][2];
+#pragma unroll
+        for (int m = 0; m < NM; m++)
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                blk[m][r] = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
+                hd[m][r].hdr = __ldg((const uint4*)blk[m][r]);
+            }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int k0 = b * 256 + 64 * j;
+            // B: bytes 4 c .. 4 c + 3 and 16 + 4 c .. of the block of 32, for the low (k0) and the high (k0 + 32) nibbles' blocks
+            uint32_t bl[2][2], bh[2][2];  // [instruction][register]
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int ka = k0 + 32 * h;
+                const size_t o0 = ((size_t)swz(ka >> 4) << 4) + 4 * c, o1 = ((size_t)swz((ka >> 4) + 1) << 4) + 4 * c;
+                uint32_t* dst = h ? &bh[0][0] : &bl[0][0];
+                dst[0] = bcol ? *(const uint32_t*)(bp1 + o0) : 0u;
+                dst[1] = bcol ? *(const uint32_t*)(bp1 + o1) : 0u;
+                dst[2] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o0) : 0u;
+                dst[3] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o1) : 0u;
+            }
+            const float4 sx = *(const float4*)(sx_t + (k0 >> 5));  // {scale, sum} of the two blocks of this lane's token
+#pragma unroll
+            for (int m = 0; m < NM; m++) {
+                uint32_t wq[2][2];  // [row][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    wq[r][0] = __ldg((const uint32_t*)(blk[m][r] + 16 + 32 * j + 4 * c));
+                    wq[r][1] = __ldg((const uint32_t*)(blk[m][r] + 32 + 32 * j + 4 * c));
+                }
+                int lo[2], hi[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t a[4] = {(wq[0][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[1][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[0][1] >> (4 * h)) & 0x0F0F0F0Fu,
+                                           (wq[1][1] >> (4 * h)) & 0x0F0F0F0Fu};
+                    const uint32_t(&bb)[2][2] = h ? bh : bl;
+                    int s1[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
+                    imma_16832(s1, a, bb[0][0], bb[0][1]);
+                    if (NP == 3) imma_16832(s2, a, bb[1][0], bb[1][1]);
+                    // columns 2 c, 2 c + 1 of the first instruction = this lane's token, its two planes; column 2 c of the second = the third
+                    const int va = NP == 3 ? planes_sum<3>(s1[0], s1[1], s2[0]) : planes_sum<2>(0, s1[0], s1[1]);
+                    const int vb = NP == 3 ? planes_sum<3>(s1[2], s1[3], s2[2]) : planes_sum<2>(0, s1[2], s1[3]);
+                    if (h) {
+                        hi[0] = va;
+                        hi[1] = vb;
+                    } else {
+                        lo[0] = va;
+                        lo[1] = vb;
+                    }
+                }
+                F::tail(hd[m][0], j, sx, lo[0], hi[0], acc[m][0][j]);
+                F::tail(hd[m][1], j, sx, lo[1], hi[1], acc[m][1][j]);
+            }
+        }
+    }
+    __syncthreads();  // every warp is done with the planes: their shared memory now takes the accumulators
+    float* comb = (float*)smem;  // [matrix][row 16][token 4][accumulator 32]
+    if (c < NT) {
+#pragma unroll
+        for (int m = 0; m < NM; m++)
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) comb[(((size_t)m * 16 + g + 8 * r) * 4 + c) * 32 + 4 * warp + j] = acc[m][r][j];
+    }
+    __syncthreads();
+    if (threadIdx.x < IMMA_ROWS * NT) {
+        const int r = threadIdx.x / NT, tk = threadIdx.x % NT;
+        float tot[NM];
+#pragma unroll
+        for (int m = 0; m < NM; m++) {
+            float a[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) a[i] = comb[(((size_t)m * 16 + r) * 4 + tk) * 32 + i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)  // the butterfly of warp_sum, as lane 0 sees it
+#pragma unroll
+                for (int i = 0; i < o; i++) a[i] += a[i + o];
+            float ks = kscale[0];
+#pragma unroll
+            for (int i = 1; i < NT; i++)
+                if (tk == i) ks = kscale[i];
+            tot[m] = a[0] * ks;
+        }
+        if (row0 + r < n_out) {
+            float* o = y + (size_t)tk * multi.y_stride + row0 + r;
+            if (PAIR)
+                *o = (mode == B2_MODE_SILU_PAIR ? silu(tot[0]) : gelu_tanh(tot[0])) * tot[NM - 1];
+            else if (mode == B2_MODE_STORE)
+                *o = tot[0];
+            else
+                *o += tot[0];
+        }
+    }
+}
+
 // The 4-bit formats: the same products with the weights brought in by bulk copies into per-warp rings (gemv_ring.cuh).
 // The first copies are issued before the kernel waits for the one ahead of it in the stream.
 constexpr int RING_SLOTS = 3;
@@ -529,6 +687,31 @@ static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, cons
     }
 }
 
+template <class F, int NT>
+static cudaError_t launch_imma_nt(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, cudaStream_t st, GemvMulti m, bool pdl,
+                                  NormScale ns) {
+    const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
+    const bool np2 = xp.np == 2;
+    auto kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2> : gemv4_imma_kernel<F, true, NT, 3>)
+                     : (np2 ? gemv4_imma_kernel<F, false, NT, 2> : gemv4_imma_kernel<F, false, NT, 3>);
+    const size_t per_tok = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
+    const size_t smem = std::max(per_tok * NT, (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float));
+    if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
+    const unsigned grid = (unsigned)((w.n_out + IMMA_ROWS - 1) / IMMA_ROWS);
+    return launch_k(kern, dim3(grid), dim3(IMMA_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, ns, m);
+}
+
+// B2_GEMV_IMMA=0: the several-token 4-bit products on the dp4a kernel (for A/B runs; the results are the same bits).
+static bool imma_enabled() {
+    static const bool on = env_int("B2_GEMV_IMMA", 1) != 0;
+    return on;
+}
+
+bool gemv_multi_pays(const WeightDev& w, int nt) {
+    const bool tensor = imma_enabled() && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4);
+    return gemv_multi_fits(w, nt) && nt >= (tensor ? 2 : 3);
+}
+
 bool gemv_multi_fits(const WeightDev& w, int nt) {
     const size_t per = ((w.fmt == B2_FMT_F8E4M3 ? w.n_in * 4 : xplanes_bytes(w.n_in)) + 127) / 128 * 128;
     return nt >= 1 && nt <= 4 && gemv_supports(w) && per * (size_t)nt <= 200 * 1024;
@@ -539,6 +722,14 @@ cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const flo
     const bool f8 = w.fmt == B2_FMT_F8E4M3;
     if (!gemv_multi_fits(w, nt) || mode == B2_MODE_ADD_GATED) return cudaErrorInvalidValue;  // no gate pointer travels here
     const GemvMulti m{f8 ? x_stride : xp_stride, y_stride, ns_stride};
+    if (nt >= 2 && imma_enabled() && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4)) {  // the integer dots on the tensor cores
+        const bool q4k = w.fmt == B2_FMT_Q4_K;
+        switch (nt) {
+            case 2: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 2>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 2>(w, up, xp, y, mode, st, m, pdl, ns);
+            case 3: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 3>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 3>(w, up, xp, y, mode, st, m, pdl, ns);
+            default: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 4>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 4>(w, up, xp, y, mode, st, m, pdl, ns);
+        }
+    }
     switch (nt) {
         case 1: return launch_multi_nt<1>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);
         case 2: return launch_multi_nt<2>(w, up, x, xp, y, mode, sm_count, st, m, pdl, ns);

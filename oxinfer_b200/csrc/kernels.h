@@ -198,6 +198,10 @@ cudaError_t launch_to_f16(const void* x, int x_dtype, size_t t, size_t K, void* 
                           size_t x_ld = 0);
 // Whether nt (1..4) token rows' vectors fit in shared memory together for launch_gemv_multi.
 bool gemv_multi_fits(const WeightDev& w, int nt);
+// Whether one launch for nt tokens beats nt one-token launches inside a chain of dependent launches: from two tokens on
+// for the 4-bit formats (integer dots on the tensor cores), from three for the others (their several-token kernel does a
+// token's arithmetic per token and is not the bulk-copy form).
+bool gemv_multi_pays(const WeightDev& w, int nt);
 
 // ---- gemm_f8.cu: FP8 weights x FP8 activations (tcgen05 kind::f8f6f4), 128 x 128 weight scale blocks, activations quantized
 // per token and per 128 k -----------------------------------------------------------------------------------------------

@@ -738,10 +738,9 @@ int DecodePlanImpl::run_ops_multi(cudaStream_t st, int nt, std::string& err, boo
                 break;
             case B2_OP_LINEAR: {
                 // FP8 products go token by token: their one-token kernel is the tensor-core one, and the tokens must match it.
-                // So do the products of a two-token step: the exact products are bound by instruction issue (two tokens in one
-                // launch cost two launches' arithmetic), and the one-token launches are the bulk-copy ring form inside a chain of
-                // dependent launches, which the several-token kernel is not (measured 5.2 ms together against 4.5 ms apart).
-                const bool together = nt >= 3 && o.mode != B2_MODE_ADD_GATED && o.w.fmt != B2_FMT_F8E4M3 && gemv_multi_fits(o.w, nt);
+                // So do two tokens of a Q6_K / Q8_0 product: their several-token kernel does a token's arithmetic per token, and the
+                // one-token launches are the faster form inside a chain of dependent launches (gemv_multi_pays).
+                const bool together = o.mode != B2_MODE_ADD_GATED && o.w.fmt != B2_FMT_F8E4M3 && gemv_multi_pays(o.w, nt);
                 if (together) {
                     e = launch_gemv_multi(o.w, o.pair ? &o.w2 : nullptr, o.x, block_floats_, o.xp, planes_block_, o.y, block_floats_, nt, o.mode,
                                           sm_count_, st, pdl(), o.ns, partial_block_);

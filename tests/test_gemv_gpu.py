@@ -199,3 +199,35 @@ def test_fast_planes_switch_reads_sixteen_bits(backend, fmt):
     again = np.zeros((3, n_out), np.float32)
     assert backend.matvec_rows(x, [ob.RowsJob(dev, again)])
     assert np.array_equal(again, y3)
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
+@pytest.mark.parametrize("shape", [(1000, 2048), (200, 14336), (4096, 4096), (16, 256)])
+def test_several_tokens_on_the_tensor_cores_keep_the_one_token_bits(backend, fmt, shape):
+    """Two to four tokens of a 4-bit product run their integer dots on mma.sync (u8 x s8 -> s32) and the one-token kernel's
+    float tail in its order: every row must equal its one-token row bit for bit, plain and as a SiLU pair, with all three
+    planes and with two, for row counts that are not multiples of the 16-row tiles and for K up to 14336."""
+    n_out, n_in = shape
+    ref_g, mg = make_pair(fmt, n_out, n_in, 330)
+    ref_u, _ = make_pair(fmt, n_out, n_in, 331)
+    dg, du = backend.upload(ref_g, n_out, n_in), backend.upload(ref_u, n_out, n_in)
+    x = (synth.activations(4, n_in, 332) * np.float32(0.777)).astype(np.float32)
+    try:
+        for fast in (False, True):
+            backend.set_fast_planes(fast)
+            ones = np.zeros((4, n_out), np.float32)
+            ones_p = np.zeros((4, n_out), np.float32)
+            for i in range(4):
+                assert backend.matvec_rows(x[i:i + 1], [ob.RowsJob(dg, ones[i:i + 1])])
+                assert backend.matvec_rows(x[i:i + 1], [ob.RowsJob(dg, ones_p[i:i + 1], up=du)])
+            if not fast:
+                assert row_err(ones, mg.matmul_f64(x)) < TIGHT
+            for t in (2, 3, 4):
+                y = np.full((t, n_out), np.nan, np.float32)
+                yp = np.full((t, n_out), np.nan, np.float32)
+                assert backend.matvec_rows(x[:t], [ob.RowsJob(dg, y)])
+                assert backend.matvec_rows(x[:t], [ob.RowsJob(dg, yp, up=du)])
+                assert np.array_equal(y, ones[:t]), (fast, t)
+                assert np.array_equal(yp, ones_p[:t]), (fast, t)
+    finally:
+        backend.set_fast_planes(False)
