@@ -196,8 +196,6 @@ __global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, W
     const int K = (int)w.n_in, nblk = K / 256;
     const size_t n_out = w.n_out;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
-    const size_t row0 = (size_t)blockIdx.x * IMMA_ROWS;
-    const size_t rows_ld[2] = {min(row0 + g, n_out - 1), min(row0 + g + 8, n_out - 1)};  // rows past the end repeat the last one (never stored)
     pdl_wait();
     const size_t per_tok = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
 #pragma unroll
@@ -221,108 +219,114 @@ __global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, W
     const bool b2col = bcol && (g & 1) == 0;
     // this lane's token in the accumulators: c (lanes with c >= NT carry sums that are never stored)
     const float2* sx_t = (const float2*)(smem + (size_t)min(c, NT - 1) * per_tok + 3 * (size_t)K);
-    float acc[NM][2][4];
-#pragma unroll
-    for (int m = 0; m < NM; m++)
-#pragma unroll
-        for (int r = 0; r < 2; r++) acc[m][r][0] = acc[m][r][1] = acc[m][r][2] = acc[m][r][3] = 0.0f;
-    for (int b = warp; b < nblk; b += 8) {
-        Q4Regs hd[NM][2];
-        const uint8_t* blk[NM][2];
+    float* comb = (float*)(smem + (size_t)NT * per_tok);  // [matrix][row 16][token 4][accumulator 32], behind the planes
+    const size_t groups = (n_out + IMMA_ROWS - 1) / IMMA_ROWS;
+    // The planes are staged once per CTA; the CTA then takes groups of 16 rows in turn.
+    for (size_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+        const size_t row0 = grp * IMMA_ROWS;
+        const size_t rows_ld[2] = {min(row0 + g, n_out - 1), min(row0 + g + 8, n_out - 1)};  // rows past the end repeat the last one (never stored)
+        float acc[NM][2][4];
 #pragma unroll
         for (int m = 0; m < NM; m++)
 #pragma unroll
-            for (int r = 0; r < 2; r++) {
-                blk[m][r] = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
-                hd[m][r].hdr = __ldg((const uint4*)blk[m][r]);
-            }
+            for (int r = 0; r < 2; r++) acc[m][r][0] = acc[m][r][1] = acc[m][r][2] = acc[m][r][3] = 0.0f;
+        for (int b = warp; b < nblk; b += 8) {
+            // the block's loads first, all of them in flight together: two headers and 16 words of nibbles per matrix
+            Q4Regs hd[NM][2];
+            uint32_t wq[NM][2][4][2];  // [matrix][row][group][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int k0 = b * 256 + 64 * j;
-            // B: bytes 4 c .. 4 c + 3 and 16 + 4 c .. of the block of 32, for the low (k0) and the high (k0 + 32) nibbles' blocks
-            uint32_t bl[2][2], bh[2][2];  // [instruction][register]
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int ka = k0 + 32 * h;
-                const size_t o0 = ((size_t)swz(ka >> 4) << 4) + 4 * c, o1 = ((size_t)swz((ka >> 4) + 1) << 4) + 4 * c;
-                uint32_t* dst = h ? &bh[0][0] : &bl[0][0];
-                dst[0] = bcol ? *(const uint32_t*)(bp1 + o0) : 0u;
-                dst[1] = bcol ? *(const uint32_t*)(bp1 + o1) : 0u;
-                dst[2] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o0) : 0u;
-                dst[3] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o1) : 0u;
-            }
-            const float4 sx = *(const float4*)(sx_t + (k0 >> 5));  // {scale, sum} of the two blocks of this lane's token
-#pragma unroll
-            for (int m = 0; m < NM; m++) {
-                uint32_t wq[2][2];  // [row][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
+            for (int m = 0; m < NM; m++)
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                    wq[r][0] = __ldg((const uint32_t*)(blk[m][r] + 16 + 32 * j + 4 * c));
-                    wq[r][1] = __ldg((const uint32_t*)(blk[m][r] + 32 + 32 * j + 4 * c));
-                }
-                int lo[2], hi[2];
+                    const uint8_t* blk = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
+                    hd[m][r].hdr = __ldg((const uint4*)blk);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const uint32_t a[4] = {(wq[0][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[1][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[0][1] >> (4 * h)) & 0x0F0F0F0Fu,
-                                           (wq[1][1] >> (4 * h)) & 0x0F0F0F0Fu};
-                    const uint32_t(&bb)[2][2] = h ? bh : bl;
-                    int s1[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
-                    imma_16832(s1, a, bb[0][0], bb[0][1]);
-                    if (NP == 3) imma_16832(s2, a, bb[1][0], bb[1][1]);
-                    // columns 2 c, 2 c + 1 of the first instruction = this lane's token, its two planes; column 2 c of the second = the third
-                    const int va = NP == 3 ? planes_sum<3>(s1[0], s1[1], s2[0]) : planes_sum<2>(0, s1[0], s1[1]);
-                    const int vb = NP == 3 ? planes_sum<3>(s1[2], s1[3], s2[2]) : planes_sum<2>(0, s1[2], s1[3]);
-                    if (h) {
-                        hi[0] = va;
-                        hi[1] = vb;
-                    } else {
-                        lo[0] = va;
-                        lo[1] = vb;
+                    for (int j = 0; j < 4; j++) {
+                        wq[m][r][j][0] = __ldg((const uint32_t*)(blk + 16 + 32 * j + 4 * c));
+                        wq[m][r][j][1] = __ldg((const uint32_t*)(blk + 32 + 32 * j + 4 * c));
                     }
                 }
-                F::tail(hd[m][0], j, sx, lo[0], hi[0], acc[m][0][j]);
-                F::tail(hd[m][1], j, sx, lo[1], hi[1], acc[m][1][j]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int k0 = b * 256 + 64 * j;
+                // B: bytes 4 c .. 4 c + 3 and 16 + 4 c .. of the block of 32, for the low (k0) and the high (k0 + 32) nibbles' blocks
+                uint32_t bl[2][2], bh[2][2];  // [instruction][register]
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int ka = k0 + 32 * h;
+                    const size_t o0 = ((size_t)swz(ka >> 4) << 4) + 4 * c, o1 = ((size_t)swz((ka >> 4) + 1) << 4) + 4 * c;
+                    uint32_t* dst = h ? &bh[0][0] : &bl[0][0];
+                    dst[0] = bcol ? *(const uint32_t*)(bp1 + o0) : 0u;
+                    dst[1] = bcol ? *(const uint32_t*)(bp1 + o1) : 0u;
+                    dst[2] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o0) : 0u;
+                    dst[3] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o1) : 0u;
+                }
+                const float4 sx = *(const float4*)(sx_t + (k0 >> 5));  // {scale, sum} of the two blocks of this lane's token
+#pragma unroll
+                for (int m = 0; m < NM; m++) {
+                    int lo[2], hi[2];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t a[4] = {(wq[m][0][j][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[m][1][j][0] >> (4 * h)) & 0x0F0F0F0Fu,
+                                               (wq[m][0][j][1] >> (4 * h)) & 0x0F0F0F0Fu, (wq[m][1][j][1] >> (4 * h)) & 0x0F0F0F0Fu};
+                        const uint32_t(&bb)[2][2] = h ? bh : bl;
+                        int s1[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
+                        imma_16832(s1, a, bb[0][0], bb[0][1]);
+                        if (NP == 3) imma_16832(s2, a, bb[1][0], bb[1][1]);
+                        // columns 2 c, 2 c + 1 of the first instruction = this lane's token, its two planes; column 2 c of the second = the third
+                        const int va = NP == 3 ? planes_sum<3>(s1[0], s1[1], s2[0]) : planes_sum<2>(0, s1[0], s1[1]);
+                        const int vb = NP == 3 ? planes_sum<3>(s1[2], s1[3], s2[2]) : planes_sum<2>(0, s1[2], s1[3]);
+                        if (h) {
+                            hi[0] = va;
+                            hi[1] = vb;
+                        } else {
+                            lo[0] = va;
+                            lo[1] = vb;
+                        }
+                    }
+                    F::tail(hd[m][0], j, sx, lo[0], hi[0], acc[m][0][j]);
+                    F::tail(hd[m][1], j, sx, lo[1], hi[1], acc[m][1][j]);
+                }
             }
         }
-    }
-    __syncthreads();  // every warp is done with the planes: their shared memory now takes the accumulators
-    float* comb = (float*)smem;  // [matrix][row 16][token 4][accumulator 32]
-    if (c < NT) {
+        if (c < NT) {
 #pragma unroll
-        for (int m = 0; m < NM; m++)
+            for (int m = 0; m < NM; m++)
 #pragma unroll
-            for (int r = 0; r < 2; r++)
+                for (int r = 0; r < 2; r++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) comb[(((size_t)m * 16 + g + 8 * r) * 4 + c) * 32 + 4 * warp + j] = acc[m][r][j];
-    }
-    __syncthreads();
-    if (threadIdx.x < IMMA_ROWS * NT) {
-        const int r = threadIdx.x / NT, tk = threadIdx.x % NT;
-        float tot[NM];
-#pragma unroll
-        for (int m = 0; m < NM; m++) {
-            float a[32];
-#pragma unroll
-            for (int i = 0; i < 32; i++) a[i] = comb[(((size_t)m * 16 + r) * 4 + tk) * 32 + i];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)  // the butterfly of warp_sum, as lane 0 sees it
-#pragma unroll
-                for (int i = 0; i < o; i++) a[i] += a[i + o];
-            float ks = kscale[0];
-#pragma unroll
-            for (int i = 1; i < NT; i++)
-                if (tk == i) ks = kscale[i];
-            tot[m] = a[0] * ks;
+                    for (int j = 0; j < 4; j++) comb[(((size_t)m * 16 + g + 8 * r) * 4 + c) * 32 + 4 * warp + j] = acc[m][r][j];
         }
-        if (row0 + r < n_out) {
-            float* o = y + (size_t)tk * multi.y_stride + row0 + r;
-            if (PAIR)
-                *o = (mode == B2_MODE_SILU_PAIR ? silu(tot[0]) : gelu_tanh(tot[0])) * tot[NM - 1];
-            else if (mode == B2_MODE_STORE)
-                *o = tot[0];
-            else
-                *o += tot[0];
+        __syncthreads();
+        if (threadIdx.x < IMMA_ROWS * NT) {
+            const int r = threadIdx.x / NT, tk = threadIdx.x % NT;
+            float tot[NM];
+#pragma unroll
+            for (int m = 0; m < NM; m++) {
+                float a[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) a[i] = comb[(((size_t)m * 16 + r) * 4 + tk) * 32 + i];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)  // the butterfly of warp_sum, as lane 0 sees it
+#pragma unroll
+                    for (int i = 0; i < o; i++) a[i] += a[i + o];
+                float ks = kscale[0];
+#pragma unroll
+                for (int i = 1; i < NT; i++)
+                    if (tk == i) ks = kscale[i];
+                tot[m] = a[0] * ks;
+            }
+            if (row0 + r < n_out) {
+                float* o = y + (size_t)tk * multi.y_stride + row0 + r;
+                if (PAIR)
+                    *o = (mode == B2_MODE_SILU_PAIR ? silu(tot[0]) : gelu_tanh(tot[0])) * tot[NM - 1];
+                else if (mode == B2_MODE_STORE)
+                    *o = tot[0];
+                else
+                    *o += tot[0];
+            }
         }
+        __syncthreads();  // the accumulators' shared memory is free for the next group
     }
 }
 
@@ -688,17 +692,21 @@ static cudaError_t launch_multi_nt(const WeightDev& w, const WeightDev* up, cons
 }
 
 template <class F, int NT>
-static cudaError_t launch_imma_nt(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, cudaStream_t st, GemvMulti m, bool pdl,
-                                  NormScale ns) {
+static cudaError_t launch_imma_nt(const WeightDev& w, const WeightDev* up, XPlanes xp, float* y, int mode, int sm_count, cudaStream_t st, GemvMulti m,
+                                  bool pdl, NormScale ns) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     const bool np2 = xp.np == 2;
     auto kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2> : gemv4_imma_kernel<F, true, NT, 3>)
                      : (np2 ? gemv4_imma_kernel<F, false, NT, 2> : gemv4_imma_kernel<F, false, NT, 3>);
     const size_t per_tok = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
-    const size_t smem = std::max(per_tok * NT, (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float));
+    const size_t smem = per_tok * NT + (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float);
+    if (smem > 224 * 1024) return cudaErrorInvalidValue;
     if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
-    const unsigned grid = (unsigned)((w.n_out + IMMA_ROWS - 1) / IMMA_ROWS);
-    return launch_k(kern, dim3(grid), dim3(IMMA_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, ns, m);
+    const size_t groups = (w.n_out + IMMA_ROWS - 1) / IMMA_ROWS;
+    size_t per_sm = (size_t)(224 * 1024) / (smem + 1024);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+    const size_t grid = std::min(groups, (size_t)sm_count * per_sm);
+    return launch_k(kern, dim3((unsigned)grid), dim3(IMMA_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, ns, m);
 }
 
 // B2_GEMV_IMMA=0: the several-token 4-bit products on the dp4a kernel (for A/B runs; the results are the same bits).
@@ -722,12 +730,13 @@ cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const flo
     const bool f8 = w.fmt == B2_FMT_F8E4M3;
     if (!gemv_multi_fits(w, nt) || mode == B2_MODE_ADD_GATED) return cudaErrorInvalidValue;  // no gate pointer travels here
     const GemvMulti m{f8 ? x_stride : xp_stride, y_stride, ns_stride};
-    if (nt >= 2 && imma_enabled() && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4)) {  // the integer dots on the tensor cores
+    const size_t imma_smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 * (size_t)nt + 2 * IMMA_ROWS * 4 * 32 * sizeof(float);
+    if (nt >= 2 && imma_enabled() && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && imma_smem <= 224 * 1024) {  // the integer dots on the tensor cores
         const bool q4k = w.fmt == B2_FMT_Q4_K;
         switch (nt) {
-            case 2: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 2>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 2>(w, up, xp, y, mode, st, m, pdl, ns);
-            case 3: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 3>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 3>(w, up, xp, y, mode, st, m, pdl, ns);
-            default: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 4>(w, up, xp, y, mode, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 4>(w, up, xp, y, mode, st, m, pdl, ns);
+            case 2: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 2>(w, up, xp, y, mode, sm_count, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 2>(w, up, xp, y, mode, sm_count, st, m, pdl, ns);
+            case 3: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 3>(w, up, xp, y, mode, sm_count, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 3>(w, up, xp, y, mode, sm_count, st, m, pdl, ns);
+            default: return q4k ? launch_imma_nt<FmtQ4K_T<3>, 4>(w, up, xp, y, mode, sm_count, st, m, pdl, ns) : launch_imma_nt<FmtMLX4_T<3>, 4>(w, up, xp, y, mode, sm_count, st, m, pdl, ns);
         }
     }
     switch (nt) {
