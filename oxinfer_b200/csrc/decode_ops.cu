@@ -113,12 +113,28 @@ __global__ void __launch_bounds__(256) glu_kernel(const float* __restrict__ g, c
 }
 
 // ---- attention: grid (KV heads, splits), one unit per CTA (attend_core.cuh) --------------------------------
+// blockIdx.z: the token of a step of several tokens (AttnTokens: its queries, outputs and planes a fixed stride behind token
+// 0's, its own step words, partials and counters); the keys of all the step's tokens are in the caches already.
 template <int HD, int G, typename T>
 __global__ void __launch_bounds__(ATT_THREADS) attend_kernel(const float* __restrict__ q, T* kc, T* vc, float* __restrict__ out, float* part,
                                                              uint32_t* counters, const uint32_t* __restrict__ sp, DecAttn p, XPlanes xp,
-                                                             uint32_t* status, FusedRope fr) {
+                                                             uint32_t* status, FusedRope fr, AttnTokens at) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
+    if (blockIdx.z) {
+        const size_t z = blockIdx.z;
+        q += z * at.act_stride;
+        out += z * at.act_stride;
+        part += z * at.part_stride;
+        counters += z * p.nkv;
+        sp += 4 * z;
+        if (fr.qkv) fr.qkv += z * at.act_stride;
+        if (xp.planes) {
+            xp.planes = (int8_t*)((uint8_t*)xp.planes + z * at.planes_stride);
+            xp.sx = (float2*)((uint8_t*)xp.sx + z * at.planes_stride);
+            xp.v16 = (int32_t*)((uint8_t*)xp.v16 + z * at.planes_stride);
+        }
+    }
     // the step words (position, RoPE table base) were written before this step's graph was launched
     attend_unit<HD, G, T>(smem, threadIdx.x, 0, blockIdx.x, blockIdx.y, gridDim.y, sp[0], q, kc, vc, out, part, counters, p, xp, status, nullptr,
                           fr.qkv ? &fr : nullptr, sp[1], true);
@@ -336,31 +352,36 @@ size_t attend_part_floats(uint32_t nh, uint32_t hd) { return (size_t)nh * ATT_MA
 
 template <int HD, int G, typename T>
 static cudaError_t attend_t(const float* q, void* kc, void* vc, float* out, float* part, uint32_t* counters, const uint32_t* sp,
-                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr) {
+                            const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr, const AttnTokens& at) {
     constexpr size_t smem = attend_smem<HD, G, T>();
     if (cudaError_t e = ensure_dynamic_smem((const void*)attend_kernel<HD, G, T>, smem, 0); e != cudaSuccess) return e;
     uint32_t splits = (p.max_len + ATT_TILE - 1) / ATT_TILE;
     if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
     if (splits == 0) splits = 1;
-    dim3 grid(p.nkv, splits);
-    return launch_k(attend_kernel<HD, G, T>, grid, dim3(ATT_THREADS), smem, st, pdl, q, (T*)kc, (T*)vc, out, part, counters, sp, p, xp, status, fr);
+    dim3 grid(p.nkv, splits, (unsigned)std::max(1, at.n));
+    return launch_k(attend_kernel<HD, G, T>, grid, dim3(ATT_THREADS), smem, st, pdl, q, (T*)kc, (T*)vc, out, part, counters, sp, p, xp, status, fr, at);
 }
 
 template <int HD, typename T>
 static cudaError_t attend_g(uint32_t g, const float* q, void* kc, void* vc, float* out, float* part, uint32_t* counters,
-                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr) {
+                            const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope& fr,
+                            const AttnTokens& at) {
     switch (g) {
-        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
-        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
-        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
-        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+        case 1: return attend_t<HD, 1, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
+        case 2: return attend_t<HD, 2, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
+        case 4: return attend_t<HD, 4, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
+        case 8: return attend_t<HD, 8, T>(q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_attend(const float* q, void* kc, void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
-                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope* frp) {
+                          const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl, const FusedRope* frp,
+                          const AttnTokens* atp) {
     if (!attend_supports(p.nh, p.nkv, p.hd)) return cudaErrorInvalidValue;
+    AttnTokens at{};
+    if (atp) at = *atp;
+    if (at.n > 1 && frp) return cudaErrorInvalidValue;  // the tokens of one launch must find each other's keys in the caches
     FusedRope fr{};
     if (frp) {
         fr = *frp;
@@ -369,10 +390,10 @@ cudaError_t launch_attend(const float* q, void* kc, void* vc, int kv_f16, float*
     }
     const uint32_t g = p.nh / p.nkv;
     if (p.hd == 64)
-        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr)
-                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
-    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr)
-                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr);
+        return kv_f16 ? attend_g<64, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at)
+                      : attend_g<64, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
+    return kv_f16 ? attend_g<128, __half>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at)
+                  : attend_g<128, float>(g, q, kc, vc, out, part, counters, sp, p, xp, status, st, pdl, fr, at);
 }
 
 cudaError_t launch_glu(const float* g, const float* u, float* out, uint32_t n, int gelu, cudaStream_t st, bool pdl) {

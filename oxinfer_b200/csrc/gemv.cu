@@ -34,28 +34,39 @@ constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 
 // ---- activation planes ----------------------------------------------------------------------
-__global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, XPlanes out) {
+// blockIdx.y: the token of a step of several tokens (its vector, planes and norm sums a fixed stride behind token 0's).
+struct TokenStrides {
+    size_t x, planes, partial;  // floats, bytes, floats
+};
+__device__ __forceinline__ XPlanes planes_of_token(XPlanes p, size_t bytes) {
+    p.planes = (int8_t*)((uint8_t*)p.planes + bytes);
+    p.sx = (float2*)((uint8_t*)p.sx + bytes);
+    p.v16 = (int32_t*)((uint8_t*)p.v16 + bytes);
+    return p;
+}
+
+__global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, int K, XPlanes out, TokenStrides ts) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
     if (warp >= K / 32) return;
-    xplanes_block(x[warp * 32 + lane], warp, lane, K, out);
+    xplanes_block(x[(size_t)blockIdx.y * ts.x + warp * 32 + lane], warp, lane, K, planes_of_token(out, (size_t)blockIdx.y * ts.planes));
 }
 
 // planes(x * pre * w) without the norm factor, and each block's sum of squares of x * pre (see NormScale). A warp per block.
 __global__ void __launch_bounds__(256) norm_planes_kernel(const float* __restrict__ x, const float* __restrict__ w, float pre, int K, XPlanes out,
-                                                          float* __restrict__ partial) {
+                                                          float* __restrict__ partial, TokenStrides ts) {
     pdl_launch_dependents();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const float wv = (w && warp < K / 32) ? w[warp * 32 + lane] : 1.0f;  // the weights do not depend on the kernel ahead
     pdl_wait();
     if (warp >= K / 32) return;
-    const float v = x[warp * 32 + lane] * pre;
+    const float v = x[(size_t)blockIdx.y * ts.x + warp * 32 + lane] * pre;
     float s = v * v;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) partial[warp] = s;
-    xplanes_block(v * wv, warp, lane, K, out);
+    if (lane == 0) partial[(size_t)blockIdx.y * ts.partial + warp] = s;
+    xplanes_block(v * wv, warp, lane, K, planes_of_token(out, (size_t)blockIdx.y * ts.planes));
 }
 
 // The kernel's order of events, chosen for back-to-back launches of a decode step:
@@ -631,9 +642,10 @@ bool gemv_supports(const WeightDev& w) {
     }
 }
 
-cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl) {
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl, int tokens, size_t x_stride, size_t planes_stride) {
     unsigned warps = (unsigned)(K / 32);
-    return launch_k(xplanes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, (int)K, out);
+    if (tokens < 1) return cudaErrorInvalidValue;
+    return launch_k(xplanes_kernel, dim3((warps + 7) / 8, (unsigned)tokens), dim3(256), 0, st, pdl, x, (int)K, out, TokenStrides{x_stride, planes_stride, 0});
 }
 
 __global__ void __launch_bounds__(256) xplanes_rows_kernel(const float* __restrict__ x, int rows, int K, uint8_t* planes, size_t stride) {
@@ -747,10 +759,12 @@ cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const flo
     }
 }
 
-cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl) {
-    if (K == 0 || K % 32) return cudaErrorInvalidValue;
+cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl, int tokens,
+                               size_t x_stride, size_t planes_stride, size_t partial_stride) {
+    if (K == 0 || K % 32 || tokens < 1) return cudaErrorInvalidValue;
     unsigned warps = (unsigned)(K / 32);
-    return launch_k(norm_planes_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, w, pre, (int)K, out, partial);
+    return launch_k(norm_planes_kernel, dim3((warps + 7) / 8, (unsigned)tokens), dim3(256), 0, st, pdl, x, w, pre, (int)K, out, partial,
+                    TokenStrides{x_stride, planes_stride, partial_stride});
 }
 
 static int ring_level() {  // B2_GEMV_RING: 0 never, 1 in dependent-launch chains (the default), 2 for every launch

@@ -87,7 +87,9 @@ __host__ __device__ inline XPlanes xplanes_at(void* base, size_t K) {
     p.np = 0;
     return p;
 }
-cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false);
+// tokens > 1: token i's vector x_stride floats and its planes planes_stride bytes behind token 0's, one launch for all.
+cudaError_t launch_xplanes(const float* x, size_t K, XPlanes out, cudaStream_t st, bool pdl = false, int tokens = 1, size_t x_stride = 0,
+                           size_t planes_stride = 0);
 // A vector whose RMS-norm factor is applied after the product instead of before the split: the planes hold the split of
 // x * w (no factor), `partial` holds the sum of squares of every block of 32 of x, and the product kernel multiplies its
 // sums by k = 1 / sqrt(sum(partial) * inv_n + eps). The split of a block does not depend on a common factor, so this
@@ -99,7 +101,9 @@ struct NormScale {
     float inv_n, eps;
 };
 // planes(x * pre * w) and the blocks' sums of squares of x * pre; K a multiple of 32, w may be null.
-cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl = false);
+// tokens > 1 as for launch_xplanes; token i's sums partial_stride floats behind token 0's.
+cudaError_t launch_norm_planes(const float* x, const float* w, float pre, size_t K, XPlanes out, float* partial, cudaStream_t st, bool pdl = false,
+                               int tokens = 1, size_t x_stride = 0, size_t planes_stride = 0, size_t partial_stride = 0);
 // What a product may do with its finished output, so that the kernel which would split it for the next product is not
 // launched: the CTAs then own whole blocks of 32 consecutive rows (four per warp), the warps leave their results in
 // shared memory, and after a CTA barrier one warp writes the planes of y * pre * w (w may be null) and, with `partial`,
@@ -279,10 +283,17 @@ struct FusedRope {
     const float* cs_table;
     DecRope r;
 };
+// Several tokens of a step in one launch (only without FusedRope: every token's key and value must be in the caches
+// already): token i's queries / outputs act_stride floats behind token 0's, its planes planes_stride bytes, its partials
+// part_stride floats, its counters nkv words, its step words 4 words.
+struct AttnTokens {
+    int n;  // 0 or 1: one token
+    size_t act_stride, planes_stride, part_stride;
+};
 // counters: nkv zeroed words (left zero by every launch); status: set to 1 if a bounded wait gave up.
 cudaError_t launch_attend(const float* q, void* kc, void* vc, int kv_f16, float* out, float* part, uint32_t* counters,
                           const uint32_t* sp, const DecAttn& p, XPlanes xp, uint32_t* status, cudaStream_t st, bool pdl = false,
-                          const FusedRope* fr = nullptr);
+                          const FusedRope* fr = nullptr, const AttnTokens* tokens = nullptr);
 // Host-order rows [n][nkv][hd] f32 <-> cache rows pos0 .. pos0 + n - 1.
 cudaError_t launch_kv_rows(float* rows, void* cache, int kv_f16, bool to_cache, uint32_t nkv, uint32_t hd, uint32_t max_len, uint32_t pos0,
                            uint32_t n, cudaStream_t st);

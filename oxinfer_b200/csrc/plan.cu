@@ -583,8 +583,9 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     }
 
     // ---- scratch ------------------------------------------------------------------------------------
-    if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, attend_part_floats(max_nh, max_hd) * sizeof(float)), "cudaMalloc(attention partials)");
-    size_t n_words = 8 + std::max<uint32_t>(max_nkv, 1) + 4 * T;
+    p->part_stride_ = max_nh ? attend_part_floats(max_nh, max_hd) : 0;
+    if (max_nh) PLAN_CUDA(cudaMalloc((void**)&p->part_, (prefill ? 1 : T) * p->part_stride_ * sizeof(float)), "cudaMalloc(attention partials)");
+    size_t n_words = 8 + T * std::max<uint32_t>(max_nkv, 1) + 4 * T;  // (a prefill plan's T counters are unused: a few KB)
     PLAN_CUDA(cudaMalloc((void**)&p->words_, n_words * 4), "cudaMalloc(step words)");
     PLAN_CUDA(cudaMemset(p->words_, 0, n_words * 4), "cudaMemset(step words)");
     if (p->has_exchange_) {
@@ -595,7 +596,8 @@ int DecodePlanImpl::create(const b2_graph* g, const std::function<const WeightDe
     p->status_ = p->words_ + 4;
     p->argmax_counter_ = p->words_ + 5;
     p->att_counters_ = p->words_ + 8;
-    p->sp_multi_ = p->words_ + 8 + std::max<uint32_t>(max_nkv, 1);
+    p->n_counters_ = T * std::max<uint32_t>(max_nkv, 1);
+    p->sp_multi_ = p->words_ + 8 + p->n_counters_;
     size_t table = (size_t)std::max<uint32_t>(p->cs_stride_, 1) * g->max_len;
     PLAN_CUDA(cudaMalloc((void**)&p->rope_table_, table * sizeof(float)), "cudaMalloc(rope table)");
     PLAN_CUDA(cudaMemset(p->rope_table_, 0, table * sizeof(float)), "cudaMemset(rope table)");
@@ -729,12 +731,12 @@ int DecodePlanImpl::run_ops_multi(cudaStream_t st, int nt, std::string& err, boo
                 for (int tk = 0; tk < nt && e == cudaSuccess; tk++)
                     e = launch_norm(A(o.x, tk), A(o.y, tk), o.p0, o.norm, o.rows, P(o.xp, tk), st, pdl());
                 break;
-            case OP_XPLANES:
-                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) e = launch_xplanes(A(o.x, tk), o.n, P(o.xp, tk), st, pdl());
+            case OP_XPLANES:  // one launch for all tokens (a block of a token's planes is made by one warp either way: the same bits)
+                e = launch_xplanes(o.x, o.n, o.xp, st, pdl(), nt, block_floats_, planes_block_);
                 break;
             case OP_NORM_DEFERRED:
-                for (int tk = 0; tk < nt && e == cudaSuccess; tk++)
-                    e = launch_norm_planes(A(o.x, tk), o.p0, o.norm.pre, o.norm.n, P(o.xp, tk), const_cast<float*>(N(o.ns, tk).partial), st, pdl());
+                e = launch_norm_planes(o.x, o.p0, o.norm.pre, o.norm.n, o.xp, const_cast<float*>(o.ns.partial), st, pdl(), nt, block_floats_, planes_block_,
+                                       partial_block_);
                 break;
             case B2_OP_LINEAR: {
                 // FP8 products go token by token: their one-token kernel is the tensor-core one, and the tokens must match it.
@@ -745,12 +747,12 @@ int DecodePlanImpl::run_ops_multi(cudaStream_t st, int nt, std::string& err, boo
                     e = launch_gemv_multi(o.w, o.pair ? &o.w2 : nullptr, o.x, block_floats_, o.xp, planes_block_, o.y, block_floats_, nt, o.mode,
                                           sm_count_, st, pdl(), o.ns, partial_block_);
                     // the split the one-token product does in its epilogue (the same bits as the kernels of their own)
-                    for (int tk = 0; tk < nt && e == cudaSuccess && o.epi.out.planes; tk++) {
+                    if (e == cudaSuccess && o.epi.out.planes) {
                         if (o.epi.partial)
-                            e = launch_norm_planes(A(o.y, tk), o.epi.w, o.epi.pre, o.w.n_out, P(o.epi.out, tk),
-                                                   o.epi.partial + (size_t)tk * partial_block_, st, pdl());
+                            e = launch_norm_planes(o.y, o.epi.w, o.epi.pre, o.w.n_out, o.epi.out, o.epi.partial, st, pdl(), nt, block_floats_, planes_block_,
+                                                   partial_block_);
                         else
-                            e = launch_xplanes(A(o.y, tk), o.w.n_out, P(o.epi.out, tk), st, pdl());
+                            e = launch_xplanes(o.y, o.w.n_out, o.epi.out, st, pdl(), nt, block_floats_, planes_block_);
                     }
                     break;
                 }
@@ -765,25 +767,28 @@ int DecodePlanImpl::run_ops_multi(cudaStream_t st, int nt, std::string& err, boo
                 }
                 break;
             }
-            case B2_OP_QK_ROPE:
-                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) {
-                    e = launch_qk_rope(A(o.x, tk), A(o.y, tk), kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_multi_ + 4 * tk, o.rope, st,
-                                       false);
-                    first = false;
+            case B2_OP_QK_ROPE:  // all tokens in one launch (the one-token arithmetic per head)
+                e = launch_qk_rope_rows(o.x, o.y, block_floats_, (uint32_t)nt, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.p0, o.p1, rope_table_, sp_multi_, o.rope,
+                                        st);
+                first = false;
+                count++;
+                break;
+            case B2_OP_ATTEND: {
+                // Where the one-token plan rotates and appends inside the attention kernel, the tokens' keys and values go into
+                // the caches first (the same arithmetic in a kernel of its own); then one launch attends for all tokens.
+                if (o.fr.qkv) {
+                    e = launch_qk_rope_rows(o.fr.qkv, o.x, block_floats_, (uint32_t)nt, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, nullptr, nullptr, rope_table_,
+                                            sp_multi_, o.fr.r, st);
                     count++;
                 }
+                const AttnTokens at{nt, block_floats_, planes_block_, part_stride_};
+                if (e == cudaSuccess)
+                    e = launch_attend(o.x, kv_[o.kv].k, kv_[o.kv].v, kv_f16_, o.y, part_, att_counters_, sp_multi_, o.attn, o.xp, status_, st, false, nullptr,
+                                      &at);
+                first = false;
+                count++;
                 break;
-            case B2_OP_ATTEND:
-                for (int tk = 0; tk < nt && e == cudaSuccess; tk++) {
-                    FusedRope fr = o.fr;
-                    fr.qkv = A(o.fr.qkv, tk);
-                    fr.cs_table = rope_table_;
-                    e = launch_attend(A(o.x, tk), kv_[o.kv].k, kv_[o.kv].v, kv_f16_, A(o.y, tk), part_, att_counters_, sp_multi_ + 4 * tk, o.attn,
-                                      P(o.xp, tk), status_, st, false, o.fr.qkv ? &fr : nullptr);
-                    first = false;
-                    count++;
-                }
-                break;
+            }
             case B2_OP_GLU:
                 for (int tk = 0; tk < nt && e == cudaSuccess; tk++) e = launch_glu(A(o.x, tk), A(o.z, tk), A(o.y, tk), o.n, o.gelu, st, pdl());
                 break;
@@ -829,7 +834,7 @@ int DecodePlanImpl::check_status(std::string& err) {
     PLAN_CUDA(cudaMemcpy(&s, status_, 4, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
     if (s) {
         cudaMemset(status_, 0, 4);
-        cudaMemset(att_counters_, 0, 4 * kv_.size());  // a CTA that gave up never counted itself
+        cudaMemset(att_counters_, 0, 4 * n_counters_);  // a CTA that gave up never counted itself
         err = s == 4 ? "[b200qmm: plan: a peer did not arrive at an exchange within the time limit]"
                      : "[b200qmm: plan: an attention kernel's wait on its copy ran into the time limit]";
         return B2_ERR_TIMEOUT;

@@ -81,6 +81,8 @@ class DecodePlanImpl {
     std::vector<uint32_t> cs_off_;        // start of each RoPE table's values inside a row of the device table
     cudaGraphExec_t multi_exec_[5] = {};  // [nt], nt = 2 .. tokens
     uint64_t multi_launches_[5] = {};     // kernels of a step of nt tokens
+    size_t part_stride_ = 0;              // floats of attention partials per token
+    size_t n_counters_ = 0;               // attention counter words (KV heads x tokens)
     // prefill plans
     bool prefill_ = false;
     bool loop_attend_ = false;       // B2_PREFILL_ATTEND=loop: the one-token attention kernel token by token (for comparisons)
