@@ -527,14 +527,18 @@ class Backend {
             }
             return B2_OK;
         }
-        if (t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev) && !(fp8_act && w->dev.fmt == B2_FMT_F8E4M3)) {
+        // Two to eight tokens of a 4-bit format: four at a time through the several-token matrix-vector kernel (its integer
+        // dots on the tensor cores), every row equal to its one-token row bit for bit.
+        const bool few_4bit = t >= 2 && t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && (w->dev.fmt == B2_FMT_Q4_K || w->dev.fmt == B2_FMT_MLX4) &&
+                              gemv_supports(w->dev) && gemv_multi_pays(w->dev, (int)std::min<size_t>(t, 4));
+        if (!few_4bit && t <= 8 && x_dtype == B2_F32 && y_dtype == B2_F32 && gemv_supports(w->dev) && !(fp8_act && w->dev.fmt == B2_FMT_F8E4M3)) {
             for (size_t i = 0; i < t; i++) {
                 int rc = matvec_dev(h, 0, (const float*)x + i * K, (float*)y + i * w->dev.n_out, B2_MODE_STORE, nullptr);
                 if (rc) return rc;
             }
             return B2_OK;
         }
-        if (rows_path(w->dev) && x_dtype == B2_F32 && y_dtype == B2_F32 && (exact || !gemm_tc_supports(w->dev, t))) {
+        if (few_4bit || (rows_path(w->dev) && x_dtype == B2_F32 && y_dtype == B2_F32 && (exact || !gemm_tc_supports(w->dev, t)))) {
             // Q6_K / Q8_0 under the exact switch (or at a shape the tensor-core kernel does not take): the tokens go four at a
             // time through the multi-row matrix-vector kernel (the weights are read once per four tokens; every row equals its
             // one-token result bit for bit).

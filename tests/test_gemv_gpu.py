@@ -231,3 +231,23 @@ def test_several_tokens_on_the_tensor_cores_keep_the_one_token_bits(backend, fmt
                 assert np.array_equal(yp, ones_p[:t]), (fast, t)
     finally:
         backend.set_fast_planes(False)
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "mlx4"])
+def test_matmul_of_two_to_eight_tokens_keeps_the_one_token_bits(backend, fmt):
+    """Backend::matmul below the tensor-core GEMM's range (t <= 8): the 4-bit formats run four tokens at a time through the
+    several-token kernel; every row equals what a one-token call gives."""
+    n_out, n_in = 1000, 2048
+    ref, m = make_pair(fmt, n_out, n_in, 360)
+    dev = backend.upload(ref, n_out, n_in)
+    x = synth.activations(8, n_in, 361)
+    ones = np.zeros((8, n_out), np.float32)
+    for i in range(8):
+        assert backend.matmul(x[i:i + 1], [ob.Job(dev, ones[i:i + 1])])
+    assert row_err(ones, m.matmul_f64(x)) < TIGHT
+    for t in (2, 3, 5, 8):
+        y = np.full((t, n_out), np.nan, np.float32)
+        before = backend.launch_count()
+        assert backend.matmul(x[:t], [ob.Job(dev, y)])
+        assert backend.launch_count() - before == 1 + (t + 3) // 4   # the planes of all rows, then a product per four rows
+        assert np.array_equal(y, ones[:t]), t
