@@ -198,21 +198,23 @@ __device__ __forceinline__ void imma_16832(int (&c)[4], const uint32_t (&a)[4], 
 
 constexpr int IMMA_ROWS = 16, IMMA_THREADS = 256;
 
-template <class F, bool PAIR, int NT, int NP>
-__global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
+// HALVES = 2: 16 warps, two groups of 16 rows at a time (for vectors whose planes leave room for one CTA per SM only).
+template <class F, bool PAIR, int NT, int NP, int HALVES>
+__global__ void __launch_bounds__(IMMA_THREADS * HALVES) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
                                                                   NormScale ns, GemvMulti multi) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NM = PAIR ? 2 : 1;
     pdl_launch_dependents();
     const int K = (int)w.n_in, nblk = K / 256;
     const size_t n_out = w.n_out;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int half = (int)(threadIdx.x >> 8), tid = (int)(threadIdx.x & 255);  // the half's own 8 warps
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     pdl_wait();
     const size_t per_tok = (xplanes_bytes((size_t)K) + 127) / 128 * 128;
 #pragma unroll
     for (int tk = 0; tk < NT; tk++) {
         const XPlanes xpt = tk == 0 ? xp : xplanes_at((uint8_t*)xp.planes + (size_t)tk * multi.x_stride, (size_t)K);
-        xplanes_stage(xpt, K, smem + (size_t)tk * per_tok, threadIdx.x, IMMA_THREADS);
+        xplanes_stage(xpt, K, smem + (size_t)tk * per_tok, threadIdx.x, IMMA_THREADS * HALVES);
     }
     float kscale[NT];
 #pragma unroll
@@ -230,10 +232,15 @@ __global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, W
     const bool b2col = bcol && (g & 1) == 0;
     // this lane's token in the accumulators: c (lanes with c >= NT carry sums that are never stored)
     const float2* sx_t = (const float2*)(smem + (size_t)min(c, NT - 1) * per_tok + 3 * (size_t)K);
-    float* comb = (float*)(smem + (size_t)NT * per_tok);  // [matrix][row 16][token 4][accumulator 32], behind the planes
+    // [matrix][row 16][token 4][accumulator 32] per half, behind the planes
+    float* comb = (float*)(smem + (size_t)NT * per_tok) + (size_t)half * NM * IMMA_ROWS * 4 * 32;
     const size_t groups = (n_out + IMMA_ROWS - 1) / IMMA_ROWS;
-    // The planes are staged once per CTA; the CTA then takes groups of 16 rows in turn.
-    for (size_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    auto half_sync = [&] {  // the 256 threads of this half (the halves run on their own, each with its named barrier)
+        if (HALVES == 1) __syncthreads();
+        else asm volatile("bar.sync %0, 256;" ::"r"(1 + half) : "memory");
+    };
+    // The planes are staged once per CTA; each half of the CTA then takes groups of 16 rows in turn.
+    for (size_t grp = (size_t)blockIdx.x * HALVES + half; grp < groups; grp += (size_t)gridDim.x * HALVES) {
         const size_t row0 = grp * IMMA_ROWS;
         const size_t rows_ld[2] = {min(row0 + g, n_out - 1), min(row0 + g + 8, n_out - 1)};  // rows past the end repeat the last one (never stored)
         float acc[NM][2][4];
@@ -308,9 +315,9 @@ __global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, W
 #pragma unroll
                     for (int j = 0; j < 4; j++) comb[(((size_t)m * 16 + g + 8 * r) * 4 + c) * 32 + 4 * warp + j] = acc[m][r][j];
         }
-        __syncthreads();
-        if (threadIdx.x < IMMA_ROWS * NT) {
-            const int r = threadIdx.x / NT, tk = threadIdx.x % NT;
+        half_sync();
+        if (tid < IMMA_ROWS * NT) {
+            const int r = tid / NT, tk = tid % NT;
             float tot[NM];
 #pragma unroll
             for (int m = 0; m < NM; m++) {
@@ -337,7 +344,7 @@ __global__ void __launch_bounds__(IMMA_THREADS) gemv4_imma_kernel(WeightDev w, W
                     *o += tot[0];
             }
         }
-        __syncthreads();  // the accumulators' shared memory is free for the next group
+        half_sync();  // the accumulators' shared memory is free for the next group
     }
 }
 
@@ -708,17 +715,26 @@ static cudaError_t launch_imma_nt(const WeightDev& w, const WeightDev* up, XPlan
                                   bool pdl, NormScale ns) {
     const bool pair = mode == B2_MODE_SILU_PAIR || mode == B2_MODE_GELU_PAIR;
     const bool np2 = xp.np == 2;
-    auto kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2> : gemv4_imma_kernel<F, true, NT, 3>)
-                     : (np2 ? gemv4_imma_kernel<F, false, NT, 2> : gemv4_imma_kernel<F, false, NT, 3>);
     const size_t per_tok = (xplanes_bytes(w.n_in) + 127) / 128 * 128;
-    const size_t smem = per_tok * NT + (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float);
+    const size_t comb = (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float);
+    // planes that leave room for one CTA per SM only: 16 warps in that CTA instead of 8
+    const bool wide = per_tok * NT + comb + 1024 > 112 * 1024 && per_tok * NT + 2 * comb <= 224 * 1024;
+    const size_t smem = per_tok * NT + (wide ? 2 : 1) * comb;
     if (smem > 224 * 1024) return cudaErrorInvalidValue;
+    void (*kern)(WeightDev, WeightDev, XPlanes, float*, int, NormScale, GemvMulti);
+    if (wide)
+        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 2> : gemv4_imma_kernel<F, true, NT, 3, 2>)
+                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 2> : gemv4_imma_kernel<F, false, NT, 3, 2>);
+    else
+        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 1> : gemv4_imma_kernel<F, true, NT, 3, 1>)
+                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 1> : gemv4_imma_kernel<F, false, NT, 3, 1>);
     if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
     const size_t groups = (w.n_out + IMMA_ROWS - 1) / IMMA_ROWS;
     size_t per_sm = (size_t)(224 * 1024) / (smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
-    const size_t grid = std::min(groups, (size_t)sm_count * per_sm);
-    return launch_k(kern, dim3((unsigned)grid), dim3(IMMA_THREADS), smem, st, pdl, w, pair ? *up : w, xp, y, mode, ns, m);
+    const size_t halves = wide ? 2 : 1;
+    const size_t grid = std::min((groups + halves - 1) / halves, (size_t)sm_count * per_sm);
+    return launch_k(kern, dim3((unsigned)grid), dim3((unsigned)(IMMA_THREADS * halves)), smem, st, pdl, w, pair ? *up : w, xp, y, mode, ns, m);
 }
 
 // B2_GEMV_IMMA=0: the several-token 4-bit products on the dp4a kernel (for A/B runs; the results are the same bits).
@@ -742,7 +758,7 @@ cudaError_t launch_gemv_multi(const WeightDev& w, const WeightDev* up, const flo
     const bool f8 = w.fmt == B2_FMT_F8E4M3;
     if (!gemv_multi_fits(w, nt) || mode == B2_MODE_ADD_GATED) return cudaErrorInvalidValue;  // no gate pointer travels here
     const GemvMulti m{f8 ? x_stride : xp_stride, y_stride, ns_stride};
-    const size_t imma_smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 * (size_t)nt + 2 * IMMA_ROWS * 4 * 32 * sizeof(float);
+    const size_t imma_smem = (xplanes_bytes(w.n_in) + 127) / 128 * 128 * (size_t)nt + 2 * IMMA_ROWS * 4 * 32 * sizeof(float);  // (the pair's)
     if (nt >= 2 && imma_enabled() && (w.fmt == B2_FMT_Q4_K || w.fmt == B2_FMT_MLX4) && imma_smem <= 224 * 1024) {  // the integer dots on the tensor cores
         const bool q4k = w.fmt == B2_FMT_Q4_K;
         switch (nt) {
