@@ -200,7 +200,7 @@ constexpr int IMMA_ROWS = 16, IMMA_THREADS = 256;
 
 // HALVES = 2: 16 warps, two groups of 16 rows at a time (for vectors whose planes leave room for one CTA per SM only).
 template <class F, bool PAIR, int NT, int NP, int HALVES>
-__global__ void __launch_bounds__(IMMA_THREADS * HALVES) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
+__global__ void __launch_bounds__(IMMA_THREADS * HALVES, HALVES == 1 ? 2 : 1) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
                                                                   NormScale ns, GemvMulti multi) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NM = PAIR ? 2 : 1;
@@ -249,48 +249,40 @@ __global__ void __launch_bounds__(IMMA_THREADS * HALVES) gemv4_imma_kernel(Weigh
 #pragma unroll
             for (int r = 0; r < 2; r++) acc[m][r][0] = acc[m][r][1] = acc[m][r][2] = acc[m][r][3] = 0.0f;
         for (int b = warp; b < nblk; b += 8) {
-            // the block's loads first, all of them in flight together: two headers and 16 words of nibbles per matrix
-            Q4Regs hd[NM][2];
-            uint32_t wq[NM][2][4][2];  // [matrix][row][group][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
 #pragma unroll
-            for (int m = 0; m < NM; m++)
+            for (int m = 0; m < NM; m++) {  // (a pair: one matrix after the other, so that only one's words are live)
+                // the block's loads first, all of them in flight together: two headers and 16 words of nibbles
+                Q4Regs hd[2];
+                uint32_t wq[2][4][2];  // [row][group][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const uint8_t* blk = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
-                    hd[m][r].hdr = __ldg((const uint4*)blk);
+                    hd[r].hdr = __ldg((const uint4*)blk);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        wq[m][r][j][0] = __ldg((const uint32_t*)(blk + 16 + 32 * j + 4 * c));
-                        wq[m][r][j][1] = __ldg((const uint32_t*)(blk + 32 + 32 * j + 4 * c));
+                        wq[r][j][0] = __ldg((const uint32_t*)(blk + 16 + 32 * j + 4 * c));
+                        wq[r][j][1] = __ldg((const uint32_t*)(blk + 32 + 32 * j + 4 * c));
                     }
                 }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int k0 = b * 256 + 64 * j;
-                // B: bytes 4 c .. 4 c + 3 and 16 + 4 c .. of the block of 32, for the low (k0) and the high (k0 + 32) nibbles' blocks
-                uint32_t bl[2][2], bh[2][2];  // [instruction][register]
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int ka = k0 + 32 * h;
-                    const size_t o0 = ((size_t)swz(ka >> 4) << 4) + 4 * c, o1 = ((size_t)swz((ka >> 4) + 1) << 4) + 4 * c;
-                    uint32_t* dst = h ? &bh[0][0] : &bl[0][0];
-                    dst[0] = bcol ? *(const uint32_t*)(bp1 + o0) : 0u;
-                    dst[1] = bcol ? *(const uint32_t*)(bp1 + o1) : 0u;
-                    dst[2] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o0) : 0u;
-                    dst[3] = (NP == 3 && b2col) ? *(const uint32_t*)(bp2 + o1) : 0u;
-                }
-                const float4 sx = *(const float4*)(sx_t + (k0 >> 5));  // {scale, sum} of the two blocks of this lane's token
-#pragma unroll
-                for (int m = 0; m < NM; m++) {
+                for (int j = 0; j < 4; j++) {
+                    const int k0 = b * 256 + 64 * j;
+                    const float4 sx = *(const float4*)(sx_t + (k0 >> 5));  // {scale, sum} of the two blocks of this lane's token
                     int lo[2], hi[2];
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const uint32_t a[4] = {(wq[m][0][j][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[m][1][j][0] >> (4 * h)) & 0x0F0F0F0Fu,
-                                               (wq[m][0][j][1] >> (4 * h)) & 0x0F0F0F0Fu, (wq[m][1][j][1] >> (4 * h)) & 0x0F0F0F0Fu};
-                        const uint32_t(&bb)[2][2] = h ? bh : bl;
+                        // B: bytes 4 c .. 4 c + 3 and 16 + 4 c .. of the block of 32 (low nibbles: k0, high: k0 + 32)
+                        const int ka = k0 + 32 * h;
+                        const size_t o0 = ((size_t)swz(ka >> 4) << 4) + 4 * c, o1 = ((size_t)swz((ka >> 4) + 1) << 4) + 4 * c;
+                        const uint32_t b10 = bcol ? *(const uint32_t*)(bp1 + o0) : 0u, b11 = bcol ? *(const uint32_t*)(bp1 + o1) : 0u;
+                        const uint32_t a[4] = {(wq[0][j][0] >> (4 * h)) & 0x0F0F0F0Fu, (wq[1][j][0] >> (4 * h)) & 0x0F0F0F0Fu,
+                                               (wq[0][j][1] >> (4 * h)) & 0x0F0F0F0Fu, (wq[1][j][1] >> (4 * h)) & 0x0F0F0F0Fu};
                         int s1[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
-                        imma_16832(s1, a, bb[0][0], bb[0][1]);
-                        if (NP == 3) imma_16832(s2, a, bb[1][0], bb[1][1]);
+                        imma_16832(s1, a, b10, b11);
+                        if (NP == 3) {
+                            const uint32_t b20 = b2col ? *(const uint32_t*)(bp2 + o0) : 0u, b21 = b2col ? *(const uint32_t*)(bp2 + o1) : 0u;
+                            imma_16832(s2, a, b20, b21);
+                        }
                         // columns 2 c, 2 c + 1 of the first instruction = this lane's token, its two planes; column 2 c of the second = the third
                         const int va = NP == 3 ? planes_sum<3>(s1[0], s1[1], s2[0]) : planes_sum<2>(0, s1[0], s1[1]);
                         const int vb = NP == 3 ? planes_sum<3>(s1[2], s1[3], s2[2]) : planes_sum<2>(0, s1[2], s1[3]);
@@ -302,8 +294,8 @@ __global__ void __launch_bounds__(IMMA_THREADS * HALVES) gemv4_imma_kernel(Weigh
                             lo[1] = vb;
                         }
                     }
-                    F::tail(hd[m][0], j, sx, lo[0], hi[0], acc[m][0][j]);
-                    F::tail(hd[m][1], j, sx, lo[1], hi[1], acc[m][1][j]);
+                    F::tail(hd[0], j, sx, lo[0], hi[0], acc[m][0][j]);
+                    F::tail(hd[1], j, sx, lo[1], hi[1], acc[m][1][j]);
                 }
             }
         }
