@@ -198,8 +198,19 @@ __device__ __forceinline__ void imma_16832(int (&c)[4], const uint32_t (&a)[4], 
 
 constexpr int IMMA_ROWS = 16, IMMA_THREADS = 256;
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+constexpr int IMMA_TILE_BYTES = IMMA_ROWS * 144;  // one 256-block of 16 rows, packed
+
 // HALVES = 2: 16 warps, two groups of 16 rows at a time (for vectors whose planes leave room for one CTA per SM only).
-template <class F, bool PAIR, int NT, int NP, int HALVES>
+// RING: every warp brings its next (block, matrix) tile of packed weights into its own two shared-memory buffers with cp.async
+// while it works on the current one (the kernel is bound by the latency of those loads otherwise).
+template <class F, bool PAIR, int NT, int NP, int HALVES, bool RING>
 __global__ void __launch_bounds__(IMMA_THREADS * HALVES, HALVES == 1 ? 2 : 1) gemv4_imma_kernel(WeightDev w, WeightDev w2, XPlanes xp, float* __restrict__ y, int mode,
                                                                   NormScale ns, GemvMulti multi) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -248,20 +259,57 @@ __global__ void __launch_bounds__(IMMA_THREADS * HALVES, HALVES == 1 ? 2 : 1) ge
         for (int m = 0; m < NM; m++)
 #pragma unroll
             for (int r = 0; r < 2; r++) acc[m][r][0] = acc[m][r][1] = acc[m][r][2] = acc[m][r][3] = 0.0f;
+        // RING: tile (b, m) of this warp = the 144 packed bytes of block b of the group's 16 rows of matrix m
+        uint8_t* wbuf = smem + (size_t)NT * per_tok + (size_t)HALVES * NM * IMMA_ROWS * 4 * 32 * sizeof(float) + (size_t)warp * 2 * IMMA_TILE_BYTES;
+        auto issue = [&](int b, int m, int buf) {
+            const uint8_t* wp = m ? w2.p0 : w.p0;
+            for (int q = lane; q < IMMA_ROWS * 9; q += 32) {
+                const int row = q / 9, part = q - row * 9;
+                cp_async_16(wbuf + (size_t)buf * IMMA_TILE_BYTES + row * 144 + part * 16,
+                            wp + (min(row0 + row, n_out - 1) * (size_t)nblk + b) * 144 + part * 16);
+            }
+            cp_async_commit();
+        };
+        int buf = 0;
+        if (RING && warp < nblk) issue(warp, 0, 0);
         for (int b = warp; b < nblk; b += 8) {
 #pragma unroll
             for (int m = 0; m < NM; m++) {  // (a pair: one matrix after the other, so that only one's words are live)
                 // the block's loads first, all of them in flight together: two headers and 16 words of nibbles
                 Q4Regs hd[2];
                 uint32_t wq[2][4][2];  // [row][group][word]: bytes 4 c .. and 16 + 4 c .. of the group's 32
+                if constexpr (RING) {
+                    const int nb = m == NM - 1 ? b + 8 : b, nm = m == NM - 1 ? 0 : m + 1;  // the tile behind this one
+                    if (nb < nblk) {
+                        issue(nb, nm, buf ^ 1);
+                        cp_async_wait<1>();
+                    } else {
+                        cp_async_wait<0>();
+                    }
+                    __syncwarp();  // every lane's copies of this tile have landed
+                    const uint8_t* tile = wbuf + (size_t)buf * IMMA_TILE_BYTES;
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    const uint8_t* blk = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
-                    hd[r].hdr = __ldg((const uint4*)blk);
+                    for (int r = 0; r < 2; r++) {
+                        const uint8_t* blk = tile + (g + 8 * r) * 144;
+                        hd[r].hdr = *(const uint4*)blk;
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        wq[r][j][0] = __ldg((const uint32_t*)(blk + 16 + 32 * j + 4 * c));
-                        wq[r][j][1] = __ldg((const uint32_t*)(blk + 32 + 32 * j + 4 * c));
+                        for (int j = 0; j < 4; j++) {
+                            wq[r][j][0] = *(const uint32_t*)(blk + 16 + 32 * j + 4 * c);
+                            wq[r][j][1] = *(const uint32_t*)(blk + 32 + 32 * j + 4 * c);
+                        }
+                    }
+                    __syncwarp();  // the buffer may be overwritten by the copies issued in the next round
+                    buf ^= 1;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const uint8_t* blk = (m ? w2.p0 : w.p0) + (rows_ld[r] * (size_t)nblk + b) * 144;
+                        hd[r].hdr = __ldg((const uint4*)blk);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            wq[r][j][0] = __ldg((const uint32_t*)(blk + 16 + 32 * j + 4 * c));
+                            wq[r][j][1] = __ldg((const uint32_t*)(blk + 32 + 32 * j + 4 * c));
+                        }
                     }
                 }
 #pragma unroll
@@ -711,15 +759,22 @@ static cudaError_t launch_imma_nt(const WeightDev& w, const WeightDev* up, XPlan
     const size_t comb = (size_t)(pair ? 2 : 1) * IMMA_ROWS * 4 * 32 * sizeof(float);
     // planes that leave room for one CTA per SM only: 16 warps in that CTA instead of 8
     const bool wide = per_tok * NT + comb + 1024 > 112 * 1024 && per_tok * NT + 2 * comb <= 224 * 1024;
-    const size_t smem = per_tok * NT + (wide ? 2 : 1) * comb;
+    // room for the warps' weight buffers beside two CTAs per SM: the cp.async form
+    const size_t ring_bytes = (size_t)8 * 2 * IMMA_TILE_BYTES;
+    static const bool ring_on = env_int("B2_GEMV_IMMA_RING", 1) != 0;
+    const bool ring = ring_on && !wide && per_tok * NT + comb + ring_bytes + 1024 <= 112 * 1024;
+    const size_t smem = per_tok * NT + (wide ? 2 : 1) * comb + (ring ? ring_bytes : 0);
     if (smem > 224 * 1024) return cudaErrorInvalidValue;
     void (*kern)(WeightDev, WeightDev, XPlanes, float*, int, NormScale, GemvMulti);
     if (wide)
-        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 2> : gemv4_imma_kernel<F, true, NT, 3, 2>)
-                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 2> : gemv4_imma_kernel<F, false, NT, 3, 2>);
+        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 2, false> : gemv4_imma_kernel<F, true, NT, 3, 2, false>)
+                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 2, false> : gemv4_imma_kernel<F, false, NT, 3, 2, false>);
+    else if (ring)
+        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 1, true> : gemv4_imma_kernel<F, true, NT, 3, 1, true>)
+                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 1, true> : gemv4_imma_kernel<F, false, NT, 3, 1, true>);
     else
-        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 1> : gemv4_imma_kernel<F, true, NT, 3, 1>)
-                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 1> : gemv4_imma_kernel<F, false, NT, 3, 1>);
+        kern = pair ? (np2 ? gemv4_imma_kernel<F, true, NT, 2, 1, false> : gemv4_imma_kernel<F, true, NT, 3, 1, false>)
+                    : (np2 ? gemv4_imma_kernel<F, false, NT, 2, 1, false> : gemv4_imma_kernel<F, false, NT, 3, 1, false>);
     if (cudaError_t e = ensure_dynamic_smem((const void*)kern, smem); e != cudaSuccess) return e;
     const size_t groups = (w.n_out + IMMA_ROWS - 1) / IMMA_ROWS;
     size_t per_sm = (size_t)(224 * 1024) / (smem + 1024);
