@@ -254,3 +254,30 @@ def test_one_query_head_per_kv_head(backend, hd, kv_f16):
     assert row_err(hp, h1.astype(np.float64)) < 2e-3
     one.close()
     pre.close()
+
+
+def test_prefill_over_fp8_weights(backend):
+    """One layer with every product in FP8 e4m3 with 128 x 128 block scales (config 4's format): the prefill plan multiplies
+    them on the tensor-core GEMM (e4m3 expanded to f16), the one-token plan on its FP8 matrix-vector kernel; both within the
+    FP8 bound of each other."""
+    cfg = dict(n_layers=1, h=256, nh=4, nkv=2, hd=64, inter=512, vocab=512)
+    shapes = {"q": (256, 256), "k": (128, 256), "v": (128, 256), "o": (256, 256), "gate": (512, 256), "up": (512, 256), "down": (256, 512)}
+    rng = np.random.default_rng(97)
+    L = {name: backend.upload(synth.f8_e4m3(n_out, n_in, 1400 + i), n_out, n_in) for i, (name, (n_out, n_in)) in enumerate(shapes.items())}
+    L["ln_pre"] = (1.0 + 0.1 * rng.standard_normal(cfg["h"])).astype(np.float32)
+    L["ln_post"] = (1.0 + 0.1 * rng.standard_normal(cfg["h"])).astype(np.float32)
+    final_norm = (1.0 + 0.1 * rng.standard_normal(cfg["h"])).astype(np.float32)
+    head = backend.upload(synth.f8_e4m3(cfg["vocab"], cfg["h"], 1410), cfg["vocab"], cfg["h"])
+    lc = D.LlamaConfig(eps=1e-5, **cfg)
+    one = D.decode_plan(backend, D.llama_graph(lc, [L], final_norm, head), 256)
+    pre = D.decode_plan_prefill(backend, D.llama_graph(lc, [L], final_norm, head, prefill=True), 256, 140)
+    assert one is not None and pre is not None, backend.last_declined
+    inv_freq = O.rope_inv_freq(cfg["hd"], lc.rope_theta)
+    pos, t = 20, 140
+    fill((one, pre), cfg, pos, 71)
+    xs = rng.standard_normal((t, cfg["h"])).astype(np.float32)
+    h1 = one_by_one(one, pos, xs, inv_freq)
+    hp, _ = pre.step_multi(pos, xs, rope_rows(pos, t, inv_freq))
+    assert row_err(hp, h1.astype(np.float64)) < 4e-3   # two FP8 paths against each other: twice the 2e-3 of an FP8 row
+    one.close()
+    pre.close()
