@@ -946,6 +946,28 @@ def prefill_extras(be, peaks, n_layers=32, tokens=2048, kv_f16=False):
     return res
 
 
+def run_with_deadline(name, fn, seconds, stuck, rank=0):
+    """fn() in a worker thread: its result, {"error": ...} if it raised, or, if it is still running after `seconds`, an error
+    entry and `name` appended to `stuck` (the thread is a daemon: the caller prints what it has and leaves with os._exit)."""
+    box = {}
+
+    def work():
+        try:
+            box["out"] = fn()
+        except Exception as e:
+            box["out"] = {"error": str(e)}
+            print(f"[bench rank {rank}] {name} failed: {e}", file=sys.stderr, flush=True)
+
+    th = threading.Thread(target=work, daemon=True)
+    th.start()
+    th.join(seconds)
+    if th.is_alive():
+        stuck.append(name)
+        print(f"[bench rank {rank}] {name} did not finish within {seconds} s", file=sys.stderr, flush=True)
+        return {"error": f"did not finish within {seconds} s (a rank failed inside a collective step)"}
+    return box["out"]
+
+
 def run_b200(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -1154,25 +1176,12 @@ def run_b200(args, rank, world, local_rank):
     stuck = []
 
     def collective_section(name, fn, seconds=300):
-        box = {}
+        def on_device():
+            torch.cuda.set_device(local_rank)
+            with torch.cuda.stream(stream):
+                return fn()
 
-        def work():
-            try:
-                torch.cuda.set_device(local_rank)
-                with torch.cuda.stream(stream):
-                    box["out"] = fn()
-            except Exception as e:
-                box["out"] = {"error": str(e)}
-                print(f"[bench rank {rank}] {name} failed: {e}", file=sys.stderr, flush=True)
-
-        th = threading.Thread(target=work, daemon=True)
-        th.start()
-        th.join(seconds)
-        if th.is_alive():
-            stuck.append(name)
-            print(f"[bench rank {rank}] {name} did not finish within {seconds} s", file=sys.stderr, flush=True)
-            return {"error": f"did not finish within {seconds} s (a rank failed inside a collective step)"}
-        return box["out"]
+        return run_with_deadline(name, on_device, seconds, stuck, rank)
 
     dec_tp = None
     if world > 1 and args.section == "all":   # collective: every rank runs the tensor-parallel decode plan
